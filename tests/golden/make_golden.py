@@ -1,0 +1,221 @@
+"""Regenerate tests/golden/*.npz from the bmx reference itself.
+
+Run by hand in a container that has the bmx source tree:
+
+    python tests/golden/make_golden.py --reference /path/to/bmx
+
+It imports the reference's own modules (torch, CPU), feeds them small seeded inputs and
+stores inputs and outputs.  The fixtures pin `oracle/bmx_oracle.py` and give the GPU
+parity tests reference-made vectors that travel without the reference tree.  The only
+module the reference needs that this image lacks is `tensorly` (pulled in by an
+unrelated package import); three no-op stand-ins are created in a temp dir for it.
+"""
+
+from __future__ import annotations
+
+import argparse
+import math
+import os
+import sys
+import tempfile
+
+import numpy as np
+
+
+def _stub_tensorly() -> str:
+    root = tempfile.mkdtemp(prefix="tl_stub_")
+    for sub, body in (
+        ("", "def set_backend(*a, **k):\n    pass\n"),
+        ("decomposition", "def parafac(*a, **k): raise NotImplementedError\n"
+                          "def partial_tucker(*a, **k): raise NotImplementedError\n"
+                          "def tucker(*a, **k): raise NotImplementedError\n"),
+        ("tenalg", "def multi_mode_dot(*a, **k): raise NotImplementedError\n"),
+    ):
+        d = os.path.join(root, "tensorly", sub)
+        os.makedirs(d, exist_ok=True)
+        with open(os.path.join(d, "__init__.py"), "w") as f:
+            f.write(body)
+    return root
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
+    args = ap.parse_args()
+    sys.path[:0] = [_stub_tensorly(), os.path.join(args.reference, "src")]
+
+    import torch
+    from transformers import LlamaConfig
+
+    from bmx.cache import chunked_attention as ca
+    from bmx.cache import codecs, spectral
+    from bmx.cache import triton_dequant_attention as tda
+    from bmx.cache.rope import rope_cos_sin
+    from bmx.cache.streaming import compute_flush_schedule
+    from bmx.quant.hadamard import fwht, orthogonalize
+    from bmx.quant.rtn import rtn_quantize_packed
+
+    # The reference's run-time Lloyd codebook depends on torch's intra-op thread count in the last
+    # ulp (1 and 2 threads each move one level by one ulp; 4 and 8 agree), so fix it at 8.
+    torch.set_num_threads(8)
+    npy = lambda t: t.detach().cpu().numpy()  # noqa: E731
+
+    def gen(seed):
+        return torch.Generator().manual_seed(seed)
+
+    # ---- constants -------------------------------------------------------
+    out = {
+        "cb2": npy(codecs.gaussian_codebook(2)),
+        "cb3": npy(codecs.gaussian_codebook(3)),
+        "signs_d128_s0": npy(codecs._hadamard_signs(128, 0)),
+        "signs_d128_s1": npy(codecs._hadamard_signs(128, 1)),
+        "signs_d64_s0": npy(codecs._hadamard_signs(64, 0)),
+        "flush_kat": np.array(
+            [[S, W, g, compute_flush_schedule(S, W, g)]
+             for S, W, g in ((100, 32, 16), (40, 32, 16), (20, 32, 16), (160, 32, 1),
+                             (4224, 128, 128), (255, 128, 128), (256, 128, 128), (16512, 128, 64))]
+        ),
+    }
+    np.savez_compressed(os.path.join(args.out, "consts.npz"), **out)
+
+    # ---- codec vectors: h_kv = 2, d = 128, one 128-token page -------------
+    h_kv, d, S = 2, 128, 128
+    C = h_kv * d
+    out = {}
+    M = torch.randn(S, C, generator=gen(11))
+    M[:, :4] *= 8.0  # outlier channels, as in the RTN config
+    out["M"] = npy(M)
+    for arm, bits, g in (("rtn_token", 2, 32), ("rtn_token", 4, 32), ("rtn_channel", 4, 32),
+                         ("rtn_channel", 2, 64), ("rtn_token", 4, 64)):
+        p, bpe = codecs.quantize_packed(arm, M, bits=bits, group=g)
+        tag = f"{arm}_b{bits}_g{g}"
+        out[tag + "_Q"] = npy(p["Q_int"])
+        out[tag + "_scale"] = npy(p["scale"])
+        out[tag + "_deq"] = npy(codecs.dequant_packed(arm, p, group=g))
+        out[tag + "_bpe"] = np.float64(bpe)
+    for bits in (2, 3):
+        p, bpe = codecs.quantize_packed("turboquant_mse_perhead", M, bits=bits, seed=0, h_heads=h_kv)
+        out[f"tq_b{bits}_idx"] = npy(p["indices"])
+        out[f"tq_b{bits}_norms"] = npy(p["norms"])
+        out[f"tq_b{bits}_deq"] = npy(codecs.dequant_packed("turboquant_mse_perhead", p, seed=0))
+        out[f"tq_b{bits}_bpe"] = np.float64(bpe)
+    # low-rank keys: frozen cross-head basis (C, r) and a per-head basis run per head
+    for rank in (16, 32):
+        Vb = orthogonalize(torch.randn(C, rank, generator=gen(12 + rank)))
+        coef = torch.randn(S, rank, generator=gen(13)) * torch.arange(1, rank + 1).float() ** -1.5
+        Mk = coef @ Vb.T + 0.1 * torch.randn(S, C, generator=gen(14))
+        Us = Mk @ Vb
+        p, bpe = codecs.quantize_packed("lowrank_rtn_channel", Mk, bits=3, group=64, rank=rank,
+                                        svd_factors=(Us, Vb))
+        tag = f"lr{rank}"
+        out[tag + "_M"], out[tag + "_Vb"], out[tag + "_Us_in"] = npy(Mk), npy(Vb), npy(Us)
+        for k in ("Us", "V", "res_Q_int", "res_scale"):
+            out[f"{tag}_{k}"] = npy(p[k])
+        out[tag + "_deq"] = npy(codecs.dequant_packed("lowrank_rtn_channel", p, group=64))
+        out[tag + "_bpe"] = np.float64(bpe)
+    x = torch.randn(5, 128, generator=gen(15))
+    out["fwht_in"], out["fwht_out"] = npy(x), npy(fwht(x))
+    # bit packing over the full code ranges
+    u2 = torch.randint(0, 4, (8, 64), generator=gen(16))
+    u4 = torch.randint(0, 16, (8, 64), generator=gen(17))
+    s3 = torch.randint(-4, 4, (8, 64), generator=gen(18))
+    s4 = torch.randint(-8, 8, (8, 64), generator=gen(19))
+    out["u2"], out["u2_packed"] = npy(u2).astype(np.int16), npy(tda.pack_codes(u2, 2))
+    out["u4"], out["u4_packed"] = npy(u4).astype(np.int16), npy(tda.pack_codes(u4, 4))
+    out["s3"], out["s3_packed"] = npy(s3).astype(np.int8), npy(tda.pack_signed_codes(s3, 3))
+    out["s4"], out["s4_packed"] = npy(s4).astype(np.int8), npy(tda.pack_signed_codes(s4, 4))
+    np.savez_compressed(os.path.join(args.out, "codec.npz"), **out)
+
+    # ---- decode vectors: 3 pages + fp16 tail, G = 4 -----------------------
+    G, n_pages, PAGE, tail_len = 4, 3, 128, 37
+    T = n_pages * PAGE
+    cfg = LlamaConfig(hidden_size=h_kv * G * d, num_attention_heads=h_kv * G, num_key_value_heads=h_kv,
+                      head_dim=d, rope_theta=500000.0, max_position_embeddings=1 << 17)
+    cos32, sin32 = rope_cos_sin(cfg, T + tail_len)
+    cos16, sin16 = cos32.half(), sin32.half()
+    # both halves of the head share the angle: keep the first d/2 columns only
+    out = {"rope_cos_f32": npy(cos32[:, : d // 2]), "rope_sin_f32": npy(sin32[:, : d // 2])}
+    q = torch.randn(h_kv * G, 1, d, generator=gen(21)) / math.sqrt(d)
+    scale = 1.0 / math.sqrt(d)
+    out["q"] = npy(q)
+    # k2b, cross-head basis (reference default) with rank 16, and per-head rank 32
+    Vb = orthogonalize(torch.randn(C, 16, generator=gen(22)))
+    k_pre = (torch.randn(T, 16, generator=gen(23)) * torch.arange(1, 17).float() ** -1.5) @ Vb.T
+    k_pre = (k_pre + 0.1 * torch.randn(T, C, generator=gen(24))).half().float()
+    v = torch.randn(T, C, generator=gen(25)).half().float()
+    k_tail = torch.randn(h_kv, tail_len, d, generator=gen(26)).half()
+    v_tail = torch.randn(h_kv, tail_len, d, generator=gen(27)).half()
+    out.update(k2b_Vb=npy(Vb), k2b_k_pre=npy(k_pre), k2b_v=npy(v), k_tail=npy(k_tail), v_tail=npy(v_tail))
+    kb, vb = [], []
+    for p0 in range(0, T, PAGE):
+        Mk, Mv = k_pre[p0:p0 + PAGE], v[p0:p0 + PAGE]
+        kp, _ = codecs.quantize_packed("lowrank_rtn_channel", Mk, bits=3, group=64, rank=16,
+                                       svd_factors=(Mk @ Vb, Vb))
+        vp, _ = codecs.quantize_packed("turboquant_mse_perhead", Mv, bits=2, seed=0, h_heads=h_kv)
+        kb.append((kp, p0, p0 + PAGE))
+        vb.append((vp, p0, p0 + PAGE))
+    st = tda.build_kv_stacked_k2b(kb, vb, max_blocks=n_pages, h_kv=h_kv, blk_size=PAGE, d=d,
+                                  device="cpu", pack_v=True, pack_k=True, k_bits=3)
+    for k, t in st.items():
+        if torch.is_tensor(t):
+            out["k2b_stack_" + k] = npy(t)
+    kw = dict(k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead", group=64, seed=0,
+              k_pre_rope=True, rope_cos=cos16, rope_sin=sin16, k_tail=k_tail, v_tail=v_tail,
+              n_q_groups=G, scale=scale, v_group=64, v_seed=0)
+    out["k2b_out_chunked"] = npy(ca.chunked_dequant_attention(q, kb, vb, **kw))
+    out["k2b_out_naive"] = npy(ca.naive_dense_attention(q, kb, vb, **kw))
+    kw_nt = dict(kw, k_tail=None, v_tail=None)
+    out["k2b_out_chunked_notail"] = npy(ca.chunked_dequant_attention(q, kb, vb, **kw_nt))
+    # RTN pair of the first BASELINE config: K rtn_channel 4b, V rtn_token 2b, group 32, post-RoPE K
+    k_post = torch.randn(T, C, generator=gen(28))
+    k_post[:, [0, 1, 2, 3, d, d + 1, d + 2, d + 3]] *= 8.0
+    k_post = k_post.half().float()
+    out["rtn_k"] = npy(k_post)
+    kb2, vb2, kb3 = [], [], []
+    for p0 in range(0, T, PAGE):
+        kp, _ = codecs.quantize_packed("rtn_channel", k_post[p0:p0 + PAGE], bits=4, group=32)
+        kp3, _ = codecs.quantize_packed("rtn_token", k_post[p0:p0 + PAGE], bits=4, group=32)
+        vp, _ = codecs.quantize_packed("rtn_token", v[p0:p0 + PAGE], bits=2, group=32)
+        kb2.append((kp, p0, p0 + PAGE))
+        kb3.append((kp3, p0, p0 + PAGE))
+        vb2.append((vp, p0, p0 + PAGE))
+    kw2 = dict(k_arm="rtn_channel", v_arm="rtn_token", group=32, seed=0, k_pre_rope=False,
+               rope_cos=None, rope_sin=None, k_tail=k_tail, v_tail=v_tail, n_q_groups=G, scale=scale)
+    out["rtn_ct_out_chunked"] = npy(ca.chunked_dequant_attention(q, kb2, vb2, **kw2))
+    kw3 = dict(kw2, k_arm="rtn_token")
+    out["rtn_tt_out_chunked"] = npy(ca.chunked_dequant_attention(q, kb3, vb2, **kw3))
+    kc, vc, ks, vs = tda.build_kv_stacked_packed(kb3, vb2, max_blocks=n_pages, h_kv=h_kv,
+                                                 blk_size=PAGE, d=d, group=32, device="cpu")
+    out.update(rtn_stack_kc=npy(kc), rtn_stack_vc=npy(vc), rtn_stack_ks=npy(ks), rtn_stack_vs=npy(vs))
+    # tail partial + merge
+    acc_t, m_t, l_t = tda._tail_partial(q.squeeze(1).view(h_kv, G, d), k_tail, v_tail, scale)
+    out.update(tail_acc=npy(acc_t), tail_m=npy(m_t), tail_l=npy(l_t))
+    np.savez_compressed(os.path.join(args.out, "decode.npz"), **out)
+
+    # ---- spectral (K4) vectors: one head-sized pack, C = 128 ---------------
+    Cs = 128
+    E = orthogonalize(torch.randn(Cs, Cs, generator=gen(31)))
+    lam = torch.arange(1, Cs + 1).float() ** -1.2
+    tiers = (0, 2, 3, 4, 5, 6, 8)
+    bits_pc = codecs.allocate_bits_from_variance(lam, 2.5, tiers) if hasattr(
+        codecs, "allocate_bits_from_variance") else None
+    if bits_pc is None:
+        raise SystemExit("reference lacks allocate_bits_from_variance")
+    bits_pc = torch.as_tensor(bits_pc).long()
+    dec8 = spectral.int8_decoder_roundtrip(E.clone(), bits_pc)
+    pack = spectral.SpectralPack(enc=E, dec=dec8, lam=lam, bits=bits_pc, group=64, tiers=tiers, budget=2.5)
+    Y = torch.randn(128, Cs, generator=gen(32)) * lam.sqrt()
+    Ms = Y @ E.T
+    packed, bpe = spectral.spectral_quantize_packed(Ms, pack, mse_scale=True)
+    out = {"E": npy(E), "dec8": npy(dec8), "lam": npy(lam), "bits": npy(bits_pc), "M": npy(Ms),
+           "deq": npy(spectral.spectral_dequant_packed(packed, pack)), "bpe": np.float64(bpe)}
+    for k, t in packed.items():
+        out["p_" + k] = npy(t)
+    np.savez_compressed(os.path.join(args.out, "spectral.npz"), **out)
+    for f in ("consts", "codec", "decode", "spectral"):
+        print(f, os.path.getsize(os.path.join(args.out, f + ".npz")))
+
+
+if __name__ == "__main__":
+    main()
