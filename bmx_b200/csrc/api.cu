@@ -1,0 +1,116 @@
+// Library plumbing (version, last-error string, launch check) and the standalone bit-packing
+// kernels of the C ABI.
+#include <cstdarg>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace bmxk {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return BMXK_ERR_CUDA;
+  }
+  return BMXK_OK;
+}
+
+// One thread per output byte.  Unsigned codes, 8/bits per byte, code c at bit bits*(c % per_byte).
+__global__ void pack_u_kernel(const int16_t* __restrict__ codes, uint8_t* __restrict__ packed, int64_t n_bytes,
+                              int bits) {
+  const int per = 8 / bits;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t b = 0;
+    for (int k = 0; k < per; ++k) b |= (uint32_t)((uint8_t)codes[i * per + k]) << (bits * k);
+    packed[i] = (uint8_t)b;
+  }
+}
+__global__ void unpack_u_kernel(const uint8_t* __restrict__ packed, int16_t* __restrict__ codes, int64_t n_bytes,
+                                int bits) {
+  const int per = 8 / bits;
+  const uint32_t mask = (1u << bits) - 1u;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t b = packed[i];
+    for (int k = 0; k < per; ++k) codes[i * per + k] = (int16_t)((b >> (bits * k)) & mask);
+  }
+}
+// Signed codes as two's-complement nibbles, low nibble first.
+__global__ void pack_s4_kernel(const int8_t* __restrict__ codes, uint8_t* __restrict__ packed, int64_t n_bytes) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t lo = (uint32_t)codes[2 * i] & 0xF, hi = (uint32_t)codes[2 * i + 1] & 0xF;
+    packed[i] = (uint8_t)(lo | (hi << 4));
+  }
+}
+__global__ void unpack_s4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ codes, int64_t n_bytes) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+    const int b = packed[i];
+    codes[2 * i] = (int8_t)(((b & 0xF) ^ 8) - 8);
+    codes[2 * i + 1] = (int8_t)((((b >> 4) & 0xF) ^ 8) - 8);
+  }
+}
+
+static inline int grid_for(int64_t n, int block) {
+  int64_t g = (n + block - 1) / block;
+  const int64_t cap = 148 * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace bmxk
+
+using namespace bmxk;
+
+extern "C" {
+
+int bmxk_version(void) { return 100; }
+const char* bmxk_last_error(void) { return g_err; }
+
+int bmxk_pack_u(const int16_t* codes, uint8_t* packed, int64_t rows, int64_t C, int bits, void* stream) {
+  BMXK_REQUIRE(bits == 2 || bits == 4, "bmxk_pack_u: bits must be 2 or 4 (got %d)", bits);
+  BMXK_REQUIRE(rows >= 0 && C >= 0 && C % (8 / bits) == 0, "bmxk_pack_u: C=%lld must be a multiple of %d",
+               (long long)C, 8 / bits);
+  const int64_t n = rows * C * bits / 8;
+  if (n == 0) return BMXK_OK;
+  BMXK_REQUIRE(codes && packed, "bmxk_pack_u: null pointer");
+  pack_u_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(codes, packed, n, bits);
+  return check_launch("bmxk_pack_u");
+}
+int bmxk_unpack_u(const uint8_t* packed, int16_t* codes, int64_t rows, int64_t C, int bits, void* stream) {
+  BMXK_REQUIRE(bits == 2 || bits == 4, "bmxk_unpack_u: bits must be 2 or 4 (got %d)", bits);
+  BMXK_REQUIRE(rows >= 0 && C >= 0 && C % (8 / bits) == 0, "bmxk_unpack_u: C=%lld must be a multiple of %d",
+               (long long)C, 8 / bits);
+  const int64_t n = rows * C * bits / 8;
+  if (n == 0) return BMXK_OK;
+  BMXK_REQUIRE(codes && packed, "bmxk_unpack_u: null pointer");
+  unpack_u_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(packed, codes, n, bits);
+  return check_launch("bmxk_unpack_u");
+}
+int bmxk_pack_s4(const int8_t* codes, uint8_t* packed, int64_t rows, int64_t N, int bits, void* stream) {
+  BMXK_REQUIRE(bits >= 1 && bits <= 4, "bmxk_pack_s4: bits must be in [1,4] (got %d)", bits);
+  BMXK_REQUIRE(rows >= 0 && N >= 0 && N % 2 == 0, "bmxk_pack_s4: N=%lld must be even", (long long)N);
+  const int64_t n = rows * N / 2;
+  if (n == 0) return BMXK_OK;
+  BMXK_REQUIRE(codes && packed, "bmxk_pack_s4: null pointer");
+  pack_s4_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(codes, packed, n);
+  return check_launch("bmxk_pack_s4");
+}
+int bmxk_unpack_s4(const uint8_t* packed, int8_t* codes, int64_t rows, int64_t N, int bits, void* stream) {
+  BMXK_REQUIRE(bits >= 1 && bits <= 4, "bmxk_unpack_s4: bits must be in [1,4] (got %d)", bits);
+  BMXK_REQUIRE(rows >= 0 && N >= 0 && N % 2 == 0, "bmxk_unpack_s4: N=%lld must be even", (long long)N);
+  const int64_t n = rows * N / 2;
+  if (n == 0) return BMXK_OK;
+  BMXK_REQUIRE(codes && packed, "bmxk_unpack_s4: null pointer");
+  unpack_s4_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(packed, codes, n);
+  return check_launch("bmxk_unpack_s4");
+}
+
+}  // extern "C"

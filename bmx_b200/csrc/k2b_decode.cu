@@ -1,0 +1,781 @@
+// k2b split-KV decode for sm_100a: a persistent, warp-specialised kernel that streams packed pages
+// HBM -> shared memory with 1-D bulk async copies (one producer warp, an mbarrier ring) and has
+// eight consumer warps dequantize in registers and feed mma.sync, plus the small kernel that merges
+// the per-CTA partial states, attends over the fp16 recent window and undoes the value rotation.
+//
+// Work unit: a "tile" of 128 consecutive tokens of one (sequence, KV head).  All tiles of all
+// (sequence, head) pairs form one flat list that is cut into equal contiguous ranges, one per CTA
+// (grid = number of SMs), so every SM streams the same number of bytes whatever the batch and the
+// context lengths are.  A CTA emits one partial (max, sum, accumulator) per (sequence, head) range
+// it touches; the merge kernel combines them.
+//
+// Consumer warp w owns token rows 16w..16w+15 of every tile.  Per tile it
+//   1. loads its low-rank coefficients as mma A fragments (ldmatrix) and computes
+//        K_pre = coef x basis^T + residual      (mma m16n8k16, fp16 accumulate; the residual,
+//        nibble -> half2 by one LOP3 + one exact fix-up, times its fp16 scale, is the C operand)
+//   2. rotates K_pre by the token's offset INSIDE the tile (cos/sin of those 2 offsets live in
+//        registers for the whole kernel); the tile's base rotation is applied to q instead,
+//        once per tile, by the producer warp:  q . R(t0+o) k  =  (R(-t0) q) . (R(o) k)
+//   3. scores S^T = q_rot x K^T (mma, fp32 accumulate) -- the K accumulators are already laid out
+//        as the B operand, so nothing moves;  online softmax in base 2 with a lazy rescale
+//   4. values: 2-bit codes -> fp16 codebook levels with byte-permute lookups, straight into A
+//        fragments; O^T += V^T x (p * norm) (mma).  The 128-point Hadamard and the signs are
+//        applied once per (head, query) in the merge kernel, since they are linear in V.
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace bmxk {
+
+constexpr int DEC_CONSUMER_WARPS = 8;
+constexpr int DEC_THREADS = (DEC_CONSUMER_WARPS + 4) * 32;  // + one producer warpgroup (one warp of it works)
+constexpr int TILE_TOKENS = 128;
+constexpr int PART_STRIDE = 130;  // per query head: max (log2 units), sum, 128 accumulators
+constexpr int MAX_BH = 4096;      // (sequence, head) pairs per call
+
+struct K2bDecodeParams {
+  K2bGeom g;
+  const __half* q;
+  const uint8_t* pages;
+  const __half* coefs;
+  const __half* basis16;
+  const int32_t* page_table;
+  int table_stride;
+  const int32_t* n_pages;
+  int batch;
+  const __half* rope_cos;
+  const __half* rope_sin;
+  int64_t pos_offset;
+  uint32_t lut_lo, lut_hi;
+  float lut_alpha, lut_beta;
+  float scale_log2;  // softmax scale * log2(e)
+  float* part;       // (grid + batch*h_kv, n_q_groups, PART_STRIDE)
+  int32_t* status;
+  int n_stages;
+};
+
+// Tiles per (sequence, head) and the flat decomposition, recomputed identically by every CTA of both
+// kernels from the device-resident page counts.
+struct Decomp {
+  int total;   // tiles over all (sequence, head)
+  int per_cta; // tiles per CTA (ceil)
+};
+
+__device__ __forceinline__ int tiles_of(int n_pages, int page) { return (n_pages * page + TILE_TOKENS - 1) / TILE_TOKENS; }
+
+// cum[b] = tiles of sequences < b, times h_kv.  Filled by one warp; cum has batch + 1 entries.
+__device__ __forceinline__ void fill_cum(int* cum, const int32_t* n_pages, int batch, int h_kv, int page, int lane) {
+  int run = 0;
+  for (int b0 = 0; b0 < batch; b0 += 32) {
+    const int b = b0 + lane;
+    int v = (b < batch) ? tiles_of(n_pages[b], page) * h_kv : 0;
+    int incl = v;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, m);
+      if (lane >= m) incl += o;
+    }
+    if (b < batch) cum[b] = run + incl - v;
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) cum[batch] = run;
+}
+
+__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy was lost; report and leave
+      if (atomicCAS(status, 0, 1) == 0) {
+        status[1] = blockIdx.x;
+        status[2] = where;
+      }
+      return false;
+    }
+  }
+  return true;
+}
+
+template <int RANK, int PAGE>
+__global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDecodeParams p) {
+  constexpr int KS = RANK / 16;               // k-steps of the low-rank contraction
+  constexpr int PAGES_PER_TILE = TILE_TOKENS / PAGE;
+  constexpr int WR_PER_PAGE = PAGE / 16;
+  constexpr int COEF_TILE_BYTES = TILE_TOKENS * RANK * 2;
+  constexpr int COEF_PAGE_BYTES = PAGE * RANK * 2;
+  constexpr int QROT_BYTES = 8 * 4 * 8 * 8;   // [query row 0..7][t][k-step][2 regs] uint32
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  const K2bGeom g = p.g;
+  const int G = g.n_q_groups;
+  const int PB = k2b_page_block_bytes(PAGE, g.group);
+  const int STAGE_BYTES = COEF_TILE_BYTES + PAGES_PER_TILE * PB + QROT_BYTES;
+  const int n_stages = p.n_stages;
+
+  uint8_t* stage0 = smem;
+  float* red = reinterpret_cast<float*>(smem + (size_t)n_stages * STAGE_BYTES);  // [8 warps][8 q][128] + m/l/pn
+  float* red_m = red + DEC_CONSUMER_WARPS * 8 * HEAD_DIM;                         // [8][8]
+  float* red_l = red_m + 64;
+  float* red_pn = red_l + 64;
+  float* q_sm = red_pn + 64;                                                      // [8][128] producer's copy of q
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_sm + 8 * HEAD_DIM);
+  uint64_t* empty = full + 16;
+  int* cum = reinterpret_cast<int*>(empty + 16);                                  // [batch + 1]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, t4 = lane & 3;
+
+  if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, PAGE, lane);
+  if (tid == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], DEC_CONSUMER_WARPS);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  const int total = cum[p.batch];
+  const int per_cta = (total + gridDim.x - 1) / gridDim.x;
+  const int f_begin = min(total, (int)blockIdx.x * per_cta);
+  const int f_end = min(total, f_begin + per_cta);
+  if (f_begin >= f_end) return;
+
+  // locate the sequence of the first tile
+  int b = 0;
+  while (cum[b + 1] <= f_begin) ++b;
+
+  if (warp >= DEC_CONSUMER_WARPS) {
+    // ===================== producer warpgroup =====================
+    // Hand most of this warpgroup's registers to the consumers; only its first warp does work.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp != DEC_CONSUMER_WARPS) return;
+    // zero the query rows beyond G in every stage once (their scores are never read)
+    for (int s = 0; s < n_stages; ++s) {
+      uint32_t* qr = reinterpret_cast<uint32_t*>(stage0 + (size_t)s * STAGE_BYTES + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
+      for (int i = lane; i < QROT_BYTES / 4; i += 32) qr[i] = 0u;
+    }
+    int cur_bh = -1;
+    int it = 0;
+    for (int f = f_begin; f < f_end; ++f, ++it) {
+      while (cum[b + 1] <= f) ++b;
+      const int tiles_b = tiles_of(p.n_pages[b], PAGE);
+      const int rel = f - cum[b];
+      const int h = rel / tiles_b, j = rel % tiles_b;
+      const int bh = b * g.h_kv + h;
+      if (bh != cur_bh) {
+        cur_bh = bh;
+        const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
+        __syncwarp();
+        for (int i = lane; i < G * HEAD_DIM; i += 32) q_sm[i] = __half2float(qsrc[i]) * p.scale_log2;
+        __syncwarp();
+      }
+      const int s = it % n_stages;
+      if (!wait_or_flag(&empty[s], ((it / n_stages) & 1) ^ 1, p.status, 1)) return;
+      uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+      // q rotated back by the tile's base position
+      {
+        const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
+        __half* qr = reinterpret_cast<__half*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int c = lane + 32 * jj;  // pair (c, c + 64)
+          const float cs = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
+          const float sn = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
+          for (int qi = 0; qi < G; ++qi) {
+            const float x1 = q_sm[qi * HEAD_DIM + c], x2 = q_sm[qi * HEAD_DIM + c + 64];
+            const float y1 = x1 * cs + x2 * sn, y2 = x2 * cs - x1 * sn;
+            // channel ch -> k-step ch/16, register (ch%16)/8, t = (ch%8)/2, e = ch%2
+            const int ks1 = c >> 4, r1 = (c >> 3) & 1, tt = (c & 7) >> 1, e = c & 1;
+            const int ks2 = ks1 + 4;
+            qr[(((qi * 4 + tt) * 8 + ks1) * 2 + r1) * 2 + e] = __float2half_rn(y1);
+            qr[(((qi * 4 + tt) * 8 + ks2) * 2 + r1) * 2 + e] = __float2half_rn(y2);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const int np = p.n_pages[b];
+        const int pg0 = j * PAGES_PER_TILE;
+        const int npg = min(PAGES_PER_TILE, np - pg0);
+        const int chd = (g.n_coef_heads == 1) ? 0 : h;
+        mbar_arrive_expect_tx(&full[s], (uint32_t)(npg * (COEF_PAGE_BYTES + PB)));
+        for (int k = 0; k < npg; ++k) {
+          const int slot = p.page_table[(int64_t)b * p.table_stride + pg0 + k];
+          bulk_g2s(st + k * COEF_PAGE_BYTES,
+                   reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_PAGE_BYTES,
+                   COEF_PAGE_BYTES, &full[s]);
+          bulk_g2s(st + COEF_TILE_BYTES + k * PB, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &full[s]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ===================== consumer warps =====================
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+  // loop-invariant rotation of the two token rows this lane owns (offsets inside the tile)
+  uint32_t cosr[2][8], sinr[2][8];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int dlt = 16 * warp + 8 * c + gq;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      cosr[c][n] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)dlt * HEAD_DIM + 8 * n + 2 * t4);
+      sinr[c][n] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)dlt * HEAD_DIM + 8 * n + 2 * t4);
+    }
+  }
+  uint32_t Bb[16][KS][2];
+  float O[8][4];
+  // query rows beyond the group size keep a finite maximum so that their (unused) lanes stay finite
+  float m_run = (gq < G) ? -INFINITY : 0.f, l_run = 0.f, pn_run = 0.f;
+  int cur_bh = -1, cur_b = 0, cur_h = 0;
+  const int sub_page = warp / WR_PER_PAGE, wr = warp % WR_PER_PAGE;
+  const int grp = (16 * wr) / g.group;
+  const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
+  const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+  const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
+
+  auto flush = [&](int b_, int h_) {
+    // reduce over the 4 lanes of a quad, then over the 8 warps through shared memory
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    pn_run += __shfl_xor_sync(0xffffffffu, pn_run, 1);
+    pn_run += __shfl_xor_sync(0xffffffffu, pn_run, 2);
+    if (t4 == 0) {
+      red_m[warp * 8 + gq] = m_run;
+      red_l[warp * 8 + gq] = l_run;
+      red_pn[warp * 8 + gq] = pn_run;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      float* o = red + (warp * 8) * HEAD_DIM;
+      o[(2 * t4) * HEAD_DIM + 16 * mt + gq] = O[mt][0];
+      o[(2 * t4 + 1) * HEAD_DIM + 16 * mt + gq] = O[mt][1];
+      o[(2 * t4) * HEAD_DIM + 16 * mt + gq + 8] = O[mt][2];
+      o[(2 * t4 + 1) * HEAD_DIM + 16 * mt + gq + 8] = O[mt][3];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMER_WARPS * 32));
+    float* dst = p.part + ((int64_t)(blockIdx.x + b_ * g.h_kv + h_) * G) * PART_STRIDE;
+    for (int o = tid; o < G * HEAD_DIM; o += DEC_CONSUMER_WARPS * 32) {
+      const int qi = o / HEAD_DIM, ch = o % HEAD_DIM;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < DEC_CONSUMER_WARPS; ++w) M = fmaxf(M, red_m[w * 8 + qi]);
+      float acc = 0.f, l = 0.f, pn = 0.f;
+#pragma unroll
+      for (int w = 0; w < DEC_CONSUMER_WARPS; ++w) {
+        const float mw = red_m[w * 8 + qi];
+        const float f = (mw == -INFINITY) ? 0.f : ex2_approx(mw - M);
+        acc += red[(w * 8 + qi) * HEAD_DIM + ch] * f;
+        l += red_l[w * 8 + qi] * f;
+        pn += red_pn[w * 8 + qi] * f;
+      }
+      dst[qi * PART_STRIDE + 2 + ch] = p.lut_alpha * pn + p.lut_beta * acc;
+      if (ch == 0) {
+        dst[qi * PART_STRIDE + 0] = M;
+        dst[qi * PART_STRIDE + 1] = l;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMER_WARPS * 32));
+  };
+
+  int it = 0;
+  bool dead = false;
+  for (int f = f_begin; f < f_end; ++f, ++it) {
+    while (cum[b + 1] <= f) ++b;
+    const int np = p.n_pages[b];
+    const int tiles_b = tiles_of(np, PAGE);
+    const int rel = f - cum[b];
+    const int h = rel / tiles_b, j = rel % tiles_b;
+    const int bh = b * g.h_kv + h;
+    if (bh != cur_bh) {
+      if (cur_bh >= 0) flush(cur_b, cur_h);
+      cur_bh = bh, cur_b = b, cur_h = h;
+      m_run = (gq < G) ? -INFINITY : 0.f, l_run = 0.f, pn_run = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) O[mt][0] = O[mt][1] = O[mt][2] = O[mt][3] = 0.f;
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const __half* bp = p.basis16 + ((int64_t)h * HEAD_DIM + 8 * n + gq) * RANK + 16 * ks + 2 * t4;
+          Bb[n][ks][0] = *reinterpret_cast<const uint32_t*>(bp);
+          Bb[n][ks][1] = *reinterpret_cast<const uint32_t*>(bp + 8);
+        }
+    }
+    const int s = it % n_stages;
+    // After a wait has given up this warp stops computing but keeps walking the loop, so that it still
+    // meets the other consumer warps at every named barrier.
+    if (!dead && !wait_or_flag(&full[s], (it / n_stages) & 1, p.status, 2)) dead = true;
+    const int valid_pages = min(PAGES_PER_TILE, np - j * PAGES_PER_TILE);
+    if (!dead && sub_page < valid_pages) {
+      const uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+      const uint8_t* blk = st + COEF_TILE_BYTES + sub_page * PB;
+      // ---- low-rank coefficients as A fragments ----
+      uint32_t A[KS][4];
+      {
+        const int mi = lane >> 3, rin = lane & 7;
+        const int R = 16 * warp + (mi & 1) * 8 + rin;
+        const int sw = (RANK == 32) ? ((R >> 1) & 3) : ((R >> 2) & 1);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int chunk = ks * 2 + (mi >> 1);
+          ldmatrix_x4(A[ks][0], A[ks][1], A[ks][2], A[ks][3], smem_u32(st + (R * RANK + ((chunk ^ sw) << 3)) * 2));
+        }
+      }
+      // ---- residual -> C operand ----
+      uint32_t acc[16][2];
+      {
+        const uint4 w0 = *reinterpret_cast<const uint4*>(blk + ((wr * 2 + 0) * 32 + lane) * 16);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(blk + ((wr * 2 + 1) * 32 + lane) * 16);
+        const uint4* scp = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(PAGE) + (grp * 128 + t4 * 32) * 2);
+        uint32_t sc[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint4 v = scp[k];
+          sc[4 * k] = v.x, sc[4 * k + 1] = v.y, sc[4 * k + 2] = v.z, sc[4 * k + 3] = v.w;
+        }
+        const uint32_t ww[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            const uint32_t wlo = ww[c][qd], whi = ww[c][qd] >> 8;
+            // (w & mask) ^ magic : nibble^8 under a 1024 (or 1024 + 16 x) exponent
+            const __half2 h0 = u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u));
+            const __half2 h1 = u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u));
+            const __half2 h2 = u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u));
+            const __half2 h3 = u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u));
+            const __half2 k0 = __hsub2(h0, c1032), k1 = __hfma2(h1, c16th, cm72);
+            const __half2 k2 = __hsub2(h2, c1032), k3 = __hfma2(h3, c16th, cm72);
+            acc[4 * qd + 0][c] = h2_as_u32(__hmul2(k0, u32_as_h2(sc[4 * qd + 0])));
+            acc[4 * qd + 1][c] = h2_as_u32(__hmul2(k1, u32_as_h2(sc[4 * qd + 1])));
+            acc[4 * qd + 2][c] = h2_as_u32(__hmul2(k2, u32_as_h2(sc[4 * qd + 2])));
+            acc[4 * qd + 3][c] = h2_as_u32(__hmul2(k3, u32_as_h2(sc[4 * qd + 3])));
+          }
+      }
+      // ---- K_pre = coef x basis^T + residual ----
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+          mma_f16acc(acc[n][0], acc[n][1], A[ks][0], A[ks][1], A[ks][2], A[ks][3], Bb[n][ks][0], Bb[n][ks][1]);
+      // ---- rotate by the offset inside the tile ----
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const __half2 lo = u32_as_h2(acc[n][c]), hi = u32_as_h2(acc[n + 8][c]);
+          const __half2 cs = u32_as_h2(cosr[c][n]), sn = u32_as_h2(sinr[c][n]);
+          const __half2 lo2 = __hfma2(lo, cs, __hneg2(__hmul2(hi, sn)));
+          const __half2 hi2 = __hfma2(hi, cs, __hmul2(lo, sn));
+          acc[n][c] = h2_as_u32(lo2);
+          acc[n + 8][c] = h2_as_u32(hi2);
+        }
+      // ---- scores (transposed): rows = queries, columns = this warp's 16 tokens ----
+      float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const uint4* qp = reinterpret_cast<const uint4*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB + (gq * 4 + t4) * 64);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const uint4 v = qp[k4];  // k-steps 2*k4 and 2*k4+1
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            mma_f32acc(S[c][0], S[c][1], S[c][2], S[c][3], v.x, v.x, v.y, v.y, acc[4 * k4][c], acc[4 * k4 + 1][c]);
+            mma_f32acc(S[c][0], S[c][1], S[c][2], S[c][3], v.z, v.z, v.w, v.w, acc[4 * k4 + 2][c], acc[4 * k4 + 3][c]);
+          }
+        }
+      }
+      // ---- online softmax, base 2, rescale only when the maximum moved by more than 2^8 ----
+      float tmax = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const bool need = (gq < G) && (tmax > m_run + 8.f);
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = need ? tmax : m_run;
+        const float fsc = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
+        const float f = need ? fsc : 1.f;
+        l_run *= f, pn_run *= f, m_run = m_new;
+        const float f0 = __shfl_sync(0xffffffffu, f, (2 * t4) << 2), f1 = __shfl_sync(0xffffffffu, f, (2 * t4 + 1) << 2);
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) O[mt][0] *= f0, O[mt][1] *= f1, O[mt][2] *= f0, O[mt][3] *= f1;
+      }
+      const float p00 = ex2_approx(S[0][0] - m_run), p01 = ex2_approx(S[0][1] - m_run);
+      const float p10 = ex2_approx(S[1][0] - m_run), p11 = ex2_approx(S[1][1] - m_run);
+      l_run += (p00 + p01) + (p10 + p11);
+      const __half* vn = reinterpret_cast<const __half*>(blk + k2b_off_vnorm(PAGE, g.group)) + 16 * wr + 2 * t4;
+      const float2 n01 = __half22float2(*reinterpret_cast<const __half2*>(vn));
+      const float2 n23 = __half22float2(*reinterpret_cast<const __half2*>(vn + 8));
+      const float w00 = p00 * n01.x, w01 = p01 * n01.y, w10 = p10 * n23.x, w11 = p11 * n23.y;
+      pn_run += (w00 + w01) + (w10 + w11);
+      const uint32_t pb0 = h2_as_u32(__floats2half2_rn(w00, w01)), pb1 = h2_as_u32(__floats2half2_rn(w10, w11));
+      // ---- values: codes -> fp16 levels (A fragments), O^T += V^T x P ----
+      {
+        const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
+        const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+        for (int jw = 0; jw < 4; ++jw) {
+          const uint32_t x0 = vv[jw] & 0x33333333u, x1 = (vv[jw] >> 2) & 0x33333333u;
+#pragma unroll
+          for (int hs = 0; hs < 2; ++hs) {
+            const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
+            const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
+            const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
+            const uint32_t a0 = prmt(lo0, hi0, 0x5140u), a1 = prmt(lo0, hi0, 0x7362u);
+            const uint32_t a2 = prmt(lo1, hi1, 0x5140u), a3 = prmt(lo1, hi1, 0x7362u);
+            const int mt = 2 * jw + hs;
+            mma_f32acc(O[mt][0], O[mt][1], O[mt][2], O[mt][3], a0, a1, a2, a3, pb0, pb1);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+  if (cur_bh >= 0) flush(cur_b, cur_h);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Merge: one block of 128 threads per (sequence, KV head).
+//   1. attention over the fp16 recent window (keys already RoPE'd), as one more partial
+//      (bmx: src/bmx/cache/triton_dequant_attention.py:324-360)
+//   2. combine with the decode kernel's partials of this (sequence, head)
+//      (bmx: :409-461; maxima are in log2 units on both sides)
+//   3. undo the value rotation of the packed part: signs * fwht(acc) / sqrt(128)
+// ---------------------------------------------------------------------------------------------
+struct K2bMergeParams {
+  K2bGeom g;
+  const __half* q;
+  const int32_t* n_pages;
+  int batch;
+  int main_grid;
+  const float* part;
+  const __half* k_tail;
+  const __half* v_tail;
+  const int32_t* tail_len;
+  int tail_cap;
+  const float* signs;
+  float scale_log2;
+  void* out;
+  int out_dtype;
+  float* partial_out;
+};
+
+__global__ void __launch_bounds__(128) k2b_merge_kernel(const K2bMergeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const K2bGeom g = p.g;
+  const int G = g.n_q_groups;
+  float* sc = reinterpret_cast<float*>(smem);           // [G][tail_cap] scores, then weights
+  float* accs = sc + G * p.tail_cap;                     // [G][128] rotated accumulator exchange
+  float* tm = accs + G * HEAD_DIM;                       // [G] tail max, [G] tail sum
+  int* cum = reinterpret_cast<int*>(tm + 2 * 8);         // [batch + 1]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.x / g.h_kv, h = blockIdx.x % g.h_kv;
+
+  if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, g.page, lane);
+  __syncthreads();
+  const int total = cum[p.batch];
+  const int per_cta = max(1, (total + p.main_grid - 1) / p.main_grid);
+  const int tiles_b = tiles_of(p.n_pages[b], g.page);
+  const int T0 = cum[b] + h * tiles_b, T1 = T0 + tiles_b;
+  const int cta0 = T0 / per_cta, cta1 = (tiles_b > 0) ? (T1 - 1) / per_cta : cta0 - 1;
+  const int bh = b * g.h_kv + h;
+
+  // ---- tail scores: warp per token, lane holds 4 channels ----
+  const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
+  const __half* qsrc = p.q + (int64_t)bh * G * HEAD_DIM;
+  const __half* kt = p.k_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
+  const __half* vt = p.v_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
+  for (int qi = 0; qi < G; ++qi) {
+    float qv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) qv[k] = __half2float(qsrc[qi * HEAD_DIM + 4 * lane + k]) * p.scale_log2;
+    for (int t = warp; t < tl; t += 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(kt + (int64_t)t * HEAD_DIM + 4 * lane);
+      const float2 a = __half22float2(u32_as_h2(raw.x)), c = __half22float2(u32_as_h2(raw.y));
+      float d = qv[0] * a.x + qv[1] * a.y + qv[2] * c.x + qv[3] * c.y;
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) d += __shfl_xor_sync(0xffffffffu, d, m);
+      if (lane == 0) sc[qi * p.tail_cap + t] = d;
+    }
+  }
+  __syncthreads();
+  if (warp < G && warp < 4) {
+    for (int qi = warp; qi < G; qi += 4) {
+      float mx = -INFINITY;
+      for (int t = lane; t < tl; t += 32) mx = fmaxf(mx, sc[qi * p.tail_cap + t]);
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+      float sum = 0.f;
+      for (int t = lane; t < tl; t += 32) {
+        const float e = ex2_approx(sc[qi * p.tail_cap + t] - mx);
+        sc[qi * p.tail_cap + t] = e;
+        sum += e;
+      }
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+      if (lane == 0) tm[qi] = mx, tm[8 + qi] = sum;
+    }
+  }
+  __syncthreads();
+
+  const int ch = tid;
+  for (int qi = 0; qi < G; ++qi) {
+    // tail accumulator for (qi, ch)
+    float at = 0.f;
+    for (int t = 0; t < tl; ++t) at = fmaf(sc[qi * p.tail_cap + t], __half2float(vt[(int64_t)t * HEAD_DIM + ch]), at);
+    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
+    // global max over partial slots and the tail
+    float M = mt;
+    for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(c + bh) * G + qi) * PART_STRIDE]);
+    float l = (mt == -INFINITY) ? 0.f : lt * ex2_approx(mt - M);
+    float ar = 0.f;
+    for (int c = cta0; c <= cta1; ++c) {
+      const float* ps = p.part + ((int64_t)(c + bh) * G + qi) * PART_STRIDE;
+      const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
+      l += ps[1] * f;
+      ar += ps[2 + ch] * f;
+    }
+    accs[qi * HEAD_DIM + ch] = ar;
+    __syncthreads();
+    // rotate back: warp 0 transforms the row, everyone reads its channel
+    if (warp == 0) {
+      float x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = accs[qi * HEAD_DIM + 4 * lane + k];
+      fwht128_warp(x, lane);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) accs[qi * HEAD_DIM + 4 * lane + k] = x[k] * p.signs[4 * lane + k] * 0.08838834764831845f;
+    }
+    __syncthreads();
+    const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
+    const float o = accs[qi * HEAD_DIM + ch] + at * wt;
+    const int64_t row = (int64_t)bh * G + qi;
+    if (p.partial_out) {
+      float* po = p.partial_out + row * PART_STRIDE;
+      po[2 + ch] = o;
+      if (ch == 0) po[0] = M, po[1] = l;
+    } else {
+      const float r = o / l;
+      if (p.out_dtype == BMXK_DTYPE_F32)
+        reinterpret_cast<float*>(p.out)[row * HEAD_DIM + ch] = r;
+      else
+        reinterpret_cast<__half*>(p.out)[row * HEAD_DIM + ch] = __float2half_rn(r);
+    }
+  }
+}
+
+// Merge of whole partial states across ranks or splits: parts (n_parts, rows, 130).
+__global__ void merge_partials_kernel(const float* __restrict__ parts, int n_parts, int rows, void* out, int out_dtype) {
+  const int row = blockIdx.x, ch = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < n_parts; ++s) M = fmaxf(M, parts[((int64_t)s * rows + row) * PART_STRIDE]);
+  float l = 0.f, a = 0.f;
+  for (int s = 0; s < n_parts; ++s) {
+    const float* ps = parts + ((int64_t)s * rows + row) * PART_STRIDE;
+    const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
+    l += ps[1] * f;
+    a += ps[2 + ch] * f;
+  }
+  const float r = a / l;
+  if (out_dtype == BMXK_DTYPE_F32)
+    reinterpret_cast<float*>(out)[(int64_t)row * HEAD_DIM + ch] = r;
+  else
+    reinterpret_cast<__half*>(out)[(int64_t)row * HEAD_DIM + ch] = __float2half_rn(r);
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+static size_t decode_stage_bytes(const bmxk_k2b_geom* g) {
+  return (size_t)TILE_TOKENS * g->rank * 2 + (size_t)(TILE_TOKENS / g->page) * k2b_page_block_bytes(g->page, g->group) + 8 * 4 * 8 * 8;
+}
+static size_t decode_fixed_smem(int batch) {
+  return (size_t)(DEC_CONSUMER_WARPS * 8 * HEAD_DIM + 3 * 64 + 8 * HEAD_DIM) * 4 + 32 * 8 + (size_t)(batch + 1) * 4 + 16;
+}
+
+template <int RANK, int PAGE>
+static int launch_decode(const K2bDecodeParams& prm, int grid, size_t smem, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(k2b_decode_kernel<RANK, PAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) {
+      set_error("bmxk_k2b_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return BMXK_ERR_CUDA;
+    }
+    configured = true;
+  }
+  k2b_decode_kernel<RANK, PAGE><<<grid, DEC_THREADS, smem, s>>>(prm);
+  return check_launch("bmxk_k2b_decode");
+}
+
+}  // namespace bmxk
+
+using namespace bmxk;
+
+extern "C" {
+
+size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int max_pages) {
+  if (!g || batch <= 0) return 0;
+  (void)max_pages;
+  const size_t slots = (size_t)num_sms() + (size_t)batch * g->h_kv;
+  return 256 + slots * g->n_q_groups * PART_STRIDE * sizeof(float);
+}
+
+int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs, const void* basis_f16,
+                    const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch, int max_pages,
+                    const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail,
+                    const void* v_tail, const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs,
+                    float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* partial_out,
+                    void* stream) {
+  BMXK_REQUIRE(g != nullptr, "bmxk_k2b_decode: null geometry");
+  BMXK_REQUIRE(g->h_kv >= 1 && g->n_q_groups >= 1 && g->n_q_groups <= 8, "bmxk_k2b_decode: h_kv=%d n_q_groups=%d", g->h_kv,
+               g->n_q_groups);
+  BMXK_REQUIRE(g->page == 64 || g->page == 128, "bmxk_k2b_decode: page=%d must be 64 or 128", g->page);
+  BMXK_REQUIRE(g->rank == 16 || g->rank == 32, "bmxk_k2b_decode: rank=%d must be 16 or 32", g->rank);
+  BMXK_REQUIRE((g->group == 32 || g->group == 64 || g->group == 128) && g->page % g->group == 0,
+               "bmxk_k2b_decode: group=%d must be 32/64/128 and divide page", g->group);
+  BMXK_REQUIRE(g->n_coef_heads == 1 || g->n_coef_heads == g->h_kv, "bmxk_k2b_decode: n_coef_heads=%d", g->n_coef_heads);
+  BMXK_REQUIRE(g->vbits == 2, "bmxk_k2b_decode: vbits=%d (only 2)", g->vbits);
+  BMXK_REQUIRE(batch >= 1 && (int64_t)batch * g->h_kv <= MAX_BH, "bmxk_k2b_decode: batch*h_kv=%lld out of range",
+               (long long)batch * g->h_kv);
+  BMXK_REQUIRE(max_pages >= 0 && tail_cap >= 0, "bmxk_k2b_decode: negative sizes");
+  BMXK_REQUIRE(q && n_pages && v_lut && signs && workspace, "bmxk_k2b_decode: null pointer");
+  BMXK_REQUIRE(max_pages == 0 || (pages && coefs && basis_f16 && page_table && rope_cos && rope_sin),
+               "bmxk_k2b_decode: null page pool / tables");
+  BMXK_REQUIRE(tail_cap == 0 || (k_tail && v_tail && tail_len), "bmxk_k2b_decode: null tail");
+  BMXK_REQUIRE(out || partial_out, "bmxk_k2b_decode: no output");
+  BMXK_REQUIRE(out_dtype == BMXK_DTYPE_F16 || out_dtype == BMXK_DTYPE_F32, "bmxk_k2b_decode: out_dtype=%d", out_dtype);
+  BMXK_REQUIRE(workspace_bytes >= bmxk_k2b_decode_workspace_bytes(g, batch, max_pages), "bmxk_k2b_decode: workspace too small");
+  BMXK_REQUIRE(((uintptr_t)pages & 15) == 0 && ((uintptr_t)coefs & 15) == 0, "bmxk_k2b_decode: pools must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+
+  int32_t* status = reinterpret_cast<int32_t*>(workspace);
+  float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 256);
+  const int64_t max_tiles = (int64_t)batch * g->h_kv * (((int64_t)max_pages * g->page + TILE_TOKENS - 1) / TILE_TOKENS);
+  const int grid = (int)(max_tiles < num_sms() ? (max_tiles < 1 ? 1 : max_tiles) : num_sms());
+  const float scale_log2 = sm_scale * 1.4426950408889634f;
+  float alpha, beta;
+  memcpy(&alpha, &v_lut[2], 4);
+  memcpy(&beta, &v_lut[3], 4);
+
+  if (max_pages > 0) {
+    K2bDecodeParams prm;
+    prm.g.h_kv = g->h_kv, prm.g.n_q_groups = g->n_q_groups, prm.g.page = g->page, prm.g.rank = g->rank;
+    prm.g.group = g->group, prm.g.n_coef_heads = g->n_coef_heads, prm.g.kbits = g->kbits, prm.g.vbits = g->vbits;
+    prm.q = (const __half*)q, prm.pages = (const uint8_t*)pages, prm.coefs = (const __half*)coefs;
+    prm.basis16 = (const __half*)basis_f16, prm.page_table = page_table, prm.table_stride = table_stride;
+    prm.n_pages = n_pages, prm.batch = batch, prm.rope_cos = (const __half*)rope_cos, prm.rope_sin = (const __half*)rope_sin;
+    prm.pos_offset = pos_offset, prm.lut_lo = v_lut[0], prm.lut_hi = v_lut[1], prm.lut_alpha = alpha, prm.lut_beta = beta;
+    prm.scale_log2 = scale_log2, prm.part = part, prm.status = status;
+    const size_t stage = decode_stage_bytes(g), fixed = decode_fixed_smem(batch);
+    int n_stages = (int)((220 * 1024 - fixed) / stage);
+    if (n_stages > 8) n_stages = 8;
+    BMXK_REQUIRE(n_stages >= 2, "bmxk_k2b_decode: shared memory too small for 2 stages");
+    prm.n_stages = n_stages;
+    const size_t smem = fixed + (size_t)n_stages * stage;
+    int rc;
+    if (g->rank == 32 && g->page == 128) rc = launch_decode<32, 128>(prm, grid, smem, s);
+    else if (g->rank == 16 && g->page == 128) rc = launch_decode<16, 128>(prm, grid, smem, s);
+    else if (g->rank == 32 && g->page == 64) rc = launch_decode<32, 64>(prm, grid, smem, s);
+    else rc = launch_decode<16, 64>(prm, grid, smem, s);
+    if (rc) return rc;
+  }
+  K2bMergeParams mp;
+  mp.g.h_kv = g->h_kv, mp.g.n_q_groups = g->n_q_groups, mp.g.page = g->page, mp.g.rank = g->rank, mp.g.group = g->group;
+  mp.g.n_coef_heads = g->n_coef_heads, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits;
+  mp.q = (const __half*)q, mp.n_pages = n_pages, mp.batch = batch, mp.main_grid = grid, mp.part = part;
+  mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
+  mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
+  mp.partial_out = partial_out;
+  const size_t msmem = ((size_t)g->n_q_groups * tail_cap + g->n_q_groups * HEAD_DIM + 16) * 4 + (size_t)(batch + 1) * 4;
+  BMXK_REQUIRE(msmem <= 48 * 1024, "bmxk_k2b_decode: tail_cap=%d too large for the merge kernel", tail_cap);
+  k2b_merge_kernel<<<batch * g->h_kv, 128, msmem, s>>>(mp);
+  return check_launch("bmxk_k2b_decode(merge)");
+}
+
+int bmxk_k2b_make_v_lut(const float* codebook, uint32_t* out_lut) {
+  BMXK_REQUIRE(codebook && out_lut, "bmxk_k2b_make_v_lut: null pointer");
+  const double cb[4] = {codebook[0], codebook[1], codebook[2], codebook[3]};
+  BMXK_REQUIRE(cb[0] < cb[1] && cb[1] < cb[2] && cb[2] < cb[3] && cb[0] < 0 && cb[3] > 0,
+               "bmxk_k2b_make_v_lut: codebook must ascend through zero");
+  // Search fp16 pairs (h0, h3) over two binades around the outer levels; each pair fixes the affine
+  // map through levels 0 and 3, and the inner levels take the nearest fp16.  Keep the pair whose
+  // worst inner error is smallest, with |alpha| small so that sum(P*h) carries no large offset.
+  auto f16 = [](double x) { return (double)__half2float(__float2half_rn((float)x)); };
+  auto bits16 = [](double x) { __half h = __float2half_rn((float)x); uint16_t u; memcpy(&u, &h, 2); return u; };
+  double best = 1e30, bh[4] = {0, 0, 0, 0}, balpha = 0, bbeta = 1;
+  for (int i3 = 0; i3 < 2048; ++i3) {
+    uint16_t u3 = (uint16_t)(bits16(cb[3] * 0.5) + i3);
+    __half hh3; memcpy(&hh3, &u3, 2);
+    const double h3 = __half2float(hh3);
+    const double h0c = h3 * cb[0] / cb[3];
+    const uint16_t u0c = bits16(h0c);
+    for (int d0 = -24; d0 <= 24; ++d0) {
+      uint16_t u0 = (uint16_t)(u0c + d0);
+      __half hh0; memcpy(&hh0, &u0, 2);
+      const double h0 = __half2float(hh0);
+      if (!(h0 < 0) || !(h3 > 0)) continue;
+      const double beta = (cb[3] - cb[0]) / (h3 - h0), alpha = cb[0] - beta * h0;
+      if (fabs(alpha) > 0.02) continue;
+      const double h1 = f16((cb[1] - alpha) / beta), h2 = f16((cb[2] - alpha) / beta);
+      const double e1 = fabs(alpha + beta * h1 - cb[1]), e2 = fabs(alpha + beta * h2 - cb[2]);
+      const double e = e1 > e2 ? e1 : e2;
+      if (e < best) best = e, bh[0] = h0, bh[1] = h1, bh[2] = h2, bh[3] = h3, balpha = alpha, bbeta = beta;
+    }
+  }
+  BMXK_REQUIRE(best < 1e-3, "bmxk_k2b_make_v_lut: no fp16 table found");
+  // Remove the mean residual under the Gaussian bin probabilities, so that the leftover per-level
+  // error does not add up over many tokens.
+  double mid[3] = {(cb[0] + cb[1]) / 2, (cb[1] + cb[2]) / 2, (cb[2] + cb[3]) / 2};
+  auto Phi = [](double x) { return 0.5 * erfc(-x / sqrt(2.0)); };
+  const double P[4] = {Phi(mid[0]), Phi(mid[1]) - Phi(mid[0]), Phi(mid[2]) - Phi(mid[1]), 1.0 - Phi(mid[2])};
+  double bias = 0;
+  for (int i = 0; i < 4; ++i) bias += P[i] * (balpha + bbeta * bh[i] - cb[i]);
+  balpha -= bias;
+  uint32_t lo = 0, hi = 0;
+  for (int i = 0; i < 4; ++i) {
+    const uint16_t u = bits16(bh[i]);
+    lo |= (uint32_t)(u & 0xFF) << (8 * i);
+    hi |= (uint32_t)(u >> 8) << (8 * i);
+  }
+  const float fa = (float)balpha, fb = (float)bbeta;
+  out_lut[0] = lo, out_lut[1] = hi;
+  memcpy(&out_lut[2], &fa, 4);
+  memcpy(&out_lut[3], &fb, 4);
+  return BMXK_OK;
+}
+
+int bmxk_merge_partials(const float* parts, int n_parts, int rows, void* out, int out_dtype, void* stream) {
+  BMXK_REQUIRE(parts && out && n_parts >= 1 && rows >= 1, "bmxk_merge_partials: bad arguments");
+  BMXK_REQUIRE(out_dtype == BMXK_DTYPE_F16 || out_dtype == BMXK_DTYPE_F32, "bmxk_merge_partials: out_dtype=%d", out_dtype);
+  merge_partials_kernel<<<rows, HEAD_DIM, 0, (cudaStream_t)stream>>>(parts, n_parts, rows, out, out_dtype);
+  return check_launch("bmxk_merge_partials");
+}
+
+int bmxk_check_workspace_status(const void* workspace, void* stream) {
+  BMXK_REQUIRE(workspace != nullptr, "bmxk_check_workspace_status: null workspace");
+  int32_t st[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyAsync(st, workspace, sizeof(st), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    set_error("bmxk_check_workspace_status: %s", cudaGetErrorString(e));
+    return BMXK_ERR_CUDA;
+  }
+  if (st[0] != 0) {
+    set_error("decode kernel: a bounded wait ran out in block %d (site %d)", st[1], st[2]);
+    return BMXK_ERR_DEVICE;
+  }
+  return BMXK_OK;
+}
+
+}  // extern "C"

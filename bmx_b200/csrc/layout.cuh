@@ -1,0 +1,97 @@
+// Native HBM layout of one k2b page and the index arithmetic shared by every kernel that
+// touches it (append, export, dequant, decode).  Head dim is fixed at 128.
+//
+// A page is PAGE tokens (64 or 128) of ONE sequence.  For each physical page slot the pool
+// holds, per KV head, one contiguous "page block":
+//
+//   [ K residual nibbles | K residual scales | V codes | V norms ]
+//
+// and, per coefficient head (1 when the key basis spans all heads, h_kv when each head has
+// its own basis), one "coef block" of PAGE x rank fp16 low-rank coefficients.
+//
+// The bytes are the reference's (two's-complement residual nibbles, offset-free 2-bit V
+// indices, fp16 scales / norms / coefficients: bmx src/bmx/cache/triton_dequant_attention.py
+// :1118-1229) but ORDERED for the decode kernel: every array is cut into 16-token "warp rows"
+// and, inside a warp row, into the per-lane fragments that mma.sync m16n8k16 expects, so that
+// one bulk copy lands a page in shared memory and each lane reads its operands with 128-bit
+// loads and no shuffles.  `bmxk_k2b_export_stacks` undoes the ordering for byte parity.
+//
+// Lane coordinates: lane = 4*g + t  (g = lane / 4 in 0..7, t = lane % 4).
+//
+// K residual (4-bit container, code for (row r, channel c)):
+//   warp row wr = r / 16, rr = r % 16, token half th = rr / 8, g = rr % 8
+//   n = c / 8 (8-channel tile), t = (c % 8) / 2, e = c % 2, q = n / 4, i = n % 4
+//   32-bit word index  ((wr*2 + th)*32 + 4*g + t)*4 + q ; bit offset 16*e + 4*i
+//   -> a lane's (token g or g+8) x (channels 8n+2t, 8n+2t+1) codes sit in matching nibbles of
+//      the low and high halves of a word: one LOP3 turns them into a half2.
+// K residual scale (fp16, per channel per `group` tokens):
+//   half index  grp*128 + t*32 + n*2 + e      (grp = r / group)
+// V code (2-bit index for (row r, channel c)):
+//   wr = r / 16, rr = r % 16; mt = c / 16 (16-channel tile), cc = c % 16
+//   g = cc % 8, chi = cc / 8 ; t = (rr % 8) / 2, e = rr % 2, thi = rr / 8
+//   A-fragment register a = 2*thi + chi  (a0..a3 of mma m16n8k16 with rows = channels,
+//   k = tokens); word j = mt / 2, hs = mt % 2
+//   32-bit word index  (wr*32 + 4*g + t)*4 + j ; bit offset 16*hs + 4*(2*(a&1) + e) + 2*(a>>1)
+// V norm (fp16 per token): half index r.
+#pragma once
+#include <cstdint>
+
+#if defined(__CUDACC__)
+#define BMXK_HD __host__ __device__ __forceinline__
+#else
+#define BMXK_HD inline
+#endif
+
+namespace bmxk {
+
+constexpr int HEAD_DIM = 128;
+
+struct K2bGeom {
+  int h_kv;          // KV heads
+  int n_q_groups;    // query heads per KV head (GQA group), <= 8
+  int page;          // tokens per page: 64 or 128
+  int rank;          // low-rank coefficients per token: 16 or 32
+  int group;         // K residual scale group along tokens; divides page
+  int n_coef_heads;  // 1 (basis spans all heads) or h_kv (one basis per head)
+  int kbits;         // K residual code width (<= 4, stored as nibbles)
+  int vbits;         // V code width (2)
+};
+
+BMXK_HD int k2b_kres_bytes(int page) { return page * 64; }
+BMXK_HD int k2b_kscale_bytes(int page, int group) { return (page / group) * 128 * 2; }
+BMXK_HD int k2b_vcode_bytes(int page) { return page * 32; }
+BMXK_HD int k2b_vnorm_bytes(int page) { return page * 2; }
+BMXK_HD int k2b_off_kscale(int page) { return k2b_kres_bytes(page); }
+BMXK_HD int k2b_off_vcode(int page, int group) { return k2b_off_kscale(page) + k2b_kscale_bytes(page, group); }
+BMXK_HD int k2b_off_vnorm(int page, int group) { return k2b_off_vcode(page, group) + k2b_vcode_bytes(page); }
+BMXK_HD int k2b_page_block_bytes(int page, int group) { return k2b_off_vnorm(page, group) + k2b_vnorm_bytes(page); }
+BMXK_HD int k2b_coef_block_bytes(int page, int rank) { return page * rank * 2; }
+
+// word index (in 32-bit words from the start of the K residual array) and bit offset
+BMXK_HD void k2b_kres_loc(int r, int c, int& word, int& bit) {
+  const int wr = r >> 4, rr = r & 15, th = rr >> 3, g = rr & 7;
+  const int n = c >> 3, t = (c & 7) >> 1, e = c & 1, q = n >> 2, i = n & 3;
+  word = ((wr * 2 + th) * 32 + 4 * g + t) * 4 + q;
+  bit = 16 * e + 4 * i;
+}
+BMXK_HD int k2b_kscale_idx(int grp, int c) {
+  const int n = c >> 3, t = (c & 7) >> 1, e = c & 1;
+  return grp * 128 + t * 32 + n * 2 + e;
+}
+BMXK_HD void k2b_vcode_loc(int r, int c, int& word, int& bit) {
+  const int wr = r >> 4, rr = r & 15;
+  const int mt = c >> 4, cc = c & 15, g = cc & 7, chi = cc >> 3;
+  const int t = (rr & 7) >> 1, e = rr & 1, thi = rr >> 3;
+  const int a = 2 * thi + chi, j = mt >> 1, hs = mt & 1;
+  word = (wr * 32 + 4 * g + t) * 4 + j;
+  bit = 16 * hs + 4 * (2 * (a & 1) + e) + 2 * (a >> 1);
+}
+// Coefficient rows are stored with their 16-byte chunks XOR-swizzled so that ldmatrix reads of
+// eight consecutive rows hit distinct shared-memory banks.  Returns the half index of (r, i).
+BMXK_HD int k2b_coef_idx(int r, int i, int rank) {
+  const int chunk = i >> 3, within = i & 7;
+  const int sw = (rank == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
+  return r * rank + ((chunk ^ sw) << 3) + within;
+}
+
+}  // namespace bmxk

@@ -1,0 +1,224 @@
+"""Thin torch-facing wrappers over the bmxk C ABI (include/bmxk.h).
+
+torch is used for device memory and streams only; every function here passes raw pointers to
+libbmxk.so and raises `BmxkError` on a non-zero status.  Nothing in this module computes on the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import functools
+import struct
+
+import torch
+
+from . import _lib
+from ._lib import DTYPE_BF16, DTYPE_F16, DTYPE_F32, K2bGeom, call
+
+HEAD_DIM = 128
+
+# Lloyd-Max levels for N(0,1) exactly as bmx computes them at run time
+# (bmx: src/bmx/cache/codecs.py:346-380, 2**18 seeded samples, 40 iterations; float32).
+GAUSSIAN_CODEBOOK = {
+    2: (-1.5194618701934814, -0.46033763885498047, 0.44421979784965515, 1.5017313957214355),
+    3: (-2.174412250518799, -1.3567343950271606, -0.7671520113945007, -0.2563295364379883,
+        0.23005320131778717, 0.7372721433639526, 1.3183449506759644, 2.12149977684021),
+}
+
+
+@functools.lru_cache(maxsize=16)
+def hadamard_signs(d: int, seed: int) -> torch.Tensor:
+    """+-1 vector of the randomized Hadamard rotation (bmx: src/bmx/cache/codecs.py:114-124)."""
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 2, (d,), generator=g) * 2 - 1).to(torch.float32)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return DTYPE_F16
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("bmxk kernels take CUDA tensors; there is no CPU path")
+
+
+def k2b_geom(h_kv: int, n_q_groups: int, page: int = 128, rank: int = 16, group: int = 64,
+             n_coef_heads: int = 1, kbits: int = 3, vbits: int = 2) -> K2bGeom:
+    return K2bGeom(h_kv, n_q_groups, page, rank, group, n_coef_heads, kbits, vbits)
+
+
+def page_block_bytes(g: K2bGeom) -> int:
+    return int(_lib.lib().bmxk_k2b_page_block_bytes(ctypes.byref(g)))
+
+
+def coef_block_bytes(g: K2bGeom) -> int:
+    return int(_lib.lib().bmxk_k2b_coef_block_bytes(ctypes.byref(g)))
+
+
+class K2bPool:
+    """Device page pool of one layer: `pages[n_slots][h_kv][block]` and `coefs[n_slots][n_coef_heads][block]`."""
+
+    def __init__(self, g: K2bGeom, n_slots: int, device):
+        self.geom = g
+        self.n_slots = n_slots
+        self.pages = torch.zeros(n_slots, g.h_kv, page_block_bytes(g), dtype=torch.uint8, device=device)
+        self.coefs = torch.zeros(n_slots, g.n_coef_heads, coef_block_bytes(g), dtype=torch.uint8, device=device)
+
+    def nbytes(self) -> int:
+        return self.pages.numel() + self.coefs.numel()
+
+
+def pack_u(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    """bmx pack_codes on the GPU: int16 (rows, C) -> uint8 (rows, C*bits/8)."""
+    _require_cuda(codes)
+    codes = codes.to(torch.int16).contiguous()
+    rows, C = codes.reshape(-1, codes.shape[-1]).shape if codes.numel() else (0, codes.shape[-1])
+    if bits not in (2, 4) or C % (8 // max(bits, 1)) != 0:
+        call("bmxk_pack_u", _ptr(codes), None, rows, C, bits, _stream())  # raises with the library's message
+    out = torch.empty(*codes.shape[:-1], C * bits // 8, dtype=torch.uint8, device=codes.device)
+    call("bmxk_pack_u", _ptr(codes), _ptr(out), rows, C, bits, _stream())
+    return out
+
+
+def unpack_u(packed: torch.Tensor, bits: int, C: int) -> torch.Tensor:
+    _require_cuda(packed)
+    packed = packed.contiguous()
+    rows = packed.numel() // max(packed.shape[-1], 1)
+    out = torch.empty(*packed.shape[:-1], C, dtype=torch.int16, device=packed.device)
+    call("bmxk_unpack_u", _ptr(packed), _ptr(out), rows, C, bits, _stream())
+    return out
+
+
+def pack_s4(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    """bmx pack_signed_codes on the GPU: int8 (rows, N) -> uint8 (rows, N/2)."""
+    _require_cuda(codes)
+    codes = codes.to(torch.int8).contiguous()
+    N = codes.shape[-1]
+    rows = codes.numel() // max(N, 1)
+    if N % 2 or not 1 <= bits <= 4:
+        call("bmxk_pack_s4", _ptr(codes), None, rows, N, bits, _stream())
+    out = torch.empty(*codes.shape[:-1], N // 2, dtype=torch.uint8, device=codes.device)
+    call("bmxk_pack_s4", _ptr(codes), _ptr(out), rows, N, bits, _stream())
+    return out
+
+
+def unpack_s4(packed: torch.Tensor, bits: int, N: int) -> torch.Tensor:
+    _require_cuda(packed)
+    packed = packed.contiguous()
+    rows = packed.numel() // max(packed.shape[-1], 1)
+    out = torch.empty(*packed.shape[:-1], N, dtype=torch.int8, device=packed.device)
+    call("bmxk_unpack_s4", _ptr(packed), _ptr(out), rows, N, bits, _stream())
+    return out
+
+
+def k2b_append(pool: K2bPool, k_pre: torch.Tensor, v: torch.Tensor, basis_f32: torch.Tensor,
+               signs: torch.Tensor, codebook: torch.Tensor, slots: torch.Tensor, n_pages: int) -> None:
+    """Quantizes `n_pages` full pages of every sequence in k_pre/v (n_seq, h_kv, T, 128) into the pool.
+
+    slots: int32 (n_seq * n_pages,) physical slot per page, sequence-major.
+    """
+    g = pool.geom
+    _require_cuda(k_pre, v, basis_f32, signs, codebook, slots)
+    assert k_pre.shape == v.shape and k_pre.dim() == 4 and k_pre.shape[1] == g.h_kv and k_pre.shape[3] == HEAD_DIM
+    assert k_pre.dtype == v.dtype and k_pre.stride() == v.stride() and k_pre.stride(3) == 1
+    assert k_pre.shape[2] >= n_pages * g.page
+    n_seq = k_pre.shape[0]
+    assert slots.dtype == torch.int32 and slots.numel() == n_seq * n_pages
+    assert basis_f32.dtype == torch.float32 and basis_f32.shape == (g.h_kv * HEAD_DIM, g.rank) and basis_f32.is_contiguous()
+    call("bmxk_k2b_append", ctypes.byref(g), _ptr(k_pre), _ptr(v), _dtype_code(k_pre), k_pre.stride(0), k_pre.stride(1),
+         k_pre.stride(2), _ptr(basis_f32), _ptr(signs), _ptr(codebook), _ptr(slots), n_seq, n_pages,
+         _ptr(pool.pages), _ptr(pool.coefs), _stream())
+
+
+def k2b_export_stacks(pool: K2bPool, slots: torch.Tensor) -> dict:
+    """Pages -> the tensors bmx's build_kv_stacked_k2b(pack_k=True, pack_v=True) would hold."""
+    g = pool.geom
+    n, dev, C = slots.numel(), pool.pages.device, g.h_kv * HEAD_DIM
+    out = {
+        "us": torch.empty(n, g.n_coef_heads, g.page, g.rank, dtype=torch.float16, device=dev),
+        "res_int_packed": torch.empty(n, C, g.page // 2, dtype=torch.uint8, device=dev),
+        "res_scale": torch.empty(n, C, g.page // g.group, dtype=torch.float16, device=dev),
+        "v_idx_packed": torch.empty(n, g.page, C // 4, dtype=torch.uint8, device=dev),
+        "v_norm": torch.empty(n, g.page, g.h_kv, dtype=torch.float16, device=dev),
+    }
+    call("bmxk_k2b_export_stacks", ctypes.byref(g), _ptr(pool.pages), _ptr(pool.coefs), _ptr(slots), n, _ptr(out["us"]),
+         _ptr(out["res_int_packed"]), _ptr(out["res_scale"]), _ptr(out["v_idx_packed"]), _ptr(out["v_norm"]), _stream())
+    return out
+
+
+def k2b_dequant_pages(pool: K2bPool, slots: torch.Tensor, basis_f16: torch.Tensor, signs: torch.Tensor,
+                      codebook: torch.Tensor, want_k: bool = True, want_v: bool = True):
+    """Pages -> float32 (n, page, h_kv*128) pre-RoPE keys and values (bmx dequant_packed)."""
+    g = pool.geom
+    n, dev, C = slots.numel(), pool.pages.device, g.h_kv * HEAD_DIM
+    k = torch.empty(n, g.page, C, dtype=torch.float32, device=dev) if want_k else None
+    v = torch.empty(n, g.page, C, dtype=torch.float32, device=dev) if want_v else None
+    call("bmxk_k2b_dequant_pages", ctypes.byref(g), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16), _ptr(signs),
+         _ptr(codebook), _ptr(slots), n, _ptr(k), _ptr(v), _stream())
+    return k, v
+
+
+@functools.lru_cache(maxsize=8)
+def make_v_lut(codebook: tuple) -> tuple:
+    """(lo bytes, hi bytes, alpha bits, beta bits) of the fp16 value-level table for `codebook`."""
+    cb = (ctypes.c_float * 4)(*codebook)
+    out = (ctypes.c_uint32 * 4)()
+    call("bmxk_k2b_make_v_lut", cb, out)
+    return tuple(int(x) for x in out)
+
+
+def decode_workspace(g: K2bGeom, batch: int, max_pages: int, device) -> torch.Tensor:
+    """Zero-initialised workspace for k2b_decode (status word + per-CTA partial states)."""
+    n = int(_lib.lib().bmxk_k2b_decode_workspace_bytes(ctypes.byref(g), batch, max_pages))
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_table: torch.Tensor,
+               n_pages: torch.Tensor, max_pages: int, rope_cos: torch.Tensor, rope_sin: torch.Tensor,
+               k_tail: torch.Tensor | None, v_tail: torch.Tensor | None, tail_len: torch.Tensor | None,
+               v_lut_dev: torch.Tensor, signs: torch.Tensor, sm_scale: float, workspace: torch.Tensor,
+               out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+               pos_offset: int = 0) -> torch.Tensor:
+    """One decode step for q (batch, heads, 128) fp16 over the paged k2b cache plus the fp16 window."""
+    g = pool.geom
+    _require_cuda(q, page_table, n_pages, workspace)
+    batch = q.shape[0]
+    assert q.dtype == torch.float16 and q.is_contiguous() and q.shape[1:] == (g.h_kv * g.n_q_groups, HEAD_DIM)
+    assert page_table.dtype == torch.int32 and n_pages.dtype == torch.int32 and page_table.dim() == 2
+    tail_cap = 0 if k_tail is None else k_tail.shape[2]
+    if k_tail is not None:
+        assert k_tail.dtype == torch.float16 and k_tail.is_contiguous() and v_tail.is_contiguous()
+        assert k_tail.shape == (batch, g.h_kv, tail_cap, HEAD_DIM) == v_tail.shape
+    if out is None and partial_out is None:
+        out = torch.empty(batch, g.h_kv * g.n_q_groups, HEAD_DIM, dtype=torch.float16, device=q.device)
+    out_code = DTYPE_F16 if out is None else _dtype_code(out)
+    call("bmxk_k2b_decode", ctypes.byref(g), _ptr(q), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
+         _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, max_pages, _ptr(rope_cos), _ptr(rope_sin),
+         pos_offset, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut_dev), _ptr(signs),
+         ctypes.c_float(sm_scale), _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), _stream())
+    return out if partial_out is None else partial_out
+
+
+def v_lut_tensor(codebook: tuple, device) -> torch.Tensor:
+    """Host-side copy of the value table, as the int32 tensor whose 4 words bmxk_k2b_decode reads."""
+    return torch.tensor([struct.unpack("<i", struct.pack("<I", x))[0] for x in make_v_lut(tuple(codebook))],
+                        dtype=torch.int32)
+
+
+def check_status(workspace: torch.Tensor) -> None:
+    call("bmxk_check_workspace_status", _ptr(workspace), _stream())

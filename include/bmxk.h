@@ -1,0 +1,141 @@
+/* bmxk -- C ABI of the B200 (sm_100a) packed KV-cache kernels behind the bmx cache API.
+ *
+ * Every entry point takes plain device pointers, sizes and a cudaStream_t (passed as void*),
+ * returns 0 on success or a BMXK_ERR_* code, never throws, never synchronises the host and
+ * never allocates device memory: callers own pages, workspaces and outputs.  After a non-zero
+ * return, bmxk_last_error() describes the failure (thread-local string).
+ *
+ * "bmx:" citations name the reference function an entry point stands in for, by path inside
+ * the bmx project.
+ */
+#ifndef BMXK_H_
+#define BMXK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BMXK_OK 0
+#define BMXK_ERR_INVALID 1 /* bad argument, shape or alignment; nothing was launched */
+#define BMXK_ERR_CUDA 2    /* a CUDA runtime call or kernel launch failed */
+#define BMXK_ERR_DEVICE 3  /* a kernel reported a bounded wait that ran out (see status word) */
+
+#define BMXK_DTYPE_F16 0
+#define BMXK_DTYPE_BF16 1
+#define BMXK_DTYPE_F32 2
+
+/* Geometry of a k2b cache (head dim is 128).  Mirrors the fields bmx reads off its specs:
+ * bmx: src/bmx/cache/specs.py:82-91 and src/bmx/cache/packed_streaming.py:425-438. */
+typedef struct bmxk_k2b_geom {
+  int32_t h_kv;         /* KV heads */
+  int32_t n_q_groups;   /* query heads per KV head, 1..8 */
+  int32_t page;         /* tokens per page: 64 or 128 */
+  int32_t rank;         /* low-rank key coefficients per token: 16 or 32 */
+  int32_t group;        /* token group of the key-residual scale; divides page; 32, 64 or 128 */
+  int32_t n_coef_heads; /* 1: one basis over all heads (bmx default); h_kv: one basis per head */
+  int32_t kbits;        /* key-residual bits, 2..4 (stored as two's-complement nibbles) */
+  int32_t vbits;        /* value code bits: 2 */
+} bmxk_k2b_geom;
+
+int bmxk_version(void);
+const char* bmxk_last_error(void);
+
+/* ---- bit packing ---------------------------------------------------------------------- */
+/* bmx: src/bmx/cache/triton_dequant_attention.py:49-100 pack_codes / unpack_codes.
+ * codes int16 (rows, C) with values in [0, 2^bits); packed uint8 (rows, C*bits/8); bits 2 or 4. */
+int bmxk_pack_u(const int16_t* codes, uint8_t* packed, int64_t rows, int64_t C, int bits, void* stream);
+int bmxk_unpack_u(const uint8_t* packed, int16_t* codes, int64_t rows, int64_t C, int bits, void* stream);
+/* bmx: src/bmx/cache/triton_dequant_attention.py:103-165 pack_signed_codes / unpack_signed_codes.
+ * codes int8 (rows, N), N even, values in the signed `bits` range; packed uint8 (rows, N/2). */
+int bmxk_pack_s4(const int8_t* codes, uint8_t* packed, int64_t rows, int64_t N, int bits, void* stream);
+int bmxk_unpack_s4(const uint8_t* packed, int8_t* codes, int64_t rows, int64_t N, int bits, void* stream);
+
+/* ---- k2b page pool -------------------------------------------------------------------- */
+/* Bytes of one (slot, head) page block and of one (slot, coef head) coefficient block.
+ * Pool arrays are  pages[n_slots][h_kv][page_block_bytes]  and
+ * coefs[n_slots][n_coef_heads][coef_block_bytes], both 16-byte aligned. */
+size_t bmxk_k2b_page_block_bytes(const bmxk_k2b_geom* g);
+size_t bmxk_k2b_coef_block_bytes(const bmxk_k2b_geom* g);
+
+/* Quantize-on-append: packs n_seq * n_pages full pages.
+ * bmx: src/bmx/cache/packed_streaming.py:475-580 (_pack_k_block, _pack_v_block) over
+ *      src/bmx/cache/codecs.py:616-636, 677-695, 786-796 and src/bmx/quant/rtn.py:23-44.
+ * k_pre, v: sources of dtype `src_dtype`, element (seq s, head h, token t, channel c) at
+ *   base + s*stride_seq + h*stride_head + t*stride_tok + c  (elements); page p of a sequence
+ *   covers tokens [p*page, (p+1)*page).  k_pre is the PRE-RoPE key.
+ * basis_f32: (h_kv*128, rank) float32 frozen basis used for the projection Us = M @ V;
+ *   for n_coef_heads == h_kv the projection of head h uses rows [h*128, (h+1)*128) only.
+ * signs: 128 float32 (+1/-1) of the value rotation; codebook: 2^vbits float32 ascending levels.
+ * slots: int32 [n_seq * n_pages] physical slot of each page (device memory). */
+int bmxk_k2b_append(const bmxk_k2b_geom* g, const void* k_pre, const void* v, int src_dtype,
+                    int64_t stride_seq, int64_t stride_head, int64_t stride_tok, const float* basis_f32,
+                    const float* signs, const float* codebook, const int32_t* slots, int n_seq, int n_pages,
+                    void* pages, void* coefs, void* stream);
+
+/* Rewrites n pages into the exact tensors bmx's stack builder produces, for byte parity.
+ * bmx: src/bmx/cache/triton_dequant_attention.py:1118-1229 build_kv_stacked_k2b(pack_k, pack_v).
+ * us (n, n_coef_heads, page, rank) fp16; res_int_packed (n, h_kv*128, page/2) u8;
+ * res_scale (n, h_kv*128, page/group) fp16; v_idx_packed (n, page, h_kv*128/4) u8;
+ * v_norm (n, page, h_kv) fp16.  slots: int32[n] in device memory. */
+int bmxk_k2b_export_stacks(const bmxk_k2b_geom* g, const void* pages, const void* coefs, const int32_t* slots,
+                           int n, void* us, uint8_t* res_int_packed, void* res_scale, uint8_t* v_idx_packed,
+                           void* v_norm, void* stream);
+
+/* Dequantizes n pages to float32 (n, page, h_kv*128) pre-RoPE keys and values.
+ * bmx: src/bmx/cache/codecs.py:799-842 dequant_packed (lowrank_rtn_channel, turboquant_mse_perhead).
+ * basis_f16: (h_kv*128, rank) fp16 stored basis.  Either output may be NULL. */
+int bmxk_k2b_dequant_pages(const bmxk_k2b_geom* g, const void* pages, const void* coefs, const void* basis_f16,
+                           const float* signs, const float* codebook, const int32_t* slots, int n, float* k_out,
+                           float* v_out, void* stream);
+
+/* ---- k2b split-KV decode ---------------------------------------------------------------- */
+/* Workspace (bytes) for a decode call over at most max_pages pages per sequence. */
+size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int max_pages);
+
+/* One decode step of dequant-attention for `batch` independent sequences.
+ * bmx: src/bmx/cache/triton_dequant_attention.py:1232-1368 fused_decode_attention_k2b, with
+ *      :324-360 _tail_partial and :409-461 _fused_merge_kernel folded in.
+ * q: (batch, h_kv*n_q_groups, 128) fp16, already RoPE'd at the current position.
+ * basis_f16: (h_kv*128, rank) fp16.  page_table: int32 (batch, table_stride) slot ids;
+ * n_pages: int32 [batch] committed pages per sequence (device memory: the launch does not
+ * depend on their values).  rope_cos/rope_sin: fp16 (>= max position, 128) tables as bmx keeps
+ * them (bmx: src/bmx/cache/packed_streaming.py:94-113); a committed token at position t is
+ * rotated at read.  k_tail/v_tail: fp16 (batch, h_kv, tail_cap, 128) recent window, keys
+ * post-RoPE; tail_len: int32 [batch].  v_lut: 4 x uint32 in HOST memory {lo bytes, hi bytes,
+ * alpha bits, beta bits} from bmxk_k2b_make_v_lut.  signs: 128 float32.  sm_scale: softmax scale.
+ * out: (batch, h_kv*n_q_groups, 128), dtype out_dtype (F16 or F32).
+ * If partial_out is non-NULL the merged but un-normalised state is written instead of `out`:
+ * float32 (batch, heads, 130) = {max (log2 units), sum, 128 x accumulator}, for cross-GPU
+ * sequence splits (merge with bmxk_merge_partials).
+ * workspace: device memory of bmxk_k2b_decode_workspace_bytes(), zero-filled once by the caller
+ * (its first 16 bytes are a status word that a kernel sets only if a bounded wait ran out). */
+int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,
+                    const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages,
+                    int batch, int max_pages, const void* rope_cos, const void* rope_sin, int64_t pos_offset,
+                    const void* k_tail, const void* v_tail, const int32_t* tail_len, int tail_cap,
+                    const uint32_t* v_lut, const float* signs, float sm_scale, void* workspace,
+                    size_t workspace_bytes, void* out, int out_dtype, float* partial_out, void* stream);
+
+/* Host helper: fp16 lookup table for the value codebook.  Picks four fp16 levels h_i and an
+ * affine map so that codebook[i] = alpha + beta * h_i to ~1e-6, which lets the kernel feed
+ * fp16 levels to the tensor cores without a systematic per-level rounding error.
+ * out_lut[0] = low bytes of h_0..h_3, out_lut[1] = high bytes, out_lut[2] = alpha, [3] = beta
+ * (float bit patterns). */
+int bmxk_k2b_make_v_lut(const float* codebook, uint32_t* out_lut);
+
+/* Merges n_parts partial states (n_parts, rows, 130) float32 -> out (rows, 128).
+ * bmx: src/bmx/cache/triton_dequant_attention.py:409-461 _fused_merge_kernel (same formula,
+ * max carried in log2 units). */
+int bmxk_merge_partials(const float* parts, int n_parts, int rows, void* out, int out_dtype, void* stream);
+
+/* Reads back the status word of the last decode on this workspace (host-synchronising; for
+ * tests and diagnostics).  Returns BMXK_ERR_DEVICE if a bounded wait ran out. */
+int bmxk_check_workspace_status(const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BMXK_H_ */

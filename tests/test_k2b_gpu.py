@@ -1,0 +1,280 @@
+"""GPU parity of the k2b path (append, export, dequant, decode) against the oracle and the
+reference-made golden vectors.  Everything goes through the C ABI (bmx_b200.kernels -> libbmxk.so)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bmx_oracle as O
+from tests.helpers import full_rope, golden
+
+pytestmark = pytest.mark.gpu
+
+D = 128
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _K():
+    from bmx_b200 import kernels
+
+    return kernels
+
+
+def make_k2b_inputs(seed, n_seq, h_kv, T, rank, per_head):
+    """Keys = low-rank signal (spectrum i^-1.5) + 0.1 noise, values N(0,1); both fp16-valued."""
+    g = torch.Generator().manual_seed(seed)
+    C = h_kv * D
+    if per_head:
+        basis = torch.zeros(C, rank)
+        for h in range(h_kv):
+            Q, R = torch.linalg.qr(torch.randn(D, rank, generator=g))
+            basis[h * D:(h + 1) * D] = Q * torch.sign(torch.diagonal(R))
+        coef = torch.randn(n_seq, h_kv, T, rank, generator=g) * torch.arange(1, rank + 1).float() ** -1.5
+        k = torch.einsum("bhtr,hcr->bhtc", coef, basis.view(h_kv, D, rank))
+    else:
+        Q, R = torch.linalg.qr(torch.randn(C, rank, generator=g))
+        basis = Q * torch.sign(torch.diagonal(R))
+        coef = torch.randn(n_seq, T, rank, generator=g) * torch.arange(1, rank + 1).float() ** -1.5
+        k = (coef @ basis.T).view(n_seq, T, h_kv, D).permute(0, 2, 1, 3)
+    k = (k + 0.1 * torch.randn(n_seq, h_kv, T, D, generator=g)).half()
+    v = torch.randn(n_seq, h_kv, T, D, generator=g).half()
+    return k.contiguous(), v.contiguous(), basis.contiguous()
+
+
+def blocks_from_export(st, p, g, basis16):
+    """Block dicts (oracle form) of exported page p; the key dict is per coefficient head."""
+    C, blk = g.h_kv * D, g.page
+    res = O.unpack_signed_codes(st["res_int_packed"][p], g.kbits, blk)
+    scale = st["res_scale"][p].astype(np.float32)[..., None]
+    idx = O.unpack_codes(st["v_idx_packed"][p], 2, C)
+    vp = {"indices": idx, "norms": st["v_norm"][p].astype(np.float32), "bits": 2, "h": g.h_kv}
+    if g.n_coef_heads == 1:
+        kp = {"Us": st["us"][p, 0].astype(np.float32), "V": basis16, "res_Q_int": res, "res_scale": scale}
+    else:  # block-diagonal factors: (page, h*rank) x (C, h*rank)
+        r = g.rank
+        Us = np.concatenate([st["us"][p, h].astype(np.float32) for h in range(g.h_kv)], axis=1)
+        V = np.zeros((C, g.h_kv * r), np.float32)
+        for h in range(g.h_kv):
+            V[h * D:(h + 1) * D, h * r:(h + 1) * r] = basis16[h * D:(h + 1) * D]
+        kp = {"Us": Us, "V": V, "res_Q_int": res, "res_scale": scale}
+    return kp, vp
+
+
+def to_np(d):
+    return {k: v.cpu().numpy() for k, v in d.items()}
+
+
+def rope_tables(S):
+    cos, sin = O.default_rope_tables(500000.0, D, S)
+    return cos.astype(np.float16), sin.astype(np.float16)
+
+
+def test_bit_packing_matches_golden():
+    dev, K, c = _dev(), _K(), golden("codec")
+    for name, bits in (("u2", 2), ("u4", 4)):
+        codes = torch.from_numpy(c[name]).to(dev)
+        packed = K.pack_u(codes, bits)
+        assert np.array_equal(packed.cpu().numpy(), c[name + "_packed"])
+        assert torch.equal(K.unpack_u(packed, bits, 64), codes)
+    for name, bits in (("s3", 3), ("s4", 4)):
+        codes = torch.from_numpy(c[name]).to(dev)
+        packed = K.pack_s4(codes, bits)
+        assert np.array_equal(packed.cpu().numpy(), c[name + "_packed"])
+        assert torch.equal(K.unpack_s4(packed, bits, 64), codes)
+    # empty input and rejected shapes (bmx tests/test_packed_streaming.py:893-964)
+    assert K.pack_u(torch.zeros(0, 64, dtype=torch.int16, device=dev), 2).shape == (0, 16)
+    from bmx_b200._lib import BmxkError
+    with pytest.raises(BmxkError):
+        K.pack_u(torch.zeros(2, 64, dtype=torch.int16, device=dev), 3)
+    with pytest.raises(BmxkError):
+        K.pack_s4(torch.zeros(2, 63, dtype=torch.int8, device=dev), 3)
+
+
+@pytest.mark.parametrize("page,rank,per_head,group", [(128, 16, False, 64), (128, 32, True, 64), (64, 32, True, 64),
+                                                      (64, 16, False, 32), (128, 32, False, 128)])
+def test_append_export_dequant(page, rank, per_head, group):
+    dev, K = _dev(), _K()
+    h_kv, n_seq, n_pages = 2, 2, 3
+    k, v, basis = make_k2b_inputs(7, n_seq, h_kv, n_pages * page, rank, per_head)
+    g = K.k2b_geom(h_kv, 4, page, rank, group, h_kv if per_head else 1)
+    pool = K.K2bPool(g, 16, dev)
+    slots = torch.tensor([5, 2, 9, 0, 7, 11], dtype=torch.int32, device=dev)  # scattered on purpose
+    signs = K.hadamard_signs(D, 0)
+    cb = torch.tensor(K.GAUSSIAN_CODEBOOK[2])
+    K.k2b_append(pool, k.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev), slots, n_pages)
+    st = to_np(K.k2b_export_stacks(pool, slots))
+    basis16 = basis.half().float().numpy()
+    kd, vd = K.k2b_dequant_pages(pool, slots, basis.half().to(dev), signs.to(dev), cb.to(dev))
+    kd, vd = kd.cpu().numpy(), vd.cpu().numpy()
+    n_bad_code = n_code = n_bad_idx = n_idx = 0
+    for s in range(n_seq):
+        for p in range(n_pages):
+            i = s * n_pages + p
+            Mk = O.to_matrix(k[s, :, p * page:(p + 1) * page].float().numpy())
+            Mv = O.to_matrix(v[s, :, p * page:(p + 1) * page].float().numpy())
+            # --- coefficients: a float32 sum over 128 or 1024 channels, then fp16 ---
+            if per_head:
+                Us_ref = np.stack([Mk[:, h * D:(h + 1) * D] @ basis.numpy()[h * D:(h + 1) * D] for h in range(h_kv)])
+            else:
+                Us_ref = (Mk @ basis.numpy())[None]
+            us_gpu = st["us"][i].astype(np.float32)
+            ulp = np.maximum(np.abs(Us_ref), 2.0 ** -14) * 2.0 ** -10
+            assert np.all(np.abs(us_gpu - Us_ref) <= 1.01 * ulp), "coefficient off by more than one fp16 ulp"
+            # --- integer stages, given the GPU's own fp16 coefficients ---
+            kp, vp = blocks_from_export(st, i, g, basis16)
+            L = kp["Us"] @ kp["V"].T
+            Q, sc = O.rtn_quantize_packed(np.ascontiguousarray((Mk - L).T), 3, group)
+            n_bad_code += int((Q != kp["res_Q_int"]).sum())
+            n_code += Q.size
+            assert np.abs(Q.astype(int) - kp["res_Q_int"].astype(int)).max() <= 1
+            np.testing.assert_allclose(sc.astype(np.float16).astype(np.float32), kp["res_scale"], rtol=2e-3)
+            idx, norms = O.turboquant_perhead_pack(Mv, 2, signs.numpy(), h_kv)
+            n_bad_idx += int((idx != vp["indices"]).sum())
+            n_idx += idx.size
+            assert (norms != vp["norms"]).mean() < 0.02
+            assert kp["res_Q_int"].min() >= -3 and kp["res_Q_int"].max() <= 3
+            # --- dequant of the stored fields: values are elementwise (bit-exact), keys hold a
+            #     rank-term float32 sum whose order differs from BLAS: 2e-6 absolute ---
+            assert np.array_equal(vd[i], O.dequant_packed("turboquant_mse_perhead", vp, signs=signs.numpy()))
+            np.testing.assert_allclose(kd[i], O.dequant_packed("lowrank_rtn_channel", kp, group=group), atol=2e-6, rtol=0)
+    # codes may move only at rounding ties of a float32 value computed in another summation order
+    assert n_bad_code / n_code < 2e-3, (n_bad_code, n_code)
+    assert n_bad_idx / n_idx < 2e-3, (n_bad_idx, n_idx)
+
+
+def _decode_case(dev, K, *, n_seq, h_kv, G, page, rank, per_head, group, pages_per_seq, tail_lens, seed, tail_cap=256,
+                 shuffle_slots=True):
+    """Runs append + decode on the GPU and the oracle's chunked dequant-attention on the same
+    stored pages; returns (gpu_out, oracle_out) as (n_seq, heads, 128) float32 arrays."""
+    max_pages = max(pages_per_seq)
+    T = max(max_pages, 1) * page
+    k, v, basis = make_k2b_inputs(seed, n_seq, h_kv, T, rank, per_head)
+    g = K.k2b_geom(h_kv, G, page, rank, group, h_kv if per_head else 1)
+    n_slots = n_seq * max(max_pages, 1) + 3
+    pool = K.K2bPool(g, n_slots, dev)
+    gen = torch.Generator().manual_seed(seed + 1)
+    perm = torch.randperm(n_slots, generator=gen) if shuffle_slots else torch.arange(n_slots)
+    table = perm[: n_seq * max(max_pages, 1)].view(n_seq, max(max_pages, 1)).to(torch.int32)
+    signs, cb = K.hadamard_signs(D, 0), torch.tensor(K.GAUSSIAN_CODEBOOK[2])
+    if max_pages > 0:
+        K.k2b_append(pool, k.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev),
+                     table.reshape(-1).contiguous().to(dev), max_pages)
+    S_max = T + tail_cap + 128
+    cos16, sin16 = rope_tables(S_max)
+    q = (torch.randn(n_seq, h_kv * G, D, generator=gen) / math.sqrt(D)).half()
+    k_tail = torch.randn(n_seq, h_kv, tail_cap, D, generator=gen).half()
+    v_tail = torch.randn(n_seq, h_kv, tail_cap, D, generator=gen).half()
+    n_pages_t = torch.tensor(pages_per_seq, dtype=torch.int32)
+    tail_t = torch.tensor(tail_lens, dtype=torch.int32)
+    ws = K.decode_workspace(g, n_seq, max_pages, dev)
+    out = torch.empty(n_seq, h_kv * G, D, dtype=torch.float32, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    K.k2b_decode(pool, q.to(dev), basis.half().to(dev), table.to(dev), n_pages_t.to(dev), max_pages,
+                 torch.from_numpy(cos16).to(dev), torch.from_numpy(sin16).to(dev), k_tail.to(dev), v_tail.to(dev),
+                 tail_t.to(dev), K.v_lut_tensor(K.GAUSSIAN_CODEBOOK[2], dev), signs.to(dev), scale, ws, out=out)
+    torch.cuda.synchronize()
+    K.check_status(ws)
+    # oracle on the SAME stored pages
+    ref = np.zeros((n_seq, h_kv * G, D), np.float32)
+    basis16 = basis.half().float().numpy()
+    cosf, sinf = cos16.astype(np.float32), sin16.astype(np.float32)
+    for s in range(n_seq):
+        npg = pages_per_seq[s]
+        kb, vb = [], []
+        if npg:
+            st = to_np(K.k2b_export_stacks(pool, table[s, :npg].contiguous().to(dev)))
+            for p in range(npg):
+                kp, vp = blocks_from_export(st, p, g, basis16)
+                kb.append((kp, p * page, (p + 1) * page))
+                vb.append((vp, p * page, (p + 1) * page))
+        tl = tail_lens[s]
+        ref[s] = O.chunked_dequant_attention(
+            q[s].float().numpy()[:, None, :], kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead",
+            group=group, k_pre_rope=True, rope_cos=cosf, rope_sin=sinf,
+            k_tail=k_tail[s, :, :tl].float().numpy() if tl else None,
+            v_tail=v_tail[s, :, :tl].float().numpy() if tl else None,
+            n_q_groups=G, scale=scale, v_signs=signs.numpy())[:, 0, :]
+    return out.cpu().numpy(), ref
+
+
+def _assert_attn_close(out, ref, tol=2e-3):
+    """max |o - o_ref| <= tol * max |o_ref| per (sequence, head): the 2e-3 bar of the decode path."""
+    err = np.abs(out - ref).max(axis=-1)
+    den = np.abs(ref).max(axis=-1)
+    assert np.all(np.isfinite(out))
+    assert np.all(err <= tol * den), f"worst relative error {float((err / den).max()):.3e}"
+
+
+@pytest.mark.parametrize("page,rank,per_head,group,G", [(128, 32, True, 64, 4), (128, 16, False, 64, 4),
+                                                        (64, 32, True, 64, 4), (64, 16, False, 32, 2),
+                                                        (128, 32, True, 128, 8), (128, 16, True, 32, 1)])
+def test_decode_matches_oracle(page, rank, per_head, group, G):
+    dev, K = _dev(), _K()
+    out, ref = _decode_case(dev, K, n_seq=2, h_kv=2, G=G, page=page, rank=rank, per_head=per_head, group=group,
+                            pages_per_seq=[5, 3], tail_lens=[37, 200], seed=11)
+    _assert_attn_close(out, ref)
+
+
+def test_decode_ragged_and_edge_cases():
+    dev, K = _dev(), _K()
+    # ragged batch: empty committed prefix (window only), one page, odd 64-token page counts, no window
+    out, ref = _decode_case(dev, K, n_seq=4, h_kv=2, G=4, page=64, rank=32, per_head=True, group=64,
+                            pages_per_seq=[0, 1, 7, 4], tail_lens=[130, 0, 1, 255], seed=13)
+    _assert_attn_close(out, ref)
+    out, ref = _decode_case(dev, K, n_seq=3, h_kv=8, G=4, page=128, rank=32, per_head=True, group=64,
+                            pages_per_seq=[33, 0, 2], tail_lens=[128, 64, 0], seed=17)
+    _assert_attn_close(out, ref)
+
+
+def test_decode_many_tiles_per_cta():
+    # more tiles than SMs so that CTAs walk several tiles and cross (sequence, head) boundaries
+    dev, K = _dev(), _K()
+    out, ref = _decode_case(dev, K, n_seq=2, h_kv=8, G=4, page=128, rank=32, per_head=True, group=64,
+                            pages_per_seq=[40, 23], tail_lens=[128, 131], seed=19)
+    _assert_attn_close(out, ref)
+
+
+def test_reference_golden_pages_and_output():
+    """Same inputs as the reference-made fixture: exported bytes agree with the reference's stacks up
+    to rounding ties, and the decode output meets the 2e-3 bar against the reference's own output."""
+    dev, K, c = _dev(), _K(), golden("decode")
+    h_kv, G, page, rank, n_pages = 2, 4, 128, 16, 3
+    g = K.k2b_geom(h_kv, G, page, rank, 64, 1)
+    pool = K.K2bPool(g, n_pages, dev)
+    slots = torch.arange(n_pages, dtype=torch.int32, device=dev)
+    k_pre = torch.from_numpy(O.from_matrix(c["k2b_k_pre"], h_kv).copy())[None].half().contiguous()
+    v = torch.from_numpy(O.from_matrix(c["k2b_v"], h_kv).copy())[None].half().contiguous()
+    signs, cb = K.hadamard_signs(D, 0), torch.tensor(K.GAUSSIAN_CODEBOOK[2])
+    assert np.array_equal(signs.numpy(), golden("consts")["signs_d128_s0"].astype(np.float32))
+    basis = torch.from_numpy(c["k2b_Vb"])
+    K.k2b_append(pool, k_pre.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev), slots, n_pages)
+    st = to_np(K.k2b_export_stacks(pool, slots))
+    assert (st["us"][:, 0] != c["k2b_stack_us"]).mean() < 0.01
+    for name in ("res_int_packed", "v_idx_packed"):
+        assert (st[name] != c["k2b_stack_" + name]).mean() < 5e-3, name
+    assert (st["v_norm"] != c["k2b_stack_v_norm"]).mean() < 0.02
+    np.testing.assert_allclose(st["res_scale"].astype(np.float32), c["k2b_stack_res_scale"].astype(np.float32), rtol=2e-3)
+    tail_len = c["k_tail"].shape[1]
+    cos16 = torch.from_numpy(full_rope(c["rope_cos_f32"])).half()
+    sin16 = torch.from_numpy(full_rope(c["rope_sin_f32"])).half()
+    k_tail = torch.zeros(1, h_kv, 64, D, dtype=torch.float16)
+    v_tail = torch.zeros(1, h_kv, 64, D, dtype=torch.float16)
+    k_tail[0, :, :tail_len] = torch.from_numpy(c["k_tail"])
+    v_tail[0, :, :tail_len] = torch.from_numpy(c["v_tail"])
+    q = torch.from_numpy(c["q"][:, 0, :])[None].half().contiguous()
+    ws = K.decode_workspace(g, 1, n_pages, dev)
+    out = torch.empty(1, h_kv * G, D, dtype=torch.float32, device=dev)
+    K.k2b_decode(pool, q.to(dev), basis.half().to(dev), slots.view(1, -1), torch.tensor([n_pages], dtype=torch.int32, device=dev),
+                 n_pages, cos16.to(dev), sin16.to(dev), k_tail.to(dev), v_tail.to(dev),
+                 torch.tensor([tail_len], dtype=torch.int32, device=dev), K.v_lut_tensor(K.GAUSSIAN_CODEBOOK[2], dev),
+                 signs.to(dev), 1.0 / math.sqrt(D), ws, out=out)
+    torch.cuda.synchronize()
+    K.check_status(ws)
+    _assert_attn_close(out.cpu().numpy(), c["k2b_out_chunked"][:, 0, :][None])
