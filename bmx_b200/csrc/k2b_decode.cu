@@ -16,8 +16,9 @@
 //   2. rotates K_pre by the token's offset INSIDE the tile (cos/sin of those 2 offsets live in
 //        registers for the whole kernel); the tile's base rotation is applied to q instead,
 //        once per tile, by the producer warp:  q . R(t0+o) k  =  (R(-t0) q) . (R(o) k)
-//   3. scores S^T = q_rot x K^T (mma, fp32 accumulate) -- the K accumulators are already laid out
-//        as the B operand, so nothing moves;  online softmax in base 2 with a lazy rescale
+//   3. scores S = K x q_rot^T (mma, fp32 accumulate) -- the K accumulators are, in register order,
+//        the A operand, so nothing moves;  online softmax in base 2 with a lazy rescale; the
+//        weights are transposed into the B operand of step 4 with movmatrix
 //   4. values: 2-bit codes -> fp16 codebook levels with byte-permute lookups, straight into A
 //        fragments; O^T += V^T x (p * norm) (mma).  The 128-point Hadamard and the signs are
 //        applied once per (head, query) in the merge kernel, since they are linear in V.
@@ -83,6 +84,7 @@ __device__ __forceinline__ void fill_cum(int* cum, const int32_t* n_pages, int b
 }
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy was lost; report and leave
@@ -95,6 +97,28 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int
   }
   return true;
 }
+
+// Walks the flat tile list without divisions: (sequence b, head h, tile j of tiles_b) advance by one.
+struct TileCursor {
+  int b, h, j, tiles_b;
+  __device__ __forceinline__ void init(const int* cum, const int* npg, int f, int page) {
+    b = 0;
+    while (cum[b + 1] <= f) ++b;
+    tiles_b = tiles_of(npg[b], page);
+    const int rel = f - cum[b];
+    h = rel / tiles_b, j = rel - h * tiles_b;
+  }
+  __device__ __forceinline__ void next(const int* npg, int h_kv, int page, int batch) {
+    if (++j == tiles_b) {
+      j = 0;
+      if (++h == h_kv) {
+        h = 0;
+        do { ++b; } while (b < batch && npg[b] == 0);
+        tiles_b = (b < batch) ? tiles_of(npg[b], page) : 1;
+      }
+    }
+  }
+};
 
 template <int RANK, int PAGE>
 __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDecodeParams p) {
@@ -121,11 +145,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   uint64_t* full = reinterpret_cast<uint64_t*>(q_sm + 8 * HEAD_DIM);
   uint64_t* empty = full + 16;
   int* cum = reinterpret_cast<int*>(empty + 16);                                  // [batch + 1]
+  int* npg_sm = cum + p.batch + 1;                                                // [batch] page counts
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, t4 = lane & 3;
 
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, PAGE, lane);
+  for (int i = tid; i < p.batch; i += DEC_THREADS) npg_sm[i] = p.n_pages[i];
   if (tid == 0) {
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(&full[s], 1);
@@ -141,9 +167,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   const int f_end = min(total, f_begin + per_cta);
   if (f_begin >= f_end) return;
 
-  // locate the sequence of the first tile
-  int b = 0;
-  while (cum[b + 1] <= f_begin) ++b;
+  TileCursor cur;
+  cur.init(cum, npg_sm, f_begin, PAGE);
 
   if (warp >= DEC_CONSUMER_WARPS) {
     // ===================== producer warpgroup =====================
@@ -156,12 +181,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       for (int i = lane; i < QROT_BYTES / 4; i += 32) qr[i] = 0u;
     }
     int cur_bh = -1;
-    int it = 0;
-    for (int f = f_begin; f < f_end; ++f, ++it) {
-      while (cum[b + 1] <= f) ++b;
-      const int tiles_b = tiles_of(p.n_pages[b], PAGE);
-      const int rel = f - cum[b];
-      const int h = rel / tiles_b, j = rel % tiles_b;
+    int s = 0;
+    uint32_t ph = 1;  // parity to wait for on empty[s]: a fresh barrier passes parity 1
+    for (int f = f_begin; f < f_end; ++f, cur.next(npg_sm, g.h_kv, PAGE, p.batch)) {
+      const int b = cur.b, h = cur.h, j = cur.j;
       const int bh = b * g.h_kv + h;
       if (bh != cur_bh) {
         cur_bh = bh;
@@ -170,8 +193,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
         for (int i = lane; i < G * HEAD_DIM; i += 32) q_sm[i] = __half2float(qsrc[i]) * p.scale_log2;
         __syncwarp();
       }
-      const int s = it % n_stages;
-      if (!wait_or_flag(&empty[s], ((it / n_stages) & 1) ^ 1, p.status, 1)) return;
+      if (!wait_or_flag(&empty[s], ph, p.status, 1)) return;
       uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
       // q rotated back by the tile's base position
       {
@@ -188,14 +210,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
             // channel ch -> k-step ch/16, register (ch%16)/8, t = (ch%8)/2, e = ch%2
             const int ks1 = c >> 4, r1 = (c >> 3) & 1, tt = (c & 7) >> 1, e = c & 1;
             const int ks2 = ks1 + 4;
-            qr[(((qi * 4 + tt) * 8 + ks1) * 2 + r1) * 2 + e] = __float2half_rn(y1);
-            qr[(((qi * 4 + tt) * 8 + ks2) * 2 + r1) * 2 + e] = __float2half_rn(y2);
+            // B fragment of k-step ks: word ((ks/2)*32 + 4*qi + tt)*4 + (ks%2)*2 + r1
+            qr[((((ks1 >> 1) * 32 + qi * 4 + tt) * 4 + (ks1 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y1);
+            qr[((((ks2 >> 1) * 32 + qi * 4 + tt) * 4 + (ks2 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y2);
           }
         }
       }
       __syncwarp();
       if (lane == 0) {
-        const int np = p.n_pages[b];
+        const int np = npg_sm[b];
         const int pg0 = j * PAGES_PER_TILE;
         const int npg = min(PAGES_PER_TILE, np - pg0);
         const int chd = (g.n_coef_heads == 1) ? 0 : h;
@@ -208,6 +231,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
           bulk_g2s(st + COEF_TILE_BYTES + k * PB, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &full[s]);
         }
       }
+      if (++s == n_stages) s = 0, ph ^= 1;
     }
     return;
   }
@@ -215,7 +239,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   // ===================== consumer warps =====================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
   // loop-invariant rotation of the two token rows this lane owns (offsets inside the tile)
-  uint32_t cosr[2][8], sinr[2][8];
+  uint32_t cosr[2][8], sinr[2][8], nsinr[2][8];
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const int dlt = 16 * warp + 8 * c + gq;
@@ -223,12 +247,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
     for (int n = 0; n < 8; ++n) {
       cosr[c][n] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)dlt * HEAD_DIM + 8 * n + 2 * t4);
       sinr[c][n] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)dlt * HEAD_DIM + 8 * n + 2 * t4);
+      nsinr[c][n] = sinr[c][n] ^ 0x80008000u;
     }
   }
   uint32_t Bb[16][KS][2];
   float O[8][4];
-  // query rows beyond the group size keep a finite maximum so that their (unused) lanes stay finite
-  float m_run = (gq < G) ? -INFINITY : 0.f, l_run = 0.f, pn_run = 0.f;
+  // this lane owns queries 2t and 2t+1; columns beyond the group size keep a finite maximum so that
+  // their (unused) values stay finite
+  float m0 = (2 * t4 < G) ? -INFINITY : 0.f, m1 = (2 * t4 + 1 < G) ? -INFINITY : 0.f;
+  float l0 = 0.f, l1 = 0.f, pn0 = 0.f, pn1 = 0.f;
   int cur_bh = -1, cur_b = 0, cur_h = 0;
   const int sub_page = warp / WR_PER_PAGE, wr = warp % WR_PER_PAGE;
   const int grp = (16 * wr) / g.group;
@@ -237,15 +264,16 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
 
   auto flush = [&](int b_, int h_) {
-    // reduce over the 4 lanes of a quad, then over the 8 warps through shared memory
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    pn_run += __shfl_xor_sync(0xffffffffu, pn_run, 1);
-    pn_run += __shfl_xor_sync(0xffffffffu, pn_run, 2);
-    if (t4 == 0) {
-      red_m[warp * 8 + gq] = m_run;
-      red_l[warp * 8 + gq] = l_run;
-      red_pn[warp * 8 + gq] = pn_run;
+    // sums over this warp's tokens (the 8 lanes that share t), then over the 8 warps through shared memory
+#pragma unroll
+    for (int m = 4; m <= 16; m <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, m), l1 += __shfl_xor_sync(0xffffffffu, l1, m);
+      pn0 += __shfl_xor_sync(0xffffffffu, pn0, m), pn1 += __shfl_xor_sync(0xffffffffu, pn1, m);
+    }
+    if (gq == 0) {
+      red_m[warp * 8 + 2 * t4] = m0, red_m[warp * 8 + 2 * t4 + 1] = m1;
+      red_l[warp * 8 + 2 * t4] = l0, red_l[warp * 8 + 2 * t4 + 1] = l1;
+      red_pn[warp * 8 + 2 * t4] = pn0, red_pn[warp * 8 + 2 * t4 + 1] = pn1;
     }
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
@@ -280,19 +308,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
     asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMER_WARPS * 32));
   };
 
-  int it = 0;
+  int s = 0;
+  uint32_t ph = 0;
   bool dead = false;
-  for (int f = f_begin; f < f_end; ++f, ++it) {
-    while (cum[b + 1] <= f) ++b;
-    const int np = p.n_pages[b];
-    const int tiles_b = tiles_of(np, PAGE);
-    const int rel = f - cum[b];
-    const int h = rel / tiles_b, j = rel % tiles_b;
+  for (int f = f_begin; f < f_end; ++f, cur.next(npg_sm, g.h_kv, PAGE, p.batch)) {
+    const int b = cur.b, h = cur.h, j = cur.j;
     const int bh = b * g.h_kv + h;
     if (bh != cur_bh) {
       if (cur_bh >= 0) flush(cur_b, cur_h);
       cur_bh = bh, cur_b = b, cur_h = h;
-      m_run = (gq < G) ? -INFINITY : 0.f, l_run = 0.f, pn_run = 0.f;
+      m0 = (2 * t4 < G) ? -INFINITY : 0.f, m1 = (2 * t4 + 1 < G) ? -INFINITY : 0.f;
+      l0 = l1 = pn0 = pn1 = 0.f;
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) O[mt][0] = O[mt][1] = O[mt][2] = O[mt][3] = 0.f;
 #pragma unroll
@@ -304,11 +330,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
           Bb[n][ks][1] = *reinterpret_cast<const uint32_t*>(bp + 8);
         }
     }
-    const int s = it % n_stages;
     // After a wait has given up this warp stops computing but keeps walking the loop, so that it still
     // meets the other consumer warps at every named barrier.
-    if (!dead && !wait_or_flag(&full[s], (it / n_stages) & 1, p.status, 2)) dead = true;
-    const int valid_pages = min(PAGES_PER_TILE, np - j * PAGES_PER_TILE);
+    if (!dead && !wait_or_flag(&full[s], ph, p.status, 2)) dead = true;
+    const int valid_pages = (PAGES_PER_TILE == 1) ? 1 : min(PAGES_PER_TILE, npg_sm[b] - j * PAGES_PER_TILE);
     if (!dead && sub_page < valid_pages) {
       const uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
       const uint8_t* blk = st + COEF_TILE_BYTES + sub_page * PB;
@@ -329,11 +354,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       {
         const uint4 w0 = *reinterpret_cast<const uint4*>(blk + ((wr * 2 + 0) * 32 + lane) * 16);
         const uint4 w1 = *reinterpret_cast<const uint4*>(blk + ((wr * 2 + 1) * 32 + lane) * 16);
-        const uint4* scp = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(PAGE) + (grp * 128 + t4 * 32) * 2);
+        const uint4* scp = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(PAGE) + (grp * 128 + t4 * 8) * 2);
         uint32_t sc[16];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint4 v = scp[k];
+          const uint4 v = scp[4 * k];
           sc[4 * k] = v.x, sc[4 * k + 1] = v.y, sc[4 * k + 2] = v.z, sc[4 * k + 3] = v.w;
         }
         const uint32_t ww[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
@@ -367,50 +392,30 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const __half2 lo = u32_as_h2(acc[n][c]), hi = u32_as_h2(acc[n + 8][c]);
-          const __half2 cs = u32_as_h2(cosr[c][n]), sn = u32_as_h2(sinr[c][n]);
-          const __half2 lo2 = __hfma2(lo, cs, __hneg2(__hmul2(hi, sn)));
+          const __half2 cs = u32_as_h2(cosr[c][n]), sn = u32_as_h2(sinr[c][n]), nsn = u32_as_h2(nsinr[c][n]);
+          const __half2 lo2 = __hfma2(lo, cs, __hmul2(hi, nsn));
           const __half2 hi2 = __hfma2(hi, cs, __hmul2(lo, sn));
           acc[n][c] = h2_as_u32(lo2);
           acc[n + 8][c] = h2_as_u32(hi2);
         }
-      // ---- scores (transposed): rows = queries, columns = this warp's 16 tokens ----
-      float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      // ---- scores: rows = this warp's 16 tokens, columns = queries.  The K accumulators of n-tiles
+      //      2ks, 2ks+1 are, in register order, exactly the A fragment of k-step ks ----
+      float S[4] = {0.f, 0.f, 0.f, 0.f};  // (token g; q 2t, 2t+1), (token g+8; q 2t, 2t+1)
+      float S2[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the dependent mma chain
       {
-        const uint4* qp = reinterpret_cast<const uint4*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB + (gq * 4 + t4) * 64);
+        const uint4* qp = reinterpret_cast<const uint4*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB) + lane;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          const uint4 v = qp[k4];  // k-steps 2*k4 and 2*k4+1
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            mma_f32acc(S[c][0], S[c][1], S[c][2], S[c][3], v.x, v.x, v.y, v.y, acc[4 * k4][c], acc[4 * k4 + 1][c]);
-            mma_f32acc(S[c][0], S[c][1], S[c][2], S[c][3], v.z, v.z, v.w, v.w, acc[4 * k4 + 2][c], acc[4 * k4 + 3][c]);
-          }
+          const uint4 v = qp[32 * k4];  // B fragments of k-steps 2*k4 and 2*k4+1
+          mma_f32acc(S[0], S[1], S[2], S[3], acc[4 * k4][0], acc[4 * k4][1], acc[4 * k4 + 1][0], acc[4 * k4 + 1][1], v.x, v.y);
+          mma_f32acc(S2[0], S2[1], S2[2], S2[3], acc[4 * k4 + 2][0], acc[4 * k4 + 2][1], acc[4 * k4 + 3][0], acc[4 * k4 + 3][1], v.z, v.w);
         }
-      }
-      // ---- online softmax, base 2, rescale only when the maximum moved by more than 2^8 ----
-      float tmax = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-      const bool need = (gq < G) && (tmax > m_run + 8.f);
-      if (__any_sync(0xffffffffu, need)) {
-        const float m_new = need ? tmax : m_run;
-        const float fsc = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
-        const float f = need ? fsc : 1.f;
-        l_run *= f, pn_run *= f, m_run = m_new;
-        const float f0 = __shfl_sync(0xffffffffu, f, (2 * t4) << 2), f1 = __shfl_sync(0xffffffffu, f, (2 * t4 + 1) << 2);
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) O[mt][0] *= f0, O[mt][1] *= f1, O[mt][2] *= f0, O[mt][3] *= f1;
+        for (int i = 0; i < 4; ++i) S[i] += S2[i];
       }
-      const float p00 = ex2_approx(S[0][0] - m_run), p01 = ex2_approx(S[0][1] - m_run);
-      const float p10 = ex2_approx(S[1][0] - m_run), p11 = ex2_approx(S[1][1] - m_run);
-      l_run += (p00 + p01) + (p10 + p11);
-      const __half* vn = reinterpret_cast<const __half*>(blk + k2b_off_vnorm(PAGE, g.group)) + 16 * wr + 2 * t4;
-      const float2 n01 = __half22float2(*reinterpret_cast<const __half2*>(vn));
-      const float2 n23 = __half22float2(*reinterpret_cast<const __half2*>(vn + 8));
-      const float w00 = p00 * n01.x, w01 = p01 * n01.y, w10 = p10 * n23.x, w11 = p11 * n23.y;
-      pn_run += (w00 + w01) + (w10 + w11);
-      const uint32_t pb0 = h2_as_u32(__floats2half2_rn(w00, w01)), pb1 = h2_as_u32(__floats2half2_rn(w10, w11));
-      // ---- values: codes -> fp16 levels (A fragments), O^T += V^T x P ----
+      // ---- values: 2-bit codes -> fp16 levels, directly as the A fragments of O^T += V^T P.  Done here,
+      //      ahead of the softmax, so that these independent byte permutes fill the mma/shuffle latencies ----
+      uint32_t VA[8][4];
       {
         const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
         const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
@@ -422,16 +427,50 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
             const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
             const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
             const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
-            const uint32_t a0 = prmt(lo0, hi0, 0x5140u), a1 = prmt(lo0, hi0, 0x7362u);
-            const uint32_t a2 = prmt(lo1, hi1, 0x5140u), a3 = prmt(lo1, hi1, 0x7362u);
             const int mt = 2 * jw + hs;
-            mma_f32acc(O[mt][0], O[mt][1], O[mt][2], O[mt][3], a0, a1, a2, a3, pb0, pb1);
+            VA[mt][0] = prmt(lo0, hi0, 0x5140u), VA[mt][1] = prmt(lo0, hi0, 0x7362u);
+            VA[mt][2] = prmt(lo1, hi1, 0x5140u), VA[mt][3] = prmt(lo1, hi1, 0x7362u);
           }
         }
       }
+      // ---- online softmax, base 2; this lane owns queries 2t and 2t+1.  The running maximum only
+      //      moves when a tile exceeds it by more than 2^8 (the sums stay far from overflow) ----
+      {
+        __half2 tm = __floats2half2_rn(fmaxf(S[0], S[2]), fmaxf(S[1], S[3]));
+        tm = __hmax2(tm, u32_as_h2(__shfl_xor_sync(0xffffffffu, h2_as_u32(tm), 4)));
+        tm = __hmax2(tm, u32_as_h2(__shfl_xor_sync(0xffffffffu, h2_as_u32(tm), 8)));
+        tm = __hmax2(tm, u32_as_h2(__shfl_xor_sync(0xffffffffu, h2_as_u32(tm), 16)));
+        const float2 tmf = __half22float2(tm);
+        // fp16 rounds the maximum by at most 2^-11 relative; add a margin so that exp2 stays <= 2^9
+        const bool need0 = (2 * t4 < G) && (tmf.x > m0 + 8.f), need1 = (2 * t4 + 1 < G) && (tmf.y > m1 + 8.f);
+        if (__any_sync(0xffffffffu, need0 || need1)) {
+          const float n0 = need0 ? tmf.x + 0.5f : m0, n1 = need1 ? tmf.y + 0.5f : m1;
+          const float f0 = (m0 == -INFINITY) ? 0.f : ex2_approx(m0 - n0), f1 = (m1 == -INFINITY) ? 0.f : ex2_approx(m1 - n1);
+          l0 *= f0, l1 *= f1, pn0 *= f0, pn1 *= f1, m0 = n0, m1 = n1;
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) O[mt][0] *= f0, O[mt][1] *= f1, O[mt][2] *= f0, O[mt][3] *= f1;
+        }
+      }
+      uint32_t pb0, pb1;
+      {
+        const float p0 = ex2_approx(S[0] - m0), p1 = ex2_approx(S[1] - m1);
+        const float p2 = ex2_approx(S[2] - m0), p3 = ex2_approx(S[3] - m1);
+        l0 += p0 + p2, l1 += p1 + p3;
+        const __half* vn = reinterpret_cast<const __half*>(blk + k2b_off_vnorm(PAGE, g.group)) + 16 * wr + gq;
+        const float na = __half2float(vn[0]), nb = __half2float(vn[8]);
+        const float w0 = p0 * na, w1 = p1 * na, w2 = p2 * nb, w3 = p3 * nb;
+        pn0 += w0 + w2, pn1 += w1 + w3;
+        // (token g; q 2t, 2t+1) -> transpose -> (q g; tokens 2t, 2t+1): the B fragment of O^T += V^T P
+        pb0 = movmatrix_trans(h2_as_u32(__floats2half2_rn(w0, w1)));
+        pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(w2, w3)));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt)
+        mma_f32acc(O[mt][0], O[mt][1], O[mt][2], O[mt][3], VA[mt][0], VA[mt][1], VA[mt][2], VA[mt][3], pb0, pb1);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);
+    if (++s == n_stages) s = 0, ph ^= 1;
   }
   if (cur_bh >= 0) flush(cur_b, cur_h);
 }
@@ -600,7 +639,7 @@ static size_t decode_stage_bytes(const bmxk_k2b_geom* g) {
   return (size_t)TILE_TOKENS * g->rank * 2 + (size_t)(TILE_TOKENS / g->page) * k2b_page_block_bytes(g->page, g->group) + 8 * 4 * 8 * 8;
 }
 static size_t decode_fixed_smem(int batch) {
-  return (size_t)(DEC_CONSUMER_WARPS * 8 * HEAD_DIM + 3 * 64 + 8 * HEAD_DIM) * 4 + 32 * 8 + (size_t)(batch + 1) * 4 + 16;
+  return (size_t)(DEC_CONSUMER_WARPS * 8 * HEAD_DIM + 3 * 64 + 8 * HEAD_DIM) * 4 + 32 * 8 + (size_t)(2 * batch + 1) * 4 + 16;
 }
 
 template <int RANK, int PAGE>

@@ -25,7 +25,9 @@
 //   -> a lane's (token g or g+8) x (channels 8n+2t, 8n+2t+1) codes sit in matching nibbles of
 //      the low and high halves of a word: one LOP3 turns them into a half2.
 // K residual scale (fp16, per channel per `group` tokens):
-//   half index  grp*128 + t*32 + n*2 + e      (grp = r / group)
+//   half index  grp*128 + (n/4)*32 + t*8 + (n%4)*2 + e      (grp = r / group)
+//   -> the four 16-byte chunks a lane reads are 64 bytes apart and the four t of a quad are
+//      adjacent, so a quarter-warp's 128-bit loads fall in distinct banks
 // V code (2-bit index for (row r, channel c)):
 //   wr = r / 16, rr = r % 16; mt = c / 16 (16-channel tile), cc = c % 16
 //   g = cc % 8, chi = cc / 8 ; t = (rr % 8) / 2, e = rr % 2, thi = rr / 8
@@ -76,7 +78,7 @@ BMXK_HD void k2b_kres_loc(int r, int c, int& word, int& bit) {
 }
 BMXK_HD int k2b_kscale_idx(int grp, int c) {
   const int n = c >> 3, t = (c & 7) >> 1, e = c & 1;
-  return grp * 128 + t * 32 + n * 2 + e;
+  return grp * 128 + (n >> 2) * 32 + t * 8 + (n & 3) * 2 + e;
 }
 BMXK_HD void k2b_vcode_loc(int r, int c, int& word, int& bit) {
   const int wr = r >> 4, rr = r & 15;

@@ -253,7 +253,7 @@ def test_reference_golden_pages_and_output():
     v = torch.from_numpy(O.from_matrix(c["k2b_v"], h_kv).copy())[None].half().contiguous()
     signs, cb = K.hadamard_signs(D, 0), torch.tensor(K.GAUSSIAN_CODEBOOK[2])
     assert np.array_equal(signs.numpy(), golden("consts")["signs_d128_s0"].astype(np.float32))
-    basis = torch.from_numpy(c["k2b_Vb"])
+    basis = torch.from_numpy(np.ascontiguousarray(c["k2b_Vb"]))
     K.k2b_append(pool, k_pre.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev), slots, n_pages)
     st = to_np(K.k2b_export_stacks(pool, slots))
     assert (st["us"][:, 0] != c["k2b_stack_us"]).mean() < 0.01
