@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the packed k2b KV-cache decode path (one attention layer-step).
+
+Workload (synthetic, seeded): Llama-3.1-8B head shape (32 query heads, 8 KV heads, head dim 128),
+B = 8 sequences, 32768 committed tokens + a 128-token fp16 window per sequence; keys pre-RoPE with
+a per-head rank-32 basis and a 3-bit residual, values Hadamard + 2-bit Lloyd codes, RoPE theta
+500000 applied at read.  One step = one decode call over the whole batch (two kernel launches).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank holds its own B = 8 batch: KV heads
+and sequences are independent, so the path shards with no collective ("weak" scaling); the time is
+the maximum over ranks.  `--impl reference` times the CPU restatement of the reference's chunked
+dequant-attention (oracle/) on the host cores over a bounded sample of the same workload.
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H_KV, G, D, RANK, PAGE, GROUP, WINDOW = 8, 4, 128, 32, 128, 64, 128
+BATCH, CTX = 8, 32768
+BYTES_PER_UNIT = 166  # per (token, kv head): coefficients 64 + residual nibbles 64 + scales 4 + value codes 32 + norm 2
+ROPE_THETA = 500000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_kernel launch, from the ncu capture
+# summarised in profiles/k2b_decode_kernel_B8_T16384.md (174.4 + 4.3 MB at 16384 tokens), scaled by 2
+# to this workload's 32768 tokens (the kernel streams every page once, so traffic grows with tokens).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.37e6 + 4.26e6)
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic workload
+# ------------------------------------------------------------------------------------------------
+
+def make_basis(gen, device):
+    import torch
+
+    basis = torch.zeros(H_KV * D, RANK, device=device)
+    for h in range(H_KV):
+        Q, R = torch.linalg.qr(torch.randn(D, RANK, generator=gen, device=device))
+        basis[h * D:(h + 1) * D] = Q * torch.sign(torch.diagonal(R))
+    return basis
+
+
+def make_kv(gen, basis, n_seq, T, device):
+    """Pre-RoPE keys = per-head low-rank signal (spectrum i^-1.5) + 0.1 N(0,1); values N(0,1)."""
+    import torch
+
+    decay = torch.arange(1, RANK + 1, device=device).float() ** -1.5
+    coef = torch.randn(n_seq, H_KV, T, RANK, generator=gen, device=device) * decay
+    k = torch.einsum("bhtr,hcr->bhtc", coef, basis.view(H_KV, D, RANK))
+    k = (k + 0.1 * torch.randn(n_seq, H_KV, T, D, generator=gen, device=device)).half()
+    v = torch.randn(n_seq, H_KV, T, D, generator=gen, device=device).half()
+    return k, v
+
+
+def build_state(device, seed, batch=BATCH, ctx=CTX):
+    """A K2bLayerState holding `ctx` committed tokens + a full window, filled through the append kernel."""
+    import torch
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope, default_rope_tables
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    total = ctx + WINDOW
+    cos, sin = default_rope_tables(ROPE_THETA, D, total + 4096, device=device)
+    geom = K.k2b_geom(H_KV, G, PAGE, RANK, GROUP, H_KV)
+    state = K2bLayerState(geom, batch, total + 4096, WINDOW, device, cos.half(), sin.half())
+    basis = make_basis(gen, device)
+    state.set_basis(basis)
+    # one sequence at a time through a scratch state keeps the transient fp16 K/V small
+    for b in range(batch):
+        k_pre, v = make_kv(gen, basis, 1, total, device)
+        k_post = apply_rope(k_pre.float(), cos[:total], sin[:total]).half()
+        n_pg = ctx // PAGE
+        slots = state.page_table[b, :n_pg].contiguous()
+        K.k2b_append(state.pool, k_pre, v, state.basis_f32, state.signs, state.codebook, slots, n_pg)
+        state.k_win[b, :, :WINDOW] = k_post[0, :, ctx:]
+        state.v_win[b, :, :WINDOW] = v[0, :, ctx:]
+        state.k_pre_win[b, :, :WINDOW] = k_pre[0, :, ctx:]
+    state.committed, state.tail_len = ctx, WINDOW
+    state.n_pages_dev.fill_(ctx // PAGE)
+    state.tail_len_dev.fill_(WINDOW)
+    q = (torch.randn(batch, H_KV * G, D, generator=gen, device=device) / math.sqrt(D)).half()
+    return state, q, gen, basis, (cos, sin)
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's chunked dequant-attention over a bounded sample of the same workload
+# ------------------------------------------------------------------------------------------------
+
+def cpu_reference_arm(budget_s: float = 12.0, seed: int = 2000):
+    """Times oracle.chunked_dequant_attention (numpy, all BLAS threads) on n pages of one sequence
+    (8 KV heads, 32 query heads), pages quantized by the oracle codec.  Returns (GB/s of packed
+    bytes consumed, cores used, sample description, us per full layer-step extrapolated)."""
+    import numpy as np
+    import torch  # only for the seeded sign vector, as the reference draws it
+
+    from oracle import bmx_oracle as O
+
+    rng = np.random.default_rng(seed)
+    C = H_KV * D
+    basis = np.zeros((C, H_KV * RANK), np.float32)  # block-diagonal: one rank-32 basis per head
+    for h in range(H_KV):
+        Qm, _ = np.linalg.qr(rng.standard_normal((D, RANK)).astype(np.float32))
+        basis[h * D:(h + 1) * D, h * RANK:(h + 1) * RANK] = Qm
+    g = torch.Generator().manual_seed(0)
+    signs = (torch.randint(0, 2, (D,), generator=g) * 2 - 1).numpy().astype(np.float32)
+    decay = (np.arange(1, RANK + 1, dtype=np.float32) ** -1.5)
+    cos, sin = O.default_rope_tables(ROPE_THETA, D, 64 * PAGE)
+    cos16, sin16 = cos.astype(np.float16).astype(np.float32), sin.astype(np.float16).astype(np.float32)
+    q = (rng.standard_normal((H_KV * G, 1, D)) / math.sqrt(D)).astype(np.float32)
+
+    def make_pages(n):
+        kb, vb = [], []
+        for p in range(n):
+            coef = rng.standard_normal((PAGE, H_KV * RANK)).astype(np.float32) * np.tile(decay, H_KV)
+            Mk = (coef @ basis.T + 0.1 * rng.standard_normal((PAGE, C)).astype(np.float32)).astype(np.float16).astype(np.float32)
+            Mv = rng.standard_normal((PAGE, C)).astype(np.float16).astype(np.float32)
+            kp, _ = O.quantize_packed("lowrank_rtn_channel", Mk, bits=3, group=GROUP, rank=RANK, svd_factors=(Mk @ basis, basis))
+            vp, _ = O.quantize_packed("turboquant_mse_perhead", Mv, bits=2, h_heads=H_KV, signs=signs)
+            kb.append((kp, p * PAGE, (p + 1) * PAGE))
+            vb.append((vp, p * PAGE, (p + 1) * PAGE))
+        return kb, vb
+
+    def run(kb, vb):
+        t0 = time.perf_counter()
+        O.chunked_dequant_attention(q, kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead", group=GROUP,
+                                    k_pre_rope=True, rope_cos=cos16, rope_sin=sin16, k_tail=None, v_tail=None,
+                                    n_q_groups=G, scale=1.0 / math.sqrt(D), v_signs=signs)
+        return time.perf_counter() - t0
+
+    kb, vb = make_pages(4)
+    run(kb, vb)
+    per_page = run(kb, vb) / 4
+    n = int(max(4, min(64, budget_s / max(per_page, 1e-4))))
+    kb, vb = make_pages(n)
+    dt = run(kb, vb)
+    units = n * PAGE * H_KV
+    gbs = units * BYTES_PER_UNIT / dt / 1e9
+    full_us = dt / units * (BATCH * H_KV * CTX) * 1e6
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    sample = f"{n} pages x {PAGE} tokens x {H_KV} kv heads of one sequence ({units} of {BATCH * H_KV * CTX} units), numpy oracle"
+    return gbs, cores, sample, full_us
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    gbs, cores, sample, full_us = cpu_reference_arm(budget_s=max(5.0, min(30.0, 4.0 * args.steps)))
+    line = {
+        "impl": "reference", "metric": "k2b_decode_effective_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_us / 1e3, "us_per_layer_step": full_us,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "k2b packed-cache decode, 1 layer-step: Llama-3.1-8B heads (32 q / 8 kv, d=128), B=8 per GPU, "
+                        "T=32768 committed + 128-token fp16 window, K rank-32 per-head basis + 3-bit residual (group 64), "
+                        "V Hadamard + 2-bit Lloyd, RoPE theta 5e5 at read, 128-token pages",
+            "batch_per_gpu": BATCH, "context": CTX, "window": WINDOW, "page": PAGE, "rank": RANK,
+            "bytes_per_token_head": BYTES_PER_UNIT, "parallelism": f"kv-head/batch shards x{n_gpus}, no collective",
+            "l2": "packed pages read per step (348 MB per GPU) exceed the 126 MB L2; no explicit flush"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    state, q, gen, basis, (cos, sin) = build_state(device, seed=2000 + rank)
+    from bmx_b200 import kernels as K
+
+    out = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16, device=device)
+    units = BATCH * H_KV * CTX
+    algo_bytes = units * BYTES_PER_UNIT
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        state.decode(q, out=out)
+    torch.cuda.synchronize()
+    K.check_status(state.workspace)
+
+    # ---- device-resident steps: K decode calls back to back; the dominant kernel is timed apart with
+    #      events on the launching stream (phase 1 = page-streaming kernel, phase 2 = merge kernel) ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            ev[i][0].record()
+            state.decode(q, out=out, phases=1)
+            ev[i][1].record()
+            state.decode(q, out=out, phases=2)
+            ev[i][2].record()
+        e1.record()
+        barrier()
+    total_ms = e0.elapsed_time(e1)
+    main_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    merge_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    K.check_status(state.workspace)
+
+    # ---- end to end through the layer-state API with host buffers: per step the new token's K/V and
+    #      the query come from pinned host memory, the attention output goes back to the host ----
+    n_e2e = min(args.steps, 64)
+    hq = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16).pin_memory()
+    hq.copy_(q.cpu())
+    hk = torch.randn(BATCH, H_KV, 1, D).half().pin_memory()
+    hv = torch.randn(BATCH, H_KV, 1, D).half().pin_memory()
+    hout = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty(BATCH, H_KV, 1, D, dtype=torch.float16, device=device), \
+        torch.empty(BATCH, H_KV, 1, D, dtype=torch.float16, device=device)
+    h2d = hq.numel() * 2 + 2 * hk.numel() * 2 + hv.numel() * 2  # q, k_pre, k_post, v
+    d2h = hout.numel() * 2
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        state.append(dk, dk, dv)
+        state.decode(dq, out=out)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    g1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(g0.elapsed_time(g1), (time.perf_counter() - t0) * 1e3) / n_e2e
+
+    t = torch.tensor([total_ms, main_ms, merge_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, main_ms, merge_ms, e2e_ms = t.tolist()
+    ms_per_step = total_ms / args.steps
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        achieved = algo_bytes / (main_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1:
+            gbs, cores, sample, full_us = cpu_reference_arm(budget_s=10.0)
+            cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                   "us_per_layer_step_extrapolated": full_us}
+        line = {
+            "metric": "k2b_decode_effective_GBps", "value": world * algo_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "us_per_layer_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+            "frac_of_8TBps": world * algo_bytes / (ms_per_step * 1e-3) / 1e9 / (8000.0 * world),
+            "roofline": {"bound": "hbm", "kernel": "k2b_decode_kernel<32,128>", "achieved": achieved, "peak": peak,
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": algo_bytes,
+                         "kernel_us": main_ms * 1e3, "merge_kernel_us": merge_ms * 1e3},
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer_step": e2e_ms * 1e3,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -337,6 +337,29 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
     if (!dead && sub_page < valid_pages) {
       const uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
       const uint8_t* blk = st + COEF_TILE_BYTES + sub_page * PB;
+      // ---- values: 2-bit codes -> fp16 levels, directly as the A fragments of O^T += V^T P.  The two warps that
+      //      share a scheduler do this ALU-bound step at opposite ends of the key work (FMA and tensor bound),
+      //      so that the pipes overlap ----
+      uint32_t VA[8][4];
+      auto unpack_v = [&]() {
+        const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
+        const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+        for (int jw = 0; jw < 4; ++jw) {
+          const uint32_t x0 = vv[jw] & 0x33333333u, x1 = (vv[jw] >> 2) & 0x33333333u;
+#pragma unroll
+          for (int hs = 0; hs < 2; ++hs) {
+            const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
+            const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
+            const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
+            const int mt = 2 * jw + hs;
+            VA[mt][0] = prmt(lo0, hi0, 0x5140u), VA[mt][1] = prmt(lo0, hi0, 0x7362u);
+            VA[mt][2] = prmt(lo1, hi1, 0x5140u), VA[mt][3] = prmt(lo1, hi1, 0x7362u);
+          }
+        }
+      };
+      const bool v_first = (warp >> 2) & 1;
+      if (v_first) unpack_v();
       // ---- low-rank coefficients as A fragments ----
       uint32_t A[KS][4];
       {
@@ -413,26 +436,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 #pragma unroll
         for (int i = 0; i < 4; ++i) S[i] += S2[i];
       }
-      // ---- values: 2-bit codes -> fp16 levels, directly as the A fragments of O^T += V^T P.  Done here,
-      //      ahead of the softmax, so that these independent byte permutes fill the mma/shuffle latencies ----
-      uint32_t VA[8][4];
-      {
-        const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
-        const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
-#pragma unroll
-        for (int jw = 0; jw < 4; ++jw) {
-          const uint32_t x0 = vv[jw] & 0x33333333u, x1 = (vv[jw] >> 2) & 0x33333333u;
-#pragma unroll
-          for (int hs = 0; hs < 2; ++hs) {
-            const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
-            const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
-            const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
-            const int mt = 2 * jw + hs;
-            VA[mt][0] = prmt(lo0, hi0, 0x5140u), VA[mt][1] = prmt(lo0, hi0, 0x7362u);
-            VA[mt][2] = prmt(lo1, hi1, 0x5140u), VA[mt][3] = prmt(lo1, hi1, 0x7362u);
-          }
-        }
-      }
+      if (!v_first) unpack_v();
       // ---- online softmax, base 2; this lane owns queries 2t and 2t+1.  The running maximum only
       //      moves when a tile exceeds it by more than 2^8 (the sums stay far from overflow) ----
       {
@@ -675,8 +679,9 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
                     const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail,
                     const void* v_tail, const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs,
                     float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* partial_out,
-                    void* stream) {
+                    int phases, void* stream) {
   BMXK_REQUIRE(g != nullptr, "bmxk_k2b_decode: null geometry");
+  BMXK_REQUIRE(phases >= 1 && phases <= 3, "bmxk_k2b_decode: phases=%d must be 1, 2 or 3", phases);
   BMXK_REQUIRE(g->h_kv >= 1 && g->n_q_groups >= 1 && g->n_q_groups <= 8, "bmxk_k2b_decode: h_kv=%d n_q_groups=%d", g->h_kv,
                g->n_q_groups);
   BMXK_REQUIRE(g->page == 64 || g->page == 128, "bmxk_k2b_decode: page=%d must be 64 or 128", g->page);
@@ -707,7 +712,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   memcpy(&alpha, &v_lut[2], 4);
   memcpy(&beta, &v_lut[3], 4);
 
-  if (max_pages > 0) {
+  if (max_pages > 0 && (phases & 1)) {
     K2bDecodeParams prm;
     prm.g.h_kv = g->h_kv, prm.g.n_q_groups = g->n_q_groups, prm.g.page = g->page, prm.g.rank = g->rank;
     prm.g.group = g->group, prm.g.n_coef_heads = g->n_coef_heads, prm.g.kbits = g->kbits, prm.g.vbits = g->vbits;
@@ -729,6 +734,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
     else rc = launch_decode<16, 64>(prm, grid, smem, s);
     if (rc) return rc;
   }
+  if (!(phases & 2)) return BMXK_OK;
   K2bMergeParams mp;
   mp.g.h_kv = g->h_kv, mp.g.n_q_groups = g->n_q_groups, mp.g.page = g->page, mp.g.rank = g->rank, mp.g.group = g->group;
   mp.g.n_coef_heads = g->n_coef_heads, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits;

@@ -1,0 +1,143 @@
+"""Device-resident state of one attention layer's packed k2b cache, batched over sequences.
+
+This is the B200-native counterpart of the state bmx keeps per `PackedStreamingLayer`
+(bmx: src/bmx/cache/packed_streaming.py:321-446): committed tokens live as packed pages in a page
+pool, the most recent `recent_window .. recent_window + page` tokens live as fp16 in a window
+buffer, and the flush schedule is bmx's (`compute_flush_schedule`, src/bmx/cache/streaming.py:144).
+Differences by design: pages are written by one CUDA launch straight into the layout the decode
+kernel reads (no per-page Python dicts, no re-stacking), all sequences of a batch advance in lock
+step, and a decode step is two launches with no allocation.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import kernels as K
+from .schedule import compute_flush_schedule
+
+HEAD_DIM = K.HEAD_DIM
+
+
+class K2bLayerState:
+    """Packed pages + fp16 recent window of one layer for `batch` sequences of equal length."""
+
+    def __init__(self, geom, batch: int, max_tokens: int, recent_window: int, device, rope_cos: torch.Tensor,
+                 rope_sin: torch.Tensor, *, codebook=None, v_seed: int = 0, pre_rope: bool = True):
+        assert rope_cos.dtype == torch.float16 and rope_cos.shape[1] == HEAD_DIM and rope_cos.shape[0] >= 128
+        self.geom, self.batch, self.device = geom, batch, torch.device(device)
+        self.page, self.W, self.pre_rope = geom.page, recent_window, pre_rope
+        self.max_pages = max(1, math.ceil(max_tokens / geom.page))
+        self.pool = K.K2bPool(geom, batch * self.max_pages, self.device)
+        self.page_table = torch.arange(batch * self.max_pages, dtype=torch.int32, device=self.device).view(batch, -1)
+        self.n_pages_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_len_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_cap = recent_window + geom.page
+        shape = (batch, geom.h_kv, self.tail_cap, HEAD_DIM)
+        self.k_win = torch.zeros(shape, dtype=torch.float16, device=self.device)      # post-RoPE keys
+        self.v_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.k_pre_win = torch.zeros(shape, dtype=torch.float16, device=self.device)  # pre-RoPE keys (page source)
+        self.rope_cos, self.rope_sin = rope_cos, rope_sin
+        cb = tuple(codebook) if codebook is not None else K.GAUSSIAN_CODEBOOK[geom.vbits]
+        self.codebook = torch.tensor(cb, dtype=torch.float32, device=self.device)
+        self.v_lut = K.v_lut_tensor(cb, self.device)
+        self.signs = K.hadamard_signs(HEAD_DIM, v_seed).to(self.device)
+        self.basis_f32: torch.Tensor | None = None
+        self.basis_f16: torch.Tensor | None = None
+        self.workspace = K.decode_workspace(geom, batch, self.max_pages, self.device)
+        self.committed = 0   # tokens held as packed pages (per sequence)
+        self.tail_len = 0    # tokens held in the fp16 window (per sequence)
+        self.sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+
+    # ---- frozen key basis -------------------------------------------------------------------
+    def set_basis(self, basis_f32: torch.Tensor) -> None:
+        """(h_kv*128, rank) float32 basis, frozen from now on (bmx: packed_streaming.py:513-520)."""
+        g = self.geom
+        assert basis_f32.shape == (g.h_kv * HEAD_DIM, g.rank)
+        self.basis_f32 = basis_f32.to(self.device, torch.float32).contiguous()
+        self.basis_f16 = self.basis_f32.half().contiguous()
+
+    def fit_basis(self, k_pre_page: torch.Tensor) -> None:
+        """Rank-r right singular vectors of the first page, as bmx fits them on the first flush
+        (bmx: src/bmx/decomp/lrs.py:35-41).  k_pre_page: (h_kv, page, 128) of sequence 0."""
+        g = self.geom
+        x = k_pre_page.float()
+        if g.n_coef_heads == 1:
+            M = x.permute(1, 0, 2).reshape(x.shape[1], g.h_kv * HEAD_DIM)
+            _, _, Vh = torch.linalg.svd(M, full_matrices=False)
+            basis = Vh[: g.rank].mT.contiguous()
+        else:
+            basis = torch.cat([torch.linalg.svd(x[h], full_matrices=False)[2][: g.rank].mT for h in range(g.h_kv)], 0)
+        self.set_basis(basis)
+
+    # ---- append -----------------------------------------------------------------------------
+    def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
+        """Quantizes the first n_pages pages of (batch, h_kv, T, 128) sources into the next slots."""
+        if self.basis_f32 is None:
+            self.fit_basis(k_src[0, :, : self.page])
+        if v_src.dtype != k_src.dtype:
+            v_src = v_src.to(k_src.dtype)
+        if k_src.stride() != v_src.stride() or k_src.stride(3) != 1:
+            k_src, v_src = k_src.contiguous(), v_src.contiguous()
+        p0 = self.committed // self.page
+        assert p0 + n_pages <= self.max_pages, "page pool exhausted"
+        slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
+        K.k2b_append(self.pool, k_src, v_src, self.basis_f32, self.signs, self.codebook, slots, n_pages)
+        self.committed += n_pages * self.page
+        self.n_pages_dev.fill_(self.committed // self.page)
+
+    def append(self, k_pre: torch.Tensor | None, k_post: torch.Tensor, v: torch.Tensor) -> None:
+        """Appends n new tokens per sequence: (batch, h_kv, n, 128) tensors (fp16 or bf16).
+
+        k_pre is the pre-RoPE key (the page source when the cache quantizes pre-RoPE keys); k_post
+        is the RoPE'd key that attention over the recent window uses.
+        """
+        src_k = k_pre if self.pre_rope else k_post
+        n = k_post.shape[2]
+        total = self.committed + self.tail_len + n
+        new_commit = compute_flush_schedule(total, self.W, self.page)
+        if n == 1 and new_commit <= self.committed:  # the common decode step: one token into the window
+            t = self.tail_len
+            self.k_win[:, :, t] = k_post[:, :, 0]
+            self.v_win[:, :, t] = v[:, :, 0]
+            self.k_pre_win[:, :, t] = src_k[:, :, 0]
+            self.tail_len += 1
+            self.tail_len_dev.fill_(self.tail_len)
+            return
+        # general path: window ++ new tokens, commit whole pages, keep the rest as the new window
+        t = self.tail_len
+        if t:
+            src_k = torch.cat([self.k_pre_win[:, :, :t].to(src_k.dtype), src_k], 2)
+            k_post = torch.cat([self.k_win[:, :, :t].to(k_post.dtype), k_post], 2)
+            v = torch.cat([self.v_win[:, :, :t].to(v.dtype), v], 2)
+        n_flush = (new_commit - self.committed) // self.page
+        if n_flush > 0:
+            self._commit_pages(src_k, v, n_flush)
+        off = n_flush * self.page
+        rest = k_post.shape[2] - off
+        assert rest <= self.tail_cap
+        self.k_win[:, :, :rest] = k_post[:, :, off:]
+        self.v_win[:, :, :rest] = v[:, :, off:]
+        self.k_pre_win[:, :, :rest] = src_k[:, :, off:]
+        self.tail_len = rest
+        self.tail_len_dev.fill_(rest)
+
+    # ---- decode -----------------------------------------------------------------------------
+    def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+               phases: int = 3) -> torch.Tensor:
+        """q (batch, heads, 128) fp16 -> attention output (batch, heads, 128) over pages + window."""
+        max_pages = self.max_pages if self.committed else 0  # nothing committed yet: window only
+        return K.k2b_decode(self.pool, q, self.basis_f16, self.page_table, self.n_pages_dev, max_pages,
+                            self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
+                            self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, phases=phases)
+
+    def seq_len(self) -> int:
+        return self.committed + self.tail_len
+
+    def packed_bytes(self) -> int:
+        """Bytes of packed pages a decode step streams (per layer, all sequences)."""
+        g = self.geom
+        per_unit = K.page_block_bytes(g) / g.page + K.coef_block_bytes(g) * g.n_coef_heads / (g.page * g.h_kv)
+        return int(self.batch * g.h_kv * self.committed * per_unit)

@@ -193,7 +193,7 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
                k_tail: torch.Tensor | None, v_tail: torch.Tensor | None, tail_len: torch.Tensor | None,
                v_lut_dev: torch.Tensor, signs: torch.Tensor, sm_scale: float, workspace: torch.Tensor,
                out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
-               pos_offset: int = 0) -> torch.Tensor:
+               pos_offset: int = 0, phases: int = 3) -> torch.Tensor:
     """One decode step for q (batch, heads, 128) fp16 over the paged k2b cache plus the fp16 window."""
     g = pool.geom
     _require_cuda(q, page_table, n_pages, workspace)
@@ -210,7 +210,7 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
     call("bmxk_k2b_decode", ctypes.byref(g), _ptr(q), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
          _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, max_pages, _ptr(rope_cos), _ptr(rope_sin),
          pos_offset, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut_dev), _ptr(signs),
-         ctypes.c_float(sm_scale), _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), _stream())
+         ctypes.c_float(sm_scale), _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), phases, _stream())
     return out if partial_out is None else partial_out
 
 

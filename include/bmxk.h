@@ -110,6 +110,8 @@ size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int ma
  * If partial_out is non-NULL the merged but un-normalised state is written instead of `out`:
  * float32 (batch, heads, 130) = {max (log2 units), sum, 128 x accumulator}, for cross-GPU
  * sequence splits (merge with bmxk_merge_partials).
+ * phases: 3 runs the whole step; 1 launches only the page-streaming kernel and 2 only the merge
+ * kernel (same arguments), so that a caller can time them apart.
  * workspace: device memory of bmxk_k2b_decode_workspace_bytes(), zero-filled once by the caller
  * (its first 16 bytes are a status word that a kernel sets only if a bounded wait ran out). */
 int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,
@@ -117,7 +119,8 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
                     int batch, int max_pages, const void* rope_cos, const void* rope_sin, int64_t pos_offset,
                     const void* k_tail, const void* v_tail, const int32_t* tail_len, int tail_cap,
                     const uint32_t* v_lut, const float* signs, float sm_scale, void* workspace,
-                    size_t workspace_bytes, void* out, int out_dtype, float* partial_out, void* stream);
+                    size_t workspace_bytes, void* out, int out_dtype, float* partial_out, int phases,
+                    void* stream);
 
 /* Host helper: fp16 lookup table for the value codebook.  Picks four fp16 levels h_i and an
  * affine map so that codebook[i] = alpha + beta * h_i to ~1e-6, which lets the kernel feed
