@@ -505,102 +505,184 @@ struct K2bMergeParams {
   float* partial_out;
 };
 
-__global__ void __launch_bounds__(128) k2b_merge_kernel(const K2bMergeParams p) {
+constexpr int MERGE_THREADS = 512;
+constexpr int MERGE_SPLIT = MERGE_THREADS / 128;  // token ranges of the window accumulation
+
+__global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMergeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const K2bGeom g = p.g;
   const int G = g.n_q_groups;
-  float* sc = reinterpret_cast<float*>(smem);           // [G][tail_cap] scores, then weights
-  float* accs = sc + G * p.tail_cap;                     // [G][128] rotated accumulator exchange
-  float* tm = accs + G * HEAD_DIM;                       // [G] tail max, [G] tail sum
-  int* cum = reinterpret_cast<int*>(tm + 2 * 8);         // [batch + 1]
+  float* sc = reinterpret_cast<float*>(smem);            // [G][tail_cap] scores, then weights
+  float* accs = sc + G * p.tail_cap;                      // [G][128] rotated accumulators
+  float* atl = accs + G * HEAD_DIM;                       // [MERGE_SPLIT][G][128] window accumulators
+  float* qs = atl + MERGE_SPLIT * G * HEAD_DIM;                     // [G][128] scaled queries
+  float* redm = qs + G * HEAD_DIM;                        // [16 warps][8] partial max / sum
+  float* tm = redm + 128;                                  // [8] window max, [8] window sum
+  int* cum = reinterpret_cast<int*>(tm + 16);             // [batch + 1]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x / g.h_kv, h = blockIdx.x % g.h_kv;
+  const int bh = b * g.h_kv + h;
 
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, g.page, lane);
+  const __half* qsrc = p.q + (int64_t)bh * G * HEAD_DIM;
+  for (int i = tid; i < G * HEAD_DIM; i += MERGE_THREADS) qs[i] = __half2float(qsrc[i]) * p.scale_log2;
   __syncthreads();
   const int total = cum[p.batch];
   const int per_cta = max(1, (total + p.main_grid - 1) / p.main_grid);
   const int tiles_b = tiles_of(p.n_pages[b], g.page);
   const int T0 = cum[b] + h * tiles_b, T1 = T0 + tiles_b;
   const int cta0 = T0 / per_cta, cta1 = (tiles_b > 0) ? (T1 - 1) / per_cta : cta0 - 1;
-  const int bh = b * g.h_kv + h;
 
-  // ---- tail scores: warp per token, lane holds 4 channels ----
+  // ---- window scores: thread = token, one pass over its key row for all G queries ----
   const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
-  const __half* qsrc = p.q + (int64_t)bh * G * HEAD_DIM;
   const __half* kt = p.k_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
   const __half* vt = p.v_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
-  for (int qi = 0; qi < G; ++qi) {
-    float qv[4];
+  float mx[8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) qv[k] = __half2float(qsrc[qi * HEAD_DIM + 4 * lane + k]) * p.scale_log2;
-    for (int t = warp; t < tl; t += 4) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(kt + (int64_t)t * HEAD_DIM + 4 * lane);
-      const float2 a = __half22float2(u32_as_h2(raw.x)), c = __half22float2(u32_as_h2(raw.y));
-      float d = qv[0] * a.x + qv[1] * a.y + qv[2] * c.x + qv[3] * c.y;
+  for (int qi = 0; qi < 8; ++qi) mx[qi] = -INFINITY;
+  for (int t = tid; t < tl; t += MERGE_THREADS) {
+    float d[8];
 #pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) d += __shfl_xor_sync(0xffffffffu, d, m);
-      if (lane == 0) sc[qi * p.tail_cap + t] = d;
+    for (int qi = 0; qi < 8; ++qi) d[qi] = 0.f;
+    const uint4* row = reinterpret_cast<const uint4*>(kt + (int64_t)t * HEAD_DIM);
+    uint4 rw[16];  // the whole 256-byte key row in flight at once: this kernel is latency bound
+#pragma unroll
+    for (int c8 = 0; c8 < 16; ++c8) rw[c8] = row[c8];
+#pragma unroll
+    for (int c8 = 0; c8 < 16; ++c8) {
+      const uint4 raw = rw[c8];
+      const float2 k0 = __half22float2(u32_as_h2(raw.x)), k1 = __half22float2(u32_as_h2(raw.y));
+      const float2 k2 = __half22float2(u32_as_h2(raw.z)), k3 = __half22float2(u32_as_h2(raw.w));
+#pragma unroll
+      for (int qi = 0; qi < 8; ++qi)
+        if (qi < G) {
+          const float4 qa = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8);
+          const float4 qb = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8 + 4);
+          d[qi] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
+        }
     }
-  }
-  __syncthreads();
-  if (warp < G && warp < 4) {
-    for (int qi = warp; qi < G; qi += 4) {
-      float mx = -INFINITY;
-      for (int t = lane; t < tl; t += 32) mx = fmaxf(mx, sc[qi * p.tail_cap + t]);
 #pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
-      float sum = 0.f;
-      for (int t = lane; t < tl; t += 32) {
-        const float e = ex2_approx(sc[qi * p.tail_cap + t] - mx);
-        sc[qi * p.tail_cap + t] = e;
-        sum += e;
+    for (int qi = 0; qi < 8; ++qi)
+      if (qi < G) {
+        sc[qi * p.tail_cap + t] = d[qi];
+        mx[qi] = fmaxf(mx[qi], d[qi]);
       }
+  }
+  // block max per query
 #pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
-      if (lane == 0) tm[qi] = mx, tm[8 + qi] = sum;
+  for (int qi = 0; qi < 8; ++qi)
+    if (qi < G) {
+      float v = mx[qi];
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+      if (lane == 0) redm[warp * 8 + qi] = v;
     }
+  __syncthreads();
+  if (tid < G) {
+    float v = -INFINITY;
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) v = fmaxf(v, redm[w * 8 + tid]);
+    tm[tid] = v;
   }
   __syncthreads();
-
-  const int ch = tid;
-  for (int qi = 0; qi < G; ++qi) {
-    // tail accumulator for (qi, ch)
-    float at = 0.f;
-    for (int t = 0; t < tl; ++t) at = fmaf(sc[qi * p.tail_cap + t], __half2float(vt[(int64_t)t * HEAD_DIM + ch]), at);
-    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
-    // global max over partial slots and the tail
-    float M = mt;
+  // weights and their sum
+  float sm[8];
+#pragma unroll
+  for (int qi = 0; qi < 8; ++qi) sm[qi] = 0.f;
+  for (int t = tid; t < tl; t += MERGE_THREADS) {
+#pragma unroll
+    for (int qi = 0; qi < 8; ++qi)
+      if (qi < G) {
+        const float e = ex2_approx(sc[qi * p.tail_cap + t] - tm[qi]);
+        sc[qi * p.tail_cap + t] = e;
+        sm[qi] += e;
+      }
+  }
+  __syncthreads();  // redm reuse
+#pragma unroll
+  for (int qi = 0; qi < 8; ++qi)
+    if (qi < G) {
+      float v = sm[qi];
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+      if (lane == 0) redm[warp * 8 + qi] = v;
+    }
+  __syncthreads();
+  if (tid < G) {
+    float v = 0.f;
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) v += redm[w * 8 + tid];
+    tm[8 + tid] = v;
+  }
+  // ---- window accumulators: thread = (token half, channel), all G queries in one pass over V ----
+  {
+    const int ch = tid & 127, part = tid >> 7;
+    float a[8];
+#pragma unroll
+    for (int qi = 0; qi < 8; ++qi) a[qi] = 0.f;
+    const int per = (tl + MERGE_SPLIT - 1) / MERGE_SPLIT;
+    const int t_lo = min(tl, part * per), t_hi = min(tl, t_lo + per);
+    for (int t0 = t_lo; t0 < t_hi; t0 += 16) {
+      __half vv[16];  // 16 loads in flight
+#pragma unroll
+      for (int k = 0; k < 16; ++k) vv[k] = (t0 + k < t_hi) ? vt[(int64_t)(t0 + k) * HEAD_DIM + ch] : __float2half(0.f);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float vf = __half2float(vv[k]);
+        const int t = min(t0 + k, t_hi - 1);
+#pragma unroll
+        for (int qi = 0; qi < 8; ++qi)
+          if (qi < G) a[qi] = fmaf(sc[qi * p.tail_cap + t], vf, a[qi]);
+      }
+    }
+#pragma unroll
+    for (int qi = 0; qi < 8; ++qi)
+      if (qi < G) atl[(part * G + qi) * HEAD_DIM + ch] = a[qi];
+  }
+  // ---- partial slots of the page-streaming kernel: thread = (query pair, channel) ----
+  for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
+    const int qi = o >> 7, ch = o & 127;
+    float M = (tl > 0) ? tm[qi] : -INFINITY;  // tm written before the last barrier
     for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(c + bh) * G + qi) * PART_STRIDE]);
-    float l = (mt == -INFINITY) ? 0.f : lt * ex2_approx(mt - M);
     float ar = 0.f;
     for (int c = cta0; c <= cta1; ++c) {
       const float* ps = p.part + ((int64_t)(c + bh) * G + qi) * PART_STRIDE;
       const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
-      l += ps[1] * f;
       ar += ps[2 + ch] * f;
     }
-    accs[qi * HEAD_DIM + ch] = ar;
-    __syncthreads();
-    // rotate back: warp 0 transforms the row, everyone reads its channel
-    if (warp == 0) {
-      float x[4];
+    accs[o] = ar;
+  }
+  __syncthreads();
+  // ---- undo the value rotation: warp qi transforms row qi ----
+  for (int qi = warp; qi < G; qi += MERGE_THREADS / 32) {
+    float x[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = accs[qi * HEAD_DIM + 4 * lane + k];
-      fwht128_warp(x, lane);
+    for (int k = 0; k < 4; ++k) x[k] = accs[qi * HEAD_DIM + 4 * lane + k];
+    fwht128_warp(x, lane);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) accs[qi * HEAD_DIM + 4 * lane + k] = x[k] * p.signs[4 * lane + k] * 0.08838834764831845f;
-    }
-    __syncthreads();
+    for (int k = 0; k < 4; ++k) accs[qi * HEAD_DIM + 4 * lane + k] = x[k] * p.signs[4 * lane + k] * 0.08838834764831845f;
+  }
+  __syncthreads();
+  for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
+    const int qi = o >> 7, ch = o & 127;
+    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
+    float M = mt;
+    for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(c + bh) * G + qi) * PART_STRIDE]);
     const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
-    const float o = accs[qi * HEAD_DIM + ch] + at * wt;
+    float l = lt * wt;
+    for (int c = cta0; c <= cta1; ++c) {
+      const float* ps = p.part + ((int64_t)(c + bh) * G + qi) * PART_STRIDE;
+      l += (ps[0] == -INFINITY) ? 0.f : ps[1] * ex2_approx(ps[0] - M);
+    }
+    float at = 0.f;
+#pragma unroll
+    for (int k = 0; k < MERGE_SPLIT; ++k) at += atl[(k * G + qi) * HEAD_DIM + ch];
+    const float val = accs[o] + at * wt;
     const int64_t row = (int64_t)bh * G + qi;
     if (p.partial_out) {
       float* po = p.partial_out + row * PART_STRIDE;
-      po[2 + ch] = o;
+      po[2 + ch] = val;
       if (ch == 0) po[0] = M, po[1] = l;
     } else {
-      const float r = o / l;
+      const float r = val / l;
       if (p.out_dtype == BMXK_DTYPE_F32)
         reinterpret_cast<float*>(p.out)[row * HEAD_DIM + ch] = r;
       else
@@ -742,9 +824,9 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  const size_t msmem = ((size_t)g->n_q_groups * tail_cap + g->n_q_groups * HEAD_DIM + 16) * 4 + (size_t)(batch + 1) * 4;
+  const size_t msmem = ((size_t)g->n_q_groups * tail_cap + (2 + MERGE_SPLIT) * g->n_q_groups * HEAD_DIM + 128 + 16) * 4 + (size_t)(batch + 1) * 4 + 16;
   BMXK_REQUIRE(msmem <= 48 * 1024, "bmxk_k2b_decode: tail_cap=%d too large for the merge kernel", tail_cap);
-  k2b_merge_kernel<<<batch * g->h_kv, 128, msmem, s>>>(mp);
+  k2b_merge_kernel<<<batch * g->h_kv, MERGE_THREADS, msmem, s>>>(mp);
   return check_launch("bmxk_k2b_decode(merge)");
 }
 
