@@ -248,11 +248,11 @@ def run_ours(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    state, q, gen, basis, (cos, sin) = build_state(device, seed=2000 + rank)
+    state, q, gen, basis, (cos, sin) = build_state(device, seed=2000 + rank, ctx=args.ctx)
     from bmx_b200 import kernels as K
 
     out = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16, device=device)
-    units = BATCH * H_KV * CTX
+    units = BATCH * H_KV * args.ctx
     algo_bytes = units * BYTES_PER_UNIT
 
     def barrier():
@@ -344,11 +344,11 @@ def run_ours(args, rank, world, local_rank):
             "metric": "k2b_decode_effective_GBps", "value": world * algo_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "us_per_layer_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+            "dtype": "f16", "data": "synthetic", "config": dict(workload_config(world), context=args.ctx),
             "frac_of_8TBps": world * algo_bytes / (ms_per_step * 1e-3) / 1e9 / (8000.0 * world),
             "roofline": {"bound": "hbm", "kernel": "k2b_decode_kernel<32,128>", "achieved": achieved, "peak": peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": algo_bytes,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * args.ctx / CTX, "algorithmic_bytes": algo_bytes,
                          "kernel_us": main_ms * 1e3, "merge_kernel_us": merge_ms * 1e3},
             "cpu_baseline": cpu,
             "e2e": {"value": world * algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer_step": e2e_ms * 1e3,
@@ -367,7 +367,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=CTX, help="committed tokens per sequence (smaller cases for profiling)")
     args = ap.parse_args()
+    assert args.ctx % PAGE == 0 and args.ctx >= PAGE
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
