@@ -53,6 +53,9 @@ _SIGNATURES = {
                                  c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_size_t, c_void_p,
                                  c_int, c_void_p, c_int, c_void_p]),
+    "bmxk_k2b_decode_static": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p]),
     "bmxk_k2b_make_v_lut": (c_int, [POINTER(c_float), POINTER(c_uint32)]),
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),

@@ -24,6 +24,7 @@
 //        applied once per (head, query) in the merge kernel, since they are linear in V.
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -745,6 +746,13 @@ static int launch_decode(const K2bDecodeParams& prm, int grid, size_t smem, cuda
 
 }  // namespace bmxk
 
+// Built-in scratch of bmxk_k2b_decode_static: one copy per GPU that loads the library, held until the
+// process exits.  Zero-initialised when the module is loaded.
+static __device__ __align__(256) unsigned char g_static_scratch[BMXK_STATIC_SCRATCH_BYTES];
+constexpr int kMaxStaticDevices = 64;
+static void* g_static_ptr[kMaxStaticDevices] = {};
+static std::mutex g_static_mu;
+
 using namespace bmxk;
 
 extern "C" {
@@ -828,6 +836,53 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   BMXK_REQUIRE(msmem <= 48 * 1024, "bmxk_k2b_decode: tail_cap=%d too large for the merge kernel", tail_cap);
   k2b_merge_kernel<<<batch * g->h_kv, MERGE_THREADS, msmem, s>>>(mp);
   return check_launch("bmxk_k2b_decode(merge)");
+}
+
+int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,
+                           const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages,
+                           int batch, int max_pages, const void* rope_cos, const void* rope_sin, int64_t pos_offset,
+                           const void* k_tail, const void* v_tail, const int32_t* tail_len, int tail_cap,
+                           const uint32_t* v_lut, const float* signs, float sm_scale, void* out, int out_dtype,
+                           void* stream) {
+  BMXK_REQUIRE(g != nullptr && batch >= 1, "bmxk_k2b_decode_static: null geometry or empty batch");
+  const size_t need = bmxk_k2b_decode_workspace_bytes(g, batch, max_pages);
+  BMXK_REQUIRE(need <= (size_t)BMXK_STATIC_SCRATCH_BYTES,
+               "bmxk_k2b_decode_static: this call needs %zu bytes of scratch but the built-in scratch holds %d "
+               "(batch*h_kv=%d, n_q_groups=%d); use bmxk_k2b_decode with a caller-owned workspace",
+               need, BMXK_STATIC_SCRATCH_BYTES, batch * g->h_kv, g->n_q_groups);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxStaticDevices) {
+    set_error("bmxk_k2b_decode_static: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    return BMXK_ERR_CUDA;
+  }
+  void* scratch = nullptr;
+  {
+    // First call on this device: resolve the device address of the built-in array.  The array's name
+    // is only a host-side handle; what a kernel needs is the address cudaGetSymbolAddress returns for
+    // the device that is current now.
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess || ptr == nullptr) {
+        set_error("bmxk_k2b_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        return BMXK_ERR_CUDA;
+      }
+      g_static_ptr[dev] = ptr;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  // The scratch keeps whatever the previous call left.  Partial states are fully rewritten by every
+  // call; the status word at its start must read zero before the kernels run, so clear it in stream order.
+  e = cudaMemsetAsync(scratch, 0, 256, (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    set_error("bmxk_k2b_decode_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return BMXK_ERR_CUDA;
+  }
+  return bmxk_k2b_decode(g, q, pages, coefs, basis_f16, page_table, table_stride, n_pages, batch, max_pages, rope_cos,
+                         rope_sin, pos_offset, k_tail, v_tail, tail_len, tail_cap, v_lut, signs, sm_scale, scratch,
+                         (size_t)BMXK_STATIC_SCRATCH_BYTES, out, out_dtype, nullptr, 3, stream);
 }
 
 int bmxk_k2b_make_v_lut(const float* codebook, uint32_t* out_lut) {

@@ -214,6 +214,29 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
     return out if partial_out is None else partial_out
 
 
+STATIC_SCRATCH_BYTES = 2 * 1024 * 1024
+
+
+def k2b_decode_static(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_table: torch.Tensor,
+                      n_pages: torch.Tensor, max_pages: int, rope_cos: torch.Tensor, rope_sin: torch.Tensor,
+                      k_tail: torch.Tensor | None, v_tail: torch.Tensor | None, tail_len: torch.Tensor | None,
+                      v_lut: torch.Tensor, signs: torch.Tensor, sm_scale: float, out: torch.Tensor,
+                      pos_offset: int = 0) -> torch.Tensor:
+    """k2b_decode for callers that may not allocate device memory: no workspace argument, the library's
+    built-in 2 MiB scratch is used (one per GPU, shared by all calls: do not overlap calls on a GPU).
+    Raises BmxkError if the batch needs more scratch than that."""
+    g = pool.geom
+    _require_cuda(q, page_table, n_pages, out)
+    batch = q.shape[0]
+    assert q.dtype == torch.float16 and q.is_contiguous() and q.shape[1:] == (g.h_kv * g.n_q_groups, HEAD_DIM)
+    tail_cap = 0 if k_tail is None else k_tail.shape[2]
+    call("bmxk_k2b_decode_static", ctypes.byref(g), _ptr(q), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
+         _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, max_pages, _ptr(rope_cos), _ptr(rope_sin),
+         pos_offset, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut), _ptr(signs),
+         ctypes.c_float(sm_scale), _ptr(out), _dtype_code(out), _stream())
+    return out
+
+
 def v_lut_tensor(codebook: tuple, device) -> torch.Tensor:
     """Host-side copy of the value table, as the int32 tensor whose 4 words bmxk_k2b_decode reads."""
     return torch.tensor([struct.unpack("<i", struct.pack("<I", x))[0] for x in make_v_lut(tuple(codebook))],

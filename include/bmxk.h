@@ -122,6 +122,38 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
                     size_t workspace_bytes, void* out, int out_dtype, float* partial_out, int phases,
                     void* stream);
 
+/* Decode step for hosts that must not allocate device memory.  (This entry point has no counterpart in
+ * bmx; it exists for embedding.)
+ *
+ * Some hosts of this library cannot call cudaMalloc where they decode: an inference server that gave
+ * every free byte of HBM to its KV-page pool at start-up has nothing left to carve a workspace from,
+ * and a plugin loaded into another runtime's process may be forbidden to touch the CUDA allocator at
+ * all.  bmxk_k2b_decode needs a caller-owned workspace for its per-CTA partial states; this variant
+ * uses a scratch array that is part of the library image instead and takes no workspace argument.
+ * Same arguments, same kernels and same results as bmxk_k2b_decode(..., phases = 3) with `out`.
+ *
+ * Limits and rules:
+ *  - the scratch is BMXK_STATIC_SCRATCH_BYTES (2 MiB) per GPU, resident from the moment the library is
+ *    loaded on that GPU until the process exits; a call whose
+ *    bmxk_k2b_decode_workspace_bytes(g, batch, max_pages) exceeds it is rejected with
+ *    BMXK_ERR_INVALID and a message naming both sizes (2 MiB covers about 860 (sequence, KV head) pairs at 4
+ *    query heads per KV head and about 350 at 8);
+ *  - the first call on each device looks up the scratch's device address (one cudaGetSymbolAddress,
+ *    no allocation) with that device current; make that first call before any stream capture begins;
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine; it issues one 256-byte
+ *    cudaMemsetAsync on `stream` to clear the status word, because the scratch keeps the previous
+ *    call's contents;
+ *  - every call on a GPU shares the one scratch: two calls whose kernels overlap on that GPU (different
+ *    streams, or different threads) race on it and produce garbage.  Serialise them, or give the
+ *    concurrent ones bmxk_k2b_decode with their own workspaces. */
+#define BMXK_STATIC_SCRATCH_BYTES (2 * 1024 * 1024)
+int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,
+                           const void* basis_f16, const int32_t* page_table, int table_stride,
+                           const int32_t* n_pages, int batch, int max_pages, const void* rope_cos,
+                           const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                           const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs,
+                           float sm_scale, void* out, int out_dtype, void* stream);
+
 /* Host helper: fp16 lookup table for the value codebook.  Picks four fp16 levels h_i and an
  * affine map so that codebook[i] = alpha + beta * h_i to ~1e-6, which lets the kernel feed
  * fp16 levels to the tensor cores without a systematic per-level rounding error.
