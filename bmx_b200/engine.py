@@ -72,6 +72,22 @@ class K2bLayerState:
             basis = torch.cat([torch.linalg.svd(x[h], full_matrices=False)[2][: g.rank].mT for h in range(g.h_kv)], 0)
         self.set_basis(basis)
 
+    def ensure_pages(self, n_more: int) -> None:
+        """Grows the page pool (doubling) so that n_more further pages per sequence fit."""
+        need = self.committed // self.page + n_more
+        if need <= self.max_pages:
+            return
+        new_max = max(need, 2 * self.max_pages)
+        old_pool, old_table, used = self.pool, self.page_table, self.committed // self.page
+        self.pool = K.K2bPool(self.geom, self.batch * new_max, self.device)
+        self.page_table = torch.arange(self.batch * new_max, dtype=torch.int32, device=self.device).view(self.batch, -1)
+        if used:
+            src = old_table[:, :used].reshape(-1).long()
+            dst = self.page_table[:, :used].reshape(-1).long()
+            self.pool.pages[dst] = old_pool.pages[src]
+            self.pool.coefs[dst] = old_pool.coefs[src]
+        self.max_pages = new_max
+
     # ---- append -----------------------------------------------------------------------------
     def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
         """Quantizes the first n_pages pages of (batch, h_kv, T, 128) sources into the next slots."""
@@ -81,8 +97,8 @@ class K2bLayerState:
             v_src = v_src.to(k_src.dtype)
         if k_src.stride() != v_src.stride() or k_src.stride(3) != 1:
             k_src, v_src = k_src.contiguous(), v_src.contiguous()
+        self.ensure_pages(n_pages)
         p0 = self.committed // self.page
-        assert p0 + n_pages <= self.max_pages, "page pool exhausted"
         slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
         K.k2b_append(self.pool, k_src, v_src, self.basis_f32, self.signs, self.codebook, slots, n_pages)
         self.committed += n_pages * self.page

@@ -1,0 +1,313 @@
+"""Packed streaming KV cache for Hugging Face models, on the bmxk CUDA kernels.
+
+Drop-in for bmx's `PackedStreamingCache` / `PackedStreamingLayer`
+(bmx: src/bmx/cache/packed_streaming.py:310-1222): same constructor arguments, same attach / detach /
+context-manager protocol, same registered attention name ("chunked_dequant") and mask function, same
+flush schedule and bits-per-entry accounting.  What differs is underneath: committed tokens live in
+a device page pool written by one quantize-on-append launch per flush, and a decode step is the
+split-KV dequant-attention kernel reading those pages; there are no per-page Python dicts and no
+CPU or PyTorch fallback for decode.  Arm pairs without a CUDA decode kernel raise.
+"""
+
+from __future__ import annotations
+
+import weakref
+
+import torch
+import torch.nn.functional as F
+from transformers.cache_utils import Cache, DynamicLayer
+from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS, sdpa_mask
+from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+from . import kernels as K
+from .engine import K2bLayerState
+from .rope import apply_rope, rope_tables_from_config
+from .schedule import codec_bpe, compute_flush_schedule
+from .specs import FUSED_PAIRS, CacheCodecSpec
+
+_ATTN_NAME = "chunked_dequant"
+HEAD_DIM = K.HEAD_DIM
+
+# Process-shared growing RoPE tables keyed by (device, rope parameters): every layer of every cache on
+# one model reads the same fp16 pair (bmx: src/bmx/cache/packed_streaming.py:79-113).
+_ROPE_SHARED: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def resolve_text_config(model_config):
+    tc = getattr(model_config, "text_config", None)
+    return tc if tc is not None and hasattr(tc, "num_attention_heads") else model_config
+
+
+def resolve_decoder_layers(model):
+    inner = getattr(model, "model", None)
+    if inner is not None:
+        lm = getattr(inner, "language_model", None)
+        if lm is not None and hasattr(lm, "layers"):
+            return lm.layers
+        if hasattr(inner, "layers"):
+            return inner.layers
+    raise ValueError(f"cannot locate decoder layers of {type(model).__name__}")
+
+
+def resolve_k_capture_module(self_attn):
+    """Module whose forward output is the pre-RoPE key: k_norm when the family normalises per head
+    (Qwen3), else k_proj (bmx: src/bmx/cache/hf_compat.py:60-96)."""
+    has_q, has_k = hasattr(self_attn, "q_norm"), hasattr(self_attn, "k_norm")
+    assert has_q == has_k, "attention has only one of q_norm / k_norm; capture point ambiguous"
+    for alt in ("q_layernorm", "k_layernorm", "qk_norm"):
+        assert not hasattr(self_attn, alt), f"unsupported pre-RoPE norm '{alt}'"
+    return self_attn.k_norm if has_k else self_attn.k_proj
+
+
+def _rope_key(config, device) -> tuple:
+    return (str(device), float(getattr(config, "rope_theta", 0.0) or 0.0), int(getattr(config, "head_dim", 0) or 0),
+            int(getattr(config, "hidden_size", 0)), int(getattr(config, "num_attention_heads", 0)),
+            str(getattr(config, "rope_parameters", getattr(config, "rope_scaling", None))))
+
+
+def shared_rope(config, upto: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp16 cos/sin (>= upto, head_dim) shared by all layers; grows by doubling."""
+    config = resolve_text_config(config)
+    key = _rope_key(config, device)
+    cur = _ROPE_SHARED.get(key)
+    if cur is None or cur[0].shape[0] < upto:
+        n = max(upto, 2 * (cur[0].shape[0] if cur else 0), 1024)
+        cos, sin = rope_tables_from_config(config, n, device=device)
+        _ROPE_SHARED[key] = (cos.half().contiguous(), sin.half().contiguous())
+    return _ROPE_SHARED[key]
+
+
+def chunked_attention_forward(module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
+    """Registered attention function: (b, H, n_q, d) query -> ((b, n_q, H*d), None), computed from the
+    packed state on `module._packed_layer`; the dense key/value arguments are ignored
+    (bmx: src/bmx/cache/packed_streaming.py:270-298)."""
+    assert hasattr(module, "_packed_layer"), "PackedStreamingCache.attach(model) must be called before forward"
+    layer = module._packed_layer
+    n_q = query.shape[2]
+    out = layer.attend(query, scaling, is_causal=(n_q > 1), attention_mask=attention_mask)  # (b, H, n_q, d)
+    b, H, n_q, d = out.shape
+    return out.transpose(1, 2).reshape(b, n_q, H * d).to(query.dtype), None
+
+
+ALL_ATTENTION_FUNCTIONS.register(_ATTN_NAME, chunked_attention_forward)
+ALL_MASK_ATTENTION_FUNCTIONS.register(_ATTN_NAME, sdpa_mask)
+
+
+class PackedStreamingLayer(DynamicLayer):
+    """Per-layer packed cache: page pool + frozen key basis + fp16 recent window."""
+
+    def __init__(self, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, model_config, recent_window: int = 32,
+                 pack_v: bool = True, pack_k: bool = True, pack=None):
+        super().__init__()
+        self.k_spec, self.v_spec, self.model_config = k_spec, v_spec, model_config
+        self.recent_window, self.pack_v, self.pack_k = recent_window, pack_v, pack_k
+        kind = FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
+        if kind != "k2b":
+            raise NotImplementedError(
+                f"no CUDA decode kernel for arms K={k_spec.arm!r} / V={v_spec.arm!r} in PackedStreamingLayer; "
+                "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph'). There is no CPU fallback.")
+        tc = resolve_text_config(model_config)
+        self._h_kv = getattr(tc, "num_key_value_heads", tc.num_attention_heads)
+        self._d_head = getattr(tc, "head_dim", None) or tc.hidden_size // tc.num_attention_heads
+        self._n_q_groups = tc.num_attention_heads // self._h_kv
+        if self._d_head != HEAD_DIM:
+            raise NotImplementedError(f"head_dim={self._d_head}: the bmxk kernels are built for head_dim 128")
+        self._g = k_spec.group
+        self._page = max(self._g, (128 // self._g) * self._g) if self._g > 1 else 128
+        self._k_pre: torch.Tensor | None = None   # pre-RoPE keys captured by the hook since the last update
+        self._committed_S_q = 0
+        self._quant_bits_k = self._quant_bits_v = 0.0
+        self.bpe_k = self.bpe_v = float("nan")
+        self._k_blocks: list[tuple[int, int, int]] = []   # (page index, start, end) of committed pages
+        self._v_blocks: list[tuple[int, int, int]] = []
+        self._frozen_svd: tuple | None = None
+        self._state: K2bLayerState | None = None
+        self._batch = 0
+
+    # ---- hooks ----------------------------------------------------------------------------------
+    def stash_pre_rope(self, out: torch.Tensor) -> None:
+        """k_proj / k_norm output (b, S, h_kv*d) or (b, S, h_kv, d) -> (b, h_kv, S, d) fp16, kept until update()."""
+        b, S = out.shape[0], out.shape[1]
+        block = out.reshape(b, S, self._h_kv, self._d_head).permute(0, 2, 1, 3).to(torch.float16)
+        self._k_pre = block if self._k_pre is None else torch.cat([self._k_pre, block], dim=2)
+
+    # ---- state ----------------------------------------------------------------------------------
+    def _ensure_state(self, key_states: torch.Tensor) -> K2bLayerState:
+        if self._state is None:
+            self._batch = key_states.shape[0]
+            rank = self.k_spec.rank
+            geom = K.k2b_geom(self._h_kv, self._n_q_groups, self._page, rank, self.k_spec.group, 1, self.k_spec.bits,
+                              self.v_spec.bits)
+            cos, sin = shared_rope(self.model_config, 4096, key_states.device)
+            self._state = K2bLayerState(geom, self._batch, 4096, self.recent_window, key_states.device, cos, sin,
+                                        v_seed=self.v_spec.seed, pre_rope=self.k_spec.pre_rope)
+            self.dtype, self.device, self.is_initialized = key_states.dtype, key_states.device, True
+        return self._state
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, *args, **kwargs):
+        """Appends (b, h_kv, n, d) keys/values, flushing whole pages on the reference's schedule; returns the
+        fp16 window as (keys, values) for HF bookkeeping (attention reads the packed state instead)."""
+        st = self._ensure_state(key_states)
+        n = key_states.shape[2]
+        if self.k_spec.pre_rope:
+            assert self._k_pre is not None and self._k_pre.shape[2] == n, (
+                "k_spec.pre_rope=True but no pre-RoPE keys were captured; call cache.attach(model) before the forward")
+            k_pre, self._k_pre = self._k_pre, None
+        else:
+            k_pre = None
+        total = st.seq_len() + n
+        cos, sin = shared_rope(self.model_config, total + 1, key_states.device)
+        st.rope_cos, st.rope_sin = cos, sin
+        before = st.committed
+        st.append(k_pre, key_states.to(torch.float16), value_states.to(torch.float16))
+        if st.basis_f32 is not None and self._frozen_svd is None:
+            self._frozen_svd = (None, st.basis_f32)
+        # accounting: every newly committed page is charged the codec's bits per entry, the window 16 bits
+        C = self._h_kv * self._d_head
+        for pg0 in range(before, st.committed, self._page):
+            entries = self._page * C
+            self._quant_bits_k += codec_bpe(self.k_spec.arm, bits=self.k_spec.bits, group=self.k_spec.group,
+                                            rank=self.k_spec.rank, S=self._page, C=C) * entries
+            self._quant_bits_v += codec_bpe(self.v_spec.arm, bits=self.v_spec.bits, group=self.v_spec.group,
+                                            rank=0, S=self._page, C=C, h_heads=self._h_kv) * entries
+            self._k_blocks.append((pg0 // self._page, pg0, pg0 + self._page))
+            self._v_blocks.append((pg0 // self._page, pg0, pg0 + self._page))
+        self._committed_S_q = st.committed
+        S = st.seq_len()
+        if S > 0:
+            self.bpe_k = (self._quant_bits_k + st.tail_len * C * 16.0) / (S * C)
+            self.bpe_v = (self._quant_bits_v + st.tail_len * C * 16.0) / (S * C)
+        self.keys = st.k_win[:, :, : st.tail_len]
+        self.values = st.v_win[:, :, : st.tail_len]
+        return self.keys, self.values
+
+    def get_seq_length(self) -> int:
+        return 0 if self._state is None else self._state.seq_len()
+
+    # ---- attention ------------------------------------------------------------------------------
+    def _dense_kv(self, dtype):
+        """All committed pages dequantized (keys rotated at their positions) + the window: (b, h_kv, S, d)."""
+        st = self._state
+        n_pg = st.committed // self._page
+        parts_k, parts_v = [], []
+        if n_pg:
+            slots = st.page_table[:, :n_pg].contiguous().view(-1)
+            kd, vd = K.k2b_dequant_pages(st.pool, slots, st.basis_f16, st.signs, st.codebook)
+            shp = (st.batch, n_pg * self._page, self._h_kv, self._d_head)
+            kd = kd.view(*shp).permute(0, 2, 1, 3)
+            vd = vd.view(*shp).permute(0, 2, 1, 3)
+            if self.k_spec.pre_rope:
+                kd = apply_rope(kd.to(dtype), st.rope_cos[: st.committed].to(dtype), st.rope_sin[: st.committed].to(dtype))
+            parts_k.append(kd.to(dtype))
+            parts_v.append(vd.to(dtype))
+        parts_k.append(st.k_win[:, :, : st.tail_len].to(dtype))
+        parts_v.append(st.v_win[:, :, : st.tail_len].to(dtype))
+        return torch.cat(parts_k, 2), torch.cat(parts_v, 2)
+
+    def attend(self, q: torch.Tensor, scaling: float, is_causal: bool = False, attention_mask=None) -> torch.Tensor:
+        """q (b, H, n_q, d) -> (b, H, n_q, d).  Decode (n_q == 1) runs the split-KV dequant-attention kernel;
+        prefill dequantizes the pages once and calls SDPA with the model's mask, as the reference does
+        (bmx: src/bmx/cache/chunked_attention.py:320-395)."""
+        st = self._state
+        assert st is not None, "attend() before update()"
+        if q.dim() == 3:
+            q = q.unsqueeze(0)
+        b, H, n_q, d = q.shape
+        if n_q == 1 and not is_causal:
+            st.sm_scale = float(scaling)
+            out = st.decode(q[:, :, 0, :].to(torch.float16).contiguous())
+            return out.unsqueeze(2).to(q.dtype)
+        Kd, Vd = self._dense_kv(q.dtype)
+        Kx = Kd.repeat_interleave(self._n_q_groups, dim=1)
+        Vx = Vd.repeat_interleave(self._n_q_groups, dim=1)
+        # a single query row attends every cached key; only a multi-row block without a mask is causal
+        return F.scaled_dot_product_attention(q, Kx, Vx, attn_mask=attention_mask,
+                                              is_causal=(attention_mask is None and n_q > 1), scale=scaling)
+
+
+class PackedStreamingCache(Cache):
+    """Cache container replicating PackedStreamingLayer across the model; drop-in `past_key_values`.
+
+        cache = PackedStreamingCache(model.config, k_spec=k_spec, v_spec=v_spec, recent_window=128)
+        with cache.attach(model):
+            out = model.generate(..., past_key_values=cache)
+    """
+
+    def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32,
+                 pack_v: bool = True, pack_k: bool = True):
+        if k_spec.arm == "spectral":
+            raise NotImplementedError("the spectral key arm has no CUDA decode kernel yet; there is no CPU fallback")
+        wself = weakref.proxy(self)  # a strong capture would make a cycle that keeps the page pools alive
+
+        def _make_layer():
+            return PackedStreamingLayer(k_spec, v_spec, model_config, recent_window, pack_v=pack_v, pack_k=pack_k,
+                                        pack=wself._pack_for_layer(len(wself.layers)))
+
+        self._make_layer = _make_layer
+        super().__init__(layer_class_to_replicate=_make_layer)
+        self.model_config, self.k_spec, self.v_spec = model_config, k_spec, v_spec
+        self.recent_window, self.pack_v, self.pack_k = recent_window, pack_v, pack_k
+        self._handles: list = []
+        self._saved_impl: str | None = None
+        self._model = None
+
+    def _pack_for_layer(self, i: int):
+        return None
+
+    def bits_per_entry(self):
+        """(bpe_k, bpe_v): blended bits per entry averaged across layers (bmx: streaming.py:154-260)."""
+        layers = list(self.layers)
+        if not layers:
+            return float("nan"), float("nan")
+        return (sum(l.bpe_k for l in layers) / len(layers), sum(l.bpe_v for l in layers) / len(layers))
+
+    def memory_report(self, seq_len: int) -> dict:
+        """Dense fp16 bytes vs packed (bpe-derived) bytes of the whole cache (bmx: streaming.py:263-305)."""
+        bpe_k, bpe_v = self.bits_per_entry()
+        cfg = resolve_text_config(self.model_config)
+        h_kv = getattr(cfg, "num_key_value_heads", cfg.num_attention_heads)
+        d = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+        entries = cfg.num_hidden_layers * h_kv * seq_len * d
+        fp16_bytes = 2 * entries * 2
+        bpe_k = 16.0 if bpe_k != bpe_k else bpe_k
+        bpe_v = 16.0 if bpe_v != bpe_v else bpe_v
+        packed_bytes = entries * (bpe_k + bpe_v) / 8.0
+        return {"fp16_bytes": float(fp16_bytes), "packed_bytes": float(packed_bytes),
+                "compression": fp16_bytes / max(packed_bytes, 1e-9)}
+
+    def attach(self, model) -> "PackedStreamingCache":
+        self.detach()
+        self._model = model
+        self._saved_impl = model.config._attn_implementation
+        model.config._attn_implementation = _ATTN_NAME
+        n_layers = len(resolve_decoder_layers(model))
+        while len(self.layers) < n_layers:
+            self.layers.append(self._make_layer())
+        for i, mlayer in enumerate(resolve_decoder_layers(model)):
+            mlayer.self_attn._packed_layer = self.layers[i]
+            if self.k_spec.pre_rope:
+                def k_hook(module, inp, out, i=i):
+                    self.layers[i].stash_pre_rope(out)
+
+                self._handles.append(resolve_k_capture_module(mlayer.self_attn).register_forward_hook(k_hook))
+        return self
+
+    def detach(self) -> "PackedStreamingCache":
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+        if self._model is not None:
+            for mlayer in resolve_decoder_layers(self._model):
+                if hasattr(mlayer.self_attn, "_packed_layer"):
+                    del mlayer.self_attn._packed_layer
+            if self._saved_impl is not None:
+                self._model.config._attn_implementation = self._saved_impl
+        self._model, self._saved_impl = None, None
+        return self
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.detach()
+        return False
