@@ -24,6 +24,13 @@ class K2bGeom(ctypes.Structure):
                 ("h_kv", "n_q_groups", "page", "rank", "group", "n_coef_heads", "kbits", "vbits")]
 
 
+class RtnGeom(ctypes.Structure):
+    """Mirror of `bmxk_rtn_geom` (include/bmxk.h)."""
+
+    _fields_ = [(n, c_int32) for n in
+                ("h_kv", "n_q_groups", "page", "k_arm", "k_group", "v_group", "kbits", "vbits")]
+
+
 class BmxkError(RuntimeError):
     """A bmxk entry point returned a non-zero status."""
 
@@ -57,6 +64,15 @@ _SIGNATURES = {
                                         c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p]),
     "bmxk_k2b_make_v_lut": (c_int, [POINTER(c_float), POINTER(c_uint32)]),
+    "bmxk_rtn_page_block_bytes": (c_size_t, [POINTER(RtnGeom)]),
+    "bmxk_rtn_decode_workspace_bytes": (c_size_t, [POINTER(RtnGeom), c_int, c_int]),
+    "bmxk_rtn_append": (c_int, [POINTER(RtnGeom), c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                 c_int, c_void_p, c_void_p]),
+    "bmxk_rtn_export": (c_int, [POINTER(RtnGeom), c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p]),
+    "bmxk_rtn_decode": (c_int, [POINTER(RtnGeom), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p, c_int, c_void_p,
+                                 c_void_p]),
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),
 }

@@ -21,6 +21,7 @@ SOURCES = [
     ("api.cu", []),
     ("k2b_codec.cu", ["-fmad=false"]),
     ("k2b_decode.cu", []),
+    ("rtn.cu", ["-fmad=false"]),
 ]
 
 

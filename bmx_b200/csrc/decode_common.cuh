@@ -1,0 +1,78 @@
+// Pieces shared by the split-KV decode kernels (k2b and RTN): the flat tile decomposition, the cursor
+// that walks it, the partial-state record and the merge kernel's parameters.
+#pragma once
+#include "common.cuh"
+
+namespace bmxk {
+
+constexpr int TILE_TOKENS = 128;
+constexpr int PART_STRIDE = 130;  // per query head: max (log2 units), sum, 128 accumulators
+constexpr int MAX_BH = 4096;      // (sequence, head) pairs per call
+
+// Tiles per (sequence, head) and the flat decomposition, recomputed identically by every CTA of both
+// kernels from the device-resident page counts.
+__device__ __forceinline__ int tiles_of(int n_pages, int page) { return (n_pages * page + TILE_TOKENS - 1) / TILE_TOKENS; }
+
+// cum[b] = tiles of sequences < b, times h_kv.  Filled by one warp; cum has batch + 1 entries.
+__device__ __forceinline__ void fill_cum(int* cum, const int32_t* n_pages, int batch, int h_kv, int page, int lane) {
+  int run = 0;
+  for (int b0 = 0; b0 < batch; b0 += 32) {
+    const int b = b0 + lane;
+    int v = (b < batch) ? tiles_of(n_pages[b], page) * h_kv : 0;
+    int incl = v;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, m);
+      if (lane >= m) incl += o;
+    }
+    if (b < batch) cum[b] = run + incl - v;
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) cum[batch] = run;
+}
+
+// Walks the flat tile list without divisions: (sequence b, head h, tile j of tiles_b) advance by one.
+struct TileCursor {
+  int b, h, j, tiles_b;
+  __device__ __forceinline__ void init(const int* cum, const int* npg, int f, int page) {
+    b = 0;
+    while (cum[b + 1] <= f) ++b;
+    tiles_b = tiles_of(npg[b], page);
+    const int rel = f - cum[b];
+    h = rel / tiles_b, j = rel - h * tiles_b;
+  }
+  __device__ __forceinline__ void next(const int* npg, int h_kv, int page, int batch) {
+    if (++j == tiles_b) {
+      j = 0;
+      if (++h == h_kv) {
+        h = 0;
+        do { ++b; } while (b < batch && npg[b] == 0);
+        tiles_b = (b < batch) ? tiles_of(npg[b], page) : 1;
+      }
+    }
+  }
+};
+
+struct K2bMergeParams {
+  K2bGeom g;
+  const __half* q;
+  const int32_t* n_pages;
+  int batch;
+  int main_grid;
+  const float* part;
+  const __half* k_tail;
+  const __half* v_tail;
+  const int32_t* tail_len;
+  int tail_cap;
+  const float* signs;
+  float scale_log2;
+  void* out;
+  int out_dtype;
+  float* partial_out;
+};
+
+// SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
+int num_sms();
+int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
+
+}  // namespace bmxk

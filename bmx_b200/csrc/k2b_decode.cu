@@ -26,16 +26,12 @@
 #include <cstring>
 #include <mutex>
 
-#include "common.cuh"
+#include "decode_common.cuh"
 
 namespace bmxk {
 
 constexpr int DEC_CONSUMER_WARPS = 8;
 constexpr int DEC_THREADS = (DEC_CONSUMER_WARPS + 4) * 32;  // + one producer warpgroup (one warp of it works)
-constexpr int TILE_TOKENS = 128;
-constexpr int PART_STRIDE = 130;  // per query head: max (log2 units), sum, 128 accumulators
-constexpr int MAX_BH = 4096;      // (sequence, head) pairs per call
-
 struct K2bDecodeParams {
   K2bGeom g;
   const __half* q;
@@ -57,33 +53,6 @@ struct K2bDecodeParams {
   int n_stages;
 };
 
-// Tiles per (sequence, head) and the flat decomposition, recomputed identically by every CTA of both
-// kernels from the device-resident page counts.
-struct Decomp {
-  int total;   // tiles over all (sequence, head)
-  int per_cta; // tiles per CTA (ceil)
-};
-
-__device__ __forceinline__ int tiles_of(int n_pages, int page) { return (n_pages * page + TILE_TOKENS - 1) / TILE_TOKENS; }
-
-// cum[b] = tiles of sequences < b, times h_kv.  Filled by one warp; cum has batch + 1 entries.
-__device__ __forceinline__ void fill_cum(int* cum, const int32_t* n_pages, int batch, int h_kv, int page, int lane) {
-  int run = 0;
-  for (int b0 = 0; b0 < batch; b0 += 32) {
-    const int b = b0 + lane;
-    int v = (b < batch) ? tiles_of(n_pages[b], page) * h_kv : 0;
-    int incl = v;
-#pragma unroll
-    for (int m = 1; m < 32; m <<= 1) {
-      const int o = __shfl_up_sync(0xffffffffu, incl, m);
-      if (lane >= m) incl += o;
-    }
-    if (b < batch) cum[b] = run + incl - v;
-    run += __shfl_sync(0xffffffffu, incl, 31);
-  }
-  if (lane == 0) cum[batch] = run;
-}
-
 __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -98,28 +67,6 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int
   }
   return true;
 }
-
-// Walks the flat tile list without divisions: (sequence b, head h, tile j of tiles_b) advance by one.
-struct TileCursor {
-  int b, h, j, tiles_b;
-  __device__ __forceinline__ void init(const int* cum, const int* npg, int f, int page) {
-    b = 0;
-    while (cum[b + 1] <= f) ++b;
-    tiles_b = tiles_of(npg[b], page);
-    const int rel = f - cum[b];
-    h = rel / tiles_b, j = rel - h * tiles_b;
-  }
-  __device__ __forceinline__ void next(const int* npg, int h_kv, int page, int batch) {
-    if (++j == tiles_b) {
-      j = 0;
-      if (++h == h_kv) {
-        h = 0;
-        do { ++b; } while (b < batch && npg[b] == 0);
-        tiles_b = (b < batch) ? tiles_of(npg[b], page) : 1;
-      }
-    }
-  }
-};
 
 template <int RANK, int PAGE>
 __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDecodeParams p) {
@@ -488,24 +435,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 //      (bmx: :409-461; maxima are in log2 units on both sides)
 //   3. undo the value rotation of the packed part: signs * fwht(acc) / sqrt(128)
 // ---------------------------------------------------------------------------------------------
-struct K2bMergeParams {
-  K2bGeom g;
-  const __half* q;
-  const int32_t* n_pages;
-  int batch;
-  int main_grid;
-  const float* part;
-  const __half* k_tail;
-  const __half* v_tail;
-  const int32_t* tail_len;
-  int tail_cap;
-  const float* signs;
-  float scale_log2;
-  void* out;
-  int out_dtype;
-  float* partial_out;
-};
-
 constexpr int MERGE_THREADS = 512;
 constexpr int MERGE_SPLIT = MERGE_THREADS / 128;  // token ranges of the window accumulation
 
@@ -652,8 +581,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
     accs[o] = ar;
   }
   __syncthreads();
-  // ---- undo the value rotation: warp qi transforms row qi ----
-  for (int qi = warp; qi < G; qi += MERGE_THREADS / 32) {
+  // ---- undo the value rotation (codecs without one pass signs == nullptr): warp qi transforms row qi ----
+  for (int qi = warp; qi < G && p.signs != nullptr; qi += MERGE_THREADS / 32) {
     float x[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) x[k] = accs[qi * HEAD_DIM + 4 * lane + k];
@@ -712,7 +641,7 @@ __global__ void merge_partials_kernel(const float* __restrict__ parts, int n_par
 }
 
 static int g_num_sms = 0;
-static int num_sms() {
+int num_sms() {
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -720,6 +649,14 @@ static int num_sms() {
     if (g_num_sms <= 0) g_num_sms = 148;
   }
   return g_num_sms;
+}
+
+int launch_merge(const K2bMergeParams& mp, cudaStream_t s) {
+  const int G = mp.g.n_q_groups;
+  const size_t msmem = ((size_t)G * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
+  BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
+  k2b_merge_kernel<<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
+  return check_launch("decode(merge)");
 }
 
 static size_t decode_stage_bytes(const bmxk_k2b_geom* g) {
@@ -832,10 +769,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  const size_t msmem = ((size_t)g->n_q_groups * tail_cap + (2 + MERGE_SPLIT) * g->n_q_groups * HEAD_DIM + 128 + 16) * 4 + (size_t)(batch + 1) * 4 + 16;
-  BMXK_REQUIRE(msmem <= 48 * 1024, "bmxk_k2b_decode: tail_cap=%d too large for the merge kernel", tail_cap);
-  k2b_merge_kernel<<<batch * g->h_kv, MERGE_THREADS, msmem, s>>>(mp);
-  return check_launch("bmxk_k2b_decode(merge)");
+  return launch_merge(mp, s);
 }
 
 int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,

@@ -237,6 +237,17 @@ def k2b_decode_static(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, p
     return out
 
 
+def merge_partials(parts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """(n_parts, rows, 130) float32 partial states -> normalised (rows, 128) output (bmx split merge)."""
+    _require_cuda(parts)
+    assert parts.dtype == torch.float32 and parts.dim() == 3 and parts.shape[2] == 130 and parts.is_contiguous()
+    n, rows = parts.shape[0], parts.shape[1]
+    if out is None:
+        out = torch.empty(rows, HEAD_DIM, dtype=torch.float16, device=parts.device)
+    call("bmxk_merge_partials", _ptr(parts), n, rows, _ptr(out), _dtype_code(out), _stream())
+    return out
+
+
 def v_lut_tensor(codebook: tuple, device) -> torch.Tensor:
     """Host-side copy of the value table, as the int32 tensor whose 4 words bmxk_k2b_decode reads."""
     return torch.tensor([struct.unpack("<i", struct.pack("<I", x))[0] for x in make_v_lut(tuple(codebook))],
@@ -245,3 +256,81 @@ def v_lut_tensor(codebook: tuple, device) -> torch.Tensor:
 
 def check_status(workspace: torch.Tensor) -> None:
     call("bmxk_check_workspace_status", _ptr(workspace), _stream())
+
+
+# ---- plain RTN caches ---------------------------------------------------------------------------
+
+from ._lib import RtnGeom  # noqa: E402
+
+RTN_TOKEN, RTN_CHANNEL = 0, 1
+
+
+def rtn_geom(h_kv: int, n_q_groups: int, page: int = 128, k_arm: str = "rtn_token", k_group: int = 32,
+             v_group: int = 32, kbits: int = 4, vbits: int = 2) -> RtnGeom:
+    arm = {"rtn_token": RTN_TOKEN, "rtn_channel": RTN_CHANNEL}[k_arm]
+    return RtnGeom(h_kv, n_q_groups, page, arm, k_group, v_group, kbits, vbits)
+
+
+class RtnPool:
+    """Device page pool of one layer of an RTN cache: `pages[n_slots][h_kv][block]`."""
+
+    def __init__(self, g: RtnGeom, n_slots: int, device):
+        self.geom, self.n_slots = g, n_slots
+        nb = int(_lib.lib().bmxk_rtn_page_block_bytes(ctypes.byref(g)))
+        self.pages = torch.zeros(n_slots, g.h_kv, nb, dtype=torch.uint8, device=device)
+
+
+def rtn_append(pool: RtnPool, k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, n_pages: int) -> None:
+    """Quantizes n_pages full pages of every sequence of k/v (n_seq, h_kv, T, 128); keys are post-RoPE."""
+    g = pool.geom
+    _require_cuda(k, v, slots)
+    assert k.shape == v.shape and k.dim() == 4 and k.shape[1] == g.h_kv and k.shape[3] == HEAD_DIM
+    assert k.dtype == v.dtype and k.stride() == v.stride() and k.stride(3) == 1 and k.shape[2] >= n_pages * g.page
+    assert slots.dtype == torch.int32 and slots.numel() == k.shape[0] * n_pages
+    call("bmxk_rtn_append", ctypes.byref(g), _ptr(k), _ptr(v), _dtype_code(k), k.stride(0), k.stride(1), k.stride(2),
+         _ptr(slots), k.shape[0], n_pages, _ptr(pool.pages), _stream())
+
+
+def rtn_export(pool: RtnPool, slots: torch.Tensor, dequant: bool = False) -> dict:
+    """Pages -> bmx's int8 code containers and fp16 scales (and, on request, float32 dequantized pages)."""
+    g = pool.geom
+    n, dev, C = slots.numel(), pool.pages.device, g.h_kv * HEAD_DIM
+    if g.k_arm == RTN_TOKEN:
+        kc = torch.empty(n, g.h_kv, g.page, HEAD_DIM, dtype=torch.int8, device=dev)
+        ks = torch.empty(n, g.h_kv, g.page, HEAD_DIM // g.k_group, dtype=torch.float16, device=dev)
+    else:
+        kc = torch.empty(n, C, g.page, dtype=torch.int8, device=dev)
+        ks = torch.empty(n, C, g.page // g.k_group, dtype=torch.float16, device=dev)
+    out = {"k_codes": kc, "k_scales": ks,
+           "v_codes": torch.empty(n, g.h_kv, g.page, HEAD_DIM, dtype=torch.int8, device=dev),
+           "v_scales": torch.empty(n, g.h_kv, g.page, HEAD_DIM // g.v_group, dtype=torch.float16, device=dev)}
+    if dequant:
+        out["k_deq"] = torch.empty(n, g.page, C, dtype=torch.float32, device=dev)
+        out["v_deq"] = torch.empty(n, g.page, C, dtype=torch.float32, device=dev)
+    call("bmxk_rtn_export", ctypes.byref(g), _ptr(pool.pages), _ptr(slots), n, _ptr(kc), _ptr(ks), _ptr(out["v_codes"]),
+         _ptr(out["v_scales"]), _ptr(out.get("k_deq")), _ptr(out.get("v_deq")), _stream())
+    return out
+
+
+def rtn_workspace(g: RtnGeom, batch: int, max_pages: int, device) -> torch.Tensor:
+    n = int(_lib.lib().bmxk_rtn_decode_workspace_bytes(ctypes.byref(g), batch, max_pages))
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def rtn_decode(pool: RtnPool, q: torch.Tensor, page_table: torch.Tensor, n_pages: torch.Tensor, max_pages: int,
+               k_tail: torch.Tensor | None, v_tail: torch.Tensor | None, tail_len: torch.Tensor | None,
+               sm_scale: float, workspace: torch.Tensor, out: torch.Tensor | None = None,
+               partial_out: torch.Tensor | None = None) -> torch.Tensor:
+    """One decode step for q (batch, heads, 128) fp16 over RTN pages plus the fp16 window."""
+    g = pool.geom
+    _require_cuda(q, page_table, n_pages, workspace)
+    batch = q.shape[0]
+    assert q.dtype == torch.float16 and q.is_contiguous() and q.shape[1:] == (g.h_kv * g.n_q_groups, HEAD_DIM)
+    tail_cap = 0 if k_tail is None else k_tail.shape[2]
+    if out is None and partial_out is None:
+        out = torch.empty(batch, g.h_kv * g.n_q_groups, HEAD_DIM, dtype=torch.float16, device=q.device)
+    out_code = DTYPE_F16 if out is None else _dtype_code(out)
+    call("bmxk_rtn_decode", ctypes.byref(g), _ptr(q), _ptr(pool.pages), _ptr(page_table), page_table.stride(0),
+         _ptr(n_pages), batch, max_pages, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, ctypes.c_float(sm_scale),
+         _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), _stream())
+    return out if partial_out is None else partial_out

@@ -161,6 +161,46 @@ int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pa
  * (float bit patterns). */
 int bmxk_k2b_make_v_lut(const float* codebook, uint32_t* out_lut);
 
+/* ---- plain RTN caches (bmx arms rtn_token / rtn_channel) -------------------------------- */
+/* Geometry of an RTN cache (head dim 128).  Keys are post-RoPE.
+ * bmx: src/bmx/cache/codecs.py:720-725, src/bmx/quant/rtn.py:23-53 (symmetric, no zero point). */
+typedef struct bmxk_rtn_geom {
+  int32_t h_kv;
+  int32_t n_q_groups; /* 1..8 */
+  int32_t page;       /* 64 or 128 */
+  int32_t k_arm;      /* 0: rtn_token (groups of channels per token); 1: rtn_channel (groups of tokens per channel) */
+  int32_t k_group;    /* 32, 64 or 128; for rtn_channel it must divide page */
+  int32_t v_group;    /* value arm is rtn_token; 32, 64 or 128 */
+  int32_t kbits;      /* 2..4, stored as two's-complement nibbles */
+  int32_t vbits;      /* 2, stored as two's-complement 2-bit fields */
+} bmxk_rtn_geom;
+
+size_t bmxk_rtn_page_block_bytes(const bmxk_rtn_geom* g);   /* pool: pages[n_slots][h_kv][bytes] */
+size_t bmxk_rtn_decode_workspace_bytes(const bmxk_rtn_geom* g, int batch, int max_pages);
+
+/* Quantize-on-append of n_seq * n_pages full pages; sources addressed as in bmxk_k2b_append.
+ * bmx: src/bmx/cache/packed_streaming.py:643-678 -> quantize_packed("rtn_token" | "rtn_channel"). */
+int bmxk_rtn_append(const bmxk_rtn_geom* g, const void* k, const void* v, int src_dtype, int64_t stride_seq,
+                    int64_t stride_head, int64_t stride_tok, const int32_t* slots, int n_seq, int n_pages,
+                    void* pages, void* stream);
+
+/* Rewrites n pages into bmx's containers and/or dequantizes them; any output may be NULL.
+ * bmx: src/bmx/cache/triton_dequant_attention.py:1390-1451 build_kv_stacked_packed and
+ *      src/bmx/cache/codecs.py:807-811 dequant_packed.
+ * k_codes int8: rtn_token (n, h_kv, page, 128); rtn_channel (n, h_kv*128, page)   [Q_int of the block dict]
+ * k_scales fp16: rtn_token (n, h_kv, page, 128/k_group); rtn_channel (n, h_kv*128, page/k_group)
+ * v_codes int8 (n, h_kv, page, 128); v_scales fp16 (n, h_kv, page, 128/v_group)
+ * k_deq, v_deq float32 (n, page, h_kv*128) = code * fp16 scale. */
+int bmxk_rtn_export(const bmxk_rtn_geom* g, const void* pages, const int32_t* slots, int n, int8_t* k_codes,
+                    void* k_scales, int8_t* v_codes, void* v_scales, float* k_deq, float* v_deq, void* stream);
+
+/* One decode step over RTN pages + the fp16 window; arguments as in bmxk_k2b_decode.
+ * bmx: src/bmx/cache/triton_dequant_attention.py:580-832 fused_decode_attention_packed (+ tail, merge). */
+int bmxk_rtn_decode(const bmxk_rtn_geom* g, const void* q, const void* pages, const int32_t* page_table,
+                    int table_stride, const int32_t* n_pages, int batch, int max_pages, const void* k_tail,
+                    const void* v_tail, const int32_t* tail_len, int tail_cap, float sm_scale, void* workspace,
+                    size_t workspace_bytes, void* out, int out_dtype, float* partial_out, void* stream);
+
 /* Merges n_parts partial states (n_parts, rows, 130) float32 -> out (rows, 128).
  * bmx: src/bmx/cache/triton_dequant_attention.py:409-461 _fused_merge_kernel (same formula,
  * max carried in log2 units). */
