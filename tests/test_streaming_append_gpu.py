@@ -1,0 +1,102 @@
+"""Quantize-on-append through the layer state: token-by-token appends onto a prefix flush whole pages on
+the reference's schedule, each token is quantized once from its pristine source, and the committed
+prefix never changes afterwards (bmx: tests/test_streaming_cache.py:255-366 are the properties)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bmx_oracle as O
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+@pytest.mark.parametrize("page,dtype", [(128, torch.bfloat16), (64, torch.float16)])
+def test_token_by_token_equals_bulk_and_prefix_is_frozen(page, dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope, default_rope_tables
+    from bmx_b200.schedule import compute_flush_schedule
+
+    dev = torch.device("cuda:0")
+    B, h_kv, G, rank, group, W = 3, 2, 4, 32, 64, 128
+    prefix, steps = 3 * page + 17, 2 * page + 5
+    T = prefix + steps
+    gen = torch.Generator().manual_seed(31)
+    basis = torch.zeros(h_kv * D, rank)
+    for h in range(h_kv):
+        Q, _ = torch.linalg.qr(torch.randn(D, rank, generator=gen))
+        basis[h * D:(h + 1) * D] = Q
+    coef = torch.randn(B, h_kv, T, rank, generator=gen) * torch.arange(1, rank + 1).float() ** -1.5
+    k_pre = (torch.einsum("bhtr,hcr->bhtc", coef, basis.view(h_kv, D, rank)) + 0.1 * torch.randn(B, h_kv, T, D, generator=gen))
+    k_pre, v = k_pre.to(dtype).to(dev), torch.randn(B, h_kv, T, D, generator=gen).to(dtype).to(dev)
+    cos, sin = default_rope_tables(500000.0, D, T + 256, device=dev)
+    k_post = apply_rope(k_pre.float(), cos[:T], sin[:T]).to(dtype)
+    geom = K.k2b_geom(h_kv, G, page, rank, group, h_kv)
+
+    def fresh():
+        st = K2bLayerState(geom, B, 2 * page, W, dev, cos.half(), sin.half())  # small pool: must grow
+        st.set_basis(basis.to(dev))
+        return st
+
+    # streaming: prefix in one call, then one token per step
+    st = fresh()
+    st.append(k_pre[:, :, :prefix], k_post[:, :, :prefix], v[:, :, :prefix])
+    assert st.committed == compute_flush_schedule(prefix, W, page)
+    snap = None
+    for t in range(prefix, T):
+        st.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+        assert st.committed == compute_flush_schedule(t + 1, W, page) and st.seq_len() == t + 1
+        assert W <= st.tail_len < W + page
+        if snap is None and st.committed > compute_flush_schedule(prefix, W, page):
+            n0 = compute_flush_schedule(prefix, W, page) // page  # pages that existed before the first new flush
+            snap = (n0, {a: x.clone() for a, x in K.k2b_export_stacks(st.pool, st.page_table[:, :n0].contiguous().view(-1)).items()})
+    # bulk: everything in one call
+    bulk = fresh()
+    bulk.append(k_pre, k_post, v)
+    assert bulk.committed == st.committed == compute_flush_schedule(T, W, page) and bulk.tail_len == st.tail_len
+    n_pg = st.committed // page
+    a = K.k2b_export_stacks(st.pool, st.page_table[:, :n_pg].contiguous().view(-1))
+    b = K.k2b_export_stacks(bulk.pool, bulk.page_table[:, :n_pg].contiguous().view(-1))
+    for name in a:
+        assert torch.equal(a[name], b[name]), f"{name}: token-by-token and bulk appends wrote different bytes"
+    # the committed prefix is bitwise frozen
+    n0, before = snap
+    after = K.k2b_export_stacks(st.pool, st.page_table[:, :n0].contiguous().view(-1))
+    for name in before:
+        assert torch.equal(before[name], after[name]), f"{name}: committed pages changed after later appends"
+    assert torch.equal(st.k_win[:, :, : st.tail_len], bulk.k_win[:, :, : st.tail_len])
+    # the window holds the last tokens, fp16-exact, and a decode over the state matches the oracle
+    assert torch.equal(st.v_win[:, :, : st.tail_len], v[:, :, T - st.tail_len:].half())
+    q = (torch.randn(B, h_kv * G, D, generator=gen) / math.sqrt(D)).half().to(dev)
+    out = st.decode(q).float().cpu().numpy()
+    ex = {n: x.cpu().numpy() for n, x in a.items()}
+    basis16 = basis.half().float().numpy()
+    Vb = np.zeros((h_kv * D, h_kv * rank), np.float32)
+    for h in range(h_kv):
+        Vb[h * D:(h + 1) * D, h * rank:(h + 1) * rank] = basis16[h * D:(h + 1) * D]
+    signs = K.hadamard_signs(D, 0).numpy()
+    c16, s16 = cos.half().float().cpu().numpy(), sin.half().float().cpu().numpy()
+    for s in range(B):
+        kb, vb = [], []
+        for p in range(n_pg):
+            i = s * n_pg + p
+            kp = {"Us": np.concatenate([ex["us"][i, h].astype(np.float32) for h in range(h_kv)], 1), "V": Vb,
+                  "res_Q_int": O.unpack_signed_codes(ex["res_int_packed"][i], 3, page),
+                  "res_scale": ex["res_scale"][i].astype(np.float32)[..., None]}
+            vp = {"indices": O.unpack_codes(ex["v_idx_packed"][i], 2, h_kv * D), "norms": ex["v_norm"][i].astype(np.float32),
+                  "bits": 2, "h": h_kv}
+            kb.append((kp, p * page, (p + 1) * page))
+            vb.append((vp, p * page, (p + 1) * page))
+        ref = O.chunked_dequant_attention(
+            q[s].float().cpu().numpy()[:, None, :], kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead",
+            group=group, k_pre_rope=True, rope_cos=c16, rope_sin=s16,
+            k_tail=st.k_win[s, :, : st.tail_len].float().cpu().numpy(), v_tail=st.v_win[s, :, : st.tail_len].float().cpu().numpy(),
+            n_q_groups=G, scale=1.0 / math.sqrt(D), v_signs=signs)[:, 0, :]
+        err = np.abs(out[s] - ref).max(-1) / np.abs(ref).max(-1)
+        assert np.all(err <= 2e-3), float(err.max())
