@@ -278,3 +278,35 @@ def test_reference_golden_pages_and_output():
     torch.cuda.synchronize()
     K.check_status(ws)
     _assert_attn_close(out.cpu().numpy(), c["k2b_out_chunked"][:, 0, :][None])
+
+
+@pytest.mark.parametrize("page,rank,per_head,group,dtype", [(128, 32, True, 64, torch.float16), (128, 16, False, 64, torch.bfloat16),
+                                                            (64, 32, False, 32, torch.float16)])
+def test_append_bytes_equal_pinned_order_restatement(page, rank, per_head, group, dtype):
+    """Level II made exact: with the summation order pinned (oracle/cpu_ref.c repeats the kernel's order),
+    every byte the append kernel writes -- coefficients, residual nibbles, scales, value codes, norms --
+    equals the CPU restatement's, on the reference's own container layout."""
+    from oracle import cpu_ref
+
+    dev, K = _dev(), _K()
+    h_kv, n_seq, n_pages = 2, 2, 2
+    k, v, basis = make_k2b_inputs(23, n_seq, h_kv, n_pages * page, rank, per_head)
+    k, v = k.to(dtype), v.to(dtype)
+    g = K.k2b_geom(h_kv, 4, page, rank, group, h_kv if per_head else 1)
+    pool = K.K2bPool(g, 8, dev)
+    slots = torch.tensor([3, 0, 6, 5], dtype=torch.int32, device=dev)
+    signs, cb = K.hadamard_signs(D, 0), torch.tensor(K.GAUSSIAN_CODEBOOK[2])
+    K.k2b_append(pool, k.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev), slots, n_pages)
+    st = to_np(K.k2b_export_stacks(pool, slots))
+    for s in range(n_seq):
+        for p in range(n_pages):
+            i = s * n_pages + p
+            Mk = O.to_matrix(k[s, :, p * page:(p + 1) * page].float().numpy())
+            Mv = O.to_matrix(v[s, :, p * page:(p + 1) * page].float().numpy())
+            ref = cpu_ref.k2b_quant_page(Mk, Mv, basis.numpy(), signs.numpy(), cb.numpy(), h_kv=h_kv, page=page, rank=rank,
+                                         group=group, n_coef_heads=g.n_coef_heads)
+            assert np.array_equal(st["us"][i].view(np.uint16), ref["us"].view(np.uint16)), "coefficients"
+            assert np.array_equal(st["res_int_packed"][i], O.pack_signed_codes(ref["res_Q_int"], 3)), "residual nibbles"
+            assert np.array_equal(st["res_scale"][i].view(np.uint16), ref["res_scale"].view(np.uint16)), "residual scales"
+            assert np.array_equal(st["v_idx_packed"][i], O.pack_codes(ref["v_idx"].astype(np.int16), 2)), "value codes"
+            assert np.array_equal(st["v_norm"][i].view(np.uint16), ref["v_norm"].view(np.uint16)), "value norms"
