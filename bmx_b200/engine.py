@@ -21,6 +21,17 @@ from .schedule import compute_flush_schedule
 HEAD_DIM = K.HEAD_DIM
 
 
+def fit_basis(geom, k_pre_page: torch.Tensor) -> torch.Tensor:
+    """Rank-r right singular vectors of one page of pre-RoPE keys (h_kv, page, 128) -> (h_kv*128, rank) float32,
+    as bmx fits them on the first flush and then freezes them (bmx: src/bmx/decomp/lrs.py:35-41,
+    src/bmx/cache/packed_streaming.py:513-516).  One basis over all heads, or one per head."""
+    x = k_pre_page.float()
+    if geom.n_coef_heads == 1:
+        M = x.permute(1, 0, 2).reshape(x.shape[1], geom.h_kv * HEAD_DIM)
+        return torch.linalg.svd(M, full_matrices=False)[2][: geom.rank].mT.contiguous()
+    return torch.cat([torch.linalg.svd(x[h], full_matrices=False)[2][: geom.rank].mT for h in range(geom.h_kv)], 0).contiguous()
+
+
 class K2bLayerState:
     """Packed pages + fp16 recent window of one layer for `batch` sequences of equal length."""
 
@@ -62,14 +73,7 @@ class K2bLayerState:
     def fit_basis(self, k_pre_page: torch.Tensor) -> None:
         """Rank-r right singular vectors of the first page, as bmx fits them on the first flush
         (bmx: src/bmx/decomp/lrs.py:35-41).  k_pre_page: (h_kv, page, 128) of sequence 0."""
-        g = self.geom
-        x = k_pre_page.float()
-        if g.n_coef_heads == 1:
-            M = x.permute(1, 0, 2).reshape(x.shape[1], g.h_kv * HEAD_DIM)
-            _, _, Vh = torch.linalg.svd(M, full_matrices=False)
-            basis = Vh[: g.rank].mT.contiguous()
-        else:
-            basis = torch.cat([torch.linalg.svd(x[h], full_matrices=False)[2][: g.rank].mT for h in range(g.h_kv)], 0)
+        basis = fit_basis(self.geom, k_pre_page)
         self.set_basis(basis)
 
     def ensure_pages(self, n_more: int) -> None:

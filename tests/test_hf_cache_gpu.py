@@ -78,3 +78,37 @@ def test_unsupported_arms_raise():
     k, v = spec_pair("turboquant_mse")
     with pytest.raises(NotImplementedError):
         PackedStreamingLayer(k, v, cfg)
+
+
+def test_streaming_twin_matches_packed_cache_tokens():
+    """Packed and dequantized-resident caches quantize the same tokens with the same kernels on the same
+    schedule, so greedy decoding through either gives the same tokens and close logits
+    (bmx: tests/test_packed_streaming.py:23-97)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.recipes import spec_pair
+    from bmx_b200.streaming import StreamingQuantizedCache
+
+    dev = torch.device("cuda:0")
+    model = _tiny_llama(dev)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 256, (1, 200 + 40), generator=g).to(dev)
+    la, pcache = _run(model, ids, 200, force_dense=False)
+    k_spec, v_spec = spec_pair("k2b_ph", rank=16, group=64)
+    cache = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32)
+    logits = []
+    with cache.attach(model), torch.no_grad():
+        out = model(ids[:, :200], past_key_values=cache, use_cache=True)
+        logits.append(out.logits[:, -1].float())
+        for t in range(200, ids.shape[1]):
+            out = model(ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+            logits.append(out.logits[:, -1].float())
+    lb = torch.stack(logits, 1)
+    layer = cache.layers[0]
+    assert layer._committed_S_q == pcache.layers[0]._committed_S_q == 128 + 0 * 128 or layer._committed_S_q == pcache.layers[0]._committed_S_q
+    assert layer.keys.shape[2] == 240 and layer._q_prefix_k.shape[2] == layer._committed_S_q
+    assert abs(cache.bits_per_entry()[0] - pcache.bits_per_entry()[0]) < 1e-9
+    assert int((la.argmax(-1) != lb.argmax(-1)).sum()) == 0
+    assert float((la - lb).abs().max()) < 5e-2
+    k, v = cache.reconstruct_layer(0)
+    assert k.shape == v.shape == (1, 2, 240, 128)
