@@ -31,6 +31,12 @@ class RtnGeom(ctypes.Structure):
                 ("h_kv", "n_q_groups", "page", "k_arm", "k_group", "v_group", "kbits", "vbits")]
 
 
+class SpectralGeom(ctypes.Structure):
+    """Mirror of `bmxk_spectral_geom` (include/bmxk.h)."""
+
+    _fields_ = [(n, c_int32) for n in ("h_kv", "page", "group", "block_bytes", "scale_off")]
+
+
 class BmxkError(RuntimeError):
     """A bmxk entry point returned a non-zero status."""
 
@@ -73,6 +79,10 @@ _SIGNATURES = {
     "bmxk_rtn_decode": (c_int, [POINTER(RtnGeom), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t, c_void_p, c_int, c_void_p,
                                  c_void_p]),
+    "bmxk_spectral_append": (c_int, [POINTER(SpectralGeom), c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "bmxk_spectral_dequant_pages": (c_int, [POINTER(SpectralGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p, c_void_p]),
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),
 }

@@ -22,6 +22,7 @@ SOURCES = [
     ("k2b_codec.cu", ["-fmad=false"]),
     ("k2b_decode.cu", []),
     ("rtn.cu", ["-fmad=false"]),
+    ("spectral.cu", ["-fmad=false"]),
 ]
 
 

@@ -334,3 +334,93 @@ def rtn_decode(pool: RtnPool, q: torch.Tensor, page_table: torch.Tensor, n_pages
          _ptr(n_pages), batch, max_pages, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, ctypes.c_float(sm_scale),
          _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), _stream())
     return out if partial_out is None else partial_out
+
+
+# ---- K4 spectral key codec (per-head packs) -------------------------------------------------------
+
+from ._lib import SpectralGeom  # noqa: E402
+
+SPECTRAL_TIERS = (0, 2, 3, 4, 5, 6, 8)
+
+
+def _container_bits(b: int) -> int:
+    return 0 if b == 0 else (2 if b == 2 else (4 if b <= 4 else 8))
+
+
+class SpectralPackDev:
+    """Device copy of per-head spectral packs plus the page layout derived from their bit widths.
+
+    enc, dec: (h_kv, 128, 128) float32 with Y = M @ enc[h] and M_hat = Y_hat @ dec[h].T; bits: (h_kv, 128)
+    integers from SPECTRAL_TIERS (bmx: SpectralPack, src/bmx/cache/spectral.py:174-220, one pack per head)."""
+
+    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, page: int, group: int, device):
+        h_kv = enc.shape[0]
+        assert enc.shape == dec.shape == (h_kv, HEAD_DIM, HEAD_DIM) and bits.shape == (h_kv, HEAD_DIM)
+        assert all(int(b) in SPECTRAL_TIERS for b in bits.reshape(-1).tolist()), "bit widths must be tier members"
+        col_off = torch.zeros(h_kv, HEAD_DIM, dtype=torch.int32)
+        code_bytes = 0
+        for h in range(h_kv):
+            off = 0
+            for b in sorted(set(int(x) for x in bits[h].tolist())):  # directions laid out tier by tier, ascending
+                for j in (bits[h] == b).nonzero().flatten().tolist():
+                    col_off[h, j] = off
+                    off += page * _container_bits(b) // 8
+            code_bytes = max(code_bytes, off)
+        scale_off = (code_bytes + 15) // 16 * 16
+        block = scale_off + HEAD_DIM * (page // group) * 4
+        self.geom = SpectralGeom(h_kv, page, group, (block + 15) // 16 * 16, scale_off)
+        self.bits = bits.to(torch.int32)
+        self.enc = enc.to(device, torch.float32).contiguous()
+        self.dec = dec.to(device, torch.float32).contiguous()
+        self.col_bits = self.bits.to(device).contiguous()
+        self.col_off = col_off.to(device).contiguous()
+        self.device = device
+
+    def new_pool(self, n_slots: int) -> torch.Tensor:
+        return torch.zeros(n_slots, self.geom.h_kv, self.geom.block_bytes, dtype=torch.uint8, device=self.device)
+
+
+def spectral_append(pack: SpectralPackDev, pool: torch.Tensor, k_pre: torch.Tensor, slots: torch.Tensor, n_pages: int) -> None:
+    """Encodes and quantizes n_pages pages of every sequence of k_pre (n_seq, h_kv, T, 128) into the pool."""
+    _require_cuda(k_pre, slots, pool)
+    g = pack.geom
+    assert k_pre.dim() == 4 and k_pre.shape[1] == g.h_kv and k_pre.shape[3] == HEAD_DIM and k_pre.stride(3) == 1
+    assert slots.dtype == torch.int32 and slots.numel() == k_pre.shape[0] * n_pages
+    call("bmxk_spectral_append", ctypes.byref(g), _ptr(k_pre), _dtype_code(k_pre), k_pre.stride(0), k_pre.stride(1),
+         k_pre.stride(2), _ptr(pack.enc), _ptr(pack.col_bits), _ptr(pack.col_off), _ptr(slots), k_pre.shape[0], n_pages,
+         _ptr(pool), _stream())
+
+
+def spectral_dequant_pages(pack: SpectralPackDev, pool: torch.Tensor, slots: torch.Tensor, want_codes: bool = True,
+                           want_k: bool = True) -> dict:
+    """Pages -> {"codes": int8 (n, h, 128, page), "scales": float32 (n, h, 128, page/group), "k": float32 (n, page, h*128)}."""
+    g, n, dev = pack.geom, slots.numel(), pool.device
+    out = {}
+    if want_codes:
+        out["codes"] = torch.empty(n, g.h_kv, HEAD_DIM, g.page, dtype=torch.int8, device=dev)
+        out["scales"] = torch.empty(n, g.h_kv, HEAD_DIM, g.page // g.group, dtype=torch.float32, device=dev)
+    if want_k:
+        out["k"] = torch.empty(n, g.page, g.h_kv * HEAD_DIM, dtype=torch.float32, device=dev)
+    call("bmxk_spectral_dequant_pages", ctypes.byref(g), _ptr(pool), _ptr(pack.dec), _ptr(pack.col_bits), _ptr(pack.col_off),
+         _ptr(slots), n, _ptr(out.get("codes")), _ptr(out.get("scales")), _ptr(out.get("k")), _stream())
+    return out
+
+
+def spectral_tier_dict(pack: SpectralPackDev, codes: torch.Tensor, scales: torch.Tensor, head: int) -> dict:
+    """bmx's flat packed dict {t{b}_codes, t{b}_scale} of one page and head from unpacked codes (128, page)
+    and scales (128, page/group): the same containers spectral_quantize_packed returns."""
+    out = {}
+    bits = pack.bits[head]
+    for b in sorted(set(int(x) for x in bits.tolist())):
+        if b == 0:
+            continue
+        cols = (bits == b).nonzero().flatten().to(codes.device)
+        q = codes[cols]
+        if b in (2, 4):
+            out[f"t{b}_codes"] = pack_u((q.to(torch.int16) + 2 ** (b - 1)), b)
+        elif b == 3:
+            out[f"t{b}_codes"] = pack_s4(q, b)
+        else:
+            out[f"t{b}_codes"] = q
+        out[f"t{b}_scale"] = scales[cols].unsqueeze(-1)
+    return out

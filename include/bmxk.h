@@ -201,6 +201,37 @@ int bmxk_rtn_decode(const bmxk_rtn_geom* g, const void* q, const void* pages, co
                     const void* v_tail, const int32_t* tail_len, int tail_cap, float sm_scale, void* workspace,
                     size_t workspace_bytes, void* out, int out_dtype, float* partial_out, void* stream);
 
+/* ---- K4 spectral key codec, per-head packs ------------------------------------------------ */
+/* bmx: src/bmx/cache/spectral.py:174-220 (SpectralPack), :631-645 (tier_columns), :703-839 (packed codec).
+ * Each KV head has a 128 x 128 encoder and decoder and a bit width per encoded direction, a member of
+ * {0, 2, 3, 4, 5, 6, 8}.  The page block of one (slot, head) holds, for every direction with bits, a row of
+ * page codes in bmx's container for its tier (2/4 bits offset-binary, 3 bits in two's-complement nibbles,
+ * 5/6/8 bits as int8) at byte offset col_off[head][direction], then float32 scales [direction][page/group]
+ * at scale_off.  The host lays directions out by tier (bmx_b200.kernels.spectral_layout). */
+typedef struct bmxk_spectral_geom {
+  int32_t h_kv;
+  int32_t page;        /* 64 or 128 */
+  int32_t group;       /* token group of the scales; divides page */
+  int32_t block_bytes; /* bytes of one (slot, head) page block, the same for every head */
+  int32_t scale_off;   /* byte offset of the scales inside a block (multiple of 4) */
+} bmxk_spectral_geom;
+
+/* Quantize-on-append of pre-RoPE keys: Y = M @ enc, per-direction RTN with 10 step-refinement rounds.
+ * bmx: spectral_quantize_packed(M, pack, mse_scale=True), src/bmx/cache/spectral.py:765-809.
+ * enc: (h_kv, 128, 128) float32, enc[h][c][j]; col_bits, col_off: int32 (h_kv, 128) in device memory. */
+int bmxk_spectral_append(const bmxk_spectral_geom* g, const void* k_pre, int src_dtype, int64_t stride_seq,
+                         int64_t stride_head, int64_t stride_tok, const float* enc, const int32_t* col_bits,
+                         const int32_t* col_off, const int32_t* slots, int n_seq, int n_pages, void* pages,
+                         void* stream);
+
+/* Unpacks and/or dequantizes n pages.  bmx: spectral_dequant_packed, src/bmx/cache/spectral.py:812-839.
+ * codes int8 (n, h_kv, 128, page) signed levels per direction (0 for directions without bits);
+ * scales float32 (n, h_kv, 128, page/group); k_out float32 (n, page, h_kv*128) = Y_hat @ dec^T with
+ * dec (h_kv, 128, 128) float32, dec[h][c][j].  Any output may be NULL. */
+int bmxk_spectral_dequant_pages(const bmxk_spectral_geom* g, const void* pages, const float* dec,
+                                const int32_t* col_bits, const int32_t* col_off, const int32_t* slots, int n,
+                                int8_t* codes, float* scales, float* k_out, void* stream);
+
 /* Merges n_parts partial states (n_parts, rows, 130) float32 -> out (rows, 128).
  * bmx: src/bmx/cache/triton_dequant_attention.py:409-461 _fused_merge_kernel (same formula,
  * max carried in log2 units). */
