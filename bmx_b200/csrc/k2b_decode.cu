@@ -1,5 +1,5 @@
 // k2b split-KV decode for sm_100a: a persistent, warp-specialised kernel that streams packed pages
-// HBM -> shared memory with 1-D bulk async copies (one producer warp, an mbarrier ring) and has
+// HBM -> shared memory with 1-D bulk async copies (one copy-issuing warp, an mbarrier ring) and has
 // eight consumer warps dequantize in registers and feed mma.sync, plus the small kernel that merges
 // the per-CTA partial states, attends over the fp16 recent window and undoes the value rotation.
 //
@@ -27,6 +27,10 @@
 #include <mutex>
 
 #include "decode_common.cuh"
+
+#ifndef BMXK_SKIP
+#define BMXK_SKIP 0  // diagnostic builds only: bit mask of phases to leave out (results are then wrong)
+#endif
 
 namespace bmxk {
 
@@ -100,9 +104,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, PAGE, lane);
   for (int i = tid; i < p.batch; i += DEC_THREADS) npg_sm[i] = p.n_pages[i];
+  // query rows beyond the group size stay zero in every stage (their scores are never read)
+  for (int st_ = 0; st_ < n_stages; ++st_) {
+    uint32_t* qr0 = reinterpret_cast<uint32_t*>(stage0 + (size_t)st_ * STAGE_BYTES + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
+    for (int i = tid; i < QROT_BYTES / 4; i += DEC_THREADS) qr0[i] = 0u;
+  }
   if (tid == 0) {
     for (int s = 0; s < n_stages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], 2);  // the copy warp (with the byte count) and the query-rotation warp
       mbar_init(&empty[s], DEC_CONSUMER_WARPS);
     }
     fence_barrier_init();
@@ -120,64 +129,74 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 
   if (warp >= DEC_CONSUMER_WARPS) {
     // ===================== producer warpgroup =====================
-    // Hand most of this warpgroup's registers to the consumers; only its first warp does work.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp != DEC_CONSUMER_WARPS) return;
-    // zero the query rows beyond G in every stage once (their scores are never read)
-    for (int s = 0; s < n_stages; ++s) {
-      uint32_t* qr = reinterpret_cast<uint32_t*>(stage0 + (size_t)s * STAGE_BYTES + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
-      for (int i = lane; i < QROT_BYTES / 4; i += 32) qr[i] = 0u;
-    }
-    int cur_bh = -1;
+    // Hands most of its registers to the consumers.  Its first warp only issues the bulk copies of each
+    // tile; the other three take the tiles in turn and prepare the tile's rotated queries.  Two arrivals
+    // complete a stage: the copy warp's (with the byte count) and the rotating warp's.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     int s = 0;
     uint32_t ph = 1;  // parity to wait for on empty[s]: a fresh barrier passes parity 1
-    for (int f = f_begin; f < f_end; ++f, cur.next(npg_sm, g.h_kv, PAGE, p.batch)) {
-      const int b = cur.b, h = cur.h, j = cur.j;
-      const int bh = b * g.h_kv + h;
-      if (bh != cur_bh) {
-        cur_bh = bh;
-        const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
-        __syncwarp();
-        for (int i = lane; i < G * HEAD_DIM; i += 32) q_sm[i] = __half2float(qsrc[i]) * p.scale_log2;
-        __syncwarp();
-      }
-      if (!wait_or_flag(&empty[s], ph, p.status, 1)) return;
-      uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
-      // q rotated back by the tile's base position
-      {
-        const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
-        __half* qr = reinterpret_cast<__half*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int c = lane + 32 * jj;  // pair (c, c + 64)
-          const float cs = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
-          const float sn = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
-          for (int qi = 0; qi < G; ++qi) {
-            const float x1 = q_sm[qi * HEAD_DIM + c], x2 = q_sm[qi * HEAD_DIM + c + 64];
-            const float y1 = x1 * cs + x2 * sn, y2 = x2 * cs - x1 * sn;
-            // channel ch -> k-step ch/16, register (ch%16)/8, t = (ch%8)/2, e = ch%2
-            const int ks1 = c >> 4, r1 = (c >> 3) & 1, tt = (c & 7) >> 1, e = c & 1;
-            const int ks2 = ks1 + 4;
-            // B fragment of k-step ks: word ((ks/2)*32 + 4*qi + tt)*4 + (ks%2)*2 + r1
-            qr[((((ks1 >> 1) * 32 + qi * 4 + tt) * 4 + (ks1 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y1);
-            qr[((((ks2 >> 1) * 32 + qi * 4 + tt) * 4 + (ks2 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y2);
+    if (warp == DEC_CONSUMER_WARPS) {
+      for (int f = f_begin; f < f_end; ++f, cur.next(npg_sm, g.h_kv, PAGE, p.batch)) {
+        if (!wait_or_flag(&empty[s], ph, p.status, 1)) return;
+        if (lane == 0) {
+          const int b = cur.b, h = cur.h, j = cur.j;
+          uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+          const int pg0 = j * PAGES_PER_TILE;
+          const int npg = min(PAGES_PER_TILE, npg_sm[b] - pg0);
+          const int chd = (g.n_coef_heads == 1) ? 0 : h;
+          mbar_arrive_expect_tx(&full[s], (uint32_t)(npg * (COEF_PAGE_BYTES + PB)));
+          for (int k = 0; k < npg; ++k) {
+            const int slot = p.page_table[(int64_t)b * p.table_stride + pg0 + k];
+            bulk_g2s(st + k * COEF_PAGE_BYTES,
+                     reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_PAGE_BYTES,
+                     COEF_PAGE_BYTES, &full[s]);
+            bulk_g2s(st + COEF_TILE_BYTES + k * PB, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &full[s]);
           }
         }
+        if (++s == n_stages) s = 0, ph ^= 1;
       }
-      __syncwarp();
-      if (lane == 0) {
-        const int np = npg_sm[b];
-        const int pg0 = j * PAGES_PER_TILE;
-        const int npg = min(PAGES_PER_TILE, np - pg0);
-        const int chd = (g.n_coef_heads == 1) ? 0 : h;
-        mbar_arrive_expect_tx(&full[s], (uint32_t)(npg * (COEF_PAGE_BYTES + PB)));
-        for (int k = 0; k < npg; ++k) {
-          const int slot = p.page_table[(int64_t)b * p.table_stride + pg0 + k];
-          bulk_g2s(st + k * COEF_PAGE_BYTES,
-                   reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_PAGE_BYTES,
-                   COEF_PAGE_BYTES, &full[s]);
-          bulk_g2s(st + COEF_TILE_BYTES + k * PB, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &full[s]);
+      return;
+    }
+    // ---- query rotation warps: warp r of 3 takes tiles r, r+3, ... of the CTA's range ----
+    const int rw = warp - DEC_CONSUMER_WARPS - 1;
+    int it = 0;
+    for (int f = f_begin; f < f_end; ++f, ++it, cur.next(npg_sm, g.h_kv, PAGE, p.batch)) {
+      if (it % 3 == rw) {
+        const int b = cur.b, h = cur.h, j = cur.j;
+        // everything this tile needs from global memory is requested before the stage is waited for
+        const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
+        const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
+        float cs[2], sn[2], x1[2][8], x2[2][8];
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int c = lane + 32 * jj;  // rotary pair (c, c + 64)
+          cs[jj] = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
+          sn[jj] = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
+#pragma unroll
+          for (int qi = 0; qi < 8; ++qi) {
+            x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
+            x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
+          }
         }
+        if (!wait_or_flag(&empty[s], ph, p.status, 3)) return;
+        __half* qr = reinterpret_cast<__half*>(stage0 + (size_t)s * STAGE_BYTES + COEF_TILE_BYTES + PAGES_PER_TILE * PB);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int c = lane + 32 * jj;
+          // channel ch -> k-step ch/16, register (ch%16)/8, t = (ch%8)/2, e = ch%2
+          const int ks1 = c >> 4, r1 = (c >> 3) & 1, tt = (c & 7) >> 1, e = c & 1, ks2 = ks1 + 4;
+#pragma unroll
+          for (int qi = 0; qi < 8; ++qi)
+            if (qi < G) {
+              const float a = x1[jj][qi] * p.scale_log2, bb = x2[jj][qi] * p.scale_log2;
+              const float y1 = a * cs[jj] + bb * sn[jj], y2 = bb * cs[jj] - a * sn[jj];
+              // B fragment of k-step ks: word ((ks/2)*32 + 4*qi + tt)*4 + (ks%2)*2 + r1
+              qr[((((ks1 >> 1) * 32 + qi * 4 + tt) * 4 + (ks1 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y1);
+              qr[((((ks2 >> 1) * 32 + qi * 4 + tt) * 4 + (ks2 & 1) * 2 + r1) * 2) + e] = __float2half_rn(y2);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
       }
       if (++s == n_stages) s = 0, ph ^= 1;
     }
@@ -185,7 +204,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   }
 
   // ===================== consumer warps =====================
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
   // loop-invariant rotation of the two token rows this lane owns (offsets inside the tile)
   uint32_t cosr[2][8], sinr[2][8], nsinr[2][8];
 #pragma unroll
@@ -290,6 +309,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       //      so that the pipes overlap ----
       uint32_t VA[8][4];
       auto unpack_v = [&]() {
+        if (BMXK_SKIP & 1) {
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) VA[mt][0] = VA[mt][1] = VA[mt][2] = VA[mt][3] = 0x3C003C00u;
+          return;
+        }
         const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
         const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
 #pragma unroll
@@ -337,6 +361,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int qd = 0; qd < 4; ++qd) {
+            if (BMXK_SKIP & 8) {
+              acc[4 * qd][c] = acc[4 * qd + 1][c] = acc[4 * qd + 2][c] = acc[4 * qd + 3][c] = sc[4 * qd] & 0x3FFF3FFFu;
+              continue;
+            }
             const uint32_t wlo = ww[c][qd], whi = ww[c][qd] >> 8;
             // (w & mask) ^ magic : nibble^8 under a 1024 (or 1024 + 16 x) exponent
             const __half2 h0 = u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u));
@@ -353,13 +381,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       }
       // ---- K_pre = coef x basis^T + residual ----
 #pragma unroll
-      for (int n = 0; n < 16; ++n)
+      for (int n = 0; n < ((BMXK_SKIP & 4) ? 0 : 16); ++n)
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks)
           mma_f16acc(acc[n][0], acc[n][1], A[ks][0], A[ks][1], A[ks][2], A[ks][3], Bb[n][ks][0], Bb[n][ks][1]);
       // ---- rotate by the offset inside the tile ----
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < ((BMXK_SKIP & 2) ? 0 : 2); ++c)
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const __half2 lo = u32_as_h2(acc[n][c]), hi = u32_as_h2(acc[n + 8][c]);
@@ -376,7 +404,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       {
         const uint4* qp = reinterpret_cast<const uint4*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB) + lane;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
+        for (int k4 = 0; k4 < ((BMXK_SKIP & 16) ? 0 : 4); ++k4) {
           const uint4 v = qp[32 * k4];  // B fragments of k-steps 2*k4 and 2*k4+1
           mma_f32acc(S[0], S[1], S[2], S[3], acc[4 * k4][0], acc[4 * k4][1], acc[4 * k4 + 1][0], acc[4 * k4 + 1][1], v.x, v.y);
           mma_f32acc(S2[0], S2[1], S2[2], S2[3], acc[4 * k4 + 2][0], acc[4 * k4 + 2][1], acc[4 * k4 + 3][0], acc[4 * k4 + 3][1], v.z, v.w);
@@ -417,7 +445,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
         pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(w2, w3)));
       }
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt)
+      for (int mt = 0; mt < ((BMXK_SKIP & 1) ? 1 : 8); ++mt)
         mma_f32acc(O[mt][0], O[mt][1], O[mt][2], O[mt][3], VA[mt][0], VA[mt][1], VA[mt][2], VA[mt][3], pb0, pb1);
     }
     __syncwarp();
