@@ -21,7 +21,7 @@ class K2bGeom(ctypes.Structure):
     """Mirror of `bmxk_k2b_geom` (include/bmxk.h)."""
 
     _fields_ = [(n, c_int32) for n in
-                ("h_kv", "n_q_groups", "page", "rank", "group", "n_coef_heads", "kbits", "vbits")]
+                ("h_kv", "n_q_groups", "page", "rank", "group", "n_coef_heads", "kbits", "vbits", "layout")]
 
 
 class RtnGeom(ctypes.Structure):

@@ -21,6 +21,7 @@ SOURCES = [
     ("api.cu", []),
     ("k2b_codec.cu", ["-fmad=false"]),
     ("k2b_decode.cu", []),
+    ("k2b_decode_t5.cu", []),
     ("rtn.cu", ["-fmad=false"]),
     ("spectral.cu", ["-fmad=false"]),
 ]

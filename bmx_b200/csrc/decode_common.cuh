@@ -69,10 +69,50 @@ struct K2bMergeParams {
   void* out;
   int out_dtype;
   float* partial_out;
+  int n_sub;  // partial records per (CTA, sequence, head): record of sub s sits s*(main_grid + batch*h_kv) slots further
 };
+
+struct K2bDecodeParams {
+  K2bGeom g;
+  const __half* q;
+  const uint8_t* pages;
+  const __half* coefs;
+  const __half* basis16;
+  const int32_t* page_table;
+  int table_stride;
+  const int32_t* n_pages;
+  int batch;
+  const __half* rope_cos;
+  const __half* rope_sin;
+  int64_t pos_offset;
+  uint32_t lut_lo, lut_hi;
+  float lut_alpha, lut_beta;
+  float scale_log2;  // softmax scale * log2(e)
+  float* part;       // (grid + batch*h_kv, n_q_groups, PART_STRIDE)
+  int32_t* status;
+  int n_stages;
+};
+
+__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;  // another wait already gave up
+    if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy was lost; report and leave
+      if (atomicCAS(status, 0, 1) == 0) {
+        status[1] = blockIdx.x;
+        status[2] = where;
+      }
+      return false;
+    }
+  }
+  return true;
+}
 
 // SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
 int num_sms();
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
+// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); writes two partial records per slot
+int launch_decode_t5(const K2bDecodeParams& prm, int grid, cudaStream_t s);
 
 }  // namespace bmxk

@@ -34,7 +34,7 @@ __global__ void k2b_project_kernel(K2bGeom g, const T* __restrict__ k_pre, int64
       const float* b = basis + (int64_t)h * HEAD_DIM * g.rank + i;
       for (int c = 0; c < HEAD_DIM; ++c) acc = fmaf(load_as_float<T>(row + c), b[(int64_t)c * g.rank], acc);
     }
-    out[k2b_coef_idx(r, i, g.rank)] = __float2half_rn(acc);
+    out[k2b_coef_idx(g.layout, r, i, g.rank)] = __float2half_rn(acc);
   }
 }
 
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(128) k2b_quant_page_kernel(K2bGeom g, const T*
   const T* ksrc = k_pre + seq * stride_seq + h * stride_head + (int64_t)pg * page * stride_tok;
   const T* vsrc = v + seq * stride_seq + h * stride_head + (int64_t)pg * page * stride_tok;
 
-  for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(o / rank, o % rank, rank)]);
+  for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
   __syncthreads();
 
   // ---- keys: thread = channel ----
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(128) k2b_quant_page_kernel(K2bGeom g, const T*
         amax = fmaxf(amax, fabsf(R));
       }
       const float scale = fmaxf(amax, 1e-12f) / qmax;
-      kscale[k2b_kscale_idx(grp, c)] = __float2half_rn(scale);
+      kscale[k2b_kscale_idx(g.layout, grp, c)] = __float2half_rn(scale);
       for (int r = grp * group; r < (grp + 1) * group; ++r) {
         float L = 0.f;
 #pragma unroll
@@ -143,6 +143,29 @@ __global__ void __launch_bounds__(128) k2b_quant_page_kernel(K2bGeom g, const T*
   __syncthreads();
   // ---- assemble native words ----
   uint32_t* kres = reinterpret_cast<uint32_t*>(blk);
+  if (g.layout == 1) {
+    // row order: word w of the K residual = (chunk k, token r, word j); of the V codes = (chunk cc, channel c, word j)
+    for (int w = tid; w < page * 16; w += blockDim.x) {
+      const int j = w & 3, r = (w >> 2) & 127, k = w >> 9;
+      const int base = (j < 2) ? 16 * k + 8 * j : 64 + 16 * k + 8 * (j - 2);
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) word |= ((uint32_t)kcode[r * HEAD_DIM + base + 2 * i + e] & 0xFu) << (16 * e + 4 * i);
+      kres[w] = word;
+    }
+    uint32_t* vw1 = reinterpret_cast<uint32_t*>(blk + k2b_off_vcode(page, group));
+    for (int w = tid; w < page * 8; w += blockDim.x) {
+      const int j = w & 3, c = (w >> 2) & 127, cc = w >> 9;
+      uint32_t word = 0;
+#pragma unroll
+      for (int tau = 0; tau < 16; ++tau)
+        word |= (uint32_t)vcode[(64 * cc + 16 * j + tau) * HEAD_DIM + c] << (tau < 8 ? 4 * tau : 4 * (tau - 8) + 2);
+      vw1[w] = word;
+    }
+    return;
+  }
   for (int w = tid; w < page * 16; w += blockDim.x) {
     const int q = w & 3, ln = (w >> 2) & 31, th = (w >> 7) & 1, wr = w >> 8;
     const int gg = ln >> 2, t = ln & 3;
@@ -179,15 +202,15 @@ __global__ void __launch_bounds__(128) k2b_quant_page_kernel(K2bGeom g, const T*
 // ---------------------------------------------------------------------------------------------
 // Exporter: native page -> the reference's stacked tensors.  One block per (page, head).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ int k2b_read_kcode(const uint32_t* kres, int r, int c) {
+__device__ __forceinline__ int k2b_read_kcode(int lay, const uint32_t* kres, int r, int c) {
   int w, b;
-  k2b_kres_loc(r, c, w, b);
+  k2b_kres_loc(lay, r, c, w, b);
   const int nib = (kres[w] >> b) & 0xF;
   return (nib ^ 8) - 8;
 }
-__device__ __forceinline__ int k2b_read_vcode(const uint32_t* vw, int r, int c) {
+__device__ __forceinline__ int k2b_read_vcode(int lay, const uint32_t* vw, int r, int c) {
   int w, b;
-  k2b_vcode_loc(r, c, w, b);
+  k2b_vcode_loc(lay, r, c, w, b);
   return (vw[w] >> b) & 3;
 }
 
@@ -206,25 +229,25 @@ __global__ void k2b_export_kernel(K2bGeom g, const uint8_t* __restrict__ pages, 
   // res_int_packed[n][h*128 + c][r/2]
   for (int o = threadIdx.x; o < HEAD_DIM * page / 2; o += blockDim.x) {
     const int c = o / (page / 2), rb = o % (page / 2);
-    const uint32_t lo = k2b_read_kcode(kres, 2 * rb, c) & 0xF, hi = k2b_read_kcode(kres, 2 * rb + 1, c) & 0xF;
+    const uint32_t lo = k2b_read_kcode(g.layout, kres, 2 * rb, c) & 0xF, hi = k2b_read_kcode(g.layout, kres, 2 * rb + 1, c) & 0xF;
     res_int_packed[((int64_t)n * C + h * HEAD_DIM + c) * (page / 2) + rb] = (uint8_t)(lo | (hi << 4));
   }
   for (int o = threadIdx.x; o < HEAD_DIM * ngrp; o += blockDim.x) {
     const int c = o / ngrp, gi = o % ngrp;
-    res_scale[((int64_t)n * C + h * HEAD_DIM + c) * ngrp + gi] = kscale[k2b_kscale_idx(gi, c)];
+    res_scale[((int64_t)n * C + h * HEAD_DIM + c) * ngrp + gi] = kscale[k2b_kscale_idx(g.layout, gi, c)];
   }
   // v_idx_packed[n][r][(h*128 + c)/4]
   for (int o = threadIdx.x; o < page * HEAD_DIM / 4; o += blockDim.x) {
     const int r = o / (HEAD_DIM / 4), cb = o % (HEAD_DIM / 4);
     uint32_t b = 0;
-    for (int k = 0; k < 4; ++k) b |= (uint32_t)k2b_read_vcode(vw, r, 4 * cb + k) << (2 * k);
+    for (int k = 0; k < 4; ++k) b |= (uint32_t)k2b_read_vcode(g.layout, vw, r, 4 * cb + k) << (2 * k);
     v_idx_packed[((int64_t)n * page + r) * (C / 4) + h * (HEAD_DIM / 4) + cb] = (uint8_t)b;
   }
   for (int r = threadIdx.x; r < page; r += blockDim.x) v_norm[((int64_t)n * page + r) * g.h_kv + h] = vn[r];
   if (h < g.n_coef_heads) {
     const __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + h) * (page * rank);
     for (int o = threadIdx.x; o < page * rank; o += blockDim.x)
-      us[((int64_t)n * g.n_coef_heads + h) * (page * rank) + o] = cblk[k2b_coef_idx(o / rank, o % rank, rank)];
+      us[((int64_t)n * g.n_coef_heads + h) * (page * rank) + o] = cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)];
   }
 }
 
@@ -254,7 +277,7 @@ __global__ void __launch_bounds__(128) k2b_dequant_kernel(K2bGeom g, const uint8
   const int ch = (g.n_coef_heads == 1) ? 0 : h;
   const __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (page * rank);
   if (k_out) {
-    for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(o / rank, o % rank, rank)]);
+    for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
     __syncthreads();
     const int c = tid;
     float vb[32];
@@ -265,7 +288,7 @@ __global__ void __launch_bounds__(128) k2b_dequant_kernel(K2bGeom g, const uint8
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (i < rank) L = fmaf(us[r * rank + i], vb[i], L);
-      const float res = (float)k2b_read_kcode(kres, r, c) * __half2float(kscale[k2b_kscale_idx(r / group, c)]);
+      const float res = (float)k2b_read_kcode(g.layout, kres, r, c) * __half2float(kscale[k2b_kscale_idx(g.layout, r / group, c)]);
       k_out[((int64_t)n * page + r) * C + h * HEAD_DIM + c] = L + res;
     }
   }
@@ -277,7 +300,7 @@ __global__ void __launch_bounds__(128) k2b_dequant_kernel(K2bGeom g, const uint8
     for (int r = warp; r < page; r += 4) {
       float x[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = codebook[k2b_read_vcode(vw, r, 4 * lane + k)] / sqrt_d;
+      for (int k = 0; k < 4; ++k) x[k] = codebook[k2b_read_vcode(g.layout, vw, r, 4 * lane + k)] / sqrt_d;
       fwht128_warp(x, lane);
       const float nn = __half2float(vn[r]);
 #pragma unroll
@@ -298,13 +321,15 @@ static int check_geom(const bmxk_k2b_geom* g, const char* who) {
                g->n_coef_heads);
   BMXK_REQUIRE(g->kbits >= 2 && g->kbits <= 4, "%s: kbits=%d must be in 2..4", who, g->kbits);
   BMXK_REQUIRE(g->vbits == 2, "%s: vbits=%d (only 2-bit value codes have a kernel)", who, g->vbits);
+  BMXK_REQUIRE(g->layout == 0 || (g->layout == 1 && g->page == 128), "%s: layout=%d must be 0, or 1 with page=128", who,
+               g->layout);
   return BMXK_OK;
 }
 
 static K2bGeom to_geom(const bmxk_k2b_geom* g) {
   K2bGeom o;
   o.h_kv = g->h_kv, o.n_q_groups = g->n_q_groups, o.page = g->page, o.rank = g->rank, o.group = g->group;
-  o.n_coef_heads = g->n_coef_heads, o.kbits = g->kbits, o.vbits = g->vbits;
+  o.n_coef_heads = g->n_coef_heads, o.kbits = g->kbits, o.vbits = g->vbits, o.layout = g->layout;
   return o;
 }
 

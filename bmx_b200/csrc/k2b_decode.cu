@@ -36,42 +36,6 @@ namespace bmxk {
 
 constexpr int DEC_CONSUMER_WARPS = 8;
 constexpr int DEC_THREADS = (DEC_CONSUMER_WARPS + 4) * 32;  // + one producer warpgroup (one warp of it works)
-struct K2bDecodeParams {
-  K2bGeom g;
-  const __half* q;
-  const uint8_t* pages;
-  const __half* coefs;
-  const __half* basis16;
-  const int32_t* page_table;
-  int table_stride;
-  const int32_t* n_pages;
-  int batch;
-  const __half* rope_cos;
-  const __half* rope_sin;
-  int64_t pos_offset;
-  uint32_t lut_lo, lut_hi;
-  float lut_alpha, lut_beta;
-  float scale_log2;  // softmax scale * log2(e)
-  float* part;       // (grid + batch*h_kv, n_q_groups, PART_STRIDE)
-  int32_t* status;
-  int n_stages;
-};
-
-__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy was lost; report and leave
-      if (atomicCAS(status, 0, 1) == 0) {
-        status[1] = blockIdx.x;
-        status[2] = where;
-      }
-      return false;
-    }
-  }
-  return true;
-}
-
 template <int RANK, int PAGE>
 __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDecodeParams p) {
   constexpr int KS = RANK / 16;               // k-steps of the low-rank contraction
@@ -490,6 +454,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   const int tiles_b = tiles_of(p.n_pages[b], g.page);
   const int T0 = cum[b] + h * tiles_b, T1 = T0 + tiles_b;
   const int cta0 = T0 / per_cta, cta1 = (tiles_b > 0) ? (T1 - 1) / per_cta : cta0 - 1;
+  const int sub_slots = p.main_grid + p.batch * g.h_kv;
 
   // ---- window scores: thread = token, one pass over its key row for all G queries ----
   const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
@@ -599,13 +564,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
     const int qi = o >> 7, ch = o & 127;
     float M = (tl > 0) ? tm[qi] : -INFINITY;  // tm written before the last barrier
-    for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(c + bh) * G + qi) * PART_STRIDE]);
+    for (int sb = 0; sb < p.n_sub; ++sb)
+      for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE]);
     float ar = 0.f;
-    for (int c = cta0; c <= cta1; ++c) {
-      const float* ps = p.part + ((int64_t)(c + bh) * G + qi) * PART_STRIDE;
-      const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
-      ar += ps[2 + ch] * f;
-    }
+    for (int sb = 0; sb < p.n_sub; ++sb)
+      for (int c = cta0; c <= cta1; ++c) {
+        const float* ps = p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
+        const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
+        ar += ps[2 + ch] * f;
+      }
     accs[o] = ar;
   }
   __syncthreads();
@@ -623,13 +590,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
     const int qi = o >> 7, ch = o & 127;
     const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
     float M = mt;
-    for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(c + bh) * G + qi) * PART_STRIDE]);
+    for (int sb = 0; sb < p.n_sub; ++sb)
+      for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE]);
     const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
     float l = lt * wt;
-    for (int c = cta0; c <= cta1; ++c) {
-      const float* ps = p.part + ((int64_t)(c + bh) * G + qi) * PART_STRIDE;
-      l += (ps[0] == -INFINITY) ? 0.f : ps[1] * ex2_approx(ps[0] - M);
-    }
+    for (int sb = 0; sb < p.n_sub; ++sb)
+      for (int c = cta0; c <= cta1; ++c) {
+        const float* ps = p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
+        l += (ps[0] == -INFINITY) ? 0.f : ps[1] * ex2_approx(ps[0] - M);
+      }
     float at = 0.f;
 #pragma unroll
     for (int k = 0; k < MERGE_SPLIT; ++k) at += atl[(k * G + qi) * HEAD_DIM + ch];
@@ -725,7 +694,7 @@ extern "C" {
 size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int max_pages) {
   if (!g || batch <= 0) return 0;
   (void)max_pages;
-  const size_t slots = (size_t)num_sms() + (size_t)batch * g->h_kv;
+  const size_t slots = ((size_t)num_sms() + (size_t)batch * g->h_kv) * (g->layout == 1 ? 2 : 1);
   return 256 + slots * g->n_q_groups * PART_STRIDE * sizeof(float);
 }
 
@@ -745,6 +714,8 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
                "bmxk_k2b_decode: group=%d must be 32/64/128 and divide page", g->group);
   BMXK_REQUIRE(g->n_coef_heads == 1 || g->n_coef_heads == g->h_kv, "bmxk_k2b_decode: n_coef_heads=%d", g->n_coef_heads);
   BMXK_REQUIRE(g->vbits == 2, "bmxk_k2b_decode: vbits=%d (only 2)", g->vbits);
+  BMXK_REQUIRE(g->layout == 0 || (g->layout == 1 && g->page == 128), "bmxk_k2b_decode: layout=%d must be 0, or 1 with page=128",
+               g->layout);
   BMXK_REQUIRE(batch >= 1 && (int64_t)batch * g->h_kv <= MAX_BH, "bmxk_k2b_decode: batch*h_kv=%lld out of range",
                (long long)batch * g->h_kv);
   BMXK_REQUIRE(max_pages >= 0 && tail_cap >= 0, "bmxk_k2b_decode: negative sizes");
@@ -771,11 +742,17 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
     K2bDecodeParams prm;
     prm.g.h_kv = g->h_kv, prm.g.n_q_groups = g->n_q_groups, prm.g.page = g->page, prm.g.rank = g->rank;
     prm.g.group = g->group, prm.g.n_coef_heads = g->n_coef_heads, prm.g.kbits = g->kbits, prm.g.vbits = g->vbits;
+    prm.g.layout = g->layout;
     prm.q = (const __half*)q, prm.pages = (const uint8_t*)pages, prm.coefs = (const __half*)coefs;
     prm.basis16 = (const __half*)basis_f16, prm.page_table = page_table, prm.table_stride = table_stride;
     prm.n_pages = n_pages, prm.batch = batch, prm.rope_cos = (const __half*)rope_cos, prm.rope_sin = (const __half*)rope_sin;
     prm.pos_offset = pos_offset, prm.lut_lo = v_lut[0], prm.lut_hi = v_lut[1], prm.lut_alpha = alpha, prm.lut_beta = beta;
     prm.scale_log2 = scale_log2, prm.part = part, prm.status = status;
+    if (g->layout == 1) {
+      prm.n_stages = 0;
+      const int rc5 = launch_decode_t5(prm, grid, s);
+      if (rc5) return rc5;
+    } else {
     const size_t stage = decode_stage_bytes(g), fixed = decode_fixed_smem(batch);
     int n_stages = (int)((220 * 1024 - fixed) / stage);
     if (n_stages > 8) n_stages = 8;
@@ -788,11 +765,13 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
     else if (g->rank == 32 && g->page == 64) rc = launch_decode<32, 64>(prm, grid, smem, s);
     else rc = launch_decode<16, 64>(prm, grid, smem, s);
     if (rc) return rc;
+    }
   }
   if (!(phases & 2)) return BMXK_OK;
   K2bMergeParams mp;
   mp.g.h_kv = g->h_kv, mp.g.n_q_groups = g->n_q_groups, mp.g.page = g->page, mp.g.rank = g->rank, mp.g.group = g->group;
-  mp.g.n_coef_heads = g->n_coef_heads, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits;
+  mp.g.n_coef_heads = g->n_coef_heads, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits, mp.g.layout = g->layout;
+  mp.n_sub = (g->layout == 1) ? 2 : 1;
   mp.q = (const __half*)q, mp.n_pages = n_pages, mp.batch = batch, mp.main_grid = grid, mp.part = part;
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;

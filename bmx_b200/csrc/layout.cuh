@@ -57,6 +57,7 @@ struct K2bGeom {
   int n_coef_heads;  // 1 (basis spans all heads) or h_kv (one basis per head)
   int kbits;         // K residual code width (<= 4, stored as nibbles)
   int vbits;         // V code width (2)
+  int layout;        // 0: fragment order (below); 1: row order for the tcgen05 decode kernel (page 128 only)
 };
 
 BMXK_HD int k2b_kres_bytes(int page) { return page * 64; }
@@ -94,6 +95,42 @@ BMXK_HD int k2b_coef_idx(int r, int i, int rank) {
   const int chunk = i >> 3, within = i & 7;
   const int sw = (rank == 32) ? ((r >> 1) & 3) : ((r >> 2) & 1);
   return r * rank + ((chunk ^ sw) << 3) + within;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Layout 1 ("row order", page = 128 only): the same four arrays and the same sizes, ordered for a
+// decode kernel in which one thread owns one token (keys) or one channel (values) and the
+// contractions run on tcgen05.mma.  Every per-thread read is a 16-byte chunk and the chunks of
+// consecutive threads are adjacent, so a warp's 128-bit shared-memory loads are conflict free.
+//
+// K residual: chunk k (0..3) of token r is the 16 bytes at ((k*128 + r)*16).  Its four words hold
+//   channels 16k..16k+7, 16k+8..16k+15, 64+16k..64+16k+7, 64+16k+8..64+16k+15; inside a word the
+//   low half carries the even channels and the high half the odd ones (nibble i = channel pair i),
+//   so one LOP3 yields a half2 of two adjacent channels.
+// K residual scale: half index grp*128 + c.
+// V code: chunk cc (0..1) of channel c is the 16 bytes at ((cc*128 + c)*16); word j of it holds
+//   tokens 64cc+16j .. +15: token tau < 8 at bit 4*tau, token tau >= 8 at bit 4*(tau-8)+2.
+// V norm: half index r.
+// Coefficients: the K-major, unswizzled operand form of tcgen05.mma: 8-row x 16-byte core
+//   matrices, half index ((r/8)*(rank/8) + i/8)*64 + (r%8)*8 + i%8.
+// ---------------------------------------------------------------------------------------------
+BMXK_HD void k2b_kres_loc(int lay, int r, int c, int& word, int& bit) {
+  if (lay == 0) return k2b_kres_loc(r, c, word, bit);
+  const int hi = c >> 6, cc = c & 63, k = cc >> 4, j = 2 * hi + ((cc & 15) >> 3);
+  word = (k * 128 + r) * 4 + j;
+  bit = 16 * (c & 1) + 4 * ((c & 7) >> 1);
+}
+BMXK_HD int k2b_kscale_idx(int lay, int grp, int c) { return lay == 0 ? k2b_kscale_idx(grp, c) : grp * 128 + c; }
+BMXK_HD void k2b_vcode_loc(int lay, int r, int c, int& word, int& bit) {
+  if (lay == 0) return k2b_vcode_loc(r, c, word, bit);
+  const int tau = r & 15;
+  word = ((r >> 6) * 128 + c) * 4 + ((r & 63) >> 4);
+  bit = tau < 8 ? 4 * tau : 4 * (tau - 8) + 2;
+}
+BMXK_HD int k2b_coef_idx(int lay, int r, int i, int rank) {
+  if (lay == 0) return k2b_coef_idx(r, i, rank);
+  return ((r >> 3) * (rank >> 3) + (i >> 3)) * 64 + (r & 7) * 8 + (i & 7);
 }
 
 }  // namespace bmxk

@@ -517,7 +517,8 @@ int bmxk_rtn_decode(const bmxk_rtn_geom* g, const void* q, const void* pages, co
   }
   K2bMergeParams mp;
   mp.g.h_kv = g->h_kv, mp.g.n_q_groups = g->n_q_groups, mp.g.page = g->page, mp.g.rank = 0, mp.g.group = g->k_group;
-  mp.g.n_coef_heads = 0, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits;
+  mp.g.n_coef_heads = 0, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits, mp.g.layout = 0;
+  mp.n_sub = 1;
   mp.q = (const __half*)q, mp.n_pages = n_pages, mp.batch = batch, mp.main_grid = grid, mp.part = part;
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = nullptr, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;

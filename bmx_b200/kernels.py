@@ -57,9 +57,16 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise RuntimeError("bmxk kernels take CUDA tensors; there is no CPU path")
 
 
+DEFAULT_K2B_LAYOUT = int(__import__('os').environ.get('BMXK_K2B_LAYOUT', '0'))
+
+
 def k2b_geom(h_kv: int, n_q_groups: int, page: int = 128, rank: int = 16, group: int = 64,
-             n_coef_heads: int = 1, kbits: int = 3, vbits: int = 2) -> K2bGeom:
-    return K2bGeom(h_kv, n_q_groups, page, rank, group, n_coef_heads, kbits, vbits)
+             n_coef_heads: int = 1, kbits: int = 3, vbits: int = 2, layout: int | None = None) -> K2bGeom:
+    """`layout` picks the byte order inside a page block and with it the decode kernel: 1 (row order, tcgen05
+    kernel) needs page 128; 0 (fragment order, mma.sync kernel) takes page 64 or 128.  None picks 1 where it fits."""
+    if layout is None:
+        layout = DEFAULT_K2B_LAYOUT if page == 128 else 0
+    return K2bGeom(h_kv, n_q_groups, page, rank, group, n_coef_heads, kbits, vbits, layout)
 
 
 def page_block_bytes(g: K2bGeom) -> int:

@@ -38,6 +38,9 @@ typedef struct bmxk_k2b_geom {
   int32_t n_coef_heads; /* 1: one basis over all heads (bmx default); h_kv: one basis per head */
   int32_t kbits;        /* key-residual bits, 2..4 (stored as two's-complement nibbles) */
   int32_t vbits;        /* value code bits: 2 */
+  int32_t layout;       /* byte order inside a page block (the exported tensors do not depend on it):
+                           0 = per-lane fragment order, read by the mma.sync decode kernel (page 64 or 128);
+                           1 = row order, read by the tcgen05 decode kernel (page 128 only) */
 } bmxk_k2b_geom;
 
 int bmxk_version(void);
