@@ -22,6 +22,14 @@
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
+#ifdef T5_PROF  // diagnostic builds: cycle counts of one thread per role of block 0 into status[16..]
+#define PROF_T(v) const long long v = clock64()
+#define PROF_ADD(slot, a, b) if (blockIdx.x == 0 && lane == 0 && wq == 0 && q == 0) atomicAdd(&p.status[slot], (int)((b) - (a)))
+#else
+#define PROF_T(v)
+#define PROF_ADD(slot, a, b)
+#endif
+
 namespace bmxk {
 
 namespace {
@@ -58,6 +66,11 @@ struct Walker {
   }
 };
 
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void named_bar(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
 }  // namespace
@@ -126,6 +139,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   Walker w;
   w.init(cum, npg_sm, f_begin, g.h_kv);
 
+  // Registers move from the value warps and the four service warps to the key warps, whose double-buffered
+  // TMEM loads need them: each group of four warps resizes itself first thing in its branch.
+  if (warp >= 16) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");  // the four service warps, as one group
   if (warp == 16) {
     // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
     if (lane == 0) {
@@ -147,7 +164,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   } else if (warp >= 18) {
     // ===================== query rotation warps: tiles of parity rw =====================
     // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
-    // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
+    // position 16*hc + e (hc = 0..7) holds channel 8*hc + e (e < 8) or 64 + 8*hc + (e - 8).  The warp that meets the
     // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
     const int rw = warp - 18;
     int s = 0;
@@ -178,7 +195,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
           const int c = lane + 32 * jj;
-          const int k1 = 32 * (c >> 4) + (c & 15), k2 = k1 + 16;
+          const int k1 = 32 * (c >> 4) + 16 * ((c >> 3) & 1) + (c & 7), k2 = k1 + 8;
 #pragma unroll
           for (int qi = 0; qi < 8; ++qi)
             if (qi < G) {
@@ -216,21 +233,24 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (++s == T5_STAGES) s = 0, ph ^= 1;
     }
   } else if (warp == 17) {
-    // ===================== issuing thread =====================
+    // ===================== issuing warp =====================
     // Per pipeline q the n-th tile goes through  A: U1 -> low[q];  B: U2 -> sdone[q];  C: U3 -> odone[q] and
-    // the stage is handed back.  A(n) needs the tile's copy and U2(n-1) done (it rewrites the same TMEM
-    // columns) and every earlier tile's copy landed; B(n) needs the rotated keys; C(n) needs the weights and the value levels.  The thread polls
-    // the two pipelines in turn and issues whatever has become ready.
-    if (lane == 0) {
+    // the stage is handed back.  A(n) needs U2(n-1) done (it rewrites the same TMEM columns) and every
+    // earlier tile's copy landed; B(n) needs the rotated keys; C(n) needs the weights and the value levels.
+    // The whole warp walks this state machine in lockstep (so that operand descriptors stay in uniform
+    // registers and the instruction stream stays short); one elected lane issues.
+    {
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f32(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
-      struct Info { int s, bb, first; };
-      Info info[2][4];
+      const bool el = elect_one();
       Walker wa[2];
       int nA[2] = {0, 0}, nB[2] = {0, 0}, nC[2] = {0, 0}, nT[2], segp[2] = {-1, -1};
+      uint32_t firstbits[2] = {0u, 0u};
       wa[0] = w;
       wa[1] = w;
       if (n_tiles > 1) wa[1].advance(npg_sm, g.h_kv, p.batch);
       nT[0] = (n_tiles + 1) >> 1, nT[1] = n_tiles >> 1;
+      const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
+      const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       long long t_last = clock64();
       bool ok = true;
       int obs_it = 0;
@@ -238,24 +258,25 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         bool progressed = false;
         // Tiles whose copy and rotated queries have landed, observed in order: a tile's U1 also reads the
         // basis operand, which travels with the FIRST tile of its range, possibly a tile of the other pipeline.
-        while (obs_it < n_tiles && mbar_try_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
+        while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const uint32_t tq = tmem + TM_PIPE * q;
           // ---- A ----
           if (nA[q] < nT[q] && nA[q] == nB[q]) {
-            const int n = nA[q], it = 2 * n + q, s = it % T5_STAGES;
-            if (obs_it > it && (n == 0 || mbar_try_wait(&sh->sdone[q], (uint32_t)(n - 1) & 1u))) {
+            const int n = nA[q], it = 2 * n + q;
+            if (obs_it > it && (n == 0 || mbar_test_wait(&sh->sdone[q], (uint32_t)(n - 1) & 1u))) {
               tc5::fence_after();
-              Info& in = info[q][n & 3];
-              in.s = s, in.bb = wa[q].seg & 1, in.first = (wa[q].seg != segp[q]);
+              const int s = it % T5_STAGES;
+              if (wa[q].seg != segp[q]) firstbits[q] |= 1u << (n & 31); else firstbits[q] &= ~(1u << (n & 31));
               segp[q] = wa[q].seg;
-              const uint32_t a0 = smem_u32(stage0 + (size_t)s * STAGE_BYTES), b0 = smem_u32(bbuf0 + (size_t)in.bb * COEF_BYTES);
+              const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((wa[q].seg & 1) * (COEF_BYTES >> 4));
+              if (el) {
 #pragma unroll
-              for (int ks = 0; ks < KS; ++ks)
-                tc5::mma_ss(tq + TM_KD, tc5::smem_desc(a0 + 256 * ks, 128, AB_SBO), tc5::smem_desc(b0 + 256 * ks, 128, AB_SBO), ID_U1,
-                            ks > 0);
-              tc5::commit(smem_u32(&sh->low[q]));
+                for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tq + TM_KD, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+                tc5::commit(smem_u32(&sh->low[q]));
+              }
+              __syncwarp();
               if (it + 2 < n_tiles) {
                 wa[q].advance(npg_sm, g.h_kv, p.batch);
                 wa[q].advance(npg_sm, g.h_kv, p.batch);
@@ -265,42 +286,51 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             }
           }
           // ---- B ----
-          if (nB[q] < nA[q] && mbar_try_wait(&sh->krot[q], (uint32_t)nB[q] & 1u)) {
+          if (nB[q] < nA[q] && mbar_test_wait(&sh->krot[q], (uint32_t)nB[q] & 1u)) {
             tc5::fence_after();
-            const uint32_t b0 = smem_u32(qb0 + (size_t)info[q][nB[q] & 3].s * T5_QB_BYTES);
+            const int s = (2 * nB[q] + q) % T5_STAGES;
+            const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
+            if (el) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              tc5::mma_ts(tq + TM_S, tq + TM_KD + 8 * ks, tc5::smem_desc(b0 + 256 * ks, 128, 2048), ID_N16, ks > 0);
-            tc5::commit(smem_u32(&sh->sdone[q]));
+              for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tq + TM_S, tq + TM_KD + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
+              tc5::commit(smem_u32(&sh->sdone[q]));
+            }
+            __syncwarp();
             ++nB[q];
             progressed = true;
           }
           // ---- C ----
-          if (nC[q] < nB[q] && mbar_try_wait(&sh->pready[q], (uint32_t)nC[q] & 1u) &&
-              mbar_try_wait(&sh->vready[q], (uint32_t)nC[q] & 1u)) {
+          if (nC[q] < nB[q] && mbar_test_wait(&sh->pready[q], (uint32_t)nC[q] & 1u) &&
+              mbar_test_wait(&sh->vready[q], (uint32_t)nC[q] & 1u)) {
             tc5::fence_after();
-            const Info in = info[q][nC[q] & 3];
-            const uint32_t b0 = smem_u32(pbuf0 + (size_t)q * T5_QB_BYTES);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              tc5::mma_ts(tq + TM_O, tq + TM_V + 8 * ks, tc5::smem_desc(b0 + 256 * ks, 128, 2048), ID_N16, (ks > 0) || !in.first);
-            tc5::commit(smem_u32(&sh->odone[q]));
-            mbar_arrive(&sh->empty[in.s]);
+            const int s = (2 * nC[q] + q) % T5_STAGES;
+            const uint32_t keep = ((firstbits[q] >> (nC[q] & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
+            const uint64_t db = d_pb + (uint64_t)(q * (T5_QB_BYTES >> 4));
             ++nC[q];
-            sh->released[q] = nC[q];
+            if (el) {
+              tc5::mma_ts(tq + TM_O, tq + TM_V, db, ID_N16, keep);
+#pragma unroll
+              for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tq + TM_O, tq + TM_V + 8 * ks, db + 16 * ks, ID_N16, 1u);
+              tc5::commit(smem_u32(&sh->odone[q]));
+              mbar_arrive(&sh->empty[s]);
+              sh->released[q] = nC[q];
+            }
+            __syncwarp();
             progressed = true;
           }
         }
         if (progressed) {
           t_last = clock64();
         } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-          if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
+          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
           ok = false;
         }
       }
     }
+  }
   } else if (warp < 8) {
     // ===================== key warps: thread = token row of the tile =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 128;");
     const int q = warp >> 2, wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tq = tmem + TM_PIPE * q + ((uint32_t)(32 * wq) << 16);
     const int grp = row / g.group;
@@ -359,22 +389,40 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       const int s = w.it % T5_STAGES;
       const uint32_t fp = (uint32_t)(w.it / T5_STAGES) & 1u, par = (uint32_t)n & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+      PROF_T(c_0);
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 2)) alive = false;
+      PROF_T(c_1);
       if (alive && !wait_or_flag(&sh->low[q], par, p.status, 6)) alive = false;
+      PROF_T(c_2);
+      PROF_ADD(16, c_0, c_1);
+      PROF_ADD(17, c_1, c_2);
       if (alive) {
         tc5::fence_after();
         const uint4* kres4 = reinterpret_cast<const uint4*>(blk);
         const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
+        // Four chunks of 16 + 16 channels; the TMEM loads of the next chunk are in flight while this one is
+        // computed (a wait covers every load issued so far, so the depth is one chunk).  Half-chunk
+        // hc = 2k + wd covers channels 8hc..8hc+7 and 64+8hc..64+8hc+7 and rewrites the eight columns its low
+        // channels came from.
+        uint32_t dl[2][16], dh[2][16];
+        tc5::ld16(tq + TM_KD, dl[0]);
+        tc5::ld16(tq + TM_KD + 64, dh[0]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          uint32_t dl[16], dh[16], out[16];
-          tc5::ld16(tq + TM_KD + 16 * k, dl);
-          tc5::ld16(tq + TM_KD + 64 + 16 * k, dh);
+          const int cb = k & 1;
           const uint4 cw = kres4[k * 128 + row];
           const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
           const uint4 cc[2] = {cst[(2 * k) * 128 + row], cst[(2 * k + 1) * 128 + row]};
           const uint4 ss[2] = {cst[(8 + 2 * k) * 128 + row], cst[(9 + 2 * k) * 128 + row]};
+          PROF_T(w_0);
           tc5::wait_ld();
+          PROF_T(w_1);
+          PROF_ADD(27, w_0, w_1);
+          if (k < 3) {
+            tc5::ld16(tq + TM_KD + 16 * (k + 1), dl[cb ^ 1]);
+            tc5::ld16(tq + TM_KD + 64 + 16 * (k + 1), dh[cb ^ 1]);
+          }
+          uint32_t out[16];
 #pragma unroll
           for (int wd = 0; wd < 2; ++wd) {
             const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
@@ -394,17 +442,24 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const __half2 low_lo = __floats2half2_rn(__uint_as_float(dl[8 * wd + 2 * i]), __uint_as_float(dl[8 * wd + 2 * i + 1]));
-              const __half2 low_hi = __floats2half2_rn(__uint_as_float(dh[8 * wd + 2 * i]), __uint_as_float(dh[8 * wd + 2 * i + 1]));
+              const __half2 low_lo = __floats2half2_rn(__uint_as_float(dl[cb][8 * wd + 2 * i]), __uint_as_float(dl[cb][8 * wd + 2 * i + 1]));
+              const __half2 low_hi = __floats2half2_rn(__uint_as_float(dh[cb][8 * wd + 2 * i]), __uint_as_float(dh[cb][8 * wd + 2 * i + 1]));
               const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), low_lo), khi = __hfma2(rh[i], u32_as_h2(sh_[i]), low_hi);
               const __half2 c = u32_as_h2(cs_[i]), sn = u32_as_h2(sn_[i]);
-              out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
-              out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+              out[8 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+              out[8 * wd + 4 + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
             }
           }
+          PROF_T(w_2);
           tc5::st16(tq + TM_KD + 16 * k, out);
+          PROF_T(w_3);
+          PROF_ADD(28, w_1, w_2);
+          PROF_ADD(29, w_2, w_3);
         }
+        PROF_T(w_4);
         tc5::wait_st();
+        PROF_T(w_5);
+        PROF_ADD(30, w_4, w_5);
         tc5::fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->krot[q]);
@@ -413,7 +468,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       float sv[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
+      PROF_T(c_3);
+      PROF_ADD(18, c_2, c_3);
       if (alive && !wait_or_flag(&sh->sdone[q], par, p.status, 7)) alive = false;
+      PROF_T(c_4);
+      PROF_ADD(19, c_3, c_4);
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
@@ -429,7 +488,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
         if (lane == 0) sh->wmax[q][wq][qi] = v;
       }
+      PROF_T(c_5);
       named_bar(1 + q, 128);
+      PROF_T(c_6);
+      PROF_ADD(20, c_4, c_5);
+      PROF_ADD(21, c_5, c_6);
       bool resc = false;
       float mnew[GQ];
 #pragma unroll
@@ -438,7 +501,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         mnew[qi] = m[qi];
         if (qi < G && tm > m[qi] + 8.f) mnew[qi] = tm, resc = true;  // lazy: weights stay below 2^8
       }
+      PROF_T(c_7);
       if (alive && n > 0 && !wait_or_flag(&sh->odone[q], (uint32_t)(n - 1) & 1u, p.status, 8)) alive = false;
+      PROF_T(c_8);
+      PROF_ADD(22, c_7, c_8);
       if (alive) {
         if (resc) {
           float f[GQ];
@@ -473,11 +539,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->pready[q]);
       }
+      PROF_T(c_9);
+      PROF_ADD(23, c_8, c_9);
       had = true, ++n;
     }
     flush(cur_b, cur_h);
   } else {
     // ===================== value warps: thread = channel =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     const int q = (warp - 8) >> 2, wq = warp & 3, ch = 32 * wq + lane;
     const uint32_t tq = tmem + TM_PIPE * q + ((uint32_t)(32 * wq) << 16);
     int n = 0;
@@ -485,9 +554,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if ((w.it & 1) != q) continue;
       const int s = w.it % T5_STAGES;
       const uint32_t fp = (uint32_t)(w.it / T5_STAGES) & 1u;
+      PROF_T(v_0);
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
+      PROF_T(v_1);
       // the columns still feed U3 of this pipeline's previous tile
       if (n > 0 && !wait_or_flag(&sh->odone[q], (uint32_t)(n - 1) & 1u, p.status, 11)) break;
+      PROF_T(v_2);
+      PROF_ADD(24, v_0, v_1);
+      PROF_ADD(25, v_1, v_2);
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
 #pragma unroll
@@ -517,6 +591,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->vready[q]);
+      PROF_T(v_3);
+      PROF_ADD(26, v_2, v_3);
       ++n;
     }
   }
