@@ -1,30 +1,31 @@
 // k2b split-KV decode on the sm_100a tensor-core path (tcgen05.mma + tensor memory) for pools in
 // layout 1 (row order, page = 128 tokens = one tile).
 //
-// One persistent CTA per SM walks an equal share of the flat tile list, as the mma.sync kernel does,
-// but the three contractions of a tile run as tcgen05.mma instructions issued by ONE thread, with their
-// accumulators and two of their A operands in tensor memory, and the per-element work is spread over
-// sixteen warps in which a thread owns one token (keys) or one channel (values):
+// One persistent CTA per SM walks an equal share of the flat tile list, as the mma.sync kernel does.
+// The three contractions of a tile run as tcgen05.mma instructions issued by one warp, with their
+// accumulators and two of their A operands in tensor memory; the per-element work is spread over 24
+// warps in which a thread owns one token (keys, softmax) or one channel (values):
 //
-//   U1  K_low[128 tok x 128 ch]   = coef[128 x rank] (smem, straight from the bulk copy) x basis^T (smem)
-//   key warps (thread = token):     K = K_low + scale * residual   (nibble -> half2 by LOP3 + exact fix-up)
-//                                   rotate by the token's offset inside the tile, write fp16 K back into
-//                                   the same TMEM columns as the A operand of U2
+//   U1  K_low[128 tok x 128 ch]   = coef[128 x rank] (smem, straight from the bulk copy) x basis^T (smem),
+//                                   fp16 accumulators
+//   key warps (16; warp = 32 tokens x one chunk of 16 + 16 channels):
+//                                   K = K_low + scale * residual   (nibble -> half2 by LOP3 + exact fix-up),
+//                                   rotated by the token's offset inside the tile (its cos/sin stay in
+//                                   registers), written back into the same TMEM columns as the A operand of U2
 //   U2  S[128 tok x 16]            = K_rot (TMEM) x q_rot^T (smem; the tile's base rotation is applied to q)
-//   key warps:                      online softmax in base 2 with a lazy rescale; p * norm -> smem (B of U3)
-//   value warps (thread = channel): 2-bit codes -> fp16 levels by byte-permute lookups -> TMEM (A of U3)
-//   U3  O^T[128 ch x 16]          += V_lev^T (TMEM) x P (smem)
+//   softmax warps (4):              online softmax in base 2 with a lazy rescale; p * norm -> smem (B of U3)
+//   value warps (4; thread = channel): 2-bit codes -> fp16 levels by byte-permute lookups -> TMEM (A of U3)
+//   U3  O^T[128 ch x 16]          += V_lev^T (TMEM) x P (smem), fp32
 //
-// Two such pipelines (even and odd tiles) run side by side in one CTA, each with its own key
-// warpgroup, value warpgroup, TMEM columns and (max, sum, accumulator) state; they share the copy warp,
-// the issuing thread and the two warps that rotate q.  Each pipeline writes its own partial record per
-// (sequence, head) range; the merge kernel combines them.
+// The K, S, V and P buffers are double-buffered by tile parity, so the key warps start tile n+1 while U2
+// and the softmax of tile n are still under way.  Service warps: one thread issues the bulk copies, one
+// warp issues the tcgen05.mma, two warps rotate q (and lay out the basis operand when the head changes).
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
 #ifdef T5_PROF  // diagnostic builds: cycle counts of one thread per role of block 0 into status[16..]
 #define PROF_T(v) const long long v = clock64()
-#define PROF_ADD(slot, a, b) if (blockIdx.x == 0 && lane == 0 && wq == 0 && q == 0) atomicAdd(&p.status[slot], (int)((b) - (a)))
+#define PROF_ADD(slot, a, b) if (blockIdx.x == 0 && lane == 0 && wq == 0) atomicAdd(&p.status[slot], (int)((b) - (a)))
 #else
 #define PROF_T(v)
 #define PROF_ADD(slot, a, b)
@@ -34,20 +35,19 @@ namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 640;   // warps 0-3 / 4-7 key, 8-11 / 12-15 value, 16 copy, 17 issue, 18-19 query rotation
-constexpr int T5_STAGES = 6;
+constexpr int T5_THREADS = 896;   // warps 0-15 key, 16-19 softmax, 20-23 value, 24 copy, 25 issue, 26-27 query rotation
+constexpr int T5_STAGES = 7;
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
-constexpr int T5_CS_BYTES = 16 * 128 * 16;
-// TMEM columns of pipeline p start at 224*p
-constexpr uint32_t TM_KD = 0, TM_V = 128, TM_S = 192, TM_O = 208, TM_PIPE = 224, TM_COLS = 512;
+// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output at 416
+constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
   uint64_t full[T5_STAGES], empty[T5_STAGES];
   uint64_t low[2], krot[2], sdone[2], pready[2], vready[2], odone[2];
   uint32_t tmem_base;
-  volatile int released[2];   // tiles of pipeline p whose stage has been handed back
-  float wmax[2][4][8];
-  float red[2][4][16];
+  volatile int released;   // tiles whose stage has been handed back
+  float wmax[4][8];
+  float red[4][16];
 };
 
 // Walks the CTA's tile range; `seg` counts the (sequence, head) ranges met so far.
@@ -87,11 +87,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   const int STAGE_BYTES = COEF_BYTES + PB;
 
   uint8_t* stage0 = smem;
-  uint8_t* qb0 = stage0 + T5_STAGES * STAGE_BYTES;       // [stage][4096]
+  uint8_t* qb0 = stage0 + T5_STAGES * STAGE_BYTES;       // [stage][4096] rotated queries
   uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [2][COEF_BYTES] basis operand per range parity
-  uint8_t* pbuf0 = bbuf0 + 2 * COEF_BYTES;               // [2][4096] softmax weights per pipeline
-  uint4* cst = reinterpret_cast<uint4*>(pbuf0 + 2 * T5_QB_BYTES);  // [16 chunks][128 offsets] cos | sin
-  T5Smem* sh = reinterpret_cast<T5Smem*>(reinterpret_cast<uint8_t*>(cst) + T5_CS_BYTES);
+  uint8_t* pbuf0 = bbuf0 + 2 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
+  T5Smem* sh = reinterpret_cast<T5Smem*>(pbuf0 + 2 * T5_QB_BYTES);
   int* cum = reinterpret_cast<int*>(sh + 1);
   int* npg_sm = cum + p.batch + 1;
 
@@ -107,26 +106,21 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   const int n_tiles = f_end - f_begin;
   if (n_tiles <= 0) return;
 
-  // ---- prologue: tables, zeroed operand rows, barriers, tensor memory ----
-  for (int i = tid; i < 16 * 128; i += T5_THREADS) {
-    const int ck = i >> 7, dlt = i & 127;
-    const __half* src = (ck < 8 ? p.rope_cos : p.rope_sin) + (int64_t)dlt * HEAD_DIM + 8 * (ck & 7);
-    cst[i] = *reinterpret_cast<const uint4*>(src);
-  }
+  // ---- prologue: zeroed operand rows, barriers, tensor memory ----
   for (int i = tid; i < (T5_STAGES + 2) * T5_QB_BYTES / 16; i += T5_THREADS) {
     uint8_t* base = (i < T5_STAGES * T5_QB_BYTES / 16) ? qb0 + (size_t)i * 16 : pbuf0 + ((size_t)i - T5_STAGES * T5_QB_BYTES / 16) * 16;
     *reinterpret_cast<uint4*>(base) = make_uint4(0u, 0u, 0u, 0u);
   }
   if (tid == 0) {
     for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1);
-    for (int q = 0; q < 2; ++q) {
-      mbar_init(&sh->low[q], 1), mbar_init(&sh->krot[q], 4), mbar_init(&sh->sdone[q], 1);
-      mbar_init(&sh->pready[q], 4), mbar_init(&sh->vready[q], 4), mbar_init(&sh->odone[q], 1);
-      sh->released[q] = 0;
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->low[b], 1), mbar_init(&sh->krot[b], 16), mbar_init(&sh->sdone[b], 1);
+      mbar_init(&sh->pready[b], 4), mbar_init(&sh->vready[b], 4), mbar_init(&sh->odone[b], 1);
     }
+    sh->released = 0;
     fence_barrier_init();
   }
-  if (warp == 17) {
+  if (warp == 25) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -139,185 +133,166 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   Walker w;
   w.init(cum, npg_sm, f_begin, g.h_kv);
 
-  // Registers move from the value warps and the four service warps to the key warps, whose double-buffered
-  // TMEM loads need them: each group of four warps resizes itself first thing in its branch.
-  if (warp >= 16) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");  // the four service warps, as one group
-  if (warp == 16) {
-    // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
-    if (lane == 0) {
+  // Registers move from the softmax, value and service warps to the key warps: each group of four warps
+  // resizes itself first thing in its branch.
+  if (warp >= 24) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // the four service warps, as one group
+    if (warp == 24) {
+      // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
+      if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 1;  // a fresh barrier passes parity 1
+        for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
+          if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
+          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
+          uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+          const int chd = (g.n_coef_heads == 1) ? 0 : h;
+          const int slot = p.page_table[(int64_t)b * p.table_stride + j];
+          mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
+          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+                   &sh->full[s]);
+          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
+          if (++s == T5_STAGES) s = 0, ph ^= 1;
+        }
+      }
+    } else if (warp >= 26) {
+      // ===================== query rotation warps: tiles of parity rw =====================
+      // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
+      // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
+      // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
+      const int rw = warp - 26;
       int s = 0;
-      uint32_t ph = 1;  // a fresh barrier passes parity 1
-      for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-        if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
-        const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
-        uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
-        const int chd = (g.n_coef_heads == 1) ? 0 : h;
-        const int slot = p.page_table[(int64_t)b * p.table_stride + j];
-        mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
-        bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
-                 &sh->full[s]);
-        bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
+      uint32_t ph = 1;
+      int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
+      bool alive = true;
+      for (; w.it < n_tiles && alive; w.advance(npg_sm, g.h_kv, p.batch)) {
+        const bool new_seg = (w.seg != prev_seg);
+        if (new_seg) first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
+        if ((w.it & 1) == rw) {
+          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
+          const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
+          const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
+          float cs[2], sn[2], x1[2][GQ], x2[2][GQ];
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int c = lane + 32 * jj;  // rotary pair (c, c + 64)
+            cs[jj] = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
+            sn[jj] = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
+#pragma unroll
+            for (int qi = 0; qi < GQ; ++qi) {
+              x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
+              x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
+            }
+          }
+          if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
+          __half* qr = reinterpret_cast<__half*>(qb0 + (size_t)s * T5_QB_BYTES);
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int c = lane + 32 * jj;
+            const int k1 = 32 * (c >> 4) + (c & 15), k2 = k1 + 16;
+#pragma unroll
+            for (int qi = 0; qi < GQ; ++qi)
+              if (qi < G) {
+                const float a = x1[jj][qi] * p.scale_log2, bb = x2[jj][qi] * p.scale_log2;
+                qr[(k1 >> 3) * 64 + qi * 8 + (k1 & 7)] = __float2half_rn(a * cs[jj] + bb * sn[jj]);
+                qr[(k2 >> 3) * 64 + qi * 8 + (k2 & 7)] = __float2half_rn(bb * cs[jj] - a * sn[jj]);
+              }
+          }
+          if (new_seg) {
+            if (w.seg >= 2) {
+              // the buffer still serves the range before the previous one until all its tiles are handed back
+              const long long c0 = clock64();
+              while (sh->released < first_prev) {
+                if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+                  if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
+                  alive = false;
+                  break;
+                }
+              }
+              if (!alive) break;
+            }
+            uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg & 1) * COEF_BYTES);
+            const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
+            for (int o = lane; o < 128 * (RANK / 8); o += 32) {
+              const int c = o / (RANK / 8), i8 = o % (RANK / 8);
+              bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->full[s]);
+        }
         if (++s == T5_STAGES) s = 0, ph ^= 1;
       }
-    }
-  } else if (warp >= 18) {
-    // ===================== query rotation warps: tiles of parity rw =====================
-    // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
-    // position 16*hc + e (hc = 0..7) holds channel 8*hc + e (e < 8) or 64 + 8*hc + (e - 8).  The warp that meets the
-    // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
-    const int rw = warp - 18;
-    int s = 0;
-    uint32_t ph = 1;
-    int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
-    bool alive = true;
-    for (; w.it < n_tiles && alive; w.advance(npg_sm, g.h_kv, p.batch)) {
-      const bool new_seg = (w.seg != prev_seg);
-      if (new_seg) first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
-      if ((w.it & 1) == rw) {
-        const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
-        const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
-        const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
-        float cs[2], sn[2], x1[2][8], x2[2][8];
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int c = lane + 32 * jj;  // rotary pair (c, c + 64)
-          cs[jj] = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
-          sn[jj] = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
-#pragma unroll
-          for (int qi = 0; qi < 8; ++qi) {
-            x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
-            x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
-          }
-        }
-        if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
-        __half* qr = reinterpret_cast<__half*>(qb0 + (size_t)s * T5_QB_BYTES);
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int c = lane + 32 * jj;
-          const int k1 = 32 * (c >> 4) + 16 * ((c >> 3) & 1) + (c & 7), k2 = k1 + 8;
-#pragma unroll
-          for (int qi = 0; qi < 8; ++qi)
-            if (qi < G) {
-              const float a = x1[jj][qi] * p.scale_log2, bb = x2[jj][qi] * p.scale_log2;
-              qr[(k1 >> 3) * 64 + qi * 8 + (k1 & 7)] = __float2half_rn(a * cs[jj] + bb * sn[jj]);
-              qr[(k2 >> 3) * 64 + qi * 8 + (k2 & 7)] = __float2half_rn(bb * cs[jj] - a * sn[jj]);
-            }
-        }
-        if (new_seg) {
-          if (w.seg >= 2) {
-            // the buffer still serves the range before the previous one until all its tiles are handed back
-            const int last2 = first_prev - 1;
-            const int need0 = (last2 + 2) >> 1, need1 = (last2 + 1) >> 1;
-            const long long c0 = clock64();
-            while (sh->released[0] < need0 || sh->released[1] < need1) {
-              if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-                if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
-                alive = false;
-                break;
-              }
-            }
-            if (!alive) break;
-          }
-          uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg & 1) * COEF_BYTES);
-          const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
-          for (int o = lane; o < 128 * (RANK / 8); o += 32) {
-            const int c = o / (RANK / 8), i8 = o % (RANK / 8);
-            bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
-          }
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->full[s]);
-      }
-      if (++s == T5_STAGES) s = 0, ph ^= 1;
-    }
-  } else if (warp == 17) {
-    // ===================== issuing warp =====================
-    // Per pipeline q the n-th tile goes through  A: U1 -> low[q];  B: U2 -> sdone[q];  C: U3 -> odone[q] and
-    // the stage is handed back.  A(n) needs U2(n-1) done (it rewrites the same TMEM columns) and every
-    // earlier tile's copy landed; B(n) needs the rotated keys; C(n) needs the weights and the value levels.
-    // The whole warp walks this state machine in lockstep (so that operand descriptors stay in uniform
-    // registers and the instruction stream stays short); one elected lane issues.
-    {
-      constexpr uint32_t ID_U1 = tc5::idesc_f16_f32(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
+    } else {
+      // ===================== issuing warp =====================
+      // Tile n (buffer b = n & 1) goes through  A: U1 -> low[b];  B: U2 -> sdone[b];  C: U3 -> odone[b], after
+      // which its stage is handed back.  A(n) needs every copy up to tile n landed (the basis operand travels
+      // with the first tile of its range) and U2(n-2) done (same TMEM columns); B(n) needs the rotated keys
+      // and the softmax of tile n-2 finished with the score columns; C(n) needs the weights and the value
+      // levels.  The whole warp walks this state machine in lockstep, so that operand descriptors stay in
+      // uniform registers and the instruction stream stays short; one elected lane issues.
+      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
-      Walker wa[2];
-      int nA[2] = {0, 0}, nB[2] = {0, 0}, nC[2] = {0, 0}, nT[2], segp[2] = {-1, -1};
-      uint32_t firstbits[2] = {0u, 0u};
-      wa[0] = w;
-      wa[1] = w;
-      if (n_tiles > 1) wa[1].advance(npg_sm, g.h_kv, p.batch);
-      nT[0] = (n_tiles + 1) >> 1, nT[1] = n_tiles >> 1;
+      int nA = 0, nB = 0, nC = 0, segp = -1, obs_it = 0;
+      uint32_t firstbits = 0u;
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
       const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       long long t_last = clock64();
       bool ok = true;
-      int obs_it = 0;
-      while (ok && (nC[0] < nT[0] || nC[1] < nT[1])) {
+      while (ok && nC < n_tiles) {
         bool progressed = false;
-        // Tiles whose copy and rotated queries have landed, observed in order: a tile's U1 also reads the
-        // basis operand, which travels with the FIRST tile of its range, possibly a tile of the other pipeline.
         while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
+        // ---- A ----
+        if (nA < n_tiles && nA < nB + 2 && obs_it > nA &&
+            (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
+          tc5::fence_after();
+          const int s = nA % T5_STAGES, b = nA & 1;
+          if (w.seg != segp) firstbits |= 1u << (nA & 31); else firstbits &= ~(1u << (nA & 31));
+          segp = w.seg;
+          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg & 1) * (COEF_BYTES >> 4));
+          if (el) {
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t tq = tmem + TM_PIPE * q;
-          // ---- A ----
-          if (nA[q] < nT[q] && nA[q] == nB[q]) {
-            const int n = nA[q], it = 2 * n + q;
-            if (obs_it > it && (n == 0 || mbar_test_wait(&sh->sdone[q], (uint32_t)(n - 1) & 1u))) {
-              tc5::fence_after();
-              const int s = it % T5_STAGES;
-              if (wa[q].seg != segp[q]) firstbits[q] |= 1u << (n & 31); else firstbits[q] &= ~(1u << (n & 31));
-              segp[q] = wa[q].seg;
-              const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((wa[q].seg & 1) * (COEF_BYTES >> 4));
-              if (el) {
-#pragma unroll
-                for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tq + TM_KD, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
-                tc5::commit(smem_u32(&sh->low[q]));
-              }
-              __syncwarp();
-              if (it + 2 < n_tiles) {
-                wa[q].advance(npg_sm, g.h_kv, p.batch);
-                wa[q].advance(npg_sm, g.h_kv, p.batch);
-              }
-              ++nA[q];
-              progressed = true;
-            }
+            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+            tc5::commit(smem_u32(&sh->low[b]));
           }
-          // ---- B ----
-          if (nB[q] < nA[q] && mbar_test_wait(&sh->krot[q], (uint32_t)nB[q] & 1u)) {
-            tc5::fence_after();
-            const int s = (2 * nB[q] + q) % T5_STAGES;
-            const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
-            if (el) {
+          __syncwarp();
+          w.advance(npg_sm, g.h_kv, p.batch);
+          ++nA;
+          progressed = true;
+        }
+        // ---- B ----
+        if (nB < nA && nB < nC + 2 && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u)) {
+          tc5::fence_after();
+          const int s = nB % T5_STAGES, b = nB & 1;
+          const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
+          if (el) {
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tq + TM_S, tq + TM_KD + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
-              tc5::commit(smem_u32(&sh->sdone[q]));
-            }
-            __syncwarp();
-            ++nB[q];
-            progressed = true;
+            for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
+            tc5::commit(smem_u32(&sh->sdone[b]));
           }
-          // ---- C ----
-          if (nC[q] < nB[q] && mbar_test_wait(&sh->pready[q], (uint32_t)nC[q] & 1u) &&
-              mbar_test_wait(&sh->vready[q], (uint32_t)nC[q] & 1u)) {
-            tc5::fence_after();
-            const int s = (2 * nC[q] + q) % T5_STAGES;
-            const uint32_t keep = ((firstbits[q] >> (nC[q] & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
-            const uint64_t db = d_pb + (uint64_t)(q * (T5_QB_BYTES >> 4));
-            ++nC[q];
-            if (el) {
-              tc5::mma_ts(tq + TM_O, tq + TM_V, db, ID_N16, keep);
+          __syncwarp();
+          ++nB;
+          progressed = true;
+        }
+        // ---- C ----
+        if (nC < nB && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
+            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
+          tc5::fence_after();
+          const int s = nC % T5_STAGES, b = nC & 1;
+          const uint32_t keep = ((firstbits >> (nC & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
+          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
+          ++nC;
+          if (el) {
+            tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b, db, ID_N16, keep);
 #pragma unroll
-              for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tq + TM_O, tq + TM_V + 8 * ks, db + 16 * ks, ID_N16, 1u);
-              tc5::commit(smem_u32(&sh->odone[q]));
-              mbar_arrive(&sh->empty[s]);
-              sh->released[q] = nC[q];
-            }
-            __syncwarp();
-            progressed = true;
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            tc5::commit(smem_u32(&sh->odone[b]));
+            mbar_arrive(&sh->empty[s]);
+            sh->released = nC;
           }
+          __syncwarp();
+          progressed = true;
         }
         if (progressed) {
           t_last = clock64();
@@ -327,32 +302,99 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         }
       }
     }
-  }
-  } else if (warp < 8) {
-    // ===================== key warps: thread = token row of the tile =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 128;");
-    const int q = warp >> 2, wq = warp & 3, row = 32 * wq + lane;
-    const uint32_t tq = tmem + TM_PIPE * q + ((uint32_t)(32 * wq) << 16);
+  } else if (warp < 16) {
+    // ===================== key warps: 32 token rows x one chunk of 16 + 16 channels =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 80;");
+    const int wq = warp & 3, k = warp >> 2, row = 32 * wq + lane;
+    const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
     const int grp = row / g.group;
     const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
     const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
     const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
+    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15
+    uint32_t cs_[8], sn_[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      cs_[i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * k + 2 * i);
+      sn_[i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * k + 2 * i);
+    }
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      const uint32_t par = (uint32_t)(n >> 1) & 1u;
+      const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+      PROF_T(c_0);
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
+      PROF_T(c_1);
+      if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
+      PROF_T(c_2);
+      tc5::fence_after();
+      uint32_t dl[8], dh[8], out[16];
+      tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
+      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k, dh);
+      const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
+      const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
+      const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
+      tc5::wait_ld();
+#pragma unroll
+      for (int wd = 0; wd < 2; ++wd) {
+        const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
+        const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
+        __half2 rl[4], rh[4];
+        {
+          const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
+          rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
+          rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+          rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
+          rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+          rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
+          rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+          rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
+          rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[4 * wd + i]));
+          const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[4 * wd + i]));
+          const __half2 c = u32_as_h2(cs_[4 * wd + i]), sn = u32_as_h2(sn_[4 * wd + i]);
+          out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+          out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+        }
+      }
+      tc5::st16(tk + 128 * b + 16 * k, out);
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->krot[b]);
+      PROF_T(c_3);
+      PROF_ADD(16, c_0, c_1);
+      PROF_ADD(17, c_1, c_2);
+      PROF_ADD(18, c_2, c_3);
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
+    }
+  } else if (warp < 20) {
+    // ===================== softmax warps: thread = token row; also owns the running (max, sum) =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int n = 0, cur_seg = -1, cur_b = 0, cur_h = 0;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, s = 0;
+    uint32_t fp = 0;
     bool had = false, alive = true;
-    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
 
-    auto flush = [&](int b_, int h_) {
+    // Writes the partial record of the range that just ended.  `last` is its last tile.
+    auto flush = [&](int b_, int h_, int last) {
       float acc[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (had && alive && !wait_or_flag(&sh->odone[q], (uint32_t)(n - 1) & 1u, p.status, 9)) alive = false;
-      if (had && alive) {
+      if (alive && !wait_or_flag(&sh->odone[last & 1], (uint32_t)(last >> 1) & 1u, p.status, 9)) alive = false;
+      if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tq + TM_O, r); else tc5::ld8(tq + TM_O, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
@@ -363,120 +405,43 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         float a = l[qi], b2 = pn[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[q][wq][qi] = a, sh->red[q][wq][GQ + qi] = b2;
+        if (lane == 0) sh->red[wq][qi] = a, sh->red[wq][GQ + qi] = b2;
       }
-      named_bar(1 + q, 128);
-      float* dst = p.part + ((q * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
+      named_bar(1, 128);
+      float* dst = p.part + (((int64_t)blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
-          const float L = sh->red[q][0][qi] + sh->red[q][1][qi] + sh->red[q][2][qi] + sh->red[q][3][qi];
-          const float P = sh->red[q][0][GQ + qi] + sh->red[q][1][GQ + qi] + sh->red[q][2][GQ + qi] + sh->red[q][3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
-          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
+          const float L = sh->red[0][qi] + sh->red[1][qi] + sh->red[2][qi] + sh->red[3][qi];
+          const float P = sh->red[0][GQ + qi] + sh->red[1][GQ + qi] + sh->red[2][GQ + qi] + sh->red[3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = p.lut_alpha * P + p.lut_beta * acc[qi];
+          if (row == 0) dst[qi * PART_STRIDE] = m[qi], dst[qi * PART_STRIDE + 1] = L;
         }
-      named_bar(1 + q, 128);
+      named_bar(1, 128);
     };
 
     for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
+      const int n = w.it, b = n & 1;
+      const uint32_t par = (uint32_t)(n >> 1) & 1u;
       if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h);
+        if (cur_seg >= 0) flush(cur_b, cur_h, n - 1);
         cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
       }
-      if ((w.it & 1) != q) continue;
-      const int s = w.it % T5_STAGES;
-      const uint32_t fp = (uint32_t)(w.it / T5_STAGES) & 1u, par = (uint32_t)n & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
-      PROF_T(c_0);
-      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 2)) alive = false;
-      PROF_T(c_1);
-      if (alive && !wait_or_flag(&sh->low[q], par, p.status, 6)) alive = false;
-      PROF_T(c_2);
-      PROF_ADD(16, c_0, c_1);
-      PROF_ADD(17, c_1, c_2);
-      if (alive) {
-        tc5::fence_after();
-        const uint4* kres4 = reinterpret_cast<const uint4*>(blk);
-        const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
-        // Four chunks of 16 + 16 channels; the TMEM loads of the next chunk are in flight while this one is
-        // computed (a wait covers every load issued so far, so the depth is one chunk).  Half-chunk
-        // hc = 2k + wd covers channels 8hc..8hc+7 and 64+8hc..64+8hc+7 and rewrites the eight columns its low
-        // channels came from.
-        uint32_t dl[2][16], dh[2][16];
-        tc5::ld16(tq + TM_KD, dl[0]);
-        tc5::ld16(tq + TM_KD + 64, dh[0]);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int cb = k & 1;
-          const uint4 cw = kres4[k * 128 + row];
-          const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
-          const uint4 cc[2] = {cst[(2 * k) * 128 + row], cst[(2 * k + 1) * 128 + row]};
-          const uint4 ss[2] = {cst[(8 + 2 * k) * 128 + row], cst[(9 + 2 * k) * 128 + row]};
-          PROF_T(w_0);
-          tc5::wait_ld();
-          PROF_T(w_1);
-          PROF_ADD(27, w_0, w_1);
-          if (k < 3) {
-            tc5::ld16(tq + TM_KD + 16 * (k + 1), dl[cb ^ 1]);
-            tc5::ld16(tq + TM_KD + 64 + 16 * (k + 1), dh[cb ^ 1]);
-          }
-          uint32_t out[16];
-#pragma unroll
-          for (int wd = 0; wd < 2; ++wd) {
-            const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
-            const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
-            const uint32_t cs_[4] = {cc[wd].x, cc[wd].y, cc[wd].z, cc[wd].w}, sn_[4] = {ss[wd].x, ss[wd].y, ss[wd].z, ss[wd].w};
-            __half2 rl[4], rh[4];
-            {
-              const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
-              rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
-              rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-              rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
-              rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-              rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
-              rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-              rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
-              rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const __half2 low_lo = __floats2half2_rn(__uint_as_float(dl[cb][8 * wd + 2 * i]), __uint_as_float(dl[cb][8 * wd + 2 * i + 1]));
-              const __half2 low_hi = __floats2half2_rn(__uint_as_float(dh[cb][8 * wd + 2 * i]), __uint_as_float(dh[cb][8 * wd + 2 * i + 1]));
-              const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), low_lo), khi = __hfma2(rh[i], u32_as_h2(sh_[i]), low_hi);
-              const __half2 c = u32_as_h2(cs_[i]), sn = u32_as_h2(sn_[i]);
-              out[8 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
-              out[8 * wd + 4 + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
-            }
-          }
-          PROF_T(w_2);
-          tc5::st16(tq + TM_KD + 16 * k, out);
-          PROF_T(w_3);
-          PROF_ADD(28, w_1, w_2);
-          PROF_ADD(29, w_2, w_3);
-        }
-        PROF_T(w_4);
-        tc5::wait_st();
-        PROF_T(w_5);
-        PROF_ADD(30, w_4, w_5);
-        tc5::fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->krot[q]);
-      }
-      // ---- scores of this token, the tile maximum, the softmax weights ----
       float sv[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
       PROF_T(c_3);
-      PROF_ADD(18, c_2, c_3);
-      if (alive && !wait_or_flag(&sh->sdone[q], par, p.status, 7)) alive = false;
+      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
+      if (alive && !wait_or_flag(&sh->sdone[b], par, p.status, 7)) alive = false;
       PROF_T(c_4);
       PROF_ADD(19, c_3, c_4);
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tq + TM_S, r); else tc5::ld8(tq + TM_S, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * b, r); else tc5::ld8(tl + TM_S + 16 * b, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
@@ -486,10 +451,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         float v = sv[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-        if (lane == 0) sh->wmax[q][wq][qi] = v;
+        if (lane == 0) sh->wmax[wq][qi] = v;
       }
       PROF_T(c_5);
-      named_bar(1 + q, 128);
+      named_bar(1, 128);
       PROF_T(c_6);
       PROF_ADD(20, c_4, c_5);
       PROF_ADD(21, c_5, c_6);
@@ -497,12 +462,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       float mnew[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) {
-        const float tm = fmaxf(fmaxf(sh->wmax[q][0][qi], sh->wmax[q][1][qi]), fmaxf(sh->wmax[q][2][qi], sh->wmax[q][3][qi]));
+        const float tm = fmaxf(fmaxf(sh->wmax[0][qi], sh->wmax[1][qi]), fmaxf(sh->wmax[2][qi], sh->wmax[3][qi]));
         mnew[qi] = m[qi];
         if (qi < G && tm > m[qi] + 8.f) mnew[qi] = tm, resc = true;  // lazy: weights stay below 2^8
       }
       PROF_T(c_7);
-      if (alive && n > 0 && !wait_or_flag(&sh->odone[q], (uint32_t)(n - 1) & 1u, p.status, 8)) alive = false;
+      // the weight buffer still feeds U3 of tile n-2; a rescale of the accumulator needs U3 of tile n-1 done
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      if (alive && resc && had && !wait_or_flag(&sh->odone[b ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 13)) alive = false;
       PROF_T(c_8);
       PROF_ADD(22, c_7, c_8);
       if (alive) {
@@ -516,16 +483,16 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
             tc5::fence_after();
             uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tq + TM_O, r); else tc5::ld8(tq + TM_O, r);
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
             tc5::wait_ld();
 #pragma unroll
             for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tq + TM_O, r); else tc5::st8(tq + TM_O, r);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
             tc5::wait_st();
           }
         }
         const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)q * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)b * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi)
           if (qi < G) {
@@ -537,28 +504,28 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         fence_proxy_async();
         tc5::fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->pready[q]);
+        if (lane == 0) mbar_arrive(&sh->pready[b]);
       }
       PROF_T(c_9);
       PROF_ADD(23, c_8, c_9);
-      had = true, ++n;
+      had = true;
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-    flush(cur_b, cur_h);
+    flush(cur_b, cur_h, n_tiles - 1);
   } else {
     // ===================== value warps: thread = channel =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-    const int q = (warp - 8) >> 2, wq = warp & 3, ch = 32 * wq + lane;
-    const uint32_t tq = tmem + TM_PIPE * q + ((uint32_t)(32 * wq) << 16);
-    int n = 0;
-    for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-      if ((w.it & 1) != q) continue;
-      const int s = w.it % T5_STAGES;
-      const uint32_t fp = (uint32_t)(w.it / T5_STAGES) & 1u;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    const int wq = warp & 3, ch = 32 * wq + lane;
+    const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
       PROF_T(v_0);
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
       PROF_T(v_1);
-      // the columns still feed U3 of this pipeline's previous tile
-      if (n > 0 && !wait_or_flag(&sh->odone[q], (uint32_t)(n - 1) & 1u, p.status, 11)) break;
+      // the columns still feed U3 of tile n-2
+      if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
       PROF_T(v_2);
       PROF_ADD(24, v_0, v_1);
       PROF_ADD(25, v_1, v_2);
@@ -584,23 +551,23 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               out[8 * jj + 4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), out[8 * jj + 4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);
             }
           }
-          tc5::st16(tq + TM_V + 32 * cc + 16 * jp, out);
+          tc5::st16(tv + 64 * b + 32 * cc + 16 * jp, out);
         }
       }
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->vready[q]);
+      if (lane == 0) mbar_arrive(&sh->vready[b]);
       PROF_T(v_3);
       PROF_ADD(26, v_2, v_3);
-      ++n;
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
 
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 17) {
+  if (warp == 25) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
@@ -608,7 +575,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
 static size_t t5_smem_bytes(int rank, int group, int batch) {
   const size_t coef = (size_t)128 * rank * 2;
-  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 2 * coef + T5_CS_BYTES +
+  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 2 * coef +
          sizeof(T5Smem) + (size_t)(2 * batch + 1) * 4 + 16;
 }
 

@@ -6,7 +6,7 @@
 //   * shared-memory operands are K-major, no swizzle: 8-row x 16-byte "core matrices"; the two core
 //     matrices that one K=16 fp16 instruction reads are LBO bytes apart, 8-row groups are SBO bytes apart
 //   * a tensor-memory A operand has one matrix row per TMEM lane and two fp16 K-elements per 32-bit column
-//   * accumulators are fp32, one matrix row per lane, one column per 32-bit TMEM column
+//   * accumulators (fp32, or fp16 in the low half) take one 32-bit TMEM column each, one matrix row per lane
 //   * a warp reaches lanes 32*(warp % 4) .. +31 only; addresses are (lane << 16) | column
 #pragma once
 #include <cstdint>
@@ -23,6 +23,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo_b
 __host__ __device__ constexpr uint32_t idesc_f16_f32(int M, int N) {
   return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// Same operands, fp16 accumulate: each accumulator sits in the low half of its own 32-bit column.
+__host__ __device__ constexpr uint32_t idesc_f16_f16(int M, int N) { return ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24); }
 
 __device__ __forceinline__ void alloc(uint32_t smem_dst_addr, uint32_t n_cols) {  // one whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst_addr), "r"(n_cols) : "memory");
@@ -75,6 +77,12 @@ __device__ __forceinline__ void ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
+}
+// 16 columns of fp16 accumulators, adjacent columns packed into one register as a half2
+__device__ __forceinline__ void ld16_pack(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.pack::16b.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void st4(uint32_t taddr, const uint32_t (&r)[4]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
