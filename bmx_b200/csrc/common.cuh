@@ -59,6 +59,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that may park the thread for up to `ns` nanoseconds (it wakes as soon as the phase completes), so
+// that a waiting warp leaves the issue slots to the warps that work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Non-blocking test of a phase, for a thread that polls several barriers in turn (try_wait may park the
 // thread for a hardware-chosen time before it reports "not yet").
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {

@@ -96,23 +96,47 @@ struct K2bDecodeParams {
 __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;  // another wait already gave up
-    if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy was lost; report and leave
-      if (atomicCAS(status, 0, 1) == 0) {
-        status[1] = blockIdx.x;
-        status[2] = where;
+  // try_wait parks the warp for a hardware-chosen time per poll; the error flag and the clock are looked at
+  // once in a while only.
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 0u) {
+      if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;  // another wait already gave up
+      if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy or an arrival was lost; report and leave
+        if (atomicCAS(status, 0, 1) == 0) {
+          status[1] = blockIdx.x;
+          status[2] = where;
+        }
+        return false;
       }
-      return false;
     }
   }
-  return true;
+}
+
+// The same bounded wait for a warp whose wake-up latency sits on the critical path (the issuing warp of the
+// tcgen05 kernel): it spins on the non-blocking test instead of parking.
+__device__ __forceinline__ bool spin_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 0u) {
+      if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        if (atomicCAS(status, 0, 1) == 0) {
+          status[1] = blockIdx.x;
+          status[2] = where;
+        }
+        return false;
+      }
+    }
+  }
 }
 
 // SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
 int num_sms();
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
-// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); same partial records as the mma.sync kernel
+// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); two partial records per slot (one per tile parity)
 int launch_decode_t5(const K2bDecodeParams& prm, int grid, cudaStream_t s);
 
 }  // namespace bmxk

@@ -23,22 +23,21 @@
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
-#ifdef T5_PROF  // diagnostic builds: cycle counts of one thread per role of block 0 into status[16..]
-#define PROF_T(v) const long long v = clock64()
-#define PROF_ADD(slot, a, b) if (blockIdx.x == 0 && lane == 0 && wq == 0) atomicAdd(&p.status[slot], (int)((b) - (a)))
+#ifdef T5_TRACE  // diagnostic builds: event clocks of six tiles of block 0, written 1 MiB into the workspace (the caller makes it that large)
+#define TRACE(ev, n) do { if (blockIdx.x == 0 && (n) >= 40 && (n) < 46 && lane == 0) reinterpret_cast<volatile int*>(p.status)[262144 + ((n) - 40) * 12 + (ev)] = (int)clock64(); } while (0)
 #else
-#define PROF_T(v)
-#define PROF_ADD(slot, a, b)
+#define TRACE(ev, n)
 #endif
+
 
 namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 896;   // warps 0-15 key, 16-19 softmax, 20-23 value, 24 copy, 25 issue, 26-27 query rotation
+constexpr int T5_THREADS = 1024;  // warps 0-15 key, 16-23 softmax (two sets), 24-27 value, 28 copy, 29 issue, 30-31 query rotation
 constexpr int T5_STAGES = 7;
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
-// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output at 416
+// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output of tile parity e at 416 + 16*e
 constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
@@ -46,8 +45,9 @@ struct T5Smem {
   uint64_t low[2], krot[2], sdone[2], pready[2], vready[2], odone[2];
   uint32_t tmem_base;
   volatile int released;   // tiles whose stage has been handed back
-  float wmax[4][8];
-  float red[4][16];
+  float wmax[2][4][8];
+  __align__(16) int flag[2][4];
+  float red[2][4][16];
 };
 
 // Walks the CTA's tile range; `seg` counts the (sequence, head) ranges met so far.
@@ -88,8 +88,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   uint8_t* stage0 = smem;
   uint8_t* qb0 = stage0 + T5_STAGES * STAGE_BYTES;       // [stage][4096] rotated queries
-  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [2][COEF_BYTES] basis operand per range parity
-  uint8_t* pbuf0 = bbuf0 + 2 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
+  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [3][COEF_BYTES] basis operand, by range index mod 3
+  uint8_t* pbuf0 = bbuf0 + 3 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
   T5Smem* sh = reinterpret_cast<T5Smem*>(pbuf0 + 2 * T5_QB_BYTES);
   int* cum = reinterpret_cast<int*>(sh + 1);
   int* npg_sm = cum + p.batch + 1;
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     sh->released = 0;
     fence_barrier_init();
   }
-  if (warp == 25) {
+  if (warp == 29) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -135,39 +135,84 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   // Registers move from the softmax, value and service warps to the key warps: each group of four warps
   // resizes itself first thing in its branch.
-  if (warp >= 24) {
+  if (warp >= 28) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // the four service warps, as one group
-    if (warp == 24) {
-      // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
-      if (lane == 0) {
-        int s = 0;
-        uint32_t ph = 1;  // a fresh barrier passes parity 1
-        for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-          if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
-          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
+    if (warp == 28) {
+      // ===================== copy + U3 warp =====================
+      // Two jobs polled in turn, neither on the critical path of the key warps: (1) the bulk copies of the next
+      // tile as soon as its stage is free (the page's slot index is fetched one tile ahead); (2) C(n): once the
+      // softmax weights and the value levels of tile n are in place, U3 -> odone[n & 1] and the stage goes back.
+      // The output accumulators are per tile parity: a tile is "first" when its parity has none yet in its range.
+      constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
+      const bool el = elect_one();
+      const uint64_t d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
+      Walker wc = w;                       // walks with C
+      int nC = 0, nP = 0, segp[2] = {-1, -1};
+      int slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
+      long long t_last = clock64();
+      bool ok = true;
+      while (ok && nC < n_tiles) {
+        bool progressed = false;
+        if (nP < n_tiles && mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
+          const int s = nP % T5_STAGES, h = w.cur.h, slot = slot_next;
           uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
           const int chd = (g.n_coef_heads == 1) ? 0 : h;
-          const int slot = p.page_table[(int64_t)b * p.table_stride + j];
-          mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
-          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
-                   &sh->full[s]);
-          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
-          if (++s == T5_STAGES) s = 0, ph ^= 1;
+          if (el) {
+            mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
+            bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+                     &sh->full[s]);
+            bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
+          }
+          __syncwarp();
+          TRACE(0, nP);
+          ++nP;
+          if (nP < n_tiles) {
+            w.advance(npg_sm, g.h_kv, p.batch);
+            slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
+          }
+          progressed = true;
+        }
+        if (nC < nP && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
+            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
+          tc5::fence_after();
+          const int s = nC % T5_STAGES, b = nC & 1;
+          const uint32_t keep = (wc.seg != segp[b]) ? 0u : 1u;
+          segp[b] = wc.seg;
+          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
+          ++nC;
+          if (el) {
+            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            tc5::commit(smem_u32(&sh->odone[b]));
+            mbar_arrive(&sh->empty[s]);
+            sh->released = nC;
+          }
+          TRACE(11, nC - 1);
+          __syncwarp();
+          if (nC < n_tiles) wc.advance(npg_sm, g.h_kv, p.batch);
+          progressed = true;
+        }
+        if (progressed) {
+          t_last = clock64();
+        } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 1;
+          ok = false;
         }
       }
-    } else if (warp >= 26) {
+    } else if (warp >= 30) {
       // ===================== query rotation warps: tiles of parity rw =====================
       // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
       // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
       // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
-      const int rw = warp - 26;
+      const int rw = warp - 30;
       int s = 0;
       uint32_t ph = 1;
-      int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
+      int prev_seg = -1, first_cur = 0, first_prev = 0, first_prev2 = 0;  // first tiles of this range and the two before
       bool alive = true;
       for (; w.it < n_tiles && alive; w.advance(npg_sm, g.h_kv, p.batch)) {
         const bool new_seg = (w.seg != prev_seg);
-        if (new_seg) first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
+        if (new_seg) first_prev2 = first_prev, first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
         if ((w.it & 1) == rw) {
           const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
           const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
@@ -199,10 +244,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               }
           }
           if (new_seg) {
-            if (w.seg >= 2) {
-              // the buffer still serves the range before the previous one until all its tiles are handed back
+            if (w.seg >= 3) {
+              // the buffer still serves the range three back until all its tiles are handed back
               const long long c0 = clock64();
-              while (sh->released < first_prev) {
+              while (sh->released < first_prev2) {
                 if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
                   if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
                   alive = false;
@@ -211,7 +256,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               }
               if (!alive) break;
             }
-            uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg & 1) * COEF_BYTES);
+            uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg % 3) * COEF_BYTES);
             const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
             for (int o = lane; o < 128 * (RANK / 8); o += 32) {
               const int c = o / (RANK / 8), i8 = o % (RANK / 8);
@@ -221,48 +266,45 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
+          TRACE(1, w.it);
         }
         if (++s == T5_STAGES) s = 0, ph ^= 1;
       }
     } else {
-      // ===================== issuing warp =====================
-      // Tile n (buffer b = n & 1) goes through  A: U1 -> low[b];  B: U2 -> sdone[b];  C: U3 -> odone[b], after
-      // which its stage is handed back.  A(n) needs every copy up to tile n landed (the basis operand travels
-      // with the first tile of its range) and U2(n-2) done (same TMEM columns); B(n) needs the rotated keys
-      // and the softmax of tile n-2 finished with the score columns; C(n) needs the weights and the value
-      // levels.  The whole warp walks this state machine in lockstep, so that operand descriptors stay in
-      // uniform registers and the instruction stream stays short; one elected lane issues.
+      // ===================== U1 + U2 warp =====================
+      // A(n): U1 of tile n (buffer b = n & 1) -> low[b]; needs every copy up to tile n landed (the basis operand
+      // travels with the first tile of its range) and U2(n-2) done (same TMEM columns).  B(n): U2 -> sdone[b]; needs
+      // the rotated keys of tile n and the softmax of tile n-2 finished with the score columns.  The key warps
+      // wait on this chain, so the warp does nothing else and spins on the non-blocking barrier test; it runs
+      // in lockstep (operand descriptors stay in uniform registers) and one elected lane issues.
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
-      int nA = 0, nB = 0, nC = 0, segp = -1, obs_it = 0;
-      uint32_t firstbits = 0u;
+      int nA = 0, nB = 0, obs_it = 0;
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
-      const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
+      const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048);
       long long t_last = clock64();
       bool ok = true;
-      while (ok && nC < n_tiles) {
+      while (ok && nB < n_tiles) {
         bool progressed = false;
         while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
-        // ---- A ----
         if (nA < n_tiles && nA < nB + 2 && obs_it > nA &&
             (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
           tc5::fence_after();
           const int s = nA % T5_STAGES, b = nA & 1;
-          if (w.seg != segp) firstbits |= 1u << (nA & 31); else firstbits &= ~(1u << (nA & 31));
-          segp = w.seg;
-          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg & 1) * (COEF_BYTES >> 4));
+          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg % 3) * (COEF_BYTES >> 4));
           if (el) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
+          TRACE(2, nA);
           __syncwarp();
           w.advance(npg_sm, g.h_kv, p.batch);
           ++nA;
           progressed = true;
         }
-        // ---- B ----
-        if (nB < nA && nB < nC + 2 && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u)) {
+        if (nB < nA && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u) &&
+            (nB < 2 || mbar_test_wait(&sh->pready[nB & 1], (uint32_t)((nB - 2) >> 1) & 1u))) {
           tc5::fence_after();
           const int s = nB % T5_STAGES, b = nB & 1;
           const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
@@ -271,27 +313,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
             tc5::commit(smem_u32(&sh->sdone[b]));
           }
+          TRACE(6, nB);
           __syncwarp();
           ++nB;
-          progressed = true;
-        }
-        // ---- C ----
-        if (nC < nB && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
-            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
-          tc5::fence_after();
-          const int s = nC % T5_STAGES, b = nC & 1;
-          const uint32_t keep = ((firstbits >> (nC & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
-          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
-          ++nC;
-          if (el) {
-            tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b, db, ID_N16, keep);
-#pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
-            tc5::commit(smem_u32(&sh->odone[b]));
-            mbar_arrive(&sh->empty[s]);
-            sh->released = nC;
-          }
-          __syncwarp();
           progressed = true;
         }
         if (progressed) {
@@ -304,7 +328,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     }
   } else if (warp < 16) {
     // ===================== key warps: 32 token rows x one chunk of 16 + 16 channels =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 72;");
     const int wq = warp & 3, k = warp >> 2, row = 32 * wq + lane;
     const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
     const int grp = row / g.group;
@@ -324,11 +348,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       const int b = n & 1;
       const uint32_t par = (uint32_t)(n >> 1) & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
-      PROF_T(c_0);
       if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
-      PROF_T(c_1);
       if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
-      PROF_T(c_2);
+      if (warp == 0) TRACE(3, n);
       tc5::fence_after();
       uint32_t dl[8], dh[8], out[16];
       tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
@@ -367,34 +389,35 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->krot[b]);
-      PROF_T(c_3);
-      PROF_ADD(16, c_0, c_1);
-      PROF_ADD(17, c_1, c_2);
-      PROF_ADD(18, c_2, c_3);
+      if (warp == 0) TRACE(4, n);
+      if (warp == 15) TRACE(5, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-  } else if (warp < 20) {
-    // ===================== softmax warps: thread = token row; also owns the running (max, sum) =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    const int wq = warp & 3, row = 32 * wq + lane;
+  } else if (warp < 24) {
+    // ===================== softmax warps: thread = token row =====================
+    // Two sets of four warps; set e takes the tiles of parity e and owns the running (max, sum) and the output
+    // accumulator of that parity, so each set has two tile periods per tile.  Each set writes its own partial
+    // record per (sequence, head) range.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    const int e = (warp - 16) >> 2, wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int cur_seg = -1, cur_b = 0, cur_h = 0, s = 0;
-    uint32_t fp = 0;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
     bool had = false, alive = true;
+    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
 
-    // Writes the partial record of the range that just ended.  `last` is its last tile.
-    auto flush = [&](int b_, int h_, int last) {
+    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
+    auto flush = [&](int b_, int h_) {
       float acc[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (alive && !wait_or_flag(&sh->odone[last & 1], (uint32_t)(last >> 1) & 1u, p.status, 9)) alive = false;
-      if (alive) {
+      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
+      if (had && alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
@@ -405,75 +428,76 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         float a = l[qi], b2 = pn[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[wq][qi] = a, sh->red[wq][GQ + qi] = b2;
+        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
       }
-      named_bar(1, 128);
-      float* dst = p.part + (((int64_t)blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
+      named_bar(1 + e, 128);
+      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
-          const float L = sh->red[0][qi] + sh->red[1][qi] + sh->red[2][qi] + sh->red[3][qi];
-          const float P = sh->red[0][GQ + qi] + sh->red[1][GQ + qi] + sh->red[2][GQ + qi] + sh->red[3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = p.lut_alpha * P + p.lut_beta * acc[qi];
-          if (row == 0) dst[qi * PART_STRIDE] = m[qi], dst[qi * PART_STRIDE + 1] = L;
+          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
+          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
+          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
         }
-      named_bar(1, 128);
+      named_bar(1 + e, 128);
     };
 
     for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-      const int n = w.it, b = n & 1;
-      const uint32_t par = (uint32_t)(n >> 1) & 1u;
+      const int n = w.it;
       if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h, n - 1);
+        if (cur_seg >= 0) flush(cur_b, cur_h);
         cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
       }
+      if ((n & 1) != e) continue;
+      const int s = n % T5_STAGES;
+      const uint32_t fp = (uint32_t)(n / T5_STAGES) & 1u, par = (uint32_t)(n >> 1) & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       float sv[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
-      PROF_T(c_3);
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
-      if (alive && !wait_or_flag(&sh->sdone[b], par, p.status, 7)) alive = false;
-      PROF_T(c_4);
-      PROF_ADD(19, c_3, c_4);
+      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
+      if (wq == 0) TRACE(7, n);
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * b, r); else tc5::ld8(tl + TM_S + 16 * b, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
       }
+      // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
+      // below 2^8), nothing is reduced; the four warps only exchange one flag each.
+      bool need = false;
 #pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) {
-        float v = sv[qi];
+      for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
+      const bool wneed = __any_sync(0xffffffffu, need);
+      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
+      named_bar(1 + e, 128);
+      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
+      const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
+      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      if (resc) {
+        float mnew[GQ];
 #pragma unroll
-        for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-        if (lane == 0) sh->wmax[wq][qi] = v;
-      }
-      PROF_T(c_5);
-      named_bar(1, 128);
-      PROF_T(c_6);
-      PROF_ADD(20, c_4, c_5);
-      PROF_ADD(21, c_5, c_6);
-      bool resc = false;
-      float mnew[GQ];
+        for (int qi = 0; qi < GQ; ++qi) {
+          float v = sv[qi];
 #pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) {
-        const float tm = fmaxf(fmaxf(sh->wmax[0][qi], sh->wmax[1][qi]), fmaxf(sh->wmax[2][qi], sh->wmax[3][qi]));
-        mnew[qi] = m[qi];
-        if (qi < G && tm > m[qi] + 8.f) mnew[qi] = tm, resc = true;  // lazy: weights stay below 2^8
-      }
-      PROF_T(c_7);
-      // the weight buffer still feeds U3 of tile n-2; a rescale of the accumulator needs U3 of tile n-1 done
-      if (alive && n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
-      if (alive && resc && had && !wait_or_flag(&sh->odone[b ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 13)) alive = false;
-      PROF_T(c_8);
-      PROF_ADD(22, c_7, c_8);
-      if (alive) {
-        if (resc) {
+          for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
+          if (lane == 0) sh->wmax[e][wq][qi] = v;
+        }
+        named_bar(1 + e, 128);
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) {
+          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
+          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
+        }
+        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
+        if (alive) {
           float f[GQ];
 #pragma unroll
           for (int qi = 0; qi < GQ; ++qi) {
@@ -483,52 +507,46 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
             tc5::fence_after();
             uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
             tc5::wait_ld();
 #pragma unroll
             for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
             tc5::wait_st();
           }
         }
+      }
+      if (alive) {
         const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)b * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
 #pragma unroll
-        for (int qi = 0; qi < GQ; ++qi)
-          if (qi < G) {
-            const float pe = ex2_approx(sv[qi] - m[qi]);
-            const __half hw = __float2half_rn(pe * norm);
-            l[qi] += pe, pn[qi] += __half2float(hw);
-            pb[qi * 8] = hw;
-          }
+        for (int qi = 0; qi < GQ; qi += 2) {
+          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
+          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
+          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
+          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
+        }
         fence_proxy_async();
         tc5::fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->pready[b]);
+        if (lane == 0) mbar_arrive(&sh->pready[e]);
+        if (wq == 0) TRACE(8, n);
       }
-      PROF_T(c_9);
-      PROF_ADD(23, c_8, c_9);
-      had = true;
-      if (++s == T5_STAGES) s = 0, fp ^= 1u;
+      had = true, last_n = n;
     }
-    flush(cur_b, cur_h, n_tiles - 1);
+    flush(cur_b, cur_h);
   } else {
     // ===================== value warps: thread = channel =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-    const int wq = warp & 3, ch = 32 * wq + lane;
+    const int wq = warp & 3, ch = 32 * wq + lane;  // keeps the 64 registers of the launch
     const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
     int s = 0;
     uint32_t fp = 0;
     for (int n = 0; n < n_tiles; ++n) {
       const int b = n & 1;
-      PROF_T(v_0);
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
-      PROF_T(v_1);
       // the columns still feed U3 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
-      PROF_T(v_2);
-      PROF_ADD(24, v_0, v_1);
-      PROF_ADD(25, v_1, v_2);
+      if (wq == 0) TRACE(9, n);
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
 #pragma unroll
@@ -558,8 +576,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->vready[b]);
-      PROF_T(v_3);
-      PROF_ADD(26, v_2, v_3);
+      if (wq == 0) TRACE(10, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
@@ -567,7 +584,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 25) {
+  if (warp == 29) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
@@ -575,7 +592,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
 static size_t t5_smem_bytes(int rank, int group, int batch) {
   const size_t coef = (size_t)128 * rank * 2;
-  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 2 * coef +
+  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 3 * coef +
          sizeof(T5Smem) + (size_t)(2 * batch + 1) * 4 + 16;
 }
 
