@@ -18,8 +18,11 @@
 //   U3  O^T[128 ch x 16]          += V_lev^T (TMEM) x P (smem), fp32
 //
 // The K, S, V and P buffers are double-buffered by tile parity, so the key warps start tile n+1 while U2
-// and the softmax of tile n are still under way.  Service warps: one thread issues the bulk copies, one
-// warp issues the tcgen05.mma, two warps rotate q (and lay out the basis operand when the head changes).
+// and the softmax of tile n are still under way.  No warp is set aside to issue the tcgen05.mma: whoever
+// completes an operand issues the instruction that was waiting for it -- the key warp that arrives last
+// issues U2, the softmax warp that sees U2 finish issues U1 of the tile two ahead (same TMEM columns), the
+// last softmax / value warp to arrive issues U3 and hands the stage back.  Service warps: one thread issues
+// the bulk copies, one warp rotates q (and lays out the basis operand when the head changes).
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
@@ -30,11 +33,12 @@
 #endif
 
 
+
 namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 1024;  // warps 0-15 key, 16-23 softmax (two sets), 24-27 value, 28 copy, 29 issue, 30-31 query rotation
+constexpr int T5_THREADS = 1024;  // warps 0-15 key, 16-23 softmax (two sets), 24-27 value, 28 copy, 29 query rotation, 30-31 idle
 constexpr int T5_STAGES = 7;
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
 // TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output of tile parity e at 416 + 16*e
@@ -42,8 +46,13 @@ constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
   uint64_t full[T5_STAGES], empty[T5_STAGES];
-  uint64_t low[2], krot[2], sdone[2], pready[2], vready[2], odone[2];
+  uint64_t low[2], sdone[2], odone[2];   // completion of U1 / U2 / U3 on buffer b (tcgen05.commit)
   uint32_t tmem_base;
+  int kcnt[2];             // arrivals of key warps on buffer b (16 per tile)
+  int ccnt[2];             // arrivals of softmax + value warps on buffer b (8 per tile)
+  volatile int sread[2];   // softmax warps that have read the score columns of buffer b (4 per tile)
+  volatile int keep[2];    // 0 when the pending U3 on buffer b starts a new accumulator
+  volatile int bsel[T5_STAGES];  // basis buffer of the tile in this stage
   volatile int released;   // tiles whose stage has been handed back
   float wmax[2][4][8];
   __align__(16) int flag[2][4];
@@ -88,8 +97,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   uint8_t* stage0 = smem;
   uint8_t* qb0 = stage0 + T5_STAGES * STAGE_BYTES;       // [stage][4096] rotated queries
-  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [3][COEF_BYTES] basis operand, by range index mod 3
-  uint8_t* pbuf0 = bbuf0 + 3 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
+  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [4][COEF_BYTES] basis operand, by range index mod 4
+  uint8_t* pbuf0 = bbuf0 + 4 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
   T5Smem* sh = reinterpret_cast<T5Smem*>(pbuf0 + 2 * T5_QB_BYTES);
   int* cum = reinterpret_cast<int*>(sh + 1);
   int* npg_sm = cum + p.batch + 1;
@@ -112,10 +121,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     *reinterpret_cast<uint4*>(base) = make_uint4(0u, 0u, 0u, 0u);
   }
   if (tid == 0) {
-    for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1);
+    for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1), sh->bsel[s] = 0;
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&sh->low[b], 1), mbar_init(&sh->krot[b], 16), mbar_init(&sh->sdone[b], 1);
-      mbar_init(&sh->pready[b], 4), mbar_init(&sh->vready[b], 4), mbar_init(&sh->odone[b], 1);
+      mbar_init(&sh->low[b], 1), mbar_init(&sh->sdone[b], 1), mbar_init(&sh->odone[b], 1);
+      sh->kcnt[b] = 0, sh->ccnt[b] = 0, sh->sread[b] = 0, sh->keep[b] = 0;
     }
     sh->released = 0;
     fence_barrier_init();
@@ -133,197 +142,173 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   Walker w;
   w.init(cum, npg_sm, f_begin, g.h_kv);
 
-  // Registers move from the softmax, value and service warps to the key warps: each group of four warps
-  // resizes itself first thing in its branch.
+  constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
+  const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
+  const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
+  const bool el = elect_one();
+
+  // The three issue routines are called by a whole (converged) warp; one elected lane issues.
+  // U1 of tile n: the caller has seen the tile's copy land (and with it, the rotation warp works in tile order,
+  // the basis operand of its range) and U2 of tile n-2 finish, which read the same TMEM columns.
+  auto issue_U1 = [&](int n) {
+    const int s = n % T5_STAGES, b = n & 1;
+    const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[s] * (COEF_BYTES >> 4));
+    tc5::fence_after();
+    if (el) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+      tc5::commit(smem_u32(&sh->low[b]));
+    }
+    TRACE(2, n);
+    __syncwarp();
+  };
+  // U2 of tile n: every key warp has stored its rotated keys; the softmax of tile n-2 has read the score columns.
+  auto issue_U2 = [&](int n) {
+    const int s = n % T5_STAGES, b = n & 1;
+    const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
+    tc5::fence_after();
+    if (el) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
+      tc5::commit(smem_u32(&sh->sdone[b]));
+    }
+    TRACE(6, n);
+    __syncwarp();
+  };
+  // U3 of tile n: weights and value levels are in place.  The stage goes back with it: every reader of the
+  // stage has arrived by now and U1 / U2 of the tile have completed.
+  auto issue_U3 = [&](int n) {
+    const int s = n % T5_STAGES, b = n & 1;
+    const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
+    const uint32_t keep = (uint32_t)sh->keep[b];
+    tc5::fence_after();
+    if (el) {
+      tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
+#pragma unroll
+      for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+      tc5::commit(smem_u32(&sh->odone[b]));
+      mbar_arrive(&sh->empty[s]);
+      TRACE(11, n);
+      atomicAdd(const_cast<int*>(&sh->released), 1);
+    }
+    __syncwarp();
+  };
+  // Arrival on a shared counter; true in the warp that arrives last (`per_tile` arrivals per tile).
+  auto arrive_last = [&](int* cnt, int per_tile) {
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = ((atomicAdd(cnt, 1) + 1) % per_tile) == 0;
+      __threadfence_block();
+    }
+    return __shfl_sync(0xffffffffu, last, 0) != 0;
+  };
+
+  // Registers move from the softmax and service warps to the key warps: each group of four warps resizes
+  // itself first thing in its branch.
   if (warp >= 28) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // the four service warps, as one group
     if (warp == 28) {
-      // ===================== copy + U3 warp =====================
-      // Two jobs polled in turn, neither on the critical path of the key warps: (1) the bulk copies of the next
-      // tile as soon as its stage is free (the page's slot index is fetched one tile ahead); (2) C(n): once the
-      // softmax weights and the value levels of tile n are in place, U3 -> odone[n & 1] and the stage goes back.
-      // The output accumulators are per tile parity: a tile is "first" when its parity has none yet in its range.
-      constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
-      const bool el = elect_one();
-      const uint64_t d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
-      Walker wc = w;                       // walks with C
-      int nC = 0, nP = 0, segp[2] = {-1, -1};
-      int slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
-      long long t_last = clock64();
-      bool ok = true;
-      while (ok && nC < n_tiles) {
-        bool progressed = false;
-        if (nP < n_tiles && mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
-          const int s = nP % T5_STAGES, h = w.cur.h, slot = slot_next;
-          uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+      // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
+      if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 1;  // a fresh barrier passes parity 1
+        int slot = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
+        while (w.it < n_tiles) {
+          const int h = w.cur.h;
           const int chd = (g.n_coef_heads == 1) ? 0 : h;
-          if (el) {
-            mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
-            bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
-                     &sh->full[s]);
-            bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
-          }
-          __syncwarp();
-          TRACE(0, nP);
-          ++nP;
-          if (nP < n_tiles) {
-            w.advance(npg_sm, g.h_kv, p.batch);
-            slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
-          }
-          progressed = true;
-        }
-        if (nC < nP && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
-            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
-          tc5::fence_after();
-          const int s = nC % T5_STAGES, b = nC & 1;
-          const uint32_t keep = (wc.seg != segp[b]) ? 0u : 1u;
-          segp[b] = wc.seg;
-          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
-          ++nC;
-          if (el) {
-            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
-#pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
-            tc5::commit(smem_u32(&sh->odone[b]));
-            mbar_arrive(&sh->empty[s]);
-            sh->released = nC;
-          }
-          TRACE(11, nC - 1);
-          __syncwarp();
-          if (nC < n_tiles) wc.advance(npg_sm, g.h_kv, p.batch);
-          progressed = true;
-        }
-        if (progressed) {
-          t_last = clock64();
-        } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 1;
-          ok = false;
+          const int slot_now = slot;
+          w.advance(npg_sm, g.h_kv, p.batch);
+          if (w.it < n_tiles) slot = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];  // one tile ahead
+          if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
+          uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+          mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
+          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot_now * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+                   &sh->full[s]);
+          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot_now * g.h_kv + h) * PB, PB, &sh->full[s]);
+          TRACE(0, w.it - 1);
+          if (++s == T5_STAGES) s = 0, ph ^= 1;
         }
       }
-    } else if (warp >= 30) {
-      // ===================== query rotation warps: tiles of parity rw =====================
+    } else if (warp == 29) {
+      // ===================== query rotation warp (every tile, in order) =====================
       // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
-      // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
-      // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
-      const int rw = warp - 30;
+      // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  On the first tile of a
+      // (sequence, head) range it also lays out that head's basis as the B operand of U1, in one of four
+      // buffers.  Because it works in tile order, a landed tile implies the basis of its range is in place.
       int s = 0;
       uint32_t ph = 1;
-      int prev_seg = -1, first_cur = 0, first_prev = 0, first_prev2 = 0;  // first tiles of this range and the two before
+      int prev_seg = -1, first_cur = 0, first_prev = 0, first_prev2 = 0, first_prev3 = 0;  // first tiles of this range and the three before
       bool alive = true;
-      for (; w.it < n_tiles && alive; w.advance(npg_sm, g.h_kv, p.batch)) {
+      // lane owns rotary pairs (c0, c0 + 64) and (c0 + 1, c0 + 65); the tile's cos / sin are fetched one tile ahead
+      const int c0 = 2 * lane;
+      const int k1 = 32 * (c0 >> 4) + (c0 & 15), k2 = k1 + 16;
+      float x1[2][GQ], x2[2][GQ];
+      uint32_t cs_nx = *reinterpret_cast<const uint32_t*>(p.rope_cos + (p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS) * HEAD_DIM + c0);
+      uint32_t sn_nx = *reinterpret_cast<const uint32_t*>(p.rope_sin + (p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS) * HEAD_DIM + c0);
+      while (w.it < n_tiles && alive) {
         const bool new_seg = (w.seg != prev_seg);
-        if (new_seg) first_prev2 = first_prev, first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
-        if ((w.it & 1) == rw) {
-          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
-          const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
-          const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
-          float cs[2], sn[2], x1[2][GQ], x2[2][GQ];
+        if (new_seg) first_prev3 = first_prev2, first_prev2 = first_prev, first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
+        const int h = w.cur.h, seg = w.seg;
+        if (new_seg) {
+          const __half* qsrc = p.q + ((int64_t)w.cur.b * g.h_kv + h) * G * HEAD_DIM;
 #pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int c = lane + 32 * jj;  // rotary pair (c, c + 64)
-            cs[jj] = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
-            sn[jj] = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
-#pragma unroll
-            for (int qi = 0; qi < GQ; ++qi) {
-              x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
-              x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
-            }
+          for (int qi = 0; qi < GQ; ++qi) {
+            const float2 a = (qi < G) ? __half22float2(*reinterpret_cast<const __half2*>(qsrc + qi * HEAD_DIM + c0)) : make_float2(0.f, 0.f);
+            const float2 bq = (qi < G) ? __half22float2(*reinterpret_cast<const __half2*>(qsrc + qi * HEAD_DIM + 64 + c0)) : make_float2(0.f, 0.f);
+            x1[0][qi] = a.x * p.scale_log2, x1[1][qi] = a.y * p.scale_log2;
+            x2[0][qi] = bq.x * p.scale_log2, x2[1][qi] = bq.y * p.scale_log2;
           }
-          if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
-          __half* qr = reinterpret_cast<__half*>(qb0 + (size_t)s * T5_QB_BYTES);
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const int c = lane + 32 * jj;
-            const int k1 = 32 * (c >> 4) + (c & 15), k2 = k1 + 16;
-#pragma unroll
-            for (int qi = 0; qi < GQ; ++qi)
-              if (qi < G) {
-                const float a = x1[jj][qi] * p.scale_log2, bb = x2[jj][qi] * p.scale_log2;
-                qr[(k1 >> 3) * 64 + qi * 8 + (k1 & 7)] = __float2half_rn(a * cs[jj] + bb * sn[jj]);
-                qr[(k2 >> 3) * 64 + qi * 8 + (k2 & 7)] = __float2half_rn(bb * cs[jj] - a * sn[jj]);
-              }
-          }
-          if (new_seg) {
-            if (w.seg >= 3) {
-              // the buffer still serves the range three back until all its tiles are handed back
-              const long long c0 = clock64();
-              while (sh->released < first_prev2) {
-                if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-                  if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
-                  alive = false;
-                  break;
-                }
-              }
-              if (!alive) break;
-            }
-            uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg % 3) * COEF_BYTES);
-            const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
-            for (int o = lane; o < 128 * (RANK / 8); o += 32) {
-              const int c = o / (RANK / 8), i8 = o % (RANK / 8);
-              bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
-            }
-          }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh->full[s]);
-          TRACE(1, w.it);
         }
+        const float2 cs = __half22float2(u32_as_h2(cs_nx)), sn = __half22float2(u32_as_h2(sn_nx));
+        const int it = w.it;
+        w.advance(npg_sm, g.h_kv, p.batch);
+        if (w.it < n_tiles) {
+          const int64_t t1 = p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS;
+          cs_nx = *reinterpret_cast<const uint32_t*>(p.rope_cos + t1 * HEAD_DIM + c0);
+          sn_nx = *reinterpret_cast<const uint32_t*>(p.rope_sin + t1 * HEAD_DIM + c0);
+        }
+        if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
+        uint32_t* qr = reinterpret_cast<uint32_t*>(qb0 + (size_t)s * T5_QB_BYTES);
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi)
+          if (qi < G) {
+            const __half2 y1 = __floats2half2_rn(x1[0][qi] * cs.x + x2[0][qi] * sn.x, x1[1][qi] * cs.y + x2[1][qi] * sn.y);
+            const __half2 y2 = __floats2half2_rn(x2[0][qi] * cs.x - x1[0][qi] * sn.x, x2[1][qi] * cs.y - x1[1][qi] * sn.y);
+            qr[((k1 >> 3) * 64 + qi * 8 + (k1 & 7)) >> 1] = h2_as_u32(y1);
+            qr[((k2 >> 3) * 64 + qi * 8 + (k2 & 7)) >> 1] = h2_as_u32(y2);
+          }
+        if (new_seg) {
+          if (seg >= 4) {
+            // The buffer still serves the range four back until its tiles are done (four buffers, so that this
+            // never waits for a tile whose softmax warp may itself be waiting for the tile being prepared here).
+            // Stages can be handed back out of order by one tile, hence the + 1.
+            const long long tc0 = clock64();
+            while (sh->released < first_prev3 + 1) {
+              if (clock64() - tc0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+                if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
+                alive = false;
+                break;
+              }
+            }
+            if (!alive) break;
+          }
+          uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(seg & 3) * COEF_BYTES);
+          const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
+          for (int o = lane; o < 128 * (RANK / 8); o += 32) {
+            const int c = o / (RANK / 8), i8 = o % (RANK / 8);
+            bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
+          }
+        }
+        if (lane == 0) sh->bsel[s] = seg & 3;
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          mbar_arrive(&sh->full[s]);
+        }
+        TRACE(1, it);
         if (++s == T5_STAGES) s = 0, ph ^= 1;
-      }
-    } else {
-      // ===================== U1 + U2 warp =====================
-      // A(n): U1 of tile n (buffer b = n & 1) -> low[b]; needs every copy up to tile n landed (the basis operand
-      // travels with the first tile of its range) and U2(n-2) done (same TMEM columns).  B(n): U2 -> sdone[b]; needs
-      // the rotated keys of tile n and the softmax of tile n-2 finished with the score columns.  The key warps
-      // wait on this chain, so the warp does nothing else and spins on the non-blocking barrier test; it runs
-      // in lockstep (operand descriptors stay in uniform registers) and one elected lane issues.
-      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
-      const bool el = elect_one();
-      int nA = 0, nB = 0, obs_it = 0;
-      const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
-      const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048);
-      long long t_last = clock64();
-      bool ok = true;
-      while (ok && nB < n_tiles) {
-        bool progressed = false;
-        while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
-        if (nA < n_tiles && nA < nB + 2 && obs_it > nA &&
-            (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
-          tc5::fence_after();
-          const int s = nA % T5_STAGES, b = nA & 1;
-          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg % 3) * (COEF_BYTES >> 4));
-          if (el) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
-            tc5::commit(smem_u32(&sh->low[b]));
-          }
-          TRACE(2, nA);
-          __syncwarp();
-          w.advance(npg_sm, g.h_kv, p.batch);
-          ++nA;
-          progressed = true;
-        }
-        if (nB < nA && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u) &&
-            (nB < 2 || mbar_test_wait(&sh->pready[nB & 1], (uint32_t)((nB - 2) >> 1) & 1u))) {
-          tc5::fence_after();
-          const int s = nB % T5_STAGES, b = nB & 1;
-          const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
-          if (el) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
-            tc5::commit(smem_u32(&sh->sdone[b]));
-          }
-          TRACE(6, nB);
-          __syncwarp();
-          ++nB;
-          progressed = true;
-        }
-        if (progressed) {
-          t_last = clock64();
-        } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
-          ok = false;
-        }
       }
     }
   } else if (warp < 16) {
@@ -388,9 +373,25 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->krot[b]);
       if (warp == 0) TRACE(4, n);
-      if (warp == 15) TRACE(5, n);
+      if (arrive_last(&sh->kcnt[b], 16)) {
+        TRACE(5, n);
+        // the score columns of this buffer: the softmax of tile n-2 must have read them
+        bool ok = true;
+        if (n >= 2 && sh->sread[b] < 4 * (n >> 1)) {
+          const long long c0 = clock64();
+          while (sh->sread[b] < 4 * (n >> 1)) {
+            if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+              if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 15;
+              ok = false;
+              break;
+            }
+          }
+        }
+        if (!ok) break;
+        __threadfence_block();
+        issue_U2(n);
+      }
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   } else if (warp < 24) {
@@ -407,6 +408,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
     bool had = false, alive = true;
     const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
+    // U1 of this set's first tile (afterwards each U1 is issued two tiles ahead, when U2 has freed the columns)
+    if (wq == 0 && e < n_tiles) {
+      if (wait_or_flag(&sh->full[e], 0u, p.status, 18)) issue_U1(e); else alive = false;
+    }
 
     // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
     auto flush = [&](int b_, int h_) {
@@ -465,9 +470,20 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         tc5::fence_after();
         uint32_t r[GQ];
         if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
+        // U2 is done with the key columns of this buffer: start U1 of the tile that uses them next
+        if (wq == 0 && n + 2 < n_tiles) {
+          if (wait_or_flag(&sh->full[(n + 2) % T5_STAGES], (uint32_t)((n + 2) / T5_STAGES) & 1u, p.status, 14)) issue_U1(n + 2);
+          else alive = false;
+        }
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
+        tc5::fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicAdd(const_cast<int*>(&sh->sread[e]), 1);  // the score columns may be overwritten by U2 of tile n+2
+        }
       }
       // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
       // below 2^8), nothing is reduced; the four warps only exchange one flag each.
@@ -528,9 +544,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         }
         fence_proxy_async();
         tc5::fence_before();
+        if (wq == 0 && lane == 0) sh->keep[e] = had ? 1 : 0;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->pready[e]);
         if (wq == 0) TRACE(8, n);
+        if (arrive_last(&sh->ccnt[e], 8)) issue_U3(n);
       }
       had = true, last_n = n;
     }
@@ -575,8 +592,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->vready[b]);
       if (wq == 0) TRACE(10, n);
+      if (arrive_last(&sh->ccnt[b], 8)) issue_U3(n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
@@ -592,7 +609,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
 static size_t t5_smem_bytes(int rank, int group, int batch) {
   const size_t coef = (size_t)128 * rank * 2;
-  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 3 * coef +
+  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 4 * coef +
          sizeof(T5Smem) + (size_t)(2 * batch + 1) * 4 + 16;
 }
 
