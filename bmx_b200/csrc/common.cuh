@@ -70,6 +70,21 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
       : "memory");
   return ok != 0;
 }
+// Shared-memory atomics that are themselves the synchronisation point (release on the way in, acquire on the
+// way out, CTA scope), so that no separate fence is needed around them.
+__device__ __forceinline__ int smem_add_acq_rel(int* addr, int v) {
+  int old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(addr)), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void smem_or_release(int* addr, int v) {
+  asm volatile("red.release.cta.shared::cta.or.b32 [%0], %1;" ::"r"(smem_u32(addr)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int smem_exch_acquire(int* addr, int v) {
+  int old;
+  asm volatile("atom.acquire.cta.shared::cta.exch.b32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(addr)), "r"(v) : "memory");
+  return old;
+}
 // Non-blocking test of a phase, for a thread that polls several barriers in turn (try_wait may park the
 // thread for a hardware-chosen time before it reports "not yet").
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {

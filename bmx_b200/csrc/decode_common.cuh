@@ -100,6 +100,9 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int
   // once in a while only.
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef BMXK_SLEEP_NS
+    __nanosleep(BMXK_SLEEP_NS);
+#endif
     if ((spin & 255u) == 0u) {
       if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;  // another wait already gave up
       if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy or an arrival was lost; report and leave
@@ -136,7 +139,7 @@ __device__ __forceinline__ bool spin_or_flag(uint64_t* bar, uint32_t parity, int
 // SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
 int num_sms();
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
-// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); two partial records per slot (one per tile parity)
+// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); same partial records as the mma.sync kernel
 int launch_decode_t5(const K2bDecodeParams& prm, int grid, cudaStream_t s);
 
 }  // namespace bmxk

@@ -18,45 +18,34 @@
 //   U3  O^T[128 ch x 16]          += V_lev^T (TMEM) x P (smem), fp32
 //
 // The K, S, V and P buffers are double-buffered by tile parity, so the key warps start tile n+1 while U2
-// and the softmax of tile n are still under way.  No warp is set aside to issue the tcgen05.mma: whoever
-// completes an operand issues the instruction that was waiting for it -- the key warp that arrives last
-// issues U2, the softmax warp that sees U2 finish issues U1 of the tile two ahead (same TMEM columns), the
-// last softmax / value warp to arrive issues U3 and hands the stage back.  Service warps: one thread issues
-// the bulk copies, one warp rotates q (and lays out the basis operand when the head changes).
+// and the softmax of tile n are still under way.  Service warps: one thread issues the bulk copies, one
+// warp issues the tcgen05.mma, two warps rotate q (and lay out the basis operand when the head changes).
 #include "decode_common.cuh"
 #include "tc5.cuh"
-
-#ifdef T5_TRACE  // diagnostic builds: event clocks of six tiles of block 0, written 1 MiB into the workspace (the caller makes it that large)
-#define TRACE(ev, n) do { if (blockIdx.x == 0 && (n) >= 40 && (n) < 46 && lane == 0) reinterpret_cast<volatile int*>(p.status)[262144 + ((n) - 40) * 12 + (ev)] = (int)clock64(); } while (0)
-#else
-#define TRACE(ev, n)
-#endif
-
 
 
 namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 1024;  // warps 0-15 key, 16-23 softmax (two sets), 24-27 value, 28 copy, 29 query rotation, 30-31 idle
+constexpr int T5_THREADS = 896;   // warps 0-15 key, 16-19 softmax, 20-23 value, 24 copy, 25 issue, 26-27 query rotation
 constexpr int T5_STAGES = 7;
+// Registers per thread after each role resizes itself.  setmaxnreg.inc blocks (without a time limit) until the
+// CTA's pool has room, and the pool is what the launch handed out: 72 registers x 896 threads = 28 warps x 72.
+constexpr int REG_LAUNCH = 72, REG_KEY = 80, REG_SOFTMAX = 56, REG_VALUE = 64, REG_SERVICE = 56;
+static_assert(16 * REG_KEY + 4 * REG_SOFTMAX + 4 * REG_VALUE + 4 * REG_SERVICE <= 28 * REG_LAUNCH, "register split exceeds the CTA's pool");
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
-// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output of tile parity e at 416 + 16*e
+// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output at 416
 constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
   uint64_t full[T5_STAGES], empty[T5_STAGES];
-  uint64_t low[2], sdone[2], odone[2];   // completion of U1 / U2 / U3 on buffer b (tcgen05.commit)
+  uint64_t low[2], krot[2], sdone[2], pready[2], vready[2], odone[2];
   uint32_t tmem_base;
-  int kcnt[2];             // arrivals of key warps on buffer b (16 per tile)
-  int ccnt[2];             // arrivals of softmax + value warps on buffer b (8 per tile)
-  volatile int sread[2];   // softmax warps that have read the score columns of buffer b (4 per tile)
-  volatile int keep[2];    // 0 when the pending U3 on buffer b starts a new accumulator
-  volatile int bsel[T5_STAGES];  // basis buffer of the tile in this stage
   volatile int released;   // tiles whose stage has been handed back
-  float wmax[2][4][8];
+  float wmax[4][8];
   __align__(16) int flag[2][4];
-  float red[2][4][16];
+  float red[4][16];
 };
 
 // Walks the CTA's tile range; `seg` counts the (sequence, head) ranges met so far.
@@ -97,8 +86,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   uint8_t* stage0 = smem;
   uint8_t* qb0 = stage0 + T5_STAGES * STAGE_BYTES;       // [stage][4096] rotated queries
-  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [4][COEF_BYTES] basis operand, by range index mod 4
-  uint8_t* pbuf0 = bbuf0 + 4 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
+  uint8_t* bbuf0 = qb0 + T5_STAGES * T5_QB_BYTES;        // [2][COEF_BYTES] basis operand per range parity
+  uint8_t* pbuf0 = bbuf0 + 2 * COEF_BYTES;               // [2][4096] softmax weights per tile parity
   T5Smem* sh = reinterpret_cast<T5Smem*>(pbuf0 + 2 * T5_QB_BYTES);
   int* cum = reinterpret_cast<int*>(sh + 1);
   int* npg_sm = cum + p.batch + 1;
@@ -121,15 +110,15 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     *reinterpret_cast<uint4*>(base) = make_uint4(0u, 0u, 0u, 0u);
   }
   if (tid == 0) {
-    for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1), sh->bsel[s] = 0;
+    for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&sh->low[b], 1), mbar_init(&sh->sdone[b], 1), mbar_init(&sh->odone[b], 1);
-      sh->kcnt[b] = 0, sh->ccnt[b] = 0, sh->sread[b] = 0, sh->keep[b] = 0;
+      mbar_init(&sh->low[b], 1), mbar_init(&sh->krot[b], 16), mbar_init(&sh->sdone[b], 1);
+      mbar_init(&sh->pready[b], 4), mbar_init(&sh->vready[b], 4), mbar_init(&sh->odone[b], 1);
     }
     sh->released = 0;
     fence_barrier_init();
   }
-  if (warp == 29) {
+  if (warp == 25) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -142,178 +131,178 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   Walker w;
   w.init(cum, npg_sm, f_begin, g.h_kv);
 
-  constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
-  const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
-  const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
-  const bool el = elect_one();
-
-  // The three issue routines are called by a whole (converged) warp; one elected lane issues.
-  // U1 of tile n: the caller has seen the tile's copy land (and with it, the rotation warp works in tile order,
-  // the basis operand of its range) and U2 of tile n-2 finish, which read the same TMEM columns.
-  auto issue_U1 = [&](int n) {
-    const int s = n % T5_STAGES, b = n & 1;
-    const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[s] * (COEF_BYTES >> 4));
-    tc5::fence_after();
-    if (el) {
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
-      tc5::commit(smem_u32(&sh->low[b]));
-    }
-    TRACE(2, n);
-    __syncwarp();
-  };
-  // U2 of tile n: every key warp has stored its rotated keys; the softmax of tile n-2 has read the score columns.
-  auto issue_U2 = [&](int n) {
-    const int s = n % T5_STAGES, b = n & 1;
-    const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
-    tc5::fence_after();
-    if (el) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
-      tc5::commit(smem_u32(&sh->sdone[b]));
-    }
-    TRACE(6, n);
-    __syncwarp();
-  };
-  // U3 of tile n: weights and value levels are in place.  The stage goes back with it: every reader of the
-  // stage has arrived by now and U1 / U2 of the tile have completed.
-  auto issue_U3 = [&](int n) {
-    const int s = n % T5_STAGES, b = n & 1;
-    const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
-    const uint32_t keep = (uint32_t)sh->keep[b];
-    tc5::fence_after();
-    if (el) {
-      tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
-#pragma unroll
-      for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
-      tc5::commit(smem_u32(&sh->odone[b]));
-      mbar_arrive(&sh->empty[s]);
-      TRACE(11, n);
-      atomicAdd(const_cast<int*>(&sh->released), 1);
-    }
-    __syncwarp();
-  };
-  // Arrival on a shared counter; true in the warp that arrives last (`per_tile` arrivals per tile).
-  auto arrive_last = [&](int* cnt, int per_tile) {
-    int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = ((atomicAdd(cnt, 1) + 1) % per_tile) == 0;
-      __threadfence_block();
-    }
-    return __shfl_sync(0xffffffffu, last, 0) != 0;
-  };
-
-  // Registers move from the softmax and service warps to the key warps: each group of four warps resizes
-  // itself first thing in its branch.
-  if (warp >= 28) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // the four service warps, as one group
-    if (warp == 28) {
+  // Registers move from the softmax, value and service warps to the key warps: each group of four warps
+  // resizes itself first thing in its branch.
+  if (warp >= 24) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
+    if (warp == 24) {
       // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
       if (lane == 0) {
         int s = 0;
         uint32_t ph = 1;  // a fresh barrier passes parity 1
-        int slot = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
-        while (w.it < n_tiles) {
-          const int h = w.cur.h;
-          const int chd = (g.n_coef_heads == 1) ? 0 : h;
-          const int slot_now = slot;
-          w.advance(npg_sm, g.h_kv, p.batch);
-          if (w.it < n_tiles) slot = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];  // one tile ahead
+        for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
           if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
+          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
           uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
+          const int chd = (g.n_coef_heads == 1) ? 0 : h;
+          const int slot = p.page_table[(int64_t)b * p.table_stride + j];
           mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
-          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot_now * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
                    &sh->full[s]);
-          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot_now * g.h_kv + h) * PB, PB, &sh->full[s]);
-          TRACE(0, w.it - 1);
+          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
           if (++s == T5_STAGES) s = 0, ph ^= 1;
         }
       }
-    } else if (warp == 29) {
-      // ===================== query rotation warp (every tile, in order) =====================
+    } else if (warp >= 26) {
+      // ===================== query rotation warps: tiles of parity rw =====================
       // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
-      // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  On the first tile of a
-      // (sequence, head) range it also lays out that head's basis as the B operand of U1, in one of four
-      // buffers.  Because it works in tile order, a landed tile implies the basis of its range is in place.
+      // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
+      // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
+      const int rw = warp - 26;
       int s = 0;
       uint32_t ph = 1;
-      int prev_seg = -1, first_cur = 0, first_prev = 0, first_prev2 = 0, first_prev3 = 0;  // first tiles of this range and the three before
+      int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
       bool alive = true;
-      // lane owns rotary pairs (c0, c0 + 64) and (c0 + 1, c0 + 65); the tile's cos / sin are fetched one tile ahead
-      const int c0 = 2 * lane;
-      const int k1 = 32 * (c0 >> 4) + (c0 & 15), k2 = k1 + 16;
-      float x1[2][GQ], x2[2][GQ];
-      uint32_t cs_nx = *reinterpret_cast<const uint32_t*>(p.rope_cos + (p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS) * HEAD_DIM + c0);
-      uint32_t sn_nx = *reinterpret_cast<const uint32_t*>(p.rope_sin + (p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS) * HEAD_DIM + c0);
-      while (w.it < n_tiles && alive) {
+      for (; w.it < n_tiles && alive; w.advance(npg_sm, g.h_kv, p.batch)) {
         const bool new_seg = (w.seg != prev_seg);
-        if (new_seg) first_prev3 = first_prev2, first_prev2 = first_prev, first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
-        const int h = w.cur.h, seg = w.seg;
-        if (new_seg) {
-          const __half* qsrc = p.q + ((int64_t)w.cur.b * g.h_kv + h) * G * HEAD_DIM;
+        if (new_seg) first_prev = first_cur, first_cur = w.it, prev_seg = w.seg;
+        if ((w.it & 1) == rw) {
+          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
+          const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
+          const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
+          float cs[2], sn[2], x1[2][GQ], x2[2][GQ];
 #pragma unroll
-          for (int qi = 0; qi < GQ; ++qi) {
-            const float2 a = (qi < G) ? __half22float2(*reinterpret_cast<const __half2*>(qsrc + qi * HEAD_DIM + c0)) : make_float2(0.f, 0.f);
-            const float2 bq = (qi < G) ? __half22float2(*reinterpret_cast<const __half2*>(qsrc + qi * HEAD_DIM + 64 + c0)) : make_float2(0.f, 0.f);
-            x1[0][qi] = a.x * p.scale_log2, x1[1][qi] = a.y * p.scale_log2;
-            x2[0][qi] = bq.x * p.scale_log2, x2[1][qi] = bq.y * p.scale_log2;
-          }
-        }
-        const float2 cs = __half22float2(u32_as_h2(cs_nx)), sn = __half22float2(u32_as_h2(sn_nx));
-        const int it = w.it;
-        w.advance(npg_sm, g.h_kv, p.batch);
-        if (w.it < n_tiles) {
-          const int64_t t1 = p.pos_offset + (int64_t)w.cur.j * TILE_TOKENS;
-          cs_nx = *reinterpret_cast<const uint32_t*>(p.rope_cos + t1 * HEAD_DIM + c0);
-          sn_nx = *reinterpret_cast<const uint32_t*>(p.rope_sin + t1 * HEAD_DIM + c0);
-        }
-        if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
-        uint32_t* qr = reinterpret_cast<uint32_t*>(qb0 + (size_t)s * T5_QB_BYTES);
+          for (int jj = 0; jj < 2; ++jj) {
+            const int c = lane + 32 * jj;  // rotary pair (c, c + 64)
+            cs[jj] = __half2float(p.rope_cos[t0 * HEAD_DIM + c]);
+            sn[jj] = __half2float(p.rope_sin[t0 * HEAD_DIM + c]);
 #pragma unroll
-        for (int qi = 0; qi < GQ; ++qi)
-          if (qi < G) {
-            const __half2 y1 = __floats2half2_rn(x1[0][qi] * cs.x + x2[0][qi] * sn.x, x1[1][qi] * cs.y + x2[1][qi] * sn.y);
-            const __half2 y2 = __floats2half2_rn(x2[0][qi] * cs.x - x1[0][qi] * sn.x, x2[1][qi] * cs.y - x1[1][qi] * sn.y);
-            qr[((k1 >> 3) * 64 + qi * 8 + (k1 & 7)) >> 1] = h2_as_u32(y1);
-            qr[((k2 >> 3) * 64 + qi * 8 + (k2 & 7)) >> 1] = h2_as_u32(y2);
-          }
-        if (new_seg) {
-          if (seg >= 4) {
-            // The buffer still serves the range four back until its tiles are done (four buffers, so that this
-            // never waits for a tile whose softmax warp may itself be waiting for the tile being prepared here).
-            // Stages can be handed back out of order by one tile, hence the + 1.
-            const long long tc0 = clock64();
-            while (sh->released < first_prev3 + 1) {
-              if (clock64() - tc0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-                if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
-                alive = false;
-                break;
-              }
+            for (int qi = 0; qi < GQ; ++qi) {
+              x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
+              x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
             }
-            if (!alive) break;
           }
-          uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(seg & 3) * COEF_BYTES);
-          const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
-          for (int o = lane; o < 128 * (RANK / 8); o += 32) {
-            const int c = o / (RANK / 8), i8 = o % (RANK / 8);
-            bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
+          if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
+          __half* qr = reinterpret_cast<__half*>(qb0 + (size_t)s * T5_QB_BYTES);
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const int c = lane + 32 * jj;
+            const int k1 = 32 * (c >> 4) + (c & 15), k2 = k1 + 16;
+#pragma unroll
+            for (int qi = 0; qi < GQ; ++qi)
+              if (qi < G) {
+                const float a = x1[jj][qi] * p.scale_log2, bb = x2[jj][qi] * p.scale_log2;
+                qr[(k1 >> 3) * 64 + qi * 8 + (k1 & 7)] = __float2half_rn(a * cs[jj] + bb * sn[jj]);
+                qr[(k2 >> 3) * 64 + qi * 8 + (k2 & 7)] = __float2half_rn(bb * cs[jj] - a * sn[jj]);
+              }
           }
+          if (new_seg) {
+            if (w.seg >= 2) {
+              // the buffer still serves the range before the previous one until all its tiles are handed back
+              const long long c0 = clock64();
+              while (sh->released < first_prev) {
+                if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+                  if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 4;
+                  alive = false;
+                  break;
+                }
+              }
+              if (!alive) break;
+            }
+            uint4* bd = reinterpret_cast<uint4*>(bbuf0 + (size_t)(w.seg & 1) * COEF_BYTES);
+            const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
+            for (int o = lane; o < 128 * (RANK / 8); o += 32) {
+              const int c = o / (RANK / 8), i8 = o % (RANK / 8);
+              bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->full[s]);
         }
-        if (lane == 0) sh->bsel[s] = seg & 3;
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          mbar_arrive(&sh->full[s]);
-        }
-        TRACE(1, it);
         if (++s == T5_STAGES) s = 0, ph ^= 1;
+      }
+    } else {
+      // ===================== issuing warp =====================
+      // Tile n (buffer b = n & 1) goes through  A: U1 -> low[b];  B: U2 -> sdone[b];  C: U3 -> odone[b], after
+      // which its stage is handed back.  A(n) needs every copy up to tile n landed (the basis operand travels
+      // with the first tile of its range) and U2(n-2) done (same TMEM columns); B(n) needs the rotated keys
+      // and the softmax of tile n-2 finished with the score columns; C(n) needs the weights and the value
+      // levels.  The whole warp walks this state machine in lockstep, so that operand descriptors stay in
+      // uniform registers and the instruction stream stays short; one elected lane issues.
+      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
+      const bool el = elect_one();
+      int nA = 0, nB = 0, nC = 0, segp = -1, obs_it = 0;
+      uint32_t firstbits = 0u;
+      const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
+      const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
+      long long t_last = clock64();
+      bool ok = true;
+      while (ok && nC < n_tiles) {
+        bool progressed = false;
+        while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
+        // ---- A ----
+        if (nA < n_tiles && nA < nB + 2 && obs_it > nA &&
+            (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
+          tc5::fence_after();
+          const int s = nA % T5_STAGES, b = nA & 1;
+          if (w.seg != segp) firstbits |= 1u << (nA & 31); else firstbits &= ~(1u << (nA & 31));
+          segp = w.seg;
+          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg & 1) * (COEF_BYTES >> 4));
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+            tc5::commit(smem_u32(&sh->low[b]));
+          }
+          __syncwarp();
+          w.advance(npg_sm, g.h_kv, p.batch);
+          ++nA;
+          progressed = true;
+        }
+        // ---- B ----
+        if (nB < nA && nB < nC + 2 && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u)) {
+          tc5::fence_after();
+          const int s = nB % T5_STAGES, b = nB & 1;
+          const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
+            tc5::commit(smem_u32(&sh->sdone[b]));
+          }
+          __syncwarp();
+          ++nB;
+          progressed = true;
+        }
+        // ---- C ----
+        if (nC < nB && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
+            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
+          tc5::fence_after();
+          const int s = nC % T5_STAGES, b = nC & 1;
+          const uint32_t keep = ((firstbits >> (nC & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
+          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
+          ++nC;
+          if (el) {
+            tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b, db, ID_N16, keep);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            tc5::commit(smem_u32(&sh->odone[b]));
+            mbar_arrive(&sh->empty[s]);
+            sh->released = nC;
+          }
+          __syncwarp();
+          progressed = true;
+        }
+        if (progressed) {
+          t_last = clock64();
+        } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
+          ok = false;
+        }
       }
     }
   } else if (warp < 16) {
     // ===================== key warps: 32 token rows x one chunk of 16 + 16 channels =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 72;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
     const int wq = warp & 3, k = warp >> 2, row = 32 * wq + lane;
     const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
     const int grp = row / g.group;
@@ -335,7 +324,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
       if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
-      if (warp == 0) TRACE(3, n);
       tc5::fence_after();
       uint32_t dl[8], dh[8], out[16];
       tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
@@ -373,56 +361,31 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (warp == 0) TRACE(4, n);
-      if (arrive_last(&sh->kcnt[b], 16)) {
-        TRACE(5, n);
-        // the score columns of this buffer: the softmax of tile n-2 must have read them
-        bool ok = true;
-        if (n >= 2 && sh->sread[b] < 4 * (n >> 1)) {
-          const long long c0 = clock64();
-          while (sh->sread[b] < 4 * (n >> 1)) {
-            if (clock64() - c0 > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-              if (atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 15;
-              ok = false;
-              break;
-            }
-          }
-        }
-        if (!ok) break;
-        __threadfence_block();
-        issue_U2(n);
-      }
+      if (lane == 0) mbar_arrive(&sh->krot[b]);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-  } else if (warp < 24) {
-    // ===================== softmax warps: thread = token row =====================
-    // Two sets of four warps; set e takes the tiles of parity e and owns the running (max, sum) and the output
-    // accumulator of that parity, so each set has two tile periods per tile.  Each set writes its own partial
-    // record per (sequence, head) range.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-    const int e = (warp - 16) >> 2, wq = warp & 3, row = 32 * wq + lane;
+  } else if (warp < 20) {
+    // ===================== softmax warps: thread = token row; also owns the running (max, sum) =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
+    const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, s = 0;
+    uint32_t fp = 0;
     bool had = false, alive = true;
-    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
-    // U1 of this set's first tile (afterwards each U1 is issued two tiles ahead, when U2 has freed the columns)
-    if (wq == 0 && e < n_tiles) {
-      if (wait_or_flag(&sh->full[e], 0u, p.status, 18)) issue_U1(e); else alive = false;
-    }
 
-    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
-    auto flush = [&](int b_, int h_) {
+    // Writes the partial record of the range that just ended.  `last` is its last tile.
+    auto flush = [&](int b_, int h_, int last) {
       float acc[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
-      if (had && alive) {
+      if (alive && !wait_or_flag(&sh->odone[last & 1], (uint32_t)(last >> 1) & 1u, p.status, 9)) alive = false;
+      if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
@@ -433,57 +396,43 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         float a = l[qi], b2 = pn[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
+        if (lane == 0) sh->red[wq][qi] = a, sh->red[wq][GQ + qi] = b2;
       }
-      named_bar(1 + e, 128);
-      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
+      named_bar(1, 128);
+      float* dst = p.part + (((int64_t)blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
-          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
-          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
-          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
+          const float L = sh->red[0][qi] + sh->red[1][qi] + sh->red[2][qi] + sh->red[3][qi];
+          const float P = sh->red[0][GQ + qi] + sh->red[1][GQ + qi] + sh->red[2][GQ + qi] + sh->red[3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = p.lut_alpha * P + p.lut_beta * acc[qi];
+          if (row == 0) dst[qi * PART_STRIDE] = m[qi], dst[qi * PART_STRIDE + 1] = L;
         }
-      named_bar(1 + e, 128);
+      named_bar(1, 128);
     };
 
     for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-      const int n = w.it;
+      const int n = w.it, b = n & 1;
+      const uint32_t par = (uint32_t)(n >> 1) & 1u;
       if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h);
+        if (cur_seg >= 0) flush(cur_b, cur_h, n - 1);
         cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
       }
-      if ((n & 1) != e) continue;
-      const int s = n % T5_STAGES;
-      const uint32_t fp = (uint32_t)(n / T5_STAGES) & 1u, par = (uint32_t)(n >> 1) & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       float sv[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
-      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
-      if (wq == 0) TRACE(7, n);
+      if (alive && !wait_or_flag(&sh->sdone[b], par, p.status, 7)) alive = false;
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
-        // U2 is done with the key columns of this buffer: start U1 of the tile that uses them next
-        if (wq == 0 && n + 2 < n_tiles) {
-          if (wait_or_flag(&sh->full[(n + 2) % T5_STAGES], (uint32_t)((n + 2) / T5_STAGES) & 1u, p.status, 14)) issue_U1(n + 2);
-          else alive = false;
-        }
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * b, r); else tc5::ld8(tl + TM_S + 16 * b, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
-        tc5::fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          atomicAdd(const_cast<int*>(&sh->sread[e]), 1);  // the score columns may be overwritten by U2 of tile n+2
-        }
       }
       // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
       // below 2^8), nothing is reduced; the four warps only exchange one flag each.
@@ -491,29 +440,33 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
       const bool wneed = __any_sync(0xffffffffu, need);
-      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
-      named_bar(1 + e, 128);
-      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
+      if (lane == 0) sh->flag[b][wq] = wneed ? 1 : 0;
+      named_bar(1, 128);
+      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[b]);
       const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
-      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
-      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      float mnew[GQ];
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) mnew[qi] = m[qi];
       if (resc) {
-        float mnew[GQ];
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) {
           float v = sv[qi];
 #pragma unroll
           for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-          if (lane == 0) sh->wmax[e][wq][qi] = v;
+          if (lane == 0) sh->wmax[wq][qi] = v;
         }
-        named_bar(1 + e, 128);
+        named_bar(1, 128);
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) {
-          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
-          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
+          const float tm = fmaxf(fmaxf(sh->wmax[0][qi], sh->wmax[1][qi]), fmaxf(sh->wmax[2][qi], sh->wmax[3][qi]));
+          if (qi < G && tm > m[qi] + 8.f) mnew[qi] = tm;
         }
-        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
-        if (alive) {
+      }
+      // the weight buffer still feeds U3 of tile n-2; a rescale of the accumulator needs U3 of tile n-1 done
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      if (alive && resc && had && !wait_or_flag(&sh->odone[b ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 13)) alive = false;
+      if (alive) {
+        if (resc) {
           float f[GQ];
 #pragma unroll
           for (int qi = 0; qi < GQ; ++qi) {
@@ -523,38 +476,37 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
             tc5::fence_after();
             uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
             tc5::wait_ld();
 #pragma unroll
             for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
             tc5::wait_st();
           }
         }
-      }
-      if (alive) {
         const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)b * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
 #pragma unroll
-        for (int qi = 0; qi < GQ; qi += 2) {
-          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
-          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
-          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
-          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
-        }
+        for (int qi = 0; qi < GQ; ++qi)
+          if (qi < G) {
+            const float pe = ex2_approx(sv[qi] - m[qi]);
+            const __half hw = __float2half_rn(pe * norm);
+            l[qi] += pe, pn[qi] += __half2float(hw);
+            pb[qi * 8] = hw;
+          }
         fence_proxy_async();
         tc5::fence_before();
-        if (wq == 0 && lane == 0) sh->keep[e] = had ? 1 : 0;
         __syncwarp();
-        if (wq == 0) TRACE(8, n);
-        if (arrive_last(&sh->ccnt[e], 8)) issue_U3(n);
+        if (lane == 0) mbar_arrive(&sh->pready[b]);
       }
-      had = true, last_n = n;
+      had = true;
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-    flush(cur_b, cur_h);
+    flush(cur_b, cur_h, n_tiles - 1);
   } else {
     // ===================== value warps: thread = channel =====================
-    const int wq = warp & 3, ch = 32 * wq + lane;  // keeps the 64 registers of the launch
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
+    const int wq = warp & 3, ch = 32 * wq + lane;
     const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
     int s = 0;
     uint32_t fp = 0;
@@ -563,7 +515,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
       // the columns still feed U3 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
-      if (wq == 0) TRACE(9, n);
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
 #pragma unroll
@@ -592,8 +543,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (wq == 0) TRACE(10, n);
-      if (arrive_last(&sh->ccnt[b], 8)) issue_U3(n);
+      if (lane == 0) mbar_arrive(&sh->vready[b]);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
@@ -601,7 +551,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 29) {
+  if (warp == 25) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
@@ -609,7 +559,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
 static size_t t5_smem_bytes(int rank, int group, int batch) {
   const size_t coef = (size_t)128 * rank * 2;
-  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 4 * coef +
+  return (size_t)T5_STAGES * (coef + k2b_page_block_bytes(128, group)) + (size_t)(T5_STAGES + 2) * T5_QB_BYTES + 2 * coef +
          sizeof(T5Smem) + (size_t)(2 * batch + 1) * 4 + 16;
 }
 

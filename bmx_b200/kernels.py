@@ -57,7 +57,7 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise RuntimeError("bmxk kernels take CUDA tensors; there is no CPU path")
 
 
-DEFAULT_K2B_LAYOUT = int(__import__('os').environ.get('BMXK_K2B_LAYOUT', '0'))
+DEFAULT_K2B_LAYOUT = int(__import__('os').environ.get('BMXK_K2B_LAYOUT', '1'))
 
 
 def k2b_geom(h_kv: int, n_q_groups: int, page: int = 128, rank: int = 16, group: int = 64,
