@@ -33,10 +33,10 @@ H_KV, G, D, RANK, PAGE, GROUP, WINDOW = 8, 4, 128, 32, 128, 64, 128
 BATCH, CTX = 8, 32768
 BYTES_PER_UNIT = 166  # per (token, kv head): coefficients 64 + residual nibbles 64 + scales 4 + value codes 32 + norm 2
 ROPE_THETA = 500000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_kernel launch, from the ncu capture
-# summarised in profiles/k2b_decode_kernel_B8_T16384.md (174.4 + 4.3 MB at 16384 tokens), scaled by 2
+# dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_t5_kernel launch, from the ncu capture
+# summarised in profiles/k2b_decode_t5_kernel_B8_T16384.md (174.4 + 5.4 MB at 16384 tokens), scaled by 2
 # to this workload's 32768 tokens (the kernel streams every page once, so traffic grows with tokens).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.37e6 + 4.26e6)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.37e6 + 5.40e6)
 
 
 def measured_peak_gbs():
@@ -346,7 +346,7 @@ def run_ours(args, rank, world, local_rank):
             "us_per_layer_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic", "config": dict(workload_config(world), context=args.ctx),
             "frac_of_8TBps": world * algo_bytes / (ms_per_step * 1e-3) / 1e9 / (8000.0 * world),
-            "roofline": {"bound": "hbm", "kernel": "k2b_decode_kernel<32,128>", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "k2b_decode_t5_kernel<32,4>", "achieved": achieved, "peak": peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * args.ctx / CTX, "algorithmic_bytes": algo_bytes,
                          "kernel_us": main_ms * 1e3, "merge_kernel_us": merge_ms * 1e3},

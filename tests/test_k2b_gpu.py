@@ -150,13 +150,13 @@ def test_append_export_dequant(page, rank, per_head, group):
 
 
 def _decode_case(dev, K, *, n_seq, h_kv, G, page, rank, per_head, group, pages_per_seq, tail_lens, seed, tail_cap=256,
-                 shuffle_slots=True):
+                 shuffle_slots=True, layout=None):
     """Runs append + decode on the GPU and the oracle's chunked dequant-attention on the same
     stored pages; returns (gpu_out, oracle_out) as (n_seq, heads, 128) float32 arrays."""
     max_pages = max(pages_per_seq)
     T = max(max_pages, 1) * page
     k, v, basis = make_k2b_inputs(seed, n_seq, h_kv, T, rank, per_head)
-    g = K.k2b_geom(h_kv, G, page, rank, group, h_kv if per_head else 1)
+    g = K.k2b_geom(h_kv, G, page, rank, group, h_kv if per_head else 1, layout=layout)
     n_slots = n_seq * max(max_pages, 1) + 3
     pool = K.K2bPool(g, n_slots, dev)
     gen = torch.Generator().manual_seed(seed + 1)
@@ -230,6 +230,29 @@ def test_decode_ragged_and_edge_cases():
     _assert_attn_close(out, ref)
     out, ref = _decode_case(dev, K, n_seq=3, h_kv=8, G=4, page=128, rank=32, per_head=True, group=64,
                             pages_per_seq=[33, 0, 2], tail_lens=[128, 64, 0], seed=17)
+    _assert_attn_close(out, ref)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_decode_both_page_layouts(layout):
+    """128-token pages can be stored in either byte order; each order has its own decode kernel (0: mma.sync,
+    1: tcgen05) and both must give the oracle's attention on the pages they stored."""
+    dev, K = _dev(), _K()
+    out, ref = _decode_case(dev, K, n_seq=2, h_kv=4, G=4, page=128, rank=32, per_head=True, group=64,
+                            pages_per_seq=[9, 5], tail_lens=[40, 128], seed=29, layout=layout)
+    _assert_attn_close(out, ref)
+    out, ref = _decode_case(dev, K, n_seq=3, h_kv=2, G=8, page=128, rank=16, per_head=False, group=32,
+                            pages_per_seq=[1, 1, 3], tail_lens=[0, 7, 255], seed=31, layout=layout)
+    _assert_attn_close(out, ref)
+
+
+def test_decode_short_sequences_many_ranges_per_cta():
+    """Many (sequence, head) ranges of one or two tiles each: every CTA crosses range boundaries on almost
+    every tile, which exercises the per-range flush, the basis hand-over and the first-tile accumulate flag."""
+    dev, K = _dev(), _K()
+    pages = [1, 2, 1, 3, 1, 1, 2, 1, 1, 2, 1, 1, 1, 2, 1, 1, 2, 1, 1, 1, 3, 1, 1, 2]
+    out, ref = _decode_case(dev, K, n_seq=len(pages), h_kv=8, G=4, page=128, rank=32, per_head=True, group=64,
+                            pages_per_seq=pages, tail_lens=[(7 * i) % 200 for i in range(len(pages))], seed=37)
     _assert_attn_close(out, ref)
 
 
