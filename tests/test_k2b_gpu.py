@@ -250,7 +250,7 @@ def test_decode_short_sequences_many_ranges_per_cta():
     """Many (sequence, head) ranges of one or two tiles each: every CTA crosses range boundaries on almost
     every tile, which exercises the per-range flush, the basis hand-over and the first-tile accumulate flag."""
     dev, K = _dev(), _K()
-    pages = [1, 2, 1, 3, 1, 1, 2, 1, 1, 2, 1, 1, 1, 2, 1, 1, 2, 1, 1, 1, 3, 1, 1, 2]
+    pages = [[1, 2, 1, 3, 1, 1, 2, 1][i % 8] for i in range(64)]   # 512 ranges, ~770 tiles: 5-6 tiles per CTA
     out, ref = _decode_case(dev, K, n_seq=len(pages), h_kv=8, G=4, page=128, rank=32, per_head=True, group=64,
                             pages_per_seq=pages, tail_lens=[(7 * i) % 200 for i in range(len(pages))], seed=37)
     _assert_attn_close(out, ref)
