@@ -85,6 +85,16 @@ __device__ __forceinline__ int smem_exch_acquire(int* addr, int v) {
   asm volatile("atom.acquire.cta.shared::cta.exch.b32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(addr)), "r"(v) : "memory");
   return old;
 }
+// Arrival counters in shared memory for a consumer that polls several of them with plain loads (an mbarrier
+// test costs ~70 cycles and they cannot overlap; loads can): release on the producer's add, acquire on the load.
+__device__ __forceinline__ void smem_add_release(int* addr, int v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(smem_u32(addr)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int smem_load_acquire(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(addr)) : "memory");
+  return v;
+}
 // Non-blocking test of a phase, for a thread that polls several barriers in turn (try_wait may park the
 // thread for a hardware-chosen time before it reports "not yet").
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {

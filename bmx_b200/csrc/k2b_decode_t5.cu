@@ -28,21 +28,23 @@ namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 896;   // warps 0-15 key, 16-19 softmax, 20-23 value, 24 copy, 25 issue, 26-27 query rotation
+constexpr int T5_THREADS = 640;   // warps 0-7 key, 8-11 softmax, 12-15 value, 16 copy, 17 issue, 18-19 query rotation
 constexpr int T5_STAGES = 7;
 // Registers per thread after each role resizes itself.  setmaxnreg.inc blocks (without a time limit) until the
-// CTA's pool has room, and the pool is what the launch handed out: 72 registers x 896 threads = 28 warps x 72.
-constexpr int REG_LAUNCH = 72, REG_KEY = 80, REG_SOFTMAX = 56, REG_VALUE = 64, REG_SERVICE = 56;
-static_assert(16 * REG_KEY + 4 * REG_SOFTMAX + 4 * REG_VALUE + 4 * REG_SERVICE <= 28 * REG_LAUNCH, "register split exceeds the CTA's pool");
+// CTA's pool has room, and the pool is what the launch handed out: 96 registers x 640 threads = 20 warps x 96.
+constexpr int REG_LAUNCH = 96, REG_KEY = 128, REG_SOFTMAX = 64, REG_VALUE = 72, REG_SERVICE = 64;
+static_assert(8 * REG_KEY + 4 * REG_SOFTMAX + 4 * REG_VALUE + 4 * REG_SERVICE <= 20 * REG_LAUNCH, "register split exceeds the CTA's pool");
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
 // TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output at 416
 constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
   uint64_t full[T5_STAGES], empty[T5_STAGES];
-  uint64_t low[2], krot[2], sdone[2], pready[2], vready[2], odone[2];
+  uint64_t low[2], sdone[2], odone[2];   // completion of U1 / U2 / U3 on buffer b (tcgen05.commit)
   uint32_t tmem_base;
   volatile int released;   // tiles whose stage has been handed back
+  int kcnt[2], pcnt[2], vcnt[2];           // arrivals of key (8 per tile) / softmax (4) / value (4) warps on buffer b, never reset
+  volatile int bsel[T5_STAGES], first[T5_STAGES];  // per stage: basis buffer of the tile, and whether it starts a range
   float wmax[4][8];
   __align__(16) int flag[2][4];
   float red[4][16];
@@ -112,13 +114,13 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   if (tid == 0) {
     for (int s = 0; s < T5_STAGES; ++s) mbar_init(&sh->full[s], 2), mbar_init(&sh->empty[s], 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&sh->low[b], 1), mbar_init(&sh->krot[b], 16), mbar_init(&sh->sdone[b], 1);
-      mbar_init(&sh->pready[b], 4), mbar_init(&sh->vready[b], 4), mbar_init(&sh->odone[b], 1);
+      mbar_init(&sh->low[b], 1), mbar_init(&sh->sdone[b], 1), mbar_init(&sh->odone[b], 1);
     }
     sh->released = 0;
+    for (int b = 0; b < 2; ++b) sh->kcnt[b] = sh->pcnt[b] = sh->vcnt[b] = 0;
     fence_barrier_init();
   }
-  if (warp == 25) {
+  if (warp == 17) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -133,9 +135,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   // Registers move from the softmax, value and service warps to the key warps: each group of four warps
   // resizes itself first thing in its branch.
-  if (warp >= 24) {
+  if (warp >= 16) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
-    if (warp == 24) {
+    if (warp == 16) {
       // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
       if (lane == 0) {
         int s = 0;
@@ -153,12 +155,12 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (++s == T5_STAGES) s = 0, ph ^= 1;
         }
       }
-    } else if (warp >= 26) {
+    } else if (warp >= 18) {
       // ===================== query rotation warps: tiles of parity rw =====================
       // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
       // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
       // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
-      const int rw = warp - 26;
+      const int rw = warp - 18;
       int s = 0;
       uint32_t ph = 1;
       int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
@@ -216,6 +218,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
             }
           }
+          if (lane == 0) sh->bsel[s] = w.seg & 1, sh->first[s] = new_seg ? 1 : 0;
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
@@ -232,35 +235,21 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       // uniform registers and the instruction stream stays short; one elected lane issues.
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
-      int nA = 0, nB = 0, nC = 0, segp = -1, obs_it = 0;
-      uint32_t firstbits = 0u;
+      int nA = 0, nB = 0, nC = 0;
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
       const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       long long t_last = clock64();
+      uint32_t idle = 0;
       bool ok = true;
       while (ok && nC < n_tiles) {
         bool progressed = false;
-        while (obs_it < n_tiles && mbar_test_wait(&sh->full[obs_it % T5_STAGES], (uint32_t)(obs_it / T5_STAGES) & 1u)) ++obs_it;
-        // ---- A ----
-        if (nA < n_tiles && nA < nB + 2 && obs_it > nA &&
-            (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
-          tc5::fence_after();
-          const int s = nA % T5_STAGES, b = nA & 1;
-          if (w.seg != segp) firstbits |= 1u << (nA & 31); else firstbits &= ~(1u << (nA & 31));
-          segp = w.seg;
-          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)((w.seg & 1) * (COEF_BYTES >> 4));
-          if (el) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
-            tc5::commit(smem_u32(&sh->low[b]));
-          }
-          __syncwarp();
-          w.advance(npg_sm, g.h_kv, p.batch);
-          ++nA;
-          progressed = true;
-        }
+        // the three software counters are read together (independent loads), the two hardware barriers only
+        // when U1 could otherwise go
+        const int kc = smem_load_acquire(&sh->kcnt[nB & 1]);
+        const int pc = smem_load_acquire(&sh->pcnt[nC & 1]);
+        const int vc = smem_load_acquire(&sh->vcnt[nC & 1]);
         // ---- B ----
-        if (nB < nA && nB < nC + 2 && mbar_test_wait(&sh->krot[nB & 1], (uint32_t)(nB >> 1) & 1u)) {
+        if (nB < nA && nB < nC + 2 && kc >= 8 * ((nB >> 1) + 1)) {
           tc5::fence_after();
           const int s = nB % T5_STAGES, b = nB & 1;
           const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
@@ -273,12 +262,26 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           ++nB;
           progressed = true;
         }
+        // ---- A ----
+        if (nA < n_tiles && nA < nB + 2 && mbar_test_wait(&sh->full[nA % T5_STAGES], (uint32_t)(nA / T5_STAGES) & 1u) &&
+            (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
+          tc5::fence_after();
+          const int s = nA % T5_STAGES, b = nA & 1;
+          const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[s] * (COEF_BYTES >> 4));
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+            tc5::commit(smem_u32(&sh->low[b]));
+          }
+          __syncwarp();
+          ++nA;
+          progressed = true;
+        }
         // ---- C ----
-        if (nC < nB && mbar_test_wait(&sh->pready[nC & 1], (uint32_t)(nC >> 1) & 1u) &&
-            mbar_test_wait(&sh->vready[nC & 1], (uint32_t)(nC >> 1) & 1u)) {
+        if (nC < nB && pc >= 4 * ((nC >> 1) + 1) && vc >= 4 * ((nC >> 1) + 1)) {
           tc5::fence_after();
           const int s = nC % T5_STAGES, b = nC & 1;
-          const uint32_t keep = ((firstbits >> (nC & 31)) & 1u) ^ 1u;  // 0 on the first tile of a range
+          const uint32_t keep = sh->first[s] ? 0u : 1u;  // a range's first tile starts a new accumulator
           const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
           ++nC;
           if (el) {
@@ -293,29 +296,34 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           progressed = true;
         }
         if (progressed) {
-          t_last = clock64();
-        } else if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
-          ok = false;
+          idle = 0;
+        } else if ((++idle & 255u) == 0u) {
+          if (idle == 256u) t_last = clock64();
+          if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+            if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 5;
+            ok = false;
+          }
         }
       }
     }
-  } else if (warp < 16) {
-    // ===================== key warps: 32 token rows x one chunk of 16 + 16 channels =====================
+  } else if (warp < 8) {
+    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
-    const int wq = warp & 3, k = warp >> 2, row = 32 * wq + lane;
+    const int wq = warp & 3, k0 = 2 * (warp >> 2), row = 32 * wq + lane;
     const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
     const int grp = row / g.group;
     const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
     const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
     const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
-    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15
-    uint32_t cs_[8], sn_[8];
+    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
+    uint32_t cs_[2][8], sn_[2][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      cs_[i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * k + 2 * i);
-      sn_[i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * k + 2 * i);
-    }
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+        sn_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+      }
     int s = 0;
     uint32_t fp = 0;
     for (int n = 0; n < n_tiles; ++n) {
@@ -325,46 +333,53 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
       if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
       tc5::fence_after();
-      uint32_t dl[8], dh[8], out[16];
-      tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
-      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k, dh);
-      const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
+      uint32_t dl[2][8], dh[2][8];
+      tc5::ld16_pack(tk + 128 * b + 16 * k0, dl[0]);
+      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0, dh[0]);
+      tc5::ld16_pack(tk + 128 * b + 16 * k0 + 16, dl[1]);
+      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0 + 16, dh[1]);
       const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
-      const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
-      tc5::wait_ld();
 #pragma unroll
-      for (int wd = 0; wd < 2; ++wd) {
-        const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
-        const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
-        __half2 rl[4], rh[4];
-        {
-          const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
-          rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
-          rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-          rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
-          rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-          rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
-          rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-          rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
-          rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-        }
+      for (int kk = 0; kk < 2; ++kk) {
+        const int k = k0 + kk;
+        uint32_t out[16];
+        const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
+        const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
+        if (kk == 0) tc5::wait_ld();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[4 * wd + i]));
-          const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[4 * wd + i]));
-          const __half2 c = u32_as_h2(cs_[4 * wd + i]), sn = u32_as_h2(sn_[4 * wd + i]);
-          out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
-          out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+        for (int wd = 0; wd < 2; ++wd) {
+          const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
+          const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
+          __half2 rl[4], rh[4];
+          {
+            const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
+            rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
+            rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
+            rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
+            rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
+            rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[kk][4 * wd + i]));
+            const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[kk][4 * wd + i]));
+            const __half2 c = u32_as_h2(cs_[kk][4 * wd + i]), sn = u32_as_h2(sn_[kk][4 * wd + i]);
+            out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+            out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+          }
         }
+        tc5::st16(tk + 128 * b + 16 * k, out);
       }
-      tc5::st16(tk + 128 * b + 16 * k, out);
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->krot[b]);
+      if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-  } else if (warp < 20) {
+  } else if (warp < 12) {
     // ===================== softmax warps: thread = token row; also owns the running (max, sum) =====================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
     const int wq = warp & 3, row = 32 * wq + lane;
@@ -497,7 +512,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         fence_proxy_async();
         tc5::fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->pready[b]);
+        if (lane == 0) smem_add_release(&sh->pcnt[b], 1);
       }
       had = true;
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
@@ -543,7 +558,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->vready[b]);
+      if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
@@ -551,7 +566,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 25) {
+  if (warp == 17) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
