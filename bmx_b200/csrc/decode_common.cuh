@@ -139,7 +139,7 @@ __device__ __forceinline__ bool spin_or_flag(uint64_t* bar, uint32_t parity, int
 // SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
 int num_sms();
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
-// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); same partial records as the mma.sync kernel
+// tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); two partial records per slot (one per tile parity)
 int launch_decode_t5(const K2bDecodeParams& prm, int grid, cudaStream_t s);
 
 }  // namespace bmxk

@@ -694,7 +694,7 @@ extern "C" {
 size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int max_pages) {
   if (!g || batch <= 0) return 0;
   (void)max_pages;
-  const size_t slots = (size_t)num_sms() + (size_t)batch * g->h_kv;
+  const size_t slots = ((size_t)num_sms() + (size_t)batch * g->h_kv) * (g->layout == 1 ? 2 : 1);
   return 256 + slots * g->n_q_groups * PART_STRIDE * sizeof(float);
 }
 
@@ -771,7 +771,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   K2bMergeParams mp;
   mp.g.h_kv = g->h_kv, mp.g.n_q_groups = g->n_q_groups, mp.g.page = g->page, mp.g.rank = g->rank, mp.g.group = g->group;
   mp.g.n_coef_heads = g->n_coef_heads, mp.g.kbits = g->kbits, mp.g.vbits = g->vbits, mp.g.layout = g->layout;
-  mp.n_sub = 1;
+  mp.n_sub = (g->layout == 1) ? 2 : 1;  // the tcgen05 kernel keeps one state per tile parity
   mp.q = (const __half*)q, mp.n_pages = n_pages, mp.batch = batch, mp.main_grid = grid, mp.part = part;
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;

@@ -28,14 +28,14 @@ namespace bmxk {
 
 namespace {
 
-constexpr int T5_THREADS = 640;   // warps 0-7 key, 8-11 softmax, 12-15 value, 16 copy, 17 issue, 18-19 query rotation
+constexpr int T5_THREADS = 896;   // warps 0-7 key, 8-15 softmax (two sets), 16-23 value (two halves), 24 copy, 25 issue, 26-27 query rotation
 constexpr int T5_STAGES = 7;
 // Registers per thread after each role resizes itself.  setmaxnreg.inc blocks (without a time limit) until the
-// CTA's pool has room, and the pool is what the launch handed out: 96 registers x 640 threads = 20 warps x 96.
-constexpr int REG_LAUNCH = 96, REG_KEY = 128, REG_SOFTMAX = 64, REG_VALUE = 72, REG_SERVICE = 64;
-static_assert(8 * REG_KEY + 4 * REG_SOFTMAX + 4 * REG_VALUE + 4 * REG_SERVICE <= 20 * REG_LAUNCH, "register split exceeds the CTA's pool");
+// CTA's pool has room, and the pool is what the launch handed out: 72 registers x 896 threads = 28 warps x 72.
+constexpr int REG_LAUNCH = 72, REG_KEY = 112, REG_SOFTMAX = 56, REG_VALUE = 56, REG_SERVICE = 56;
+static_assert(8 * REG_KEY + 8 * REG_SOFTMAX + 8 * REG_VALUE + 4 * REG_SERVICE <= 28 * REG_LAUNCH, "register split exceeds the CTA's pool");
 constexpr int T5_QB_BYTES = 4096;  // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
-// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output at 416
+// TMEM columns: K_low / K_rot of buffer b at 128*b; value levels at 256 + 64*b; scores at 384 + 16*b; output of tile parity e at 416 + 16*e
 constexpr uint32_t TM_KD = 0, TM_V = 256, TM_S = 384, TM_O = 416, TM_COLS = 512;
 
 struct T5Smem {
@@ -45,9 +45,9 @@ struct T5Smem {
   volatile int released;   // tiles whose stage has been handed back
   int kcnt[2], pcnt[2], vcnt[2];           // arrivals of key (8 per tile) / softmax (4) / value (4) warps on buffer b, never reset
   volatile int bsel[T5_STAGES], first[T5_STAGES];  // per stage: basis buffer of the tile, and whether it starts a range
-  float wmax[4][8];
+  float wmax[2][4][8];
   __align__(16) int flag[2][4];
-  float red[4][16];
+  float red[2][4][16];
 };
 
 // Walks the CTA's tile range; `seg` counts the (sequence, head) ranges met so far.
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     for (int b = 0; b < 2; ++b) sh->kcnt[b] = sh->pcnt[b] = sh->vcnt[b] = 0;
     fence_barrier_init();
   }
-  if (warp == 17) {
+  if (warp == 25) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -135,9 +135,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   // Registers move from the softmax, value and service warps to the key warps: each group of four warps
   // resizes itself first thing in its branch.
-  if (warp >= 16) {
+  if (warp >= 24) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
-    if (warp == 16) {
+    if (warp == 24) {
       // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
       if (lane == 0) {
         int s = 0;
@@ -155,12 +155,12 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (++s == T5_STAGES) s = 0, ph ^= 1;
         }
       }
-    } else if (warp >= 18) {
+    } else if (warp >= 26) {
       // ===================== query rotation warps: tiles of parity rw =====================
       // q_rot = R(-t0) q * scale, written as the B operand of U2 in the K order the key warps produce:
       // position 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the
       // first tile of a (sequence, head) range also lays out that head's basis as the B operand of U1.
-      const int rw = warp - 18;
+      const int rw = warp - 26;
       int s = 0;
       uint32_t ph = 1;
       int prev_seg = -1, first_cur = 0, first_prev = 0;  // first tile of the current / previous range
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
             }
           }
-          if (lane == 0) sh->bsel[s] = w.seg & 1, sh->first[s] = new_seg ? 1 : 0;
+          if (lane == 0) sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it - first_cur < 2) ? 1 : 0;
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
@@ -278,16 +278,16 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           progressed = true;
         }
         // ---- C ----
-        if (nC < nB && pc >= 4 * ((nC >> 1) + 1) && vc >= 4 * ((nC >> 1) + 1)) {
+        if (nC < nB && pc >= 4 * ((nC >> 1) + 1) && vc >= 8 * ((nC >> 1) + 1)) {
           tc5::fence_after();
           const int s = nC % T5_STAGES, b = nC & 1;
-          const uint32_t keep = sh->first[s] ? 0u : 1u;  // a range's first tile starts a new accumulator
+          const uint32_t keep = sh->first[s] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
           const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
           ++nC;
           if (el) {
-            tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b, db, ID_N16, keep);
+            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
             tc5::commit(smem_u32(&sh->odone[b]));
             mbar_arrive(&sh->empty[s]);
             sh->released = nC;
@@ -379,28 +379,31 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
-  } else if (warp < 12) {
-    // ===================== softmax warps: thread = token row; also owns the running (max, sum) =====================
+  } else if (warp < 16) {
+    // ===================== softmax warps: thread = token row =====================
+    // Two sets of four warps; set e takes the tiles of parity e and owns the running (max, sum) and the output
+    // accumulator of that parity, so each set has two tile periods per tile.  Each set writes its own partial
+    // record per (sequence, head) range.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
-    const int wq = warp & 3, row = 32 * wq + lane;
+    const int e = (warp - 8) >> 2, wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int cur_seg = -1, cur_b = 0, cur_h = 0, s = 0;
-    uint32_t fp = 0;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
     bool had = false, alive = true;
+    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
 
-    // Writes the partial record of the range that just ended.  `last` is its last tile.
-    auto flush = [&](int b_, int h_, int last) {
+    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
+    auto flush = [&](int b_, int h_) {
       float acc[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (alive && !wait_or_flag(&sh->odone[last & 1], (uint32_t)(last >> 1) & 1u, p.status, 9)) alive = false;
-      if (alive) {
+      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
+      if (had && alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
@@ -411,40 +414,42 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         float a = l[qi], b2 = pn[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[wq][qi] = a, sh->red[wq][GQ + qi] = b2;
+        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
       }
-      named_bar(1, 128);
-      float* dst = p.part + (((int64_t)blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
+      named_bar(1 + e, 128);
+      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
-          const float L = sh->red[0][qi] + sh->red[1][qi] + sh->red[2][qi] + sh->red[3][qi];
-          const float P = sh->red[0][GQ + qi] + sh->red[1][GQ + qi] + sh->red[2][GQ + qi] + sh->red[3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = p.lut_alpha * P + p.lut_beta * acc[qi];
-          if (row == 0) dst[qi * PART_STRIDE] = m[qi], dst[qi * PART_STRIDE + 1] = L;
+          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
+          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
+          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
         }
-      named_bar(1, 128);
+      named_bar(1 + e, 128);
     };
 
     for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-      const int n = w.it, b = n & 1;
-      const uint32_t par = (uint32_t)(n >> 1) & 1u;
+      const int n = w.it;
       if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h, n - 1);
+        if (cur_seg >= 0) flush(cur_b, cur_h);
         cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
       }
+      if ((n & 1) != e) continue;
+      const int s = n % T5_STAGES;
+      const uint32_t fp = (uint32_t)(n / T5_STAGES) & 1u, par = (uint32_t)(n >> 1) & 1u;
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       float sv[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
-      if (alive && !wait_or_flag(&sh->sdone[b], par, p.status, 7)) alive = false;
+      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * b, r); else tc5::ld8(tl + TM_S + 16 * b, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
@@ -455,33 +460,29 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
       const bool wneed = __any_sync(0xffffffffu, need);
-      if (lane == 0) sh->flag[b][wq] = wneed ? 1 : 0;
-      named_bar(1, 128);
-      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[b]);
+      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
+      named_bar(1 + e, 128);
+      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
       const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
-      float mnew[GQ];
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) mnew[qi] = m[qi];
+      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
       if (resc) {
+        float mnew[GQ];
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) {
           float v = sv[qi];
 #pragma unroll
           for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-          if (lane == 0) sh->wmax[wq][qi] = v;
+          if (lane == 0) sh->wmax[e][wq][qi] = v;
         }
-        named_bar(1, 128);
+        named_bar(1 + e, 128);
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) {
-          const float tm = fmaxf(fmaxf(sh->wmax[0][qi], sh->wmax[1][qi]), fmaxf(sh->wmax[2][qi], sh->wmax[3][qi]));
-          if (qi < G && tm > m[qi] + 8.f) mnew[qi] = tm;
+          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
+          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
         }
-      }
-      // the weight buffer still feeds U3 of tile n-2; a rescale of the accumulator needs U3 of tile n-1 done
-      if (alive && n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
-      if (alive && resc && had && !wait_or_flag(&sh->odone[b ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 13)) alive = false;
-      if (alive) {
-        if (resc) {
+        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
+        if (alive) {
           float f[GQ];
 #pragma unroll
           for (int qi = 0; qi < GQ; ++qi) {
@@ -491,37 +492,37 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
             tc5::fence_after();
             uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
             tc5::wait_ld();
 #pragma unroll
             for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
             tc5::wait_st();
           }
         }
+      }
+      if (alive) {
         const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)b * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
 #pragma unroll
-        for (int qi = 0; qi < GQ; ++qi)
-          if (qi < G) {
-            const float pe = ex2_approx(sv[qi] - m[qi]);
-            const __half hw = __float2half_rn(pe * norm);
-            l[qi] += pe, pn[qi] += __half2float(hw);
-            pb[qi * 8] = hw;
-          }
+        for (int qi = 0; qi < GQ; qi += 2) {
+          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
+          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
+          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
+          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
+        }
         fence_proxy_async();
         tc5::fence_before();
         __syncwarp();
-        if (lane == 0) smem_add_release(&sh->pcnt[b], 1);
+        if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
       }
-      had = true;
-      if (++s == T5_STAGES) s = 0, fp ^= 1u;
+      had = true, last_n = n;
     }
-    flush(cur_b, cur_h, n_tiles - 1);
+    flush(cur_b, cur_h);
   } else {
-    // ===================== value warps: thread = channel =====================
+    // ===================== value warps: thread = channel, warp = one half (64 tokens) of the tile =====================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
-    const int wq = warp & 3, ch = 32 * wq + lane;
+    const int wq = warp & 3, cc = (warp - 16) >> 2, ch = 32 * wq + lane;
     const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
     int s = 0;
     uint32_t fp = 0;
@@ -532,8 +533,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
@@ -566,7 +566,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 17) {
+  if (warp == 25) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
