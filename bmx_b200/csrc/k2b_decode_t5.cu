@@ -8,20 +8,34 @@
 //
 //   U1  K_low[128 tok x 128 ch]   = coef[128 x rank] (smem, straight from the bulk copy) x basis^T (smem),
 //                                   fp16 accumulators
-//   key warps (16; warp = 32 tokens x one chunk of 16 + 16 channels):
+//   key warps (8; warp = 32 tokens x two chunks of 16 + 16 channels):
 //                                   K = K_low + scale * residual   (nibble -> half2 by LOP3 + exact fix-up),
 //                                   rotated by the token's offset inside the tile (its cos/sin stay in
 //                                   registers), written back into the same TMEM columns as the A operand of U2
 //   U2  S[128 tok x 16]            = K_rot (TMEM) x q_rot^T (smem; the tile's base rotation is applied to q)
-//   softmax warps (4):              online softmax in base 2 with a lazy rescale; p * norm -> smem (B of U3)
-//   value warps (4; thread = channel): 2-bit codes -> fp16 levels by byte-permute lookups -> TMEM (A of U3)
-//   U3  O^T[128 ch x 16]          += V_lev^T (TMEM) x P (smem), fp32
+//   softmax warps (two sets of 4; set e takes the tiles of parity e and owns that parity's running
+//                                   (max, sum) and output accumulator): online softmax in base 2 with a lazy
+//                                   rescale; p * norm -> smem (B of U3)
+//   value warps (8; thread = channel, warp = 64 tokens): 2-bit codes -> fp16 levels by byte-permute lookups
+//                                   -> TMEM (A of U3)
+//   U3  O_e^T[128 ch x 16]        += V_lev^T (TMEM) x P (smem), fp32
 //
 // The K, S, V and P buffers are double-buffered by tile parity, so the key warps start tile n+1 while U2
-// and the softmax of tile n are still under way.  Service warps: one thread issues the bulk copies, one
-// warp issues the tcgen05.mma, two warps rotate q (and lay out the basis operand when the head changes).
+// and the softmax of tile n are still under way.  Service warps: one thread issues the bulk copies, two
+// warps rotate q (and lay out the basis operand when the head changes), one warp issues every
+// tcgen05.mma.  That warp shares its scheduler with compute warps, so what it executes between "operand
+// complete" and "MMA issued" is kept minimal: the compute warps arrive on plain counters in shared memory,
+// which it reads with independent loads (an mbarrier test costs ~70 cycles and tests do not overlap), and
+// per-tile facts it would have to derive (basis buffer, first tile of a range) are left for it in shared
+// memory by the rotation warps.  The two parities end as two partial records per (CTA, range).
 #include "decode_common.cuh"
 #include "tc5.cuh"
+
+#ifdef T5_TRACE  // diagnostic builds: event clocks of six tiles of block 0, written 1 MiB into the workspace (the caller makes it that large)
+#define TRACE(ev, n) do { if (blockIdx.x == 0 && (n) >= 40 && (n) < 46 && lane == 0) reinterpret_cast<volatile int*>(p.status)[262144 + ((n) - 40) * 16 + (ev)] = (int)clock64(); } while (0)
+#else
+#define TRACE(ev, n)
+#endif
 
 
 namespace bmxk {
@@ -43,6 +57,7 @@ struct T5Smem {
   uint64_t low[2], sdone[2], odone[2];   // completion of U1 / U2 / U3 on buffer b (tcgen05.commit)
   uint32_t tmem_base;
   volatile int released;   // tiles whose stage has been handed back
+  int bcnt, ccnt;                          // U2 / U3 issued so far, each written by its issuing warp for the other
   int kcnt[2], pcnt[2], vcnt[2];           // arrivals of key (8 per tile) / softmax (4) / value (4) warps on buffer b, never reset
   volatile int bsel[T5_STAGES], first[T5_STAGES];  // per stage: basis buffer of the tile, and whether it starts a range
   float wmax[2][4][8];
@@ -116,7 +131,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sh->low[b], 1), mbar_init(&sh->sdone[b], 1), mbar_init(&sh->odone[b], 1);
     }
-    sh->released = 0;
+    sh->released = 0, sh->bcnt = 0, sh->ccnt = 0;
     for (int b = 0; b < 2; ++b) sh->kcnt[b] = sh->pcnt[b] = sh->vcnt[b] = 0;
     fence_barrier_init();
   }
@@ -138,21 +153,70 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
   if (warp >= 24) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
     if (warp == 24) {
-      // ===================== copy warp: one thread issues the two bulk copies of every tile =====================
-      if (lane == 0) {
-        int s = 0;
-        uint32_t ph = 1;  // a fresh barrier passes parity 1
-        for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-          if (!wait_or_flag(&sh->empty[s], ph, p.status, 1)) break;
-          const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
+      // ===================== copy + U3 warp =====================
+      // Two jobs polled in turn: (1) the bulk copies of the next tile as soon as its stage is free (the page's
+      // slot index is fetched one tile ahead); (2) C(n): once the softmax weights and the value levels of tile n
+      // are in place, U3 -> odone[n & 1], and the stage is handed back.  U3 is issued here and not by the U1 / U2
+      // warp because three issues per tile are more than one warp gets through in a tile period.
+      constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
+      const bool el = elect_one();
+      const uint64_t d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
+      int nC = 0, nP = 0;
+      int slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
+      long long t_last = clock64();
+      uint32_t idle = 0;
+      bool ok = true;
+      while (ok && nC < n_tiles) {
+        bool progressed = false;
+        const int pc = smem_load_acquire(&sh->pcnt[nC & 1]);
+        const int vc = smem_load_acquire(&sh->vcnt[nC & 1]);
+        const int bdone = smem_load_acquire(&sh->bcnt);
+        if (nC < bdone && pc >= 4 * ((nC >> 1) + 1) && vc >= 8 * ((nC >> 1) + 1)) {
+          tc5::fence_after();
+          const int s = nC % T5_STAGES, b = nC & 1;
+          const uint32_t keep = sh->first[s] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
+          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
+          ++nC;
+          if (el) {
+            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            tc5::commit(smem_u32(&sh->odone[b]));
+            mbar_arrive(&sh->empty[s]);
+            smem_add_release(&sh->ccnt, 1);
+            sh->released = nC;
+          }
+          TRACE(11, nC - 1);
+          __syncwarp();
+          progressed = true;
+        }
+        if (nP < n_tiles && mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
+          const int s = nP % T5_STAGES, h = w.cur.h, slot = slot_next;
           uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
           const int chd = (g.n_coef_heads == 1) ? 0 : h;
-          const int slot = p.page_table[(int64_t)b * p.table_stride + j];
-          mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
-          bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
-                   &sh->full[s]);
-          bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
-          if (++s == T5_STAGES) s = 0, ph ^= 1;
+          if (el) {
+            mbar_arrive_expect_tx(&sh->full[s], (uint32_t)(COEF_BYTES + PB));
+            bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+                     &sh->full[s]);
+            bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
+          }
+          TRACE(0, nP);
+          __syncwarp();
+          ++nP;
+          if (nP < n_tiles) {
+            w.advance(npg_sm, g.h_kv, p.batch);
+            slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
+          }
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if ((++idle & 255u) == 0u) {
+          if (idle == 256u) t_last = clock64();
+          if (clock64() - t_last > 4000000000LL || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+            if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 1;
+            ok = false;
+          }
         }
       }
     } else if (warp >= 26) {
@@ -222,32 +286,32 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
+          TRACE(1, w.it);
         }
         if (++s == T5_STAGES) s = 0, ph ^= 1;
       }
     } else {
       // ===================== issuing warp =====================
       // Tile n (buffer b = n & 1) goes through  A: U1 -> low[b];  B: U2 -> sdone[b];  C: U3 -> odone[b], after
-      // which its stage is handed back.  A(n) needs every copy up to tile n landed (the basis operand travels
-      // with the first tile of its range) and U2(n-2) done (same TMEM columns); B(n) needs the rotated keys
-      // and the softmax of tile n-2 finished with the score columns; C(n) needs the weights and the value
-      // levels.  The whole warp walks this state machine in lockstep, so that operand descriptors stay in
-      // uniform registers and the instruction stream stays short; one elected lane issues.
+      // which its stage is handed back.  A(n) needs the tile's copy landed (tiles are taken in order, so the
+      // basis operand, which travels with the first tile of its range, has landed too) and U2(n-2) done (same
+      // TMEM columns); B(n) needs the rotated keys of all key warps and the softmax of tile n-2 finished with
+      // the score columns; C(n) needs the weights and the value levels.  The whole warp walks this state machine
+      // in lockstep, so that operand descriptors stay in uniform registers; one elected lane issues.
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
-      int nA = 0, nB = 0, nC = 0;
+      int nA = 0, nB = 0;
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
       const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       long long t_last = clock64();
       uint32_t idle = 0;
       bool ok = true;
-      while (ok && nC < n_tiles) {
+      while (ok && nB < n_tiles) {
         bool progressed = false;
-        // the three software counters are read together (independent loads), the two hardware barriers only
+        // the software counters are read together (independent loads), the two hardware barriers only
         // when U1 could otherwise go
         const int kc = smem_load_acquire(&sh->kcnt[nB & 1]);
-        const int pc = smem_load_acquire(&sh->pcnt[nC & 1]);
-        const int vc = smem_load_acquire(&sh->vcnt[nC & 1]);
+        const int nC = smem_load_acquire(&sh->ccnt);   // U3 issued so far (the other issuing warp)
         // ---- B ----
         if (nB < nA && nB < nC + 2 && kc >= 8 * ((nB >> 1) + 1)) {
           tc5::fence_after();
@@ -257,7 +321,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) tc5::mma_ts(tmem + TM_S + 16 * b, tmem + TM_KD + 128 * b + 8 * ks, db + 16 * ks, ID_N16, ks > 0);
             tc5::commit(smem_u32(&sh->sdone[b]));
+            smem_add_release(&sh->bcnt, 1);
           }
+          TRACE(6, nB);
           __syncwarp();
           ++nB;
           progressed = true;
@@ -273,26 +339,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
+          TRACE(2, nA);
           __syncwarp();
           ++nA;
-          progressed = true;
-        }
-        // ---- C ----
-        if (nC < nB && pc >= 4 * ((nC >> 1) + 1) && vc >= 8 * ((nC >> 1) + 1)) {
-          tc5::fence_after();
-          const int s = nC % T5_STAGES, b = nC & 1;
-          const uint32_t keep = sh->first[s] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
-          const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
-          ++nC;
-          if (el) {
-            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
-#pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
-            tc5::commit(smem_u32(&sh->odone[b]));
-            mbar_arrive(&sh->empty[s]);
-            sh->released = nC;
-          }
-          __syncwarp();
           progressed = true;
         }
         if (progressed) {
@@ -332,6 +381,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
       if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
+      if (warp == 0) TRACE(3, n);
+      if (warp == 7) TRACE(5, n);
       tc5::fence_after();
       uint32_t dl[2][8], dh[2][8];
       tc5::ld16_pack(tk + 128 * b + 16 * k0, dl[0]);
@@ -377,6 +428,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
+      if (warp == 0) TRACE(4, n);
+      if (warp == 7) TRACE(12, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   } else if (warp < 16) {
@@ -446,6 +499,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
       if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
+      if (wq == 0) TRACE(7, n);
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
@@ -515,6 +569,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         tc5::fence_before();
         __syncwarp();
         if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
+        if (wq == 0) TRACE(8, n);
       }
       had = true, last_n = n;
     }
@@ -531,6 +586,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
       // the columns still feed U3 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
+      if (warp == 16) TRACE(9, n);
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
       {
@@ -559,6 +615,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
+      if (warp == 16) TRACE(10, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
