@@ -34,9 +34,9 @@ BATCH, CTX = 8, 32768
 BYTES_PER_UNIT = 166  # per (token, kv head): coefficients 64 + residual nibbles 64 + scales 4 + value codes 32 + norm 2
 ROPE_THETA = 500000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_t5_kernel launch, from the ncu capture
-# summarised in profiles/k2b_decode_t5_kernel_B8_T16384.md (174.4 + 5.4 MB at 16384 tokens), scaled by 2
+# summarised in profiles/k2b_decode_t5_kernel_B8_T16384.md (174.9 + 4.7 MB at 16384 tokens), scaled by 2
 # to this workload's 32768 tokens (the kernel streams every page once, so traffic grows with tokens).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.37e6 + 5.40e6)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.90e6 + 4.69e6)
 
 
 def measured_peak_gbs():
