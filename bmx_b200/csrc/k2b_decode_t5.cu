@@ -385,10 +385,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (warp == 7) TRACE(5, n);
       tc5::fence_after();
       uint32_t dl[2][8], dh[2][8];
+      // a warp's TMEM loads complete one after the other, so the second chunk's are issued only after the first
+      // chunk's have landed and travel while the first chunk is computed
       tc5::ld16_pack(tk + 128 * b + 16 * k0, dl[0]);
       tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0, dh[0]);
-      tc5::ld16_pack(tk + 128 * b + 16 * k0 + 16, dl[1]);
-      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0 + 16, dh[1]);
       const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
@@ -396,7 +396,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         uint32_t out[16];
         const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
         const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
-        if (kk == 0) tc5::wait_ld();
+        tc5::wait_ld();
+        if (kk == 0) {
+          tc5::ld16_pack(tk + 128 * b + 16 * k0 + 16, dl[1]);
+          tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0 + 16, dh[1]);
+        }
 #pragma unroll
         for (int wd = 0; wd < 2; ++wd) {
           const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
