@@ -430,6 +430,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 constexpr int MERGE_THREADS = 512;
 constexpr int MERGE_SPLIT = MERGE_THREADS / 128;  // token ranges of the window accumulation
 
+// GQ = 4 or 8: an upper bound of the group size known at compile time, so that the per-query loops carry no
+// predicated-off iterations (they would still be issued).
+template <int GQ>
 __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMergeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const K2bGeom g = p.g;
@@ -460,13 +463,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
   const __half* kt = p.k_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
   const __half* vt = p.v_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
-  float mx[8];
+  float mx[GQ];
 #pragma unroll
-  for (int qi = 0; qi < 8; ++qi) mx[qi] = -INFINITY;
+  for (int qi = 0; qi < GQ; ++qi) mx[qi] = -INFINITY;
   for (int t = tid; t < tl; t += MERGE_THREADS) {
-    float d[8];
+    float d[GQ];
 #pragma unroll
-    for (int qi = 0; qi < 8; ++qi) d[qi] = 0.f;
+    for (int qi = 0; qi < GQ; ++qi) d[qi] = 0.f;
     const uint4* row = reinterpret_cast<const uint4*>(kt + (int64_t)t * HEAD_DIM);
     uint4 rw[16];  // the whole 256-byte key row in flight at once: this kernel is latency bound
 #pragma unroll
@@ -477,7 +480,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
       const float2 k0 = __half22float2(u32_as_h2(raw.x)), k1 = __half22float2(u32_as_h2(raw.y));
       const float2 k2 = __half22float2(u32_as_h2(raw.z)), k3 = __half22float2(u32_as_h2(raw.w));
 #pragma unroll
-      for (int qi = 0; qi < 8; ++qi)
+      for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
           const float4 qa = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8);
           const float4 qb = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8 + 4);
@@ -485,7 +488,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
         }
     }
 #pragma unroll
-    for (int qi = 0; qi < 8; ++qi)
+    for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) {
         sc[qi * p.tail_cap + t] = d[qi];
         mx[qi] = fmaxf(mx[qi], d[qi]);
@@ -493,7 +496,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   }
   // block max per query
 #pragma unroll
-  for (int qi = 0; qi < 8; ++qi)
+  for (int qi = 0; qi < GQ; ++qi)
     if (qi < G) {
       float v = mx[qi];
 #pragma unroll
@@ -508,12 +511,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   }
   __syncthreads();
   // weights and their sum
-  float sm[8];
+  float sm[GQ];
 #pragma unroll
-  for (int qi = 0; qi < 8; ++qi) sm[qi] = 0.f;
+  for (int qi = 0; qi < GQ; ++qi) sm[qi] = 0.f;
   for (int t = tid; t < tl; t += MERGE_THREADS) {
 #pragma unroll
-    for (int qi = 0; qi < 8; ++qi)
+    for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) {
         const float e = ex2_approx(sc[qi * p.tail_cap + t] - tm[qi]);
         sc[qi * p.tail_cap + t] = e;
@@ -522,7 +525,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   }
   __syncthreads();  // redm reuse
 #pragma unroll
-  for (int qi = 0; qi < 8; ++qi)
+  for (int qi = 0; qi < GQ; ++qi)
     if (qi < G) {
       float v = sm[qi];
 #pragma unroll
@@ -538,9 +541,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   // ---- window accumulators: thread = (token half, channel), all G queries in one pass over V ----
   {
     const int ch = tid & 127, part = tid >> 7;
-    float a[8];
+    float a[GQ];
 #pragma unroll
-    for (int qi = 0; qi < 8; ++qi) a[qi] = 0.f;
+    for (int qi = 0; qi < GQ; ++qi) a[qi] = 0.f;
     const int per = (tl + MERGE_SPLIT - 1) / MERGE_SPLIT;
     const int t_lo = min(tl, part * per), t_hi = min(tl, t_lo + per);
     for (int t0 = t_lo; t0 < t_hi; t0 += 16) {
@@ -552,12 +555,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
         const float vf = __half2float(vv[k]);
         const int t = min(t0 + k, t_hi - 1);
 #pragma unroll
-        for (int qi = 0; qi < 8; ++qi)
+        for (int qi = 0; qi < GQ; ++qi)
           if (qi < G) a[qi] = fmaf(sc[qi * p.tail_cap + t], vf, a[qi]);
       }
     }
 #pragma unroll
-    for (int qi = 0; qi < 8; ++qi)
+    for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) atl[(part * G + qi) * HEAD_DIM + ch] = a[qi];
   }
   // ---- partial slots of the page-streaming kernel: thread = (query pair, channel) ----
@@ -652,7 +655,8 @@ int launch_merge(const K2bMergeParams& mp, cudaStream_t s) {
   const int G = mp.g.n_q_groups;
   const size_t msmem = ((size_t)G * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
   BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
-  k2b_merge_kernel<<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
+  if (G <= 4) k2b_merge_kernel<4><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
+  else k2b_merge_kernel<8><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
   return check_launch("decode(merge)");
 }
 
