@@ -437,8 +437,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   extern __shared__ __align__(128) uint8_t smem[];
   const K2bGeom g = p.g;
   const int G = g.n_q_groups;
-  float* sc = reinterpret_cast<float*>(smem);            // [G][tail_cap] scores, then weights
-  float* accs = sc + G * p.tail_cap;                      // [G][128] rotated accumulators
+  float* sc = reinterpret_cast<float*>(smem);            // [tail_cap][GQ] scores, then weights
+  float* accs = sc + GQ * p.tail_cap;                     // [G][128] rotated accumulators
   float* atl = accs + G * HEAD_DIM;                       // [MERGE_SPLIT][G][128] window accumulators
   float* qs = atl + MERGE_SPLIT * G * HEAD_DIM;                     // [G][128] scaled queries
   float* redm = qs + G * HEAD_DIM;                        // [16 warps][8] partial max / sum
@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) {
-        sc[qi * p.tail_cap + t] = d[qi];
+        sc[t * GQ + qi] = d[qi];
         mx[qi] = fmaxf(mx[qi], d[qi]);
       }
   }
@@ -518,8 +518,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) {
-        const float e = ex2_approx(sc[qi * p.tail_cap + t] - tm[qi]);
-        sc[qi * p.tail_cap + t] = e;
+        const float e = ex2_approx(sc[t * GQ + qi] - tm[qi]);
+        sc[t * GQ + qi] = e;
         sm[qi] += e;
       }
   }
@@ -554,9 +554,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
       for (int k = 0; k < 16; ++k) {
         const float vf = __half2float(vv[k]);
         const int t = min(t0 + k, t_hi - 1);
+        float wq[GQ];  // the token's weights for all queries: one or two 128-bit loads, the same address for the whole warp
+#pragma unroll
+        for (int q4 = 0; q4 < GQ; q4 += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(sc + t * GQ + q4);
+          wq[q4] = w4.x, wq[q4 + 1] = w4.y, wq[q4 + 2] = w4.z, wq[q4 + 3] = w4.w;
+        }
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi)
-          if (qi < G) a[qi] = fmaf(sc[qi * p.tail_cap + t], vf, a[qi]);
+          if (qi < G) a[qi] = fmaf(wq[qi], vf, a[qi]);
       }
     }
 #pragma unroll
@@ -653,7 +659,7 @@ int num_sms() {
 
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s) {
   const int G = mp.g.n_q_groups;
-  const size_t msmem = ((size_t)G * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
+  const size_t msmem = ((size_t)(G <= 4 ? 4 : 8) * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
   BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
   if (G <= 4) k2b_merge_kernel<4><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
   else k2b_merge_kernel<8><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
