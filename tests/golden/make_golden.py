@@ -40,9 +40,11 @@ def _stub_tensorly() -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("BMX_REFERENCE", ""), help="checkout of pherber3/bmx (its src/ is imported)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("--reference (or BMX_REFERENCE) must point at a checkout of the bmx reference")
     sys.path[:0] = [_stub_tensorly(), os.path.join(args.reference, "src")]
 
     import torch
