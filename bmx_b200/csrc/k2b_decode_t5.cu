@@ -59,6 +59,8 @@ struct T5Smem {
   volatile int released;   // tiles whose stage has been handed back
   int bcnt, ccnt;                          // U2 / U3 issued so far, each written by its issuing warp for the other
   int kcnt[2], pcnt[2], vcnt[2];           // arrivals of key (8 per tile) / softmax (4) / value (4) warps on buffer b, never reset
+  volatile int slot_ring[16];              // page slot of tile n at n % 16, fetched by the rotation warps ahead of the copy
+  int slot_seq[2];                         // rotation warp r has published the slots of its tiles below this index
   volatile int bsel[T5_STAGES], first[T5_STAGES];  // per stage: basis buffer of the tile, and whether it starts a range
   float wmax[2][4][8];
   __align__(16) int flag[2][4];
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sh->low[b], 1), mbar_init(&sh->sdone[b], 1), mbar_init(&sh->odone[b], 1);
     }
-    sh->released = 0, sh->bcnt = 0, sh->ccnt = 0;
+    sh->released = 0, sh->bcnt = 0, sh->ccnt = 0, sh->slot_seq[0] = sh->slot_seq[1] = 0;
     for (int b = 0; b < 2; ++b) sh->kcnt[b] = sh->pcnt[b] = sh->vcnt[b] = 0;
     fence_barrier_init();
   }
@@ -155,14 +157,13 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
     if (warp == 24) {
       // ===================== copy + U3 warp =====================
       // Two jobs polled in turn: (1) the bulk copies of the next tile as soon as its stage is free (the page's
-      // slot index is fetched one tile ahead); (2) C(n): once the softmax weights and the value levels of tile n
+      // slot index comes from the rotation warps through shared memory); (2) C(n): once the softmax weights and the value levels of tile n
       // are in place, U3 -> odone[n & 1], and the stage is handed back.  U3 is issued here and not by the U1 / U2
       // warp because three issues per tile are more than one warp gets through in a tile period.
       constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
       const uint64_t d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       int nC = 0, nP = 0;
-      int slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
       long long t_last = clock64();
       uint32_t idle = 0;
       bool ok = true;
@@ -190,8 +191,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           __syncwarp();
           progressed = true;
         }
-        if (nP < n_tiles && mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
-          const int s = nP % T5_STAGES, h = w.cur.h, slot = slot_next;
+        if (nP < n_tiles && smem_load_acquire(&sh->slot_seq[nP & 1]) > nP &&
+            mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
+          const int s = nP % T5_STAGES, h = w.cur.h, slot = sh->slot_ring[nP & 15];
           uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
           const int chd = (g.n_coef_heads == 1) ? 0 : h;
           if (el) {
@@ -203,10 +205,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           TRACE(0, nP);
           __syncwarp();
           ++nP;
-          if (nP < n_tiles) {
-            w.advance(npg_sm, g.h_kv, p.batch);
-            slot_next = p.page_table[(int64_t)w.cur.b * p.table_stride + w.cur.j];
-          }
+          if (nP < n_tiles) w.advance(npg_sm, g.h_kv, p.batch);
           progressed = true;
         }
         if (progressed) {
@@ -236,6 +235,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           const int b = w.cur.b, h = w.cur.h, j = w.cur.j;
           const int64_t t0 = p.pos_offset + (int64_t)j * TILE_TOKENS;
           const __half* qsrc = p.q + ((int64_t)b * g.h_kv + h) * G * HEAD_DIM;
+          // the page-table entry of this tile, for the copy warp: a global load there would sit in front of every
+          // release it does, so it is fetched here, where loads are prefetched anyway
+          const int slot = p.page_table[(int64_t)b * p.table_stride + j];
           float cs[2], sn[2], x1[2][GQ], x2[2][GQ];
 #pragma unroll
           for (int jj = 0; jj < 2; ++jj) {
@@ -247,6 +249,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
               x1[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c]) : 0.f;
               x2[jj][qi] = (qi < G) ? __half2float(qsrc[qi * HEAD_DIM + c + 64]) : 0.f;
             }
+          }
+          if (lane == 0) {
+            sh->slot_ring[w.it & 15] = slot;
+            asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&sh->slot_seq[rw])), "r"(w.it + 1) : "memory");
           }
           if (!wait_or_flag(&sh->empty[s], ph, p.status, 3)) { alive = false; break; }
           __half* qr = reinterpret_cast<__half*>(qb0 + (size_t)s * T5_QB_BYTES);
