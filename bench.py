@@ -296,20 +296,21 @@ def run_ours(args, rank, world, local_rank):
     # ---- end to end through the layer-state API with host buffers: per step the new token's K/V and
     #      the query come from pinned host memory, the attention output goes back to the host ----
     n_e2e = min(args.steps, 64)
-    hq = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16).pin_memory()
-    hq.copy_(q.cpu())
-    hk = torch.randn(BATCH, H_KV, 1, D).half().pin_memory()
-    hv = torch.randn(BATCH, H_KV, 1, D).half().pin_memory()
+    # one pinned staging buffer [q | k | v] and one device mirror: a step's inputs travel in a single copy
+    nq, nk = BATCH * H_KV * G * D, BATCH * H_KV * D
+    hin = torch.empty(nq + 2 * nk, dtype=torch.float16).pin_memory()
+    hin[:nq].copy_(q.cpu().reshape(-1))
+    hin[nq:].copy_(torch.randn(2 * nk).half())
+    din = torch.empty(nq + 2 * nk, dtype=torch.float16, device=device)
+    dq = din[:nq].view(BATCH, H_KV * G, D)
+    dk = din[nq:nq + nk].view(BATCH, H_KV, 1, D)
+    dv = din[nq + nk:].view(BATCH, H_KV, 1, D)
     hout = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16).pin_memory()
-    dq, dk, dv = torch.empty_like(q), torch.empty(BATCH, H_KV, 1, D, dtype=torch.float16, device=device), \
-        torch.empty(BATCH, H_KV, 1, D, dtype=torch.float16, device=device)
-    h2d = hq.numel() * 2 + 2 * hk.numel() * 2 + hv.numel() * 2  # q, k_pre, k_post, v
+    h2d = hin.numel() * 2  # q, the new token's key (used both as page source and as window key) and value
     d2h = hout.numel() * 2
 
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
+        din.copy_(hin, non_blocking=True)
         state.append(dk, dk, dv)
         state.decode(dq, out=out)
         hout.copy_(out, non_blocking=True)

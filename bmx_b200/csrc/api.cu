@@ -69,6 +69,28 @@ static inline int grid_for(int64_t n, int block) {
 
 using namespace bmxk;
 
+namespace bmxk {
+
+constexpr int WIN_HEAD_DIM = 128;
+
+// One decode step's new token into the fp16 recent window: post-RoPE key, value and the page-source key of every
+// (sequence, head) at position t, and the window length t + 1 for every sequence.  One block per (sequence, head).
+template <typename T>
+__global__ void window_append_kernel(const T* __restrict__ k_post, const T* __restrict__ v, const T* __restrict__ k_src,
+                                     int64_t stride_seq, int64_t stride_head, __half* __restrict__ k_win,
+                                     __half* __restrict__ v_win, __half* __restrict__ k_src_win, int32_t* __restrict__ tail_len,
+                                     int h_kv, int tail_cap, int t) {
+  const int bh = blockIdx.x, b = bh / h_kv, h = bh % h_kv, c = threadIdx.x;
+  const int64_t src = (int64_t)b * stride_seq + (int64_t)h * stride_head + c;
+  const int64_t dst = ((int64_t)bh * tail_cap + t) * WIN_HEAD_DIM + c;
+  k_win[dst] = __float2half_rn(load_as_float<T>(k_post + src));
+  v_win[dst] = __float2half_rn(load_as_float<T>(v + src));
+  k_src_win[dst] = __float2half_rn(load_as_float<T>(k_src + src));
+  if (h == 0 && c == 0) tail_len[b] = t + 1;
+}
+
+}  // namespace bmxk
+
 extern "C" {
 
 int bmxk_version(void) { return 100; }
@@ -111,6 +133,31 @@ int bmxk_unpack_s4(const uint8_t* packed, int8_t* codes, int64_t rows, int64_t N
   BMXK_REQUIRE(codes && packed, "bmxk_unpack_s4: null pointer");
   unpack_s4_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(packed, codes, n);
   return check_launch("bmxk_unpack_s4");
+}
+
+int bmxk_window_append(const void* k_post, const void* v, const void* k_src, int src_dtype, int64_t stride_seq,
+                       int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len, int batch,
+                       int h_kv, int tail_cap, int t, void* stream) {
+  BMXK_REQUIRE(k_post && v && k_src && k_win && v_win && k_src_win && tail_len, "bmxk_window_append: null pointer");
+  BMXK_REQUIRE(batch >= 1 && h_kv >= 1 && tail_cap >= 1, "bmxk_window_append: batch=%d h_kv=%d tail_cap=%d", batch, h_kv, tail_cap);
+  BMXK_REQUIRE(t >= 0 && t < tail_cap, "bmxk_window_append: position %d outside the window of %d tokens", t, tail_cap);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = batch * h_kv;
+  if (src_dtype == BMXK_DTYPE_F16)
+    window_append_kernel<__half><<<grid, WIN_HEAD_DIM, 0, s>>>((const __half*)k_post, (const __half*)v, (const __half*)k_src, stride_seq,
+                                                            stride_head, (__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_len,
+                                                            h_kv, tail_cap, t);
+  else if (src_dtype == BMXK_DTYPE_BF16)
+    window_append_kernel<__nv_bfloat16><<<grid, WIN_HEAD_DIM, 0, s>>>((const __nv_bfloat16*)k_post, (const __nv_bfloat16*)v,
+                                                                   (const __nv_bfloat16*)k_src, stride_seq, stride_head, (__half*)k_win,
+                                                                   (__half*)v_win, (__half*)k_src_win, tail_len, h_kv, tail_cap, t);
+  else if (src_dtype == BMXK_DTYPE_F32)
+    window_append_kernel<float><<<grid, WIN_HEAD_DIM, 0, s>>>((const float*)k_post, (const float*)v, (const float*)k_src, stride_seq,
+                                                          stride_head, (__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_len, h_kv,
+                                                          tail_cap, t);
+  else
+    BMXK_REQUIRE(false, "bmxk_window_append: src_dtype=%d", src_dtype);
+  return check_launch("bmxk_window_append");
 }
 
 }  // extern "C"

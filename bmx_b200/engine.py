@@ -119,12 +119,8 @@ class K2bLayerState:
         total = self.committed + self.tail_len + n
         new_commit = compute_flush_schedule(total, self.W, self.page)
         if n == 1 and new_commit <= self.committed:  # the common decode step: one token into the window
-            t = self.tail_len
-            self.k_win[:, :, t] = k_post[:, :, 0]
-            self.v_win[:, :, t] = v[:, :, 0]
-            self.k_pre_win[:, :, t] = src_k[:, :, 0]
+            K.window_append(k_post, v, src_k, self.k_win, self.v_win, self.k_pre_win, self.tail_len_dev, self.tail_len)
             self.tail_len += 1
-            self.tail_len_dev.fill_(self.tail_len)
             return
         # general path: window ++ new tokens, commit whole pages, keep the rest as the new window
         t = self.tail_len

@@ -244,6 +244,21 @@ def k2b_decode_static(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, p
     return out
 
 
+def window_append(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor,
+                  k_src_win: torch.Tensor, tail_len: torch.Tensor, t: int) -> None:
+    """One new token per sequence, (batch, h_kv, 1, 128) each, into position t of the fp16 windows; one launch."""
+    _require_cuda(k_post, v, k_src, k_win, v_win, k_src_win, tail_len)
+    batch, h_kv = k_post.shape[0], k_post.shape[1]
+    srcs = [k_post, v, k_src]
+    if any(x.shape[2] != 1 or x.shape[3] != 128 for x in srcs):
+        raise ValueError("window_append: sources must be (batch, h_kv, 1, 128)")
+    if any(x.dtype != k_post.dtype or x.stride() != k_post.stride() or x.stride(3) != 1 for x in srcs):
+        srcs = [x.to(k_post.dtype).contiguous() for x in srcs]  # a few KB: one common layout for the kernel
+    k_post, v, k_src = srcs
+    call("bmxk_window_append", _ptr(k_post), _ptr(v), _ptr(k_src), _dtype_code(k_post), k_post.stride(0), k_post.stride(1),
+         _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), batch, h_kv, k_win.shape[2], int(t), _stream())
+
+
 def merge_partials(parts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """(n_parts, rows, 130) float32 partial states -> normalised (rows, 128) output (bmx split merge)."""
     _require_cuda(parts)

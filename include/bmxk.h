@@ -240,6 +240,19 @@ int bmxk_spectral_dequant_pages(const bmxk_spectral_geom* g, const void* pages, 
  * max carried in log2 units). */
 int bmxk_merge_partials(const float* parts, int n_parts, int rows, void* out, int out_dtype, void* stream);
 
+/* ---- recent window ------------------------------------------------------------------------ */
+/* One decode step's new token into the fp16 window that precedes quantization.
+ * bmx: src/bmx/cache/packed_streaming.py:582-628 (PackedStreamingLayer.update: the torch.cat of the new token
+ * onto the fp16 tail tensors; here the window is preallocated and the token is written in place).
+ * k_post (post-RoPE key, what attention over the window reads), v and k_src (the key the page quantizer will
+ * read later: pre-RoPE for k2b) are sources of dtype `src_dtype` with element (seq s, head h, channel c) at
+ * base + s*stride_seq + h*stride_head + c.  Windows are fp16 [batch][h_kv][tail_cap][128]; the token goes to
+ * position t of every (sequence, head) and tail_len[s] becomes t + 1 (device int32[batch]). */
+int bmxk_window_append(const void* k_post, const void* v, const void* k_src, int src_dtype, int64_t stride_seq,
+                       int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len, int batch,
+                       int h_kv, int tail_cap, int t, void* stream);
+
+
 /* Reads back the status word of the last decode on this workspace (host-synchronising; for
  * tests and diagnostics).  Returns BMXK_ERR_DEVICE if a bounded wait ran out. */
 int bmxk_check_workspace_status(const void* workspace, void* stream);
