@@ -83,6 +83,15 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "bmxk_spectral_dequant_pages": (c_int, [POINTER(SpectralGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_void_p]),
+    "bmxk_vblock_bytes": (c_size_t, []),
+    "bmxk_vblock_append": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_void_p, c_void_p]),
+    "bmxk_vblock_export": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "bmxk_spectral_decode_workspace_bytes": (c_size_t, [POINTER(SpectralGeom), c_int, c_int]),
+    "bmxk_spectral_decode": (c_int, [POINTER(SpectralGeom), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_void_p, c_void_p, c_float, c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_int,
+                                      c_void_p]),
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "bmxk_window_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

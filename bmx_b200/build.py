@@ -24,6 +24,8 @@ SOURCES = [
     ("k2b_decode_t5.cu", []),
     ("rtn.cu", ["-fmad=false"]),
     ("spectral.cu", ["-fmad=false"]),
+    ("spectral_decode_t5.cu", []),
+    ("value_blocks.cu", ["-fmad=false"]),
 ]
 
 

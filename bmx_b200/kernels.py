@@ -397,6 +397,19 @@ class SpectralPackDev:
         self.col_bits = self.bits.to(device).contiguous()
         self.col_off = col_off.to(device).contiguous()
         self.device = device
+        # what the fused decode kernel reads: directions in tier order (ascending bits, then ascending index),
+        # the decoder with its columns in that order as the fp16 tensor-core operand, and one word per position
+        order = torch.stack([torch.tensor(sorted(range(HEAD_DIM), key=lambda j: (int(bits[h, j]), j))) for h in range(h_kv)])
+        self.order = order
+        meta = col_off.gather(1, order) | (order.to(torch.int32) << 16) | (self.bits.gather(1, order) << 24)
+        self.meta = meta.to(torch.int32).to(device).contiguous()
+        self.set_decode_decoder(dec)
+
+    def set_decode_decoder(self, dec: torch.Tensor) -> None:
+        """Decoder used by the fused decode kernel, (h_kv, 128, 128) float32 (e.g. the int8 round trip of the
+        pack's decoder, bmx: src/bmx/cache/spectral.py:913-943); stored as fp16 with columns in tier order."""
+        idx = self.order.unsqueeze(1).expand(-1, HEAD_DIM, -1)
+        self.dec16 = dec.to(torch.float32).cpu().gather(2, idx).to(torch.float16).to(self.device).contiguous()
 
     def new_pool(self, n_slots: int) -> torch.Tensor:
         return torch.zeros(n_slots, self.geom.h_kv, self.geom.block_bytes, dtype=torch.uint8, device=self.device)
@@ -446,3 +459,62 @@ def spectral_tier_dict(pack: SpectralPackDev, codes: torch.Tensor, scales: torch
             out[f"t{b}_codes"] = q
         out[f"t{b}_scale"] = scales[cols].unsqueeze(-1)
     return out
+
+
+# ---- value-only page blocks and the fused spectral decode -----------------------------------------
+
+
+def vblock_pool(h_kv: int, n_slots: int, device) -> torch.Tensor:
+    return torch.zeros(n_slots, h_kv, int(_lib.lib().bmxk_vblock_bytes()), dtype=torch.uint8, device=device)
+
+
+def vblock_append(vpool: torch.Tensor, v: torch.Tensor, signs: torch.Tensor, codebook: torch.Tensor, slots: torch.Tensor,
+                  n_pages: int) -> None:
+    """Quantizes n_pages 128-token pages of every sequence of v (n_seq, h_kv, T, 128) into value blocks."""
+    _require_cuda(vpool, v, signs, codebook, slots)
+    h_kv = vpool.shape[1]
+    assert v.dim() == 4 and v.shape[1] == h_kv and v.shape[3] == HEAD_DIM and v.stride(3) == 1 and v.shape[2] >= 128 * n_pages
+    assert slots.dtype == torch.int32 and slots.numel() == v.shape[0] * n_pages
+    call("bmxk_vblock_append", h_kv, _ptr(v), _dtype_code(v), v.stride(0), v.stride(1), v.stride(2), _ptr(signs), _ptr(codebook),
+         _ptr(slots), v.shape[0], n_pages, _ptr(vpool), _stream())
+
+
+def vblock_export(vpool: torch.Tensor, slots: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Value blocks -> bmx's (v_idx_packed uint8 (n, 128, C/4), v_norm fp16 (n, 128, h_kv))."""
+    h_kv, n, dev = vpool.shape[1], slots.numel(), vpool.device
+    idx = torch.empty(n, 128, h_kv * HEAD_DIM // 4, dtype=torch.uint8, device=dev)
+    norm = torch.empty(n, 128, h_kv, dtype=torch.float16, device=dev)
+    call("bmxk_vblock_export", h_kv, _ptr(vpool), _ptr(slots), n, _ptr(idx), _ptr(norm), _stream())
+    return idx, norm
+
+
+def spectral_decode_workspace(pack: SpectralPackDev, n_q_groups: int, batch: int) -> torch.Tensor:
+    n = int(_lib.lib().bmxk_spectral_decode_workspace_bytes(ctypes.byref(pack.geom), n_q_groups, batch))
+    return torch.zeros(n, dtype=torch.uint8, device=pack.device)
+
+
+def spectral_decode(pack: SpectralPackDev, n_q_groups: int, kpool: torch.Tensor, vpool: torch.Tensor, q: torch.Tensor,
+                    page_table: torch.Tensor, n_pages: torch.Tensor, max_pages: int, rope_cos: torch.Tensor,
+                    rope_sin: torch.Tensor, k_tail: torch.Tensor | None, v_tail: torch.Tensor | None,
+                    tail_len: torch.Tensor | None, v_lut: torch.Tensor, signs: torch.Tensor, sm_scale: float,
+                    workspace: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+                    pos_offset: int = 0, phases: int = 3) -> torch.Tensor:
+    """One decode step for q (batch, heads, 128) fp16 over spectral key pages + value blocks + the fp16 window."""
+    g = pack.geom
+    _require_cuda(q, kpool, vpool, page_table, n_pages, workspace)
+    batch = q.shape[0]
+    assert q.dtype == torch.float16 and q.is_contiguous() and q.shape[1:] == (g.h_kv * n_q_groups, HEAD_DIM)
+    assert page_table.dtype == torch.int32 and n_pages.dtype == torch.int32 and page_table.dim() == 2
+    assert rope_cos.dtype == torch.float16 and rope_sin.dtype == torch.float16
+    tail_cap = 0 if k_tail is None else k_tail.shape[2]
+    if k_tail is not None:
+        assert k_tail.dtype == torch.float16 and k_tail.is_contiguous() and v_tail.is_contiguous()
+        assert k_tail.shape == (batch, g.h_kv, tail_cap, HEAD_DIM) == v_tail.shape
+    if out is None and partial_out is None:
+        out = torch.empty(batch, g.h_kv * n_q_groups, HEAD_DIM, dtype=torch.float16, device=q.device)
+    out_code = DTYPE_F16 if out is None else _dtype_code(out)
+    call("bmxk_spectral_decode", ctypes.byref(g), n_q_groups, _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(pack.dec16), _ptr(pack.meta),
+         _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, max_pages, _ptr(rope_cos), _ptr(rope_sin), pos_offset,
+         _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut), _ptr(signs), ctypes.c_float(sm_scale),
+         _ptr(workspace), workspace.numel(), _ptr(out), out_code, _ptr(partial_out), phases, _stream())
+    return out if partial_out is None else partial_out

@@ -235,6 +235,38 @@ int bmxk_spectral_dequant_pages(const bmxk_spectral_geom* g, const void* pages, 
                                 const int32_t* col_bits, const int32_t* col_off, const int32_t* slots, int n,
                                 int8_t* codes, float* scales, float* k_out, void* stream);
 
+/* Value-only page blocks, for caches whose keys live in a pool of their own (the spectral codec): the
+ * per-head Hadamard + 2-bit Lloyd value codec of bmx (`turboquant_mse_perhead`, src/bmx/cache/codecs.py:616-636;
+ * called per page from PackedStreamingLayer._pack_v_block, src/bmx/cache/packed_streaming.py:544-580).
+ * One block per (slot, head), bmxk_vblock_bytes() = 4352 bytes: 2-bit codes of 128 tokens x 128 channels, then
+ * 128 fp16 norms, ordered as the value part of a k2b page block of layout 1.  v: element (seq s, head h, token t,
+ * channel c) at base + s*stride_seq + h*stride_head + t*stride_tok + c; slots: int32 (n_seq * n_pages). */
+size_t bmxk_vblock_bytes(void);
+int bmxk_vblock_append(int h_kv, const void* v, int src_dtype, int64_t stride_seq, int64_t stride_head, int64_t stride_tok,
+                       const float* signs, const float* codebook, const int32_t* slots, int n_seq, int n_pages, void* vpages,
+                       void* stream);
+/* Blocks -> bmx's stacked containers: v_idx_packed uint8 (n, 128, h_kv*128/4), v_norm fp16 (n, 128, h_kv)
+ * (bmx: build_kv_stacked_k2b, src/bmx/cache/triton_dequant_attention.py:1118-1229, pack_v=True). */
+int bmxk_vblock_export(int h_kv, const void* vpages, const int32_t* slots, int n, uint8_t* v_idx_packed, void* v_norm,
+                       void* stream);
+
+/* One decode step over a spectral key pool + a value-block pool + the fp16 window, fused: the tier codes are
+ * dequantized on chip, decoded (Y_hat @ dec^T on tcgen05.mma), rotated and attended without K_hat ever reaching
+ * HBM.  bmx runs this codec pair through its chunked path (src/bmx/cache/packed_streaming.py:832-1064 attend ->
+ * src/bmx/cache/chunked_attention.py:478-530 with _dequant_block :52-145 and spectral_dequant_packed,
+ * src/bmx/cache/spectral.py:812-839); this entry point replaces that call for decode.
+ * g: the key pool's geometry (page must be 128).  dec_f16: (h_kv, 128, 128) fp16, dec_f16[h][c][k] = dec[h][c][d_k]
+ * with d_k the k-th direction of head h in tier order (ascending bits, then ascending index).  meta: int32
+ * (h_kv, 128), meta[h][k] = col_off[h][d_k] | d_k << 16 | bits[h][d_k] << 24.  Everything else as in
+ * bmxk_k2b_decode; the workspace size comes from bmxk_spectral_decode_workspace_bytes. */
+size_t bmxk_spectral_decode_workspace_bytes(const bmxk_spectral_geom* g, int n_q_groups, int batch);
+int bmxk_spectral_decode(const bmxk_spectral_geom* g, int n_q_groups, const void* q, const void* kpages, const void* vpages,
+                         const void* dec_f16, const int32_t* meta, const int32_t* page_table, int table_stride,
+                         const int32_t* n_pages, int batch, int max_pages, const void* rope_cos, const void* rope_sin,
+                         int64_t pos_offset, const void* k_tail, const void* v_tail, const int32_t* tail_len, int tail_cap,
+                         const uint32_t* v_lut, const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
+                         void* out, int out_dtype, float* partial_out, int phases, void* stream);
+
 /* Merges n_parts partial states (n_parts, rows, 130) float32 -> out (rows, 128).
  * bmx: src/bmx/cache/triton_dequant_attention.py:409-461 _fused_merge_kernel (same formula,
  * max carried in log2 units). */
