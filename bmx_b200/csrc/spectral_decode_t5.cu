@@ -22,6 +22,10 @@
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
+#ifndef S5_SKIP
+#define S5_SKIP 0  // diagnostic builds only: bit mask of phases to leave out (results are then wrong)
+#endif
+
 namespace bmxk {
 
 namespace {
@@ -335,7 +339,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           const uint64_t da = d_y + (uint64_t)(b * (OPER_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[sA] * (OPER_BYTES >> 4));
           if (el) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+            for (int ks = 0; ks < ((S5_SKIP & 8) ? 1 : 8); ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
           __syncwarp();
@@ -373,7 +377,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
       tc5::fence_after();
 #pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
+      for (int kk = 0; kk < ((S5_SKIP & 2) ? 0 : 2); ++kk) {
         const int k = k0 + kk;
         uint32_t dl[8], dh[8], out[16];
         tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
@@ -546,7 +550,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < ((S5_SKIP & 4) ? 0 : 2); ++cc) {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
@@ -598,7 +602,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
       const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
 #pragma unroll 1
-      for (int oo = 0; oo < 4; ++oo) {
+      for (int oo = 0; oo < ((S5_SKIP & 1) ? 0 : 4); ++oo) {
         const int o = 4 * oo + wd;
         const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
         const uint8_t* rowp = kb + off;

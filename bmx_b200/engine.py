@@ -157,3 +157,101 @@ class K2bLayerState:
         g = self.geom
         per_unit = K.page_block_bytes(g) / g.page + K.coef_block_bytes(g) * g.n_coef_heads / (g.page * g.h_kv)
         return int(self.batch * g.h_kv * self.committed * per_unit)
+
+
+class SpectralLayerState(K2bLayerState):
+    """Same state for the K4 spectral key codec (per-head packs): keys go to a spectral page pool, values to a
+    pool of value-only blocks, and a decode step is the fused spectral kernel plus the merge kernel.
+
+    bmx keeps such a layer as per-page dicts of tier containers and decodes it through its chunked path
+    (bmx: src/bmx/cache/packed_streaming.py:491-511, 1024-1034); the flush schedule, the fp16 window and
+    pre-RoPE quantization are the same as for k2b.
+    """
+
+    def __init__(self, pack: "K.SpectralPackDev", n_q_groups: int, batch: int, max_tokens: int, recent_window: int, device,
+                 rope_cos: torch.Tensor, rope_sin: torch.Tensor, *, codebook=None, v_seed: int = 0):
+        assert rope_cos.dtype == torch.float16 and rope_cos.shape[1] == HEAD_DIM and rope_cos.shape[0] >= 128
+        assert pack.geom.page == 128, "the fused spectral decode reads 128-token pages"
+        self.pack, self.n_q_groups, self.batch, self.device = pack, n_q_groups, batch, torch.device(device)
+        self.geom = pack.geom
+        self.page, self.W, self.pre_rope = 128, recent_window, True
+        self.max_pages = max(1, math.ceil(max_tokens / self.page))
+        h_kv = pack.geom.h_kv
+        self.kpool = pack.new_pool(batch * self.max_pages)
+        self.vpool = K.vblock_pool(h_kv, batch * self.max_pages, self.device)
+        self.page_table = torch.arange(batch * self.max_pages, dtype=torch.int32, device=self.device).view(batch, -1)
+        self.n_pages_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_len_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_cap = recent_window + self.page
+        shape = (batch, h_kv, self.tail_cap, HEAD_DIM)
+        self.k_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.v_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.k_pre_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.rope_cos, self.rope_sin = rope_cos, rope_sin
+        cb = tuple(codebook) if codebook is not None else K.GAUSSIAN_CODEBOOK[2]
+        self.codebook = torch.tensor(cb, dtype=torch.float32, device=self.device)
+        self.v_lut = K.v_lut_tensor(cb, self.device)
+        self.signs = K.hadamard_signs(HEAD_DIM, v_seed).to(self.device)
+        self.basis_f32 = self.basis_f16 = None  # the pack is fitted offline: nothing is frozen at the first flush
+        self.workspace = K.spectral_decode_workspace(pack, n_q_groups, batch)
+        self.committed = 0
+        self.tail_len = 0
+        self.sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+
+    def ensure_pages(self, n_more: int) -> None:
+        need = self.committed // self.page + n_more
+        if need <= self.max_pages:
+            return
+        new_max = max(need, 2 * self.max_pages)
+        old_k, old_v, old_table, used = self.kpool, self.vpool, self.page_table, self.committed // self.page
+        self.kpool = self.pack.new_pool(self.batch * new_max)
+        self.vpool = K.vblock_pool(self.geom.h_kv, self.batch * new_max, self.device)
+        self.page_table = torch.arange(self.batch * new_max, dtype=torch.int32, device=self.device).view(self.batch, -1)
+        if used:
+            src = old_table[:, :used].reshape(-1).long()
+            dst = self.page_table[:, :used].reshape(-1).long()
+            self.kpool[dst] = old_k[src]
+            self.vpool[dst] = old_v[src]
+        self.max_pages = new_max
+
+    def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
+        if k_src.stride(3) != 1:
+            k_src = k_src.contiguous()
+        if v_src.stride(3) != 1:
+            v_src = v_src.contiguous()
+        self.ensure_pages(n_pages)
+        p0 = self.committed // self.page
+        slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
+        K.spectral_append(self.pack, self.kpool, k_src, slots, n_pages)
+        K.vblock_append(self.vpool, v_src, self.signs, self.codebook, slots, n_pages)
+        self.committed += n_pages * self.page
+        self.n_pages_dev.fill_(self.committed // self.page)
+
+    def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+               phases: int = 3) -> torch.Tensor:
+        max_pages = self.max_pages if self.committed else 0
+        return K.spectral_decode(self.pack, self.n_q_groups, self.kpool, self.vpool, q, self.page_table, self.n_pages_dev,
+                                 max_pages, self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
+                                 self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, phases=phases)
+
+    def dense_pages(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """All committed pages dequantized: pre-RoPE keys and values, float32 (batch, h_kv, committed, 128).
+        Keys by the page dequantizer kernel; values from the exported codes (codebook level, inverse rotation,
+        norm), as bmx: src/bmx/cache/codecs.py:639-649."""
+        n_pg, h_kv = self.committed // self.page, self.geom.h_kv
+        slots = self.page_table[:, :n_pg].contiguous().view(-1)
+        kd = K.spectral_dequant_pages(self.pack, self.kpool, slots, want_codes=False, want_k=True)["k"]
+        shp = (self.batch, n_pg * self.page, h_kv, HEAD_DIM)
+        kd = kd.view(*shp).permute(0, 2, 1, 3)
+        idx, norm = K.vblock_export(self.vpool, slots)
+        codes = torch.stack([(idx >> (2 * k)) & 3 for k in range(4)], -1).reshape(idx.shape[0], 128, h_kv, HEAD_DIM).long()
+        lev = self.codebook[codes] / math.sqrt(HEAD_DIM)
+        H = torch.tensor([[1.0]], device=self.device)
+        while H.shape[0] < HEAD_DIM:
+            H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+        vd = (lev @ (H / math.sqrt(HEAD_DIM))) * self.signs * norm.float().unsqueeze(-1)
+        vd = vd.view(self.batch, n_pg * self.page, h_kv, HEAD_DIM).permute(0, 2, 1, 3)
+        return kd, vd
+
+    def packed_bytes(self) -> int:
+        return int(self.batch * self.geom.h_kv * (self.committed // self.page) * (self.geom.block_bytes + self.vpool.shape[2]))

@@ -20,9 +20,9 @@ from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS, sdpa_mask
 from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
 from . import kernels as K
-from .engine import K2bLayerState
+from .engine import K2bLayerState, SpectralLayerState
 from .rope import apply_rope, rope_tables_from_config
-from .schedule import codec_bpe, compute_flush_schedule
+from .schedule import codec_bpe, compute_flush_schedule, scale_bits
 from .specs import FUSED_PAIRS, CacheCodecSpec
 
 _ATTN_NAME = "chunked_dequant"
@@ -93,6 +93,16 @@ ALL_ATTENTION_FUNCTIONS.register(_ATTN_NAME, chunked_attention_forward)
 ALL_MASK_ATTENTION_FUNCTIONS.register(_ATTN_NAME, sdpa_mask)
 
 
+class SpectralHeadPacks:
+    """Per-head K4 spectral packs of one layer: enc, dec (h_kv, 128, 128) float32 with Y = M @ enc[h] and
+    M_hat = Y_hat @ dec[h].T, bits (h_kv, 128) from {0, 2, 3, 4, 5, 6, 8}, group = token group of the scales
+    (the fields of bmx's SpectralPack that the codec reads, src/bmx/cache/spectral.py:174-220, one per head)."""
+
+    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, group: int = 64):
+        assert enc.shape == dec.shape and enc.dim() == 3 and enc.shape[1:] == (HEAD_DIM, HEAD_DIM) and bits.shape == enc.shape[:2]
+        self.enc, self.dec, self.bits, self.group = enc.float(), dec.float(), bits.to(torch.int32), int(group)
+
+
 class PackedStreamingLayer(DynamicLayer):
     """Per-layer packed cache: page pool + frozen key basis + fp16 recent window."""
 
@@ -102,17 +112,24 @@ class PackedStreamingLayer(DynamicLayer):
         self.k_spec, self.v_spec, self.model_config = k_spec, v_spec, model_config
         self.recent_window, self.pack_v, self.pack_k = recent_window, pack_v, pack_k
         kind = FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
-        if kind != "k2b":
+        if kind not in ("k2b", "spectral"):
             raise NotImplementedError(
                 f"no CUDA decode kernel for arms K={k_spec.arm!r} / V={v_spec.arm!r} in PackedStreamingLayer; "
-                "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph'). There is no CPU fallback.")
+                "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph') and spectral + "
+                "turboquant_mse_perhead with per-head packs. There is no CPU fallback.")
+        if kind == "spectral" and pack is None:
+            raise NotImplementedError(
+                "the spectral key arm needs per-head packs (enc, dec, bits of shape (h_kv, 128, 128) / (h_kv, 128)) passed as "
+                "PackedStreamingCache(..., spectral_packs={layer: SpectralHeadPacks}); pack files holding one encoder over "
+                "all heads have no fused kernel")
+        self._kind, self._pack = kind, pack
         tc = resolve_text_config(model_config)
         self._h_kv = getattr(tc, "num_key_value_heads", tc.num_attention_heads)
         self._d_head = getattr(tc, "head_dim", None) or tc.hidden_size // tc.num_attention_heads
         self._n_q_groups = tc.num_attention_heads // self._h_kv
         if self._d_head != HEAD_DIM:
             raise NotImplementedError(f"head_dim={self._d_head}: the bmxk kernels are built for head_dim 128")
-        self._g = k_spec.group
+        self._g = k_spec.group if kind == "k2b" else pack.group  # spectral: the pack's own fitted group
         self._page = max(self._g, (128 // self._g) * self._g) if self._g > 1 else 128
         self._k_pre: torch.Tensor | None = None   # pre-RoPE keys captured by the hook since the last update
         self._committed_S_q = 0
@@ -135,12 +152,18 @@ class PackedStreamingLayer(DynamicLayer):
     def _ensure_state(self, key_states: torch.Tensor) -> K2bLayerState:
         if self._state is None:
             self._batch = key_states.shape[0]
-            rank = self.k_spec.rank
-            geom = K.k2b_geom(self._h_kv, self._n_q_groups, self._page, rank, self.k_spec.group, 1, self.k_spec.bits,
-                              self.v_spec.bits)
             cos, sin = shared_rope(self.model_config, 4096, key_states.device)
-            self._state = K2bLayerState(geom, self._batch, 4096, self.recent_window, key_states.device, cos, sin,
-                                        v_seed=self.v_spec.seed, pre_rope=self.k_spec.pre_rope)
+            if self._kind == "spectral":
+                assert self.k_spec.pre_rope, "the spectral arm quantizes pre-RoPE keys"
+                dev_pack = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g,
+                                             device=key_states.device)
+                self._state = SpectralLayerState(dev_pack, self._n_q_groups, self._batch, 4096, self.recent_window,
+                                                 key_states.device, cos, sin, v_seed=self.v_spec.seed)
+            else:
+                geom = K.k2b_geom(self._h_kv, self._n_q_groups, self._page, self.k_spec.rank, self.k_spec.group, 1,
+                                  self.k_spec.bits, self.v_spec.bits)
+                self._state = K2bLayerState(geom, self._batch, 4096, self.recent_window, key_states.device, cos, sin,
+                                            v_seed=self.v_spec.seed, pre_rope=self.k_spec.pre_rope)
             self.dtype, self.device, self.is_initialized = key_states.dtype, key_states.device, True
         return self._state
 
@@ -166,8 +189,13 @@ class PackedStreamingLayer(DynamicLayer):
         C = self._h_kv * self._d_head
         for pg0 in range(before, st.committed, self._page):
             entries = self._page * C
-            self._quant_bits_k += codec_bpe(self.k_spec.arm, bits=self.k_spec.bits, group=self.k_spec.group,
-                                            rank=self.k_spec.rank, S=self._page, C=C) * entries
+            if self._kind == "spectral":  # mean bits + scales of the directions that carry any (bmx: spectral.py:602-615)
+                bits = self._pack.bits.float()
+                bpe_page = float(bits.mean()) + scale_bits(self._g) * float((bits > 0).float().mean())
+            else:
+                bpe_page = codec_bpe(self.k_spec.arm, bits=self.k_spec.bits, group=self.k_spec.group, rank=self.k_spec.rank,
+                                     S=self._page, C=C)
+            self._quant_bits_k += bpe_page * entries
             self._quant_bits_v += codec_bpe(self.v_spec.arm, bits=self.v_spec.bits, group=self.v_spec.group,
                                             rank=0, S=self._page, C=C, h_heads=self._h_kv) * entries
             self._k_blocks.append((pg0 // self._page, pg0, pg0 + self._page))
@@ -191,11 +219,14 @@ class PackedStreamingLayer(DynamicLayer):
         n_pg = st.committed // self._page
         parts_k, parts_v = [], []
         if n_pg:
-            slots = st.page_table[:, :n_pg].contiguous().view(-1)
-            kd, vd = K.k2b_dequant_pages(st.pool, slots, st.basis_f16, st.signs, st.codebook)
-            shp = (st.batch, n_pg * self._page, self._h_kv, self._d_head)
-            kd = kd.view(*shp).permute(0, 2, 1, 3)
-            vd = vd.view(*shp).permute(0, 2, 1, 3)
+            if self._kind == "spectral":
+                kd, vd = st.dense_pages()
+            else:
+                slots = st.page_table[:, :n_pg].contiguous().view(-1)
+                kd, vd = K.k2b_dequant_pages(st.pool, slots, st.basis_f16, st.signs, st.codebook)
+                shp = (st.batch, n_pg * self._page, self._h_kv, self._d_head)
+                kd = kd.view(*shp).permute(0, 2, 1, 3)
+                vd = vd.view(*shp).permute(0, 2, 1, 3)
             if self.k_spec.pre_rope:
                 kd = apply_rope(kd.to(dtype), st.rope_cos[: st.committed].to(dtype), st.rope_sin[: st.committed].to(dtype))
             parts_k.append(kd.to(dtype))
@@ -234,9 +265,8 @@ class PackedStreamingCache(Cache):
     """
 
     def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32,
-                 pack_v: bool = True, pack_k: bool = True):
-        if k_spec.arm == "spectral":
-            raise NotImplementedError("the spectral key arm has no CUDA decode kernel yet; there is no CPU fallback")
+                 pack_v: bool = True, pack_k: bool = True, spectral_packs: dict | None = None):
+        self._packs = dict(spectral_packs or {})
         wself = weakref.proxy(self)  # a strong capture would make a cycle that keeps the page pools alive
 
         def _make_layer():
@@ -252,7 +282,14 @@ class PackedStreamingCache(Cache):
         self._model = None
 
     def _pack_for_layer(self, i: int):
-        return None
+        """Layer i's spectral packs (bmx: src/bmx/cache/packed_streaming.py:1144-1148); None for other arms."""
+        if self.k_spec.arm != "spectral":
+            return None
+        if i not in self._packs:
+            raise NotImplementedError(
+                f"no spectral pack for layer {i}: pass spectral_packs={{layer: SpectralHeadPacks}} (per-head packs); loading "
+                "bmx pack files (one encoder over all heads) is not supported")
+        return self._packs[i]
 
     def bits_per_entry(self):
         """(bpe_k, bpe_v): blended bits per entry averaged across layers (bmx: streaming.py:154-260)."""

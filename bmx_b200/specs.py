@@ -32,4 +32,5 @@ FUSED_PAIRS = {
     ("lowrank_rtn_channel", "turboquant_mse_perhead"): "k2b",
     ("rtn_token", "rtn_token"): "rtn",
     ("rtn_channel", "rtn_token"): "rtn",
+    ("spectral", "turboquant_mse_perhead"): "spectral",
 }

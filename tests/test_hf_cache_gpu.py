@@ -112,3 +112,73 @@ def test_streaming_twin_matches_packed_cache_tokens():
     assert float((la - lb).abs().max()) < 5e-2
     k, v = cache.reconstruct_layer(0)
     assert k.shape == v.shape == (1, 2, 240, 128)
+
+
+def _spectral_packs(model, seed=3):
+    """Seeded per-head packs for every layer: orthogonal encoders (decoder = encoder), bits by direction index."""
+    from bmx_b200.packed_streaming import SpectralHeadPacks
+
+    cfg = model.config
+    g = torch.Generator().manual_seed(seed)
+    packs = {}
+    tiers = [8] * 6 + [6] * 10 + [5] * 12 + [4] * 20 + [3] * 28 + [2] * 36 + [0] * 16
+    for i in range(cfg.num_hidden_layers):
+        enc, bits = [], []
+        for h in range(cfg.num_key_value_heads):
+            Q, _ = torch.linalg.qr(torch.randn(128, 128, generator=g))
+            enc.append(Q)
+            bits.append(torch.tensor(tiers, dtype=torch.int32)[torch.randperm(128, generator=g)])
+        enc = torch.stack(enc)
+        packs[i] = SpectralHeadPacks(enc, enc.clone(), torch.stack(bits), group=64)
+    return packs
+
+
+def test_spectral_cache_decode_kernel_vs_dense_path_under_hf_model():
+    """The fused spectral decode kernel against dequantize-all + SDPA on the same pages, 64 teacher-forced steps."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.packed_streaming import PackedStreamingCache, PackedStreamingLayer
+    from bmx_b200.specs import CacheCodecSpec
+
+    dev = torch.device("cuda:0")
+    model = _tiny_llama(dev)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 256, (2, 300 + 64), generator=g).to(dev)
+    k_spec = CacheCodecSpec(arm="spectral", pre_rope=True, group=64)
+    v_spec = CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)
+    packs = _spectral_packs(model)
+
+    def run(force_dense):
+        cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32, spectral_packs=packs)
+        logits = []
+        orig = PackedStreamingLayer.attend
+        if force_dense:
+            def dense_attend(self, q, scaling, is_causal=False, attention_mask=None):
+                return orig(self, q, scaling, is_causal=True, attention_mask=attention_mask)
+            PackedStreamingLayer.attend = dense_attend
+        try:
+            with cache.attach(model), torch.no_grad():
+                out = model(ids[:, :300], past_key_values=cache, use_cache=True)
+                logits.append(out.logits[:, -1].float())
+                for t in range(300, ids.shape[1]):
+                    out = model(ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+                    logits.append(out.logits[:, -1].float())
+        finally:
+            PackedStreamingLayer.attend = orig
+        return torch.stack(logits, 1), cache
+
+    la, cache = run(False)
+    lb, _ = run(True)
+    layer = cache.layers[0]
+    assert layer._committed_S_q == 256 and layer.get_seq_length() == 364 and layer.keys.shape[2] == 108
+    bpe_k, bpe_v = cache.bits_per_entry()
+    assert 3.0 < bpe_k < 16.0 and 2.0 < bpe_v < 16.0
+    diff = float((la - lb).abs().max())
+    assert diff < 5e-3
+    # a random-init model's top two logits are often closer than that; count the flips where they are not
+    top2 = lb.topk(2, dim=-1).values
+    decided = (top2[..., 0] - top2[..., 1]) > 4 * diff
+    flips = int(((la.argmax(-1) != lb.argmax(-1)) & decided).sum())
+    assert int(decided.sum()) >= la.shape[1] and flips == 0, f"{flips} argmax flips (max logit diff {diff:.3e})"
+    with pytest.raises(NotImplementedError):
+        PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)._pack_for_layer(0)
