@@ -30,11 +30,19 @@ namespace bmxk {
 
 namespace {
 
-constexpr int S5_THREADS = 896;  // warps 0-7 key, 8-15 softmax (two sets), 16-19 value, 20-23 dequant, 24 copy + U3, 25 U1 + U2, 26-27 query rotation
+#ifndef S5_DQ_WARPS
+#define S5_DQ_WARPS 8
+#endif
+constexpr int DQ_WARPS = S5_DQ_WARPS;   // dequant warps: 4 or 8
+constexpr int SVC0 = 20 + DQ_WARPS;     // first of the four service warps: copy + U3, U1 + U2, two query rotation warps
+constexpr int S5_THREADS = (SVC0 + 4) * 32;  // warps 0-7 key, 8-15 softmax (two sets), 16-19 value, 20.. dequant, then service
 constexpr int S5_MAX_STAGES = 8;
-// Registers per thread after each role resizes itself; the pool is what the launch handed out (72 x 896).
-constexpr int REG_LAUNCH = 72, REG_KEY = 96, REG_SOFTMAX = 56, REG_VALUE = 56, REG_DEQUANT = 88, REG_SERVICE = 56;
-static_assert(8 * REG_KEY + 8 * REG_SOFTMAX + 4 * REG_VALUE + 4 * REG_DEQUANT + 4 * REG_SERVICE <= 28 * REG_LAUNCH,
+// Registers per thread after each role resizes itself; the pool is what the launch handed out.
+constexpr int REG_LAUNCH = (DQ_WARPS == 4) ? 72 : 64, REG_KEY = (DQ_WARPS == 4) ? 96 : 88, REG_SOFTMAX = (DQ_WARPS == 4) ? 56 : 48;
+constexpr int REG_VALUE = 56, REG_DEQUANT = (DQ_WARPS == 4) ? 88 : 64, REG_SERVICE = 56;
+static_assert(DQ_WARPS == 4 || DQ_WARPS == 8, "dequant warps come in groups of four");
+static_assert(REG_LAUNCH * S5_THREADS <= 65536, "launch registers exceed the register file");
+static_assert(8 * REG_KEY + 8 * REG_SOFTMAX + 4 * REG_VALUE + DQ_WARPS * REG_DEQUANT + 4 * REG_SERVICE <= (SVC0 + 4) * REG_LAUNCH,
               "register split exceeds the CTA's pool");
 constexpr int QB_BYTES = 4096;        // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
 constexpr int OPER_BYTES = 128 * 128 * 2;  // Y_hat / decoder operand: 128 rows x 128 fp16
@@ -48,7 +56,7 @@ struct S5Smem {
   uint32_t tmem_base;
   volatile int released;
   int bcnt, ccnt;
-  int kcnt[2], pcnt[2], vcnt[2], ycnt[2];  // arrivals of key (8 per tile) / softmax (4) / value (4) / dequant (4) warps on buffer b, never reset
+  int kcnt[2], pcnt[2], vcnt[2], ycnt[2];  // arrivals of key (8 per tile) / softmax (4) / value (4) / dequant (DQ_WARPS) warps on buffer b, never reset
   volatile int slot_ring[16];
   int slot_seq[2];
   volatile int bsel[S5_MAX_STAGES], first[S5_MAX_STAGES];
@@ -102,8 +110,9 @@ __device__ __forceinline__ void named_bar(int id, int n) { asm volatile("bar.syn
 // Four 8 x 8 fp16 blocks, each stored transposed: a thread passes (column lane / 4; rows 2 (lane % 4), + 1) of
 // block m in r[m]; lane l supplies the address of row l % 8 of block l / 8.
 __device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, const uint32_t (&r)[4]) {
-  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
-               : "memory");
+  // no memory clobber: nothing the compiler can see reads these bytes, and the loads of the next pieces should
+  // be free to move above it; the fence + release that publish the buffer carry the clobber
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]));
 }
 
 }  // namespace
@@ -148,7 +157,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
     sh->released = 0, sh->bcnt = 0, sh->ccnt = 0, sh->slot_seq[0] = sh->slot_seq[1] = 0;
     fence_barrier_init();
   }
-  if (warp == 25) {
+  if (warp == SVC0 + 1) {
     tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
     tc5::relinquish();
   }
@@ -161,9 +170,9 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
   Walker w;
   w.init(cum, npg_sm, f_begin, h_kv);
 
-  if (warp >= 24) {
+  if (warp >= SVC0) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
-    if (warp == 24) {
+    if (warp == SVC0) {
       // ===================== copy + U3 warp =====================
       constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
@@ -221,12 +230,12 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           }
         }
       }
-    } else if (warp >= 26) {
+    } else if (warp >= SVC0 + 2) {
       // ===================== query rotation warps: tiles of parity rw =====================
       // q_rot = R(-t0) q * scale as the B operand of U2, in the K order the key warps produce: position
       // 32k + e holds channel 16k + e (e < 16) or 64 + 16k + (e - 16).  The warp that meets the first tile of
       // a (sequence, head) range also lays out that head's decoder as the B operand of U1.
-      const int rw = warp - 26;
+      const int rw = warp - (SVC0 + 2);
       int s = 0;
       uint32_t ph = 1;
       int prev_seg = -1, first_cur = 0, first_prev = 0;
@@ -332,7 +341,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           progressed = true;
         }
         // ---- A ----
-        if (nA < n_tiles && nA < nB + 2 && yc >= 4 * ((nA >> 1) + 1) &&
+        if (nA < n_tiles && nA < nB + 2 && yc >= DQ_WARPS * ((nA >> 1) + 1) &&
             (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
           tc5::fence_after();
           const int b = nA & 1;
@@ -580,21 +589,29 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
     }
   } else {
     // ===================== dequant warps: tier codes -> fp16 Y_hat, the A operand of U1 =====================
-    // Warp wd takes the direction octets wd, wd + 4, wd + 8, wd + 12 (positions in tier order).  Lane = (direction
+    // Warp wd takes the direction octets wd, wd + DQ_WARPS, ... (positions in tier order).  Lane = (direction
     // lane / 4 of the octet, token pair q = lane % 4): for every 8-token block B it produces the half2 of tokens
     // 8B + 2q, 8B + 2q + 1 of its direction, which is exactly what a transposed stmatrix wants from it.  Four
-    // blocks (32 tokens, one 16 / 8 / 32-byte piece of the direction's row) go out per stmatrix.
+    // blocks (32 tokens, one 8 / 16 / 32-byte piece of the direction's row) go out per stmatrix.
+    // A half2 costs four instructions whatever the tier: a byte permute drops the thread's code byte(s) under the
+    // fp16 exponent of 1024 in both halves, one LOP3 masks each half down to its field and flips two's-complement
+    // sign bits, an exact subtraction removes 1024 and the field's offset (times the field's position in the byte),
+    // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
+    // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
+    // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_DEQUANT));
+    constexpr int OCT = 16 / DQ_WARPS;
     const int wd = warp - 20, q = lane & 3, dsub = lane >> 2;
     const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
     const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
+    const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
     int s = 0;
     uint32_t fp = 0;
     for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
       const int n = w.it, b = n & 1, h = w.cur.h;
-      int meta[4];
+      int meta[OCT];
 #pragma unroll
-      for (int oo = 0; oo < 4; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (4 * oo + wd) + dsub);
+      for (int oo = 0; oo < OCT; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (DQ_WARPS * oo + wd) + dsub);
       if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
       // the buffer still feeds U1 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
@@ -602,56 +619,44 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
       const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
 #pragma unroll 1
-      for (int oo = 0; oo < ((S5_SKIP & 1) ? 0 : 4); ++oo) {
-        const int o = 4 * oo + wd;
+      for (int oo = 0; oo < ((S5_SKIP & 1) ? 0 : OCT); ++oo) {
+        const int o = DQ_WARPS * oo + wd;
         const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
-        const uint8_t* rowp = kb + off;
-        float sc[4];
+        // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
+        const bool w2 = (bits == 2), w8 = (bits >= 5);
+        const uint32_t piece = w2 ? 8u : (w8 ? 32u : 16u);
+        // word (byte offset inside the piece) and byte selector of block m = 0..3 of a piece
+        //   2-bit: byte 2 (m % 2) + q / 2 of word m / 2;  4-bit: byte q of word m;  8-bit: bytes 2 (q % 2), + 1 of word 2 m + q / 2
+        const uint32_t wstep = w2 ? 2u : (w8 ? 8u : 4u);            // byte offset of block m's word = (m * wstep rounded down to 4) + wbase
+        const uint32_t wbase = w8 ? 4u * (uint32_t)(q >> 1) : 0u;
+        const uint32_t byte_e = w2 ? (uint32_t)(q >> 1) : (w8 ? 2u * (uint32_t)(q & 1) : (uint32_t)q);   // source byte that lands in the low half
+        const uint32_t hi_inc = w8 ? 1u : 0u;                                                              // the high half takes the next byte (8-bit) or the same one
+        const uint32_t sel_e = 0x4040u | byte_e | ((byte_e + hi_inc) << 8);
+        const uint32_t sel_o = w2 ? sel_e + 0x0202u : sel_e;       // 2-bit: odd blocks sit two bytes further in the same word
+        const uint32_t mask = w2 ? (((0xFF00u | (0x3u << (a2 + 2))) << 16) | (0xFF00u | (0x3u << a2))) : (w8 ? 0xFFFFFFFFu : 0xFFF0FF0Fu);
+        const uint32_t X2 = (bits == 3) ? 0x00800008u : (w8 ? 0x00800080u : 0u);   // two's-complement fields: flip the sign bit
+        // field offset still to subtract (times the field's position) and the position itself
+        const float blo = w2 ? (float)(2 << a2) : (w8 ? 128.f : 8.f), bhi = w2 ? (float)(2 << (a2 + 2)) : 128.f;
+        const float plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
+        const __half2 bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
+        const uint8_t* rowp = kb + off + wbase;
+        __half2 s2c[4];
 #pragma unroll
-        for (int gi = 0; gi < 4; ++gi) sc[gi] = (gi < ngrp && bits) ? scales[d * ngrp + gi] : 0.f;
-        // field -> integer: 2- and 4-bit tiers are offset binary, the 3-bit tier a two's-complement nibble, wider
-        // tiers two's-complement bytes; X flips the sign bit of the latter two, Y is the offset left to subtract
-        const uint32_t X = (bits == 3) ? 8u : (bits >= 5 ? 0x80u : 0u);
-        const float Y = (bits == 2) ? 2.f : (bits <= 4 ? 8.f : 128.f);
-        const uint32_t C2 = 0x64006400u ^ (X | (X << 16));
-        const __half2 bias2 = __float2half2_rn(1024.f + Y);
+        for (int c = 0; c < 4; ++c) {
+          const int gi = (gsh == 0) ? c : (gsh == 1 ? (c >> 1) : 0);
+          const float scf = bits ? scales[d * ngrp + gi] : 0.f;   // directions without bits: everything times zero
+          s2c[c] = __floats2half2_rn(scf * plo, scf * phi);
+        }
         const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const float scf = (gsh == 0) ? sc[c] : (gsh == 1 ? sc[c >> 1] : sc[0]);
-          const __half2 s2 = __float2half2_rn(scf);
           uint32_t r[4];
-          if (bits == 0) {
-            r[0] = r[1] = r[2] = r[3] = 0u;
-          } else if (bits == 2) {
-            const uint2 W = *reinterpret_cast<const uint2*>(rowp + 8 * c);
 #pragma unroll
-            for (int m_ = 0; m_ < 4; ++m_) {
-              const uint32_t wv = (m_ >> 1) ? W.y : W.x;
-              const uint32_t x = (wv >> (8 * (2 * (m_ & 1) + (q >> 1)) + 4 * (q & 1))) & 0xFu;
-              r[m_] = lop3<0x6A>(x * 0x4001u, 0x00030003u, C2);
-            }
-          } else if (bits <= 4) {
-            const uint4 W = *reinterpret_cast<const uint4*>(rowp + 16 * c);
-            const uint32_t wv[4] = {W.x, W.y, W.z, W.w};
-#pragma unroll
-            for (int m_ = 0; m_ < 4; ++m_) {
-              const uint32_t x = (wv[m_] >> (8 * q)) & 0xFFu;
-              r[m_] = lop3<0x6A>(x * 0x1001u, 0x000F000Fu, C2);
-            }
-          } else {
-            const uint4 W0 = *reinterpret_cast<const uint4*>(rowp + 32 * c), W1 = *reinterpret_cast<const uint4*>(rowp + 32 * c + 16);
-            const uint32_t wv[8] = {W0.x, W0.y, W0.z, W0.w, W1.x, W1.y, W1.z, W1.w};
-#pragma unroll
-            for (int m_ = 0; m_ < 4; ++m_) {
-              const uint32_t ww = (q >> 1) ? wv[2 * m_ + 1] : wv[2 * m_];
-              const uint32_t x = (ww >> (16 * (q & 1))) & 0xFFFFu;
-              r[m_] = prmt(x, 0u, 0x4140u) ^ C2;
-            }
-          }
-          if (bits != 0) {
-#pragma unroll
-            for (int m_ = 0; m_ < 4; ++m_) r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(r[m_]), bias2), s2));
+          for (int m_ = 0; m_ < 4; ++m_) {
+            const uint32_t wo = ((uint32_t)m_ * wstep) & ~3u;
+            const uint32_t wv = *reinterpret_cast<const uint32_t*>(rowp + (uint32_t)c * piece + wo);
+            const uint32_t t = lop3<0x6A>(prmt(wv, 0x64646464u, (m_ & 1) ? sel_o : sel_e), mask, X2);
+            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2c[c]));
           }
           stmatrix_x4_trans(st_addr + (uint32_t)(4 * c) * 16u * 128u, r);
         }
@@ -666,7 +671,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
   // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
   tc5::fence_before();
   __syncthreads();
-  if (warp == 25) {
+  if (warp == SVC0 + 1) {
     tc5::fence_after();
     tc5::dealloc(tmem, TM_COLS);
   }
