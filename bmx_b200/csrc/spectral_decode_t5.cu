@@ -6,7 +6,7 @@
 // The kernel is the k2b tcgen05 kernel (k2b_decode_t5.cu) with the low-rank product replaced by the full
 // decoder product and the residual replaced by a dequantization stage in front of it:
 //
-//   dequant warps (4; thread = one direction x the token pairs 2q, 2q+1 of every 8-token block):
+//   dequant warps (8; thread = one direction x the token pairs 2q, 2q+1 of every 8-token block):
 //         tier codes (2-, 4- or 8-bit containers along tokens, as the append kernel wrote them) -> fp16
 //         Y_hat = (code - offset) * scale -> shared memory in the K-major operand form, one stmatrix per
 //         four 8 x 8 blocks.  Directions are visited in the pack's tier order (the decoder operand the host
@@ -59,7 +59,7 @@ struct S5Smem {
   int kcnt[2], pcnt[2], vcnt[2], ycnt[2];  // arrivals of key (8 per tile) / softmax (4) / value (4) / dequant (DQ_WARPS) warps on buffer b, never reset
   volatile int slot_ring[16];
   int slot_seq[2];
-  volatile int bsel[S5_MAX_STAGES], first[S5_MAX_STAGES];
+  volatile int bsel[S5_MAX_STAGES], first[S5_MAX_STAGES], ksteps[S5_MAX_STAGES];  // per stage: decoder buffer, range start, K=16 steps of U1
   float wmax[2][4][8];
   __align__(16) int flag[2][4];
   float red[2][4][16];
@@ -71,7 +71,7 @@ struct SpectralDecodeParams {
   const uint8_t* kpages;   // [slot][head][kblock_bytes]
   const uint8_t* vpages;   // [slot][head][VBLOCK]
   const __half* dec16;     // [head][channel][position in tier order]
-  const int32_t* meta;     // [head][position]: row offset | direction << 16 | bits << 24
+  const int32_t* meta;     // [head][position]: row offset | direction << 16 | bits << 24; word 0 of a head also carries (K steps - 1) << 28
   const int32_t* page_table;
   int table_stride;
   const int32_t* n_pages;
@@ -298,7 +298,10 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
               bd[((c >> 3) * 16 + i8) * 8 + (c & 7)] = bs[o];
             }
           }
-          if (lane == 0) sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it - first_cur < 2) ? 1 : 0;
+          if (lane == 0) {
+            sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it - first_cur < 2) ? 1 : 0;
+            sh->ksteps[s] = ((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1;
+          }
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
@@ -346,9 +349,11 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           tc5::fence_after();
           const int b = nA & 1;
           const uint64_t da = d_y + (uint64_t)(b * (OPER_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[sA] * (OPER_BYTES >> 4));
+          const int nks = sh->ksteps[sA];  // directions without bits sit last in tier order: their K steps are left out
           if (el) {
 #pragma unroll
-            for (int ks = 0; ks < ((S5_SKIP & 8) ? 1 : 8); ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
+            for (int ks = 0; ks < ((S5_SKIP & 8) ? 1 : 8); ++ks)
+              if (ks < nks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
           __syncwarp();
@@ -612,6 +617,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       int meta[OCT];
 #pragma unroll
       for (int oo = 0; oo < OCT; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (DQ_WARPS * oo + wd) + dsub);
+      const int n_oct = 2 * (((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1);  // octets that U1 reads for this head
       if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
       // the buffer still feeds U1 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
@@ -621,6 +627,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
 #pragma unroll 1
       for (int oo = 0; oo < ((S5_SKIP & 1) ? 0 : OCT); ++oo) {
         const int o = DQ_WARPS * oo + wd;
+        if (o >= n_oct) break;  // the same for the whole warp
         const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
         // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
         const bool w2 = (bits == 2), w8 = (bits >= 5);

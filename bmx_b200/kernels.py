@@ -397,11 +397,15 @@ class SpectralPackDev:
         self.col_bits = self.bits.to(device).contiguous()
         self.col_off = col_off.to(device).contiguous()
         self.device = device
-        # what the fused decode kernel reads: directions in tier order (ascending bits, then ascending index),
+        # what the fused decode kernel reads: directions in tier order (those with bits first, by ascending bits, then
+        # ascending index; those without last),
         # the decoder with its columns in that order as the fp16 tensor-core operand, and one word per position
-        order = torch.stack([torch.tensor(sorted(range(HEAD_DIM), key=lambda j: (int(bits[h, j]), j))) for h in range(h_kv)])
+        order = torch.stack([torch.tensor(sorted(range(HEAD_DIM), key=lambda j: (int(bits[h, j]) == 0, int(bits[h, j]), j)))
+                             for h in range(h_kv)])
         self.order = order
         meta = col_off.gather(1, order) | (order.to(torch.int32) << 16) | (self.bits.gather(1, order) << 24)
+        used = (self.bits > 0).sum(1).clamp(min=1)
+        meta[:, 0] |= (((used + 15) // 16 - 1).to(torch.int32) << 28)  # K = 16 steps of the decoder product
         self.meta = meta.to(torch.int32).to(device).contiguous()
         self.set_decode_decoder(dec)
 

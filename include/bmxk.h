@@ -256,8 +256,11 @@ int bmxk_vblock_export(int h_kv, const void* vpages, const int32_t* slots, int n
  * src/bmx/cache/chunked_attention.py:478-530 with _dequant_block :52-145 and spectral_dequant_packed,
  * src/bmx/cache/spectral.py:812-839); this entry point replaces that call for decode.
  * g: the key pool's geometry (page must be 128).  dec_f16: (h_kv, 128, 128) fp16, dec_f16[h][c][k] = dec[h][c][d_k]
- * with d_k the k-th direction of head h in tier order (ascending bits, then ascending index).  meta: int32
- * (h_kv, 128), meta[h][k] = col_off[h][d_k] | d_k << 16 | bits[h][d_k] << 24.  Everything else as in
+ * with d_k the k-th direction of head h in tier order (directions with bits first, by ascending bits, then by
+ * ascending index; directions without bits last).  meta: int32 (h_kv, 128), meta[h][k] = col_off[h][d_k] |
+ * d_k << 16 | bits[h][d_k] << 24, and meta[h][0] also carries (ceil(max(used_h, 1) / 16) - 1) << 28, used_h being
+ * the number of directions of head h that have bits: the decoder product runs over that many 16-direction steps
+ * only.  Everything else as in
  * bmxk_k2b_decode; the workspace size comes from bmxk_spectral_decode_workspace_bytes. */
 size_t bmxk_spectral_decode_workspace_bytes(const bmxk_spectral_geom* g, int n_q_groups, int batch);
 int bmxk_spectral_decode(const bmxk_spectral_geom* g, int n_q_groups, const void* q, const void* kpages, const void* vpages,
