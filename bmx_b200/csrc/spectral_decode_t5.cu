@@ -30,6 +30,24 @@ namespace bmxk {
 
 namespace {
 
+#ifndef S5_COMPACT
+#define S5_COMPACT 0
+#endif
+#if S5_COMPACT & 1
+#define S5_UNROLL_DQ _Pragma("unroll 1")
+#else
+#define S5_UNROLL_DQ _Pragma("unroll")
+#endif
+#if S5_COMPACT & 2
+#define S5_UNROLL_KEY _Pragma("unroll 1")
+#else
+#define S5_UNROLL_KEY _Pragma("unroll")
+#endif
+#if S5_COMPACT & 4
+#define S5_UNROLL_VAL _Pragma("unroll 1")
+#else
+#define S5_UNROLL_VAL _Pragma("unroll")
+#endif
 #ifndef S5_DQ_WARPS
 #define S5_DQ_WARPS 8
 #endif
@@ -390,7 +408,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       const int b = n & 1;
       if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
       tc5::fence_after();
-#pragma unroll
+S5_UNROLL_KEY
       for (int kk = 0; kk < ((S5_SKIP & 2) ? 0 : 2); ++kk) {
         const int k = k0 + kk;
         uint32_t dl[8], dh[8], out[16];
@@ -563,7 +581,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
-#pragma unroll
+S5_UNROLL_VAL
       for (int cc = 0; cc < ((S5_SKIP & 4) ? 0 : 2); ++cc) {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -647,23 +665,19 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         const float plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
         const __half2 bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
         const uint8_t* rowp = kb + off + wbase;
-        __half2 s2c[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int gi = (gsh == 0) ? c : (gsh == 1 ? (c >> 1) : 0);
-          const float scf = bits ? scales[d * ngrp + gi] : 0.f;   // directions without bits: everything times zero
-          s2c[c] = __floats2half2_rn(scf * plo, scf * phi);
-        }
+        const float* scp = scales + d * ngrp;
         const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
-#pragma unroll
+S5_UNROLL_DQ
         for (int c = 0; c < 4; ++c) {
           uint32_t r[4];
+          const float scf = bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
+          const __half2 s2 = __floats2half2_rn(scf * plo, scf * phi);
 #pragma unroll
           for (int m_ = 0; m_ < 4; ++m_) {
             const uint32_t wo = ((uint32_t)m_ * wstep) & ~3u;
             const uint32_t wv = *reinterpret_cast<const uint32_t*>(rowp + (uint32_t)c * piece + wo);
             const uint32_t t = lop3<0x6A>(prmt(wv, 0x64646464u, (m_ & 1) ? sel_o : sel_e), mask, X2);
-            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2c[c]));
+            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2));
           }
           stmatrix_x4_trans(st_addr + (uint32_t)(4 * c) * 16u * 128u, r);
         }
