@@ -47,6 +47,17 @@ def test_argument_errors_are_reported_not_launched(lib):
     assert lib.bmxk_k2b_coef_block_bytes(ctypes.byref(g)) == 128 * 32 * 2
     with pytest.raises(_lib.BmxkError):
         _lib.call("bmxk_merge_partials", None, 0, 0, None, 0, None)
+    # fused spectral decode: 64-token pages and inconsistent block sizes are refused before any launch
+    sg = _lib.SpectralGeom(8, 64, 64, 7424, 6400)
+    args = [4, None, None, None, None, None, None, 0, None, 1, 1, None, None, 0, None, None, None, 0, None, None, 0.1, None, 0, None, 0,
+            None, 3, None]
+    assert lib.bmxk_spectral_decode(ctypes.byref(sg), *args) == _lib.BMXK_ERR_INVALID
+    assert b"page" in lib.bmxk_last_error()
+    sg = _lib.SpectralGeom(8, 128, 64, 7424, 7000)
+    assert lib.bmxk_spectral_decode(ctypes.byref(sg), *args) == _lib.BMXK_ERR_INVALID
+    assert b"block_bytes" in lib.bmxk_last_error()
+    assert lib.bmxk_vblock_bytes() == 128 * 32 + 128 * 2
+    assert lib.bmxk_vblock_append(0, None, 0, 0, 0, 0, None, None, None, 1, 1, None, None) == _lib.BMXK_ERR_INVALID
 
 
 def test_value_table_is_exact_to_1e6(lib):
