@@ -31,7 +31,7 @@ namespace bmxk {
 namespace {
 
 #ifndef S5_COMPACT
-#define S5_COMPACT 0
+#define S5_COMPACT 1
 #endif
 #if S5_COMPACT & 1
 #define S5_UNROLL_DQ _Pragma("unroll 1")
