@@ -179,8 +179,8 @@ class PackedStreamingLayer(DynamicLayer):
         else:
             k_pre = None
         total = st.seq_len() + n
-        cos, sin = shared_rope(self.model_config, total + 1, key_states.device)
-        st.rope_cos, st.rope_sin = cos, sin
+        if total + 1 > st.rope_cos.shape[0]:  # the shared table grows by doubling: rarely
+            st.rope_cos, st.rope_sin = shared_rope(self.model_config, total + 1, key_states.device)
         before = st.committed
         st.append(k_pre, key_states.to(torch.float16), value_states.to(torch.float16))
         if st.basis_f32 is not None and self._frozen_svd is None:
