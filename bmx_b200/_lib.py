@@ -95,6 +95,8 @@ _SIGNATURES = {
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "bmxk_window_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "bmxk_window_append_devpos": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),
 }
 

@@ -904,6 +904,10 @@ int bmxk_check_workspace_status(const void* workspace, void* stream) {
     set_error("bmxk_check_workspace_status: %s", cudaGetErrorString(e));
     return BMXK_ERR_CUDA;
   }
+  if (st[0] == 2) {
+    set_error("window append: a sequence's fp16 window was full (a flush was skipped); nothing was written");
+    return BMXK_ERR_DEVICE;
+  }
   if (st[0] != 0) {
     set_error("decode kernel: a bounded wait ran out in block %d (site %d)", st[1], st[2]);
     return BMXK_ERR_DEVICE;

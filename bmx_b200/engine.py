@@ -255,3 +255,72 @@ class SpectralLayerState(K2bLayerState):
 
     def packed_bytes(self) -> int:
         return int(self.batch * self.geom.h_kv * (self.committed // self.page) * (self.geom.block_bytes + self.vpool.shape[2]))
+
+
+class DecodeStepGraph:
+    """One decode step of a layer state, host buffers to host buffer, as a CUDA graph.
+
+    The step is: copy the pinned staging buffer [q | k_post | v | k_pre] to the device, append the token to the
+    fp16 window at the device-side position, run the two decode kernels, copy the attention output to the pinned
+    output buffer.  None of these launches has a per-step argument (positions and page counts live in device
+    memory), so the sequence is captured once and replayed; on the steps where the flush schedule commits pages
+    (one in `page`) the step runs through `append` / `decode` instead.  bmx's counterpart is the Python of
+    PackedStreamingLayer.update + attend per token (bmx: src/bmx/cache/packed_streaming.py:582-730, 832-1064).
+
+    hin: pinned fp16, batch * (heads + 3 * h_kv) * 128 elements laid out as q (batch, heads, 128), then k_post, v
+    and k_pre, each (batch, h_kv, 1, 128); states that quantize post-RoPE keys ignore k_pre.  hout: pinned fp16
+    (batch, heads, 128).
+    """
+
+    def __init__(self, state: K2bLayerState, hin: torch.Tensor, hout: torch.Tensor):
+        g = state.geom
+        h_kv = g.h_kv
+        n_q_groups = getattr(state, "n_q_groups", None) or g.n_q_groups
+        heads, B = h_kv * n_q_groups, state.batch
+        nq, nk = B * heads * HEAD_DIM, B * h_kv * HEAD_DIM
+        assert hin.is_pinned() and hout.is_pinned() and hin.dtype == hout.dtype == torch.float16
+        assert hin.numel() == nq + 3 * nk and hout.numel() == nq
+        self.state, self.hin, self.hout = state, hin, hout.view(B, heads, HEAD_DIM)
+        self.din = torch.empty(nq + 3 * nk, dtype=torch.float16, device=state.device)
+        self.q = self.din[:nq].view(B, heads, HEAD_DIM)
+        self.k_post = self.din[nq:nq + nk].view(B, h_kv, 1, HEAD_DIM)
+        self.v = self.din[nq + nk:nq + 2 * nk].view(B, h_kv, 1, HEAD_DIM)
+        self.k_pre = self.din[nq + 2 * nk:].view(B, h_kv, 1, HEAD_DIM)
+        self.out = torch.empty(B, heads, HEAD_DIM, dtype=torch.float16, device=state.device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self._captured_for = None  # (max_pages, pool identity): a pool that grew invalidates the captured pointers
+
+    def _launches(self) -> None:
+        st = self.state
+        self.din.copy_(self.hin, non_blocking=True)
+        K.window_append_devpos(self.k_post, self.v, self.k_pre if st.pre_rope else self.k_post, st.k_win, st.v_win, st.k_pre_win,
+                               st.tail_len_dev, st.workspace.view(torch.int32))
+        st.decode(self.q, out=self.out)
+        self.hout.copy_(self.out, non_blocking=True)
+
+    def _key(self):
+        st = self.state
+        pools = (st.pool.pages.data_ptr(),) if hasattr(st, "pool") else (st.kpool.data_ptr(), st.vpool.data_ptr())
+        return (st.max_pages if st.committed else 0, pools, st.rope_cos.data_ptr())
+
+    def step(self) -> None:
+        """Runs one step on the current stream; the caller synchronizes the stream before reading hout."""
+        st = self.state
+        total = st.committed + st.tail_len + 1
+        if compute_flush_schedule(total, st.W, st.page) > st.committed:  # pages are committed on this step: eager path
+            self.din.copy_(self.hin, non_blocking=True)
+            st.append(self.k_pre, self.k_post, self.v)
+            st.decode(self.q, out=self.out)
+            self.hout.copy_(self.out, non_blocking=True)
+            return
+        if self.graph is None or self._captured_for != self._key():
+            self._launches()  # one eager pass first: lazy initialisation must not happen inside the capture
+            st.tail_len += 1
+            torch.cuda.current_stream().synchronize()
+            self.graph, self._captured_for = torch.cuda.CUDAGraph(), self._key()
+            # the capture itself executes nothing; undo nothing
+            with torch.cuda.graph(self.graph):
+                self._launches()
+            return
+        self.graph.replay()
+        st.tail_len += 1

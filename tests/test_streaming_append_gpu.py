@@ -100,3 +100,64 @@ def test_token_by_token_equals_bulk_and_prefix_is_frozen(page, dtype):
             n_q_groups=G, scale=1.0 / math.sqrt(D), v_signs=signs)[:, 0, :]
         err = np.abs(out[s] - ref).max(-1) / np.abs(ref).max(-1)
         assert np.all(err <= 2e-3), float(err.max())
+
+
+def test_decode_step_graph_equals_eager_steps():
+    """The captured (copy in, append at the device-side position, decode, copy out) step replayed token after token
+    gives the outputs and the state of append() + decode() called per token, across flushes and a pool that grows."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import DecodeStepGraph, K2bLayerState
+    from bmx_b200.rope import apply_rope, default_rope_tables
+
+    dev = torch.device("cuda:0")
+    B, h_kv, G, rank, group, W, page = 2, 2, 4, 16, 64, 32, 128
+    prefix, steps = 2 * page + 40, 2 * page + 9
+    T = prefix + steps
+    gen = torch.Generator().manual_seed(41)
+    basis = torch.zeros(h_kv * D, rank)
+    for h in range(h_kv):
+        Q, _ = torch.linalg.qr(torch.randn(D, rank, generator=gen))
+        basis[h * D:(h + 1) * D] = Q
+    coef = torch.randn(B, h_kv, T, rank, generator=gen) * torch.arange(1, rank + 1).float() ** -1.5
+    k_pre = (torch.einsum("bhtr,hcr->bhtc", coef, basis.view(h_kv, D, rank)) + 0.1 * torch.randn(B, h_kv, T, D, generator=gen))
+    k_pre, v = k_pre.half().to(dev), torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    cos, sin = default_rope_tables(500000.0, D, T + 256, device=dev)
+    k_post = apply_rope(k_pre.float(), cos[:T], sin[:T]).half()
+    qs = (torch.randn(steps, B, h_kv * G, D, generator=gen) / math.sqrt(D)).half()
+    geom = K.k2b_geom(h_kv, G, page, rank, group, h_kv)
+
+    def fresh():
+        st = K2bLayerState(geom, B, 3 * page, W, dev, cos.half(), sin.half())  # room for 3 pages: the fourth makes it grow
+        st.set_basis(basis.to(dev))
+        st.append(k_pre[:, :, :prefix], k_post[:, :, :prefix], v[:, :, :prefix])
+        return st
+
+    eager, graphed = fresh(), fresh()
+    nq, nk = B * h_kv * G * D, B * h_kv * D
+    hin = torch.empty(nq + 3 * nk, dtype=torch.float16).pin_memory()
+    hout = torch.empty(B, h_kv * G, D, dtype=torch.float16).pin_memory()
+    stepper = DecodeStepGraph(graphed, hin, hout)
+    replays = 0
+    for i in range(steps):
+        t = prefix + i
+        ref = eager.decode_after_append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1], qs[i].to(dev)) \
+            if hasattr(eager, "decode_after_append") else None
+        if ref is None:
+            eager.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+            ref = eager.decode(qs[i].to(dev))
+        hin[:nq] = qs[i].reshape(-1)
+        hin[nq:nq + nk] = k_post[:, :, t].reshape(-1).cpu()
+        hin[nq + nk:nq + 2 * nk] = v[:, :, t].reshape(-1).cpu()
+        hin[nq + 2 * nk:] = k_pre[:, :, t].reshape(-1).cpu()
+        had_graph = stepper.graph is not None and stepper._captured_for == stepper._key()
+        stepper.step()
+        torch.cuda.current_stream().synchronize()
+        replays += int(had_graph and stepper._captured_for == stepper._key())
+        assert graphed.committed == eager.committed and graphed.tail_len == eager.tail_len
+        assert int(graphed.tail_len_dev[0]) == graphed.tail_len
+        assert torch.equal(hout, ref.cpu()), f"step {i}"
+    K.check_status(graphed.workspace)
+    assert replays > steps // 2, "most steps must have gone through the captured graph"
+    assert graphed.committed // page >= 4, "the pool had to grow during the run"
