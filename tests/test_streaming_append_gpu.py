@@ -142,11 +142,8 @@ def test_decode_step_graph_equals_eager_steps():
     replays = 0
     for i in range(steps):
         t = prefix + i
-        ref = eager.decode_after_append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1], qs[i].to(dev)) \
-            if hasattr(eager, "decode_after_append") else None
-        if ref is None:
-            eager.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
-            ref = eager.decode(qs[i].to(dev))
+        eager.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+        ref = eager.decode(qs[i].to(dev))
         hin[:nq] = qs[i].reshape(-1)
         hin[nq:nq + nk] = k_post[:, :, t].reshape(-1).cpu()
         hin[nq + nk:nq + 2 * nk] = v[:, :, t].reshape(-1).cpu()
