@@ -138,7 +138,10 @@ __device__ __forceinline__ bool spin_or_flag(uint64_t* bar, uint32_t parity, int
 
 // SM count of the current device (cached) and the launcher of the merge kernel (defined in k2b_decode.cu).
 int num_sms();
-int launch_merge(const K2bMergeParams& mp, cudaStream_t s);
+// `after_main`: the page-streaming kernel of the same step was launched just before on the same stream.  The merge
+// kernel is then launched as its programmatic dependent: its blocks may start while that kernel drains, attend over
+// the fp16 window (which that kernel does not write) and wait for it only before they read the partial states.
+int launch_merge(const K2bMergeParams& mp, cudaStream_t s, bool after_main = false);
 // tcgen05 decode kernel for layout-1 pools (k2b_decode_t5.cu); two partial records per slot (one per tile parity)
 int launch_decode_t5(const K2bDecodeParams& prm, int grid, cudaStream_t s);
 

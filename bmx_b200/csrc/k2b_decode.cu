@@ -569,6 +569,10 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
     for (int qi = 0; qi < GQ; ++qi)
       if (qi < G) atl[(part * G + qi) * HEAD_DIM + ch] = a[qi];
   }
+  // Everything above reads only what earlier steps' kernels wrote.  When this kernel was launched as a programmatic
+  // dependent of the page-streaming kernel, that kernel's partial states are complete and visible from here on
+  // (a plain launch passes straight through).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- partial slots of the page-streaming kernel: thread = (query pair, channel) ----
   for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
     const int qi = o >> 7, ch = o & 127;
@@ -657,12 +661,21 @@ int num_sms() {
   return g_num_sms;
 }
 
-int launch_merge(const K2bMergeParams& mp, cudaStream_t s) {
+int launch_merge(const K2bMergeParams& mp, cudaStream_t s, bool after_main) {
   const int G = mp.g.n_q_groups;
   const size_t msmem = ((size_t)(G <= 4 ? 4 : 8) * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
   BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
-  if (G <= 4) k2b_merge_kernel<4><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
-  else k2b_merge_kernel<8><<<mp.batch * mp.g.h_kv, MERGE_THREADS, msmem, s>>>(mp);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(mp.batch * mp.g.h_kv)), cfg.blockDim = dim3(MERGE_THREADS), cfg.dynamicSmemBytes = msmem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = after_main ? 1 : 0;
+  const cudaError_t e = (G <= 4) ? cudaLaunchKernelEx(&cfg, k2b_merge_kernel<4>, mp) : cudaLaunchKernelEx(&cfg, k2b_merge_kernel<8>, mp);
+  if (e != cudaSuccess) {
+    set_error("decode(merge): %s", cudaGetErrorString(e));
+    return BMXK_ERR_CUDA;
+  }
   return check_launch("decode(merge)");
 }
 
@@ -786,7 +799,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  return launch_merge(mp, s);
+  return launch_merge(mp, s, max_pages > 0 && (phases & 1) && g->layout == 1);
 }
 
 int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,

@@ -113,6 +113,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // the merge kernel is launched as this kernel's programmatic dependent: let its blocks become resident as soon as
+  // SMs free up (it waits for this grid's completion itself before it reads the partial states)
+  asm volatile("griddepcontrol.launch_dependents;");
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, 128, lane);
   for (int i = tid; i < p.batch; i += T5_THREADS) npg_sm[i] = p.n_pages[i];
   __syncthreads();

@@ -154,6 +154,8 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+  // the merge kernel is launched as this kernel's programmatic dependent (see launch_merge)
+  asm volatile("griddepcontrol.launch_dependents;");
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, h_kv, 128, lane);
   for (int i = tid; i < p.batch; i += S5_THREADS) npg_sm[i] = p.n_pages[i];
   __syncthreads();
@@ -795,7 +797,7 @@ int bmxk_spectral_decode(const bmxk_spectral_geom* g, int n_q_groups, const void
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  return launch_merge(mp, s);
+  return launch_merge(mp, s, max_pages > 0 && (phases & 1));
 }
 
 }  // extern "C"
