@@ -444,6 +444,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   float* redm = qs + G * HEAD_DIM;                        // [16 warps][8] partial max / sum
   float* tm = redm + 128;                                  // [8] window max, [8] window sum
   int* cum = reinterpret_cast<int*>(tm + 16);             // [batch + 1]
+  float* fin = reinterpret_cast<float*>(cum + p.batch + 1);  // [8] overall max, [8] sum, [8] weight of the window
+  float* fw = fin + 24;                                    // [G][n_sub * main_grid] weights of the partial records
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x / g.h_kv, h = blockIdx.x % g.h_kv;
   const int bh = b * g.h_kv + h;
@@ -573,19 +575,39 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   // dependent of the page-streaming kernel, that kernel's partial states are complete and visible from here on
   // (a plain launch passes straight through).
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // ---- partial slots of the page-streaming kernel: thread = (query pair, channel) ----
+  __syncthreads();  // the window's maxima and sums (written by the first threads) are read by the warps below
+  // ---- partial records of the page-streaming kernel.  Record r of this (sequence, head): sub-record r / n_cta of
+  //      CTA cta0 + r % n_cta.  Warp qi first finds the overall maximum of query qi, every record's weight and the
+  //      sum (lanes = records); then thread = (query, channel) adds up the weighted accumulators ----
+  const int n_cta = max(0, cta1 - cta0 + 1), n_rec = n_cta * p.n_sub, rec_cap = p.n_sub * p.main_grid;
+  auto rec_ptr = [&](int r, int qi) {
+    const int sb = r / n_cta, c = cta0 + (r - sb * n_cta);
+    return p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
+  };
+  if (warp < G) {
+    const int qi = warp;
+    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
+    float M = mt;
+    for (int r = lane; r < n_rec; r += 32) M = fmaxf(M, rec_ptr(r, qi)[0]);
+#pragma unroll
+    for (int mk = 16; mk >= 1; mk >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, mk));
+    float l = 0.f;
+    for (int r = lane; r < n_rec; r += 32) {
+      const float* ps = rec_ptr(r, qi);
+      const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
+      fw[qi * rec_cap + r] = f;
+      l += ps[1] * f;
+    }
+#pragma unroll
+    for (int mk = 16; mk >= 1; mk >>= 1) l += __shfl_xor_sync(0xffffffffu, l, mk);
+    const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
+    if (lane == 0) fin[qi] = M, fin[8 + qi] = l + lt * wt, fin[16 + qi] = wt;
+  }
+  __syncthreads();
   for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
     const int qi = o >> 7, ch = o & 127;
-    float M = (tl > 0) ? tm[qi] : -INFINITY;  // tm written before the last barrier
-    for (int sb = 0; sb < p.n_sub; ++sb)
-      for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE]);
     float ar = 0.f;
-    for (int sb = 0; sb < p.n_sub; ++sb)
-      for (int c = cta0; c <= cta1; ++c) {
-        const float* ps = p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
-        const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
-        ar += ps[2 + ch] * f;
-      }
+    for (int r = 0; r < n_rec; ++r) ar = fmaf(rec_ptr(r, qi)[2 + ch], fw[qi * rec_cap + r], ar);
     accs[o] = ar;
   }
   __syncthreads();
@@ -601,17 +623,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMerge
   __syncthreads();
   for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
     const int qi = o >> 7, ch = o & 127;
-    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
-    float M = mt;
-    for (int sb = 0; sb < p.n_sub; ++sb)
-      for (int c = cta0; c <= cta1; ++c) M = fmaxf(M, p.part[((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE]);
-    const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
-    float l = lt * wt;
-    for (int sb = 0; sb < p.n_sub; ++sb)
-      for (int c = cta0; c <= cta1; ++c) {
-        const float* ps = p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
-        l += (ps[0] == -INFINITY) ? 0.f : ps[1] * ex2_approx(ps[0] - M);
-      }
+    const float M = fin[qi], l = fin[8 + qi], wt = fin[16 + qi];
     float at = 0.f;
 #pragma unroll
     for (int k = 0; k < MERGE_SPLIT; ++k) at += atl[(k * G + qi) * HEAD_DIM + ch];
@@ -663,7 +675,8 @@ int num_sms() {
 
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s, bool after_main) {
   const int G = mp.g.n_q_groups;
-  const size_t msmem = ((size_t)(G <= 4 ? 4 : 8) * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 + 16;
+  const size_t msmem = ((size_t)(G <= 4 ? 4 : 8) * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 +
+                       (size_t)(24 + G * mp.n_sub * mp.main_grid) * 4 + 16;
   BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(mp.batch * mp.g.h_kv)), cfg.blockDim = dim3(MERGE_THREADS), cfg.dynamicSmemBytes = msmem, cfg.stream = s;
