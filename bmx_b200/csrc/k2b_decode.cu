@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, t4 = lane & 3;
 
+  asm volatile("griddepcontrol.launch_dependents;");  // the merge kernel is this kernel's programmatic dependent (see launch_merge)
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, PAGE, lane);
   for (int i = tid; i < p.batch; i += DEC_THREADS) npg_sm[i] = p.n_pages[i];
   // query rows beyond the group size stay zero in every stage (their scores are never read)
@@ -812,7 +813,7 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  return launch_merge(mp, s, max_pages > 0 && (phases & 1) && g->layout == 1);
+  return launch_merge(mp, s, max_pages > 0 && (phases & 1));
 }
 
 int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pages, const void* coefs,

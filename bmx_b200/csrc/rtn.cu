@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(256, 1) rtn_decode_kernel(const RtnDecodeParam
   const RtnGeom g = p.g;
   const int G = g.n_q_groups, PB = rtn_block_bytes(g);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t4 = lane & 3;
+  asm volatile("griddepcontrol.launch_dependents;");  // the merge kernel is this kernel's programmatic dependent (see launch_merge)
   if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, PAGE, lane);
   for (int i = tid; i < p.batch; i += 256) npg_sm[i] = p.n_pages[i];
   __syncthreads();
@@ -523,7 +524,7 @@ int bmxk_rtn_decode(const bmxk_rtn_geom* g, const void* q, const void* pages, co
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = nullptr, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
   mp.partial_out = partial_out;
-  return launch_merge(mp, s);
+  return launch_merge(mp, s, max_pages > 0);
 }
 
 }  // extern "C"
