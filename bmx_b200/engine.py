@@ -32,6 +32,20 @@ def fit_basis(geom, k_pre_page: torch.Tensor) -> torch.Tensor:
     return torch.cat([torch.linalg.svd(x[h], full_matrices=False)[2][: geom.rank].mT for h in range(geom.h_kv)], 0).contiguous()
 
 
+def dequant_value_blocks(vpool: torch.Tensor, slots: torch.Tensor, codebook: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+    """Value-only page blocks -> float32 (n, 128 tokens, h_kv, 128): codebook level / sqrt(d), inverse Hadamard,
+    signs, norm (bmx: src/bmx/cache/codecs.py:639-649).  Off the decode path (prefill, the dequantized-resident
+    cache): the codes come from the exporter kernel, the rest is a few torch ops."""
+    h_kv, dev = vpool.shape[1], vpool.device
+    idx, norm = K.vblock_export(vpool, slots)
+    codes = torch.stack([(idx >> (2 * k)) & 3 for k in range(4)], -1).reshape(idx.shape[0], 128, h_kv, HEAD_DIM).long()
+    lev = codebook[codes] / math.sqrt(HEAD_DIM)
+    H = torch.tensor([[1.0]], device=dev)
+    while H.shape[0] < HEAD_DIM:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    return (lev @ (H / math.sqrt(HEAD_DIM))) * signs * norm.float().unsqueeze(-1)
+
+
 class K2bLayerState:
     """Packed pages + fp16 recent window of one layer for `batch` sequences of equal length."""
 
@@ -243,13 +257,7 @@ class SpectralLayerState(K2bLayerState):
         kd = K.spectral_dequant_pages(self.pack, self.kpool, slots, want_codes=False, want_k=True)["k"]
         shp = (self.batch, n_pg * self.page, h_kv, HEAD_DIM)
         kd = kd.view(*shp).permute(0, 2, 1, 3)
-        idx, norm = K.vblock_export(self.vpool, slots)
-        codes = torch.stack([(idx >> (2 * k)) & 3 for k in range(4)], -1).reshape(idx.shape[0], 128, h_kv, HEAD_DIM).long()
-        lev = self.codebook[codes] / math.sqrt(HEAD_DIM)
-        H = torch.tensor([[1.0]], device=self.device)
-        while H.shape[0] < HEAD_DIM:
-            H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
-        vd = (lev @ (H / math.sqrt(HEAD_DIM))) * self.signs * norm.float().unsqueeze(-1)
+        vd = dequant_value_blocks(self.vpool, slots, self.codebook, self.signs)
         vd = vd.view(self.batch, n_pg * self.page, h_kv, HEAD_DIM).permute(0, 2, 1, 3)
         return kd, vd
 

@@ -14,7 +14,7 @@ import torch
 from transformers.cache_utils import Cache, DynamicLayer
 
 from . import kernels as K
-from .engine import fit_basis
+from .engine import dequant_value_blocks, fit_basis
 from .packed_streaming import resolve_decoder_layers, resolve_k_capture_module, resolve_text_config
 from .rope import apply_rope, rope_tables_from_config
 from .schedule import codec_bpe, compute_flush_schedule
@@ -30,14 +30,19 @@ class StreamingQuantizedLayer(DynamicLayer):
         super().__init__()
         self.k_spec, self.v_spec, self.model_config, self.recent_window = k_spec, v_spec, model_config, recent_window
         self._passthrough = k_spec.arm == "fp16" and v_spec.arm == "fp16"
-        if not self._passthrough and FUSED_PAIRS.get((k_spec.arm, v_spec.arm)) != "k2b":
+        self._kind = None if self._passthrough else FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
+        if not self._passthrough and self._kind not in ("k2b", "spectral"):
             raise NotImplementedError(f"no CUDA codec for arms K={k_spec.arm!r} / V={v_spec.arm!r}; there is no CPU fallback")
+        if self._kind == "spectral" and pack is None:
+            raise NotImplementedError("the spectral key arm needs per-head packs: StreamingQuantizedCache(..., "
+                                      "spectral_packs={layer: SpectralHeadPacks}); pack files are not loaded")
+        self._pack, self._pack_dev = pack, None
         tc = resolve_text_config(model_config)
         self._h_kv = getattr(tc, "num_key_value_heads", tc.num_attention_heads)
         self._d_head = getattr(tc, "head_dim", None) or tc.hidden_size // tc.num_attention_heads
         if not self._passthrough and self._d_head != HEAD_DIM:
             raise NotImplementedError(f"head_dim={self._d_head}: the bmxk kernels are built for head_dim 128")
-        self._g = k_spec.group if not self._passthrough else 1
+        self._g = 1 if self._passthrough else (pack.group if self._kind == "spectral" else k_spec.group)
         self._page = max(self._g, (128 // self._g) * self._g) if self._g > 1 else 128
         self._k_pre: torch.Tensor | None = None
         self._k_pre_offset = 0
@@ -58,6 +63,8 @@ class StreamingQuantizedLayer(DynamicLayer):
         """Quantize-then-dequantize tokens [start, end) (whole pages): returns (k_post, v) in `dtype`."""
         dev, b = k_src.device, k_src.shape[0]
         n_pg = (end - start) // self._page
+        if self._kind == "spectral":
+            return self._flush_spectral(k_src, v_src, start, end, dtype)
         if self._geom is None:
             n_q_groups = resolve_text_config(self.model_config).num_attention_heads // self._h_kv
             self._geom = K.k2b_geom(self._h_kv, min(n_q_groups, 8), self._page, self.k_spec.rank, self.k_spec.group, 1,
@@ -78,6 +85,31 @@ class StreamingQuantizedLayer(DynamicLayer):
             cos, sin = rope_tables_from_config(self.model_config, end - start, start=start, device=dev)
             kd = apply_rope(kd, cos, sin)  # float32 tables, float32 keys, then cast
         return kd.to(dtype), vd.to(dtype)
+
+    def _flush_spectral(self, k_src: torch.Tensor, v_src: torch.Tensor, start: int, end: int, dtype):
+        """The same for the spectral key codec: spectral append + page dequantizer for keys, value blocks for values."""
+        dev, b = k_src.device, k_src.shape[0]
+        n_pg = (end - start) // self._page
+        if self._pack_dev is None:
+            self._pack_dev = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g, device=dev)
+            self._signs = K.hadamard_signs(HEAD_DIM, self.v_spec.seed).to(dev)
+            self._codebook = torch.tensor(K.GAUSSIAN_CODEBOOK[self.v_spec.bits], device=dev)
+        slots = torch.arange(b * n_pg, dtype=torch.int32, device=dev)
+        kpool, vpool = self._pack_dev.new_pool(b * n_pg), K.vblock_pool(self._h_kv, b * n_pg, dev)
+        K.spectral_append(self._pack_dev, kpool, k_src.to(torch.float16).contiguous(), slots, n_pg)
+        K.vblock_append(vpool, v_src.to(torch.float16).contiguous(), self._signs, self._codebook, slots, n_pg)
+        kd = K.spectral_dequant_pages(self._pack_dev, kpool, slots, want_codes=False, want_k=True)["k"]
+        shp = (b, n_pg * self._page, self._h_kv, self._d_head)
+        kd = kd.view(*shp).permute(0, 2, 1, 3)
+        vd = dequant_value_blocks(vpool, slots, self._codebook, self._signs).view(*shp).permute(0, 2, 1, 3)
+        cos, sin = rope_tables_from_config(self.model_config, end - start, start=start, device=dev)
+        return apply_rope(kd, cos, sin).to(dtype), vd.to(dtype)
+
+    def _page_bpe_k(self, C: int) -> float:
+        if self._kind == "spectral":  # mean bits + scales of the directions that carry any (bmx: spectral.py:602-615)
+            bits = self._pack.bits.float()
+            return float(bits.mean()) + 16.0 / self._g * float((bits > 0).float().mean())
+        return codec_bpe(self.k_spec.arm, bits=self.k_spec.bits, group=self.k_spec.group, rank=self.k_spec.rank, S=self._page, C=C)
 
     def update(self, key_states, value_states, *args, **kwargs):
         keys, values = super().update(key_states, value_states, *args, **kwargs)
@@ -100,8 +132,7 @@ class StreamingQuantizedLayer(DynamicLayer):
             values = torch.cat([self._q_prefix_v, values[:, :, end:]], 2)
             for _ in range(start, end, self._page):
                 entries = self._page * C
-                self._quant_bits_k += codec_bpe(self.k_spec.arm, bits=self.k_spec.bits, group=self.k_spec.group,
-                                                rank=self.k_spec.rank, S=self._page, C=C) * entries
+                self._quant_bits_k += self._page_bpe_k(C) * entries
                 self._quant_bits_v += codec_bpe(self.v_spec.arm, bits=self.v_spec.bits, group=self.v_spec.group, rank=0,
                                                 S=self._page, C=C, h_heads=self._h_kv) * entries
             self._committed_S_q = end
@@ -118,12 +149,19 @@ class StreamingQuantizedLayer(DynamicLayer):
 class StreamingQuantizedCache(Cache):
     """Cache container replicating StreamingQuantizedLayer across the model (bmx: streaming.py:663-815)."""
 
-    def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32):
-        if k_spec.arm == "spectral":
-            raise NotImplementedError("the spectral key arm has no CUDA codec in this cache yet; there is no CPU fallback")
+    def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32,
+                 spectral_packs: dict | None = None):
+        self._packs = dict(spectral_packs or {})
+        wself = weakref.proxy(self)
 
         def _make_layer():
-            return StreamingQuantizedLayer(k_spec, v_spec, model_config, recent_window)
+            pack = None
+            if k_spec.arm == "spectral":  # layers are appended in order: the new layer's index is the current length
+                i = len(wself.layers)
+                if i not in wself._packs:
+                    raise NotImplementedError(f"no spectral pack for layer {i}: pass spectral_packs={{layer: SpectralHeadPacks}}")
+                pack = wself._packs[i]
+            return StreamingQuantizedLayer(k_spec, v_spec, model_config, recent_window, pack=pack)
 
         self._make_layer = _make_layer
         super().__init__(layer_class_to_replicate=_make_layer)

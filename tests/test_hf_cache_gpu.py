@@ -182,3 +182,42 @@ def test_spectral_cache_decode_kernel_vs_dense_path_under_hf_model():
     assert int(decided.sum()) >= la.shape[1] and flips == 0, f"{flips} argmax flips (max logit diff {diff:.3e})"
     with pytest.raises(NotImplementedError):
         PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)._pack_for_layer(0)
+
+
+def test_spectral_streaming_twin_matches_packed_cache():
+    """The dequantized-resident cache quantizes the same tokens with the same kernels on the same schedule as the
+    packed cache, so teacher-forced logits through either agree (spectral keys, per-head packs)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.packed_streaming import PackedStreamingCache
+    from bmx_b200.specs import CacheCodecSpec
+    from bmx_b200.streaming import StreamingQuantizedCache
+
+    dev = torch.device("cuda:0")
+    model = _tiny_llama(dev)
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, 256, (1, 200 + 40), generator=g).to(dev)
+    k_spec = CacheCodecSpec(arm="spectral", pre_rope=True, group=64)
+    v_spec = CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)
+    packs = _spectral_packs(model)
+
+    def run(cache):
+        logits = []
+        with cache.attach(model), torch.no_grad():
+            out = model(ids[:, :200], past_key_values=cache, use_cache=True)
+            logits.append(out.logits[:, -1].float())
+            for t in range(200, ids.shape[1]):
+                out = model(ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+                logits.append(out.logits[:, -1].float())
+        return torch.stack(logits, 1)
+
+    pc = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32, spectral_packs=packs)
+    sc = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32, spectral_packs=packs)
+    la, lb = run(pc), run(sc)
+    assert sc.layers[0]._committed_S_q == pc.layers[0]._committed_S_q == 128
+    assert sc.layers[0].keys.shape[2] == 240
+    assert abs(sc.bits_per_entry()[0] - pc.bits_per_entry()[0]) < 1e-9
+    assert float((la - lb).abs().max()) < 1e-2
+    no_packs = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32)
+    with pytest.raises(NotImplementedError):
+        no_packs._make_layer()
