@@ -152,6 +152,12 @@ class StreamingQuantizedCache(Cache):
     def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32,
                  spectral_packs: dict | None = None):
         self._packs = dict(spectral_packs or {})
+        if k_spec.arm == "spectral" and not self._packs and k_spec.pack_path:
+            from .packs import load_head_packs
+
+            tc = resolve_text_config(model_config)
+            self._packs = load_head_packs(k_spec.pack_path, k_spec.budget, getattr(tc, "num_key_value_heads", tc.num_attention_heads),
+                                          k_spec.dec_quant)
         wself = weakref.proxy(self)
 
         def _make_layer():

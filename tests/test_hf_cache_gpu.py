@@ -184,7 +184,7 @@ def test_spectral_cache_decode_kernel_vs_dense_path_under_hf_model():
         PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)._pack_for_layer(0)
 
 
-def test_spectral_streaming_twin_matches_packed_cache():
+def test_spectral_streaming_twin_matches_packed_cache(tmp_path):
     """The dequantized-resident cache quantizes the same tokens with the same kernels on the same schedule as the
     packed cache, so teacher-forced logits through either agree (spectral keys, per-head packs)."""
     if not torch.cuda.is_available():
@@ -221,3 +221,11 @@ def test_spectral_streaming_twin_matches_packed_cache():
     no_packs = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32)
     with pytest.raises(NotImplementedError):
         no_packs._make_layer()
+    # the same packs through a pack file named by the spec (bmx's route: pack_path + budget on the spectral spec)
+    from bmx_b200.packs import save_head_packs
+
+    path = tmp_path / "packs.safetensors"
+    save_head_packs(path, packs, 2.5)
+    k_file = CacheCodecSpec(arm="spectral", pre_rope=True, group=64, pack_path=str(path), budget=2.5)
+    lc = run(PackedStreamingCache(model.config, k_file, v_spec, recent_window=32))
+    assert torch.equal(lc, la)
