@@ -166,6 +166,42 @@ class K2bLayerState:
     def seq_len(self) -> int:
         return self.committed + self.tail_len
 
+    # ---- save / restore ---------------------------------------------------------------------
+    def _pools(self) -> dict:
+        return {"pages": self.pool.pages, "coefs": self.pool.coefs}
+
+    def state_dict(self) -> dict:
+        """Everything a later process needs to go on decoding: the used page slots (compacted, in page-table order),
+        the fp16 windows, the frozen basis and the counters, as CPU tensors and ints."""
+        used = self.committed // self.page
+        src = self.page_table[:, :used].reshape(-1).long()
+        t = self.tail_len
+        return {"kind": type(self).__name__, "batch": self.batch, "page": self.page, "recent_window": self.W,
+                "committed": self.committed, "tail_len": t, "pre_rope": self.pre_rope,
+                "pools": {name: pool[src].cpu() for name, pool in self._pools().items()},
+                "k_win": self.k_win[:, :, :t].cpu(), "v_win": self.v_win[:, :, :t].cpu(), "k_pre_win": self.k_pre_win[:, :, :t].cpu(),
+                "basis_f32": None if self.basis_f32 is None else self.basis_f32.cpu()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        """Restores a state saved by state_dict() into this (freshly built, same geometry) state."""
+        assert sd["kind"] == type(self).__name__ and sd["batch"] == self.batch and sd["page"] == self.page
+        assert sd["recent_window"] == self.W and sd["pre_rope"] == self.pre_rope and self.committed == 0 and self.tail_len == 0
+        used = sd["committed"] // self.page
+        self.ensure_pages(used)
+        dst = self.page_table[:, :used].reshape(-1).long()
+        for name, pool in self._pools().items():
+            assert pool.shape[1:] == sd["pools"][name].shape[1:], f"pool {name}: block shape differs"
+            pool[dst] = sd["pools"][name].to(self.device)
+        t = sd["tail_len"]
+        self.k_win[:, :, :t] = sd["k_win"].to(self.device)
+        self.v_win[:, :, :t] = sd["v_win"].to(self.device)
+        self.k_pre_win[:, :, :t] = sd["k_pre_win"].to(self.device)
+        if sd["basis_f32"] is not None:
+            self.set_basis(sd["basis_f32"])
+        self.committed, self.tail_len = sd["committed"], t
+        self.n_pages_dev.fill_(used)
+        self.tail_len_dev.fill_(t)
+
     def packed_bytes(self) -> int:
         """Bytes of packed pages a decode step streams (per layer, all sequences)."""
         g = self.geom
@@ -247,6 +283,9 @@ class SpectralLayerState(K2bLayerState):
         return K.spectral_decode(self.pack, self.n_q_groups, self.kpool, self.vpool, q, self.page_table, self.n_pages_dev,
                                  max_pages, self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
                                  self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, phases=phases)
+
+    def _pools(self) -> dict:
+        return {"kpool": self.kpool, "vpool": self.vpool}
 
     def dense_pages(self) -> tuple[torch.Tensor, torch.Tensor]:
         """All committed pages dequantized: pre-RoPE keys and values, float32 (batch, h_kv, committed, 128).

@@ -158,3 +158,58 @@ def test_decode_step_graph_equals_eager_steps():
     K.check_status(graphed.workspace)
     assert replays > steps // 2, "most steps must have gone through the captured graph"
     assert graphed.committed // page >= 4, "the pool had to grow during the run"
+
+
+@pytest.mark.parametrize("kind", ["k2b", "spectral"])
+def test_state_dict_round_trip_continues_bit_equal(kind):
+    """A layer state saved with state_dict(), serialized, and loaded into a fresh state decodes and keeps appending
+    exactly like the original (pools are compacted to the used slots on the way)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import io
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState, SpectralLayerState
+    from bmx_b200.rope import default_rope_tables
+
+    dev = torch.device("cuda:0")
+    B, h_kv, G, W, page = 2, 2, 4, 32, 128
+    T = 3 * page + 50 + 140
+    gen = torch.Generator().manual_seed(51)
+    k_pre = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    k_post = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    v = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    cos, sin = default_rope_tables(500000.0, D, T + 256, device=dev)
+    if kind == "k2b":
+        geom = K.k2b_geom(h_kv, G, page, 16, 64, h_kv)
+        basis = torch.cat([torch.linalg.qr(torch.randn(D, 16, generator=gen))[0] for _ in range(h_kv)], 0)
+
+        def fresh(max_tokens):
+            return K2bLayerState(geom, B, max_tokens, W, dev, cos.half(), sin.half())
+    else:
+        enc = torch.stack([torch.linalg.qr(torch.randn(D, D, generator=gen))[0] for _ in range(h_kv)])
+        bits = torch.tensor([8] * 8 + [4] * 40 + [2] * 48 + [0] * 32, dtype=torch.int32).repeat(h_kv, 1)
+        pack = K.SpectralPackDev(enc, enc.clone(), bits, page=128, group=64, device=dev)
+
+        def fresh(max_tokens):
+            return SpectralLayerState(pack, G, B, max_tokens, W, dev, cos.half(), sin.half())
+
+    a = fresh(8 * page)
+    if kind == "k2b":
+        a.set_basis(basis)
+    n0 = 3 * page + 50
+    a.append(k_pre[:, :, :n0], k_post[:, :, :n0], v[:, :, :n0])
+    buf = io.BytesIO()
+    torch.save(a.state_dict(), buf)
+    buf.seek(0)
+    b = fresh(page)  # a smaller pool: loading must grow it
+    b.load_state_dict(torch.load(buf))
+    assert (b.committed, b.tail_len) == (a.committed, a.tail_len)
+    q = (torch.randn(B, h_kv * G, D, generator=gen) / math.sqrt(D)).half().to(dev)
+    assert torch.equal(a.decode(q), b.decode(q))
+    for t in range(n0, T):  # crosses a flush
+        a.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+        b.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+    assert a.committed == b.committed == 4 * page
+    assert torch.equal(a.decode(q), b.decode(q))
+    K.check_status(b.workspace)
