@@ -51,16 +51,22 @@ namespace {
 #ifndef S5_DQ_WARPS
 #define S5_DQ_WARPS 8
 #endif
+#ifndef S5_KEY_WARPS
+#define S5_KEY_WARPS 4  // 4: four key warps (all four chunks each) and eight value warps; 8: eight key warps, four value warps
+#endif
+constexpr int KEY_WARPS = S5_KEY_WARPS, VAL_WARPS = 12 - KEY_WARPS;
+constexpr int W_SOFT = KEY_WARPS, W_VAL = KEY_WARPS + 8;  // first softmax / value warp; dequant warps start at 20
 constexpr int DQ_WARPS = S5_DQ_WARPS;   // dequant warps: 4 or 8
 constexpr int SVC0 = 20 + DQ_WARPS;     // first of the four service warps: copy + U3, U1 + U2, two query rotation warps
-constexpr int S5_THREADS = (SVC0 + 4) * 32;  // warps 0-7 key, 8-15 softmax (two sets), 16-19 value, 20.. dequant, then service
+constexpr int S5_THREADS = (SVC0 + 4) * 32;  // key warps, 8 softmax warps (two sets), value warps (12 with the key warps), 20.. dequant, then service
 constexpr int S5_MAX_STAGES = 8;
 // Registers per thread after each role resizes itself; the pool is what the launch handed out.
-constexpr int REG_LAUNCH = (DQ_WARPS == 4) ? 72 : 64, REG_KEY = (DQ_WARPS == 4) ? 96 : 88, REG_SOFTMAX = (DQ_WARPS == 4) ? 56 : 48;
+constexpr int REG_LAUNCH = (DQ_WARPS == 4) ? 72 : 64, REG_KEY = (DQ_WARPS == 4) ? 96 : (KEY_WARPS == 4 ? 120 : 88), REG_SOFTMAX = (DQ_WARPS == 4) ? 56 : 48;
 constexpr int REG_VALUE = 56, REG_DEQUANT = (DQ_WARPS == 4) ? 88 : 64, REG_SERVICE = 56;
 static_assert(DQ_WARPS == 4 || DQ_WARPS == 8, "dequant warps come in groups of four");
 static_assert(REG_LAUNCH * S5_THREADS <= 65536, "launch registers exceed the register file");
-static_assert(8 * REG_KEY + 8 * REG_SOFTMAX + 4 * REG_VALUE + DQ_WARPS * REG_DEQUANT + 4 * REG_SERVICE <= (SVC0 + 4) * REG_LAUNCH,
+static_assert(KEY_WARPS == 8 || (KEY_WARPS == 4 && DQ_WARPS == 8), "key warps: 4 or 8");
+static_assert(KEY_WARPS * REG_KEY + 8 * REG_SOFTMAX + VAL_WARPS * REG_VALUE + DQ_WARPS * REG_DEQUANT + 4 * REG_SERVICE <= (SVC0 + 4) * REG_LAUNCH,
               "register split exceeds the CTA's pool");
 constexpr int QB_BYTES = 4096;        // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
 constexpr int OPER_BYTES = 128 * 128 * 2;  // Y_hat / decoder operand: 128 rows x 128 fp16
@@ -207,7 +213,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         const int pc = smem_load_acquire(&sh->pcnt[nC & 1]);
         const int vc = smem_load_acquire(&sh->vcnt[nC & 1]);
         const int bdone = smem_load_acquire(&sh->bcnt);
-        if (nC < bdone && pc >= 4 * ((nC >> 1) + 1) && vc >= 4 * ((nC >> 1) + 1)) {
+        if (nC < bdone && pc >= 4 * ((nC >> 1) + 1) && vc >= VAL_WARPS * ((nC >> 1) + 1)) {
           tc5::fence_after();
           const int b = nC & 1;
           const uint32_t keep = sh->first[sC] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
@@ -348,7 +354,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         const int nC = smem_load_acquire(&sh->ccnt);
         const int yc = smem_load_acquire(&sh->ycnt[nA & 1]);
         // ---- B ----
-        if (nB < nA && nB < nC + 2 && kc >= 8 * ((nB >> 1) + 1)) {
+        if (nB < nA && nB < nC + 2 && kc >= KEY_WARPS * ((nB >> 1) + 1)) {
           tc5::fence_after();
           const int b = nB & 1;
           const uint64_t db = d_qb + (uint64_t)(sB * (QB_BYTES >> 4));
@@ -392,15 +398,16 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         }
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < KEY_WARPS) {
     // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
-    const int wq = warp & 3, k0 = 2 * (warp >> 2), row = 32 * wq + lane;
+    constexpr int KCH = 16 / KEY_WARPS;  // chunks of 16 + 16 channels per key warp
+    const int wq = warp & 3, k0 = KCH * (warp >> 2), row = 32 * wq + lane;
     const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
     // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
-    uint32_t cs_[2][8], sn_[2][8];
+    uint32_t cs_[KCH][8], sn_[KCH][8];
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk)
+    for (int kk = 0; kk < KCH; ++kk)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
@@ -411,7 +418,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
       tc5::fence_after();
 S5_UNROLL_KEY
-      for (int kk = 0; kk < ((S5_SKIP & 2) ? 0 : 2); ++kk) {
+      for (int kk = 0; kk < ((S5_SKIP & 2) ? 0 : KCH); ++kk) {
         const int k = k0 + kk;
         uint32_t dl[8], dh[8], out[16];
         tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
@@ -431,10 +438,10 @@ S5_UNROLL_KEY
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
     }
-  } else if (warp < 16) {
+  } else if (warp < W_VAL) {
     // ===================== softmax warps: thread = token row; set e takes the tiles of parity e =====================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
-    const int e = (warp - 8) >> 2, wq = warp & 3, row = 32 * wq + lane;
+    const int e = (warp - W_SOFT) >> 2, wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
@@ -570,9 +577,10 @@ S5_UNROLL_KEY
     }
     flush(cur_b, cur_h);
   } else if (warp < 20) {
-    // ===================== value warps: thread = channel, both 64-token halves of the tile =====================
+    // ===================== value warps: thread = channel; eight warps take one 64-token half each, four take both =====================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
     const int wq = warp & 3, ch = 32 * wq + lane;
+    const int cc0 = (VAL_WARPS == 8) ? ((warp - W_VAL) >> 2) : 0, cc1 = (VAL_WARPS == 8) ? cc0 + 1 : 2;
     const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
     int s = 0;
     uint32_t fp = 0;
@@ -584,7 +592,7 @@ S5_UNROLL_KEY
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
 S5_UNROLL_VAL
-      for (int cc = 0; cc < ((S5_SKIP & 4) ? 0 : 2); ++cc) {
+      for (int cc = cc0; cc < ((S5_SKIP & 4) ? 0 : cc1); ++cc) {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
