@@ -213,3 +213,51 @@ def test_state_dict_round_trip_continues_bit_equal(kind):
     assert a.committed == b.committed == 4 * page
     assert torch.equal(a.decode(q), b.decode(q))
     K.check_status(b.workspace)
+
+
+def test_decode_step_graph_on_a_spectral_state():
+    """The graph step drives the spectral layer state as well (two pools, fused spectral decode)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import DecodeStepGraph, SpectralLayerState
+    from bmx_b200.rope import default_rope_tables
+
+    dev = torch.device("cuda:0")
+    B, h_kv, G, W, page = 2, 2, 4, 32, 128
+    prefix, steps = page + 60, page + 20
+    T = prefix + steps
+    gen = torch.Generator().manual_seed(61)
+    k_pre = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    k_post = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    v = torch.randn(B, h_kv, T, D, generator=gen).half().to(dev)
+    cos, sin = default_rope_tables(500000.0, D, T + 256, device=dev)
+    enc = torch.stack([torch.linalg.qr(torch.randn(D, D, generator=gen))[0] for _ in range(h_kv)])
+    bits = torch.tensor([8] * 8 + [5] * 8 + [4] * 32 + [3] * 16 + [2] * 40 + [0] * 24, dtype=torch.int32).repeat(h_kv, 1)
+    pack = K.SpectralPackDev(enc, enc.clone(), bits, page=128, group=64, device=dev)
+
+    def fresh():
+        st = SpectralLayerState(pack, G, B, 2 * page, W, dev, cos.half(), sin.half())
+        st.append(k_pre[:, :, :prefix], k_post[:, :, :prefix], v[:, :, :prefix])
+        return st
+
+    eager, graphed = fresh(), fresh()
+    nq, nk = B * h_kv * G * D, B * h_kv * D
+    hin = torch.empty(nq + 3 * nk, dtype=torch.float16).pin_memory()
+    hout = torch.empty(B, h_kv * G, D, dtype=torch.float16).pin_memory()
+    stepper = DecodeStepGraph(graphed, hin, hout)
+    qs = (torch.randn(steps, B, h_kv * G, D, generator=gen) / math.sqrt(D)).half()
+    for i in range(steps):
+        t = prefix + i
+        eager.append(k_pre[:, :, t:t + 1], k_post[:, :, t:t + 1], v[:, :, t:t + 1])
+        ref = eager.decode(qs[i].to(dev))
+        hin[:nq] = qs[i].reshape(-1)
+        hin[nq:nq + nk] = k_post[:, :, t].reshape(-1).cpu()
+        hin[nq + nk:nq + 2 * nk] = v[:, :, t].reshape(-1).cpu()
+        hin[nq + 2 * nk:] = k_pre[:, :, t].reshape(-1).cpu()
+        stepper.step()
+        torch.cuda.current_stream().synchronize()
+        assert (graphed.committed, graphed.tail_len) == (eager.committed, eager.tail_len)
+        assert torch.equal(hout, ref.cpu()), f"step {i}"
+    K.check_status(graphed.workspace)
+    assert stepper.graph is not None and graphed.committed == 2 * page
