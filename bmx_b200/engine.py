@@ -336,6 +336,7 @@ class DecodeStepGraph:
         self.out = torch.empty(B, heads, HEAD_DIM, dtype=torch.float16, device=state.device)
         self.graph: torch.cuda.CUDAGraph | None = None
         self._captured_for = None  # (max_pages, pool identity): a pool that grew invalidates the captured pointers
+        self._check_key = True     # pools and tables only change on the steps that go through append()
 
     def _launches(self) -> None:
         st = self.state
@@ -350,6 +351,10 @@ class DecodeStepGraph:
         pools = (st.pool.pages.data_ptr(),) if hasattr(st, "pool") else (st.kpool.data_ptr(), st.vpool.data_ptr())
         return (st.max_pages if st.committed else 0, pools, st.rope_cos.data_ptr())
 
+    def invalidate(self) -> None:
+        """Call after changing the state from outside (other RoPE tables, pools swapped): the next step re-captures."""
+        self._check_key = True
+
     def step(self) -> None:
         """Runs one step on the current stream; the caller synchronizes the stream before reading hout."""
         st = self.state
@@ -359,8 +364,11 @@ class DecodeStepGraph:
             st.append(self.k_pre, self.k_post, self.v)
             st.decode(self.q, out=self.out)
             self.hout.copy_(self.out, non_blocking=True)
+            self._check_key = True
             return
-        if self.graph is None or self._captured_for != self._key():
+        if self._check_key and self.graph is not None and self._captured_for == self._key():
+            self._check_key = False
+        if self.graph is None or self._check_key:
             self._launches()  # one eager pass first: lazy initialisation must not happen inside the capture
             st.tail_len += 1
             torch.cuda.current_stream().synchronize()
@@ -368,6 +376,7 @@ class DecodeStepGraph:
             # the capture itself executes nothing; undo nothing
             with torch.cuda.graph(self.graph):
                 self._launches()
+            self._check_key = False
             return
         self.graph.replay()
         st.tail_len += 1
