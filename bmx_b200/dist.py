@@ -41,22 +41,19 @@ def gather_partials(part: torch.Tensor, group=None) -> torch.Tensor:
 class SequenceSplitDecoder:
     """Decode step of one long sequence whose committed pages are split across the ranks of `group`.
 
-    `state` is this rank's K2bLayerState holding ITS pages only (and the window on the last rank);
+    `state` is this rank's layer state (k2b or spectral) holding ITS pages only (and the window on the last rank);
     `first_page` is the index of its first page in the whole sequence, which fixes the rotary positions.
     """
 
     def __init__(self, state, first_page: int, group=None):
         self.state, self.first_page, self.group = state, first_page, group
-        rows = state.batch * state.geom.h_kv * state.geom.n_q_groups
+        rows = state.batch * state.geom.h_kv * (getattr(state, "n_q_groups", None) or state.geom.n_q_groups)
         self.part = torch.empty(rows, PART_STRIDE, dtype=torch.float32, device=state.device)
 
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         from . import kernels as K
 
-        st = self.state
-        max_pages = st.max_pages if st.committed else 0
-        K.k2b_decode(st.pool, q, st.basis_f16, st.page_table, st.n_pages_dev, max_pages, st.rope_cos, st.rope_sin,
-                     st.k_win, st.v_win, st.tail_len_dev, st.v_lut, st.signs, st.sm_scale, st.workspace,
-                     partial_out=self.part, pos_offset=self.first_page * st.page)
+        st = self.state  # a K2bLayerState or a SpectralLayerState: same call
+        st.decode(q, partial_out=self.part, pos_offset=self.first_page * st.page)
         gathered = gather_partials(self.part, self.group)
         return K.merge_partials(gathered, out=out)

@@ -156,12 +156,14 @@ class K2bLayerState:
 
     # ---- decode -----------------------------------------------------------------------------
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
-               phases: int = 3) -> torch.Tensor:
-        """q (batch, heads, 128) fp16 -> attention output (batch, heads, 128) over pages + window."""
+               phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
+        """q (batch, heads, 128) fp16 -> attention output (batch, heads, 128) over pages + window.  pos_offset: rotary
+        position of this state's first committed token (a rank that holds a later part of a split sequence)."""
         max_pages = self.max_pages if self.committed else 0  # nothing committed yet: window only
         return K.k2b_decode(self.pool, q, self.basis_f16, self.page_table, self.n_pages_dev, max_pages,
                             self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
-                            self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, phases=phases)
+                            self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, pos_offset=pos_offset,
+                            phases=phases)
 
     def seq_len(self) -> int:
         return self.committed + self.tail_len
@@ -278,11 +280,12 @@ class SpectralLayerState(K2bLayerState):
         self.n_pages_dev.fill_(self.committed // self.page)
 
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
-               phases: int = 3) -> torch.Tensor:
+               phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
         max_pages = self.max_pages if self.committed else 0
         return K.spectral_decode(self.pack, self.n_q_groups, self.kpool, self.vpool, q, self.page_table, self.n_pages_dev,
                                  max_pages, self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
-                                 self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, phases=phases)
+                                 self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out,
+                                 pos_offset=pos_offset, phases=phases)
 
     def _pools(self) -> dict:
         return {"kpool": self.kpool, "vpool": self.vpool}
