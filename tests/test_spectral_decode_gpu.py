@@ -179,3 +179,51 @@ def test_spectral_decode_many_tiles_per_cta():
     # ~7.5 tiles per CTA on 148 SMs: the stage ring wraps and ranges span CTAs
     out, ref = _case(dev, n_seq=2, h_kv=1, G=4, group=64, tier_counts=TIERS_B, pages_per_seq=[600, 520], tail_lens=[11, 0], seed=31)
     _assert_attn_close(out, ref)
+
+
+def test_spectral_sequence_split_partials_merge_to_the_whole():
+    """One sequence cut into two states (the second starts at a later rotary position and owns the window): their
+    partial states merged by bmxk_merge_partials equal the whole sequence decoded at once (the multi-GPU sequence
+    split, both parts on one GPU here)."""
+    dev = _dev()
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import SpectralLayerState
+    from bmx_b200.rope import default_rope_tables
+
+    h_kv, G, W, n_pg = 2, 4, 64, 12
+    enc, bits_perm = make_pack(71, h_kv, TIERS_A)
+    bits = torch.stack([b for b, _ in bits_perm])
+    pack = K.SpectralPackDev(enc, enc.clone(), bits, page=128, group=64, device=dev)
+    T = n_pg * 128 + W
+    gen = torch.Generator().manual_seed(72)
+    k_pre = make_keys(73, 1, T, enc, bits_perm).to(dev)
+    k_post = torch.randn(1, h_kv, T, D, generator=gen).half().to(dev)
+    v = torch.randn(1, h_kv, T, D, generator=gen).half().to(dev)
+    q = (torch.randn(1, h_kv * G, D, generator=gen) / math.sqrt(D)).half().to(dev)
+    cos, sin = default_rope_tables(500000.0, D, T + 256, device=dev)
+
+    def state(first, count, window):
+        st = SpectralLayerState(pack, G, 1, max(count, 1) * 128, W, dev, cos.half(), sin.half())
+        sl = slice(first * 128, (first + count) * 128)
+        slots = st.page_table[0, :count].contiguous()
+        K.spectral_append(pack, st.kpool, k_pre[:, :, sl].contiguous(), slots, count)
+        K.vblock_append(st.vpool, v[:, :, sl].contiguous(), st.signs, st.codebook, slots, count)
+        st.committed = count * 128
+        st.n_pages_dev.fill_(count)
+        if window:
+            st.k_win[:, :, :W] = k_post[:, :, n_pg * 128:]
+            st.v_win[:, :, :W] = v[:, :, n_pg * 128:]
+            st.tail_len = W
+            st.tail_len_dev.fill_(W)
+        return st
+
+    whole = state(0, n_pg, True).decode(q, out=torch.empty(1, h_kv * G, D, dtype=torch.float32, device=dev))
+    parts = []
+    for first, count, window in ((0, 5, False), (5, 7, True)):
+        part = torch.empty(h_kv * G, 130, dtype=torch.float32, device=dev)
+        state(first, count, window).decode(q, partial_out=part, pos_offset=first * 128)
+        parts.append(part)
+    merged = K.merge_partials(torch.stack(parts), out=torch.empty(h_kv * G, D, dtype=torch.float32, device=dev))
+    torch.cuda.synchronize()
+    err = (merged - whole[0]).abs().max(dim=-1).values / whole[0].abs().max(dim=-1).values
+    assert float(err.max()) < 1e-5, float(err.max())
