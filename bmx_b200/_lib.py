@@ -96,7 +96,7 @@ _SIGNATURES = {
     "bmxk_window_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "bmxk_window_append_devpos": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
-                                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),
 }
 

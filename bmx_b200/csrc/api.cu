@@ -89,29 +89,35 @@ __global__ void window_append_kernel(const T* __restrict__ k_post, const T* __re
   if (h == 0 && c == 0) tail_len[b] = t + 1;
 }
 
-// The same append with the position taken from device memory: one block per sequence reads tail_len[b], writes
-// the token of every head there and then advances tail_len[b].  Nothing in the launch depends on the step, so a
-// captured CUDA graph of (append, decode) can be replayed token after token.
+// The same append with the position taken from device memory: every block (one per sequence and head) reads
+// tail_len[b] and writes its head's token there; the block of a sequence that finishes last (a per-sequence
+// counter tells) advances tail_len[b] and clears the counter, so no block can read the new position.  Nothing in the
+// launch depends on the step, so a captured CUDA graph of (append, decode) can be replayed token after token.
 template <typename T>
 __global__ void window_append_devpos_kernel(const T* __restrict__ k_post, const T* __restrict__ v, const T* __restrict__ k_src,
                                             int64_t stride_seq, int64_t stride_head, __half* __restrict__ k_win,
                                             __half* __restrict__ v_win, __half* __restrict__ k_src_win,
-                                            int32_t* __restrict__ tail_len, int32_t* __restrict__ status, int h_kv, int tail_cap) {
-  const int b = blockIdx.x, c = threadIdx.x;
-  const int t = tail_len[b];
-  __syncthreads();  // every thread has read the position before thread 0 advances it
-  if (t < 0 || t >= tail_cap) {  // the window is full: the host should have flushed; report instead of writing outside
-    if (c == 0 && status) atomicCAS(status, 0, 2);
-    return;
-  }
-  for (int h = 0; h < h_kv; ++h) {
+                                            int32_t* __restrict__ tail_len, int32_t* __restrict__ counters,
+                                            int32_t* __restrict__ status, int h_kv, int tail_cap) {
+  const int bh = blockIdx.x, b = bh / h_kv, h = bh % h_kv, c = threadIdx.x;
+  const int t = *reinterpret_cast<volatile int32_t*>(tail_len + b);
+  if (t >= 0 && t < tail_cap) {
     const int64_t src = (int64_t)b * stride_seq + (int64_t)h * stride_head + c;
-    const int64_t dst = (((int64_t)b * h_kv + h) * tail_cap + t) * WIN_HEAD_DIM + c;
+    const int64_t dst = ((int64_t)bh * tail_cap + t) * WIN_HEAD_DIM + c;
     k_win[dst] = __float2half_rn(load_as_float<T>(k_post + src));
     v_win[dst] = __float2half_rn(load_as_float<T>(v + src));
     k_src_win[dst] = __float2half_rn(load_as_float<T>(k_src + src));
+  } else if (c == 0 && status) {
+    atomicCAS(status, 0, 2);  // the window is full: the host should have flushed; report instead of writing outside
   }
-  if (c == 0) tail_len[b] = t + 1;
+  __syncthreads();  // every thread of this block has read the position
+  if (c == 0) {
+    __threadfence();
+    if (atomicAdd(counters + b, 1) == h_kv - 1) {  // all blocks of the sequence have read the position
+      counters[b] = 0;
+      if (t >= 0 && t < tail_cap) tail_len[b] = t + 1;
+    }
+  }
 }
 
 }  // namespace bmxk
@@ -186,24 +192,24 @@ int bmxk_window_append(const void* k_post, const void* v, const void* k_src, int
 }
 
 int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_src, int src_dtype, int64_t stride_seq,
-                              int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len, int32_t* status,
-                              int batch, int h_kv, int tail_cap, void* stream) {
-  BMXK_REQUIRE(k_post && v && k_src && k_win && v_win && k_src_win && tail_len, "bmxk_window_append_devpos: null pointer");
+                              int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len, int32_t* counters,
+                              int32_t* status, int batch, int h_kv, int tail_cap, void* stream) {
+  BMXK_REQUIRE(k_post && v && k_src && k_win && v_win && k_src_win && tail_len && counters, "bmxk_window_append_devpos: null pointer");
   BMXK_REQUIRE(batch >= 1 && h_kv >= 1 && tail_cap >= 1, "bmxk_window_append_devpos: batch=%d h_kv=%d tail_cap=%d", batch, h_kv, tail_cap);
   cudaStream_t s = (cudaStream_t)stream;
   if (src_dtype == BMXK_DTYPE_F16)
-    window_append_devpos_kernel<__half><<<batch, WIN_HEAD_DIM, 0, s>>>((const __half*)k_post, (const __half*)v, (const __half*)k_src,
+    window_append_devpos_kernel<__half><<<batch * h_kv, WIN_HEAD_DIM, 0, s>>>((const __half*)k_post, (const __half*)v, (const __half*)k_src,
                                                                      stride_seq, stride_head, (__half*)k_win, (__half*)v_win,
-                                                                     (__half*)k_src_win, tail_len, status, h_kv, tail_cap);
+                                                                     (__half*)k_src_win, tail_len, counters, status, h_kv, tail_cap);
   else if (src_dtype == BMXK_DTYPE_BF16)
-    window_append_devpos_kernel<__nv_bfloat16><<<batch, WIN_HEAD_DIM, 0, s>>>((const __nv_bfloat16*)k_post, (const __nv_bfloat16*)v,
+    window_append_devpos_kernel<__nv_bfloat16><<<batch * h_kv, WIN_HEAD_DIM, 0, s>>>((const __nv_bfloat16*)k_post, (const __nv_bfloat16*)v,
                                                                             (const __nv_bfloat16*)k_src, stride_seq, stride_head,
                                                                             (__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_len,
-                                                                            status, h_kv, tail_cap);
+                                                                            counters, status, h_kv, tail_cap);
   else if (src_dtype == BMXK_DTYPE_F32)
-    window_append_devpos_kernel<float><<<batch, WIN_HEAD_DIM, 0, s>>>((const float*)k_post, (const float*)v, (const float*)k_src,
+    window_append_devpos_kernel<float><<<batch * h_kv, WIN_HEAD_DIM, 0, s>>>((const float*)k_post, (const float*)v, (const float*)k_src,
                                                                    stride_seq, stride_head, (__half*)k_win, (__half*)v_win,
-                                                                   (__half*)k_src_win, tail_len, status, h_kv, tail_cap);
+                                                                   (__half*)k_src_win, tail_len, counters, status, h_kv, tail_cap);
   else
     BMXK_REQUIRE(false, "bmxk_window_append_devpos: src_dtype=%d", src_dtype);
   return check_launch("bmxk_window_append_devpos");

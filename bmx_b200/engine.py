@@ -59,6 +59,7 @@ class K2bLayerState:
         self.page_table = torch.arange(batch * self.max_pages, dtype=torch.int32, device=self.device).view(batch, -1)
         self.n_pages_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.tail_len_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.append_cnt = torch.zeros(batch, dtype=torch.int32, device=self.device)  # scratch of window_append_devpos
         self.tail_cap = recent_window + geom.page
         shape = (batch, geom.h_kv, self.tail_cap, HEAD_DIM)
         self.k_win = torch.zeros(shape, dtype=torch.float16, device=self.device)      # post-RoPE keys
@@ -234,6 +235,7 @@ class SpectralLayerState(K2bLayerState):
         self.page_table = torch.arange(batch * self.max_pages, dtype=torch.int32, device=self.device).view(batch, -1)
         self.n_pages_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.tail_len_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.append_cnt = torch.zeros(batch, dtype=torch.int32, device=self.device)  # scratch of window_append_devpos
         self.tail_cap = recent_window + self.page
         shape = (batch, h_kv, self.tail_cap, HEAD_DIM)
         self.k_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
@@ -345,7 +347,7 @@ class DecodeStepGraph:
         st = self.state
         self.din.copy_(self.hin, non_blocking=True)
         K.window_append_devpos(self.k_post, self.v, self.k_pre if st.pre_rope else self.k_post, st.k_win, st.v_win, st.k_pre_win,
-                               st.tail_len_dev, st.workspace.view(torch.int32))
+                               st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))
         st.decode(self.q, out=self.out)
         self.hout.copy_(self.out, non_blocking=True)
 

@@ -267,16 +267,20 @@ def window_append(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_
 
 
 def window_append_devpos(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor,
-                         k_src_win: torch.Tensor, tail_len: torch.Tensor, status: torch.Tensor | None = None) -> None:
+                         k_src_win: torch.Tensor, tail_len: torch.Tensor, counters: torch.Tensor,
+                         status: torch.Tensor | None = None) -> None:
     """window_append at the position held in tail_len (device int32 per sequence), which the kernel advances: no
-    per-step argument, so the launch can sit in a CUDA graph.  Sources: (batch, h_kv, 1, 128), one dtype and layout."""
-    _require_cuda(k_post, v, k_src, k_win, v_win, k_src_win, tail_len)
+    per-step argument, so the launch can sit in a CUDA graph.  Sources: (batch, h_kv, 1, 128), one dtype and layout.
+    counters: device int32 (batch), zero-initialised once and owned by these calls."""
+    _require_cuda(k_post, v, k_src, k_win, v_win, k_src_win, tail_len, counters)
+    assert counters.dtype == torch.int32 and counters.numel() >= k_post.shape[0]
     batch, h_kv = k_post.shape[0], k_post.shape[1]
     for x in (k_post, v, k_src):
         if x.shape != k_post.shape or x.dtype != k_post.dtype or x.stride() != k_post.stride() or x.stride(3) != 1:
             raise ValueError("window_append_devpos: sources must share shape (batch, h_kv, 1, 128), dtype and strides")
     call("bmxk_window_append_devpos", _ptr(k_post), _ptr(v), _ptr(k_src), _dtype_code(k_post), k_post.stride(0), k_post.stride(1),
-         _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), _ptr(status), batch, h_kv, k_win.shape[2], _stream())
+         _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), _ptr(counters), _ptr(status), batch, h_kv, k_win.shape[2],
+         _stream())
 
 
 def merge_partials(parts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -289,11 +289,13 @@ int bmxk_window_append(const void* k_post, const void* v, const void* k_src, int
 
 /* The same append with the position read from tail_len[s] on the device (and advanced there), so that the launch
  * has no per-step argument and an (append, decode) pair can be captured once in a CUDA graph and replayed per
- * token.  A full window (tail_len[s] == tail_cap: the host skipped a flush) writes nothing and sets *status to 2
- * when status is not NULL (the decode workspace's first word: bmxk_check_workspace_status reports it). */
+ * token.  counters: device int32[batch], zero before the first call and left zero by every call (the blocks of a
+ * sequence count themselves there; the last one advances tail_len[s]).  A full window (tail_len[s] == tail_cap: the
+ * host skipped a flush) writes nothing and sets *status to 2 when status is not NULL (the decode workspace's first
+ * word: bmxk_check_workspace_status reports it). */
 int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_src, int src_dtype, int64_t stride_seq,
                               int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len,
-                              int32_t* status, int batch, int h_kv, int tail_cap, void* stream);
+                              int32_t* counters, int32_t* status, int batch, int h_kv, int tail_cap, void* stream);
 
 
 /* Reads back the status word of the last decode on this workspace (host-synchronising; for
