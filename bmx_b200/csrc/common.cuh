@@ -25,6 +25,27 @@ int check_launch(const char* what);
     }                                      \
   } while (0)
 
+// Launch configuration that belongs to a device (opt-in shared-memory sizes, the SM count) is kept per device: one
+// process may drive several GPUs, and cudaFuncSetAttribute only affects the device that is current when it is called.
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) d = 0;
+  return d;
+}
+// One flag per device; `test_and_set()` returns true the first time it is called with a given device current.  Two
+// threads racing on the first call both see true: what follows (setting an attribute) is idempotent.
+struct PerDeviceOnce {
+  volatile unsigned char done[MAX_DEVICES] = {};
+  bool first() {
+    const int d = current_device();
+    if (done[d]) return false;
+    done[d] = 1;
+    return true;
+  }
+  void retract() { done[current_device()] = 0; }  // the set-up failed: try again on the next call
+};
+
 // Device-side status word layout (int32[4], owned by the caller's workspace):
 //   [0] non-zero once any bounded wait gave up, [1] block that gave up, [2] where, [3] spare.
 constexpr int STATUS_WORDS = 4;

@@ -93,19 +93,19 @@ struct K2bDecodeParams {
   int n_stages;
 };
 
-__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int32_t* status, int where,
+                                             long long limit = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   // try_wait parks the warp for a hardware-chosen time per poll; the error flag and the clock are looked at
   // once in a while only.
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef BMXK_SLEEP_NS
-    __nanosleep(BMXK_SLEEP_NS);
-#endif
     if ((spin & 255u) == 0u) {
       if (*reinterpret_cast<volatile int32_t*>(status) != 0) return false;  // another wait already gave up
-      if (clock64() - t0 > 4000000000LL) {  // ~2 s at 2 GHz: a copy or an arrival was lost; report and leave
+      if (clock64() - t0 > limit) {  // a copy or an arrival was lost; report and leave
         if (atomicCAS(status, 0, 1) == 0) {
           status[1] = blockIdx.x;
           status[2] = where;

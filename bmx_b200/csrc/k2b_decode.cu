@@ -28,10 +28,6 @@
 
 #include "decode_common.cuh"
 
-#ifndef BMXK_SKIP
-#define BMXK_SKIP 0  // diagnostic builds only: bit mask of phases to leave out (results are then wrong)
-#endif
-
 namespace bmxk {
 
 constexpr int DEC_CONSUMER_WARPS = 8;
@@ -274,11 +270,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       //      so that the pipes overlap ----
       uint32_t VA[8][4];
       auto unpack_v = [&]() {
-        if (BMXK_SKIP & 1) {
-#pragma unroll
-          for (int mt = 0; mt < 8; ++mt) VA[mt][0] = VA[mt][1] = VA[mt][2] = VA[mt][3] = 0x3C003C00u;
-          return;
-        }
         const uint4 vw = *reinterpret_cast<const uint4*>(blk + k2b_off_vcode(PAGE, g.group) + (wr * 32 + lane) * 16);
         const uint32_t vv[4] = {vw.x, vw.y, vw.z, vw.w};
 #pragma unroll
@@ -326,10 +317,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int qd = 0; qd < 4; ++qd) {
-            if (BMXK_SKIP & 8) {
-              acc[4 * qd][c] = acc[4 * qd + 1][c] = acc[4 * qd + 2][c] = acc[4 * qd + 3][c] = sc[4 * qd] & 0x3FFF3FFFu;
-              continue;
-            }
             const uint32_t wlo = ww[c][qd], whi = ww[c][qd] >> 8;
             // (w & mask) ^ magic : nibble^8 under a 1024 (or 1024 + 16 x) exponent
             const __half2 h0 = u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u));
@@ -346,13 +333,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       }
       // ---- K_pre = coef x basis^T + residual ----
 #pragma unroll
-      for (int n = 0; n < ((BMXK_SKIP & 4) ? 0 : 16); ++n)
+      for (int n = 0; n < 16; ++n)
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks)
           mma_f16acc(acc[n][0], acc[n][1], A[ks][0], A[ks][1], A[ks][2], A[ks][3], Bb[n][ks][0], Bb[n][ks][1]);
       // ---- rotate by the offset inside the tile ----
 #pragma unroll
-      for (int c = 0; c < ((BMXK_SKIP & 2) ? 0 : 2); ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const __half2 lo = u32_as_h2(acc[n][c]), hi = u32_as_h2(acc[n + 8][c]);
@@ -369,7 +356,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
       {
         const uint4* qp = reinterpret_cast<const uint4*>(st + COEF_TILE_BYTES + PAGES_PER_TILE * PB) + lane;
 #pragma unroll
-        for (int k4 = 0; k4 < ((BMXK_SKIP & 16) ? 0 : 4); ++k4) {
+        for (int k4 = 0; k4 < 4; ++k4) {
           const uint4 v = qp[32 * k4];  // B fragments of k-steps 2*k4 and 2*k4+1
           mma_f32acc(S[0], S[1], S[2], S[3], acc[4 * k4][0], acc[4 * k4][1], acc[4 * k4 + 1][0], acc[4 * k4 + 1][1], v.x, v.y);
           mma_f32acc(S2[0], S2[1], S2[2], S2[3], acc[4 * k4 + 2][0], acc[4 * k4 + 2][1], acc[4 * k4 + 3][0], acc[4 * k4 + 3][1], v.z, v.w);
@@ -410,7 +397,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
         pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(w2, w3)));
       }
 #pragma unroll
-      for (int mt = 0; mt < ((BMXK_SKIP & 1) ? 1 : 8); ++mt)
+      for (int mt = 0; mt < 8; ++mt)
         mma_f32acc(O[mt][0], O[mt][1], O[mt][2], O[mt][3], VA[mt][0], VA[mt][1], VA[mt][2], VA[mt][3], pb0, pb1);
     }
     __syncwarp();
@@ -663,15 +650,29 @@ __global__ void merge_partials_kernel(const float* __restrict__ parts, int n_par
     reinterpret_cast<__half*>(out)[(int64_t)row * HEAD_DIM + ch] = __float2half_rn(r);
 }
 
-static int g_num_sms = 0;
-int num_sms() {
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (g_num_sms <= 0) g_num_sms = 148;
+// Self-test of the bounded wait every decode kernel uses: one warp waits on an mbarrier on which nothing ever arrives.
+// The wait must give up after `limit` cycles, record (block, site) in the status word and return, so that the
+// kernel ends and the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, long long limit, int site) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_barrier_init();
   }
-  return g_num_sms;
+  __syncthreads();
+  const bool ok = wait_or_flag(&bar, 0, status, site, limit);
+  if (threadIdx.x == 0) status[3] = ok ? 1 : 2;  // 2: the wait gave up, as it must
+}
+
+static int g_num_sms[MAX_DEVICES] = {};
+int num_sms() {
+  const int dev = current_device();
+  int n = g_num_sms[dev];
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_num_sms[dev] = n;
+  }
+  return n;
 }
 
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s, bool after_main) {
@@ -702,14 +703,14 @@ static size_t decode_fixed_smem(int batch) {
 
 template <int RANK, int PAGE>
 static int launch_decode(const K2bDecodeParams& prm, int grid, size_t smem, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(k2b_decode_kernel<RANK, PAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) {
+      configured.retract();
       set_error("bmxk_k2b_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return BMXK_ERR_CUDA;
     }
-    configured = true;
   }
   k2b_decode_kernel<RANK, PAGE><<<grid, DEC_THREADS, smem, s>>>(prm);
   return check_launch("bmxk_k2b_decode");
@@ -861,6 +862,26 @@ int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pa
   return bmxk_k2b_decode(g, q, pages, coefs, basis_f16, page_table, table_stride, n_pages, batch, max_pages, rope_cos,
                          rope_sin, pos_offset, k_tail, v_tail, tail_len, tail_cap, v_lut, signs, sm_scale, scratch,
                          (size_t)BMXK_STATIC_SCRATCH_BYTES, out, out_dtype, nullptr, 3, stream);
+}
+
+int bmxk_k2b_decode_static_status(void* stream) {
+  const int dev = current_device();
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    scratch = g_static_ptr[dev];
+  }
+  if (scratch == nullptr) return BMXK_OK;  // no call of bmxk_k2b_decode_static on this device yet: nothing to report
+  return bmxk_check_workspace_status(scratch, stream);
+}
+
+int bmxk_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, void* stream) {
+  BMXK_REQUIRE(status != nullptr, "bmxk_selftest_bounded_wait: null status word");
+  BMXK_REQUIRE(limit_cycles >= 1000 && limit_cycles <= 200000000LL,
+               "bmxk_selftest_bounded_wait: limit of %lld cycles outside [1e3, 2e8] (this test must end within a fraction of a second)",
+               (long long)limit_cycles);
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (long long)limit_cycles, 77);
+  return check_launch("bmxk_selftest_bounded_wait");
 }
 
 int bmxk_k2b_make_v_lut(const float* codebook, uint32_t* out_lut) {

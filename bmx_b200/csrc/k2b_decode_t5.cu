@@ -31,13 +31,6 @@
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
-#ifdef T5_TRACE  // diagnostic builds: event clocks of six tiles of block 0, written 1 MiB into the workspace (the caller makes it that large)
-#define TRACE(ev, n) do { if (blockIdx.x == 0 && (n) >= 40 && (n) < 46 && lane == 0) reinterpret_cast<volatile int*>(p.status)[262144 + ((n) - 40) * 16 + (ev)] = (int)clock64(); } while (0)
-#else
-#define TRACE(ev, n)
-#endif
-
-
 namespace bmxk {
 
 namespace {
@@ -190,7 +183,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             smem_add_release(&sh->ccnt, 1);
             sh->released = nC;
           }
-          TRACE(11, nC - 1);
           __syncwarp();
           progressed = true;
         }
@@ -205,7 +197,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
                      &sh->full[s]);
             bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[s]);
           }
-          TRACE(0, nP);
           __syncwarp();
           ++nP;
           if (nP < n_tiles) w.advance(npg_sm, g.h_kv, p.batch);
@@ -295,7 +286,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->full[s]);
-          TRACE(1, w.it);
         }
         if (++s == T5_STAGES) s = 0, ph ^= 1;
       }
@@ -332,7 +322,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             tc5::commit(smem_u32(&sh->sdone[b]));
             smem_add_release(&sh->bcnt, 1);
           }
-          TRACE(6, nB);
           __syncwarp();
           ++nB;
           progressed = true;
@@ -348,7 +337,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
             for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
-          TRACE(2, nA);
           __syncwarp();
           ++nA;
           progressed = true;
@@ -390,8 +378,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
       if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
       if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
-      if (warp == 0) TRACE(3, n);
-      if (warp == 7) TRACE(5, n);
       tc5::fence_after();
       uint32_t dl[2][8], dh[2][8];
       // a warp's TMEM loads complete one after the other, so the second chunk's are issued only after the first
@@ -441,8 +427,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
-      if (warp == 0) TRACE(4, n);
-      if (warp == 7) TRACE(12, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   } else if (warp < 16) {
@@ -512,7 +496,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
       if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
       if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
-      if (wq == 0) TRACE(7, n);
       if (alive) {
         tc5::fence_after();
         uint32_t r[GQ];
@@ -582,7 +565,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         tc5::fence_before();
         __syncwarp();
         if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
-        if (wq == 0) TRACE(8, n);
       }
       had = true, last_n = n;
     }
@@ -599,7 +581,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
       // the columns still feed U3 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
-      if (warp == 16) TRACE(9, n);
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
       {
@@ -628,7 +609,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
-      if (warp == 16) TRACE(10, n);
       if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
@@ -650,14 +630,14 @@ static size_t t5_smem_bytes(int rank, int group, int batch) {
 
 template <int RANK, int GQ>
 static int launch_t5(const K2bDecodeParams& prm, int grid, size_t smem, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(k2b_decode_t5_kernel<RANK, GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
+      configured.retract();
       set_error("bmxk_k2b_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return BMXK_ERR_CUDA;
     }
-    configured = true;
   }
   k2b_decode_t5_kernel<RANK, GQ><<<grid, T5_THREADS, smem, s>>>(prm);
   return check_launch("bmxk_k2b_decode(tcgen05)");

@@ -504,11 +504,10 @@ int bmxk_rtn_decode(const bmxk_rtn_geom* g, const void* q, const void* pages, co
     prm.g = to_rtn(g), prm.q = (const __half*)q, prm.pages = (const uint8_t*)pages, prm.page_table = page_table;
     prm.table_stride = table_stride, prm.n_pages = n_pages, prm.batch = batch, prm.scale_log2 = scale_log2, prm.part = part;
     const size_t smem = (size_t)(8 * 8 * HEAD_DIM + 128) * 4 + (size_t)(2 * batch + 1) * 4 + 16;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    if (configured.first()) {
       cudaFuncSetAttribute(rtn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
       cudaFuncSetAttribute(rtn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      configured = true;
     }
     BMXK_REQUIRE(smem <= 96 * 1024, "bmxk_rtn_decode: batch too large");
     if (g->page == 128) rtn_decode_kernel<128><<<grid, 256, smem, s>>>(prm);

@@ -157,13 +157,11 @@ int bmxk_spectral_append(const bmxk_spectral_geom* g, const void* k_pre, int src
   const int blocks = n_seq * n_pages * g->h_kv;
   const size_t smem = (size_t)g->page * HEAD_DIM * 4;
   cudaStream_t s = (cudaStream_t)stream;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(spectral_quant_page_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     cudaFuncSetAttribute(spectral_quant_page_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     cudaFuncSetAttribute(spectral_quant_page_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    cudaFuncSetAttribute(spectral_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    configured = true;
   }
   if (src_dtype == BMXK_DTYPE_F16)
     spectral_quant_page_kernel<__half><<<blocks, 128, smem, s>>>(gg, (const __half*)k_pre, stride_seq, stride_head, stride_tok, enc,
@@ -190,11 +188,8 @@ int bmxk_spectral_dequant_pages(const bmxk_spectral_geom* g, const void* pages, 
   BMXK_REQUIRE(n >= 0, "bmxk_spectral_dequant_pages: n < 0");
   if (n == 0) return BMXK_OK;
   BMXK_REQUIRE(pages && col_bits && col_off && slots && (!k_out || dec), "bmxk_spectral_dequant_pages: null pointer");
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(spectral_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (configured.first()) cudaFuncSetAttribute(spectral_dequant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
   spectral_dequant_kernel<<<n * g->h_kv, 128, (size_t)g->page * HEAD_DIM * 4, (cudaStream_t)stream>>>(
       to_s(g), (const uint8_t*)pages, dec, col_bits, col_off, slots, codes, scales, k_out);
   return check_launch("bmxk_spectral_dequant_pages");

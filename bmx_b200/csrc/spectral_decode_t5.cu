@@ -22,41 +22,13 @@
 #include "decode_common.cuh"
 #include "tc5.cuh"
 
-#ifndef S5_SKIP
-#define S5_SKIP 0  // diagnostic builds only: bit mask of phases to leave out (results are then wrong)
-#endif
-
 namespace bmxk {
 
 namespace {
 
-#ifndef S5_COMPACT
-#define S5_COMPACT 1
-#endif
-#if S5_COMPACT & 1
-#define S5_UNROLL_DQ _Pragma("unroll 1")
-#else
-#define S5_UNROLL_DQ _Pragma("unroll")
-#endif
-#if S5_COMPACT & 2
-#define S5_UNROLL_KEY _Pragma("unroll 1")
-#else
-#define S5_UNROLL_KEY _Pragma("unroll")
-#endif
-#if S5_COMPACT & 4
-#define S5_UNROLL_VAL _Pragma("unroll 1")
-#else
-#define S5_UNROLL_VAL _Pragma("unroll")
-#endif
-#ifndef S5_DQ_WARPS
-#define S5_DQ_WARPS 8
-#endif
-#ifndef S5_KEY_WARPS
-#define S5_KEY_WARPS 4  // 4: four key warps (all four chunks each) and eight value warps; 8: eight key warps, four value warps
-#endif
-constexpr int KEY_WARPS = S5_KEY_WARPS, VAL_WARPS = 12 - KEY_WARPS;
+constexpr int KEY_WARPS = 4, VAL_WARPS = 12 - KEY_WARPS;  // four key warps (all four chunks each), eight value warps
 constexpr int W_SOFT = KEY_WARPS, W_VAL = KEY_WARPS + 8;  // first softmax / value warp; dequant warps start at 20
-constexpr int DQ_WARPS = S5_DQ_WARPS;   // dequant warps: 4 or 8
+constexpr int DQ_WARPS = 8;            // dequant warps
 constexpr int SVC0 = 20 + DQ_WARPS;     // first of the four service warps: copy + U3, U1 + U2, two query rotation warps
 constexpr int S5_THREADS = (SVC0 + 4) * 32;  // key warps, 8 softmax warps (two sets), value warps (12 with the key warps), 20.. dequant, then service
 constexpr int S5_MAX_STAGES = 8;
@@ -378,7 +350,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           const int nks = sh->ksteps[sA];  // directions without bits sit last in tier order: their K steps are left out
           if (el) {
 #pragma unroll
-            for (int ks = 0; ks < ((S5_SKIP & 8) ? 1 : 8); ++ks)
+            for (int ks = 0; ks < 8; ++ks)
               if (ks < nks) tc5::mma_ss(tmem + TM_KD + 128 * b, da + 16 * ks, db + 16 * ks, ID_U1, ks > 0);
             tc5::commit(smem_u32(&sh->low[b]));
           }
@@ -417,8 +389,8 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       const int b = n & 1;
       if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
       tc5::fence_after();
-S5_UNROLL_KEY
-      for (int kk = 0; kk < ((S5_SKIP & 2) ? 0 : KCH); ++kk) {
+#pragma unroll
+      for (int kk = 0; kk < KCH; ++kk) {
         const int k = k0 + kk;
         uint32_t dl[8], dh[8], out[16];
         tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
@@ -591,8 +563,8 @@ S5_UNROLL_KEY
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
-S5_UNROLL_VAL
-      for (int cc = cc0; cc < ((S5_SKIP & 4) ? 0 : cc1); ++cc) {
+#pragma unroll
+      for (int cc = cc0; cc < cc1; ++cc) {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
@@ -653,7 +625,7 @@ S5_UNROLL_VAL
       const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
       const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
 #pragma unroll 1
-      for (int oo = 0; oo < ((S5_SKIP & 1) ? 0 : OCT); ++oo) {
+      for (int oo = 0; oo < OCT; ++oo) {
         const int o = DQ_WARPS * oo + wd;
         if (o >= n_oct) break;  // the same for the whole warp
         const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
@@ -677,7 +649,7 @@ S5_UNROLL_VAL
         const uint8_t* rowp = kb + off + wbase;
         const float* scp = scales + d * ngrp;
         const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
-S5_UNROLL_DQ
+#pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t r[4];
           const float scf = bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
@@ -710,14 +682,14 @@ S5_UNROLL_DQ
 
 template <int GQ>
 static int launch_s5(const SpectralDecodeParams& prm, int grid, size_t smem, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(spectral_decode_t5_kernel<GQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
+      configured.retract();
       set_error("bmxk_spectral_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return BMXK_ERR_CUDA;
     }
-    configured = true;
   }
   spectral_decode_t5_kernel<GQ><<<grid, S5_THREADS, smem, s>>>(prm);
   return check_launch("bmxk_spectral_decode");

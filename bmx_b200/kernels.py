@@ -64,7 +64,7 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise RuntimeError("bmxk kernels take CUDA tensors; there is no CPU path")
 
 
-DEFAULT_K2B_LAYOUT = int(__import__('os').environ.get('BMXK_K2B_LAYOUT', '1'))
+DEFAULT_K2B_LAYOUT = 1  # row order, read by the tcgen05 decode kernel
 
 
 def k2b_geom(h_kv: int, n_q_groups: int, page: int = 128, rank: int = 16, group: int = 64,
@@ -249,6 +249,19 @@ def k2b_decode_static(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, p
          pos_offset, _ptr(k_tail), _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut), _ptr(signs),
          ctypes.c_float(sm_scale), _ptr(out), _dtype_code(out), _stream())
     return out
+
+
+def k2b_decode_static_status() -> None:
+    """Raises BmxkError if a bounded wait of the last k2b_decode_static call on the current device ran out
+    (synchronises the current stream; allocates nothing)."""
+    call("bmxk_k2b_decode_static_status", _stream())
+
+
+def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> None:
+    """Launches the one-warp kernel that waits on a barrier nobody arrives on; status: zeroed device int32[4]."""
+    _require_cuda(status)
+    assert status.dtype == torch.int32 and status.numel() >= 4
+    call("bmxk_selftest_bounded_wait", _ptr(status), int(limit_cycles), _stream())
 
 
 def window_append(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor,

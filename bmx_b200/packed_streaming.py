@@ -110,6 +110,10 @@ class PackedStreamingLayer(DynamicLayer):
                  pack_v: bool = True, pack_k: bool = True, pack=None):
         super().__init__()
         self.k_spec, self.v_spec, self.model_config = k_spec, v_spec, model_config
+        if not (pack_v and pack_k):
+            # bmx keeps unpacked codes in int8 / int16 containers when these are False (a debugging aid of its Triton
+            # path, bmx: src/bmx/cache/packed_streaming.py:1087-1089); pages here exist in the packed form only
+            raise NotImplementedError("pack_k=False / pack_v=False: this library stores codes bit-packed only")
         self.recent_window, self.pack_v, self.pack_k = recent_window, pack_v, pack_k
         kind = FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
         if kind not in ("k2b", "spectral"):
@@ -330,8 +334,10 @@ class PackedStreamingCache(Cache):
         for i, mlayer in enumerate(resolve_decoder_layers(model)):
             mlayer.self_attn._packed_layer = self.layers[i]
             if self.k_spec.pre_rope:
-                def k_hook(module, inp, out, i=i):
-                    self.layers[i].stash_pre_rope(out)
+                wself = weakref.proxy(self)  # a hook that held the cache would keep its page pools alive with the model
+
+                def k_hook(module, inp, out, i=i, wself=wself):
+                    wself.layers[i].stash_pre_rope(out)
 
                 self._handles.append(resolve_k_capture_module(mlayer.self_attn).register_forward_hook(k_hook))
         return self

@@ -139,8 +139,10 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
  *  - the scratch is BMXK_STATIC_SCRATCH_BYTES (2 MiB) per GPU, resident from the moment the library is
  *    loaded on that GPU until the process exits; a call whose
  *    bmxk_k2b_decode_workspace_bytes(g, batch, max_pages) exceeds it is rejected with
- *    BMXK_ERR_INVALID and a message naming both sizes (2 MiB covers about 860 (sequence, KV head) pairs at 4
- *    query heads per KV head and about 350 at 8);
+ *    BMXK_ERR_INVALID and a message naming both sizes.  With 148 SMs the limit in (sequence, KV head) pairs is
+ *    (2 MiB - 256) / (n_sub * n_q_groups * 520) - 148, n_sub = 2 for layout 1 (the default for 128-token pages)
+ *    and 1 for layout 0: layout 1 holds 356 pairs at 4 query heads per KV head and 104 at 8; layout 0 holds 860
+ *    and 356;
  *  - the first call on each device looks up the scratch's device address (one cudaGetSymbolAddress,
  *    no allocation) with that device current; make that first call before any stream capture begins;
  *  - it calls no cudaMalloc / cudaFree and no allocating library routine; it issues one 256-byte
@@ -156,6 +158,13 @@ int bmxk_k2b_decode_static(const bmxk_k2b_geom* g, const void* q, const void* pa
                            const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
                            const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs,
                            float sm_scale, void* out, int out_dtype, void* stream);
+/* Status word of the built-in scratch on the current device (no counterpart in bmx).  The caller of
+ * bmxk_k2b_decode_static holds no workspace pointer, so bmxk_check_workspace_status cannot serve it: this
+ * reads the same four words from the built-in scratch (one 16-byte cudaMemcpyAsync on `stream` and a
+ * synchronisation of `stream`; no allocation) and returns BMXK_ERR_DEVICE, with the site in bmxk_last_error(),
+ * if a bounded wait of the last bmxk_k2b_decode_static call ran out.  The next call clears the word, so check
+ * after the call whose result matters.  Before the first bmxk_k2b_decode_static call on a device: BMXK_OK. */
+int bmxk_k2b_decode_static_status(void* stream);
 
 /* Host helper: fp16 lookup table for the value codebook.  Picks four fp16 levels h_i and an
  * affine map so that codebook[i] = alpha + beta * h_i to ~1e-6, which lets the kernel feed
@@ -301,6 +310,14 @@ int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_s
 /* Reads back the status word of the last decode on this workspace (host-synchronising; for
  * tests and diagnostics).  Returns BMXK_ERR_DEVICE if a bounded wait ran out. */
 int bmxk_check_workspace_status(const void* workspace, void* stream);
+
+/* Self-test of the bounded device waits (no counterpart in bmx).  Every wait inside the decode kernels (on a bulk
+ * copy, a tensor-core completion or another warp) gives up after a cycle limit, writes (1, block, site) to the status
+ * word and lets the kernel end, so that a lost arrival costs an error code and not the GPU.  This launches one warp
+ * that waits, with that same routine, on a barrier nothing ever arrives on; after `limit_cycles` (1e3 .. 2e8 SM
+ * cycles, i.e. at most ~0.1 s) it must return with status = {1, 0, 77, 2}.  status: device int32[4], zeroed by the
+ * caller; read it with bmxk_check_workspace_status, which must then return BMXK_ERR_DEVICE. */
+int bmxk_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }
