@@ -11,135 +11,313 @@ namespace bmxk {
 
 __device__ __forceinline__ float half_round(float x) { return __half2float(__float2half_rn(x)); }
 
+// Four consecutive source elements as float32 (exact for every source type).  `vec`: the address is aligned for one
+// wide load (the host checks base pointer and strides once per call).
+template <typename T>
+__device__ __forceinline__ void load4_as_float(const T* p, bool vec, float (&f)[4]);
+template <>
+__device__ __forceinline__ void load4_as_float<__half>(const __half* p, bool vec, float (&f)[4]) {
+  if (vec) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(u32_as_h2(u.x)), b = __half22float2(u32_as_h2(u.y));
+    f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) f[k] = __half2float(p[k]);
+  }
+}
+template <>
+__device__ __forceinline__ void load4_as_float<__nv_bfloat16>(const __nv_bfloat16* p, bool vec, float (&f)[4]) {
+  if (vec) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    f[0] = __uint_as_float(u.x << 16), f[1] = __uint_as_float(u.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(u.y << 16), f[3] = __uint_as_float(u.y & 0xFFFF0000u);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) f[k] = __bfloat162float(p[k]);
+  }
+}
+template <>
+__device__ __forceinline__ void load4_as_float<float>(const float* p, bool vec, float (&f)[4]) {
+  if (vec) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x, f[1] = u.y, f[2] = u.z, f[3] = u.w;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) f[k] = p[k];
+  }
+}
+
+constexpr int KF_STRIDE = 132;  // floats per staged key row: consecutive rows start 16 bytes apart modulo 128
+                                // (4 consecutive rows x one 128-bit load each fall in distinct bank groups)
+
 // ---------------------------------------------------------------------------------------------
 // Projection  Us = M @ V  (bmx: src/bmx/cache/packed_streaming.py:518-520), rounded to fp16 and
-// written to the coefficient block.  One block per (item, coef head); thread -> (row, i).
-// Order: acc = 0; for c ascending: acc = fmaf(M[r,c], V[c,i], acc).
+// written to the coefficient block, for a basis that spans several heads (the fused page kernel below
+// projects by itself when every head has its own basis).  One block per (item, coef head, 32 rows);
+// thread -> (row, four consecutive i).  Order per output: acc = 0; heads ascending, c ascending:
+// acc = fmaf(M[r,c], V[c,i], acc).  Each head's 32 x 128 key rows and 128 x rank basis slice are staged
+// in shared memory so that global loads are coalesced and every operand is read with 128-bit loads.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void k2b_project_kernel(K2bGeom g, const T* __restrict__ k_pre, int64_t stride_seq, int64_t stride_head,
                                    int64_t stride_tok, const float* __restrict__ basis, const int32_t* __restrict__ slots,
-                                   int n_pages, __half* __restrict__ coefs) {
-  const int item = blockIdx.x / g.n_coef_heads, ch = blockIdx.x % g.n_coef_heads;
+                                   int n_pages, __half* __restrict__ coefs, int vec) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* ks = reinterpret_cast<float*>(smem);   // [32][KF_STRIDE]
+  float* bs = ks + 32 * KF_STRIDE;              // [128][rank]
+  const int rank = g.rank, IQ = rank >> 2, n_rb = g.page >> 5;
+  int blk = blockIdx.x;
+  const int rb = blk % n_rb;
+  blk /= n_rb;
+  const int ch = blk % g.n_coef_heads, item = blk / g.n_coef_heads;
   const int seq = item / n_pages, pg = item % n_pages;
   const int slot = slots[item];
   const int h0 = (g.n_coef_heads == 1) ? 0 : ch, nh = (g.n_coef_heads == 1) ? g.h_kv : 1;
-  __half* out = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (g.page * g.rank);
-  const T* src = k_pre + seq * stride_seq + (int64_t)pg * g.page * stride_tok;
-  for (int o = threadIdx.x; o < g.page * g.rank; o += blockDim.x) {
-    const int r = o / g.rank, i = o % g.rank;
-    float acc = 0.f;
-    for (int h = h0; h < h0 + nh; ++h) {
-      const T* row = src + h * stride_head + r * stride_tok;
-      const float* b = basis + (int64_t)h * HEAD_DIM * g.rank + i;
-      for (int c = 0; c < HEAD_DIM; ++c) acc = fmaf(load_as_float<T>(row + c), b[(int64_t)c * g.rank], acc);
+  const int tid = threadIdx.x, rl = tid / IQ, iq = tid % IQ;
+  const T* src = k_pre + seq * stride_seq + ((int64_t)pg * g.page + rb * 32) * stride_tok;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int h = h0; h < h0 + nh; ++h) {
+    for (int o = tid; o < 32 * 32; o += blockDim.x) {
+      const int r = o >> 5, c4 = o & 31;
+      float f[4];
+      load4_as_float<T>(src + h * stride_head + r * stride_tok + 4 * c4, vec != 0, f);
+      *reinterpret_cast<float4*>(ks + r * KF_STRIDE + 4 * c4) = make_float4(f[0], f[1], f[2], f[3]);
     }
-    out[k2b_coef_idx(g.layout, r, i, g.rank)] = __float2half_rn(acc);
+    const float4* bsrc = reinterpret_cast<const float4*>(basis + (int64_t)h * HEAD_DIM * rank);
+    for (int o = tid; o < HEAD_DIM * IQ; o += blockDim.x) reinterpret_cast<float4*>(bs)[o] = bsrc[o];
+    __syncthreads();
+#pragma unroll 4
+    for (int c4 = 0; c4 < 32; ++c4) {
+      const float4 m = *reinterpret_cast<const float4*>(ks + rl * KF_STRIDE + 4 * c4);
+      const float mm[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float4 vv = *reinterpret_cast<const float4*>(bs + (4 * c4 + k) * rank + 4 * iq);
+        acc[0] = fmaf(mm[k], vv.x, acc[0]), acc[1] = fmaf(mm[k], vv.y, acc[1]);
+        acc[2] = fmaf(mm[k], vv.z, acc[2]), acc[3] = fmaf(mm[k], vv.w, acc[3]);
+      }
+    }
+    __syncthreads();
   }
+  __half* out = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (g.page * rank);
+  const int r = rb * 32 + rl;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) out[k2b_coef_idx(g.layout, r, 4 * iq + j, rank)] = __float2half_rn(acc[j]);
 }
 
 // ---------------------------------------------------------------------------------------------
-// Page quantizer.  One block of 128 threads per (item, kv head).
-//   keys  : thread = channel.  L[r,c] = sum_i Us16[r,i] V16[c,i] (fmaf, i ascending), R = M - L,
-//           per group of `group` tokens scale = max(absmax, 1e-12) / qmax, code = rint(R / scale)
-//           clamped to [-qmax-1, qmax]   (bmx: src/bmx/cache/codecs.py:677-695, src/bmx/quant/rtn.py:34-44)
-//   values: warp = token.   n = fp16(max(sqrt(sum v^2), 1e-12)); u = v / n; y = fwht(u * signs);
+// Page quantizer.  One block of 256 threads per (item, kv head); two blocks share an SM.
+//   staging: the head's key page (float32, KF_STRIDE per row) and its basis slice go to shared memory.
+//   coefficients (FUSED: one basis per head): thread = (row slot, four i), ROWS rows each;
+//           Us[r,i] = fmaf chain over c ascending, rounded to fp16, written to the coefficient block.
+//           Otherwise the coefficients come from the coefficient block the projection kernel wrote.
+//   keys  : thread = (channel, half of the page).  L[r,c] = sum_i Us16[r,i] V16[c,i] (fmaf, i ascending), R = M - L
+//           is computed ONCE and kept in registers; per group of `group` tokens scale = max(absmax, 1e-12) / qmax,
+//           code = rint(R / scale) clamped to [-qmax-1, qmax]
+//           (bmx: src/bmx/cache/codecs.py:677-695, src/bmx/quant/rtn.py:34-44)
+//   values: warp = token, two tokens in flight.  n = fp16(max(sqrt(sum v^2), 1e-12)); u = v / n; y = fwht(u * signs);
 //           idx = #{mid_k < y * sqrt(128)}        (bmx: src/bmx/cache/codecs.py:616-636)
-// Codes are staged in shared memory and then assembled into whole 32-bit words of the native layout.
+// Codes are staged in shared memory (over the key page, which is dead by then) and assembled into whole
+// 32-bit words of the native layout.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(128) k2b_quant_page_kernel(K2bGeom g, const T* __restrict__ k_pre,
-                                                             const T* __restrict__ v, int64_t stride_seq,
-                                                             int64_t stride_head, int64_t stride_tok,
-                                                             const float* __restrict__ basis,
-                                                             const float* __restrict__ signs,
-                                                             const float* __restrict__ codebook,
-                                                             const int32_t* __restrict__ slots, int n_pages,
-                                                             uint8_t* __restrict__ pages, const __half* __restrict__ coefs) {
+constexpr int QP_THREADS = 256;
+// floats of the region that first holds the basis slice and the coefficients and later the two code buffers
+__host__ __device__ constexpr int quant_region_floats(int page, int rank) {
+  return (HEAD_DIM * (rank + 4) + page * rank) > (2 * page * HEAD_DIM / 4) ? (HEAD_DIM * (rank + 4) + page * rank) : (2 * page * HEAD_DIM / 4);
+}
+
+template <typename T, int PAGE, bool FUSED>
+__global__ void __launch_bounds__(QP_THREADS, 2) k2b_quant_page_kernel(K2bGeom g, const T* __restrict__ k_pre,
+                                                                        const T* __restrict__ v, int64_t stride_seq,
+                                                                        int64_t stride_head, int64_t stride_tok,
+                                                                        const float* __restrict__ basis,
+                                                                        const float* __restrict__ signs,
+                                                                        const float* __restrict__ codebook,
+                                                                        const int32_t* __restrict__ slots, int n_pages,
+                                                                        uint8_t* __restrict__ pages, __half* __restrict__ coefs,
+                                                                        int vec) {
   extern __shared__ __align__(16) uint8_t smem[];
-  int8_t* kcode = reinterpret_cast<int8_t*>(smem);                     // [page][128]
-  uint8_t* vcode = smem + g.page * HEAD_DIM;                            // [page][128]
-  float* us = reinterpret_cast<float*>(smem + 2 * g.page * HEAD_DIM);   // [page][rank]
+  constexpr int HALF_ROWS = PAGE / 2, SUBS = PAGE / 32;  // rows per thread in the key phase; 32-row sub-blocks
+  const int rank = g.rank, group = g.group, BS = rank + 4;  // basis rows padded: eight consecutive rows, one 128-bit load each, conflict free
+  float* kf = reinterpret_cast<float*>(smem);                 // [PAGE][KF_STRIDE] key page, overwritten in place by the residual
+  float* bs = kf + PAGE * KF_STRIDE;                           // [128][rank + 4] basis slice (float32)
+  float* us = bs + HEAD_DIM * BS;                              // [PAGE][rank] fp16-valued coefficients
+  int8_t* kcode = reinterpret_cast<int8_t*>(bs);               // [PAGE][128]   } over the basis and the coefficients
+  uint8_t* vcode = reinterpret_cast<uint8_t*>(bs) + PAGE * HEAD_DIM;  // [PAGE][128] } once they are dead
+  float* amax_s = bs + quant_region_floats(PAGE, rank);        // [SUBS][128] absmax of 32-row sub-blocks
 
   const int item = blockIdx.x / g.h_kv, h = blockIdx.x % g.h_kv;
   const int seq = item / n_pages, pg = item % n_pages;
   const int slot = slots[item];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int page = g.page, rank = g.rank, group = g.group;
   const int ch = (g.n_coef_heads == 1) ? 0 : h;
-  const __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (page * rank);
-  uint8_t* blk = pages + ((int64_t)slot * g.h_kv + h) * k2b_page_block_bytes(page, group);
-  const T* ksrc = k_pre + seq * stride_seq + h * stride_head + (int64_t)pg * page * stride_tok;
-  const T* vsrc = v + seq * stride_seq + h * stride_head + (int64_t)pg * page * stride_tok;
+  __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (PAGE * rank);
+  uint8_t* blk = pages + ((int64_t)slot * g.h_kv + h) * k2b_page_block_bytes(PAGE, group);
+  const T* ksrc = k_pre + seq * stride_seq + h * stride_head + (int64_t)pg * PAGE * stride_tok;
+  const T* vsrc = v + seq * stride_seq + h * stride_head + (int64_t)pg * PAGE * stride_tok;
 
-  for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
+  // ---- staging ----
+  for (int o0 = 0; o0 < PAGE * 32; o0 += QP_THREADS * 8) {
+    float f[8][4];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {  // eight wide loads in flight per thread
+      const int o = o0 + u * QP_THREADS + tid, r = o >> 5, c4 = o & 31;
+      load4_as_float<T>(ksrc + r * stride_tok + 4 * c4, vec != 0, f[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int o = o0 + u * QP_THREADS + tid, r = o >> 5, c4 = o & 31;
+      *reinterpret_cast<float4*>(kf + r * KF_STRIDE + 4 * c4) = make_float4(f[u][0], f[u][1], f[u][2], f[u][3]);
+    }
+  }
+  {
+    const float4* bsrc = reinterpret_cast<const float4*>(basis + (int64_t)h * HEAD_DIM * rank);
+    const int IQ = rank >> 2;
+    for (int o = tid; o < HEAD_DIM * IQ; o += QP_THREADS) {
+      const int c = o / IQ, i4 = o % IQ;
+      *reinterpret_cast<float4*>(bs + c * BS + 4 * i4) = bsrc[o];
+    }
+  }
+  if (!FUSED)
+    for (int o = tid; o < PAGE * rank; o += QP_THREADS) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
   __syncthreads();
 
-  // ---- keys: thread = channel ----
+  // ---- coefficients (one basis per head) ----
+  if (FUSED) {
+    const int IQ = rank >> 2, slots_r = QP_THREADS / IQ;  // 32 (rank 32) or 64 (rank 16) rows in flight
+    const int rs = tid / IQ, iq = tid % IQ;
+    for (int r0 = 0; r0 < PAGE; r0 += 4 * slots_r) {      // up to four rows per thread and pass
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+#pragma unroll 2
+      for (int c4 = 0; c4 < 32; ++c4) {
+        float mm[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const int r = min(r0 + a * slots_r + rs, PAGE - 1);
+          const float4 m = *reinterpret_cast<const float4*>(kf + r * KF_STRIDE + 4 * c4);
+          mm[a][0] = m.x, mm[a][1] = m.y, mm[a][2] = m.z, mm[a][3] = m.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 vv = *reinterpret_cast<const float4*>(bs + (4 * c4 + k) * BS + 4 * iq);
+#pragma unroll
+          for (int a = 0; a < 4; ++a) {
+            acc[a][0] = fmaf(mm[a][k], vv.x, acc[a][0]), acc[a][1] = fmaf(mm[a][k], vv.y, acc[a][1]);
+            acc[a][2] = fmaf(mm[a][k], vv.z, acc[a][2]), acc[a][3] = fmaf(mm[a][k], vv.w, acc[a][3]);
+          }
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const int r = r0 + a * slots_r + rs;
+        if (r < PAGE) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __half hv = __float2half_rn(acc[a][j]);
+            us[r * rank + 4 * iq + j] = __half2float(hv);
+            cblk[k2b_coef_idx(g.layout, r, 4 * iq + j, rank)] = hv;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- keys: thread = (channel, half of the page); the residuals stay in registers ----
   {
-    const int c = tid;
+    const int c = tid & 127, hf = tid >> 7, r_base = hf * HALF_ROWS;
     float vb[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) vb[i] = (i < rank) ? half_round(basis[((int64_t)h * HEAD_DIM + c) * rank + i]) : 0.f;
-    const float qmax = (float)((1 << (g.kbits - 1)) - 1);
-    __half* kscale = reinterpret_cast<__half*>(blk + k2b_off_kscale(page));
-    for (int grp = 0; grp < page / group; ++grp) {
-      float amax = 0.f;
-      for (int r = grp * group; r < (grp + 1) * group; ++r) {
-        float L = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < rank) L = fmaf(us[r * rank + i], vb[i], L);
-        const float R = load_as_float<T>(ksrc + r * stride_tok + c) - L;
-        amax = fmaxf(amax, fabsf(R));
+    for (int i4 = 0; i4 < 8; ++i4) {
+      if (4 * i4 < rank) {
+        const float4 t = *reinterpret_cast<const float4*>(bs + c * BS + 4 * i4);
+        vb[4 * i4] = half_round(t.x), vb[4 * i4 + 1] = half_round(t.y), vb[4 * i4 + 2] = half_round(t.z), vb[4 * i4 + 3] = half_round(t.w);
+      } else {
+        vb[4 * i4] = vb[4 * i4 + 1] = vb[4 * i4 + 2] = vb[4 * i4 + 3] = 0.f;
       }
-      const float scale = fmaxf(amax, 1e-12f) / qmax;
-      kscale[k2b_kscale_idx(g.layout, grp, c)] = __float2half_rn(scale);
-      for (int r = grp * group; r < (grp + 1) * group; ++r) {
+    }
+#pragma unroll
+    for (int sb = 0; sb < HALF_ROWS / 32; ++sb) {
+      float am = 0.f;
+#pragma unroll 4
+      for (int rr = 0; rr < 32; ++rr) {
+        const int r = r_base + 32 * sb + rr;
         float L = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < rank) L = fmaf(us[r * rank + i], vb[i], L);
-        const float R = load_as_float<T>(ksrc + r * stride_tok + c) - L;
-        float q = rintf(R / scale);
+        for (int i4 = 0; i4 < 8; ++i4)
+          if (4 * i4 < rank) {
+            const float4 u = *reinterpret_cast<const float4*>(us + r * rank + 4 * i4);
+            L = fmaf(u.x, vb[4 * i4], L), L = fmaf(u.y, vb[4 * i4 + 1], L), L = fmaf(u.z, vb[4 * i4 + 2], L), L = fmaf(u.w, vb[4 * i4 + 3], L);
+          }
+        const float res = kf[r * KF_STRIDE + c] - L;
+        kf[r * KF_STRIDE + c] = res;  // this thread is the only one that touches column c of these rows
+        am = fmaxf(am, fabsf(res));
+      }
+      amax_s[(hf * (HALF_ROWS / 32) + sb) * HEAD_DIM + c] = am;
+    }
+    __syncthreads();  // basis and coefficients are dead from here on: the code buffers may overwrite them
+    const float qmax = (float)((1 << (g.kbits - 1)) - 1);
+    __half* kscale = reinterpret_cast<__half*>(blk + k2b_off_kscale(PAGE));
+    const int subs_per_group = group >> 5;
+#pragma unroll
+    for (int sb = 0; sb < HALF_ROWS / 32; ++sb) {
+      const int gsb = hf * (HALF_ROWS / 32) + sb, grp = gsb / subs_per_group;
+      float amax = 0.f;
+      for (int k = 0; k < subs_per_group; ++k) amax = fmaxf(amax, amax_s[(grp * subs_per_group + k) * HEAD_DIM + c]);
+      const float scale = fmaxf(amax, 1e-12f) / qmax;
+      if (gsb == grp * subs_per_group) kscale[k2b_kscale_idx(g.layout, grp, c)] = __float2half_rn(scale);
+#pragma unroll 8
+      for (int rr = 0; rr < 32; ++rr) {
+        const int r = r_base + 32 * sb + rr;
+        float q = rintf(kf[r * KF_STRIDE + c] / scale);
         q = fminf(fmaxf(q, -qmax - 1.f), qmax);
         kcode[r * HEAD_DIM + c] = (int8_t)q;
       }
     }
+    (void)SUBS;
   }
-  // ---- values: warp = token ----
+  // ---- values: warp = token, two tokens in flight ----
   {
     const float c0 = codebook[0], c1 = codebook[1], c2 = codebook[2], c3 = codebook[3];
     const float m0 = (c0 + c1) / 2.f, m1 = (c1 + c2) / 2.f, m2 = (c2 + c3) / 2.f;
     float sg[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) sg[k] = signs[4 * lane + k];
-    __half* vnorm = reinterpret_cast<__half*>(blk + k2b_off_vnorm(page, group));
-    for (int r = warp; r < page; r += 4) {
-      float x[4];
+    __half* vnorm = reinterpret_cast<__half*>(blk + k2b_off_vnorm(PAGE, group));
+    constexpr int NW = QP_THREADS / 32;
+    for (int r0 = warp; r0 < PAGE; r0 += 2 * NW) {
+      float x[2][4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = load_as_float<T>(vsrc + r * stride_tok + 4 * lane + k);
-      float ss = 0.f;
+      for (int u = 0; u < 2; ++u) load4_as_float<T>(vsrc + (r0 + u * NW) * stride_tok + 4 * lane, vec != 0, x[u]);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) ss = fmaf(x[k], x[k], ss);
+      for (int u = 0; u < 2; ++u) {
+        const int r = r0 + u * NW;
+        float ss = 0.f;
 #pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, m);
-      const float n = half_round(fmaxf(sqrtf(ss), 1e-12f));
+        for (int k = 0; k < 4; ++k) ss = fmaf(x[u][k], x[u][k], ss);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) x[k] = (x[k] / n) * sg[k];
-      fwht128_warp(x, lane);
-      const float sqrt_d = 11.313708498984761f;
-      uint32_t packed4 = 0;
+        for (int m = 16; m >= 1; m >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, m);
+        const float n = half_round(fmaxf(sqrtf(ss), 1e-12f));
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float y = x[k] * sqrt_d;
-        const uint32_t idx = (y > m0) + (y > m1) + (y > m2);
-        packed4 |= idx << (8 * k);
+        for (int k = 0; k < 4; ++k) x[u][k] = (x[u][k] / n) * sg[k];
+        fwht128_warp(x[u], lane);
+        const float sqrt_d = 11.313708498984761f;
+        uint32_t packed4 = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float y = x[u][k] * sqrt_d;
+          const uint32_t idx = (y > m0) + (y > m1) + (y > m2);
+          packed4 |= idx << (8 * k);
+        }
+        *reinterpret_cast<uint32_t*>(vcode + r * HEAD_DIM + 4 * lane) = packed4;
+        if (lane == 0) vnorm[r] = __float2half_rn(n);
       }
-      *reinterpret_cast<uint32_t*>(vcode + r * HEAD_DIM + 4 * lane) = packed4;
-      if (lane == 0) vnorm[r] = __float2half_rn(n);
     }
   }
+  const int page = PAGE;
   __syncthreads();
   // ---- assemble native words ----
   uint32_t* kres = reinterpret_cast<uint32_t*>(blk);
@@ -333,21 +511,55 @@ static K2bGeom to_geom(const bmxk_k2b_geom* g) {
   return o;
 }
 
+static size_t quant_smem_bytes(int page, int rank) {
+  return ((size_t)page * KF_STRIDE + (size_t)quant_region_floats(page, rank) + (size_t)(page / 32) * HEAD_DIM) * sizeof(float);
+}
+
+template <typename T, int PAGE, bool FUSED>
+static int launch_quant(const K2bGeom& gg, const T* k_pre, const T* v, int64_t ss, int64_t sh, int64_t st, const float* basis,
+                        const float* signs, const float* codebook, const int32_t* slots, int items, int n_pages, uint8_t* pages,
+                        __half* coefs, int vec, cudaStream_t s) {
+  const size_t smem = quant_smem_bytes(PAGE, gg.rank);
+  static PerDeviceOnce configured;
+  if (configured.first()) {
+    cudaError_t e = cudaFuncSetAttribute(k2b_quant_page_kernel<T, PAGE, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    if (e != cudaSuccess) {
+      configured.retract();
+      set_error("bmxk_k2b_append: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return BMXK_ERR_CUDA;
+    }
+  }
+  k2b_quant_page_kernel<T, PAGE, FUSED><<<items * gg.h_kv, QP_THREADS, smem, s>>>(gg, k_pre, v, ss, sh, st, basis, signs, codebook, slots,
+                                                                                n_pages, pages, coefs, vec);
+  return check_launch("bmxk_k2b_append(quantize)");
+}
+
 template <typename T>
 static int append_impl(const bmxk_k2b_geom* g, const void* k_pre, const void* v, int64_t ss, int64_t sh, int64_t st,
                        const float* basis, const float* signs, const float* codebook, const int32_t* slots, int n_seq,
                        int n_pages, void* pages, void* coefs, cudaStream_t s) {
   const K2bGeom gg = to_geom(g);
   const int items = n_seq * n_pages;
-  k2b_project_kernel<T><<<items * g->n_coef_heads, 256, 0, s>>>(gg, (const T*)k_pre, ss, sh, st, basis, slots, n_pages,
-                                                                 (__half*)coefs);
-  int rc = check_launch("bmxk_k2b_append(project)");
-  if (rc) return rc;
-  const size_t smem = 2 * g->page * HEAD_DIM + (size_t)g->page * g->rank * 4;
-  k2b_quant_page_kernel<T><<<items * g->h_kv, 128, smem, s>>>(gg, (const T*)k_pre, (const T*)v, ss, sh, st, basis, signs,
-                                                              codebook, slots, n_pages, (uint8_t*)pages,
-                                                              (const __half*)coefs);
-  return check_launch("bmxk_k2b_append(quantize)");
+  // one wide load per four source elements needs every row start aligned to it
+  const uintptr_t align = 4 * sizeof(T);
+  const bool vec = ((uintptr_t)k_pre % align == 0) && ((uintptr_t)v % align == 0) && (ss * sizeof(T)) % align == 0 &&
+                   (sh * sizeof(T)) % align == 0 && (st * sizeof(T)) % align == 0 && ((uintptr_t)basis % 16 == 0);
+  const bool fused = g->n_coef_heads == g->h_kv;  // one basis per head: the page kernel projects by itself
+  if (!fused) {
+    BMXK_REQUIRE((uintptr_t)basis % 16 == 0, "bmxk_k2b_append: basis must be 16-byte aligned");
+    const size_t psmem = ((size_t)32 * KF_STRIDE + (size_t)HEAD_DIM * g->rank) * sizeof(float);
+    k2b_project_kernel<T><<<items * g->n_coef_heads * (g->page / 32), 8 * g->rank, psmem, s>>>(
+        gg, (const T*)k_pre, ss, sh, st, basis, slots, n_pages, (__half*)coefs, vec ? 1 : 0);
+    int rc = check_launch("bmxk_k2b_append(project)");
+    if (rc) return rc;
+  }
+  BMXK_REQUIRE((uintptr_t)basis % 16 == 0, "bmxk_k2b_append: basis must be 16-byte aligned");
+#define BMXK_LAUNCH_QUANT(PAGE, FUSED)                                                                                              \
+  launch_quant<T, PAGE, FUSED>(gg, (const T*)k_pre, (const T*)v, ss, sh, st, basis, signs, codebook, slots, items, n_pages, \
+                               (uint8_t*)pages, (__half*)coefs, vec ? 1 : 0, s)
+  if (g->page == 128) return fused ? BMXK_LAUNCH_QUANT(128, true) : BMXK_LAUNCH_QUANT(128, false);
+  return fused ? BMXK_LAUNCH_QUANT(64, true) : BMXK_LAUNCH_QUANT(64, false);
+#undef BMXK_LAUNCH_QUANT
 }
 
 }  // namespace bmxk

@@ -408,225 +408,224 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) k2b_decode_kernel(const K2bDec
 }
 
 // ---------------------------------------------------------------------------------------------
-// Merge: one block of 128 threads per (sequence, KV head).
-//   1. attention over the fp16 recent window (keys already RoPE'd), as one more partial
+// Merge: one block of 256 threads per (sequence, KV head, query head).
+//   1. attention over the fp16 recent window (keys already RoPE'd), as one more partial state
 //      (bmx: src/bmx/cache/triton_dequant_attention.py:324-360)
-//   2. combine with the decode kernel's partials of this (sequence, head)
-//      (bmx: :409-461; maxima are in log2 units on both sides)
-//   3. undo the value rotation of the packed part: signs * fwht(acc) / sqrt(128)
+//   2. the page-streaming kernel's partial records of this (sequence, head), folded by an online
+//      softmax over records (bmx: :409-461; maxima are in log2 units on both sides)
+//   3. the inverse value rotation of the packed part: signs * fwht(acc) / sqrt(128)
+// The kernel is bound by the latency of its dependent global loads, not by bytes: it is laid out so that one
+// (sequence, head, query) costs two load round trips before the grid dependency (window keys, window values)
+// and one after it (all partial records of a thread in flight together).
 // ---------------------------------------------------------------------------------------------
-constexpr int MERGE_THREADS = 512;
-constexpr int MERGE_SPLIT = MERGE_THREADS / 128;  // token ranges of the window accumulation
+constexpr int MERGE_THREADS = 256;
 
-// GQ = 4 or 8: an upper bound of the group size known at compile time, so that the per-query loops carry no
-// predicated-off iterations (they would still be issued).
-template <int GQ>
-__global__ void __launch_bounds__(MERGE_THREADS) k2b_merge_kernel(const K2bMergeParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(MERGE_THREADS, 2) k2b_merge_kernel(const K2bMergeParams p) {
+  extern __shared__ __align__(16) float msm[];
   const K2bGeom g = p.g;
   const int G = g.n_q_groups;
-  float* sc = reinterpret_cast<float*>(smem);            // [tail_cap][GQ] scores, then weights
-  float* accs = sc + GQ * p.tail_cap;                     // [G][128] rotated accumulators
-  float* atl = accs + G * HEAD_DIM;                       // [MERGE_SPLIT][G][128] window accumulators
-  float* qs = atl + MERGE_SPLIT * G * HEAD_DIM;                     // [G][128] scaled queries
-  float* redm = qs + G * HEAD_DIM;                        // [16 warps][8] partial max / sum
-  float* tm = redm + 128;                                  // [8] window max, [8] window sum
-  int* cum = reinterpret_cast<int*>(tm + 16);             // [batch + 1]
-  float* fin = reinterpret_cast<float*>(cum + p.batch + 1);  // [8] overall max, [8] sum, [8] weight of the window
-  float* fw = fin + 24;                                    // [G][n_sub * main_grid] weights of the partial records
+  const int cap4 = (p.tail_cap + 3) & ~3;
+  float* sc = msm;             // [tail_cap] window scores, then weights
+  float* qs = sc + cap4;       // [128] scaled query
+  float* red = qs + HEAD_DIM;  // [16][128] window accumulators per token group; later [2][128] record halves
+  float* atl = red + 16 * HEAD_DIM;  // [128] window accumulator
+  float* sm = atl + HEAD_DIM;  // [32]: warp maxima [0..7], warp sums [8..15], record states [16..19]
+  int* si = reinterpret_cast<int*>(sm + 32);  // tiles before this sequence, tiles in all
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int b = blockIdx.x / g.h_kv, h = blockIdx.x % g.h_kv;
-  const int bh = b * g.h_kv + h;
+  const int qi = blockIdx.x % G, bh = blockIdx.x / G, b = bh / g.h_kv, h = bh % g.h_kv;
 
-  if (warp == 0) fill_cum(cum, p.n_pages, p.batch, g.h_kv, g.page, lane);
-  const __half* qsrc = p.q + (int64_t)bh * G * HEAD_DIM;
-  for (int i = tid; i < G * HEAD_DIM; i += MERGE_THREADS) qs[i] = __half2float(qsrc[i]) * p.scale_log2;
+  if (warp == 0) {
+    int pre = 0, tot = 0;
+    for (int i = lane; i < p.batch; i += 32) {
+      const int t = tiles_of(p.n_pages[i], g.page) * g.h_kv;
+      tot += t;
+      if (i < b) pre += t;
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) pre += __shfl_xor_sync(0xffffffffu, pre, m), tot += __shfl_xor_sync(0xffffffffu, tot, m);
+    if (lane == 0) si[0] = pre, si[1] = tot;
+  }
+  if (tid < HEAD_DIM) qs[tid] = __half2float(p.q[((int64_t)bh * G + qi) * HEAD_DIM + tid]) * p.scale_log2;
   __syncthreads();
-  const int total = cum[p.batch];
-  const int per_cta = max(1, (total + p.main_grid - 1) / p.main_grid);
-  const int tiles_b = tiles_of(p.n_pages[b], g.page);
-  const int T0 = cum[b] + h * tiles_b, T1 = T0 + tiles_b;
-  const int cta0 = T0 / per_cta, cta1 = (tiles_b > 0) ? (T1 - 1) / per_cta : cta0 - 1;
-  const int sub_slots = p.main_grid + p.batch * g.h_kv;
 
-  // ---- window scores: thread = token, one pass over its key row for all G queries ----
+  // ---- window scores: eight lanes per token (16 channels each: 8l..8l+7 and 64+8l..), 32 tokens per pass ----
   const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
   const __half* kt = p.k_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
   const __half* vt = p.v_tail + (int64_t)bh * p.tail_cap * HEAD_DIM;
-  float mx[GQ];
-#pragma unroll
-  for (int qi = 0; qi < GQ; ++qi) mx[qi] = -INFINITY;
-  for (int t = tid; t < tl; t += MERGE_THREADS) {
-    float d[GQ];
-#pragma unroll
-    for (int qi = 0; qi < GQ; ++qi) d[qi] = 0.f;
-    const uint4* row = reinterpret_cast<const uint4*>(kt + (int64_t)t * HEAD_DIM);
-    uint4 rw[16];  // the whole 256-byte key row in flight at once: this kernel is latency bound
-#pragma unroll
-    for (int c8 = 0; c8 < 16; ++c8) rw[c8] = row[c8];
-#pragma unroll
-    for (int c8 = 0; c8 < 16; ++c8) {
-      const uint4 raw = rw[c8];
-      const float2 k0 = __half22float2(u32_as_h2(raw.x)), k1 = __half22float2(u32_as_h2(raw.y));
-      const float2 k2 = __half22float2(u32_as_h2(raw.z)), k3 = __half22float2(u32_as_h2(raw.w));
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi)
-        if (qi < G) {
-          const float4 qa = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8);
-          const float4 qb = *reinterpret_cast<const float4*>(qs + qi * HEAD_DIM + 8 * c8 + 4);
-          d[qi] += k0.x * qa.x + k0.y * qa.y + k1.x * qa.z + k1.y * qa.w + k2.x * qb.x + k2.y * qb.y + k3.x * qb.z + k3.y * qb.w;
-        }
-    }
-#pragma unroll
-    for (int qi = 0; qi < GQ; ++qi)
-      if (qi < G) {
-        sc[t * GQ + qi] = d[qi];
-        mx[qi] = fmaxf(mx[qi], d[qi]);
-      }
-  }
-  // block max per query
-#pragma unroll
-  for (int qi = 0; qi < GQ; ++qi)
-    if (qi < G) {
-      float v = mx[qi];
-#pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
-      if (lane == 0) redm[warp * 8 + qi] = v;
-    }
-  __syncthreads();
-  if (tid < G) {
-    float v = -INFINITY;
-    for (int w = 0; w < MERGE_THREADS / 32; ++w) v = fmaxf(v, redm[w * 8 + tid]);
-    tm[tid] = v;
-  }
-  __syncthreads();
-  // weights and their sum
-  float sm[GQ];
-#pragma unroll
-  for (int qi = 0; qi < GQ; ++qi) sm[qi] = 0.f;
-  for (int t = tid; t < tl; t += MERGE_THREADS) {
-#pragma unroll
-    for (int qi = 0; qi < GQ; ++qi)
-      if (qi < G) {
-        const float e = ex2_approx(sc[t * GQ + qi] - tm[qi]);
-        sc[t * GQ + qi] = e;
-        sm[qi] += e;
-      }
-  }
-  __syncthreads();  // redm reuse
-#pragma unroll
-  for (int qi = 0; qi < GQ; ++qi)
-    if (qi < G) {
-      float v = sm[qi];
-#pragma unroll
-      for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-      if (lane == 0) redm[warp * 8 + qi] = v;
-    }
-  __syncthreads();
-  if (tid < G) {
-    float v = 0.f;
-    for (int w = 0; w < MERGE_THREADS / 32; ++w) v += redm[w * 8 + tid];
-    tm[8 + tid] = v;
-  }
-  // ---- window accumulators: thread = (token half, channel), all G queries in one pass over V ----
+  float mx = -INFINITY;
   {
-    const int ch = tid & 127, part = tid >> 7;
-    float a[GQ];
+    const int l8 = tid & 7, tp = tid >> 3;
+    float qr[16];
 #pragma unroll
-    for (int qi = 0; qi < GQ; ++qi) a[qi] = 0.f;
-    const int per = (tl + MERGE_SPLIT - 1) / MERGE_SPLIT;
-    const int t_lo = min(tl, part * per), t_hi = min(tl, t_lo + per);
-    for (int t0 = t_lo; t0 < t_hi; t0 += 16) {
-      __half vv[16];  // 16 loads in flight
+    for (int k = 0; k < 8; ++k) qr[k] = qs[8 * l8 + k], qr[8 + k] = qs[64 + 8 * l8 + k];
+    for (int t0 = 0; t0 < tl; t0 += 256) {
+      uint4 ka[8], kb[8];
 #pragma unroll
-      for (int k = 0; k < 16; ++k) vv[k] = (t0 + k < t_hi) ? vt[(int64_t)(t0 + k) * HEAD_DIM + ch] : __float2half(0.f);
+      for (int i = 0; i < 8; ++i) {  // all loads of the chunk in flight together
+        const int t = t0 + 32 * i + tp;
+        const uint4* row = reinterpret_cast<const uint4*>(kt + (int64_t)min(t, tl - 1) * HEAD_DIM);
+        ka[i] = row[l8], kb[i] = row[8 + l8];
+      }
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        const float vf = __half2float(vv[k]);
-        const int t = min(t0 + k, t_hi - 1);
-        float wq[GQ];  // the token's weights for all queries: one or two 128-bit loads, the same address for the whole warp
+      for (int i = 0; i < 8; ++i) {
+        const int t = t0 + 32 * i + tp;
+        const uint32_t w[8] = {ka[i].x, ka[i].y, ka[i].z, ka[i].w, kb[i].x, kb[i].y, kb[i].z, kb[i].w};
+        float d = 0.f;
 #pragma unroll
-        for (int q4 = 0; q4 < GQ; q4 += 4) {
-          const float4 w4 = *reinterpret_cast<const float4*>(sc + t * GQ + q4);
-          wq[q4] = w4.x, wq[q4 + 1] = w4.y, wq[q4 + 2] = w4.z, wq[q4 + 3] = w4.w;
+        for (int k = 0; k < 8; ++k) {
+          const float2 f = __half22float2(u32_as_h2(w[k]));
+          d = fmaf(f.x, qr[2 * k], d), d = fmaf(f.y, qr[2 * k + 1], d);
         }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        if (t < tl) {
+          mx = fmaxf(mx, d);
+          if (l8 == 0) sc[t] = d;
+        }
+      }
+    }
+  }
+  // ---- window values: thread = (token group of 16, channel octet); the first 256 tokens' loads are issued before
+  //      the softmax reductions so that they travel meanwhile ----
+  const int c8 = tid & 15, tg = tid >> 4;
+  uint4 vv[16];
 #pragma unroll
-        for (int qi = 0; qi < GQ; ++qi)
-          if (qi < G) a[qi] = fmaf(wq[qi], vf, a[qi]);
+  for (int i = 0; i < 16; ++i) {
+    const int t = tg + 16 * i;
+    vv[i] = (t < tl) ? reinterpret_cast<const uint4*>(vt + (int64_t)t * HEAD_DIM)[c8] : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+  if (lane == 0) sm[warp] = mx;
+  __syncthreads();
+  float m_w = sm[0];
+#pragma unroll
+  for (int w = 1; w < MERGE_THREADS / 32; ++w) m_w = fmaxf(m_w, sm[w]);
+  float lsum = 0.f;
+  for (int t = tid; t < tl; t += MERGE_THREADS) {
+    const float e = ex2_approx(sc[t] - m_w);
+    sc[t] = e, lsum += e;
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, m);
+  if (lane == 0) sm[8 + warp] = lsum;
+  __syncthreads();
+  float l_w = 0.f;
+#pragma unroll
+  for (int w = 0; w < MERGE_THREADS / 32; ++w) l_w += sm[8 + w];
+  {
+    float a[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = 0.f;
+    for (int t0 = 0; t0 < tl; t0 += 256) {
+      if (t0 > 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int t = t0 + tg + 16 * i;
+          vv[i] = (t < tl) ? reinterpret_cast<const uint4*>(vt + (int64_t)t * HEAD_DIM)[c8] : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = t0 + tg + 16 * i;
+        const float wgt = (t < tl) ? sc[t] : 0.f;
+        const uint32_t w[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __half22float2(u32_as_h2(w[k]));
+          a[2 * k] = fmaf(wgt, f.x, a[2 * k]), a[2 * k + 1] = fmaf(wgt, f.y, a[2 * k + 1]);
+        }
       }
     }
 #pragma unroll
-    for (int qi = 0; qi < GQ; ++qi)
-      if (qi < G) atl[(part * G + qi) * HEAD_DIM + ch] = a[qi];
+    for (int k = 0; k < 8; ++k) red[tg * HEAD_DIM + 8 * c8 + k] = a[k];
+  }
+  __syncthreads();
+  if (tid < HEAD_DIM) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) s += red[k * HEAD_DIM + tid];
+    atl[tid] = s;
   }
   // Everything above reads only what earlier steps' kernels wrote.  When this kernel was launched as a programmatic
   // dependent of the page-streaming kernel, that kernel's partial states are complete and visible from here on
   // (a plain launch passes straight through).
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  __syncthreads();  // the window's maxima and sums (written by the first threads) are read by the warps below
+  __syncthreads();  // `red` is reused below
+
   // ---- partial records of the page-streaming kernel.  Record r of this (sequence, head): sub-record r / n_cta of
-  //      CTA cta0 + r % n_cta.  Warp qi first finds the overall maximum of query qi, every record's weight and the
-  //      sum (lanes = records); then thread = (query, channel) adds up the weighted accumulators ----
-  const int n_cta = max(0, cta1 - cta0 + 1), n_rec = n_cta * p.n_sub, rec_cap = p.n_sub * p.main_grid;
-  auto rec_ptr = [&](int r, int qi) {
+  //      CTA cta0 + r % n_cta.  Thread = (record parity, channel): an online softmax over its records ----
+  const int total = si[1];
+  const int per_cta = max(1, (total + p.main_grid - 1) / p.main_grid);
+  const int tiles_b = tiles_of(p.n_pages[b], g.page);
+  const int T0 = si[0] + h * tiles_b, T1 = T0 + tiles_b;
+  const int cta0 = T0 / per_cta, cta1 = (tiles_b > 0) ? (T1 - 1) / per_cta : cta0 - 1;
+  const int sub_slots = p.main_grid + p.batch * g.h_kv;
+  const int n_cta = max(0, cta1 - cta0 + 1), n_rec = n_cta * p.n_sub;
+  auto rec_ptr = [&](int r) {
     const int sb = r / n_cta, c = cta0 + (r - sb * n_cta);
     return p.part + ((int64_t)(sb * sub_slots + c + bh) * G + qi) * PART_STRIDE;
   };
-  if (warp < G) {
-    const int qi = warp;
-    const float mt = (tl > 0) ? tm[qi] : -INFINITY, lt = (tl > 0) ? tm[8 + qi] : 0.f;
-    float M = mt;
-    for (int r = lane; r < n_rec; r += 32) M = fmaxf(M, rec_ptr(r, qi)[0]);
+  {
+    const int ch = tid & 127, half = tid >> 7;
+    float M = -INFINITY, L = 0.f, A = 0.f;
+    for (int r0 = half; r0 < n_rec; r0 += 8) {
+      float m_[4], l_[4], a_[4];
 #pragma unroll
-    for (int mk = 16; mk >= 1; mk >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, mk));
-    float l = 0.f;
-    for (int r = lane; r < n_rec; r += 32) {
-      const float* ps = rec_ptr(r, qi);
-      const float f = (ps[0] == -INFINITY) ? 0.f : ex2_approx(ps[0] - M);
-      fw[qi * rec_cap + r] = f;
-      l += ps[1] * f;
+      for (int j = 0; j < 4; ++j) {
+        const int r = r0 + 2 * j;
+        if (r < n_rec) {
+          const float* ps = rec_ptr(r);
+          m_[j] = ps[0], l_[j] = ps[1], a_[j] = ps[2 + ch];
+        } else {
+          m_[j] = -INFINITY, l_[j] = 0.f, a_[j] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float Mn = fmaxf(M, m_[j]);
+        const float fo = (M == -INFINITY) ? 0.f : ex2_approx(M - Mn);
+        const float fn = (m_[j] == -INFINITY) ? 0.f : ex2_approx(m_[j] - Mn);
+        L = L * fo + l_[j] * fn, A = A * fo + a_[j] * fn, M = Mn;
+      }
     }
-#pragma unroll
-    for (int mk = 16; mk >= 1; mk >>= 1) l += __shfl_xor_sync(0xffffffffu, l, mk);
-    const float wt = (mt == -INFINITY) ? 0.f : ex2_approx(mt - M);
-    if (lane == 0) fin[qi] = M, fin[8 + qi] = l + lt * wt, fin[16 + qi] = wt;
+    red[half * HEAD_DIM + ch] = A;
+    if (ch == 0) sm[16 + 2 * half] = M, sm[17 + 2 * half] = L;
   }
   __syncthreads();
-  for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
-    const int qi = o >> 7, ch = o & 127;
-    float ar = 0.f;
-    for (int r = 0; r < n_rec; ++r) ar = fmaf(rec_ptr(r, qi)[2 + ch], fw[qi * rec_cap + r], ar);
-    accs[o] = ar;
-  }
-  __syncthreads();
-  // ---- undo the value rotation (codecs without one pass signs == nullptr): warp qi transforms row qi ----
-  for (int qi = warp; qi < G && p.signs != nullptr; qi += MERGE_THREADS / 32) {
+  if (warp == 0) {
+    const float M0 = sm[16], L0 = sm[17], M1 = sm[18], L1 = sm[19];
+    const float Mp = fmaxf(M0, M1);
+    const float f0 = (M0 == -INFINITY) ? 0.f : ex2_approx(M0 - Mp), f1 = (M1 == -INFINITY) ? 0.f : ex2_approx(M1 - Mp);
+    const float Lp = L0 * f0 + L1 * f1;
     float x[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) x[k] = accs[qi * HEAD_DIM + 4 * lane + k];
-    fwht128_warp(x, lane);
+    for (int k = 0; k < 4; ++k) x[k] = red[4 * lane + k] * f0 + red[HEAD_DIM + 4 * lane + k] * f1;
+    if (p.signs != nullptr) {  // undo the value rotation (codecs without one pass signs == nullptr)
+      fwht128_warp(x, lane);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) accs[qi * HEAD_DIM + 4 * lane + k] = x[k] * p.signs[4 * lane + k] * 0.08838834764831845f;
-  }
-  __syncthreads();
-  for (int o = tid; o < G * HEAD_DIM; o += MERGE_THREADS) {
-    const int qi = o >> 7, ch = o & 127;
-    const float M = fin[qi], l = fin[8 + qi], wt = fin[16 + qi];
-    float at = 0.f;
-#pragma unroll
-    for (int k = 0; k < MERGE_SPLIT; ++k) at += atl[(k * G + qi) * HEAD_DIM + ch];
-    const float val = accs[o] + at * wt;
+      for (int k = 0; k < 4; ++k) x[k] = x[k] * p.signs[4 * lane + k] * 0.08838834764831845f;
+    }
+    const float mw = (tl > 0) ? m_w : -INFINITY;
+    const float Mf = fmaxf(Mp, mw);
+    const float fp = (Mp == -INFINITY) ? 0.f : ex2_approx(Mp - Mf), fw = (mw == -INFINITY) ? 0.f : ex2_approx(mw - Mf);
+    const float l = Lp * fp + ((tl > 0) ? l_w : 0.f) * fw;
     const int64_t row = (int64_t)bh * G + qi;
+    float val[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) val[k] = x[k] * fp + atl[4 * lane + k] * fw;
     if (p.partial_out) {
       float* po = p.partial_out + row * PART_STRIDE;
-      po[2 + ch] = val;
-      if (ch == 0) po[0] = M, po[1] = l;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) po[2 + 4 * lane + k] = val[k];
+      if (lane == 0) po[0] = Mf, po[1] = l;
+    } else if (p.out_dtype == BMXK_DTYPE_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + row * HEAD_DIM + 4 * lane) =
+          make_float4(val[0] / l, val[1] / l, val[2] / l, val[3] / l);
     } else {
-      const float r = val / l;
-      if (p.out_dtype == BMXK_DTYPE_F32)
-        reinterpret_cast<float*>(p.out)[row * HEAD_DIM + ch] = r;
-      else
-        reinterpret_cast<__half*>(p.out)[row * HEAD_DIM + ch] = __float2half_rn(r);
+      const __half2 h01 = __floats2half2_rn(val[0] / l, val[1] / l), h23 = __floats2half2_rn(val[2] / l, val[3] / l);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + row * HEAD_DIM + 4 * lane) = make_uint2(h2_as_u32(h01), h2_as_u32(h23));
     }
   }
 }
@@ -677,16 +676,15 @@ int num_sms() {
 
 int launch_merge(const K2bMergeParams& mp, cudaStream_t s, bool after_main) {
   const int G = mp.g.n_q_groups;
-  const size_t msmem = ((size_t)(G <= 4 ? 4 : 8) * mp.tail_cap + (2 + MERGE_SPLIT) * G * HEAD_DIM + 128 + 16) * 4 + (size_t)(mp.batch + 1) * 4 +
-                       (size_t)(24 + G * mp.n_sub * mp.main_grid) * 4 + 16;
+  const size_t msmem = ((size_t)((mp.tail_cap + 3) & ~3) + (1 + 16 + 1) * HEAD_DIM + 32 + 4) * sizeof(float);
   BMXK_REQUIRE(msmem <= 48 * 1024, "decode: tail_cap=%d too large for the merge kernel", mp.tail_cap);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(mp.batch * mp.g.h_kv)), cfg.blockDim = dim3(MERGE_THREADS), cfg.dynamicSmemBytes = msmem, cfg.stream = s;
+  cfg.gridDim = dim3((unsigned)(mp.batch * mp.g.h_kv * G)), cfg.blockDim = dim3(MERGE_THREADS), cfg.dynamicSmemBytes = msmem, cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = after_main ? 1 : 0;
-  const cudaError_t e = (G <= 4) ? cudaLaunchKernelEx(&cfg, k2b_merge_kernel<4>, mp) : cudaLaunchKernelEx(&cfg, k2b_merge_kernel<8>, mp);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, k2b_merge_kernel, mp);
   if (e != cudaSuccess) {
     set_error("decode(merge): %s", cudaGetErrorString(e));
     return BMXK_ERR_CUDA;
