@@ -309,6 +309,83 @@ class SpectralLayerState(K2bLayerState):
         return int(self.batch * self.geom.h_kv * (self.committed // self.page) * (self.geom.block_bytes + self.vpool.shape[2]))
 
 
+class RtnLayerState(K2bLayerState):
+    """Same state for the plain RTN arms (bmx rtn_token / rtn_channel keys, rtn_token values): keys are quantized
+    after RoPE, so there is no basis, no rotation at read and no separate page-source window.  A decode step is the RTN
+    page-streaming kernel plus the merge kernel (bmx: src/bmx/cache/packed_streaming.py:904-944 dispatches this arm pair
+    to fused_decode_attention_packed; quantize-on-append as :643-678)."""
+
+    def __init__(self, geom: "K.RtnGeom", batch: int, max_tokens: int, recent_window: int, device):
+        self.geom, self.batch, self.device = geom, batch, torch.device(device)
+        self.page, self.W, self.pre_rope = geom.page, recent_window, False
+        self.max_pages = max(1, math.ceil(max_tokens / geom.page))
+        self.pool = K.RtnPool(geom, batch * self.max_pages, self.device)
+        self.page_table = torch.arange(batch * self.max_pages, dtype=torch.int32, device=self.device).view(batch, -1)
+        self.n_pages_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_len_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.append_cnt = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.tail_cap = recent_window + geom.page
+        shape = (batch, geom.h_kv, self.tail_cap, HEAD_DIM)
+        self.k_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.v_win = torch.zeros(shape, dtype=torch.float16, device=self.device)
+        self.k_pre_win = self.k_win  # the page source IS the post-RoPE key: one window serves both
+        self.rope_cos = self.rope_sin = None
+        self.basis_f32 = self.basis_f16 = None
+        self.workspace = K.rtn_workspace(geom, batch, self.max_pages, self.device)
+        self.committed = 0
+        self.tail_len = 0
+        self.sm_scale = 1.0 / math.sqrt(HEAD_DIM)
+
+    def ensure_pages(self, n_more: int) -> None:
+        need = self.committed // self.page + n_more
+        if need <= self.max_pages:
+            return
+        new_max = max(need, 2 * self.max_pages)
+        old_pool, old_table, used = self.pool, self.page_table, self.committed // self.page
+        self.pool = K.RtnPool(self.geom, self.batch * new_max, self.device)
+        self.page_table = torch.arange(self.batch * new_max, dtype=torch.int32, device=self.device).view(self.batch, -1)
+        if used:
+            src = old_table[:, :used].reshape(-1).long()
+            dst = self.page_table[:, :used].reshape(-1).long()
+            self.pool.pages[dst] = old_pool.pages[src]
+        self.max_pages = new_max
+        self.workspace = K.rtn_workspace(self.geom, self.batch, self.max_pages, self.device)
+
+    def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
+        if v_src.dtype != k_src.dtype:
+            v_src = v_src.to(k_src.dtype)
+        if k_src.stride() != v_src.stride() or k_src.stride(3) != 1:
+            k_src, v_src = k_src.contiguous(), v_src.contiguous()
+        self.ensure_pages(n_pages)
+        p0 = self.committed // self.page
+        slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
+        K.rtn_append(self.pool, k_src, v_src, slots, n_pages)
+        self.committed += n_pages * self.page
+        self.n_pages_dev.fill_(self.committed // self.page)
+
+    def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+               phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
+        """q (batch, heads, 128) fp16 -> attention output over RTN pages + window (keys carry their rotation already, so
+        pos_offset has no effect; the step always runs both kernels)."""
+        max_pages = self.max_pages if self.committed else 0
+        return K.rtn_decode(self.pool, q, self.page_table, self.n_pages_dev, max_pages, self.k_win, self.v_win, self.tail_len_dev,
+                            self.sm_scale, self.workspace, out=out, partial_out=partial_out)
+
+    def _pools(self) -> dict:
+        return {"pages": self.pool.pages}
+
+    def dense_pages(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """All committed pages dequantized (code x fp16 scale): post-RoPE keys and values, float32 (batch, h_kv, committed, 128)."""
+        n_pg, h_kv = self.committed // self.page, self.geom.h_kv
+        slots = self.page_table[:, :n_pg].contiguous().view(-1)
+        ex = K.rtn_export(self.pool, slots, dequant=True)
+        shp = (self.batch, n_pg * self.page, h_kv, HEAD_DIM)
+        return ex["k_deq"].view(*shp).permute(0, 2, 1, 3), ex["v_deq"].view(*shp).permute(0, 2, 1, 3)
+
+    def packed_bytes(self) -> int:
+        return int(self.batch * self.geom.h_kv * (self.committed // self.page) * self.pool.pages.shape[2])
+
+
 class DecodeStepGraph:
     """One decode step of a layer state, host buffers to host buffer, as a CUDA graph.
 
@@ -354,7 +431,8 @@ class DecodeStepGraph:
     def _key(self):
         st = self.state
         pools = (st.pool.pages.data_ptr(),) if hasattr(st, "pool") else (st.kpool.data_ptr(), st.vpool.data_ptr())
-        return (st.max_pages if st.committed else 0, pools, st.rope_cos.data_ptr())
+        rope = 0 if getattr(st, "rope_cos", None) is None else st.rope_cos.data_ptr()
+        return (st.max_pages if st.committed else 0, pools, rope)
 
     def invalidate(self) -> None:
         """Call after changing the state from outside (other RoPE tables, pools swapped): the next step re-captures."""

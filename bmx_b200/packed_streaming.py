@@ -20,9 +20,9 @@ from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS, sdpa_mask
 from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
 from . import kernels as K
-from .engine import K2bLayerState, SpectralLayerState
+from .engine import K2bLayerState, RtnLayerState, SpectralLayerState
 from .rope import apply_rope, rope_tables_from_config
-from .schedule import codec_bpe, compute_flush_schedule, scale_bits
+from .schedule import cache_bits_per_entry, codec_bpe, compute_flush_schedule, scale_bits
 from .specs import FUSED_PAIRS, CacheCodecSpec
 
 _ATTN_NAME = "chunked_dequant"
@@ -98,9 +98,33 @@ class SpectralHeadPacks:
     M_hat = Y_hat @ dec[h].T, bits (h_kv, 128) from {0, 2, 3, 4, 5, 6, 8}, group = token group of the scales
     (the fields of bmx's SpectralPack that the codec reads, src/bmx/cache/spectral.py:174-220, one per head)."""
 
-    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, group: int = 64):
+    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, group: int = 64,
+                 tiers: tuple = (0, 2, 3, 4, 5, 6, 8), dec_tier: int | None = None):
         assert enc.shape == dec.shape and enc.dim() == 3 and enc.shape[1:] == (HEAD_DIM, HEAD_DIM) and bits.shape == enc.shape[:2]
         self.enc, self.dec, self.bits, self.group = enc.float(), dec.float(), bits.to(torch.int32), int(group)
+        # accounting only: the tier grid the bits were allocated on, and the tier threshold up to which `dec` was put
+        # through the int8 round trip when the pack was materialised (None: none was; bmx: SpectralPack.dec_tier)
+        self.tiers, self.dec_tier = tuple(tiers), dec_tier
+
+    @property
+    def c_used(self) -> int:
+        """Decoder columns that carry bits, over all heads (bmx: SpectralPack.c_used, src/bmx/cache/spectral.py:208-211)."""
+        return int((self.bits != 0).sum())
+
+    def c_int8(self, tier_threshold: int) -> int:
+        """Used decoder columns held as int8 at that threshold (bmx: src/bmx/cache/spectral.py:213-220)."""
+        return int(((self.bits > 0) & (self.bits <= tier_threshold)).sum())
+
+
+def check_rtn_specs(k_spec: CacheCodecSpec, v_spec: CacheCodecSpec) -> None:
+    """What the RTN kernels cover: post-RoPE keys of 2..4 bits, 2-bit values, groups of 32 / 64 / 128."""
+    if k_spec.pre_rope:
+        raise NotImplementedError("RTN keys are quantized after RoPE (bmx routes pre-RoPE RTN keys to its chunked path: "
+                                  "src/bmx/cache/packed_streaming.py:904-912); set pre_rope=False")
+    if not 2 <= k_spec.bits <= 4 or v_spec.bits != 2:
+        raise NotImplementedError(f"RTN kernels: key bits {k_spec.bits} must be 2..4 and value bits {v_spec.bits} must be 2")
+    if k_spec.group not in (32, 64, 128) or v_spec.group not in (32, 64, 128):
+        raise NotImplementedError(f"RTN kernels: groups {k_spec.group} / {v_spec.group} must be 32, 64 or 128")
 
 
 class PackedStreamingLayer(DynamicLayer):
@@ -116,11 +140,14 @@ class PackedStreamingLayer(DynamicLayer):
             raise NotImplementedError("pack_k=False / pack_v=False: this library stores codes bit-packed only")
         self.recent_window, self.pack_v, self.pack_k = recent_window, pack_v, pack_k
         kind = FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
-        if kind not in ("k2b", "spectral"):
+        if kind not in ("k2b", "spectral", "rtn"):
             raise NotImplementedError(
                 f"no CUDA decode kernel for arms K={k_spec.arm!r} / V={v_spec.arm!r} in PackedStreamingLayer; "
-                "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph') and spectral + "
-                "turboquant_mse_perhead with per-head packs. There is no CPU fallback.")
+                "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph'), rtn_token or rtn_channel keys "
+                "with rtn_token values (recipe 'kivi'), and spectral + turboquant_mse_perhead with per-head packs. "
+                "There is no CPU fallback.")
+        if kind == "rtn":
+            check_rtn_specs(k_spec, v_spec)
         if kind == "spectral" and pack is None:
             raise NotImplementedError(
                 "the spectral key arm needs per-head packs (enc, dec, bits of shape (h_kv, 128, 128) / (h_kv, 128)) passed as "
@@ -163,6 +190,10 @@ class PackedStreamingLayer(DynamicLayer):
                                              device=key_states.device)
                 self._state = SpectralLayerState(dev_pack, self._n_q_groups, self._batch, 4096, self.recent_window,
                                                  key_states.device, cos, sin, v_seed=self.v_spec.seed)
+            elif self._kind == "rtn":
+                geom = K.rtn_geom(self._h_kv, self._n_q_groups, self._page, self.k_spec.arm, self.k_spec.group, self.v_spec.group,
+                                  self.k_spec.bits, self.v_spec.bits)
+                self._state = RtnLayerState(geom, self._batch, 4096, self.recent_window, key_states.device)
             else:
                 geom = K.k2b_geom(self._h_kv, self._n_q_groups, self._page, self.k_spec.rank, self.k_spec.group, 1,
                                   self.k_spec.bits, self.v_spec.bits)
@@ -183,9 +214,11 @@ class PackedStreamingLayer(DynamicLayer):
         else:
             k_pre = None
         total = st.seq_len() + n
-        if total + 1 > st.rope_cos.shape[0]:  # the shared table grows by doubling: rarely
+        if st.rope_cos is not None and total + 1 > st.rope_cos.shape[0]:  # the shared table grows by doubling: rarely
             st.rope_cos, st.rope_sin = shared_rope(self.model_config, total + 1, key_states.device)
         before = st.committed
+        if self._frozen_svd is not None and self._kind == "k2b" and st.basis_f32 is None:
+            st.set_basis(self._frozen_svd[1])  # a basis frozen elsewhere (restored state, another cache): never refit
         st.append(k_pre, key_states.to(torch.float16), value_states.to(torch.float16))
         if st.basis_f32 is not None and self._frozen_svd is None:
             self._frozen_svd = (None, st.basis_f32)
@@ -223,7 +256,7 @@ class PackedStreamingLayer(DynamicLayer):
         n_pg = st.committed // self._page
         parts_k, parts_v = [], []
         if n_pg:
-            if self._kind == "spectral":
+            if self._kind in ("spectral", "rtn"):
                 kd, vd = st.dense_pages()
             else:
                 slots = st.page_table[:, :n_pg].contiguous().view(-1)
@@ -304,10 +337,7 @@ class PackedStreamingCache(Cache):
 
     def bits_per_entry(self):
         """(bpe_k, bpe_v): blended bits per entry averaged across layers (bmx: streaming.py:154-260)."""
-        layers = list(self.layers)
-        if not layers:
-            return float("nan"), float("nan")
-        return (sum(l.bpe_k for l in layers) / len(layers), sum(l.bpe_v for l in layers) / len(layers))
+        return cache_bits_per_entry(self.layers, self.k_spec)
 
     def memory_report(self, seq_len: int) -> dict:
         """Dense fp16 bytes vs packed (bpe-derived) bytes of the whole cache (bmx: streaming.py:263-305)."""

@@ -83,7 +83,7 @@ def load_head_packs(path: str | Path, budget: float, h_kv: int, dec_quant: str =
     if dec_quant == "fp32":
         quant, thr = False, None
     elif dec_quant == "int8":
-        quant, thr = True, None
+        quant, thr = True, 8  # every direction with bits is at most 8: the blanket round trip (bmx: spectral.py:1234-1235)
     elif dec_quant.startswith("int8_t") and dec_quant[6:].isdigit():
         quant, thr = True, int(dec_quant[6:])
     else:
@@ -100,5 +100,5 @@ def load_head_packs(path: str | Path, budget: float, h_kv: int, dec_quant: str =
             raise ValueError(f"layer{i}: pack shapes {tuple(enc.shape)} / {tuple(bits.shape)} do not fit h_kv={h_kv}")
         if quant:
             dec = int8_decoder_roundtrip(dec, bits, thr)
-        out[i] = SpectralHeadPacks(enc, dec, bits, group=int(sidecar["group"]))
+        out[i] = SpectralHeadPacks(enc, dec, bits, group=int(sidecar["group"]), tiers=tuple(sidecar["tiers"]), dec_tier=thr if quant else None)
     return out

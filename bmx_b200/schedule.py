@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 
 def compute_flush_schedule(S: int, W: int, g: int) -> int:
     """Largest multiple of g that leaves at least W recent tokens in fp16, else 0.
@@ -40,3 +42,37 @@ def codec_bpe(arm: str, *, bits: int, group: int, rank: int, S: int, C: int, h_h
     if arm == "fp16":
         return 16.0
     raise NotImplementedError(f"no packed accounting for arm {arm!r}")
+
+
+def tier_bits(tiers, S: int) -> float:
+    """Tier map of the spectral codec: ceil(log2(number of tiers)) bits per channel, amortized over S tokens
+    (bmx: src/bmx/cache/codecs.py:94-96)."""
+    return math.ceil(math.log2(len(tiers))) / S
+
+
+def mixed_dec_charge(C: int, S: int, tiers, *, c_used: float, c_int8: float) -> float:
+    """Per-sequence charge of a spectral pack's decoder and tier map, in bits per entry: `c_int8` of the `c_used`
+    decoder columns that carry bits are held as int8 (8 bits per entry plus one fp16 scale per column), the rest as
+    fp16 (bmx: src/bmx/cache/spectral.py:1036-1064)."""
+    assert 0 <= c_int8 <= c_used <= C, f"need 0 <= c_int8 <= c_used <= C; got {c_int8}, {c_used}, {C}"
+    int8_term = 8.0 * c_int8 / S + 16.0 * c_int8 / (S * C)
+    fp16_term = 16.0 * (c_used - c_int8) / S
+    return int8_term + fp16_term + tier_bits(tiers, S)
+
+
+def cache_bits_per_entry(layers, k_spec) -> tuple[float, float]:
+    """(bpe_k, bpe_v): blended bits per entry averaged across layers; a spectral cache that has committed pages is
+    also charged its packs' decoders and tier map once per sequence (bmx: src/bmx/cache/streaming.py:154-260).
+    `layers` expose bpe_k, bpe_v, _committed_S_q, get_seq_length(), _h_kv, _d_head and (spectral) _pack."""
+    layers = list(layers)
+    if not layers:
+        return float("nan"), float("nan")
+    last = layers[-1]
+    bpe_k = sum(layer.bpe_k for layer in layers) / len(layers)
+    bpe_v = sum(layer.bpe_v for layer in layers) / len(layers)
+    if k_spec.arm == "spectral" and last._committed_S_q > 0:
+        S, C = last.get_seq_length(), last._h_kv * last._d_head
+        mean_c_used = sum(layer._pack.c_used for layer in layers) / len(layers)
+        mean_c_int8 = sum(0 if layer._pack.dec_tier is None else layer._pack.c_int8(layer._pack.dec_tier) for layer in layers) / len(layers)
+        bpe_k = bpe_k + mixed_dec_charge(C, S, last._pack.tiers, c_used=mean_c_used, c_int8=mean_c_int8)
+    return bpe_k, bpe_v

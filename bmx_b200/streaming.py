@@ -15,9 +15,9 @@ from transformers.cache_utils import Cache, DynamicLayer
 
 from . import kernels as K
 from .engine import dequant_value_blocks, fit_basis
-from .packed_streaming import resolve_decoder_layers, resolve_k_capture_module, resolve_text_config
+from .packed_streaming import check_rtn_specs, resolve_decoder_layers, resolve_k_capture_module, resolve_text_config
 from .rope import apply_rope, rope_tables_from_config
-from .schedule import codec_bpe, compute_flush_schedule
+from .schedule import cache_bits_per_entry, codec_bpe, compute_flush_schedule
 from .specs import FUSED_PAIRS, CacheCodecSpec
 
 HEAD_DIM = K.HEAD_DIM
@@ -31,8 +31,10 @@ class StreamingQuantizedLayer(DynamicLayer):
         self.k_spec, self.v_spec, self.model_config, self.recent_window = k_spec, v_spec, model_config, recent_window
         self._passthrough = k_spec.arm == "fp16" and v_spec.arm == "fp16"
         self._kind = None if self._passthrough else FUSED_PAIRS.get((k_spec.arm, v_spec.arm))
-        if not self._passthrough and self._kind not in ("k2b", "spectral"):
+        if not self._passthrough and self._kind not in ("k2b", "spectral", "rtn"):
             raise NotImplementedError(f"no CUDA codec for arms K={k_spec.arm!r} / V={v_spec.arm!r}; there is no CPU fallback")
+        if self._kind == "rtn":
+            check_rtn_specs(k_spec, v_spec)
         if self._kind == "spectral" and pack is None:
             raise NotImplementedError("the spectral key arm needs per-head packs: StreamingQuantizedCache(..., "
                                       "spectral_packs={layer: SpectralHeadPacks}); pack files are not loaded")
@@ -65,6 +67,8 @@ class StreamingQuantizedLayer(DynamicLayer):
         n_pg = (end - start) // self._page
         if self._kind == "spectral":
             return self._flush_spectral(k_src, v_src, start, end, dtype)
+        if self._kind == "rtn":
+            return self._flush_rtn(k_src, v_src, start, end, dtype)
         if self._geom is None:
             n_q_groups = resolve_text_config(self.model_config).num_attention_heads // self._h_kv
             self._geom = K.k2b_geom(self._h_kv, min(n_q_groups, 8), self._page, self.k_spec.rank, self.k_spec.group, 1,
@@ -85,6 +89,21 @@ class StreamingQuantizedLayer(DynamicLayer):
             cos, sin = rope_tables_from_config(self.model_config, end - start, start=start, device=dev)
             kd = apply_rope(kd, cos, sin)  # float32 tables, float32 keys, then cast
         return kd.to(dtype), vd.to(dtype)
+
+    def _flush_rtn(self, k_src: torch.Tensor, v_src: torch.Tensor, start: int, end: int, dtype):
+        """The same for the plain RTN arms: post-RoPE keys, code x fp16 scale on the way back (bmx: codecs.py:720-725, 807-811)."""
+        dev, b = k_src.device, k_src.shape[0]
+        n_pg = (end - start) // self._page
+        if self._geom is None:
+            n_q_groups = resolve_text_config(self.model_config).num_attention_heads // self._h_kv
+            self._geom = K.rtn_geom(self._h_kv, min(n_q_groups, 8), self._page, self.k_spec.arm, self.k_spec.group, self.v_spec.group,
+                                    self.k_spec.bits, self.v_spec.bits)
+        pool = K.RtnPool(self._geom, b * n_pg, dev)
+        slots = torch.arange(b * n_pg, dtype=torch.int32, device=dev)
+        K.rtn_append(pool, k_src.to(torch.float16).contiguous(), v_src.to(torch.float16).contiguous(), slots, n_pg)
+        ex = K.rtn_export(pool, slots, dequant=True)
+        shp = (b, n_pg * self._page, self._h_kv, self._d_head)
+        return ex["k_deq"].view(*shp).permute(0, 2, 1, 3).to(dtype), ex["v_deq"].view(*shp).permute(0, 2, 1, 3).to(dtype)
 
     def _flush_spectral(self, k_src: torch.Tensor, v_src: torch.Tensor, start: int, end: int, dtype):
         """The same for the spectral key codec: spectral append + page dequantizer for keys, value blocks for values."""
@@ -207,10 +226,7 @@ class StreamingQuantizedCache(Cache):
         return layer.keys, layer.values
 
     def bits_per_entry(self):
-        layers = list(self.layers)
-        if not layers:
-            return float("nan"), float("nan")
-        return sum(l.bpe_k for l in layers) / len(layers), sum(l.bpe_v for l in layers) / len(layers)
+        return cache_bits_per_entry(self.layers, self.k_spec)
 
     def memory_report(self, seq_len: int, h_kv: int | None = None, d_head: int | None = None) -> dict:
         bpe_k, bpe_v = self.bits_per_entry()

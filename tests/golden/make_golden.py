@@ -42,6 +42,8 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("BMX_REFERENCE", ""), help="checkout of pherber3/bmx (its src/ is imported)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
+    ap.add_argument("--skip-model", action="store_true", help="leave tests/golden/model.npz alone (the model-level part takes minutes)")
+    ap.add_argument("--only-model", action="store_true", help="regenerate tests/golden/model.npz only")
     args = ap.parse_args()
     if not args.reference:
         ap.error("--reference (or BMX_REFERENCE) must point at a checkout of the bmx reference")
@@ -65,6 +67,10 @@ def main() -> None:
 
     def gen(seed):
         return torch.Generator().manual_seed(seed)
+
+    if args.only_model:
+        model_level(args, torch, gen, npy)
+        return
 
     # ---- constants -------------------------------------------------------
     out = {
@@ -215,8 +221,120 @@ def main() -> None:
     for k, t in packed.items():
         out["p_" + k] = npy(t)
     np.savez_compressed(os.path.join(args.out, "spectral.npz"), **out)
-    for f in ("consts", "codec", "decode", "spectral"):
+    if not args.skip_model:
+        model_level(args, torch, gen, npy)
+    for f in ("consts", "codec", "decode", "spectral", "model"):
         print(f, os.path.getsize(os.path.join(args.out, f + ".npz")))
+
+
+def tiny_llama_config():
+    """The model of the model-level fixtures: Llama-shaped, head_dim 128, 2 layers, random weights from seed 0.
+    tests/test_hf_cache_gpu.py builds the same model from the same seed."""
+    from transformers import LlamaConfig
+
+    return LlamaConfig(vocab_size=256, hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=128, max_position_embeddings=4096, rope_theta=500000.0)
+
+
+def model_level(args, torch, gen, npy) -> None:
+    """Teacher-forced logits of the reference's own PackedStreamingCache (its CPU chunked path, float32) under a tiny
+    random-init Llama: 300 prompt tokens, then 64 single-token steps (the method of the reference's
+    scripts/profile_decode_ab.py).  One fixture per recipe; the frozen key basis each layer fitted is stored too, so
+    that a replay does not depend on which SVD library fits it.  Also stores the cache-level bits per entry."""
+    import warnings
+
+    from safetensors.torch import save_file
+    from transformers import LlamaForCausalLM
+
+    from bmx.cache.packed_streaming import PackedStreamingCache
+    from bmx.cache.recipes import spec_pair
+    from bmx.cache.specs import CacheCodecSpec
+    from bmx.cache.streaming import StreamingQuantizedCache
+    from bmx.quant.hadamard import orthogonalize
+
+    cfg = tiny_llama_config()
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg).eval()
+    n_prefill, n_steps = 300, 64
+    out = {}
+
+    def run(cache, ids):
+        logits = []
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            with cache.attach(model), torch.no_grad():
+                o = model(ids[:, :n_prefill], past_key_values=cache, use_cache=True)
+                logits.append(o.logits[:, -1].float())
+                for t in range(n_prefill, ids.shape[1]):
+                    o = model(ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+                    logits.append(o.logits[:, -1].float())
+        return torch.stack(logits, 1)[0]
+
+    # spectral packs in the reference's own file format: one (C, C) encoder per layer, here block diagonal over the
+    # two KV heads (orthogonal blocks, decoder = encoder), bits drawn from the tier grid per direction
+    C, tiers = 256, (0, 2, 3, 4, 5, 6, 8)
+    by_tier = [8] * 6 + [6] * 10 + [5] * 12 + [4] * 20 + [3] * 28 + [2] * 36 + [0] * 16
+    tensors = {}
+    g = gen(41)
+    for i in range(cfg.num_hidden_layers):
+        enc = torch.zeros(C, C)
+        bits = torch.zeros(C, dtype=torch.int64)
+        for h in range(2):
+            enc[h * 128:(h + 1) * 128, h * 128:(h + 1) * 128] = orthogonalize(torch.randn(128, 128, generator=g))
+            bits[h * 128:(h + 1) * 128] = torch.tensor(by_tier)[torch.randperm(128, generator=g)]
+        tensors[f"layer{i}.enc"], tensors[f"layer{i}.dec"] = enc, enc.clone()
+        tensors[f"layer{i}.lam"] = torch.ones(C)
+        tensors[f"layer{i}.bits_b2.5"] = bits
+        out[f"spectral_enc_l{i}"], out[f"spectral_bits_l{i}"] = npy(enc), npy(bits).astype(np.int32)
+    import json
+    import tempfile
+
+    pack_path = os.path.join(tempfile.mkdtemp(prefix="bmx_pack_"), "packs.safetensors")
+    save_file(tensors, pack_path)
+    with open(pack_path + ".json", "w") as f:
+        json.dump({"tiers": list(tiers), "group": 64, "budgets": [2.5]}, f)
+
+    recipes = {
+        "k2b_ph": spec_pair("k2b_ph", rank=16, group=64),
+        "kivi": spec_pair("kivi", group=64),
+        "rtn_c4t2": (CacheCodecSpec(arm="rtn_channel", bits=4, group=32), CacheCodecSpec(arm="rtn_token", bits=2, group=32)),
+        "spectral": (CacheCodecSpec(arm="spectral", pre_rope=True, group=64, pack_path=pack_path, budget=2.5),
+                     CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)),
+        "spectral_dec8": (CacheCodecSpec(arm="spectral", pre_rope=True, group=64, pack_path=pack_path, budget=2.5, dec_quant="int8"),
+                          CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)),
+    }
+    for seed, (name, (k_spec, v_spec)) in enumerate(recipes.items()):
+        # Prompts are drawn until the reference's own top-2 logit gap is at least 0.005 at every step: a random-init
+        # model's top two logits are sometimes closer than any two correct implementations agree to, and a flip at
+        # such a step would say nothing.  The seed that was kept is stored.
+        for attempt in range(200):
+            ids = torch.randint(0, 256, (1, n_prefill + n_steps), generator=gen(50 + seed + 100 * attempt))
+            cache = PackedStreamingCache(cfg, k_spec, v_spec, recent_window=32)
+            lg = run(cache, ids)
+            top2 = lg.topk(2, dim=-1).values
+            if float((top2[:, 0] - top2[:, 1]).min()) >= 0.005:
+                break
+        else:
+            raise SystemExit(f"{name}: no prompt with a clear top-2 margin in 200 draws")
+        out[f"{name}_ids_seed"] = np.int64(50 + seed + 100 * attempt)
+        out[f"{name}_ids"], out[f"{name}_logits"] = npy(ids).astype(np.int32), npy(lg)
+        out[f"{name}_min_top2_gap"] = np.float64((top2[:, 0] - top2[:, 1]).min())
+        out[f"{name}_bpe"] = np.array(cache.bits_per_entry(), dtype=np.float64)
+        rep = cache.memory_report(n_prefill + n_steps)
+        out[f"{name}_memory_report"] = np.array([rep["fp16_bytes"], rep["packed_bytes"], rep["compression"]], dtype=np.float64)
+        layer = cache.layers[0]
+        out[f"{name}_committed"] = np.int64(layer._committed_S_q)
+        if k_spec.arm == "lowrank_rtn_channel":
+            for i, l in enumerate(cache.layers):
+                out[f"{name}_basis_l{i}"] = npy(l._frozen_svd[1] if isinstance(l._frozen_svd, tuple) else l._frozen_svd)
+        # the dequantized-resident twin of the same recipe: its cache-level accounting must agree
+        twin = StreamingQuantizedCache(cfg, k_spec, v_spec, recent_window=32)
+        lt = run(twin, ids)
+        out[f"{name}_twin_bpe"] = np.array(twin.bits_per_entry(), dtype=np.float64)
+        out[f"{name}_twin_max_logit_diff"] = np.float64((lt - lg).abs().max())
+        print(name, "min top-2 gap", float(out[f"{name}_min_top2_gap"]), "bpe", out[f"{name}_bpe"], "twin", out[f"{name}_twin_bpe"],
+              "twin diff", float(out[f"{name}_twin_max_logit_diff"]))
+    np.savez_compressed(os.path.join(args.out, "model.npz"), **out)
 
 
 if __name__ == "__main__":
