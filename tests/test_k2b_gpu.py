@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import bmx_oracle as O
-from tests.helpers import full_rope, golden
+from tests.helpers import assert_bucket_ties, assert_fp16_rounding_ties, assert_round_ties, full_rope, golden
 
 pytestmark = pytest.mark.gpu
 
@@ -113,40 +113,70 @@ def test_append_export_dequant(page, rank, per_head, group):
     basis16 = basis.half().float().numpy()
     kd, vd = K.k2b_dequant_pages(pool, slots, basis.half().to(dev), signs.to(dev), cb.to(dev))
     kd, vd = kd.cpu().numpy(), vd.cpu().numpy()
-    n_bad_code = n_code = n_bad_idx = n_idx = 0
+    stats = {"coef": [0, 0, 0.0], "code": [0, 0, 0.0], "idx": [0, 0, 0.0], "norm": [0, 0, 0.0]}
+
+    def add(key, r, dist_key):
+        stats[key][0] += r["differing"]
+        stats[key][1] += r["of"]
+        stats[key][2] = max(stats[key][2], r[dist_key])
+
+    cbv = np.asarray(K.GAUSSIAN_CODEBOOK[2], np.float32)
+    mids = ((cbv[:-1] + cbv[1:]) / 2).astype(np.float64)
     for s in range(n_seq):
         for p in range(n_pages):
             i = s * n_pages + p
             Mk = O.to_matrix(k[s, :, p * page:(p + 1) * page].float().numpy())
             Mv = O.to_matrix(v[s, :, p * page:(p + 1) * page].float().numpy())
-            # --- coefficients: a float32 sum over 128 or 1024 channels, then fp16 ---
+            # --- coefficients: a float32 sum over 128 or 1024 channels, then fp16.  Against a float64 sum they may
+            #     differ by one fp16 ulp, and only where the exact value sits on an fp16 rounding boundary (to within the
+            #     float32 summation error, ~1e-6 relative of the terms' magnitude) ---
+            Mk64, b64 = Mk.astype(np.float64), basis.numpy().astype(np.float64)
             if per_head:
-                Us_ref = np.stack([Mk[:, h * D:(h + 1) * D] @ basis.numpy()[h * D:(h + 1) * D] for h in range(h_kv)])
+                Us64 = np.stack([Mk64[:, h * D:(h + 1) * D] @ b64[h * D:(h + 1) * D] for h in range(h_kv)])
+                mag = np.stack([np.abs(Mk64[:, h * D:(h + 1) * D]) @ np.abs(b64[h * D:(h + 1) * D]) for h in range(h_kv)])
             else:
-                Us_ref = (Mk @ basis.numpy())[None]
-            us_gpu = st["us"][i].astype(np.float32)
-            ulp = np.maximum(np.abs(Us_ref), 2.0 ** -14) * 2.0 ** -10
-            assert np.all(np.abs(us_gpu - Us_ref) <= 1.01 * ulp), "coefficient off by more than one fp16 ulp"
+                Us64, mag = (Mk64 @ b64)[None], (np.abs(Mk64) @ np.abs(b64))[None]
+            us_gpu = st["us"][i]
+            ref16 = Us64.astype(np.float16)
+            d = us_gpu.view(np.uint16) != ref16.view(np.uint16)
+            if d.any():
+                assert np.abs(us_gpu.view(np.uint16)[d].astype(int) - ref16.view(np.uint16)[d].astype(int)).max() == 1
+                mid = (us_gpu[d].astype(np.float64) + ref16[d].astype(np.float64)) / 2
+                # distance to the boundary, in units of the float32 error a 128..1024-term sum can have
+                n_terms = D if per_head else h_kv * D
+                assert (np.abs(Us64[d] - mid) / (mag[d] * 2.0 ** -24)).max() < 8 * math.sqrt(n_terms), "coefficient differs away from a rounding tie"
+            stats["coef"][0] += int(d.sum())
+            stats["coef"][1] += int(d.size)
             # --- integer stages, given the GPU's own fp16 coefficients ---
             kp, vp = blocks_from_export(st, i, g, basis16)
-            L = kp["Us"] @ kp["V"].T
-            Q, sc = O.rtn_quantize_packed(np.ascontiguousarray((Mk - L).T), 3, group)
-            n_bad_code += int((Q != kp["res_Q_int"]).sum())
-            n_code += Q.size
-            assert np.abs(Q.astype(int) - kp["res_Q_int"].astype(int)).max() <= 1
+            L = kp["Us"].astype(np.float64) @ kp["V"].astype(np.float64).T
+            Q, sc = O.rtn_quantize_packed(np.ascontiguousarray((Mk - (kp["Us"] @ kp["V"].T)).T), 3, group)
+            R64 = (Mk64 - L).T                                             # (C, page)
+            x = R64 / np.repeat(sc[..., 0].astype(np.float64), group, axis=1)
+            add("code", assert_round_ties(x, kp["res_Q_int"], Q, 2e-5, "key residual code"), "worst_distance_to_tie")
             np.testing.assert_allclose(sc.astype(np.float16).astype(np.float32), kp["res_scale"], rtol=2e-3)
-            idx, norms = O.turboquant_perhead_pack(Mv, 2, signs.numpy(), h_kv)
-            n_bad_idx += int((idx != vp["indices"]).sum())
-            n_idx += idx.size
-            assert (norms != vp["norms"]).mean() < 0.02
             assert kp["res_Q_int"].min() >= -3 and kp["res_Q_int"].max() <= 3
+            _, norms = O.turboquant_perhead_pack(Mv, 2, signs.numpy(), h_kv)
+            # values: y = fwht(v / n * signs) * sqrt(d) with the norm n the GPU stored (a norm that moved at an fp16 tie
+            # moves every y of its row), bucketized here against the codebook midpoints
+            Mv64 = Mv.astype(np.float64).reshape(page, h_kv, D)
+            n64 = np.sqrt((Mv64 ** 2).sum(-1))
+            unit = (Mv.reshape(page, h_kv, D) / vp["norms"].astype(np.float32)[..., None]) * signs.numpy()
+            y = (O.fwht(unit.astype(np.float32)).astype(np.float64) * float(np.float32(math.sqrt(D)))).reshape(page, h_kv * D)
+            idx = (y[..., None] > mids).sum(-1)
+            add("idx", assert_bucket_ties(y, mids, vp["indices"], idx, 2e-5, "value index"), "worst_distance_to_tie")
+            add("norm", assert_fp16_rounding_ties(n64, vp["norms"].astype(np.float16), norms.astype(np.float16), 2e-6, "value norm"),
+                "worst_rel_distance_to_tie")
             # --- dequant of the stored fields: values are elementwise (bit-exact), keys hold a
             #     rank-term float32 sum whose order differs from BLAS: 2e-6 absolute ---
             assert np.array_equal(vd[i], O.dequant_packed("turboquant_mse_perhead", vp, signs=signs.numpy()))
             np.testing.assert_allclose(kd[i], O.dequant_packed("lowrank_rtn_channel", kp, group=group), atol=2e-6, rtol=0)
-    # codes may move only at rounding ties of a float32 value computed in another summation order
-    assert n_bad_code / n_code < 2e-3, (n_bad_code, n_code)
-    assert n_bad_idx / n_idx < 2e-3, (n_bad_idx, n_idx)
+    print("append parity (differing, of, worst distance to a tie):", {a: tuple(b) for a, b in stats.items()})
+    # every difference above was shown to be a tie; their number stays at the floor a different summation order leaves:
+    # fp16 coefficients 0.24 % against torch, codes and indices ~1e-4, norms ~1e-4 of rows
+    assert stats["coef"][0] <= 0.0072 * stats["coef"][1]
+    assert stats["code"][0] <= max(2, 3e-4 * stats["code"][1]) and stats["idx"][0] <= max(2, 3e-4 * stats["idx"][1])
+    assert stats["norm"][0] <= max(1, 3e-4 * stats["norm"][1])
 
 
 def _decode_case(dev, K, *, n_seq, h_kv, G, page, rank, per_head, group, pages_per_seq, tail_lens, seed, tail_cap=256,
@@ -279,10 +309,55 @@ def test_reference_golden_pages_and_output():
     basis = torch.from_numpy(np.ascontiguousarray(c["k2b_Vb"]))
     K.k2b_append(pool, k_pre.to(dev), v.to(dev), basis.to(dev), signs.to(dev), cb.to(dev), slots, n_pages)
     st = to_np(K.k2b_export_stacks(pool, slots))
-    assert (st["us"][:, 0] != c["k2b_stack_us"]).mean() < 0.01
-    for name in ("res_int_packed", "v_idx_packed"):
-        assert (st[name] != c["k2b_stack_" + name]).mean() < 5e-3, name
-    assert (st["v_norm"] != c["k2b_stack_v_norm"]).mean() < 0.02
+    # --- against the reference's own stacks.  The reference's projection is a BLAS GEMM, so its fp16 coefficients differ
+    #     from any other summation order in ~0.24 % of entries, by one fp16 ulp, at rounding ties; a residual code may
+    #     differ only in a token row whose coefficients differ or at a rounding tie of its own; a value index only in a
+    #     row whose norm differs (an fp16 tie of the norm) or at a bucket boundary. ---
+    C, Mk64, Vb64 = h_kv * D, c["k2b_k_pre"].astype(np.float64), c["k2b_Vb"].astype(np.float64)
+    us_gpu, us_ref = st["us"][:, 0].reshape(-1, rank), c["k2b_stack_us"].reshape(-1, rank)
+    Us64, mag = Mk64 @ Vb64, np.abs(Mk64) @ np.abs(Vb64)
+    dcoef = us_gpu.view(np.uint16) != us_ref.view(np.uint16)
+    if dcoef.any():
+        assert np.abs(us_gpu.view(np.uint16)[dcoef].astype(int) - us_ref.view(np.uint16)[dcoef].astype(int)).max() == 1
+        mid = (us_gpu[dcoef].astype(np.float64) + us_ref[dcoef].astype(np.float64)) / 2
+        assert (np.abs(Us64[dcoef] - mid) / (mag[dcoef] * 2.0 ** -24)).max() < 8 * math.sqrt(C)
+    rows_coef = dcoef.any(axis=1).reshape(n_pages, page)                       # token rows whose coefficients differ
+    basis16 = c["k2b_Vb"].astype(np.float16).astype(np.float64)
+    n_code_diff = n_code_tie = n_idx_diff = n_norm_diff = 0
+    cbv = np.asarray(K.GAUSSIAN_CODEBOOK[2], np.float32)
+    mids = ((cbv[:-1] + cbv[1:]) / 2).astype(np.float64)
+    for p in range(n_pages):
+        code_gpu = O.unpack_signed_codes(st["res_int_packed"][p], 3, page)      # (C, page)
+        code_ref = O.unpack_signed_codes(c["k2b_stack_res_int_packed"][p], 3, page)
+        d = code_gpu != code_ref
+        n_code_diff += int(d.sum())
+        free = d & ~rows_coef[p][None, :]                                          # differing codes in rows with equal coefficients
+        if free.any():
+            L = st["us"][p, 0].astype(np.float64) @ basis16.T                     # (page, C)
+            R = (Mk64[p * page:(p + 1) * page] - L).T                               # (C, page)
+            scale = np.abs(R).reshape(C, page // 64, 64).max(-1) / 3.0             # the float32 scale, before its fp16 rounding
+            x = R / np.repeat(scale, 64, axis=1)
+            r = assert_round_ties(x, np.where(free, code_gpu, 0), np.where(free, code_ref, 0), 2e-5, "key residual code vs reference")
+            n_code_tie += r["differing"]
+        norm_gpu, norm_ref = st["v_norm"][p], c["k2b_stack_v_norm"][p]             # (page, h_kv)
+        dn = norm_gpu.view(np.uint16) != norm_ref.view(np.uint16)
+        n_norm_diff += int(dn.sum())
+        Mv = c["k2b_v"][p * page:(p + 1) * page].astype(np.float64).reshape(page, h_kv, D)
+        assert_fp16_rounding_ties(np.sqrt((Mv ** 2).sum(-1)), norm_gpu, norm_ref, 2e-6, "value norm vs reference")
+        idx_gpu, idx_ref = O.unpack_codes(st["v_idx_packed"][p], 2, C), O.unpack_codes(c["k2b_stack_v_idx_packed"][p], 2, C)
+        di = (idx_gpu != idx_ref).reshape(page, h_kv, D)
+        n_idx_diff += int(di.sum())
+        unit = (c["k2b_v"][p * page:(p + 1) * page].reshape(page, h_kv, D) / norm_gpu.astype(np.float32)[..., None]) * signs.numpy()
+        y = O.fwht(unit.astype(np.float32)).astype(np.float64) * float(np.float32(math.sqrt(D)))
+        free = di & ~dn[..., None]
+        assert_bucket_ties(y, mids, np.where(free, idx_gpu.reshape(page, h_kv, D), 0), np.where(free, idx_ref.reshape(page, h_kv, D), 0),
+                           2e-5, "value index vs reference")
+    n_coef = us_gpu.size
+    print(f"vs reference stacks: coefficients {int(dcoef.sum())}/{n_coef} differ (1 ulp, ties), residual codes {n_code_diff}/{n_pages * C * page} "
+          f"({n_code_tie} in rows with equal coefficients: ties), value indices {n_idx_diff}, norms {n_norm_diff}/{n_pages * page * h_kv}")
+    assert dcoef.sum() <= 0.0072 * n_coef                      # 3 x the 0.24 % floor of a different summation order
+    assert n_code_diff <= 1e-3 * n_pages * C * page and n_idx_diff <= max(2, 3e-4 * n_pages * C * page)
+    assert n_norm_diff <= max(1, 3e-4 * n_pages * page * h_kv)  # floor 1.5e-5 .. 8.5e-5 of rows
     np.testing.assert_allclose(st["res_scale"].astype(np.float32), c["k2b_stack_res_scale"].astype(np.float32), rtol=2e-3)
     tail_len = c["k_tail"].shape[1]
     cos16 = torch.from_numpy(full_rope(c["rope_cos_f32"])).half()
@@ -333,3 +408,17 @@ def test_append_bytes_equal_pinned_order_restatement(page, rank, per_head, group
             assert np.array_equal(st["res_scale"][i].view(np.uint16), ref["res_scale"].view(np.uint16)), "residual scales"
             assert np.array_equal(st["v_idx_packed"][i], O.pack_codes(ref["v_idx"].astype(np.int16), 2)), "value codes"
             assert np.array_equal(st["v_norm"][i].view(np.uint16), ref["v_norm"].view(np.uint16)), "value norms"
+
+
+@pytest.mark.parametrize("T,h_kv", [(32768, 8), (131072, 2)])
+def test_decode_parity_at_benchmark_context(T, h_kv):
+    """The bench geometry (G 4, rank 32 per head, 128-token pages, groups of 64, 128-token window) at the contexts the
+    headline numbers are quoted on: one sequence of 32768 tokens with all 8 KV heads, and one of 131072 tokens with two.
+    fp16 accumulators, fp16 weights and an fp16 value table have every reason to lose accuracy with the context length;
+    the bar stays 2e-3 against the oracle's float32 chunked dequant-attention on the same stored pages."""
+    dev, K = _dev(), _K()
+    out, ref = _decode_case(dev, K, n_seq=1, h_kv=h_kv, G=4, page=128, rank=32, per_head=True, group=64,
+                            pages_per_seq=[T // 128], tail_lens=[128], seed=41, shuffle_slots=False)
+    err = np.abs(out - ref).max(axis=-1) / np.abs(ref).max(axis=-1)
+    print(f"T={T}: worst relative error {float(err.max()):.3e} over {err.size} (sequence, head) rows")
+    _assert_attn_close(out, ref)
