@@ -10,8 +10,11 @@ a per-head rank-32 basis and a 3-bit residual, values Hadamard + 2-bit Lloyd cod
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank holds its own B = 8 batch: KV heads
 and sequences are independent, so the path shards with no collective ("weak" scaling); the time is
-the maximum over ranks.  `--impl reference` times the CPU restatement of the reference's chunked
-dequant-attention (oracle/) on the host cores over a bounded sample of the same workload.
+the maximum over ranks.  The same line carries, under `configs`, device timings of the path's other
+configurations: the RTN cache (B = 1, T = 4096), quantize-on-append (B = 16), the K4 spectral cache
+(B = 64 over all ranks) and one 131072-token sequence split across the ranks with one NCCL all-gather
+per step.  `--impl reference` times the CPU restatement of the reference's chunked dequant-attention
+(oracle/) on the host cores over a bounded, named sample of the same workload.
 Prints ONE JSON line on rank 0.
 """
 
@@ -33,9 +36,9 @@ H_KV, G, D, RANK, PAGE, GROUP, WINDOW = 8, 4, 128, 32, 128, 64, 128
 BATCH, CTX = 8, 32768
 BYTES_PER_UNIT = 166  # per (token, kv head): coefficients 64 + residual nibbles 64 + scales 4 + value codes 32 + norm 2
 ROPE_THETA = 500000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_t5_kernel launch, from the ncu capture
-# summarised in profiles/k2b_decode_t5_kernel_B8_T16384.md (174.9 + 4.7 MB at 16384 tokens), scaled by 2
-# to this workload's 32768 tokens (the kernel streams every page once, so traffic grows with tokens).
+# dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_t5_kernel launch from an ncu capture at 16384 tokens
+# (174.9 + 4.7 MB), scaled by 2 to this workload's 32768 tokens: the kernel streams every page once, so traffic grows
+# in proportion to the tokens.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.90e6 + 4.69e6)
 
 
@@ -153,71 +156,102 @@ def build_state(device, seed, batch=BATCH, ctx=CTX):
 # CPU arm: the oracle's chunked dequant-attention over a bounded sample of the same workload
 # ------------------------------------------------------------------------------------------------
 
-def cpu_reference_arm(budget_s: float = 12.0, seed: int = 2000):
-    """Times oracle.chunked_dequant_attention (numpy, all BLAS threads) on n pages of one sequence
-    (8 KV heads, 32 query heads), pages quantized by the oracle codec.  Returns (GB/s of packed
-    bytes consumed, cores used, sample description, us per full layer-step extrapolated)."""
-    import numpy as np
-    import torch  # only for the seeded sign vector, as the reference draws it
+def _host_cores() -> int:
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
-    from oracle import bmx_oracle as O
 
-    rng = np.random.default_rng(seed)
-    C = H_KV * D
-    basis = np.zeros((C, H_KV * RANK), np.float32)  # block-diagonal: one rank-32 basis per head
-    for h in range(H_KV):
-        Qm, _ = np.linalg.qr(rng.standard_normal((D, RANK)).astype(np.float32))
-        basis[h * D:(h + 1) * D, h * RANK:(h + 1) * RANK] = Qm
-    g = torch.Generator().manual_seed(0)
-    signs = (torch.randint(0, 2, (D,), generator=g) * 2 - 1).numpy().astype(np.float32)
-    decay = (np.arange(1, RANK + 1, dtype=np.float32) ** -1.5)
-    cos, sin = O.default_rope_tables(ROPE_THETA, D, 64 * PAGE)
-    cos16, sin16 = cos.astype(np.float16).astype(np.float32), sin.astype(np.float16).astype(np.float32)
-    q = (rng.standard_normal((H_KV * G, 1, D)) / math.sqrt(D)).astype(np.float32)
+class CpuReference:
+    """The CPU arm: oracle.chunked_dequant_attention (a numpy restatement of bmx's chunked dequant-attention, all BLAS
+    threads) over `n_pages` pages of ONE sequence of the workload (8 KV heads, 32 query heads), pages quantized by the
+    oracle codec.  A step attends over the whole sample once; the metric is a rate (packed bytes consumed per second),
+    so it does not depend on the sample size, and the sample is named in the output."""
 
-    def make_pages(n):
-        kb, vb = [], []
-        for p in range(n):
+    def __init__(self, n_pages: int, seed: int = 2000):
+        import numpy as np
+        import torch  # only for the seeded sign vector, as the reference draws it
+
+        from oracle import bmx_oracle as O
+
+        self.O, self.n_pages = O, n_pages
+        rng = np.random.default_rng(seed)
+        C = H_KV * D
+        basis = np.zeros((C, H_KV * RANK), np.float32)  # block-diagonal: one rank-32 basis per head
+        for h in range(H_KV):
+            Qm, _ = np.linalg.qr(rng.standard_normal((D, RANK)).astype(np.float32))
+            basis[h * D:(h + 1) * D, h * RANK:(h + 1) * RANK] = Qm
+        g = torch.Generator().manual_seed(0)
+        self.signs = (torch.randint(0, 2, (D,), generator=g) * 2 - 1).numpy().astype(np.float32)
+        decay = (np.arange(1, RANK + 1, dtype=np.float32) ** -1.5)
+        cos, sin = O.default_rope_tables(ROPE_THETA, D, n_pages * PAGE)
+        self.cos16, self.sin16 = cos.astype(np.float16).astype(np.float32), sin.astype(np.float16).astype(np.float32)
+        self.q = (rng.standard_normal((H_KV * G, 1, D)) / math.sqrt(D)).astype(np.float32)
+        self.kb, self.vb = [], []
+        for p in range(n_pages):
             coef = rng.standard_normal((PAGE, H_KV * RANK)).astype(np.float32) * np.tile(decay, H_KV)
             Mk = (coef @ basis.T + 0.1 * rng.standard_normal((PAGE, C)).astype(np.float32)).astype(np.float16).astype(np.float32)
             Mv = rng.standard_normal((PAGE, C)).astype(np.float16).astype(np.float32)
             kp, _ = O.quantize_packed("lowrank_rtn_channel", Mk, bits=3, group=GROUP, rank=RANK, svd_factors=(Mk @ basis, basis))
-            vp, _ = O.quantize_packed("turboquant_mse_perhead", Mv, bits=2, h_heads=H_KV, signs=signs)
-            kb.append((kp, p * PAGE, (p + 1) * PAGE))
-            vb.append((vp, p * PAGE, (p + 1) * PAGE))
-        return kb, vb
+            vp, _ = O.quantize_packed("turboquant_mse_perhead", Mv, bits=2, h_heads=H_KV, signs=self.signs)
+            self.kb.append((kp, p * PAGE, (p + 1) * PAGE))
+            self.vb.append((vp, p * PAGE, (p + 1) * PAGE))
+        self.units = n_pages * PAGE * H_KV
 
-    def run(kb, vb):
+    def step(self) -> float:
         t0 = time.perf_counter()
-        O.chunked_dequant_attention(q, kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead", group=GROUP,
-                                    k_pre_rope=True, rope_cos=cos16, rope_sin=sin16, k_tail=None, v_tail=None,
-                                    n_q_groups=G, scale=1.0 / math.sqrt(D), v_signs=signs)
+        self.O.chunked_dequant_attention(self.q, self.kb, self.vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead",
+                                         group=GROUP, k_pre_rope=True, rope_cos=self.cos16, rope_sin=self.sin16, k_tail=None,
+                                         v_tail=None, n_q_groups=G, scale=1.0 / math.sqrt(D), v_signs=self.signs)
         return time.perf_counter() - t0
 
-    kb, vb = make_pages(4)
-    run(kb, vb)
-    per_page = run(kb, vb) / 4
-    n = int(max(4, min(64, budget_s / max(per_page, 1e-4))))
-    kb, vb = make_pages(n)
-    dt = run(kb, vb)
-    units = n * PAGE * H_KV
-    gbs = units * BYTES_PER_UNIT / dt / 1e9
-    full_us = dt / units * (BATCH * H_KV * CTX) * 1e6
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    sample = f"{n} pages x {PAGE} tokens x {H_KV} kv heads of one sequence ({units} of {BATCH * H_KV * CTX} units), numpy oracle"
-    return gbs, cores, sample, full_us
+    def sample(self) -> str:
+        return (f"{self.n_pages} pages x {PAGE} tokens x {H_KV} kv heads of one sequence ({self.units} of {BATCH * H_KV * CTX} units of "
+                f"the workload), numpy restatement of bmx chunked_dequant_attention")
+
+
+def cpu_pages_for(total_budget_s: float, n_steps: int) -> int:
+    """Pages per step such that n_steps steps take about total_budget_s: a whole sequence (256 pages) if that fits."""
+    probe = CpuReference(8)
+    probe.step()
+    per_page = probe.step() / 8
+    return int(max(8, min(CTX // PAGE, total_budget_s / max(n_steps, 1) / max(per_page, 1e-5))))
+
+
+def cpu_baseline_leg(budget_s: float = 12.0):
+    """cpu_baseline of the GPU arm's line: one warm-up step and up to three timed steps over a bounded sample."""
+    n = cpu_pages_for(budget_s, 4)
+    ref = CpuReference(n)
+    ref.step()
+    times = [ref.step() for _ in range(3)]
+    dt = sum(times) / len(times)
+    return {"value": ref.units * BYTES_PER_UNIT / dt / 1e9, "unit": "GB/s", "cores": _host_cores(), "kind": "port",
+            "sample": ref.sample(), "ms_per_sample_step": dt * 1e3,
+            "us_per_layer_step_extrapolated": dt / ref.units * (BATCH * H_KV * CTX) * 1e6}
 
 
 def run_reference(args, rank):
+    """`--impl reference`: W warm-up and exactly K timed steps of the CPU arm on rank 0; every step attends over the
+    sample named in config.workload (one whole sequence of the workload when K steps of it fit in about two minutes)."""
     if rank != 0:
         return
-    gbs, cores, sample, full_us = cpu_reference_arm(budget_s=max(5.0, min(30.0, 4.0 * args.steps)))
+    warm = max(args.warmup, 1)
+    n = cpu_pages_for(120.0, args.steps + warm)
+    ref = CpuReference(n)
+    for _ in range(warm):
+        ref.step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ref.step()
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = ref.units * BYTES_PER_UNIT / dt / 1e9
+    cfg = workload_config(args.gpus)
+    cfg["workload"] = ("CPU arm: " + ref.sample() + "; same geometry and distributions as the GPU arm's workload (" + cfg["workload"] + ")")
+    cfg["sample_pages_per_step"], cfg["sample_units_per_step"] = n, ref.units
     line = {
         "impl": "reference", "metric": "k2b_decode_effective_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_us / 1e3, "us_per_layer_step": full_us,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "steps": args.steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+        "us_per_layer_step_extrapolated": dt / ref.units * (BATCH * H_KV * CTX) * 1e6,
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": _host_cores(), "kind": "port", "sample": ref.sample()},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -299,17 +333,26 @@ def run_ours(args, rank, world, local_rank):
     merge_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / n_k
     K.check_status(state.workspace)
 
+    # ---- the step's own output checked against the CPU oracle on the same stored pages, for one (sequence, head) at
+    #      the full context (rank 0 only; outside every timed region) ----
+    selfcheck = None
+    if rank == 0:
+        selfcheck = oracle_check_one_head(state, q, seq=0, head=min(3, H_KV - 1))
+        assert selfcheck["max_rel_err"] <= 2e-3, f"decode output off the oracle: {selfcheck}"
+
     # ---- end to end through the layer-state API with host buffers: per step the new token's K/V and
     #      the query come from pinned host memory, the attention output goes back to the host ----
-    n_e2e = min(args.steps, 64)
     # DecodeStepGraph: one pinned staging buffer [q | k_post | v | k_pre] in, the attention output out; the copies, the
-    # window append and the two decode kernels replay as one CUDA graph (steps that commit pages run eagerly)
+    # window append and the two decode kernels replay as one CUDA graph; the step on which the flush schedule commits
+    # a page per sequence (one in 128) runs the append kernels eagerly.  160 steps from a 128-token window: the timed
+    # region holds exactly one such step.
+    n_e2e = 160
     from bmx_b200.engine import DecodeStepGraph
 
     nq, nk = BATCH * H_KV * G * D, BATCH * H_KV * D
     hin = torch.empty(nq + 3 * nk, dtype=torch.float16).pin_memory()
     hin[:nq].copy_(q.cpu().reshape(-1))
-    hin[nq:].copy_(torch.randn(3 * nk).half())
+    hin[nq:].copy_((0.3 * torch.randn(3 * nk)).half())
     hout = torch.empty(BATCH, H_KV * G, D, dtype=torch.float16).pin_memory()
     stepper = DecodeStepGraph(state, hin, hout)
     h2d = hin.numel() * 2  # q, the new token's post-RoPE key, value and pre-RoPE key
@@ -322,29 +365,48 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(3):
         e2e_step()
     barrier()
+    committed_before = state.committed
+    step_wall = []
     t0 = time.perf_counter()
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     g0.record()
     for _ in range(n_e2e):
+        t1 = time.perf_counter()
         e2e_step()
+        step_wall.append(time.perf_counter() - t1)
     g1.record()
     torch.cuda.synchronize()
     e2e_ms = max(g0.elapsed_time(g1), (time.perf_counter() - t0) * 1e3) / n_e2e
+    flush_steps = (state.committed - committed_before) // PAGE
+    flush_us = max(step_wall) * 1e6
+    plain_us = sorted(step_wall)[len(step_wall) // 2] * 1e6
     K.check_status(state.workspace)
 
-    t = torch.tensor([total_ms, main_ms, merge_ms, e2e_ms], dtype=torch.float64, device=device)
+    mine = torch.tensor([total_ms / args.steps, main_ms, merge_ms, e2e_ms], dtype=torch.float64, device=device)
+    per_rank = mine.clone().unsqueeze(0)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, main_ms, merge_ms, e2e_ms = t.tolist()
-    ms_per_step = total_ms / args.steps
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        per_rank = torch.stack(gathered)
+    ms_per_step, main_ms, merge_ms, e2e_ms = per_rank.max(0).values.tolist()
+
+    # ---- the other configurations of the path (device timings with CUDA events; each builds and frees its own state) ----
+    del stepper
+    state = None
+    torch.cuda.empty_cache()
+    extra = {}
     if rank == 0:
+        extra["rtn_b1_t4096"] = config_rtn(device)
+        extra["append_b16"] = config_append(device)
+    extra_all = {"spectral_b64_t16384": config_spectral(device, rank, world, dist if world > 1 else None),
+                 "seq_split_t131072": config_seq_split(device, rank, world, dist if world > 1 else None)}
+
+    if rank == 0:
+        extra.update(extra_all)
         peak, peak_kind = measured_peak_gbs()
         achieved = algo_bytes / (main_ms * 1e-3) / 1e9
-        cpu = None
-        if world == 1:
-            gbs, cores, sample, full_us = cpu_reference_arm(budget_s=10.0)
-            cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
-                   "us_per_layer_step_extrapolated": full_us}
+        cpu = cpu_baseline_leg(10.0) if world == 1 else None
+        cols = ("ms_per_step", "kernel_ms", "merge_kernel_ms", "e2e_ms")
         line = {
             "metric": "k2b_decode_effective_GBps", "value": world * algo_bytes / (ms_per_step * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
@@ -357,33 +419,273 @@ def run_ours(args, rank, world, local_rank):
                          "kernel_us": main_ms * 1e3, "merge_kernel_us": merge_ms * 1e3},
             "cpu_baseline": cpu,
             "e2e": {"value": world * algo_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer_step": e2e_ms * 1e3,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e, "flush_steps_in_region": int(flush_steps),
+                    "us_flush_step": flush_us, "us_median_step": plain_us},
+            "per_rank": [dict(zip(cols, row)) for row in per_rank.tolist()],
+            "oracle_check": selfcheck,
+            "configs": extra,
             "gpu_launches": 2 * args.steps,
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def oracle_check_one_head(state, q, seq: int, head: int) -> dict:
+    """Decodes once into a float32 buffer and compares (sequence, head) with the CPU oracle's chunked dequant-attention
+    over the pages as stored (exported in bmx's layout) plus the fp16 window.  The oracle is the checker here."""
+    import numpy as np
+    import torch
+
+    from bmx_b200 import kernels as K
+    from oracle import bmx_oracle as O
+
+    g = state.geom
+    out = torch.empty(state.batch, g.h_kv * g.n_q_groups, D, dtype=torch.float32, device=state.device)
+    state.decode(q, out=out)
+    torch.cuda.synchronize()
+    n_pg, tl = state.committed // PAGE, state.tail_len
+    st = {a: t.cpu().numpy() for a, t in K.k2b_export_stacks(state.pool, state.page_table[seq, :n_pg].contiguous()).items()}
+    basis16 = state.basis_f16[head * D:(head + 1) * D].float().cpu().numpy()
+    signs = state.signs.cpu().numpy()
+    kb, vb = [], []
+    for p in range(n_pg):
+        kp = {"Us": st["us"][p, head].astype(np.float32), "V": basis16,
+              "res_Q_int": O.unpack_signed_codes(st["res_int_packed"][p][head * D:(head + 1) * D], g.kbits, PAGE),
+              "res_scale": st["res_scale"][p][head * D:(head + 1) * D].astype(np.float32)[..., None]}
+        idx = O.unpack_codes(st["v_idx_packed"][p], 2, g.h_kv * D)[:, head * D:(head + 1) * D]
+        vp = {"indices": idx, "norms": st["v_norm"][p][:, head:head + 1].astype(np.float32), "bits": 2, "h": 1}
+        kb.append((kp, p * PAGE, (p + 1) * PAGE))
+        vb.append((vp, p * PAGE, (p + 1) * PAGE))
+    cos, sin = state.rope_cos.float().cpu().numpy(), state.rope_sin.float().cpu().numpy()
+    qh = q[seq, head * g.n_q_groups:(head + 1) * g.n_q_groups].float().cpu().numpy()[:, None, :]
+    ref = O.chunked_dequant_attention(qh, kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead", group=g.group,
+                                      k_pre_rope=True, rope_cos=cos, rope_sin=sin,
+                                      k_tail=state.k_win[seq, head:head + 1, :tl].float().cpu().numpy(),
+                                      v_tail=state.v_win[seq, head:head + 1, :tl].float().cpu().numpy(), n_q_groups=g.n_q_groups,
+                                      scale=state.sm_scale, v_signs=signs)[:, 0, :]
+    got = out[seq, head * g.n_q_groups:(head + 1) * g.n_q_groups].cpu().numpy()
+    err = np.abs(got - ref).max(axis=-1) / np.abs(ref).max(axis=-1)
+    return {"sequence": seq, "kv_head": head, "tokens": state.committed + tl, "max_rel_err": float(err.max()), "bound": 2e-3}
+
+
+def _event_us(fn, n: int, warm: int = 3) -> float:
+    import torch
+
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / n
+
+
+def config_rtn(device) -> dict:
+    """BASELINE configs[0]: plain RTN cache, B = 1, 4096 committed tokens + a 128-token fp16 window; keys rtn_channel 4 bits,
+    values rtn_token 2 bits, groups of 32; K ~ N(0,1) with 4 channels per head x 8.  4.2 MB per step: the step is bound by
+    launch latency, so it is timed both as plain launches and replayed from a CUDA graph."""
+    import torch
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import RtnLayerState
+
+    T, W = 4096, 128
+    gen = torch.Generator(device=device).manual_seed(1000)
+    geom = K.rtn_geom(H_KV, G, PAGE, "rtn_channel", 32, 32, 4, 2)
+    st = RtnLayerState(geom, 1, T + 2 * PAGE, W, device)
+    k = torch.randn(1, H_KV, T + W, D, generator=gen, device=device)
+    k[..., :4] *= 8.0
+    v = torch.randn(1, H_KV, T + W, D, generator=gen, device=device)
+    st.append(None, k.half(), v.half())
+    assert st.committed == T and st.tail_len == W
+    q = (torch.randn(1, H_KV * G, D, generator=gen, device=device) / math.sqrt(D)).half()
+    out = torch.empty(1, H_KV * G, D, dtype=torch.float16, device=device)
+    eager_us = _event_us(lambda: st.decode(q, out=out), 200)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        st.decode(q, out=out)
+    graph_us = _event_us(graph.replay, 500)
+    K.check_status(st.workspace)
+    algo = T * H_KV * 112 + W * H_KV * 512  # codes 64 + 32, fp16 scales 8 + 8 per (token, head); the window is fp16 K and V
+    peak, _ = measured_peak_gbs()
+    return {"workload": "RTN packed-cache decode: B=1, T=4096 + 128-token window, K rtn_channel 4b / V rtn_token 2b, group 32",
+            "us_per_layer_step": eager_us, "us_per_layer_step_graph": graph_us, "algorithmic_bytes": algo,
+            "roofline": {"bound": "launch latency (4.2 MB of traffic: 0.64 us at the HBM peak)", "achieved": algo / graph_us / 1e3,
+                         "peak": peak, "unit": "GB/s", "frac": algo / graph_us / 1e3 / peak}, "gpu_launches_per_step": 2}
+
+
+def config_append(device) -> dict:
+    """BASELINE configs[2]: quantize-on-append of the k2b recipe, B = 16, bf16 sources, one layer (the 32 layers of the config
+    repeat it).  Bulk: the 16384-token prefix of all sequences in one call (128 pages x 16 sequences x 8 heads).  Streaming:
+    single-token steps on top of it, 127 of every 128 move one token into the fp16 window, the 128th commits a page per
+    sequence.  Bytes per (page, head): read 2 x 128 x 128 x 2 (key and value sources), write 13056 + 8192."""
+    import torch
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import default_rope_tables
+
+    B, T0, W = 16, 16384, 128
+    gen = torch.Generator(device=device).manual_seed(3000)
+    basis = make_basis(gen, device)
+    cos, sin = default_rope_tables(ROPE_THETA, D, T0 + 4096, device=device)
+    out = {}
+    total = T0 + W + 2 * PAGE + 8
+    k_pre = torch.empty(B, H_KV, total, D, dtype=torch.bfloat16, device=device)
+    v = torch.empty_like(k_pre)
+    for b in range(B):
+        kb_, vb_ = make_kv(gen, basis, 1, total, device)
+        k_pre[b], v[b] = kb_[0].bfloat16(), vb_[0].bfloat16()
+    peak, _ = measured_peak_gbs()
+    for page in (128, 64):
+        geom = K.k2b_geom(H_KV, G, page, RANK, GROUP, H_KV)
+        n_pg = T0 // page
+        pool = K.K2bPool(geom, B * n_pg, device)
+        slots = torch.arange(B * n_pg, dtype=torch.int32, device=device)
+        signs, cb = K.hadamard_signs(D, 0).to(device), torch.tensor(K.GAUSSIAN_CODEBOOK[2], device=device)
+        us = _event_us(lambda: K.k2b_append(pool, k_pre, v, basis, signs, cb, slots, n_pg), 3, warm=1)
+        items = B * n_pg * H_KV
+        nbytes = items * (2 * page * D * 2 + K.page_block_bytes(geom) + K.coef_block_bytes(geom))
+        out[f"bulk_prefix_page{page}"] = {"us": us, "pages_per_s": B * n_pg / us * 1e6, "page_heads_per_s": items / us * 1e6,
+                                          "GBps": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak,
+                                          "bytes": nbytes, "gpu_launches": 1}
+        del pool
+    geom = K.k2b_geom(H_KV, G, PAGE, RANK, GROUP, H_KV)
+    st = K2bLayerState(geom, B, T0 + 4096, W, device, cos.half(), sin.half())
+    st.set_basis(basis)
+    n0 = T0 + W
+    st.append(k_pre[:, :, :n0], k_pre[:, :, :n0], v[:, :, :n0])  # the post-RoPE window keys do not matter for timing
+    assert st.committed == T0 and st.tail_len == W
+    plain, flush = [], []
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(2 * PAGE + 1)]
+    e[0].record()
+    for i in range(2 * PAGE):
+        t = n0 + i
+        st.append(k_pre[:, :, t:t + 1], k_pre[:, :, t:t + 1], v[:, :, t:t + 1])
+        e[i + 1].record()
+    torch.cuda.synchronize()
+    committed = T0
+    from bmx_b200.schedule import compute_flush_schedule
+    for i in range(2 * PAGE):
+        new_c = compute_flush_schedule(n0 + i + 1, W, PAGE)
+        (flush if new_c > committed else plain).append(e[i].elapsed_time(e[i + 1]) * 1e3)
+        committed = max(committed, new_c)
+    assert st.committed == T0 + 2 * PAGE and len(flush) == 2
+    step_bytes = B * H_KV * (2 * PAGE * D * 2 + K.page_block_bytes(geom) + K.coef_block_bytes(geom))
+    out["streaming_page128"] = {"us_non_flush_step": sorted(plain)[len(plain) // 2], "us_flush_step": sum(flush) / len(flush),
+                                "flush_every_steps": PAGE, "bytes_per_flush_step": step_bytes,
+                                "us_per_token_all_32_layers": 32 * (sum(plain) + sum(flush)) / (len(plain) + len(flush)),
+                                "note": "host-launched steps (torch ops + kernel launches on one stream), one layer"}
+    out["workload"] = "k2b quantize-on-append, B=16, bf16 sources, 16384-token prefix then single-token steps, 128-token window"
+    return out
+
+
+def config_seq_split(device, rank, world, dist) -> dict:
+    """BASELINE configs[3]: one sequence of 131072 committed tokens (32 q / 8 kv heads, d 128, k2b recipe), its pages split
+    across the ranks; every rank decodes its part into an un-normalised state (max, sum, accumulator), ONE all-gather of
+    (32 x 130) floats per rank, then the merge.  Rank 0 also holds the whole sequence and checks the merged output against
+    its own single-GPU decode (2e-3).  At one GPU this is just the single-GPU long-context step."""
+    import torch
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.dist import SequenceSplitDecoder, split_pages
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope, default_rope_tables
+
+    T, W = 131072, 128
+    n_pg = T // PAGE
+    gen = torch.Generator(device=device).manual_seed(4000)  # the same sequence on every rank
+    basis = make_basis(gen, device)
+    cos, sin = default_rope_tables(ROPE_THETA, D, T + 4096, device=device)
+    geom = K.k2b_geom(H_KV, G, PAGE, RANK, GROUP, H_KV)
+    k_pre, v = make_kv(gen, basis, 1, T + W, device)
+    q = (torch.randn(1, H_KV * G, D, generator=gen, device=device) / math.sqrt(D)).half()
+    first, count = split_pages(n_pg, world)[rank]
+    last = rank == world - 1
+    st = K2bLayerState(geom, 1, count * PAGE + 2 * PAGE, W, device, cos.half(), sin.half())
+    st.set_basis(basis)
+    slots = st.page_table[0, :count].contiguous()
+    lo = first * PAGE
+    K.k2b_append(st.pool, k_pre[:, :, lo:lo + count * PAGE], v[:, :, lo:lo + count * PAGE], st.basis_f32, st.signs, st.codebook, slots, count)
+    st.committed = count * PAGE
+    st.n_pages_dev.fill_(count)
+    if last:
+        k_post = apply_rope(k_pre[:, :, T:].float(), cos[T:T + W], sin[T:T + W]).half()
+        st.k_win[:, :, :W], st.v_win[:, :, :W], st.k_pre_win[:, :, :W] = k_post, v[:, :, T:], k_pre[:, :, T:]
+        st.tail_len = W
+        st.tail_len_dev.fill_(W)
+    out = torch.empty(H_KV * G, D, dtype=torch.float32, device=device)
+    res = {"workload": "k2b decode, one sequence of 131072 tokens + 128-token window, pages split across the ranks, one all-gather "
+                       "of (32 x 130) floats per rank, merge on every rank", "pages_per_rank": count}
+    if world == 1:
+        o1 = torch.empty(1, H_KV * G, D, dtype=torch.float32, device=device)
+        step_us = _event_us(lambda: st.decode(q, out=o1), 100)
+        kern_us = _event_us(lambda: st.decode(q, out=o1, phases=1), 100)
+        K.check_status(st.workspace)
+        algo = T * H_KV * BYTES_PER_UNIT
+        peak, _ = measured_peak_gbs()
+        res.update(us_per_layer_step=step_us, kernel_us=kern_us, achieved_GBps=algo / kern_us / 1e3, frac_of_hbm_peak=algo / kern_us / 1e3 / peak,
+                   algorithmic_bytes=algo, collective=None)
+        return res
+    dec = SequenceSplitDecoder(st, first)
+    step_us = _event_us(lambda: dec.decode(q, out=out), 100)
+    kern_us = _event_us(lambda: st.decode(q, partial_out=dec.part, pos_offset=first * PAGE, phases=1), 100)
+    K.check_status(st.workspace)
+    t = torch.tensor([step_us, kern_us], dtype=torch.float64, device=device)
+    allt = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(allt, t)
+    allt = torch.stack(allt)
+    # rank 0 decodes the whole sequence by itself and compares
+    max_rel = None
+    if rank == 0:
+        full = K2bLayerState(geom, 1, T + 2 * PAGE, W, device, cos.half(), sin.half())
+        full.set_basis(basis)
+        K.k2b_append(full.pool, k_pre[:, :, :T], v[:, :, :T], full.basis_f32, full.signs, full.codebook,
+                     full.page_table[0, :n_pg].contiguous(), n_pg)
+        full.committed = T
+        full.n_pages_dev.fill_(n_pg)
+        k_post = apply_rope(k_pre[:, :, T:].float(), cos[T:T + W], sin[T:T + W]).half()
+        full.k_win[:, :, :W], full.v_win[:, :, :W], full.k_pre_win[:, :, :W] = k_post, v[:, :, T:], k_pre[:, :, T:]
+        full.tail_len = W
+        full.tail_len_dev.fill_(W)
+        o1 = torch.empty(1, H_KV * G, D, dtype=torch.float32, device=device)
+        full.decode(q, out=o1)
+        dec.decode(q, out=out)
+        torch.cuda.synchronize()
+        err = (out - o1[0]).abs().amax(-1) / o1[0].abs().amax(-1)
+        max_rel = float(err.max())
+        assert max_rel <= 2e-3, f"sequence-split output differs from the single-GPU decode: {max_rel:.3e}"
+    algo_rank = count * PAGE * H_KV * BYTES_PER_UNIT
+    peak, _ = measured_peak_gbs()
+    res.update(us_per_layer_step=float(allt[:, 0].max()), per_rank_step_us=allt[:, 0].tolist(), per_rank_kernel_us=allt[:, 1].tolist(),
+               per_rank_achieved_GBps=[algo_rank / u / 1e3 for u in allt[:, 1].tolist()],
+               frac_of_hbm_peak_per_rank=algo_rank / float(allt[:, 1].max()) / 1e3 / peak,
+               collective="NCCL all_gather_into_tensor of 32 x 130 float32 per rank", max_rel_err_vs_single_gpu=max_rel)
+    return res
 
 
 # ------------------------------------------------------------------------------------------------
 # Secondary workload (not the headline line): BASELINE configs[4], K4 spectral keys, one GPU
 # ------------------------------------------------------------------------------------------------
 
-def run_spectral(args):
-    """B = 64 sequences x 16384 committed tokens, per-head 128 x 128 packs at ~2.6 bits per direction, values as in
-    the k2b workload; one page set is quantized for real and copied to every sequence (distinct memory)."""
-    import math
-
+def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
+    """BASELINE configs[4]: K4 spectral keys, B = 64 sequences x 16384 committed tokens over all ranks (64 / N per rank:
+    sequences are independent, no collective), per-head 128 x 128 packs at ~2.6 bits per direction, values as in the k2b
+    workload; one page set is quantized for real and copied to every sequence (distinct memory).  The bound of this kernel
+    is max(bytes at the HBM peak, decoder product at the sustained tensor peak)."""
     import torch
 
     from bmx_b200 import kernels as K
     from bmx_b200.rope import default_rope_tables
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
-    dev = torch.device("cuda", 0)
-    B, T = 64, 16384
+    dev = device
+    B, T = max(1, 64 // world), 16384
     g = torch.Generator().manual_seed(5000)
     tiers = {8: 2, 6: 6, 5: 10, 4: 16, 3: 26, 2: 44}  # 104 directions with bits, 2.6 bits per direction on average
     enc, bits = [], []
@@ -420,30 +722,19 @@ def run_spectral(args):
         K.spectral_decode(pack, G, kpool, vpool, q, table, n_pages, npg, cos, sin, kt, vt, tl, lut, signs, 1 / math.sqrt(D), ws,
                           out=out, phases=ph)
 
-    clocks = ClockSampler(0).__enter__()
-    t_w, n_w = time.perf_counter(), 0
-    while n_w < max(args.warmup, 3) or time.perf_counter() - t_w < 0.4:
+    for _ in range(5):
         step(3)
-        n_w += 1
     torch.cuda.synchronize()
     K.check_status(ws)
-    steps = min(args.steps, 50)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        step(3)
-    e1.record()
-    torch.cuda.synchronize()
-    clocks.__exit__(None, None, None)
-    ms = e0.elapsed_time(e1) / steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
-    for i in range(steps):  # the page-streaming kernel alone, for the roofline
-        ev[i][0].record()
-        step(1)
-        ev[i][1].record()
-    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = _event_us(lambda: step(3), steps, warm=0) / 1e3
+    main_ms = _event_us(lambda: step(1), steps, warm=0) / 1e3
     K.check_status(ws)
-    main_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
+    t = torch.tensor([ms, main_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, main_ms = t.tolist()
     units = B * H_KV * T
     per_unit = (pack.geom.block_bytes + 4352) / 128
     algo_bytes, flops = units * per_unit, units * 2.0 * 128 * 16 * math.ceil(sum(tiers.values()) / 16)
@@ -454,19 +745,79 @@ def run_spectral(args):
     except (OSError, ValueError):
         pass
     hbm_us, mma_us = algo_bytes / peak / 1e3, flops / tf_peak / 1e6
-    print(json.dumps({
-        "metric": "spectral_decode_effective_GBps", "value": algo_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
-        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer_step": ms * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "K4 spectral packed-cache decode, 1 layer-step: 32 q / 8 kv heads, d=128, B=64, T=16384 + 128-token "
-                               "window, per-head packs (104 of 128 directions carry 2..8 bits), V Hadamard + 2-bit Lloyd",
-                   "bytes_per_token_head": per_unit, "l2": "pages read per step (0.77 GB) exceed the 126 MB L2"},
-        "roofline": {"bound": "max(hbm, tensor)", "kernel": "spectral_decode_t5_kernel<4>", "kernel_us": main_ms * 1e3,
-                     "hbm_us_at_peak": hbm_us, "tensor_us_at_peak": mma_us, "frac": max(hbm_us, mma_us) / (main_ms * 1e3),
-                     "achieved": algo_bytes / (main_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                     "achieved_tflops": flops / (main_ms * 1e-3) / 1e12, "peak_tflops": tf_peak,
-                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind}), bf16_tflops_sustained", "traffic": None},
-        "gpu_launches": 2 * steps, "clocks": clocks.summary()}), flush=True)
+    return {"workload": f"K4 spectral packed-cache decode: 32 q / 8 kv heads, d=128, B={B} per GPU ({B * world} in all), T=16384 + "
+                        "128-token window, per-head packs (104 of 128 directions carry 2..8 bits), V Hadamard + 2-bit Lloyd",
+            "value_GBps_all_gpus": world * algo_bytes / (ms * 1e-3) / 1e9, "us_per_layer_step": ms * 1e3, "steps": steps,
+            "bytes_per_token_head": per_unit, "gpu_launches_per_step": 2,
+            "roofline": {"bound": "max(hbm, tensor)", "kernel": "spectral_decode_t5_kernel<4>", "kernel_us": main_ms * 1e3,
+                         "hbm_us_at_peak": hbm_us, "tensor_us_at_peak": mma_us, "frac": max(hbm_us, mma_us) / (main_ms * 1e3),
+                         "achieved": algo_bytes / (main_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "achieved_tflops": flops / (main_ms * 1e-3) / 1e12, "peak_tflops": tf_peak,
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind}), bf16_tflops_sustained", "traffic": None}}
+
+
+def run_hf(args) -> None:
+    """`--workload hf`: per-token decode latency of a random-init Llama-shaped model (Llama-3.1-8B layer dimensions, four
+    layers, small vocabulary) with PackedStreamingCache (k2b) against DynamicCache: prefill 8192 tokens at B = 4, then time
+    single-token forwards with CUDA events.  bmx measures the same for its own classes in scripts/profile_decode_ab.py and
+    reports host overhead, not the kernel, as what dominates there.  Only time is compared: a random-init model's keys have
+    none of the structure the codecs rely on.  Prints one JSON line."""
+    import torch
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+
+    from bmx_b200.packed_streaming import PackedStreamingCache
+    from bmx_b200.recipes import spec_pair
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
+    layers, batch, context, steps, window = 4, 4, 8192, min(args.steps, 32), 128
+    dev = torch.device("cuda:0")
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, max_position_embeddings=context + steps + 64, rope_theta=500000.0)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg).to(dev).half().eval()
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (batch, context + steps + 3), generator=g).to(dev)
+
+    def run(make_cache, attach):
+        cache = make_cache()
+        ctx = cache.attach(model) if attach else None
+        try:
+            with torch.no_grad():
+                pos = 0
+                while pos < context:  # prefill in chunks
+                    n = min(2048, context - pos)
+                    model(ids[:, pos:pos + n], past_key_values=cache, use_cache=True)
+                    pos += n
+                for t in range(3):
+                    model(ids[:, pos + t:pos + t + 1], past_key_values=cache, use_cache=True)
+                pos += 3
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0 = time.perf_counter()
+                e0.record()
+                for t in range(steps):
+                    model(ids[:, pos + t:pos + t + 1], past_key_values=cache, use_cache=True)
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) / steps, (time.perf_counter() - t0) * 1e3 / steps
+        finally:
+            if ctx is not None:
+                cache.detach()
+
+    k_spec, v_spec = spec_pair("k2b_ph", rank=32, group=64)
+    dense = {}
+    for impl in ("sdpa", "eager"):
+        model.config._attn_implementation = impl
+        ms, wall = run(lambda: DynamicCache(config=cfg), attach=False)
+        dense[impl] = {"ms_per_token": ms, "wall_ms_per_token": wall}
+    model.config._attn_implementation = "sdpa"
+    packed_ms, packed_wall = run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window), attach=True)
+    dense_ms = min(v["ms_per_token"] for v in dense.values())
+    print(json.dumps({"metric": "hf_decode_ms_per_token", "model": f"Llama-3.1-8B layer shape x {layers} layers, random init, fp16",
+                      "batch": batch, "context": context, "steps": steps, "dynamic_cache": dense,
+                      "packed_streaming_cache_k2b": {"ms_per_token": packed_ms, "wall_ms_per_token": packed_wall},
+                      "per_layer_us": {"dynamic": dense_ms * 1e3 / layers, "packed": packed_ms * 1e3 / layers}}), flush=True)
 
 
 def main():
@@ -476,8 +827,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX, help="committed tokens per sequence (smaller cases for profiling)")
-    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral"],
-                    help="k2b: the headline workload; spectral: the K4 spectral cache (one GPU, kernel timings only)")
+    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "hf"],
+                    help="k2b: the headline line (carries the other configurations under `configs`); spectral: the K4 spectral "
+                         "cache alone (one GPU, for profiling); hf: per-token latency under a random-init Hugging Face model")
     args = ap.parse_args()
     assert args.ctx % PAGE == 0 and args.ctx >= PAGE
     rank = int(os.environ.get("RANK", "0"))
@@ -488,7 +840,15 @@ def main():
         return
     if args.workload == "spectral":
         if rank == 0:
-            run_spectral(args)
+            import torch
+
+            if not torch.cuda.is_available():
+                raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
+            print(json.dumps(config_spectral(torch.device("cuda", 0), 0, 1, None, steps=min(args.steps, 50))), flush=True)
+        return
+    if args.workload == "hf":
+        if rank == 0:
+            run_hf(args)
         return
     run_ours(args, rank, world, local_rank)
 
