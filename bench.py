@@ -520,7 +520,7 @@ def config_rtn(device) -> dict:
                          "peak": peak, "unit": "GB/s", "frac": algo / graph_us / 1e3 / peak}, "gpu_launches_per_step": 2}
 
 
-def config_append(device) -> dict:
+def config_append(device, B: int = 16) -> dict:
     """BASELINE configs[2]: quantize-on-append of the k2b recipe, B = 16, bf16 sources, one layer (the 32 layers of the config
     repeat it).  Bulk: the 16384-token prefix of all sequences in one call (128 pages x 16 sequences x 8 heads).  Streaming:
     single-token steps on top of it, 127 of every 128 move one token into the fp16 window, the 128th commits a page per
@@ -531,7 +531,7 @@ def config_append(device) -> dict:
     from bmx_b200.engine import K2bLayerState
     from bmx_b200.rope import default_rope_tables
 
-    B, T0, W = 16, 16384, 128
+    T0, W = 16384, 128
     gen = torch.Generator(device=device).manual_seed(3000)
     basis = make_basis(gen, device)
     cos, sin = default_rope_tables(ROPE_THETA, D, T0 + 4096, device=device)
@@ -827,9 +827,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX, help="committed tokens per sequence (smaller cases for profiling)")
-    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "hf"],
+    ap.add_argument("--batch", type=int, default=16, help="sequences of --workload append (smaller cases for profiling)")
+    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "append", "rtn", "hf"],
                     help="k2b: the headline line (carries the other configurations under `configs`); spectral: the K4 spectral "
-                         "cache alone (one GPU, for profiling); hf: per-token latency under a random-init Hugging Face model")
+                         "cache alone, append / rtn: those configurations alone (one GPU, for profiling); hf: per-token latency "
+                         "under a random-init Hugging Face model")
     args = ap.parse_args()
     assert args.ctx % PAGE == 0 and args.ctx >= PAGE
     rank = int(os.environ.get("RANK", "0"))
@@ -845,6 +847,15 @@ def main():
             if not torch.cuda.is_available():
                 raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
             print(json.dumps(config_spectral(torch.device("cuda", 0), 0, 1, None, steps=min(args.steps, 50))), flush=True)
+        return
+    if args.workload in ("append", "rtn"):
+        if rank == 0:
+            import torch
+
+            if not torch.cuda.is_available():
+                raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
+            dev0 = torch.device("cuda", 0)
+            print(json.dumps(config_append(dev0, B=args.batch) if args.workload == "append" else config_rtn(dev0)), flush=True)
         return
     if args.workload == "hf":
         if rank == 0:

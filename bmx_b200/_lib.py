@@ -66,6 +66,9 @@ _SIGNATURES = {
                                  c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_size_t, c_void_p,
                                  c_int, c_void_p, c_int, c_void_p]),
+    "bmxk_k2b_prefill": (c_int, [POINTER(K2bGeom), c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                                 c_void_p, c_void_p, c_void_p]),
     "bmxk_k2b_decode_static": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p]),

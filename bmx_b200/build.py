@@ -22,6 +22,7 @@ SOURCES = [
     ("k2b_codec.cu", ["-fmad=false"]),
     ("k2b_decode.cu", []),
     ("k2b_decode_t5.cu", []),
+    ("k2b_prefill.cu", []),
     ("rtn.cu", ["-fmad=false"]),
     ("spectral.cu", ["-fmad=false"]),
     ("spectral_decode_t5.cu", []),

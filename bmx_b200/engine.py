@@ -22,10 +22,14 @@ HEAD_DIM = K.HEAD_DIM
 
 
 def fit_basis(geom, k_pre_page: torch.Tensor) -> torch.Tensor:
-    """Rank-r right singular vectors of one page of pre-RoPE keys (h_kv, page, 128) -> (h_kv*128, rank) float32,
-    as bmx fits them on the first flush and then freezes them (bmx: src/bmx/decomp/lrs.py:35-41,
-    src/bmx/cache/packed_streaming.py:513-516).  One basis over all heads, or one per head."""
+    """Rank-r right singular vectors of the first page of pre-RoPE keys -> (h_kv*128, rank) float32, as bmx fits them
+    on the first flush and then freezes them (bmx: src/bmx/decomp/lrs.py:35-41, src/bmx/cache/packed_streaming.py:513-516).
+    One basis over all heads, or one per head.  k_pre_page: (h_kv, page, 128), or (batch, h_kv, page, 128): bmx keeps one
+    cache per sequence; a batched state shares one basis, fitted on the first pages of all its sequences stacked (the
+    same thing at batch 1)."""
     x = k_pre_page.float()
+    if x.dim() == 4:
+        x = x.permute(1, 0, 2, 3).reshape(x.shape[1], x.shape[0] * x.shape[2], x.shape[3])
     if geom.n_coef_heads == 1:
         M = x.permute(1, 0, 2).reshape(x.shape[1], geom.h_kv * HEAD_DIM)
         return torch.linalg.svd(M, full_matrices=False)[2][: geom.rank].mT.contiguous()
@@ -87,7 +91,7 @@ class K2bLayerState:
 
     def fit_basis(self, k_pre_page: torch.Tensor) -> None:
         """Rank-r right singular vectors of the first page, as bmx fits them on the first flush
-        (bmx: src/bmx/decomp/lrs.py:35-41).  k_pre_page: (h_kv, page, 128) of sequence 0."""
+        (bmx: src/bmx/decomp/lrs.py:35-41).  k_pre_page: (h_kv, page, 128) or (batch, h_kv, page, 128)."""
         basis = fit_basis(self.geom, k_pre_page)
         self.set_basis(basis)
 
@@ -111,7 +115,7 @@ class K2bLayerState:
     def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
         """Quantizes the first n_pages pages of (batch, h_kv, T, 128) sources into the next slots."""
         if self.basis_f32 is None:
-            self.fit_basis(k_src[0, :, : self.page])
+            self.fit_basis(k_src[:, :, : self.page])
         if v_src.dtype != k_src.dtype:
             v_src = v_src.to(k_src.dtype)
         if k_src.stride() != v_src.stride() or k_src.stride(3) != 1:
@@ -136,6 +140,21 @@ class K2bLayerState:
         if n == 1 and new_commit <= self.committed:  # the common decode step: one token into the window
             K.window_append(k_post, v, src_k, self.k_win, self.v_win, self.k_pre_win, self.tail_len_dev, self.tail_len)
             self.tail_len += 1
+            return
+        if n == 1 and self.tail_len < self.tail_cap:
+            # a streaming step that commits pages: the token goes into the window like any other, then whole pages are
+            # quantized straight out of the windows (no concatenation) and the remaining tokens move to the front
+            K.window_append(k_post, v, src_k, self.k_win, self.v_win, self.k_pre_win, self.tail_len_dev, self.tail_len)
+            self.tail_len += 1
+            n_flush = (new_commit - self.committed) // self.page
+            self._commit_pages(self.k_pre_win if self.pre_rope else self.k_win, self.v_win, n_flush)
+            off = n_flush * self.page
+            rest = self.tail_len - off
+            wins = [self.k_win, self.v_win] + ([] if self.k_pre_win is self.k_win else [self.k_pre_win])
+            for wbuf in wins:
+                wbuf[:, :, :rest] = wbuf[:, :, off:off + rest].clone()
+            self.tail_len = rest
+            self.tail_len_dev.fill_(rest)
             return
         # general path: window ++ new tokens, commit whole pages, keep the rest as the new window
         t = self.tail_len
@@ -165,6 +184,16 @@ class K2bLayerState:
                             self.rope_cos, self.rope_sin, self.k_win, self.v_win, self.tail_len_dev, self.v_lut,
                             self.signs, self.sm_scale, self.workspace, out=out, partial_out=partial_out, pos_offset=pos_offset,
                             phases=phases)
+
+    def prefill_attend(self, q: torch.Tensor, q_pos0: int, out: torch.Tensor | None = None) -> torch.Tensor | None:
+        """Causal attention of q (batch, heads, n_q, 128) fp16 at positions q_pos0 .. over everything held (pages + window),
+        page by page, never materialising dense K / V (bmx dequantizes every page first: src/bmx/cache/chunked_attention.py
+        :320-395).  Returns None when this state has no such kernel (64-token pages): the caller takes the dense route."""
+        if type(self) is not K2bLayerState or self.geom.layout != 1 or self.geom.n_q_groups not in (1, 2, 4, 8):
+            return None
+        return K.k2b_prefill(self.pool, q, q_pos0, self.basis_f16, self.page_table, self.n_pages_dev, self.rope_cos, self.rope_sin,
+                             self.k_win, self.v_win, self.tail_len_dev, self.v_lut, self.signs, self.sm_scale,
+                             self.workspace.view(torch.int32), out=out)
 
     def seq_len(self) -> int:
         return self.committed + self.tail_len

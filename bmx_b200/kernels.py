@@ -228,6 +228,30 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
     return out if partial_out is None else partial_out
 
 
+def k2b_prefill(pool: K2bPool, q: torch.Tensor, q_pos0: int, basis_f16: torch.Tensor, page_table: torch.Tensor, n_pages: torch.Tensor,
+                rope_cos: torch.Tensor, rope_sin: torch.Tensor, k_tail: torch.Tensor | None, v_tail: torch.Tensor | None,
+                tail_len: torch.Tensor | None, v_lut_dev: torch.Tensor, signs: torch.Tensor, sm_scale: float, status: torch.Tensor,
+                out: torch.Tensor | None = None, pos_offset: int = 0) -> torch.Tensor:
+    """Causal attention of q (batch, heads, n_q, 128) fp16, rows at positions q_pos0 .. q_pos0 + n_q - 1, over the paged k2b
+    cache and the fp16 window, page by page in shared memory (no dense K / V).  status: zeroed device int32 (>= 4)."""
+    g = pool.geom
+    _require_cuda(q, page_table, n_pages, status)
+    batch, heads, n_q = q.shape[0], q.shape[1], q.shape[2]
+    assert q.dtype == torch.float16 and q.is_contiguous() and heads == g.h_kv * g.n_q_groups and q.shape[3] == HEAD_DIM
+    assert page_table.dtype == torch.int32 and n_pages.dtype == torch.int32 and status.dtype == torch.int32 and status.numel() >= 4
+    tail_cap = 0 if k_tail is None else k_tail.shape[2]
+    if k_tail is not None:
+        assert k_tail.dtype == torch.float16 and k_tail.is_contiguous() and v_tail.is_contiguous()
+        assert k_tail.shape == (batch, g.h_kv, tail_cap, HEAD_DIM) == v_tail.shape
+    if out is None:
+        out = torch.empty_like(q)
+    assert out.dtype == torch.float16 and out.is_contiguous() and out.shape == q.shape
+    call("bmxk_k2b_prefill", ctypes.byref(g), _ptr(q), n_q, int(q_pos0), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
+         _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, _ptr(rope_cos), _ptr(rope_sin), int(pos_offset), _ptr(k_tail),
+         _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut_dev), _ptr(signs), ctypes.c_float(sm_scale), _ptr(status), _ptr(out), _stream())
+    return out
+
+
 STATIC_SCRATCH_BYTES = 2 * 1024 * 1024
 
 

@@ -272,6 +272,19 @@ class PackedStreamingLayer(DynamicLayer):
         parts_v.append(st.v_win[:, :, : st.tail_len].to(dtype))
         return torch.cat(parts_k, 2), torch.cat(parts_v, 2)
 
+    @staticmethod
+    def _mask_is_causal(attention_mask, n_q: int, S: int) -> bool:
+        """True when the mask hides exactly the keys at positions after each query row (rows are the last n_q positions
+        of S).  Boolean masks mark visible keys with True, additive ones hidden keys with a large negative number."""
+        if attention_mask is None:
+            return True
+        m = attention_mask
+        if m.dim() != 4 or m.shape[-2] != n_q or m.shape[-1] != S or m.shape[1] != 1:
+            return False
+        vis = m if m.dtype == torch.bool else (m > -1.0)
+        want = torch.ones(n_q, S, dtype=torch.bool, device=m.device).tril(S - n_q)
+        return bool((vis == want).all())
+
     def attend(self, q: torch.Tensor, scaling: float, is_causal: bool = False, attention_mask=None) -> torch.Tensor:
         """q (b, H, n_q, d) -> (b, H, n_q, d).  Decode (n_q == 1) runs the split-KV dequant-attention kernel;
         prefill dequantizes the pages once and calls SDPA with the model's mask, as the reference does
@@ -285,6 +298,14 @@ class PackedStreamingLayer(DynamicLayer):
             st.sm_scale = float(scaling)
             out = st.decode(q[:, :, 0, :].to(torch.float16).contiguous())
             return out.unsqueeze(2).to(q.dtype)
+        # prefill: rows at the last n_q positions, causal.  With the model's plain causal mask (or none) the paged kernel
+        # attends page by page; any other mask (padding) goes through the dequantize-everything route, as in bmx.
+        S = st.seq_len()
+        if self._kind == "k2b" and st.committed > 0 and n_q <= S and self._mask_is_causal(attention_mask, n_q, S):
+            st.sm_scale = float(scaling)
+            out = st.prefill_attend(q.to(torch.float16).contiguous(), S - n_q)
+            if out is not None:
+                return out.to(q.dtype)
         Kd, Vd = self._dense_kv(q.dtype)
         Kx = Kd.repeat_interleave(self._n_q_groups, dim=1)
         Vx = Vd.repeat_interleave(self._n_q_groups, dim=1)

@@ -76,7 +76,7 @@ class StreamingQuantizedLayer(DynamicLayer):
             self._signs = K.hadamard_signs(HEAD_DIM, self.v_spec.seed).to(dev)
             self._codebook = torch.tensor(K.GAUSSIAN_CODEBOOK[self.v_spec.bits], device=dev)
         if self._frozen_svd is None:
-            self._frozen_svd = (None, fit_basis(self._geom, k_src[0, :, : self._page]))
+            self._frozen_svd = (None, fit_basis(self._geom, k_src[:, :, : self._page]))
         basis = self._frozen_svd[1]
         pool = K.K2bPool(self._geom, b * n_pg, dev)
         slots = torch.arange(b * n_pg, dtype=torch.int32, device=dev)

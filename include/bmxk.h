@@ -125,6 +125,20 @@ int bmxk_k2b_decode(const bmxk_k2b_geom* g, const void* q, const void* pages, co
                     size_t workspace_bytes, void* out, int out_dtype, float* partial_out, int phases,
                     void* stream);
 
+/* Causal attention of n_q new query positions per sequence over the committed pages and the fp16 window, without
+ * building dense K / V for the context: each 128-token page is dequantized into shared memory and attended there.
+ * bmx: src/bmx/cache/chunked_attention.py:320-395 _prefill_dense_attention (dequantize every page, then SDPA with the
+ * causal mask), reached from chunked_dequant_attention(is_prefill=True) at :454-476.
+ * q, out: fp16 (batch, heads, n_q, 128).  Query row i of every sequence sits at position q_pos0 + i; committed token t of
+ * page j at pos_offset + 128 j + t, window slot r at pos_offset + 128 n_pages[s] + r; a key is visible to a query iff
+ * its position is not larger.  Row-order pools (layout 1, 128-token pages) only.  status: device int32[4], zero on
+ * entry (a bounded wait that ran out is reported there, see bmxk_check_workspace_status). */
+int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
+                     const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
+                     const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                     const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
+                     int32_t* status, void* out, void* stream);
+
 /* Decode step for hosts that must not allocate device memory.  (This entry point has no counterpart in
  * bmx; it exists for embedding.)
  *

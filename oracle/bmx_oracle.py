@@ -437,8 +437,10 @@ def chunked_dequant_attention(q, k_blocks, v_blocks, *, k_arm, v_arm, group, k_p
 
 def naive_dense_attention(q, k_blocks, v_blocks, *, k_arm, v_arm, group, k_pre_rope, rope_cos,
                           rope_sin, k_tail, v_tail, n_q_groups, scale, v_group=None,
-                          v_signs=None, k_signs=None, dtype=F32):
-    """src/bmx/cache/chunked_attention.py:254-317: dequantize everything, one softmax."""
+                          v_signs=None, k_signs=None, dtype=F32, visible=None):
+    """src/bmx/cache/chunked_attention.py:254-317: dequantize everything, one softmax.  `visible`: optional boolean
+    (n_q, S) mask, True where the key may be attended (the prefill route applies the model's causal mask the same way,
+    src/bmx/cache/chunked_attention.py:320-395)."""
     q = np.asarray(q, dtype=dtype)
     h_kv = q.shape[0] // n_q_groups
     vg = v_group if v_group is not None else group
@@ -455,6 +457,8 @@ def naive_dense_attention(q, k_blocks, v_blocks, *, k_arm, v_arm, group, k_pre_r
     K = np.repeat(np.concatenate(Ks, axis=1), n_q_groups, axis=0)
     V = np.repeat(np.concatenate(Vs, axis=1), n_q_groups, axis=0)
     s = (q @ K.transpose(0, 2, 1)) * dtype(scale)
+    if visible is not None:
+        s = np.where(np.asarray(visible, bool)[None], s, dtype(-np.inf))
     s = s - s.max(axis=-1, keepdims=True)
     p = np.exp(s)
     return (p / p.sum(axis=-1, keepdims=True)) @ V

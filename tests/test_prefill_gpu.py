@@ -1,0 +1,136 @@
+"""Paged dequant-prefill: causal attention of a block of query positions over committed k2b pages + the fp16 window, page
+by page in shared memory, against the oracle's dequantize-everything attention with the same causal mask
+(bmx: src/bmx/cache/chunked_attention.py:320-395 is the route it replaces; :254-317 the oracle)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bmx_oracle as O
+from tests.test_k2b_gpu import blocks_from_export, make_k2b_inputs, rope_tables, to_np
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def _case(*, n_seq, h_kv, G, rank, per_head, group, n_pages, tail, n_q, seed):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope
+
+    dev = torch.device("cuda:0")
+    page, W = 128, 64
+    T = n_pages * page + tail
+    k_pre, v, basis = make_k2b_inputs(seed, n_seq, h_kv, T, rank, per_head)
+    cos16, sin16 = rope_tables(T + 256)
+    cos, sin = torch.from_numpy(cos16).to(dev), torch.from_numpy(sin16).to(dev)
+    geom = K.k2b_geom(h_kv, G, page, rank, group, h_kv if per_head else 1)
+    st = K2bLayerState(geom, n_seq, T + 256, W, dev, cos, sin)
+    st.set_basis(basis.to(dev))
+    k_post = apply_rope(k_pre.to(dev).float(), cos[:T].float(), sin[:T].float()).half()
+    # the state is filled by hand so that the window length is whatever the case asks for
+    if n_pages:
+        K.k2b_append(st.pool, k_pre.to(dev), v.to(dev), st.basis_f32, st.signs, st.codebook, st.page_table[:, :n_pages].contiguous().view(-1), n_pages)
+    st.committed = n_pages * page
+    st.n_pages_dev.fill_(n_pages)
+    if tail:
+        st.k_win[:, :, :tail], st.v_win[:, :, :tail] = k_post[:, :, n_pages * page:], v[:, :, n_pages * page:].to(dev)
+    st.tail_len = tail
+    st.tail_len_dev.fill_(tail)
+    gen = torch.Generator().manual_seed(seed + 7)
+    q = (torch.randn(n_seq, h_kv * G, n_q, D, generator=gen) / math.sqrt(D)).half()
+    q_pos0 = T - n_q
+    st.sm_scale = 1.0 / math.sqrt(D)
+    out = st.prefill_attend(q.to(dev), q_pos0)
+    assert out is not None
+    torch.cuda.synchronize()
+    K.check_status(st.workspace)
+    out = out.float().cpu().numpy()
+    # ---- oracle: dense K / V from the pages as stored, one masked softmax ----
+    visible = np.arange(T)[None, :] <= (q_pos0 + np.arange(n_q))[:, None]
+    basis16 = basis.half().float().numpy()
+    cosf, sinf = cos16.astype(np.float32), sin16.astype(np.float32)
+    ref = np.zeros_like(out)
+    for s in range(n_seq):
+        kb, vb = [], []
+        if n_pages:
+            ex = to_np(K.k2b_export_stacks(st.pool, st.page_table[s, :n_pages].contiguous()))
+            for p in range(n_pages):
+                kp, vp = blocks_from_export(ex, p, geom, basis16)
+                kb.append((kp, p * page, (p + 1) * page))
+                vb.append((vp, p * page, (p + 1) * page))
+        ref[s] = O.naive_dense_attention(
+            q[s].float().numpy(), kb, vb, k_arm="lowrank_rtn_channel", v_arm="turboquant_mse_perhead", group=group, k_pre_rope=True,
+            rope_cos=cosf, rope_sin=sinf, k_tail=st.k_win[s, :, :tail].float().cpu().numpy() if tail else None,
+            v_tail=st.v_win[s, :, :tail].float().cpu().numpy() if tail else None, n_q_groups=G, scale=1.0 / math.sqrt(D),
+            v_signs=st.signs.cpu().numpy(), visible=visible)
+    err = np.abs(out - ref).max(axis=-1) / np.abs(ref).max(axis=-1)
+    return float(err.max()), out, ref
+
+
+@pytest.mark.parametrize("h_kv,G,rank,per_head,group,n_pages,tail,n_q", [
+    (2, 4, 32, True, 64, 5, 70, 710),      # whole prompt: every row, pages and window under the causal mask
+    (2, 4, 16, False, 64, 3, 33, 100),     # the last 100 positions of a longer context, cross-head basis
+    (1, 8, 32, True, 128, 2, 0, 256),      # no window; eight query heads per KV head
+    (2, 2, 16, True, 32, 4, 128, 37),      # a ragged block of rows
+    (2, 1, 32, True, 64, 1, 5, 133),       # one query head per KV head: 128 positions per CTA
+])
+def test_paged_prefill_matches_dense_oracle(h_kv, G, rank, per_head, group, n_pages, tail, n_q):
+    err, _, _ = _case(n_seq=2, h_kv=h_kv, G=G, rank=rank, per_head=per_head, group=group, n_pages=n_pages, tail=tail, n_q=n_q, seed=51)
+    print(f"paged prefill: worst relative error {err:.3e}")
+    assert err <= 1e-3
+
+
+def test_paged_prefill_long_context_rows_near_the_end():
+    """A 16384-token context and 64 query rows at its end: every page is fully visible, the window partly."""
+    err, _, _ = _case(n_seq=1, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=128, tail=90, n_q=64, seed=53)
+    print(f"paged prefill, 16384-token context: worst relative error {err:.3e}")
+    assert err <= 1e-3
+
+
+def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
+    """Under a Hugging Face model the prompt's attention goes through the paged kernel when the mask is the plain causal
+    one; forcing the dense route (dequantize every page, SDPA) gives the same logits to fp16 accuracy."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.packed_streaming import PackedStreamingCache
+    from bmx_b200.recipes import spec_pair
+    from tests.test_hf_cache_gpu import _reference_model
+
+    dev = torch.device("cuda:0")
+    model = _reference_model(dev)
+    ids = torch.randint(0, 256, (2, 700), generator=torch.Generator().manual_seed(9)).to(dev)
+    k_spec, v_spec = spec_pair("k2b_ph", rank=16, group=64)
+    calls = []
+    orig = K2bLayerState.prefill_attend
+
+    def run(paged):
+        def spy(self, q, q_pos0, out=None):
+            if not paged:
+                return None
+            calls.append((q.shape[2], q_pos0))
+            return orig(self, q, q_pos0, out)
+
+        K2bLayerState.prefill_attend = spy
+        try:
+            cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+            with cache.attach(model), torch.no_grad():
+                a = model(ids[:, :450], past_key_values=cache, use_cache=True).logits      # pages are committed before attention
+                b = model(ids[:, 450:], past_key_values=cache, use_cache=True).logits      # a second block on top of a cache
+            return torch.cat([a, b], 1).float()
+        finally:
+            K2bLayerState.prefill_attend = orig
+
+    lp, ld = run(True), run(False)
+    assert calls == [(450, 0), (450, 0), (250, 450), (250, 450)], calls  # two layers, two blocks
+    diff = float((lp - ld).abs().max())
+    print(f"paged vs dense prefill logits: max diff {diff:.3e}")
+    # the second block's keys and values come out of layers whose inputs already differ in the last fp16 bit, and 2-bit
+    # codes are discontinuous: a few codes move, so the bound here is looser than the kernel's own (1e-3, above)
+    assert diff < 5e-2 and int((lp[:, :450].argmax(-1) != ld[:, :450].argmax(-1)).sum()) <= 2
+    assert float((lp[:, :450] - ld[:, :450]).abs().max()) < 1e-2
