@@ -15,7 +15,7 @@ def _tiny_llama(dev):
                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=4096,
                       rope_theta=500000.0)
     torch.manual_seed(0)
-    return LlamaForCausalLM(cfg).to(dev).half().eval()
+    return LlamaForCausalLM(cfg).to(dev).eval()  # float32: the fp16 logits of a random-init model tie exactly at some steps
 
 
 def _run(model, ids, n_prefill, force_dense):
@@ -26,10 +26,14 @@ def _run(model, ids, n_prefill, force_dense):
     cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
     logits = []
     orig = PackedStreamingLayer.attend
-    if force_dense:  # decode through dequantize-all + SDPA instead of the decode kernel
+    from bmx_b200.engine import K2bLayerState
+
+    orig_paged = K2bLayerState.prefill_attend
+    if force_dense:  # every attention call through dequantize-all + SDPA: neither the decode nor the paged prefill kernel
         def dense_attend(self, q, scaling, is_causal=False, attention_mask=None):
             return orig(self, q, scaling, is_causal=True, attention_mask=attention_mask)
         PackedStreamingLayer.attend = dense_attend
+        K2bLayerState.prefill_attend = lambda self, q, q_pos0, out=None: None
     try:
         with cache.attach(model), torch.no_grad():
             out = model(ids[:, :n_prefill], past_key_values=cache, use_cache=True)
@@ -39,6 +43,7 @@ def _run(model, ids, n_prefill, force_dense):
                 logits.append(out.logits[:, -1].float())
     finally:
         PackedStreamingLayer.attend = orig
+        K2bLayerState.prefill_attend = orig_paged
     return torch.stack(logits, 1), cache
 
 

