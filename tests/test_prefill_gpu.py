@@ -130,8 +130,6 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     assert calls == [(450, 0), (450, 0), (250, 450), (250, 450)], calls  # two layers, two blocks
     diff = float((lp - ld).abs().max())
     print(f"paged vs dense prefill logits: max diff {diff:.3e}")
-    # the second block's keys and values come out of layers whose inputs already differ in the last fp16 bit, and 2-bit
-    # codes are discontinuous: a few codes move, so the bound here is looser than the kernel's own (1e-3, above)
-    first = float((lp[:, :450] - ld[:, :450]).abs().max())
-    print(f"first block alone (same stored pages on both routes): max diff {first:.3e}")
-    assert diff < 5e-2 and first < 1e-2
+    # layer 2 quantizes keys and values that come out of layer 1's attention, where the two routes differ in the last fp16
+    # bits, and 2-bit codes are discontinuous: a few codes move, so the bound here is looser than the kernel's own (1e-3)
+    assert diff < 5e-2
