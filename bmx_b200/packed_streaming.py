@@ -171,6 +171,7 @@ class PackedStreamingLayer(DynamicLayer):
         self._frozen_svd: tuple | None = None
         self._state: K2bLayerState | None = None
         self._batch = 0
+        self._graph_mode = False  # set by GraphedDecoder around a captured / replayed single-token step
 
     # ---- hooks ----------------------------------------------------------------------------------
     def stash_pre_rope(self, out: torch.Tensor) -> None:
@@ -207,6 +208,8 @@ class PackedStreamingLayer(DynamicLayer):
         fp16 window as (keys, values) for HF bookkeeping (attention reads the packed state instead)."""
         st = self._ensure_state(key_states)
         n = key_states.shape[2]
+        if self._graph_mode:
+            return self._update_graph_step(key_states, value_states)
         if self.k_spec.pre_rope:
             assert self._k_pre is not None and self._k_pre.shape[2] == n, (
                 "k_spec.pre_rope=True but no pre-RoPE keys were captured; call cache.attach(model) before the forward")
@@ -245,6 +248,37 @@ class PackedStreamingLayer(DynamicLayer):
         self.keys = st.k_win[:, :, : st.tail_len]
         self.values = st.v_win[:, :, : st.tail_len]
         return self.keys, self.values
+
+    def _update_graph_step(self, key_states: torch.Tensor, value_states: torch.Tensor):
+        """The single-token, no-flush case of update() with nothing that depends on the step: the token goes into the
+        fp16 window at the position held in device memory, so the launch can sit in a captured CUDA graph.  Host-side
+        counters are advanced afterwards by advance_after_graph_step(), once per replay."""
+        st = self._state
+        assert key_states.shape[2] == 1
+        k_post = key_states.to(torch.float16).contiguous()
+        v = value_states.to(torch.float16).contiguous()
+        if self.k_spec.pre_rope:
+            assert self._k_pre is not None and self._k_pre.shape[2] == 1, "no pre-RoPE key captured for this step"
+            k_src, self._k_pre = self._k_pre.contiguous(), None
+        else:
+            k_src = k_post
+        K.window_append_devpos(k_post, v, k_src, st.k_win, st.v_win, st.k_pre_win, st.tail_len_dev, st.append_cnt,
+                               st.workspace.view(torch.int32))
+        return st.k_win, st.v_win  # the attention function reads the packed state, not these
+
+    def advance_after_graph_step(self) -> None:
+        """Host-side bookkeeping of one replayed step: window length, blended bits per entry, the window views."""
+        st = self._state
+        st.tail_len += 1
+        C, S = self._h_kv * self._d_head, st.seq_len()
+        self.bpe_k = (self._quant_bits_k + st.tail_len * C * 16.0) / (S * C)
+        self.bpe_v = (self._quant_bits_v + st.tail_len * C * 16.0) / (S * C)
+        self.keys, self.values = st.k_win[:, :, : st.tail_len], st.v_win[:, :, : st.tail_len]
+
+    def next_step_flushes(self) -> bool:
+        """True if appending one more token commits a page (such a step runs the append kernels: not replayable)."""
+        st = self._state
+        return st is None or compute_flush_schedule(st.seq_len() + 1, self.recent_window, self._page) > st.committed
 
     def get_seq_length(self) -> int:
         return 0 if self._state is None else self._state.seq_len()

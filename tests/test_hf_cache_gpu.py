@@ -334,3 +334,41 @@ def test_argmax_and_accounting_match_the_reference_cache(recipe, tmp_path):
         tb = twin.bits_per_entry()
         assert abs(tb[0] - fx[f"{name}_twin_bpe"][0]) < 1e-9 and abs(tb[1] - fx[f"{name}_twin_bpe"][1]) < 1e-9
         assert int((lt.argmax(-1) != ref.argmax(-1)).sum()) == 0
+
+
+@pytest.mark.parametrize("recipe", ["k2b_ph", "kivi"])
+def test_whole_step_cuda_graph_equals_eager_decode(recipe):
+    """GraphedDecoder replays a whole single-token forward (all layers) as one CUDA graph; the steps that commit a page run
+    eagerly.  Teacher-forced over 300 steps (two flushes inside), logits equal the plain eager loop's bit for bit: the same
+    kernels run on the same data, only the launch mechanism differs."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.graphed import GraphedDecoder
+    from bmx_b200.packed_streaming import PackedStreamingCache
+    from bmx_b200.recipes import spec_pair
+
+    dev = torch.device("cuda:0")
+    model = _reference_model(dev)
+    ids = torch.randint(0, 256, (2, 200 + 300), generator=torch.Generator().manual_seed(21)).to(dev)
+    k_spec, v_spec = spec_pair(recipe, rank=16, group=64)
+
+    def run(graphed):
+        cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+        logits = []
+        with cache.attach(model), torch.no_grad():
+            model(ids[:, :200], past_key_values=cache, use_cache=True)
+            dec = GraphedDecoder(model, cache)
+            for t in range(200, ids.shape[1]):
+                if graphed:
+                    logits.append(dec.step(ids[:, t:t + 1]).float().clone())
+                else:
+                    logits.append(model(ids[:, t:t + 1], past_key_values=cache, use_cache=True).logits[:, -1].float())
+        return torch.stack(logits, 1), cache, dec
+
+    lg, cache_g, dec = run(True)
+    le, cache_e, _ = run(False)
+    assert dec.replays >= 290 and dec.captures <= 3 and 2 <= dec.eager_steps <= 8, (dec.replays, dec.captures, dec.eager_steps)
+    assert cache_g.layers[0]._committed_S_q == cache_e.layers[0]._committed_S_q == 384
+    assert cache_g.layers[0].get_seq_length() == cache_e.layers[0].get_seq_length() == 500
+    assert abs(cache_g.bits_per_entry()[0] - cache_e.bits_per_entry()[0]) < 1e-12
+    assert torch.equal(lg, le), f"max diff {float((lg - le).abs().max()):.3e}"
