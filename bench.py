@@ -401,6 +401,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         extra["rtn_b1_t4096"] = config_rtn(device)
         extra["append_b16"] = config_append(device)
+        extra["prefill_b1_t16384"] = config_prefill(device)
     extra_all = {"spectral_b64_t16384": config_spectral(device, rank, world, dist if world > 1 else None),
                  "seq_split_t131072": config_seq_split(device, rank, world, dist if world > 1 else None)}
 
@@ -758,6 +759,62 @@ def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind}), bf16_tflops_sustained", "traffic": None}}
 
 
+def config_prefill(device) -> dict:
+    """Prefill attention of the k2b cache: one sequence of 16384 committed tokens + a 128-token window (32 q / 8 kv heads);
+    (a) the last 2048 positions as one query block (a chunk of a chunked prefill), (b) the whole prompt at once.  Timed:
+    the paged kernel (pages dequantized in shared memory, no dense K / V) against the route it replaces, dequantize every
+    page + rotate + scaled_dot_product_attention with the same causal mask.  FLOPs counted over the visible part only."""
+    import torch
+    import torch.nn.functional as F
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.rope import apply_rope
+
+    T = 16384
+    state, _, gen, _, _ = build_state(device, 4000, batch=1, ctx=T)
+    S, H = T + WINDOW, H_KV * G
+    out = {"workload": f"k2b causal prefill attention, B=1, {T} committed tokens + {WINDOW}-token window, 32 q / 8 kv heads"}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops_sustained") or 0) or None
+    except (OSError, ValueError):
+        tf_peak = None
+    for name, n_q in (("last_2048_rows", 2048), ("whole_prompt", S)):
+        q = (torch.randn(1, H, n_q, D, generator=gen, device=device) / math.sqrt(D)).half()
+        o = torch.empty_like(q)
+        paged_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
+        K.check_status(state.workspace)
+
+        def dense():
+            slots = state.page_table[:, :T // PAGE].contiguous().view(-1)
+            kd, vd = K.k2b_dequant_pages(state.pool, slots, state.basis_f16, state.signs, state.codebook)
+            kd = kd.view(1, T, H_KV, D).permute(0, 2, 1, 3)
+            vd = vd.view(1, T, H_KV, D).permute(0, 2, 1, 3)
+            kd = apply_rope(kd.half(), state.rope_cos[:T], state.rope_sin[:T])
+            kx = torch.cat([kd, state.k_win[:, :, :WINDOW]], 2)
+            vx = torch.cat([vd.half(), state.v_win[:, :, :WINDOW]], 2)
+            if n_q == S:
+                return F.scaled_dot_product_attention(q, kx, vx, is_causal=True, scale=state.sm_scale, enable_gqa=True)
+            mask = torch.ones(n_q, S, dtype=torch.bool, device=device).tril(S - n_q)
+            return F.scaled_dot_product_attention(q, kx, vx, attn_mask=mask, scale=state.sm_scale, enable_gqa=True)
+
+        torch.cuda.reset_peak_memory_stats(device)
+        base = torch.cuda.memory_allocated(device)
+        ref = dense()
+        dense_peak = torch.cuda.max_memory_allocated(device) - base
+        dense_us = _event_us(dense, 3, warm=0)
+        err = float((o.float() - ref.float()).abs().max() / ref.float().abs().max())
+        visible = n_q * (S - n_q) + n_q * (n_q + 1) // 2
+        flops = 4.0 * H * D * visible
+        out[name] = {"rows": n_q, "paged_kernel_us": paged_us, "dequantize_then_sdpa_us": dense_us, "speedup": dense_us / paged_us,
+                     "paged_tflops": flops / paged_us / 1e6, "peak_tflops": tf_peak,
+                     "frac_of_tensor_peak": None if not tf_peak else flops / paged_us / 1e6 / tf_peak,
+                     "dense_route_transient_bytes": int(dense_peak), "paged_route_transient_bytes": 0,
+                     "max_rel_diff_between_routes": err, "gpu_launches": 1}
+        del q, o, ref
+    return out
+
+
 def run_hf(args) -> None:
     """`--workload hf`: per-token decode latency of a random-init Llama-shaped model (Llama-3.1-8B layer dimensions, four
     layers, small vocabulary) with PackedStreamingCache (k2b) against DynamicCache: prefill 8192 tokens at B = 4, then time
@@ -781,9 +838,15 @@ def run_hf(args) -> None:
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab_size, (batch, context + steps + 3), generator=g).to(dev)
 
-    def run(make_cache, attach):
+    def run(make_cache, attach, graphed=False):
         cache = make_cache()
         ctx = cache.attach(model) if attach else None
+        step = (lambda x: model(x, past_key_values=cache, use_cache=True))
+        if graphed:
+            from bmx_b200.graphed import GraphedDecoder
+
+            decoder = GraphedDecoder(model, cache)
+            step = decoder.step
         try:
             with torch.no_grad():
                 pos = 0
@@ -792,16 +855,18 @@ def run_hf(args) -> None:
                     model(ids[:, pos:pos + n], past_key_values=cache, use_cache=True)
                     pos += n
                 for t in range(3):
-                    model(ids[:, pos + t:pos + t + 1], past_key_values=cache, use_cache=True)
+                    step(ids[:, pos + t:pos + t + 1])
                 pos += 3
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 t0 = time.perf_counter()
                 e0.record()
                 for t in range(steps):
-                    model(ids[:, pos + t:pos + t + 1], past_key_values=cache, use_cache=True)
+                    step(ids[:, pos + t:pos + t + 1])
                 e1.record()
                 torch.cuda.synchronize()
+                if graphed:
+                    assert decoder.replays >= steps, (decoder.replays, decoder.eager_steps)
                 return e0.elapsed_time(e1) / steps, (time.perf_counter() - t0) * 1e3 / steps
         finally:
             if ctx is not None:
@@ -815,11 +880,14 @@ def run_hf(args) -> None:
         dense[impl] = {"ms_per_token": ms, "wall_ms_per_token": wall}
     model.config._attn_implementation = "sdpa"
     packed_ms, packed_wall = run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window), attach=True)
+    graph_ms, graph_wall = run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window), attach=True, graphed=True)
     dense_ms = min(v["ms_per_token"] for v in dense.values())
     print(json.dumps({"metric": "hf_decode_ms_per_token", "model": f"Llama-3.1-8B layer shape x {layers} layers, random init, fp16",
                       "batch": batch, "context": context, "steps": steps, "dynamic_cache": dense,
                       "packed_streaming_cache_k2b": {"ms_per_token": packed_ms, "wall_ms_per_token": packed_wall},
-                      "per_layer_us": {"dynamic": dense_ms * 1e3 / layers, "packed": packed_ms * 1e3 / layers}}), flush=True)
+                      "packed_streaming_cache_k2b_whole_step_graph": {"ms_per_token": graph_ms, "wall_ms_per_token": graph_wall},
+                      "per_layer_us": {"dynamic": dense_ms * 1e3 / layers, "packed": packed_ms * 1e3 / layers,
+                                       "packed_graph": graph_ms * 1e3 / layers}}), flush=True)
 
 
 def main():
@@ -830,7 +898,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX, help="committed tokens per sequence (smaller cases for profiling)")
     ap.add_argument("--batch", type=int, default=16, help="sequences of --workload append (smaller cases for profiling)")
-    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "append", "rtn", "hf"],
+    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "append", "rtn", "prefill", "hf"],
                     help="k2b: the headline line (carries the other configurations under `configs`); spectral: the K4 spectral "
                          "cache alone, append / rtn: those configurations alone (one GPU, for profiling); hf: per-token latency "
                          "under a random-init Hugging Face model")
@@ -850,14 +918,16 @@ def main():
                 raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
             print(json.dumps(config_spectral(torch.device("cuda", 0), 0, 1, None, steps=min(args.steps, 50))), flush=True)
         return
-    if args.workload in ("append", "rtn"):
+    if args.workload in ("append", "rtn", "prefill"):
         if rank == 0:
             import torch
 
             if not torch.cuda.is_available():
                 raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
             dev0 = torch.device("cuda", 0)
-            print(json.dumps(config_append(dev0, B=args.batch) if args.workload == "append" else config_rtn(dev0)), flush=True)
+            fn = {"append": lambda: config_append(dev0, B=args.batch), "rtn": lambda: config_rtn(dev0),
+                  "prefill": lambda: config_prefill(dev0)}[args.workload]
+            print(json.dumps(fn()), flush=True)
         return
     if args.workload == "hf":
         if rank == 0:

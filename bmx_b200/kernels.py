@@ -288,6 +288,13 @@ def selftest_bounded_wait(status: torch.Tensor, limit_cycles: int) -> None:
     call("bmxk_selftest_bounded_wait", _ptr(status), int(limit_cycles), _stream())
 
 
+def _same_token_layout(x: torch.Tensor, ref: torch.Tensor) -> bool:
+    """(batch, h_kv, 1, 128) sources: same dtype, unit channel stride, and equal strides wherever a stride matters
+    (a dimension of size one may carry any stride)."""
+    return (x.shape == ref.shape and x.dtype == ref.dtype and x.stride(3) == 1 and
+            all(x.shape[d] == 1 or x.stride(d) == ref.stride(d) for d in (0, 1)))
+
+
 def window_append(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor,
                   k_src_win: torch.Tensor, tail_len: torch.Tensor, t: int) -> None:
     """One new token per sequence, (batch, h_kv, 1, 128) each, into position t of the fp16 windows; one launch."""
@@ -296,7 +303,7 @@ def window_append(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor, k_
     srcs = [k_post, v, k_src]
     if any(x.shape[2] != 1 or x.shape[3] != 128 for x in srcs):
         raise ValueError("window_append: sources must be (batch, h_kv, 1, 128)")
-    if any(x.dtype != k_post.dtype or x.stride() != k_post.stride() or x.stride(3) != 1 for x in srcs):
+    if not all(_same_token_layout(x, k_post) for x in srcs):
         srcs = [x.to(k_post.dtype).contiguous() for x in srcs]  # a few KB: one common layout for the kernel
     k_post, v, k_src = srcs
     call("bmxk_window_append", _ptr(k_post), _ptr(v), _ptr(k_src), _dtype_code(k_post), k_post.stride(0), k_post.stride(1),
@@ -313,7 +320,7 @@ def window_append_devpos(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Ten
     assert counters.dtype == torch.int32 and counters.numel() >= k_post.shape[0]
     batch, h_kv = k_post.shape[0], k_post.shape[1]
     for x in (k_post, v, k_src):
-        if x.shape != k_post.shape or x.dtype != k_post.dtype or x.stride() != k_post.stride() or x.stride(3) != 1:
+        if not _same_token_layout(x, k_post):
             raise ValueError("window_append_devpos: sources must share shape (batch, h_kv, 1, 128), dtype and strides")
     call("bmxk_window_append_devpos", _ptr(k_post), _ptr(v), _ptr(k_src), _dtype_code(k_post), k_post.stride(0), k_post.stride(1),
          _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), _ptr(counters), _ptr(status), batch, h_kv, k_win.shape[2],
