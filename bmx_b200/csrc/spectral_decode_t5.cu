@@ -6,7 +6,7 @@
 // The kernel is the k2b tcgen05 kernel (k2b_decode_t5.cu) with the low-rank product replaced by the full
 // decoder product and the residual replaced by a dequantization stage in front of it:
 //
-//   dequant warps (8; thread = one direction x the token pairs 2q, 2q+1 of every 8-token block):
+//   dequant warps (16; thread = one direction x the token pairs 2q, 2q+1 of every 8-token block):
 //         tier codes (2-, 4- or 8-bit containers along tokens, as the append kernel wrote them) -> fp16
 //         Y_hat = (code - offset) * scale -> shared memory in the K-major operand form, one stmatrix per
 //         four 8 x 8 blocks.  Directions are visited in the pack's tier order (the decoder operand the host
@@ -26,19 +26,18 @@ namespace bmxk {
 
 namespace {
 
-constexpr int KEY_WARPS = 4, VAL_WARPS = 12 - KEY_WARPS;  // four key warps (all four chunks each), eight value warps
-constexpr int W_SOFT = KEY_WARPS, W_VAL = KEY_WARPS + 8;  // first softmax / value warp; dequant warps start at 20
-constexpr int DQ_WARPS = 8;            // dequant warps
-constexpr int SVC0 = 20 + DQ_WARPS;     // first of the four service warps: copy + U3, U1 + U2, two query rotation warps
-constexpr int S5_THREADS = (SVC0 + 4) * 32;  // key warps, 8 softmax warps (two sets), value warps (12 with the key warps), 20.. dequant, then service
+// Warp roles: 0-3 key (all four chunks each), 4-7 softmax, 8-11 value (both 64-token halves each), 12-27 dequant (one
+// direction octet each), 28-31 service (copy + U3, U1 + U2, two query rotation warps).  The dequantization is what a tile
+// waits for, so it gets half of the CTA's warps; the other per-element roles need a quarter of a tile period each.
+constexpr int KEY_WARPS = 4, SOFT_WARPS = 4, VAL_WARPS = 4, DQ_WARPS = 16;
+constexpr int W_SOFT = KEY_WARPS, W_VAL = W_SOFT + SOFT_WARPS, W_DQ = W_VAL + VAL_WARPS;
+constexpr int SVC0 = W_DQ + DQ_WARPS;
+constexpr int S5_THREADS = (SVC0 + 4) * 32;
 constexpr int S5_MAX_STAGES = 8;
 // Registers per thread after each role resizes itself; the pool is what the launch handed out.
-constexpr int REG_LAUNCH = (DQ_WARPS == 4) ? 72 : 64, REG_KEY = (DQ_WARPS == 4) ? 96 : (KEY_WARPS == 4 ? 120 : 88), REG_SOFTMAX = (DQ_WARPS == 4) ? 56 : 48;
-constexpr int REG_VALUE = 56, REG_DEQUANT = (DQ_WARPS == 4) ? 88 : 64, REG_SERVICE = 56;
-static_assert(DQ_WARPS == 4 || DQ_WARPS == 8, "dequant warps come in groups of four");
-static_assert(REG_LAUNCH * S5_THREADS <= 65536, "launch registers exceed the register file");
-static_assert(KEY_WARPS == 8 || (KEY_WARPS == 4 && DQ_WARPS == 8), "key warps: 4 or 8");
-static_assert(KEY_WARPS * REG_KEY + 8 * REG_SOFTMAX + VAL_WARPS * REG_VALUE + DQ_WARPS * REG_DEQUANT + 4 * REG_SERVICE <= (SVC0 + 4) * REG_LAUNCH,
+constexpr int REG_LAUNCH = 64, REG_KEY = 112, REG_SOFTMAX = 64, REG_VALUE = 56, REG_DEQUANT = 56, REG_SERVICE = 56;
+static_assert(S5_THREADS == 1024 && REG_LAUNCH * S5_THREADS <= 65536, "launch registers exceed the register file");
+static_assert(KEY_WARPS * REG_KEY + SOFT_WARPS * REG_SOFTMAX + VAL_WARPS * REG_VALUE + DQ_WARPS * REG_DEQUANT + 4 * REG_SERVICE <= (SVC0 + 4) * REG_LAUNCH,
               "register split exceeds the CTA's pool");
 constexpr int QB_BYTES = 4096;        // B operand of U2 / U3: 16 rows x 128 fp16, K-major core matrices
 constexpr int OPER_BYTES = 128 * 128 * 2;  // Y_hat / decoder operand: 128 rows x 128 fp16
@@ -111,6 +110,14 @@ __device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, const uint32_t 
   asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]));
 }
 
+// Resizes the calling warpgroup's registers to N: the instruction is .inc above the launch count, .dec below it and
+// left out when N is the launch count (an .inc to a smaller count is an illegal instruction).
+template <int N>
+__device__ __forceinline__ void set_regs() {
+  if constexpr (N > REG_LAUNCH) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+  else if constexpr (N < REG_LAUNCH) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 }  // namespace
 
 template <int GQ>
@@ -169,7 +176,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
   w.init(cum, npg_sm, f_begin, h_kv);
 
   if (warp >= SVC0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
+    set_regs<REG_SERVICE>();  // the four service warps, as one group
     if (warp == SVC0) {
       // ===================== copy + U3 warp =====================
       constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
@@ -188,13 +195,14 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         if (nC < bdone && pc >= 4 * ((nC >> 1) + 1) && vc >= VAL_WARPS * ((nC >> 1) + 1)) {
           tc5::fence_after();
           const int b = nC & 1;
-          const uint32_t keep = sh->first[sC] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
+          const uint32_t keep = sh->first[sC] ? 0u : 1u;  // the first tile of a range starts a new accumulator
           const uint64_t db = d_pb + (uint64_t)(b * (QB_BYTES >> 4));
           ++nC;
           if (el) {
-            tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
+            // one accumulator for the whole range: the U3s of consecutive tiles are issued by this thread in order
+            tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b, db, ID_N16, keep);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
+            for (int ks = 1; ks < 8; ++ks) tc5::mma_ts(tmem + TM_O, tmem + TM_V + 64 * b + 8 * ks, db + 16 * ks, ID_N16, 1u);
             tc5::commit(smem_u32(&sh->odone[b]));
             mbar_arrive(&sh->empty[sC]);
             smem_add_release(&sh->ccnt, 1);
@@ -297,7 +305,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
             }
           }
           if (lane == 0) {
-            sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it - first_cur < 2) ? 1 : 0;
+            sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it == first_cur) ? 1 : 0;
             sh->ksteps[s] = ((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1;
           }
           fence_proxy_async();
@@ -372,7 +380,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
     }
   } else if (warp < KEY_WARPS) {
     // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
+    set_regs<REG_KEY>();
     constexpr int KCH = 16 / KEY_WARPS;  // chunks of 16 + 16 channels per key warp
     const int wq = warp & 3, k0 = KCH * (warp >> 2), row = 32 * wq + lane;
     const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
@@ -411,27 +419,29 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
     }
   } else if (warp < W_VAL) {
-    // ===================== softmax warps: thread = token row; set e takes the tiles of parity e =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
-    const int e = (warp - W_SOFT) >> 2, wq = warp & 3, row = 32 * wq + lane;
+    // ===================== softmax warps: thread = token row =====================
+    // One set of four warps takes every tile: running (max, sum) and ONE output accumulator per range.  Scores, the
+    // weight buffer and the flags alternate by tile parity (U2 / U3 of neighbouring tiles overlap with this role).
+    set_regs<REG_SOFTMAX>();
+    const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
     float m[GQ], l[GQ], pn[GQ];
 #pragma unroll
     for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
     int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
     bool had = false, alive = true;
-    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * h_kv;
 
-    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
+    // Writes the partial record of the range that just ended.
     auto flush = [&](int b_, int h_) {
       float acc[GQ];
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
+      // U3s complete in issue order: the last tile's completion covers the whole range
+      if (had && alive && !wait_or_flag(&sh->odone[last_n & 1], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
       if (had && alive) {
         tc5::fence_after();
         uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
         tc5::wait_ld();
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
@@ -442,32 +452,31 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         float a = l[qi], b2 = pn[qi];
 #pragma unroll
         for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
+        if (lane == 0) sh->red[0][wq][qi] = a, sh->red[0][wq][GQ + qi] = b2;
       }
-      named_bar(1 + e, 128);
-      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * h_kv + h_) * G) * PART_STRIDE;
+      named_bar(1, 128);
+      float* dst = p.part + ((blockIdx.x + (int64_t)b_ * h_kv + h_) * G) * PART_STRIDE;
 #pragma unroll
       for (int qi = 0; qi < GQ; ++qi)
         if (qi < G) {
-          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
-          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
+          const float L = sh->red[0][0][qi] + sh->red[0][1][qi] + sh->red[0][2][qi] + sh->red[0][3][qi];
+          const float P = sh->red[0][0][GQ + qi] + sh->red[0][1][GQ + qi] + sh->red[0][2][GQ + qi] + sh->red[0][3][GQ + qi];
           dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
           if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
         }
-      named_bar(1 + e, 128);
+      named_bar(1, 128);
     };
 
     int s = 0;
     uint32_t fp = 0;
     for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch), s = (s + 1 == STG) ? 0 : s + 1, fp ^= (s == 0) ? 1u : 0u) {
-      const int n = w.it;
+      const int n = w.it, e = n & 1;
       if (w.seg != cur_seg) {
         if (cur_seg >= 0) flush(cur_b, cur_h);
         cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
       }
-      if ((n & 1) != e) continue;
       const uint32_t par = (uint32_t)(n >> 1) & 1u;
       const uint8_t* vblk = stage0 + (size_t)s * STAGE_BYTES + KB;
       float sv[GQ];
@@ -490,10 +499,10 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
       const bool wneed = __any_sync(0xffffffffu, need);
       if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
-      named_bar(1 + e, 128);
+      named_bar(1, 128);
       const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
       const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
-      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
+      // the weight buffer of this parity still belongs to U3 of tile n-2
       if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
       if (resc) {
         float mnew[GQ];
@@ -504,13 +513,15 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
           if (lane == 0) sh->wmax[e][wq][qi] = v;
         }
-        named_bar(1 + e, 128);
+        named_bar(1, 128);
 #pragma unroll
         for (int qi = 0; qi < GQ; ++qi) {
           const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
           mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
         }
-        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
+        // the accumulator is rescaled in place: U3 of tile n-1 must have finished with it (U3 of this tile waits for this
+        // role's arrival below)
+        if (alive && had && !wait_or_flag(&sh->odone[e ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 15)) alive = false;
         if (alive) {
           float f[GQ];
 #pragma unroll
@@ -521,11 +532,11 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
             tc5::fence_after();
             uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
             tc5::wait_ld();
 #pragma unroll
             for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
             tc5::wait_st();
           }
         }
@@ -548,11 +559,11 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       had = true, last_n = n;
     }
     flush(cur_b, cur_h);
-  } else if (warp < 20) {
-    // ===================== value warps: thread = channel; eight warps take one 64-token half each, four take both =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
+  } else if (warp < W_DQ) {
+    // ===================== value warps: thread = channel, both 64-token halves of the tile =====================
+    set_regs<REG_VALUE>();
     const int wq = warp & 3, ch = 32 * wq + lane;
-    const int cc0 = (VAL_WARPS == 8) ? ((warp - W_VAL) >> 2) : 0, cc1 = (VAL_WARPS == 8) ? cc0 + 1 : 2;
+    constexpr int cc0 = 0, cc1 = 2;
     const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
     int s = 0;
     uint32_t fp = 0;
@@ -604,9 +615,9 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
     // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
     // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
     // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_DEQUANT));
+    set_regs<REG_DEQUANT>();
     constexpr int OCT = 16 / DQ_WARPS;
-    const int wd = warp - 20, q = lane & 3, dsub = lane >> 2;
+    const int wd = warp - W_DQ, q = lane & 3, dsub = lane >> 2;
     const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
     const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
     const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
@@ -707,7 +718,7 @@ extern "C" {
 
 size_t bmxk_spectral_decode_workspace_bytes(const bmxk_spectral_geom* g, int n_q_groups, int batch) {
   if (!g || batch <= 0 || n_q_groups <= 0) return 0;
-  const size_t slots = ((size_t)num_sms() + (size_t)batch * g->h_kv) * 2;  // one record per tile parity
+  const size_t slots = (size_t)num_sms() + (size_t)batch * g->h_kv;  // one record per (CTA, range)
   return 256 + slots * n_q_groups * PART_STRIDE * sizeof(float);
 }
 
@@ -772,7 +783,7 @@ int bmxk_spectral_decode(const bmxk_spectral_geom* g, int n_q_groups, const void
   K2bMergeParams mp;
   mp.g.h_kv = g->h_kv, mp.g.n_q_groups = n_q_groups, mp.g.page = 128, mp.g.rank = 0, mp.g.group = g->group;
   mp.g.n_coef_heads = g->h_kv, mp.g.kbits = 0, mp.g.vbits = 2, mp.g.layout = 1;
-  mp.n_sub = 2;
+  mp.n_sub = 1;
   mp.q = (const __half*)q, mp.n_pages = n_pages, mp.batch = batch, mp.main_grid = grid, mp.part = part;
   mp.k_tail = (const __half*)k_tail, mp.v_tail = (const __half*)v_tail, mp.tail_len = tail_cap > 0 ? tail_len : nullptr;
   mp.tail_cap = tail_cap, mp.signs = signs, mp.scale_log2 = scale_log2, mp.out = out, mp.out_dtype = out_dtype;
