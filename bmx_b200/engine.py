@@ -338,6 +338,100 @@ class SpectralLayerState(K2bLayerState):
         return int(self.batch * self.geom.h_kv * (self.committed // self.page) * (self.geom.block_bytes + self.vpool.shape[2]))
 
 
+class FullSpectralLayerState(SpectralLayerState):
+    """K4 spectral keys with ONE encoder over all KV heads: enc, dec (C, C) float32 with C = h_kv * 128, bits (C,) --
+    the shape of the packs bmx fits (bmx: SpectralPack, src/bmx/cache/spectral.py:174-220; quantize / dequantize
+    :765-839).  The decoder product of such a pack mixes heads (C x C per token, h_kv times the work of per-head
+    packs), so there is no fused kernel for it; this state runs bmx's own chunked formulation on the GPU instead:
+
+      append   Y = M @ enc as one fp32 library GEMM over the flattened heads, then the per-direction quantizer and page
+               layout of the per-head path (the append kernel is handed Y with an identity encoder: directions
+               128 g .. 128 g + 127 are stored as pseudo-head g), values as in SpectralLayerState;
+      decode   pages are dequantized a chunk at a time (Y_hat by the page dequantizer kernel, M_hat = Y_hat @ dec^T by a
+               library GEMM), rotated at their positions and attended with a running softmax in float32, then the fp16
+               window; the transient is bounded by the chunk (bmx: chunked_dequant_attention,
+               src/bmx/cache/chunked_attention.py:398-530).
+    """
+
+    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, group: int, n_q_groups: int, batch: int, max_tokens: int,
+                 recent_window: int, device, rope_cos: torch.Tensor, rope_sin: torch.Tensor, *, codebook=None, v_seed: int = 0,
+                 chunk_pages: int = 32):
+        C = enc.shape[0]
+        assert enc.shape == dec.shape == (C, C) and bits.shape == (C,) and C % HEAD_DIM == 0
+        h_kv = C // HEAD_DIM
+        eye = torch.eye(HEAD_DIM).expand(h_kv, HEAD_DIM, HEAD_DIM).contiguous()
+        store = K.SpectralPackDev(eye, eye, bits.reshape(h_kv, HEAD_DIM), page=128, group=group, device=device)
+        super().__init__(store, n_q_groups, batch, max_tokens, recent_window, device, rope_cos, rope_sin, codebook=codebook, v_seed=v_seed)
+        self.enc_full = enc.to(self.device, torch.float32).contiguous()
+        self.dec_full = dec.to(self.device, torch.float32).contiguous()
+        self.chunk_pages = chunk_pages
+
+    def _commit_pages(self, k_src: torch.Tensor, v_src: torch.Tensor, n_pages: int) -> None:
+        B, h_kv, T = self.batch, self.geom.h_kv, n_pages * self.page
+        M = k_src[:, :, :T].permute(0, 2, 1, 3).reshape(B, T, h_kv * HEAD_DIM).float()
+        Y = torch.matmul(M, self.enc_full)                       # (B, T, C) float32: direction d = 128 g + j
+        y_heads = Y.view(B, T, h_kv, HEAD_DIM).permute(0, 2, 1, 3)  # pseudo-heads as a strided view, no copy
+        if v_src.stride(3) != 1:
+            v_src = v_src.contiguous()
+        self.ensure_pages(n_pages)
+        p0 = self.committed // self.page
+        slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
+        K.spectral_append(self.pack, self.kpool, y_heads, slots, n_pages)
+        K.vblock_append(self.vpool, v_src, self.signs, self.codebook, slots, n_pages)
+        self.committed += n_pages * self.page
+        self.n_pages_dev.fill_(self.committed // self.page)
+
+    def _dense_chunk(self, p0: int, p1: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Pages p0 .. p1-1 of every sequence: pre-RoPE keys and values, float32 (batch, h_kv, tokens, 128)."""
+        h_kv, n = self.geom.h_kv, p1 - p0
+        slots = self.page_table[:, p0:p1].contiguous().view(-1)
+        y_hat = K.spectral_dequant_pages(self.pack, self.kpool, slots, want_codes=False, want_k=True)["k"]  # (B n, page, C)
+        kd = torch.matmul(y_hat, self.dec_full.t()).view(self.batch, n * self.page, h_kv, HEAD_DIM).permute(0, 2, 1, 3)
+        vd = dequant_value_blocks(self.vpool, slots, self.codebook, self.signs)
+        return kd, vd.view(self.batch, n * self.page, h_kv, HEAD_DIM).permute(0, 2, 1, 3)
+
+    def dense_pages(self) -> tuple[torch.Tensor, torch.Tensor]:
+        n_pg = self.committed // self.page
+        parts = [self._dense_chunk(p, min(n_pg, p + self.chunk_pages)) for p in range(0, n_pg, self.chunk_pages)]
+        return torch.cat([k for k, _ in parts], 2), torch.cat([v for _, v in parts], 2)
+
+    def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
+               phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
+        if partial_out is not None or phases != 3:
+            raise NotImplementedError("a pack that mixes heads decodes through the chunked route: no partial states")
+        from .rope import apply_rope
+
+        B, h_kv, G = self.batch, self.geom.h_kv, self.n_q_groups
+        qf = q.float().view(B, h_kv, G, HEAD_DIM) * self.sm_scale
+        m = torch.full((B, h_kv, G, 1), float("-inf"), device=self.device)
+        l = torch.zeros(B, h_kv, G, 1, device=self.device)
+        acc = torch.zeros(B, h_kv, G, HEAD_DIM, device=self.device)
+
+        def attend(k, v):  # (B, h_kv, n, 128) float32 each: one step of the running softmax
+            nonlocal m, l, acc
+            s = torch.matmul(qf, k.transpose(2, 3))
+            m_new = torch.maximum(m, s.amax(-1, keepdim=True))
+            w, f = torch.exp(s - m_new), torch.exp(m - m_new)
+            l, acc, m = l * f + w.sum(-1, keepdim=True), acc * f + torch.matmul(w, v), m_new
+
+        n_pg = self.committed // self.page
+        for p0 in range(0, n_pg, self.chunk_pages):
+            p1 = min(n_pg, p0 + self.chunk_pages)
+            kd, vd = self._dense_chunk(p0, p1)
+            t0, t1 = pos_offset + p0 * self.page, pos_offset + p1 * self.page
+            attend(apply_rope(kd, self.rope_cos[t0:t1].float(), self.rope_sin[t0:t1].float()), vd)
+        if self.tail_len:
+            attend(self.k_win[:, :, : self.tail_len].float(), self.v_win[:, :, : self.tail_len].float())
+        res = (acc / l).view(B, h_kv * G, HEAD_DIM)
+        if out is None:
+            return res.to(torch.float16)
+        out.copy_(res)
+        return out
+
+    def packed_bytes(self) -> int:
+        return int(self.batch * self.geom.h_kv * (self.committed // self.page) * (self.geom.block_bytes + self.vpool.shape[2]))
+
+
 class RtnLayerState(K2bLayerState):
     """Same state for the plain RTN arms (bmx rtn_token / rtn_channel keys, rtn_token values): keys are quantized
     after RoPE, so there is no basis, no rotation at read and no separate page-source window.  A decode step is the RTN

@@ -20,7 +20,7 @@ from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS, sdpa_mask
 from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
 from . import kernels as K
-from .engine import K2bLayerState, RtnLayerState, SpectralLayerState
+from .engine import FullSpectralLayerState, K2bLayerState, RtnLayerState, SpectralLayerState
 from .rope import apply_rope, rope_tables_from_config
 from .schedule import cache_bits_per_entry, codec_bpe, compute_flush_schedule, scale_bits
 from .specs import FUSED_PAIRS, CacheCodecSpec
@@ -116,6 +116,27 @@ class SpectralHeadPacks:
         return int(((self.bits > 0) & (self.bits <= tier_threshold)).sum())
 
 
+class SpectralFullPack:
+    """A K4 spectral pack of one layer with ONE encoder over all KV heads, the shape bmx fits: enc, dec (C, C) float32,
+    Y = M @ enc over the concatenated heads, M_hat = Y_hat @ dec.T, bits (C,) (bmx: SpectralPack,
+    src/bmx/cache/spectral.py:174-220).  Served by the chunked route (engine.FullSpectralLayerState), not by the
+    fused decode kernel."""
+
+    def __init__(self, enc: torch.Tensor, dec: torch.Tensor, bits: torch.Tensor, group: int = 64,
+                 tiers: tuple = (0, 2, 3, 4, 5, 6, 8), dec_tier: int | None = None):
+        C = enc.shape[0]
+        assert enc.shape == dec.shape == (C, C) and C % HEAD_DIM == 0 and bits.shape == (C,)
+        self.enc, self.dec, self.bits, self.group = enc.float(), dec.float(), bits.to(torch.int32), int(group)
+        self.tiers, self.dec_tier = tuple(tiers), dec_tier
+
+    @property
+    def c_used(self) -> int:
+        return int((self.bits != 0).sum())
+
+    def c_int8(self, tier_threshold: int) -> int:
+        return int(((self.bits > 0) & (self.bits <= tier_threshold)).sum())
+
+
 def check_rtn_specs(k_spec: CacheCodecSpec, v_spec: CacheCodecSpec) -> None:
     """What the RTN kernels cover: post-RoPE keys of 2..4 bits, 2-bit values, groups of 32 / 64 / 128."""
     if k_spec.pre_rope:
@@ -144,15 +165,15 @@ class PackedStreamingLayer(DynamicLayer):
             raise NotImplementedError(
                 f"no CUDA decode kernel for arms K={k_spec.arm!r} / V={v_spec.arm!r} in PackedStreamingLayer; "
                 "supported: lowrank_rtn_channel + turboquant_mse_perhead (recipe 'k2b_ph'), rtn_token or rtn_channel keys "
-                "with rtn_token values (recipe 'kivi'), and spectral + turboquant_mse_perhead with per-head packs. "
+                "with rtn_token values (recipe 'kivi'), and spectral + turboquant_mse_perhead. "
                 "There is no CPU fallback.")
         if kind == "rtn":
             check_rtn_specs(k_spec, v_spec)
         if kind == "spectral" and pack is None:
             raise NotImplementedError(
-                "the spectral key arm needs per-head packs (enc, dec, bits of shape (h_kv, 128, 128) / (h_kv, 128)) passed as "
-                "PackedStreamingCache(..., spectral_packs={layer: SpectralHeadPacks}); pack files holding one encoder over "
-                "all heads have no fused kernel")
+                "the spectral key arm needs a pack per layer: PackedStreamingCache(..., spectral_packs={layer: pack}) with "
+                "SpectralHeadPacks (one 128 x 128 encoder per head: fused decode kernel) or SpectralFullPack (one encoder over "
+                "all heads: chunked route), or a pack file named by the spec's pack_path")
         self._kind, self._pack = kind, pack
         tc = resolve_text_config(model_config)
         self._h_kv = getattr(tc, "num_key_value_heads", tc.num_attention_heads)
@@ -187,10 +208,16 @@ class PackedStreamingLayer(DynamicLayer):
             cos, sin = shared_rope(self.model_config, 4096, key_states.device)
             if self._kind == "spectral":
                 assert self.k_spec.pre_rope, "the spectral arm quantizes pre-RoPE keys"
-                dev_pack = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g,
-                                             device=key_states.device)
-                self._state = SpectralLayerState(dev_pack, self._n_q_groups, self._batch, 4096, self.recent_window,
-                                                 key_states.device, cos, sin, v_seed=self.v_spec.seed)
+                if isinstance(self._pack, SpectralFullPack):  # one encoder over all heads: the chunked route
+                    assert self._pack.enc.shape[0] == self._h_kv * HEAD_DIM, "pack width differs from h_kv * head_dim"
+                    self._state = FullSpectralLayerState(self._pack.enc, self._pack.dec, self._pack.bits, self._g, self._n_q_groups,
+                                                         self._batch, 4096, self.recent_window, key_states.device, cos, sin,
+                                                         v_seed=self.v_spec.seed)
+                else:
+                    dev_pack = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g,
+                                                 device=key_states.device)
+                    self._state = SpectralLayerState(dev_pack, self._n_q_groups, self._batch, 4096, self.recent_window,
+                                                     key_states.device, cos, sin, v_seed=self.v_spec.seed)
             elif self._kind == "rtn":
                 geom = K.rtn_geom(self._h_kv, self._n_q_groups, self._page, self.k_spec.arm, self.k_spec.group, self.v_spec.group,
                                   self.k_spec.bits, self.v_spec.bits)
@@ -386,8 +413,8 @@ class PackedStreamingCache(Cache):
             return None
         if i not in self._packs:
             raise NotImplementedError(
-                f"no spectral pack for layer {i}: pass spectral_packs={{layer: SpectralHeadPacks}} (per-head packs); loading "
-                "bmx pack files (one encoder over all heads) is not supported")
+                f"no spectral pack for layer {i}: pass spectral_packs={{layer: SpectralHeadPacks or SpectralFullPack}} or a "
+                "pack file that holds this layer")
         return self._packs[i]
 
     def bits_per_entry(self):

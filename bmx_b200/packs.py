@@ -3,8 +3,9 @@
 and budgets (bmx: save_pack_file / load_packs, src/bmx/cache/spectral.py:1081-1164).
 
 bmx fits one encoder over all heads, (C, C) with C = h_kv * 128; the fused kernels here take one 128 x 128
-encoder per head.  Both shapes load: a per-head file stores (h_kv, 128, 128) tensors; a bmx file is accepted
-when its encoder and decoder are block diagonal over heads (the blocks are taken out), and refused otherwise.
+encoder per head.  Both shapes load: a per-head file stores (h_kv, 128, 128) tensors; a bmx file whose encoder and
+decoder are block diagonal over heads gives per-head packs (the blocks are taken out, SpectralHeadPacks: fused
+decode kernel); one that mixes heads is returned whole (SpectralFullPack: chunked route).
 The decoder's int8 storage option is the same per-column round trip as bmx's (src/bmx/cache/spectral.py:913-943).
 """
 
@@ -15,7 +16,7 @@ from pathlib import Path
 
 import torch
 
-from .packed_streaming import SpectralHeadPacks
+from .packed_streaming import SpectralFullPack, SpectralHeadPacks
 
 HEAD_DIM = 128
 TIERS = (0, 2, 3, 4, 5, 6, 8)
@@ -55,8 +56,8 @@ def save_head_packs(path: str | Path, packs: dict[int, SpectralHeadPacks], budge
     Path(str(path) + ".json").write_text(json.dumps(sidecar))
 
 
-def _blocks(M: torch.Tensor, h_kv: int, name: str) -> torch.Tensor:
-    """(h_kv*128, h_kv*128) block-diagonal matrix -> (h_kv, 128, 128); anything else is refused."""
+def _blocks(M: torch.Tensor, h_kv: int, name: str) -> torch.Tensor | None:
+    """(h_kv*128, h_kv*128) block-diagonal matrix -> (h_kv, 128, 128); None when the matrix mixes heads."""
     C = h_kv * HEAD_DIM
     if M.shape != (C, C):
         raise ValueError(f"{name}: shape {tuple(M.shape)} is neither (h_kv, 128, 128) nor ({C}, {C})")
@@ -64,13 +65,10 @@ def _blocks(M: torch.Tensor, h_kv: int, name: str) -> torch.Tensor:
     off = M.clone()
     for h in range(h_kv):
         off[h * HEAD_DIM:(h + 1) * HEAD_DIM, h * HEAD_DIM:(h + 1) * HEAD_DIM] = 0
-    if float(off.abs().max()) != 0.0:
-        raise NotImplementedError(f"{name} mixes KV heads (one encoder over all {C} channels): the fused spectral kernels take "
-                                  "one 128 x 128 pack per head")
-    return blocks
+    return blocks if float(off.abs().max()) == 0.0 else None
 
 
-def load_head_packs(path: str | Path, budget: float, h_kv: int, dec_quant: str = "fp32") -> dict[int, SpectralHeadPacks]:
+def load_head_packs(path: str | Path, budget: float, h_kv: int, dec_quant: str = "fp32") -> dict:
     """Per-layer per-head packs for one budget.  dec_quant: "fp32", "int8" (every direction with bits) or "int8_t{T}"
     (directions with at most T bits), as in bmx's CacheCodecSpec.dec_quant (src/bmx/cache/specs.py:12-91).
     Raises KeyError with the available budgets if `budget` is not in the file."""
@@ -94,8 +92,15 @@ def load_head_packs(path: str | Path, budget: float, h_kv: int, dec_quant: str =
     for i in layers:
         enc, dec, bits = tensors[f"layer{i}.enc"], tensors[f"layer{i}.dec"], tensors[f"layer{i}.bits_b{budget:g}"]
         if enc.dim() == 2:
-            enc, dec = _blocks(enc.float(), h_kv, f"layer{i}.enc"), _blocks(dec.float(), h_kv, f"layer{i}.dec")
-            bits = bits.reshape(h_kv, HEAD_DIM)
+            eb, db = _blocks(enc.float(), h_kv, f"layer{i}.enc"), _blocks(dec.float(), h_kv, f"layer{i}.dec")
+            if eb is None or db is None:  # one encoder over all heads, as bmx fits them: kept whole
+                dec = dec.float()
+                if quant:
+                    dec = int8_decoder_roundtrip(dec, bits.reshape(-1), thr)
+                out[i] = SpectralFullPack(enc.float(), dec, bits.reshape(-1), group=int(sidecar["group"]), tiers=tuple(sidecar["tiers"]),
+                                          dec_tier=thr if quant else None)
+                continue
+            enc, dec, bits = eb, db, bits.reshape(h_kv, HEAD_DIM)
         if enc.shape != (h_kv, HEAD_DIM, HEAD_DIM) or bits.shape != (h_kv, HEAD_DIM):
             raise ValueError(f"layer{i}: pack shapes {tuple(enc.shape)} / {tuple(bits.shape)} do not fit h_kv={h_kv}")
         if quant:

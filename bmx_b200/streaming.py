@@ -36,8 +36,8 @@ class StreamingQuantizedLayer(DynamicLayer):
         if self._kind == "rtn":
             check_rtn_specs(k_spec, v_spec)
         if self._kind == "spectral" and pack is None:
-            raise NotImplementedError("the spectral key arm needs per-head packs: StreamingQuantizedCache(..., "
-                                      "spectral_packs={layer: SpectralHeadPacks}); pack files are not loaded")
+            raise NotImplementedError("the spectral key arm needs a pack per layer: StreamingQuantizedCache(..., "
+                                      "spectral_packs={layer: SpectralHeadPacks or SpectralFullPack}) or the spec's pack_path")
         self._pack, self._pack_dev = pack, None
         tc = resolve_text_config(model_config)
         self._h_kv = getattr(tc, "num_key_value_heads", tc.num_attention_heads)
@@ -109,15 +109,30 @@ class StreamingQuantizedLayer(DynamicLayer):
         """The same for the spectral key codec: spectral append + page dequantizer for keys, value blocks for values."""
         dev, b = k_src.device, k_src.shape[0]
         n_pg = (end - start) // self._page
+        full = self._pack.enc.dim() == 2  # one encoder over all heads (SpectralFullPack): library GEMMs around the same kernels
         if self._pack_dev is None:
-            self._pack_dev = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g, device=dev)
+            if full:
+                eye = torch.eye(HEAD_DIM).expand(self._h_kv, HEAD_DIM, HEAD_DIM).contiguous()
+                self._pack_dev = K.SpectralPackDev(eye, eye, self._pack.bits.reshape(self._h_kv, HEAD_DIM), page=self._page, group=self._g,
+                                                   device=dev)
+                self._enc_full, self._dec_full = self._pack.enc.to(dev), self._pack.dec.to(dev)
+            else:
+                self._pack_dev = K.SpectralPackDev(self._pack.enc, self._pack.dec, self._pack.bits, page=self._page, group=self._g, device=dev)
             self._signs = K.hadamard_signs(HEAD_DIM, self.v_spec.seed).to(dev)
             self._codebook = torch.tensor(K.GAUSSIAN_CODEBOOK[self.v_spec.bits], device=dev)
         slots = torch.arange(b * n_pg, dtype=torch.int32, device=dev)
         kpool, vpool = self._pack_dev.new_pool(b * n_pg), K.vblock_pool(self._h_kv, b * n_pg, dev)
-        K.spectral_append(self._pack_dev, kpool, k_src.to(torch.float16).contiguous(), slots, n_pg)
+        k16 = k_src.to(torch.float16)
+        if full:  # Y = M @ enc over the concatenated heads; directions 128 g .. 128 g + 127 are stored as pseudo-head g
+            T, C = n_pg * self._page, self._h_kv * HEAD_DIM
+            Y = torch.matmul(k16[:, :, :T].permute(0, 2, 1, 3).reshape(b, T, C).float(), self._enc_full)
+            K.spectral_append(self._pack_dev, kpool, Y.view(b, T, self._h_kv, HEAD_DIM).permute(0, 2, 1, 3), slots, n_pg)
+        else:
+            K.spectral_append(self._pack_dev, kpool, k16.contiguous(), slots, n_pg)
         K.vblock_append(vpool, v_src.to(torch.float16).contiguous(), self._signs, self._codebook, slots, n_pg)
         kd = K.spectral_dequant_pages(self._pack_dev, kpool, slots, want_codes=False, want_k=True)["k"]
+        if full:
+            kd = torch.matmul(kd, self._dec_full.t())
         shp = (b, n_pg * self._page, self._h_kv, self._d_head)
         kd = kd.view(*shp).permute(0, 2, 1, 3)
         vd = dequant_value_blocks(vpool, slots, self._codebook, self._signs).view(*shp).permute(0, 2, 1, 3)

@@ -44,6 +44,8 @@ def main() -> None:
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     ap.add_argument("--skip-model", action="store_true", help="leave tests/golden/model.npz alone (the model-level part takes minutes)")
     ap.add_argument("--only-model", action="store_true", help="regenerate tests/golden/model.npz only")
+    ap.add_argument("--only-model-full", action="store_true",
+                    help="regenerate tests/golden/model_full.npz only (spectral packs with one encoder over all heads)")
     args = ap.parse_args()
     if not args.reference:
         ap.error("--reference (or BMX_REFERENCE) must point at a checkout of the bmx reference")
@@ -68,8 +70,8 @@ def main() -> None:
     def gen(seed):
         return torch.Generator().manual_seed(seed)
 
-    if args.only_model:
-        model_level(args, torch, gen, npy)
+    if args.only_model or args.only_model_full:
+        model_level(args, torch, gen, npy, full=args.only_model_full)
         return
 
     # ---- constants -------------------------------------------------------
@@ -236,11 +238,13 @@ def tiny_llama_config():
                        num_key_value_heads=2, head_dim=128, max_position_embeddings=4096, rope_theta=500000.0)
 
 
-def model_level(args, torch, gen, npy) -> None:
+def model_level(args, torch, gen, npy, full: bool = False) -> None:
     """Teacher-forced logits of the reference's own PackedStreamingCache (its CPU chunked path, float32) under a tiny
     random-init Llama: 300 prompt tokens, then 64 single-token steps (the method of the reference's
     scripts/profile_decode_ab.py).  One fixture per recipe; the frozen key basis each layer fitted is stored too, so
-    that a replay does not depend on which SVD library fits it.  Also stores the cache-level bits per entry."""
+    that a replay does not depend on which SVD library fits it.  Also stores the cache-level bits per entry.
+    full=True writes model_full.npz instead: the spectral recipes with ONE dense orthogonal encoder over both KV heads per
+    layer (the shape of the packs the reference fits), which the per-head kernels cannot take."""
     import warnings
 
     from safetensors.torch import save_file
@@ -300,6 +304,8 @@ def model_level(args, torch, gen, npy) -> None:
         for h in range(2):
             enc[h * 128:(h + 1) * 128, h * 128:(h + 1) * 128] = orthogonalize(torch.randn(128, 128, generator=g))
             bits[h * 128:(h + 1) * 128] = torch.tensor(by_tier)[torch.randperm(128, generator=g)]
+        if full:  # one orthogonal matrix over all 256 channels: every direction mixes both heads
+            enc = orthogonalize(torch.randn(C, C, generator=g)).contiguous()
         tensors[f"layer{i}.enc"], tensors[f"layer{i}.dec"] = enc, enc.clone()
         tensors[f"layer{i}.lam"] = torch.ones(C)
         tensors[f"layer{i}.bits_b2.5"] = bits
@@ -312,15 +318,19 @@ def model_level(args, torch, gen, npy) -> None:
     with open(pack_path + ".json", "w") as f:
         json.dump({"tiers": list(tiers), "group": 64, "budgets": [2.5]}, f)
 
-    recipes = {
-        "k2b_ph": spec_pair("k2b_ph", rank=16, group=64),
-        "kivi": spec_pair("kivi", group=64),
-        "rtn_c4t2": (CacheCodecSpec(arm="rtn_channel", bits=4, group=32), CacheCodecSpec(arm="rtn_token", bits=2, group=32)),
-        "spectral": (CacheCodecSpec(arm="spectral", pre_rope=True, group=64, pack_path=pack_path, budget=2.5),
-                     CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)),
-        "spectral_dec8": (CacheCodecSpec(arm="spectral", pre_rope=True, group=64, pack_path=pack_path, budget=2.5, dec_quant="int8"),
-                          CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)),
-    }
+    spectral_k = dict(arm="spectral", pre_rope=True, group=64, pack_path=pack_path, budget=2.5)
+    v_ph = CacheCodecSpec(arm="turboquant_mse_perhead", bits=2)
+    if full:
+        recipes = {"spectral_full": (CacheCodecSpec(**spectral_k), v_ph),
+                   "spectral_full_dec8": (CacheCodecSpec(**spectral_k, dec_quant="int8"), v_ph)}
+    else:
+        recipes = {
+            "k2b_ph": spec_pair("k2b_ph", rank=16, group=64),
+            "kivi": spec_pair("kivi", group=64),
+            "rtn_c4t2": (CacheCodecSpec(arm="rtn_channel", bits=4, group=32), CacheCodecSpec(arm="rtn_token", bits=2, group=32)),
+            "spectral": (CacheCodecSpec(**spectral_k), v_ph),
+            "spectral_dec8": (CacheCodecSpec(**spectral_k, dec_quant="int8"), v_ph),
+        }
     for seed, (name, (k_spec, v_spec)) in enumerate(recipes.items()):
         # Prompts are drawn until the reference's own top-2 logit gap is at least 0.005 at every step: a random-init
         # model's top two logits are sometimes closer than any two correct implementations agree to, and a flip at
@@ -352,7 +362,7 @@ def model_level(args, torch, gen, npy) -> None:
         out[f"{name}_twin_max_logit_diff"] = np.float64((lt - lg).abs().max())
         print(name, "min top-2 gap", float(out[f"{name}_min_top2_gap"]), "bpe", out[f"{name}_bpe"], "twin", out[f"{name}_twin_bpe"],
               "twin diff", float(out[f"{name}_twin_max_logit_diff"]))
-    np.savez_compressed(os.path.join(args.out, "model.npz"), **out)
+    np.savez_compressed(os.path.join(args.out, "model_full.npz" if full else "model.npz"), **out)
 
 
 if __name__ == "__main__":

@@ -275,13 +275,15 @@ def _write_reference_pack_file(fx, path):
         json.dump({"tiers": [0, 2, 3, 4, 5, 6, 8], "group": 64, "budgets": [2.5]}, f)
 
 
-@pytest.mark.parametrize("recipe", ["k2b_ph", "k2b_ph_own_basis", "kivi", "rtn_c4t2", "spectral", "spectral_dec8"])
+@pytest.mark.parametrize("recipe", ["k2b_ph", "k2b_ph_own_basis", "kivi", "rtn_c4t2", "spectral", "spectral_dec8", "spectral_full",
+                                    "spectral_full_dec8"])
 def test_argmax_and_accounting_match_the_reference_cache(recipe, tmp_path):
     """64 teacher-forced decode steps after a 300-token prompt: every step's argmax equals the one bmx's own
     PackedStreamingCache produced (0 flips, nothing masked), logits agree closely, and the cache-level bits per
     entry and memory report equal the reference's numbers.  `k2b_ph` replays with the key basis the reference froze;
     `k2b_ph_own_basis` fits its own (another SVD library: singular vectors may differ in sign or rotate inside a
-    near-degenerate pair, the projected subspace is the same)."""
+    near-degenerate pair, the projected subspace is the same).  `spectral_full*` use packs with one dense encoder over
+    both KV heads (the shape bmx fits), which go through the chunked route instead of the fused decode kernel."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from bmx_b200.packed_streaming import PackedStreamingCache
@@ -290,7 +292,7 @@ def test_argmax_and_accounting_match_the_reference_cache(recipe, tmp_path):
     from bmx_b200.streaming import StreamingQuantizedCache
     from tests.helpers import golden
 
-    dev, fx = torch.device("cuda:0"), golden("model")
+    dev, fx = torch.device("cuda:0"), golden("model_full" if recipe.startswith("spectral_full") else "model")
     name = "k2b_ph" if recipe.startswith("k2b_ph") else recipe
     model = _reference_model(dev)
     if name == "k2b_ph":
@@ -328,7 +330,11 @@ def test_argmax_and_accounting_match_the_reference_cache(recipe, tmp_path):
     rep = cache.memory_report(ids.shape[1])
     want = fx[f"{name}_memory_report"]
     assert abs(rep["fp16_bytes"] - want[0]) < 1e-6 and abs(rep["packed_bytes"] - want[1]) < 1e-3 and abs(rep["compression"] - want[2]) < 1e-9
-    if recipe in ("kivi", "spectral_dec8"):  # the dequantized-resident twin: same accounting, same tokens
+    if recipe.startswith("spectral_full"):
+        from bmx_b200.engine import FullSpectralLayerState
+
+        assert all(type(l._state) is FullSpectralLayerState for l in cache.layers)
+    if recipe in ("kivi", "spectral_dec8", "spectral_full"):  # the dequantized-resident twin: same accounting, same tokens
         twin = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32)
         lt = _teacher_forced(model, twin, ids)
         tb = twin.bits_per_entry()

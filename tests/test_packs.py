@@ -1,6 +1,6 @@
 """Spectral pack files (host side, no GPU): per-head packs survive a save / load round trip in bmx's container,
-a bmx-shaped file (one (C, C) encoder) loads when it is block diagonal over heads and is refused when it mixes
-heads, and the decoder's int8 round trip equals the oracle's."""
+a bmx-shaped file (one (C, C) encoder) gives per-head packs when it is block diagonal over heads and one whole pack
+when it mixes heads, and the decoder's int8 round trip equals the oracle's."""
 
 import json
 
@@ -43,7 +43,7 @@ def test_round_trip_and_budget_lookup(tmp_path):
         load_head_packs(path, 2.5, h_kv=4)
 
 
-def test_bmx_shaped_file_block_diagonal_or_refused(tmp_path):
+def test_bmx_shaped_file_block_diagonal_or_whole(tmp_path):
     from safetensors.torch import save_file
 
     from bmx_b200.packs import load_head_packs
@@ -61,8 +61,14 @@ def test_bmx_shaped_file_block_diagonal_or_refused(tmp_path):
     assert torch.equal(back.enc, packs.enc) and torch.equal(back.bits, packs.bits)
     enc[0, 200] = 0.01  # one entry that couples two heads
     save_file(dict(tensors, **{"layer0.enc": enc}), str(path))
-    with pytest.raises(NotImplementedError):
-        load_head_packs(path, 2.5, h_kv=2)
+    from bmx_b200.packed_streaming import SpectralFullPack
+
+    whole = load_head_packs(path, 2.5, h_kv=2)[0]
+    assert isinstance(whole, SpectralFullPack) and torch.equal(whole.enc, enc) and whole.bits.shape == (C,)
+    assert whole.c_used == int((packs.bits != 0).sum()) and whole.group == 64
+    q8 = load_head_packs(path, 2.5, h_kv=2, dec_quant="int8")[0]
+    assert q8.dec_tier == 8 and q8.dec.shape == (C, C)
+    np.testing.assert_array_equal(q8.dec.numpy(), O.int8_decoder_roundtrip(tensors["layer0.dec"].numpy(), packs.bits.reshape(-1).numpy(), None))
 
 
 def test_int8_decoder_round_trip_equals_oracle(tmp_path):
