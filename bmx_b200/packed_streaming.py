@@ -151,9 +151,19 @@ def check_rtn_specs(k_spec: CacheCodecSpec, v_spec: CacheCodecSpec) -> None:
 class PackedStreamingLayer(DynamicLayer):
     """Per-layer packed cache: page pool + frozen key basis + fp16 recent window."""
 
+    # Prompt attention over a k2b cache has two routes.  "paged": the kernel that dequantizes one page at a time in shared
+    # memory (no dense K / V for the context, the route for long contexts); "dense": dequantize every committed page, then
+    # the library's scaled_dot_product_attention (what bmx does; faster while its transient fits).  "auto" takes the dense
+    # route while that transient stays under DENSE_PREFILL_BUDGET bytes.
+    PREFILL_ROUTES = ("auto", "paged", "dense")
+    DENSE_PREFILL_BUDGET = 1 << 30
+    DENSE_BYTES_PER_ELEMENT = 20  # measured: float32 page dequantizer output, the rotated copy, fp16 K and V, the concatenation
+
     def __init__(self, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, model_config, recent_window: int = 32,
-                 pack_v: bool = True, pack_k: bool = True, pack=None):
+                 pack_v: bool = True, pack_k: bool = True, pack=None, prefill_route: str = "auto"):
         super().__init__()
+        assert prefill_route in self.PREFILL_ROUTES, prefill_route
+        self.prefill_route = prefill_route
         self.k_spec, self.v_spec, self.model_config = k_spec, v_spec, model_config
         if not (pack_v and pack_k):
             # bmx keeps unpacked codes in int8 / int16 containers when these are False (a debugging aid of its Triton
@@ -362,17 +372,20 @@ class PackedStreamingLayer(DynamicLayer):
         # prefill: rows at the last n_q positions, causal.  With the model's plain causal mask (or none) the paged kernel
         # attends page by page; any other mask (padding) goes through the dequantize-everything route, as in bmx.
         S = st.seq_len()
-        if self._kind == "k2b" and st.committed > 0 and n_q <= S and self._mask_is_causal(attention_mask, n_q, S):
+        paged = self._kind == "k2b" and st.committed > 0 and n_q <= S and self.prefill_route != "dense"
+        if paged and self.prefill_route == "auto":
+            paged = b * st.committed * self._h_kv * self._d_head * self.DENSE_BYTES_PER_ELEMENT > self.DENSE_PREFILL_BUDGET
+        if paged and self._mask_is_causal(attention_mask, n_q, S):
             st.sm_scale = float(scaling)
             out = st.prefill_attend(q.to(torch.float16).contiguous(), S - n_q)
             if out is not None:
                 return out.to(q.dtype)
         Kd, Vd = self._dense_kv(q.dtype)
+        if attention_mask is None:  # no mask: a multi-row block is the whole prompt, causal; KV heads are shared, not copied
+            return F.scaled_dot_product_attention(q, Kd, Vd, is_causal=n_q > 1, scale=scaling, enable_gqa=self._n_q_groups > 1)
         Kx = Kd.repeat_interleave(self._n_q_groups, dim=1)
         Vx = Vd.repeat_interleave(self._n_q_groups, dim=1)
-        # a single query row attends every cached key; only a multi-row block without a mask is causal
-        return F.scaled_dot_product_attention(q, Kx, Vx, attn_mask=attention_mask,
-                                              is_causal=(attention_mask is None and n_q > 1), scale=scaling)
+        return F.scaled_dot_product_attention(q, Kx, Vx, attn_mask=attention_mask, scale=scaling)
 
 
 class PackedStreamingCache(Cache):
@@ -384,8 +397,9 @@ class PackedStreamingCache(Cache):
     """
 
     def __init__(self, model_config, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, recent_window: int = 32,
-                 pack_v: bool = True, pack_k: bool = True, spectral_packs: dict | None = None):
+                 pack_v: bool = True, pack_k: bool = True, spectral_packs: dict | None = None, prefill_route: str = "auto"):
         self._packs = dict(spectral_packs or {})
+        self.prefill_route = prefill_route
         if k_spec.arm == "spectral" and not self._packs and k_spec.pack_path:
             # the pack file is read once here and handed out by layer index (bmx: packed_streaming.py:1086-1094)
             from .packs import load_head_packs
@@ -397,7 +411,7 @@ class PackedStreamingCache(Cache):
 
         def _make_layer():
             return PackedStreamingLayer(k_spec, v_spec, model_config, recent_window, pack_v=pack_v, pack_k=pack_k,
-                                        pack=wself._pack_for_layer(len(wself.layers)))
+                                        pack=wself._pack_for_layer(len(wself.layers)), prefill_route=wself.prefill_route)
 
         self._make_layer = _make_layer
         super().__init__(layer_class_to_replicate=_make_layer)

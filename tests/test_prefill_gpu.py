@@ -94,7 +94,8 @@ def test_paged_prefill_long_context_rows_near_the_end():
 
 def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     """Under a Hugging Face model the prompt's attention goes through the paged kernel when the mask is the plain causal
-    one; forcing the dense route (dequantize every page, SDPA) gives the same logits to fp16 accuracy."""
+    one and the cache's prefill_route asks for it ("auto" asks once the dense transient would pass its budget); the dense
+    route (dequantize every page, SDPA) gives the same logits to fp16 accuracy."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from bmx_b200.engine import K2bLayerState
@@ -118,7 +119,7 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
 
         K2bLayerState.prefill_attend = spy
         try:
-            cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+            cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32, prefill_route="paged" if paged else "dense")
             with cache.attach(model), torch.no_grad():
                 a = model(ids[:, :450], past_key_values=cache, use_cache=True).logits      # pages are committed before attention
                 b = model(ids[:, 450:], past_key_values=cache, use_cache=True).logits      # a second block on top of a cache
@@ -127,7 +128,24 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
             K2bLayerState.prefill_attend = orig
 
     lp, ld = run(True), run(False)
-    assert calls == [(450, 0), (450, 0), (250, 450), (250, 450)], calls  # two layers, two blocks
+    assert calls == [(450, 0), (450, 0), (250, 450), (250, 450)], calls  # two layers, two blocks; none from the dense run
+    from bmx_b200.packed_streaming import PackedStreamingLayer
+
+    assert PackedStreamingLayer.DENSE_PREFILL_BUDGET == 1 << 30  # "auto": a 700-token prompt is far below it -> dense route
+    cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+    n_before = len(calls)
+    K2bLayerState.prefill_attend = lambda self, q, q_pos0, out=None: calls.append("auto") or orig(self, q, q_pos0, out)
+    try:
+        with cache.attach(model), torch.no_grad():
+            la = model(ids[:, :450], past_key_values=cache, use_cache=True).logits.float()
+            assert len(calls) == n_before
+            PackedStreamingLayer.DENSE_PREFILL_BUDGET = 0  # now every committed page is over budget
+            lb = model(ids[:, 450:], past_key_values=cache, use_cache=True).logits.float()
+            assert calls[n_before:] == ["auto", "auto"]
+    finally:
+        K2bLayerState.prefill_attend = orig
+        PackedStreamingLayer.DENSE_PREFILL_BUDGET = 1 << 30
+    assert float((torch.cat([la, lb], 1) - ld).abs().max()) < 5e-2
     diff = float((lp - ld).abs().max())
     print(f"paged vs dense prefill logits: max diff {diff:.3e}")
     # layer 2 quantizes keys and values that come out of layer 1's attention, where the two routes differ in the last fp16
