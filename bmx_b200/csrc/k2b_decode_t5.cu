@@ -148,7 +148,266 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
 
   // Registers move from the softmax, value and service warps to the key warps: each group of four warps
   // resizes itself first thing in its branch.
-  if (warp >= 24) {
+  if (warp < 8) {
+    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
+    const int wq = warp & 3, k0 = 2 * (warp >> 2), row = 32 * wq + lane;
+    const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
+    const int grp = row / g.group;
+    const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
+    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
+    uint32_t cs_[2][8], sn_[2][8];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+        sn_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+      }
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      const uint32_t par = (uint32_t)(n >> 1) & 1u;
+      const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
+      if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
+      tc5::fence_after();
+      uint32_t dl[2][8], dh[2][8];
+      // a warp's TMEM loads complete one after the other, so the second chunk's are issued only after the first
+      // chunk's have landed and travel while the first chunk is computed
+      tc5::ld16_pack(tk + 128 * b + 16 * k0, dl[0]);
+      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0, dh[0]);
+      const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const int k = k0 + kk;
+        uint32_t out[16];
+        const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
+        const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
+        tc5::wait_ld();
+        if (kk == 0) {
+          tc5::ld16_pack(tk + 128 * b + 16 * k0 + 16, dl[1]);
+          tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0 + 16, dh[1]);
+        }
+#pragma unroll
+        for (int wd = 0; wd < 2; ++wd) {
+          const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
+          const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
+          __half2 rl[4], rh[4];
+          {
+            const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
+            rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
+            rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
+            rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
+            rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
+            rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[kk][4 * wd + i]));
+            const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[kk][4 * wd + i]));
+            const __half2 c = u32_as_h2(cs_[kk][4 * wd + i]), sn = u32_as_h2(sn_[kk][4 * wd + i]);
+            out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+            out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+          }
+        }
+        tc5::st16(tk + 128 * b + 16 * k, out);
+      }
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
+    }
+  } else if (warp >= 16 && warp < 24) {
+    // ===================== value warps: thread = channel, warp = one half (64 tokens) of the tile =====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
+    const int wq = warp & 3, cc = (warp - 16) >> 2, ch = 32 * wq + lane;
+    const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
+      // the columns still feed U3 of tile n-2
+      if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
+      tc5::fence_after();
+      const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
+      {
+        const uint4 cw = vc[cc * 128 + ch];
+        const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+          uint32_t out[16];
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const uint32_t wv = wd[2 * jp + jj];
+            const uint32_t x0 = wv & 0x33333333u, x1 = (wv >> 2) & 0x33333333u;
+#pragma unroll
+            for (int hs = 0; hs < 2; ++hs) {
+              const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
+              const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
+              const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
+              out[8 * jj + 2 * hs] = prmt(lo0, hi0, 0x5140u), out[8 * jj + 2 * hs + 1] = prmt(lo0, hi0, 0x7362u);
+              out[8 * jj + 4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), out[8 * jj + 4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);
+            }
+          }
+          tc5::st16(tv + 64 * b + 32 * cc + 16 * jp, out);
+        }
+      }
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
+      if (++s == T5_STAGES) s = 0, fp ^= 1u;
+    }
+  } else if (warp < 16) {
+    // ===================== softmax warps: thread = token row =====================
+    // Two sets of four warps; set e takes the tiles of parity e and owns the running (max, sum) and the output
+    // accumulator of that parity, so each set has two tile periods per tile.  Each set writes its own partial
+    // record per (sequence, head) range.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
+    const int e = (warp - 8) >> 2, wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
+    float m[GQ], l[GQ], pn[GQ];
+#pragma unroll
+    for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
+    bool had = false, alive = true;
+    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
+
+    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
+    auto flush = [&](int b_, int h_) {
+      float acc[GQ];
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
+      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
+      if (had && alive) {
+        tc5::fence_after();
+        uint32_t r[GQ];
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+        tc5::wait_ld();
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
+        tc5::fence_before();
+      }
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) {
+        float a = l[qi], b2 = pn[qi];
+#pragma unroll
+        for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
+        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
+      }
+      named_bar(1 + e, 128);
+      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi)
+        if (qi < G) {
+          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
+          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
+          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
+        }
+      named_bar(1 + e, 128);
+    };
+
+    for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
+      const int n = w.it;
+      if (w.seg != cur_seg) {
+        if (cur_seg >= 0) flush(cur_b, cur_h);
+        cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
+      }
+      if ((n & 1) != e) continue;
+      const int s = n % T5_STAGES;
+      const uint32_t fp = (uint32_t)(n / T5_STAGES) & 1u, par = (uint32_t)(n >> 1) & 1u;
+      const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+      float sv[GQ];
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
+      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
+      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
+      if (alive) {
+        tc5::fence_after();
+        uint32_t r[GQ];
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
+        tc5::wait_ld();
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
+      }
+      // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
+      // below 2^8), nothing is reduced; the four warps only exchange one flag each.
+      bool need = false;
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
+      const bool wneed = __any_sync(0xffffffffu, need);
+      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
+      named_bar(1 + e, 128);
+      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
+      const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
+      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      if (resc) {
+        float mnew[GQ];
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) {
+          float v = sv[qi];
+#pragma unroll
+          for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
+          if (lane == 0) sh->wmax[e][wq][qi] = v;
+        }
+        named_bar(1 + e, 128);
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) {
+          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
+          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
+        }
+        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
+        if (alive) {
+          float f[GQ];
+#pragma unroll
+          for (int qi = 0; qi < GQ; ++qi) {
+            f[qi] = (m[qi] == -INFINITY) ? 0.f : ex2_approx(m[qi] - mnew[qi]);
+            l[qi] *= f[qi], pn[qi] *= f[qi], m[qi] = mnew[qi];
+          }
+          if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
+            tc5::fence_after();
+            uint32_t r[GQ];
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
+            tc5::wait_ld();
+#pragma unroll
+            for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
+            tc5::wait_st();
+          }
+        }
+      }
+      if (alive) {
+        const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
+#pragma unroll
+        for (int qi = 0; qi < GQ; qi += 2) {
+          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
+          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
+          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
+          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
+        }
+        fence_proxy_async();
+        tc5::fence_before();
+        __syncwarp();
+        if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
+      }
+      had = true, last_n = n;
+    }
+    flush(cur_b, cur_h);
+  } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SERVICE));  // the four service warps, as one group
     if (warp == 24) {
       // ===================== copy + U3 warp =====================
@@ -351,265 +610,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           }
         }
       }
-    }
-  } else if (warp < 8) {
-    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REG_KEY));
-    const int wq = warp & 3, k0 = 2 * (warp >> 2), row = 32 * wq + lane;
-    const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
-    const int grp = row / g.group;
-    const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
-    const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
-    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
-    uint32_t cs_[2][8], sn_[2][8];
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
-        sn_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
-      }
-    int s = 0;
-    uint32_t fp = 0;
-    for (int n = 0; n < n_tiles; ++n) {
-      const int b = n & 1;
-      const uint32_t par = (uint32_t)(n >> 1) & 1u;
-      const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 2)) break;
-      if (!wait_or_flag(&sh->low[b], par, p.status, 6)) break;
-      tc5::fence_after();
-      uint32_t dl[2][8], dh[2][8];
-      // a warp's TMEM loads complete one after the other, so the second chunk's are issued only after the first
-      // chunk's have landed and travel while the first chunk is computed
-      tc5::ld16_pack(tk + 128 * b + 16 * k0, dl[0]);
-      tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0, dh[0]);
-      const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
-#pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        const int k = k0 + kk;
-        uint32_t out[16];
-        const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
-        const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
-        tc5::wait_ld();
-        if (kk == 0) {
-          tc5::ld16_pack(tk + 128 * b + 16 * k0 + 16, dl[1]);
-          tc5::ld16_pack(tk + 128 * b + 64 + 16 * k0 + 16, dh[1]);
-        }
-#pragma unroll
-        for (int wd = 0; wd < 2; ++wd) {
-          const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
-          const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
-          __half2 rl[4], rh[4];
-          {
-            const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
-            rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
-            rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-            rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
-            rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-            rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
-            rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-            rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
-            rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[kk][4 * wd + i]));
-            const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[kk][4 * wd + i]));
-            const __half2 c = u32_as_h2(cs_[kk][4 * wd + i]), sn = u32_as_h2(sn_[kk][4 * wd + i]);
-            out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
-            out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
-          }
-        }
-        tc5::st16(tk + 128 * b + 16 * k, out);
-      }
-      tc5::wait_st();
-      tc5::fence_before();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
-      if (++s == T5_STAGES) s = 0, fp ^= 1u;
-    }
-  } else if (warp < 16) {
-    // ===================== softmax warps: thread = token row =====================
-    // Two sets of four warps; set e takes the tiles of parity e and owns the running (max, sum) and the output
-    // accumulator of that parity, so each set has two tile periods per tile.  Each set writes its own partial
-    // record per (sequence, head) range.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_SOFTMAX));
-    const int e = (warp - 8) >> 2, wq = warp & 3, row = 32 * wq + lane;
-    const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
-    float m[GQ], l[GQ], pn[GQ];
-#pragma unroll
-    for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
-    bool had = false, alive = true;
-    const int64_t sub_slots = (int64_t)gridDim.x + (int64_t)p.batch * g.h_kv;
-
-    // Writes this set's partial record of the range that just ended (an empty one if the set had no tile in it).
-    auto flush = [&](int b_, int h_) {
-      float acc[GQ];
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      if (had && alive && !wait_or_flag(&sh->odone[e], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
-      if (had && alive) {
-        tc5::fence_after();
-        uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
-        tc5::wait_ld();
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
-        tc5::fence_before();
-      }
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) {
-        float a = l[qi], b2 = pn[qi];
-#pragma unroll
-        for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[e][wq][qi] = a, sh->red[e][wq][GQ + qi] = b2;
-      }
-      named_bar(1 + e, 128);
-      float* dst = p.part + ((e * sub_slots + blockIdx.x + (int64_t)b_ * g.h_kv + h_) * G) * PART_STRIDE;
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi)
-        if (qi < G) {
-          const float L = sh->red[e][0][qi] + sh->red[e][1][qi] + sh->red[e][2][qi] + sh->red[e][3][qi];
-          const float P = sh->red[e][0][GQ + qi] + sh->red[e][1][GQ + qi] + sh->red[e][2][GQ + qi] + sh->red[e][3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
-          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
-        }
-      named_bar(1 + e, 128);
-    };
-
-    for (; w.it < n_tiles; w.advance(npg_sm, g.h_kv, p.batch)) {
-      const int n = w.it;
-      if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h);
-        cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-      }
-      if ((n & 1) != e) continue;
-      const int s = n % T5_STAGES;
-      const uint32_t fp = (uint32_t)(n / T5_STAGES) & 1u, par = (uint32_t)(n >> 1) & 1u;
-      const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
-      float sv[GQ];
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
-      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
-      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
-      if (alive) {
-        tc5::fence_after();
-        uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
-        tc5::wait_ld();
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
-      }
-      // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
-      // below 2^8), nothing is reduced; the four warps only exchange one flag each.
-      bool need = false;
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
-      const bool wneed = __any_sync(0xffffffffu, need);
-      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
-      named_bar(1 + e, 128);
-      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
-      const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
-      // the weight buffer and the accumulator of this parity still belong to U3 of tile n-2
-      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
-      if (resc) {
-        float mnew[GQ];
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) {
-          float v = sv[qi];
-#pragma unroll
-          for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-          if (lane == 0) sh->wmax[e][wq][qi] = v;
-        }
-        named_bar(1 + e, 128);
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) {
-          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
-          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
-        }
-        named_bar(1 + e, 128);  // the flags and maxima may be rewritten by the next tile only after everyone has read them
-        if (alive) {
-          float f[GQ];
-#pragma unroll
-          for (int qi = 0; qi < GQ; ++qi) {
-            f[qi] = (m[qi] == -INFINITY) ? 0.f : ex2_approx(m[qi] - mnew[qi]);
-            l[qi] *= f[qi], pn[qi] *= f[qi], m[qi] = mnew[qi];
-          }
-          if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
-            tc5::fence_after();
-            uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O + 16 * e, r); else tc5::ld8(tl + TM_O + 16 * e, r);
-            tc5::wait_ld();
-#pragma unroll
-            for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O + 16 * e, r); else tc5::st8(tl + TM_O + 16 * e, r);
-            tc5::wait_st();
-          }
-        }
-      }
-      if (alive) {
-        const float norm = __half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * T5_QB_BYTES) + (row >> 3) * 64 + (row & 7);
-#pragma unroll
-        for (int qi = 0; qi < GQ; qi += 2) {
-          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
-          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
-          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
-          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
-        }
-        fence_proxy_async();
-        tc5::fence_before();
-        __syncwarp();
-        if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
-      }
-      had = true, last_n = n;
-    }
-    flush(cur_b, cur_h);
-  } else {
-    // ===================== value warps: thread = channel, warp = one half (64 tokens) of the tile =====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REG_VALUE));
-    const int wq = warp & 3, cc = (warp - 16) >> 2, ch = 32 * wq + lane;
-    const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
-    int s = 0;
-    uint32_t fp = 0;
-    for (int n = 0; n < n_tiles; ++n) {
-      const int b = n & 1;
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
-      // the columns still feed U3 of tile n-2
-      if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
-      tc5::fence_after();
-      const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES + k2b_off_vcode(128, g.group));
-      {
-        const uint4 cw = vc[cc * 128 + ch];
-        const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-        for (int jp = 0; jp < 2; ++jp) {
-          uint32_t out[16];
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const uint32_t wv = wd[2 * jp + jj];
-            const uint32_t x0 = wv & 0x33333333u, x1 = (wv >> 2) & 0x33333333u;
-#pragma unroll
-            for (int hs = 0; hs < 2; ++hs) {
-              const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
-              const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
-              const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
-              out[8 * jj + 2 * hs] = prmt(lo0, hi0, 0x5140u), out[8 * jj + 2 * hs + 1] = prmt(lo0, hi0, 0x7362u);
-              out[8 * jj + 4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), out[8 * jj + 4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);
-            }
-          }
-          tc5::st16(tv + 64 * b + 32 * cc + 16 * jp, out);
-        }
-      }
-      tc5::wait_st();
-      tc5::fence_before();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
-      if (++s == T5_STAGES) s = 0, fp ^= 1u;
     }
   }
 

@@ -175,7 +175,309 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
   Walker w;
   w.init(cum, npg_sm, f_begin, h_kv);
 
-  if (warp >= SVC0) {
+  if (warp >= W_DQ && warp < SVC0) {
+    // ===================== dequant warps: tier codes -> fp16 Y_hat, the A operand of U1 =====================
+    // Warp wd takes the direction octets wd, wd + DQ_WARPS, ... (positions in tier order).  Lane = (direction
+    // lane / 4 of the octet, token pair q = lane % 4): for every 8-token block B it produces the half2 of tokens
+    // 8B + 2q, 8B + 2q + 1 of its direction, which is exactly what a transposed stmatrix wants from it.  Four
+    // blocks (32 tokens, one 8 / 16 / 32-byte piece of the direction's row) go out per stmatrix.
+    // A half2 costs four instructions whatever the tier: a byte permute drops the thread's code byte(s) under the
+    // fp16 exponent of 1024 in both halves, one LOP3 masks each half down to its field and flips two's-complement
+    // sign bits, an exact subtraction removes 1024 and the field's offset (times the field's position in the byte),
+    // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
+    // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
+    // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
+    set_regs<REG_DEQUANT>();
+    constexpr int OCT = 16 / DQ_WARPS;
+    const int wd = warp - W_DQ, q = lane & 3, dsub = lane >> 2;
+    const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
+    const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
+    const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
+    int s = 0;
+    uint32_t fp = 0;
+    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
+      const int n = w.it, b = n & 1, h = w.cur.h;
+      int meta[OCT];
+#pragma unroll
+      for (int oo = 0; oo < OCT; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (DQ_WARPS * oo + wd) + dsub);
+      const int n_oct = 2 * (((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1);  // octets that U1 reads for this head
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
+      // the buffer still feeds U1 of tile n-2
+      if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
+      const uint8_t* kb = stage0 + (size_t)s * STAGE_BYTES;
+      const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
+      const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
+#pragma unroll 1
+      for (int oo = 0; oo < OCT; ++oo) {
+        const int o = DQ_WARPS * oo + wd;
+        if (o >= n_oct) break;  // the same for the whole warp
+        const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
+        // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
+        const bool w2 = (bits == 2), w8 = (bits >= 5);
+        const uint32_t piece = w2 ? 8u : (w8 ? 32u : 16u);
+        // word (byte offset inside the piece) and byte selector of block m = 0..3 of a piece
+        //   2-bit: byte 2 (m % 2) + q / 2 of word m / 2;  4-bit: byte q of word m;  8-bit: bytes 2 (q % 2), + 1 of word 2 m + q / 2
+        const uint32_t wstep = w2 ? 2u : (w8 ? 8u : 4u);            // byte offset of block m's word = (m * wstep rounded down to 4) + wbase
+        const uint32_t wbase = w8 ? 4u * (uint32_t)(q >> 1) : 0u;
+        const uint32_t byte_e = w2 ? (uint32_t)(q >> 1) : (w8 ? 2u * (uint32_t)(q & 1) : (uint32_t)q);   // source byte that lands in the low half
+        const uint32_t hi_inc = w8 ? 1u : 0u;                                                              // the high half takes the next byte (8-bit) or the same one
+        const uint32_t sel_e = 0x4040u | byte_e | ((byte_e + hi_inc) << 8);
+        const uint32_t sel_o = w2 ? sel_e + 0x0202u : sel_e;       // 2-bit: odd blocks sit two bytes further in the same word
+        const uint32_t mask = w2 ? (((0xFF00u | (0x3u << (a2 + 2))) << 16) | (0xFF00u | (0x3u << a2))) : (w8 ? 0xFFFFFFFFu : 0xFFF0FF0Fu);
+        const uint32_t X2 = (bits == 3) ? 0x00800008u : (w8 ? 0x00800080u : 0u);   // two's-complement fields: flip the sign bit
+        // field offset still to subtract (times the field's position) and the position itself
+        const float blo = w2 ? (float)(2 << a2) : (w8 ? 128.f : 8.f), bhi = w2 ? (float)(2 << (a2 + 2)) : 128.f;
+        const float plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
+        const __half2 bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
+        const uint8_t* rowp = kb + off + wbase;
+        const float* scp = scales + d * ngrp;
+        const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[4];
+          const float scf = bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
+          const __half2 s2 = __floats2half2_rn(scf * plo, scf * phi);
+#pragma unroll
+          for (int m_ = 0; m_ < 4; ++m_) {
+            const uint32_t wo = ((uint32_t)m_ * wstep) & ~3u;
+            const uint32_t wv = *reinterpret_cast<const uint32_t*>(rowp + (uint32_t)c * piece + wo);
+            const uint32_t t = lop3<0x6A>(prmt(wv, 0x64646464u, (m_ & 1) ? sel_o : sel_e), mask, X2);
+            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2));
+          }
+          stmatrix_x4_trans(st_addr + (uint32_t)(4 * c) * 16u * 128u, r);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->ycnt[b], 1);
+      if (++s == STG) s = 0, fp ^= 1u;
+    }
+  } else if (warp < KEY_WARPS) {
+    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
+    set_regs<REG_KEY>();
+    constexpr int KCH = 16 / KEY_WARPS;  // chunks of 16 + 16 channels per key warp
+    const int wq = warp & 3, k0 = KCH * (warp >> 2), row = 32 * wq + lane;
+    const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
+    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
+    uint32_t cs_[KCH][8], sn_[KCH][8];
+#pragma unroll
+    for (int kk = 0; kk < KCH; ++kk)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+        sn_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
+      }
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
+      tc5::fence_after();
+#pragma unroll
+      for (int kk = 0; kk < KCH; ++kk) {
+        const int k = k0 + kk;
+        uint32_t dl[8], dh[8], out[16];
+        tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
+        tc5::ld16_pack(tk + 128 * b + 64 + 16 * k, dh);
+        tc5::wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __half2 klo = u32_as_h2(dl[i]), khi = u32_as_h2(dh[i]);
+          const __half2 c = u32_as_h2(cs_[kk][i]), sn = u32_as_h2(sn_[kk][i]);
+          out[i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+          out[8 + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+        }
+        tc5::st16(tk + 128 * b + 16 * k, out);
+      }
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
+    }
+  } else if (warp >= W_VAL && warp < W_DQ) {
+    // ===================== value warps: thread = channel, both 64-token halves of the tile =====================
+    set_regs<REG_VALUE>();
+    const int wq = warp & 3, ch = 32 * wq + lane;
+    constexpr int cc0 = 0, cc1 = 2;
+    const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
+      // the columns still feed U3 of tile n-2
+      if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
+      tc5::fence_after();
+      const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
+#pragma unroll
+      for (int cc = cc0; cc < cc1; ++cc) {
+        const uint4 cw = vc[cc * 128 + ch];
+        const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+          uint32_t out[16];
+#pragma unroll
+          for (int jj = 0; jj < 2; ++jj) {
+            const uint32_t wv = wd[2 * jp + jj];
+            const uint32_t x0 = wv & 0x33333333u, x1 = (wv >> 2) & 0x33333333u;
+#pragma unroll
+            for (int hs = 0; hs < 2; ++hs) {
+              const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
+              const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
+              const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
+              out[8 * jj + 2 * hs] = prmt(lo0, hi0, 0x5140u), out[8 * jj + 2 * hs + 1] = prmt(lo0, hi0, 0x7362u);
+              out[8 * jj + 4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), out[8 * jj + 4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);
+            }
+          }
+          tc5::st16(tv + 64 * b + 32 * cc + 16 * jp, out);
+        }
+      }
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
+      if (++s == STG) s = 0, fp ^= 1u;
+    }
+  } else if (warp >= W_SOFT && warp < W_VAL) {
+    // ===================== softmax warps: thread = token row =====================
+    // One set of four warps takes every tile: running (max, sum) and ONE output accumulator per range.  Scores, the
+    // weight buffer and the flags alternate by tile parity (U2 / U3 of neighbouring tiles overlap with this role).
+    set_regs<REG_SOFTMAX>();
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
+    float m[GQ], l[GQ], pn[GQ];
+#pragma unroll
+    for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
+    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
+    bool had = false, alive = true;
+
+    // Writes the partial record of the range that just ended.
+    auto flush = [&](int b_, int h_) {
+      float acc[GQ];
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
+      // U3s complete in issue order: the last tile's completion covers the whole range
+      if (had && alive && !wait_or_flag(&sh->odone[last_n & 1], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
+      if (had && alive) {
+        tc5::fence_after();
+        uint32_t r[GQ];
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+        tc5::wait_ld();
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
+        tc5::fence_before();
+      }
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) {
+        float a = l[qi], b2 = pn[qi];
+#pragma unroll
+        for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
+        if (lane == 0) sh->red[0][wq][qi] = a, sh->red[0][wq][GQ + qi] = b2;
+      }
+      named_bar(1, 128);
+      float* dst = p.part + ((blockIdx.x + (int64_t)b_ * h_kv + h_) * G) * PART_STRIDE;
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi)
+        if (qi < G) {
+          const float L = sh->red[0][0][qi] + sh->red[0][1][qi] + sh->red[0][2][qi] + sh->red[0][3][qi];
+          const float P = sh->red[0][0][GQ + qi] + sh->red[0][1][GQ + qi] + sh->red[0][2][GQ + qi] + sh->red[0][3][GQ + qi];
+          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
+          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
+        }
+      named_bar(1, 128);
+    };
+
+    int s = 0;
+    uint32_t fp = 0;
+    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch), s = (s + 1 == STG) ? 0 : s + 1, fp ^= (s == 0) ? 1u : 0u) {
+      const int n = w.it, e = n & 1;
+      if (w.seg != cur_seg) {
+        if (cur_seg >= 0) flush(cur_b, cur_h);
+        cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
+      }
+      const uint32_t par = (uint32_t)(n >> 1) & 1u;
+      const uint8_t* vblk = stage0 + (size_t)s * STAGE_BYTES + KB;
+      float sv[GQ];
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
+      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
+      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
+      if (alive) {
+        tc5::fence_after();
+        uint32_t r[GQ];
+        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
+        tc5::wait_ld();
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
+      }
+      // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
+      // below 2^8), nothing is reduced; the four warps only exchange one flag each.
+      bool need = false;
+#pragma unroll
+      for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
+      const bool wneed = __any_sync(0xffffffffu, need);
+      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
+      named_bar(1, 128);
+      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
+      const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
+      // the weight buffer of this parity still belongs to U3 of tile n-2
+      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
+      if (resc) {
+        float mnew[GQ];
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) {
+          float v = sv[qi];
+#pragma unroll
+          for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
+          if (lane == 0) sh->wmax[e][wq][qi] = v;
+        }
+        named_bar(1, 128);
+#pragma unroll
+        for (int qi = 0; qi < GQ; ++qi) {
+          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
+          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
+        }
+        // the accumulator is rescaled in place: U3 of tile n-1 must have finished with it (U3 of this tile waits for this
+        // role's arrival below)
+        if (alive && had && !wait_or_flag(&sh->odone[e ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 15)) alive = false;
+        if (alive) {
+          float f[GQ];
+#pragma unroll
+          for (int qi = 0; qi < GQ; ++qi) {
+            f[qi] = (m[qi] == -INFINITY) ? 0.f : ex2_approx(m[qi] - mnew[qi]);
+            l[qi] *= f[qi], pn[qi] *= f[qi], m[qi] = mnew[qi];
+          }
+          if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
+            tc5::fence_after();
+            uint32_t r[GQ];
+            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
+            tc5::wait_ld();
+#pragma unroll
+            for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
+            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
+            tc5::wait_st();
+          }
+        }
+      }
+      if (alive) {
+        const float norm = __half2float(reinterpret_cast<const __half*>(vblk + 128 * 32)[row]);
+        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * QB_BYTES) + (row >> 3) * 64 + (row & 7);
+#pragma unroll
+        for (int qi = 0; qi < GQ; qi += 2) {
+          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
+          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
+          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
+          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
+        }
+        fence_proxy_async();
+        tc5::fence_before();
+        __syncwarp();
+        if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
+      }
+      had = true, last_n = n;
+    }
+    flush(cur_b, cur_h);
+  } else {
     set_regs<REG_SERVICE>();  // the four service warps, as one group
     if (warp == SVC0) {
       // ===================== copy + U3 warp =====================
@@ -377,308 +679,6 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           }
         }
       }
-    }
-  } else if (warp < KEY_WARPS) {
-    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
-    set_regs<REG_KEY>();
-    constexpr int KCH = 16 / KEY_WARPS;  // chunks of 16 + 16 channels per key warp
-    const int wq = warp & 3, k0 = KCH * (warp >> 2), row = 32 * wq + lane;
-    const uint32_t tk = tmem + TM_KD + ((uint32_t)(32 * wq) << 16);
-    // rotation by this token's offset inside the tile, for rotary pairs 16k .. 16k+15 of both chunks
-    uint32_t cs_[KCH][8], sn_[KCH][8];
-#pragma unroll
-    for (int kk = 0; kk < KCH; ++kk)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        cs_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_cos + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
-        sn_[kk][i] = *reinterpret_cast<const uint32_t*>(p.rope_sin + (int64_t)row * HEAD_DIM + 16 * (k0 + kk) + 2 * i);
-      }
-    for (int n = 0; n < n_tiles; ++n) {
-      const int b = n & 1;
-      if (!wait_or_flag(&sh->low[b], (uint32_t)(n >> 1) & 1u, p.status, 6)) break;
-      tc5::fence_after();
-#pragma unroll
-      for (int kk = 0; kk < KCH; ++kk) {
-        const int k = k0 + kk;
-        uint32_t dl[8], dh[8], out[16];
-        tc5::ld16_pack(tk + 128 * b + 16 * k, dl);
-        tc5::ld16_pack(tk + 128 * b + 64 + 16 * k, dh);
-        tc5::wait_ld();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const __half2 klo = u32_as_h2(dl[i]), khi = u32_as_h2(dh[i]);
-          const __half2 c = u32_as_h2(cs_[kk][i]), sn = u32_as_h2(sn_[kk][i]);
-          out[i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
-          out[8 + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
-        }
-        tc5::st16(tk + 128 * b + 16 * k, out);
-      }
-      tc5::wait_st();
-      tc5::fence_before();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
-    }
-  } else if (warp < W_VAL) {
-    // ===================== softmax warps: thread = token row =====================
-    // One set of four warps takes every tile: running (max, sum) and ONE output accumulator per range.  Scores, the
-    // weight buffer and the flags alternate by tile parity (U2 / U3 of neighbouring tiles overlap with this role).
-    set_regs<REG_SOFTMAX>();
-    const int wq = warp & 3, row = 32 * wq + lane;
-    const uint32_t tl = tmem + ((uint32_t)(32 * wq) << 16);
-    float m[GQ], l[GQ], pn[GQ];
-#pragma unroll
-    for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-    int cur_seg = -1, cur_b = 0, cur_h = 0, last_n = -1;
-    bool had = false, alive = true;
-
-    // Writes the partial record of the range that just ended.
-    auto flush = [&](int b_, int h_) {
-      float acc[GQ];
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) acc[qi] = 0.f;
-      // U3s complete in issue order: the last tile's completion covers the whole range
-      if (had && alive && !wait_or_flag(&sh->odone[last_n & 1], (uint32_t)(last_n >> 1) & 1u, p.status, 9)) alive = false;
-      if (had && alive) {
-        tc5::fence_after();
-        uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
-        tc5::wait_ld();
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) acc[qi] = __uint_as_float(r[qi]);
-        tc5::fence_before();
-      }
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) {
-        float a = l[qi], b2 = pn[qi];
-#pragma unroll
-        for (int mk = 16; mk >= 1; mk >>= 1) a += __shfl_xor_sync(0xffffffffu, a, mk), b2 += __shfl_xor_sync(0xffffffffu, b2, mk);
-        if (lane == 0) sh->red[0][wq][qi] = a, sh->red[0][wq][GQ + qi] = b2;
-      }
-      named_bar(1, 128);
-      float* dst = p.part + ((blockIdx.x + (int64_t)b_ * h_kv + h_) * G) * PART_STRIDE;
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi)
-        if (qi < G) {
-          const float L = sh->red[0][0][qi] + sh->red[0][1][qi] + sh->red[0][2][qi] + sh->red[0][3][qi];
-          const float P = sh->red[0][0][GQ + qi] + sh->red[0][1][GQ + qi] + sh->red[0][2][GQ + qi] + sh->red[0][3][GQ + qi];
-          dst[qi * PART_STRIDE + 2 + row] = had ? p.lut_alpha * P + p.lut_beta * acc[qi] : 0.f;
-          if (row == 0) dst[qi * PART_STRIDE] = had ? m[qi] : -INFINITY, dst[qi * PART_STRIDE + 1] = had ? L : 0.f;
-        }
-      named_bar(1, 128);
-    };
-
-    int s = 0;
-    uint32_t fp = 0;
-    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch), s = (s + 1 == STG) ? 0 : s + 1, fp ^= (s == 0) ? 1u : 0u) {
-      const int n = w.it, e = n & 1;
-      if (w.seg != cur_seg) {
-        if (cur_seg >= 0) flush(cur_b, cur_h);
-        cur_seg = w.seg, cur_b = w.cur.b, cur_h = w.cur.h, had = false;
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) m[qi] = -INFINITY, l[qi] = 0.f, pn[qi] = 0.f;
-      }
-      const uint32_t par = (uint32_t)(n >> 1) & 1u;
-      const uint8_t* vblk = stage0 + (size_t)s * STAGE_BYTES + KB;
-      float sv[GQ];
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) sv[qi] = -INFINITY;
-      if (alive && !wait_or_flag(&sh->full[s], fp, p.status, 12)) alive = false;
-      if (alive && !wait_or_flag(&sh->sdone[e], par, p.status, 7)) alive = false;
-      if (alive) {
-        tc5::fence_after();
-        uint32_t r[GQ];
-        if constexpr (GQ == 4) tc5::ld4(tl + TM_S + 16 * e, r); else tc5::ld8(tl + TM_S + 16 * e, r);
-        tc5::wait_ld();
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) sv[qi] = __uint_as_float(r[qi]);
-      }
-      // Lazy maximum: as long as no score of the tile exceeds the running maximum by more than 8 (weights
-      // below 2^8), nothing is reduced; the four warps only exchange one flag each.
-      bool need = false;
-#pragma unroll
-      for (int qi = 0; qi < GQ; ++qi) need |= (qi < G) && (sv[qi] > m[qi] + 8.f);
-      const bool wneed = __any_sync(0xffffffffu, need);
-      if (lane == 0) sh->flag[e][wq] = wneed ? 1 : 0;
-      named_bar(1, 128);
-      const int4 fl = *reinterpret_cast<const int4*>(sh->flag[e]);
-      const bool resc = (fl.x | fl.y | fl.z | fl.w) != 0;
-      // the weight buffer of this parity still belongs to U3 of tile n-2
-      if (alive && n >= 2 && !wait_or_flag(&sh->odone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 8)) alive = false;
-      if (resc) {
-        float mnew[GQ];
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) {
-          float v = sv[qi];
-#pragma unroll
-          for (int mk = 16; mk >= 1; mk >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mk));
-          if (lane == 0) sh->wmax[e][wq][qi] = v;
-        }
-        named_bar(1, 128);
-#pragma unroll
-        for (int qi = 0; qi < GQ; ++qi) {
-          const float tm = fmaxf(fmaxf(sh->wmax[e][0][qi], sh->wmax[e][1][qi]), fmaxf(sh->wmax[e][2][qi], sh->wmax[e][3][qi]));
-          mnew[qi] = (qi < G && tm > m[qi] + 8.f) ? tm : m[qi];
-        }
-        // the accumulator is rescaled in place: U3 of tile n-1 must have finished with it (U3 of this tile waits for this
-        // role's arrival below)
-        if (alive && had && !wait_or_flag(&sh->odone[e ^ 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 15)) alive = false;
-        if (alive) {
-          float f[GQ];
-#pragma unroll
-          for (int qi = 0; qi < GQ; ++qi) {
-            f[qi] = (m[qi] == -INFINITY) ? 0.f : ex2_approx(m[qi] - mnew[qi]);
-            l[qi] *= f[qi], pn[qi] *= f[qi], m[qi] = mnew[qi];
-          }
-          if (had) {  // this thread's TMEM lane is channel `row` of the accumulator
-            tc5::fence_after();
-            uint32_t r[GQ];
-            if constexpr (GQ == 4) tc5::ld4(tl + TM_O, r); else tc5::ld8(tl + TM_O, r);
-            tc5::wait_ld();
-#pragma unroll
-            for (int qi = 0; qi < GQ; ++qi) r[qi] = __float_as_uint(__uint_as_float(r[qi]) * f[qi]);
-            if constexpr (GQ == 4) tc5::st4(tl + TM_O, r); else tc5::st8(tl + TM_O, r);
-            tc5::wait_st();
-          }
-        }
-      }
-      if (alive) {
-        const float norm = __half2float(reinterpret_cast<const __half*>(vblk + 128 * 32)[row]);
-        __half* pb = reinterpret_cast<__half*>(pbuf0 + (size_t)e * QB_BYTES) + (row >> 3) * 64 + (row & 7);
-#pragma unroll
-        for (int qi = 0; qi < GQ; qi += 2) {
-          const float p0 = ex2_approx(sv[qi] - m[qi]), p1 = ex2_approx(sv[qi + 1] - m[qi + 1]);
-          const __half2 hw = __floats2half2_rn(p0 * norm, p1 * norm);
-          if (qi < G) l[qi] += p0, pn[qi] += __low2float(hw), pb[qi * 8] = __low2half(hw);
-          if (qi + 1 < G) l[qi + 1] += p1, pn[qi + 1] += __high2float(hw), pb[(qi + 1) * 8] = __high2half(hw);
-        }
-        fence_proxy_async();
-        tc5::fence_before();
-        __syncwarp();
-        if (lane == 0) smem_add_release(&sh->pcnt[e], 1);
-      }
-      had = true, last_n = n;
-    }
-    flush(cur_b, cur_h);
-  } else if (warp < W_DQ) {
-    // ===================== value warps: thread = channel, both 64-token halves of the tile =====================
-    set_regs<REG_VALUE>();
-    const int wq = warp & 3, ch = 32 * wq + lane;
-    constexpr int cc0 = 0, cc1 = 2;
-    const uint32_t tv = tmem + TM_V + ((uint32_t)(32 * wq) << 16);
-    int s = 0;
-    uint32_t fp = 0;
-    for (int n = 0; n < n_tiles; ++n) {
-      const int b = n & 1;
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 10)) break;
-      // the columns still feed U3 of tile n-2
-      if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
-      tc5::fence_after();
-      const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
-#pragma unroll
-      for (int cc = cc0; cc < cc1; ++cc) {
-        const uint4 cw = vc[cc * 128 + ch];
-        const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-        for (int jp = 0; jp < 2; ++jp) {
-          uint32_t out[16];
-#pragma unroll
-          for (int jj = 0; jj < 2; ++jj) {
-            const uint32_t wv = wd[2 * jp + jj];
-            const uint32_t x0 = wv & 0x33333333u, x1 = (wv >> 2) & 0x33333333u;
-#pragma unroll
-            for (int hs = 0; hs < 2; ++hs) {
-              const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
-              const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
-              const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
-              out[8 * jj + 2 * hs] = prmt(lo0, hi0, 0x5140u), out[8 * jj + 2 * hs + 1] = prmt(lo0, hi0, 0x7362u);
-              out[8 * jj + 4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), out[8 * jj + 4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);
-            }
-          }
-          tc5::st16(tv + 64 * b + 32 * cc + 16 * jp, out);
-        }
-      }
-      tc5::wait_st();
-      tc5::fence_before();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->vcnt[b], 1);
-      if (++s == STG) s = 0, fp ^= 1u;
-    }
-  } else {
-    // ===================== dequant warps: tier codes -> fp16 Y_hat, the A operand of U1 =====================
-    // Warp wd takes the direction octets wd, wd + DQ_WARPS, ... (positions in tier order).  Lane = (direction
-    // lane / 4 of the octet, token pair q = lane % 4): for every 8-token block B it produces the half2 of tokens
-    // 8B + 2q, 8B + 2q + 1 of its direction, which is exactly what a transposed stmatrix wants from it.  Four
-    // blocks (32 tokens, one 8 / 16 / 32-byte piece of the direction's row) go out per stmatrix.
-    // A half2 costs four instructions whatever the tier: a byte permute drops the thread's code byte(s) under the
-    // fp16 exponent of 1024 in both halves, one LOP3 masks each half down to its field and flips two's-complement
-    // sign bits, an exact subtraction removes 1024 and the field's offset (times the field's position in the byte),
-    // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
-    // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
-    // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
-    set_regs<REG_DEQUANT>();
-    constexpr int OCT = 16 / DQ_WARPS;
-    const int wd = warp - W_DQ, q = lane & 3, dsub = lane >> 2;
-    const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
-    const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
-    const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
-    int s = 0;
-    uint32_t fp = 0;
-    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
-      const int n = w.it, b = n & 1, h = w.cur.h;
-      int meta[OCT];
-#pragma unroll
-      for (int oo = 0; oo < OCT; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (DQ_WARPS * oo + wd) + dsub);
-      const int n_oct = 2 * (((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1);  // octets that U1 reads for this head
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
-      // the buffer still feeds U1 of tile n-2
-      if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
-      const uint8_t* kb = stage0 + (size_t)s * STAGE_BYTES;
-      const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
-      const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
-#pragma unroll 1
-      for (int oo = 0; oo < OCT; ++oo) {
-        const int o = DQ_WARPS * oo + wd;
-        if (o >= n_oct) break;  // the same for the whole warp
-        const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
-        // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
-        const bool w2 = (bits == 2), w8 = (bits >= 5);
-        const uint32_t piece = w2 ? 8u : (w8 ? 32u : 16u);
-        // word (byte offset inside the piece) and byte selector of block m = 0..3 of a piece
-        //   2-bit: byte 2 (m % 2) + q / 2 of word m / 2;  4-bit: byte q of word m;  8-bit: bytes 2 (q % 2), + 1 of word 2 m + q / 2
-        const uint32_t wstep = w2 ? 2u : (w8 ? 8u : 4u);            // byte offset of block m's word = (m * wstep rounded down to 4) + wbase
-        const uint32_t wbase = w8 ? 4u * (uint32_t)(q >> 1) : 0u;
-        const uint32_t byte_e = w2 ? (uint32_t)(q >> 1) : (w8 ? 2u * (uint32_t)(q & 1) : (uint32_t)q);   // source byte that lands in the low half
-        const uint32_t hi_inc = w8 ? 1u : 0u;                                                              // the high half takes the next byte (8-bit) or the same one
-        const uint32_t sel_e = 0x4040u | byte_e | ((byte_e + hi_inc) << 8);
-        const uint32_t sel_o = w2 ? sel_e + 0x0202u : sel_e;       // 2-bit: odd blocks sit two bytes further in the same word
-        const uint32_t mask = w2 ? (((0xFF00u | (0x3u << (a2 + 2))) << 16) | (0xFF00u | (0x3u << a2))) : (w8 ? 0xFFFFFFFFu : 0xFFF0FF0Fu);
-        const uint32_t X2 = (bits == 3) ? 0x00800008u : (w8 ? 0x00800080u : 0u);   // two's-complement fields: flip the sign bit
-        // field offset still to subtract (times the field's position) and the position itself
-        const float blo = w2 ? (float)(2 << a2) : (w8 ? 128.f : 8.f), bhi = w2 ? (float)(2 << (a2 + 2)) : 128.f;
-        const float plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
-        const __half2 bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
-        const uint8_t* rowp = kb + off + wbase;
-        const float* scp = scales + d * ngrp;
-        const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[4];
-          const float scf = bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
-          const __half2 s2 = __floats2half2_rn(scf * plo, scf * phi);
-#pragma unroll
-          for (int m_ = 0; m_ < 4; ++m_) {
-            const uint32_t wo = ((uint32_t)m_ * wstep) & ~3u;
-            const uint32_t wv = *reinterpret_cast<const uint32_t*>(rowp + (uint32_t)c * piece + wo);
-            const uint32_t t = lop3<0x6A>(prmt(wv, 0x64646464u, (m_ & 1) ? sel_o : sel_e), mask, X2);
-            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2));
-          }
-          stmatrix_x4_trans(st_addr + (uint32_t)(4 * c) * 16u * 128u, r);
-        }
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->ycnt[b], 1);
-      if (++s == STG) s = 0, fp ^= 1u;
     }
   }
 
