@@ -96,6 +96,12 @@ _SIGNATURES = {
                                       c_int, c_void_p, c_void_p, c_float, c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_int,
                                       c_void_p]),
     "bmxk_merge_partials": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "bmxk_xchg_bytes": (c_size_t, [c_int, c_int]),
+    "bmxk_xchg_alloc": (c_int, [c_int, c_int, POINTER(c_void_p), c_void_p]),
+    "bmxk_xchg_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "bmxk_xchg_close": (c_int, [c_void_p]),
+    "bmxk_xchg_free": (c_int, [c_void_p]),
+    "bmxk_xchg_merge": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(c_void_p), c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "bmxk_window_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "bmxk_window_append_devpos": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,

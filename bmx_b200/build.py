@@ -27,6 +27,7 @@ SOURCES = [
     ("spectral.cu", ["-fmad=false"]),
     ("spectral_decode_t5.cu", []),
     ("value_blocks.cu", ["-fmad=false"]),
+    ("xchg.cu", []),
 ]
 
 

@@ -5,9 +5,12 @@ Two partitions, as the path allows:
     ever talks to another during a step (`shard_range`).
   * One long sequence: rank r owns a contiguous run of pages (`split_pages`), the last rank also owns
     the fp16 window; every rank produces the un-normalised state (max, sum, accumulator) of its part
-    and ONE small all-gather (heads x 130 floats per rank) precedes the merge, which is bmx's split
+    and ONE small exchange (heads x 130 floats per rank) precedes the merge, which is bmx's split
     merge formula applied across ranks (bmx: src/bmx/cache/triton_dequant_attention.py:409-461).
-Every kernel reads only its own GPU's memory; the gathered partials land in a local buffer first.
+    The exchange is either an NCCL all-gather followed by the merge kernel (`exchange="nccl"`) or one
+    kernel per rank that stores the state into every rank's buffer over NVLink, flags, waits and merges
+    (`exchange="p2p"`, PeerExchange: no library collective in the step).
+Every kernel LOADS only from its own GPU's memory; what crosses NVLink is stored into the peer's buffer.
 """
 
 from __future__ import annotations
@@ -38,6 +41,80 @@ def gather_partials(part: torch.Tensor, group=None) -> torch.Tensor:
     return out.view(world, *part.shape)
 
 
+class PeerExchange:
+    """This rank's exchange buffer plus the mappings of every other rank's (CUDA IPC, one node), for
+    bmxk_xchg_merge.  Set-up is collective over `group` (one all-gather of the 64-byte handles); a step is not."""
+
+    WAIT_LIMIT_CYCLES = 4_000_000_000  # ~2 s: a rank that never arrives ends the wait with a status word, not a hang
+
+    def __init__(self, rows: int, device, group=None):
+        import ctypes
+
+        from ._lib import call, lib
+
+        self.rows, self.group, self.device = rows, group, torch.device(device)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if dist.get_backend(group) != "nccl":
+            raise RuntimeError("PeerExchange maps GPU memory between the ranks of one node: it needs the nccl backend (one rank per GPU)")
+        lib()
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            call("bmxk_xchg_alloc", rows, self.world, ctypes.byref(own), handle)
+            mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=self.device)
+            everyone = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
+            dist.all_gather_into_tensor(everyone, mine, group=group)
+            handles = everyone.cpu().view(self.world, 64)
+            self._own, self._peers = own.value, {}
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(own.value)
+                    continue
+                peer = ctypes.c_void_p()
+                call("bmxk_xchg_open", bytes(handles[r].tolist()), ctypes.byref(peer))
+                self._peers[r] = peer.value
+                ptrs.append(peer.value)
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.step = 0
+        dist.barrier(group=group)  # nobody pushes into a buffer that is not mapped everywhere yet
+
+    def merge(self, part: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """part: this rank's (rows, 130) float32 state -> merged, normalised (rows, 128).  Every rank calls it once per
+        step, in the same order; asynchronous on the current stream."""
+        from . import kernels as K
+        from ._lib import call
+
+        assert part.is_cuda and part.dtype == torch.float32 and part.shape == (self.rows, PART_STRIDE) and part.is_contiguous()
+        if out is None:
+            out = torch.empty(self.rows, K.HEAD_DIM, dtype=torch.float16, device=part.device)
+        self.step += 1
+        call("bmxk_xchg_merge", part.data_ptr(), self.rows, self.rank, self.world, self._ptrs, self.step, self.WAIT_LIMIT_CYCLES,
+             self.status.data_ptr(), out.data_ptr(), K._dtype_code(out), torch.cuda.current_stream().cuda_stream)
+        return out
+
+    def check(self) -> None:
+        """Synchronises and raises if a wait of an earlier step ran out (names the rank that never arrived)."""
+        st = self.status.cpu().tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"peer exchange: block {st[1]} gave up waiting for rank {st[2] - 32} (step {self.step})")
+
+    def close(self) -> None:
+        """Unmaps the peers and frees the own buffer; collective (a barrier first: nobody frees what others still write)."""
+        from ._lib import call
+
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for ptr in self._peers.values():
+                call("bmxk_xchg_close", ptr)
+            dist.barrier(group=self.group)
+            call("bmxk_xchg_free", self._own)
+        self._own, self._peers = None, {}
+
+
 class SequenceSplitDecoder:
     """Decode step of one long sequence whose committed pages are split across the ranks of `group`.
 
@@ -45,15 +122,23 @@ class SequenceSplitDecoder:
     `first_page` is the index of its first page in the whole sequence, which fixes the rotary positions.
     """
 
-    def __init__(self, state, first_page: int, group=None):
+    def __init__(self, state, first_page: int, group=None, exchange: str = "nccl"):
+        assert exchange in ("nccl", "p2p")
         self.state, self.first_page, self.group = state, first_page, group
         rows = state.batch * state.geom.h_kv * (getattr(state, "n_q_groups", None) or state.geom.n_q_groups)
         self.part = torch.empty(rows, PART_STRIDE, dtype=torch.float32, device=state.device)
+        self.peers = PeerExchange(rows, state.device, group) if exchange == "p2p" else None
 
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         from . import kernels as K
 
         st = self.state  # a K2bLayerState or a SpectralLayerState: same call
         st.decode(q, partial_out=self.part, pos_offset=self.first_page * st.page)
+        if self.peers is not None:
+            return self.peers.merge(self.part, out=out)
         gathered = gather_partials(self.part, self.group)
         return K.merge_partials(gathered, out=out)
+
+    def close(self) -> None:
+        if self.peers is not None:
+            self.peers.close()

@@ -298,6 +298,25 @@ int bmxk_spectral_decode(const bmxk_spectral_geom* g, int n_q_groups, const void
  * max carried in log2 units). */
 int bmxk_merge_partials(const float* parts, int n_parts, int rows, void* out, int out_dtype, void* stream);
 
+/* The same merge across the GPUs of one node without a library collective (bmx has no multi-GPU path; the formula is
+ * the split merge above).  Each rank owns an exchange buffer that every other rank maps (CUDA IPC); one kernel per
+ * rank and step stores the rank's (rows, 130) state into its slot of EVERY rank's buffer (peer stores over NVLink),
+ * raises a flag there, waits -- bounded by wait_limit_cycles -- until all ranks' flags of this step stand in its own
+ * buffer, and merges from local memory into out (rows, 128).  No kernel loads from a peer and nothing is multicast.
+ *   bmxk_xchg_alloc   allocates and zeroes this rank's buffer (cudaMalloc) and returns its 64-byte IPC handle;
+ *   bmxk_xchg_open    maps a peer's buffer from its handle;  bmxk_xchg_close / bmxk_xchg_free undo the two.
+ *   bmxk_xchg_merge   buffers: HOST array of `world` device pointers (index = rank, this rank's own included);
+ *                     step: 1, 2, 3, ... the same on every rank, one call per step per rank, in order;
+ *                     status: int32[4] in this rank's device memory, zero; a wait that runs out writes
+ *                     {1, block, 32 + the rank that never arrived} there and the kernel returns without a result. */
+size_t bmxk_xchg_bytes(int rows, int world);
+int bmxk_xchg_alloc(int rows, int world, void** buffer, void* ipc_handle_64);
+int bmxk_xchg_open(const void* ipc_handle_64, void** peer_buffer);
+int bmxk_xchg_close(void* peer_buffer);
+int bmxk_xchg_free(void* buffer);
+int bmxk_xchg_merge(const float* part, int rows, int rank, int world, void* const* buffers, int step, int64_t wait_limit_cycles,
+                    int32_t* status, void* out, int out_dtype, void* stream);
+
 /* ---- recent window ------------------------------------------------------------------------ */
 /* One decode step's new token into the fp16 window that precedes quantization.
  * bmx: src/bmx/cache/packed_streaming.py:582-628 (PackedStreamingLayer.update: the torch.cat of the new token

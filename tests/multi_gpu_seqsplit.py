@@ -1,5 +1,7 @@
 """Run under torchrun (one rank per GPU): a single sequence's pages split across ranks, partial states
-all-gathered over NCCL and merged, against the same sequence decoded whole on rank 0.
+exchanged (an NCCL all-gather + merge kernel, and the one-kernel peer exchange) and merged, against the same
+sequence decoded whole on rank 0; then a step that one rank skips, which must end the others' bounded wait with a
+status word and leave the GPUs usable.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29531 \
         tests/multi_gpu_seqsplit.py
@@ -56,15 +58,50 @@ def main():
         return st
 
     first, count = split_pages(n_pages, world)[rank]
-    dec = SequenceSplitDecoder(make_state(first, count, rank == world - 1), first)
-    out = dec.decode(q).float()
-    torch.cuda.synchronize()
+    state = make_state(first, count, rank == world - 1)
+    whole = make_state(0, n_pages, True) if rank == 0 else None
     ok = True
+    for exchange in ("nccl", "p2p"):
+        dec = SequenceSplitDecoder(state, first, exchange=exchange)
+        for step in range(5):  # several steps: the exchange buffers alternate by step parity
+            qs = (q.float() * (1.0 + 0.1 * step)).half()
+            out = dec.decode(qs).float()
+            torch.cuda.synchronize()
+            if dec.peers is not None:
+                dec.peers.check()
+            if rank == 0:
+                ref = whole.decode(qs).float().view(-1, D)
+                err = (out - ref).abs().amax(-1) / ref.abs().amax(-1)
+                ok = ok and bool((err <= 2e-3).all())
+                if step in (0, 4):
+                    print(f"seqsplit world={world} {exchange} step {step}: worst relative error vs single-GPU decode {float(err.max()):.3e}")
+        dec.close()
+    # ---- one rank skips a step: the others' wait must run out (1 ms limit here), say who was missing, and return ----
+    from bmx_b200.dist import PeerExchange
+
+    px = PeerExchange(h_kv * G, dev)
+    px.WAIT_LIMIT_CYCLES = 2_000_000
+    part = torch.zeros(h_kv * G, 130, device=dev)
+    part[:, 1] = 1.0
+    px.merge(part)
+    torch.cuda.synchronize()
+    px.check()  # a complete step first
+    if rank != world - 1:
+        px.merge(part)  # the last rank never makes this call
+        torch.cuda.synchronize()
+        st = px.status.cpu().tolist()
+        gave_up = st[0] == 1 and st[2] == 32 + (world - 1)
+        ok = ok and gave_up
+        if rank == 0:
+            print(f"skipped step: status {st[:3]} -> {'the wait named the missing rank' if gave_up else 'UNEXPECTED'}")
+        # the context is still usable
+        ok = ok and bool(torch.isfinite(state.decode(q, partial_out=None).float()).all())
+    px.close()
     if rank == 0:
-        whole = make_state(0, n_pages, True).decode(q).float().view(-1, D)
-        err = (out - whole).abs().amax(-1) / whole.abs().amax(-1)
-        ok = bool((err <= 2e-3).all())
-        print(f"seqsplit world={world}: worst relative error vs single-GPU decode {float(err.max()):.3e} -> {'OK' if ok else 'FAIL'}")
+        print("seqsplit", "OK" if ok else "FAIL")
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ok = bool(flag.item())
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
 
