@@ -625,7 +625,7 @@ def config_seq_split(device, rank, world, dist) -> dict:
         st.tail_len = W
         st.tail_len_dev.fill_(W)
     out = torch.empty(H_KV * G, D, dtype=torch.float32, device=device)
-    res = {"workload": "k2b decode, one sequence of 131072 tokens + 128-token window, pages split across the ranks, one all-gather "
+    res = {"workload": "k2b decode, one sequence of 131072 tokens + 128-token window, pages split across the ranks, one exchange "
                        "of (32 x 130) floats per rank, merge on every rank", "pages_per_rank": count}
     if world == 1:
         o1 = torch.empty(1, H_KV * G, D, dtype=torch.float32, device=device)
