@@ -641,14 +641,24 @@ def config_seq_split(device, rank, world, dist) -> dict:
     step_us = _event_us(lambda: dec.decode(q, out=out), 100)
     kern_us = _event_us(lambda: st.decode(q, partial_out=dec.part, pos_offset=first * PAGE, phases=1), 100)
     K.check_status(st.workspace)
-    # the same step with the one-kernel peer exchange instead of the all-gather + merge kernel
-    dec_p = SequenceSplitDecoder(st, first, exchange="p2p")
-    out_p = torch.empty_like(out)
-    dist.barrier()
-    p2p_us = _event_us(lambda: dec_p.decode(q, out=out_p), 100)
-    dec_p.peers.check()
-    dec_p.close()
-    t = torch.tensor([step_us, kern_us, p2p_us], dtype=torch.float64, device=device)
+    # the same step with the one-kernel peer exchange instead of the all-gather + merge kernel (its set-up raises on every
+    # rank together if CUDA IPC is not available between the ranks; the NCCL figures stand in then)
+    out_p, p2p_error = torch.empty_like(out), None
+    try:
+        dec_p = SequenceSplitDecoder(st, first, exchange="p2p")
+    except RuntimeError as e:
+        dec_p, p2p_error, p2p_us, p2p_graph_us = None, str(e), step_us, step_us
+        out_p.copy_(out)
+    if dec_p is not None:
+        dist.barrier()
+        p2p_us = _event_us(lambda: dec_p.decode(q, out=out_p), 100)
+        dec_p.peers.check()
+        graph = dec_p.capture(q, out_p)  # the three launches of a step replayed as one graph
+        dist.barrier()
+        p2p_graph_us = _event_us(lambda: dec_p.replay(graph), 100)
+        dec_p.peers.check()
+        dec_p.close()
+    t = torch.tensor([step_us, kern_us, p2p_us, p2p_graph_us], dtype=torch.float64, device=device)
     allt = [torch.zeros_like(t) for _ in range(world)]
     dist.all_gather(allt, t)
     allt = torch.stack(allt)
@@ -675,12 +685,14 @@ def config_seq_split(device, rank, world, dist) -> dict:
     algo_rank = count * PAGE * H_KV * BYTES_PER_UNIT
     peak, _ = measured_peak_gbs()
     res.update(us_per_layer_step=float(allt[:, 2].max()), per_rank_step_us=allt[:, 2].tolist(),
+               us_per_layer_step_graph=float(allt[:, 3].max()),
                us_per_layer_step_nccl=float(allt[:, 0].max()), per_rank_step_us_nccl=allt[:, 0].tolist(), per_rank_kernel_us=allt[:, 1].tolist(),
                per_rank_achieved_GBps=[algo_rank / u / 1e3 for u in allt[:, 1].tolist()],
                frac_of_hbm_peak_per_rank=algo_rank / float(allt[:, 1].max()) / 1e3 / peak,
                collective="one kernel per rank: 32 x 130 float32 stored into every rank's buffer over NVLink, flag, bounded wait, merge "
-                          "(us_per_layer_step); NCCL all_gather_into_tensor + merge kernel (us_per_layer_step_nccl)",
-               max_rel_err_vs_single_gpu=max_rel)
+                          "(us_per_layer_step; _graph: the step's three launches replayed as one CUDA graph); NCCL all_gather_into_tensor + "
+                          "merge kernel (us_per_layer_step_nccl)",
+               max_rel_err_vs_single_gpu=max_rel, peer_exchange_error=p2p_error)
     return res
 
 

@@ -42,8 +42,9 @@ struct XchgParams {
 
 __host__ __device__ inline size_t xchg_data_floats(int rows, int world) { return (size_t)2 * world * rows * PART_STRIDE; }
 __host__ __device__ inline size_t xchg_flag_off(int rows, int world) { return (xchg_data_floats(rows, world) * sizeof(float) + 127) / 128 * 128; }
-// flags: int32 [2][XCHG_MAX_WORLD], then the local block counters int32 [2]
-__host__ __device__ inline size_t xchg_total_bytes(int rows, int world) { return xchg_flag_off(rows, world) + (2 * XCHG_MAX_WORLD + 2) * sizeof(int32_t) + 120; }
+// flags: int32 [2][XCHG_MAX_WORLD], then local words: the push counters int32 [2], the count of blocks that have ended,
+// and the number of the last step this rank completed
+__host__ __device__ inline size_t xchg_total_bytes(int rows, int world) { return xchg_flag_off(rows, world) + (2 * XCHG_MAX_WORLD + 4) * sizeof(int32_t) + 112; }
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
@@ -54,10 +55,16 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
 
 __global__ void __launch_bounds__(XCHG_THREADS) xchg_merge_kernel(const XchgParams p) {
   __shared__ int ok_sm;
-  const int parity = p.step & 1, t = threadIdx.x;
+  const int t = threadIdx.x;
   const size_t slot = (size_t)p.rows * PART_STRIDE;
   uint8_t* own = p.bufs[p.rank];
   int32_t* own_flags = reinterpret_cast<int32_t*>(own + xchg_flag_off(p.rows, p.world));
+  int32_t* ended = own_flags + 2 * XCHG_MAX_WORLD + 2;
+  int32_t* last_step = own_flags + 2 * XCHG_MAX_WORLD + 3;
+  // step 0 = "the step after the last one this rank completed", kept in the buffer: a launch without a per-step
+  // argument, which a CUDA graph can replay
+  const int step = p.step > 0 ? p.step : *reinterpret_cast<volatile int32_t*>(last_step) + 1;
+  const int parity = step & 1;
   int32_t* counter = own_flags + 2 * XCHG_MAX_WORLD + parity;
   if (t == 0) ok_sm = 1;
 
@@ -81,7 +88,7 @@ __global__ void __launch_bounds__(XCHG_THREADS) xchg_merge_kernel(const XchgPara
       *counter = 0;  // next used two steps from now, after this kernel has ended
       __threadfence_system();
       for (int r = 0; r < p.world; ++r)
-        st_release_sys(reinterpret_cast<int32_t*>(p.bufs[r] + xchg_flag_off(p.rows, p.world)) + parity * XCHG_MAX_WORLD + p.rank, p.step);
+        st_release_sys(reinterpret_cast<int32_t*>(p.bufs[r] + xchg_flag_off(p.rows, p.world)) + parity * XCHG_MAX_WORLD + p.rank, step);
     }
   }
   // ---- wait: all ranks' flags in my own buffer ----
@@ -89,7 +96,7 @@ __global__ void __launch_bounds__(XCHG_THREADS) xchg_merge_kernel(const XchgPara
     const int32_t* f = own_flags + parity * XCHG_MAX_WORLD + t;
     const long long t0 = clock64();
     bool ok = true;
-    for (uint32_t spin = 1; ld_acquire_sys(f) != p.step; ++spin) {
+    for (uint32_t spin = 1; ld_acquire_sys(f) != step; ++spin) {
       if ((spin & 63u) == 0u) {
         if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) { ok = false; break; }
         if (clock64() - t0 > p.limit) {
@@ -102,7 +109,7 @@ __global__ void __launch_bounds__(XCHG_THREADS) xchg_merge_kernel(const XchgPara
     if (!ok) ok_sm = 0;
   }
   __syncthreads();
-  if (!ok_sm) return;
+  if (!ok_sm) return;  // the step counter stays where it was: the exchange is out of step from here on
   // ---- merge: my rows over all ranks' states, from local memory ----
   const float* base = reinterpret_cast<const float*>(own) + (size_t)parity * p.world * slot;
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
@@ -122,6 +129,11 @@ __global__ void __launch_bounds__(XCHG_THREADS) xchg_merge_kernel(const XchgPara
       reinterpret_cast<float*>(p.out)[(size_t)row * HEAD_DIM + t] = res;
     else
       reinterpret_cast<__half*>(p.out)[(size_t)row * HEAD_DIM + t] = __float2half_rn(res);
+  }
+  // ---- the last block to end records the step (every block has read the old value by now) ----
+  if (t == 0 && atomicAdd(ended, 1) == (int)gridDim.x - 1) {
+    *ended = 0;
+    *last_step = step;
   }
 }
 
@@ -198,7 +210,7 @@ int bmxk_xchg_merge(const float* part, int rows, int rank, int world, void* cons
   BMXK_REQUIRE(part && buffers && status && out, "bmxk_xchg_merge: null pointer");
   BMXK_REQUIRE(rows >= 1 && world >= 1 && world <= XCHG_MAX_WORLD && rank >= 0 && rank < world, "bmxk_xchg_merge: rows=%d rank=%d world=%d",
                rows, rank, world);
-  BMXK_REQUIRE(step >= 1, "bmxk_xchg_merge: step=%d (steps count from 1: the flags start at zero)", step);
+  BMXK_REQUIRE(step >= 0, "bmxk_xchg_merge: step=%d (1, 2, 3, ... or 0 for the buffer's own count)", step);
   BMXK_REQUIRE(wait_limit_cycles >= 1000 && wait_limit_cycles <= 8000000000LL, "bmxk_xchg_merge: wait limit %lld cycles out of range",
                (long long)wait_limit_cycles);
   BMXK_REQUIRE(out_dtype == BMXK_DTYPE_F16 || out_dtype == BMXK_DTYPE_F32, "bmxk_xchg_merge: out_dtype=%d", out_dtype);

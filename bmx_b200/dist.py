@@ -58,38 +58,57 @@ class PeerExchange:
             raise RuntimeError("PeerExchange maps GPU memory between the ranks of one node: it needs the nccl backend (one rank per GPU)")
         lib()
         own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        self._own, self._peers, ptrs, failure = None, {}, [], None
         with torch.cuda.device(self.device):
-            call("bmxk_xchg_alloc", rows, self.world, ctypes.byref(own), handle)
-            mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=self.device)
-            everyone = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
+            # Every rank goes through the same collectives whether or not its own CUDA calls succeeded: a failure is
+            # gathered as a flag and raised on all ranks together, so that no rank is left waiting in a collective.
+            try:
+                call("bmxk_xchg_alloc", rows, self.world, ctypes.byref(own), handle)
+                self._own = own.value
+            except Exception as e:  # noqa: BLE001 - reported below, on every rank
+                failure = f"rank {self.rank}: {e}"
+            mine = torch.tensor(list(handle.raw) + [0 if failure is None else 1], dtype=torch.uint8, device=self.device)
+            everyone = torch.empty(self.world * 65, dtype=torch.uint8, device=self.device)
             dist.all_gather_into_tensor(everyone, mine, group=group)
-            handles = everyone.cpu().view(self.world, 64)
-            self._own, self._peers = own.value, {}
-            ptrs = []
-            for r in range(self.world):
-                if r == self.rank:
-                    ptrs.append(own.value)
-                    continue
-                peer = ctypes.c_void_p()
-                call("bmxk_xchg_open", bytes(handles[r].tolist()), ctypes.byref(peer))
-                self._peers[r] = peer.value
-                ptrs.append(peer.value)
+            handles = everyone.cpu().view(self.world, 65)
+            if failure is None and int(handles[:, 64].sum()) == 0:
+                try:
+                    for r in range(self.world):
+                        if r == self.rank:
+                            ptrs.append(own.value)
+                            continue
+                        peer = ctypes.c_void_p()
+                        call("bmxk_xchg_open", bytes(handles[r, :64].tolist()), ctypes.byref(peer))
+                        self._peers[r] = peer.value
+                        ptrs.append(peer.value)
+                except Exception as e:  # noqa: BLE001
+                    failure = f"rank {self.rank}: {e}"
+            elif failure is None:
+                failure = f"ranks {[r for r in range(self.world) if int(handles[r, 64])]} could not allocate their exchange buffer"
+            agreed = torch.tensor([0 if failure is None else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=group)
+            if int(agreed.item()):
+                self._release_local()
+                raise RuntimeError(f"peer exchange set-up failed ({failure or 'on another rank'})")
         self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.step = 0
         dist.barrier(group=group)  # nobody pushes into a buffer that is not mapped everywhere yet
 
-    def merge(self, part: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def merge(self, part: torch.Tensor, out: torch.Tensor | None = None, device_step: bool = False) -> torch.Tensor:
         """part: this rank's (rows, 130) float32 state -> merged, normalised (rows, 128).  Every rank calls it once per
-        step, in the same order; asynchronous on the current stream."""
+        step, in the same order; asynchronous on the current stream.  device_step: the kernel takes the step number from
+        the buffer's own count instead of an argument, so that the launch can be captured in a CUDA graph (the caller
+        then advances `step` once per replay)."""
         from . import kernels as K
         from ._lib import call
 
         assert part.is_cuda and part.dtype == torch.float32 and part.shape == (self.rows, PART_STRIDE) and part.is_contiguous()
         if out is None:
             out = torch.empty(self.rows, K.HEAD_DIM, dtype=torch.float16, device=part.device)
-        self.step += 1
-        call("bmxk_xchg_merge", part.data_ptr(), self.rows, self.rank, self.world, self._ptrs, self.step, self.WAIT_LIMIT_CYCLES,
+        if not device_step:
+            self.step += 1
+        call("bmxk_xchg_merge", part.data_ptr(), self.rows, self.rank, self.world, self._ptrs, 0 if device_step else self.step, self.WAIT_LIMIT_CYCLES,
              self.status.data_ptr(), out.data_ptr(), K._dtype_code(out), torch.cuda.current_stream().cuda_stream)
         return out
 
@@ -99,8 +118,19 @@ class PeerExchange:
         if st[0] != 0:
             raise RuntimeError(f"peer exchange: block {st[1]} gave up waiting for rank {st[2] - 32} (step {self.step})")
 
+    def _release_local(self) -> None:
+        from ._lib import call
+
+        with torch.cuda.device(self.device):
+            for ptr in self._peers.values():
+                call("bmxk_xchg_close", ptr)
+            self._peers = {}
+            if self._own is not None:
+                call("bmxk_xchg_free", self._own)
+            self._own = None
+
     def close(self) -> None:
-        """Unmaps the peers and frees the own buffer; collective (a barrier first: nobody frees what others still write)."""
+        """Unmaps the peers and frees the own buffer; collective (barriers: nobody frees what others still write or map)."""
         from ._lib import call
 
         if self._own is None:
@@ -110,9 +140,9 @@ class PeerExchange:
         with torch.cuda.device(self.device):
             for ptr in self._peers.values():
                 call("bmxk_xchg_close", ptr)
+            self._peers = {}
             dist.barrier(group=self.group)
-            call("bmxk_xchg_free", self._own)
-        self._own, self._peers = None, {}
+        self._release_local()
 
 
 class SequenceSplitDecoder:
@@ -138,6 +168,24 @@ class SequenceSplitDecoder:
             return self.peers.merge(self.part, out=out)
         gathered = gather_partials(self.part, self.group)
         return K.merge_partials(gathered, out=out)
+
+    def capture(self, q: torch.Tensor, out: torch.Tensor) -> "torch.cuda.CUDAGraph":
+        """The whole step (page-streaming kernel, local merge, peer exchange + merge) as one CUDA graph over the static
+        tensors q and out; p2p exchange only (a library collective is not captured here).  One eager step runs first.
+        Use replay(graph) per step: it keeps the host-side step count in line with the buffer's own."""
+        assert self.peers is not None, "capture() needs exchange='p2p'"
+        st = self.state
+        self.decode(q, out=out)
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            st.decode(q, partial_out=self.part, pos_offset=self.first_page * st.page)
+            self.peers.merge(self.part, out=out, device_step=True)
+        return graph
+
+    def replay(self, graph) -> None:
+        graph.replay()
+        self.peers.step += 1
 
     def close(self) -> None:
         if self.peers is not None:

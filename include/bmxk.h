@@ -306,7 +306,9 @@ int bmxk_merge_partials(const float* parts, int n_parts, int rows, void* out, in
  *   bmxk_xchg_alloc   allocates and zeroes this rank's buffer (cudaMalloc) and returns its 64-byte IPC handle;
  *   bmxk_xchg_open    maps a peer's buffer from its handle;  bmxk_xchg_close / bmxk_xchg_free undo the two.
  *   bmxk_xchg_merge   buffers: HOST array of `world` device pointers (index = rank, this rank's own included);
- *                     step: 1, 2, 3, ... the same on every rank, one call per step per rank, in order;
+ *                     step: 1, 2, 3, ... the same on every rank, one call per step per rank, in order; or 0 = the step
+ *                     after the last one this rank's buffer has completed (no per-step argument: the launch can sit in
+ *                     a CUDA graph);
  *                     status: int32[4] in this rank's device memory, zero; a wait that runs out writes
  *                     {1, block, 32 + the rank that never arrived} there and the kernel returns without a result. */
 size_t bmxk_xchg_bytes(int rows, int world);

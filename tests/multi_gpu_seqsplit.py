@@ -75,6 +75,21 @@ def main():
                 ok = ok and bool((err <= 2e-3).all())
                 if step in (0, 4):
                     print(f"seqsplit world={world} {exchange} step {step}: worst relative error vs single-GPU decode {float(err.max()):.3e}")
+        if exchange == "p2p":  # the same step replayed from a CUDA graph (the kernel counts its own steps), then eager again
+            q_st, out_st = q.clone(), torch.empty(h_kv * G, D, dtype=torch.float32, device=dev)
+            graph = dec.capture(q_st, out_st)
+            for step in range(4):
+                q_st.copy_((q.float() * (1.0 - 0.05 * step)).half())
+                dec.replay(graph)
+            out = dec.decode(q_st).float()  # host-numbered step after the replays
+            torch.cuda.synchronize()
+            dec.peers.check()
+            if rank == 0:
+                ref = whole.decode(q_st).float().view(-1, D)
+                e1 = ((out_st - ref).abs().amax(-1) / ref.abs().amax(-1)).max()
+                e2 = ((out - ref).abs().amax(-1) / ref.abs().amax(-1)).max()
+                ok = ok and float(e1) <= 2e-3 and float(e2) <= 2e-3
+                print(f"seqsplit world={world} p2p graph replay / eager after it: {float(e1):.3e} / {float(e2):.3e}")
         dec.close()
     # ---- one rank skips a step: the others' wait must run out (1 ms limit here), say who was missing, and return ----
     from bmx_b200.dist import PeerExchange
