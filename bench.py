@@ -59,13 +59,17 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.windows = index, [], None, []
+
+    def mark(self, t0: float, t1: float) -> None:
+        """[t0, t1] (time.perf_counter) was spent under the measured load: only samples taken then are summarised."""
+        self.windows.append((t0, t1))
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -74,7 +78,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([x.strip() for x in line.split(",")] + [time.perf_counter()])
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -86,10 +90,12 @@ class ClockSampler:
             self.thread.join(timeout=2)
 
     def summary(self) -> dict:
-        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        # a sample describes the ~50 ms before it was printed: keep those printed inside a load window or just after it
+        rows = [r for r in self.rows if not self.windows or any(t0 <= r[-1] <= t1 + 0.06 for t0, t1 in self.windows)]
+        mhz = sorted(int(r[0]) for r in rows if r and str(r[0]).isdigit())
+        mx = [int(r[1]) for r in rows if len(r) > 1 and str(r[1]).isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(mhz)}
 
@@ -297,16 +303,17 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # nvidia-smi needs a few hundred ms to deliver its first sample: start it before the warm-up and keep
-    # the GPU on the same kernel for at least 0.4 s so that the samples are taken under this load
+    # Clock samples: nvidia-smi prints one line per 50 ms, so the timed steps (a few tens of ms) would catch one at best.
+    # The same decode call therefore keeps running for 0.35 s after the timed steps and the per-kernel loop, and the
+    # samples printed between the first warm-up step and the end of that tail are the ones summarised.  The warm-up
+    # BEFORE the timed steps is the W steps asked for and no more: a long one puts the GPU into its sustained power
+    # state first, in which the same steps run ~4 % slower (measured: 114.8 us per step in 200-step runs, 118-119 us
+    # in 2000-step runs, the sampled SM clock reading 1965 MHz in both).
     clocks = ClockSampler(local_rank).__enter__()
-    t_w = time.perf_counter()
-    n_w = 0
-    while n_w < max(args.warmup, 3) or time.perf_counter() - t_w < 0.4:
+    time.sleep(0.3)  # nvidia-smi needs a moment to print its first line
+    t_load = time.perf_counter()
+    for _ in range(max(args.warmup, 3)):
         state.decode(q, out=out)
-        n_w += 1
-        if n_w % 16 == 0:
-            torch.cuda.synchronize()
     torch.cuda.synchronize()
     K.check_status(state.workspace)
 
@@ -318,7 +325,6 @@ def run_ours(args, rank, world, local_rank):
         state.decode(q, out=out)
     e1.record()
     barrier()
-    clocks.__exit__(None, None, None)
     total_ms = e0.elapsed_time(e1)
     # ---- the same steps once more with the two kernels launched apart and events between them on the launching
     #      stream: the duration of the dominant kernel for the roofline (phase 1 = page-streaming kernel, phase 2 =
@@ -335,6 +341,14 @@ def run_ours(args, rank, world, local_rank):
     main_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / n_k
     merge_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / n_k
     K.check_status(state.workspace)
+    n_tail = 0
+    while time.perf_counter() - t_load < 0.35:
+        state.decode(q, out=out)
+        n_tail += 1
+        if n_tail % 16 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    clocks.mark(t_load, time.perf_counter())
 
     # ---- the step's own output checked against the CPU oracle on the same stored pages, for one (sequence, head) at
     #      the full context (rank 0 only; outside every timed region) ----
@@ -365,6 +379,7 @@ def run_ours(args, rank, world, local_rank):
         stepper.step()
         torch.cuda.current_stream().synchronize()
 
+    t_load = time.perf_counter()
     for _ in range(3):
         e2e_step()
     barrier()
@@ -384,6 +399,9 @@ def run_ours(args, rank, world, local_rank):
     flush_us = max(step_wall) * 1e6
     plain_us = sorted(step_wall)[len(step_wall) // 2] * 1e6
     K.check_status(state.workspace)
+    clocks.mark(t_load, time.perf_counter())
+    time.sleep(0.06)  # the sample that covers the end of the last window
+    clocks.__exit__(None, None, None)
 
     mine = torch.tensor([total_ms / args.steps, main_ms, merge_ms, e2e_ms], dtype=torch.float64, device=device)
     per_rank = mine.clone().unsqueeze(0)
