@@ -120,6 +120,39 @@ __global__ void window_append_devpos_kernel(const T* __restrict__ k_post, const 
   }
 }
 
+// A decode step's inputs in one launch: the new token goes into the windows as in window_append_devpos_kernel, and the
+// step's queries are staged into device memory (block (sequence, kv head) copies the n_q_groups query rows of its head).
+// The sources may be pinned host memory mapped into the device's address space: the kernel then IS the host-to-device
+// copy of the step (a few KB per block over PCIe), which saves the copy engine's separate launch.
+__global__ void step_ingest_kernel(const __half* __restrict__ q_src, __half* __restrict__ q_dst, int n_q_groups,
+                                   const __half* __restrict__ k_post, const __half* __restrict__ v, const __half* __restrict__ k_src,
+                                   int64_t stride_seq, int64_t stride_head, __half* __restrict__ k_win, __half* __restrict__ v_win,
+                                   __half* __restrict__ k_src_win, int32_t* __restrict__ tail_len, int32_t* __restrict__ counters,
+                                   int32_t* __restrict__ status, int h_kv, int tail_cap) {
+  const int bh = blockIdx.x, b = bh / h_kv, h = bh % h_kv, c = threadIdx.x;
+  const int t = *reinterpret_cast<volatile int32_t*>(tail_len + b);
+  const int64_t src = (int64_t)b * stride_seq + (int64_t)h * stride_head + c;
+  // all loads first (they cross PCIe when the sources are host memory), then the stores
+  const __half kp = k_post[src], vv = v[src], ks = k_src[src];
+  __half qv[8];
+  for (int g = 0; g < n_q_groups; ++g) qv[g] = q_src[((int64_t)bh * n_q_groups + g) * WIN_HEAD_DIM + c];
+  for (int g = 0; g < n_q_groups; ++g) q_dst[((int64_t)bh * n_q_groups + g) * WIN_HEAD_DIM + c] = qv[g];
+  if (t >= 0 && t < tail_cap) {
+    const int64_t dst = ((int64_t)bh * tail_cap + t) * WIN_HEAD_DIM + c;
+    k_win[dst] = kp, v_win[dst] = vv, k_src_win[dst] = ks;
+  } else if (c == 0 && status) {
+    atomicCAS(status, 0, 2);
+  }
+  __syncthreads();
+  if (c == 0) {
+    __threadfence();
+    if (atomicAdd(counters + b, 1) == h_kv - 1) {
+      counters[b] = 0;
+      if (t >= 0 && t < tail_cap) tail_len[b] = t + 1;
+    }
+  }
+}
+
 }  // namespace bmxk
 
 extern "C" {
@@ -213,6 +246,18 @@ int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_s
   else
     BMXK_REQUIRE(false, "bmxk_window_append_devpos: src_dtype=%d", src_dtype);
   return check_launch("bmxk_window_append_devpos");
+}
+
+int bmxk_step_ingest(const void* q_src, void* q_dst, int n_q_groups, const void* k_post, const void* v, const void* k_src,
+                     int64_t stride_seq, int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len,
+                     int32_t* counters, int32_t* status, int batch, int h_kv, int tail_cap, void* stream) {
+  BMXK_REQUIRE(q_src && q_dst && k_post && v && k_src && k_win && v_win && k_src_win && tail_len && counters, "bmxk_step_ingest: null pointer");
+  BMXK_REQUIRE(batch >= 1 && h_kv >= 1 && tail_cap >= 1 && n_q_groups >= 1 && n_q_groups <= 8,
+               "bmxk_step_ingest: batch=%d h_kv=%d tail_cap=%d n_q_groups=%d", batch, h_kv, tail_cap, n_q_groups);
+  step_ingest_kernel<<<batch * h_kv, WIN_HEAD_DIM, 0, (cudaStream_t)stream>>>(
+      (const __half*)q_src, (__half*)q_dst, n_q_groups, (const __half*)k_post, (const __half*)v, (const __half*)k_src, stride_seq, stride_head,
+      (__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_len, counters, status, h_kv, tail_cap);
+  return check_launch("bmxk_step_ingest");
 }
 
 }  // extern "C"

@@ -512,9 +512,11 @@ class RtnLayerState(K2bLayerState):
 class DecodeStepGraph:
     """One decode step of a layer state, host buffers to host buffer, as a CUDA graph.
 
-    The step is: copy the pinned staging buffer [q | k_post | v | k_pre] to the device, append the token to the
-    fp16 window at the device-side position, run the two decode kernels, copy the attention output to the pinned
-    output buffer.  None of these launches has a per-step argument (positions and page counts live in device
+    The step is: one ingest kernel that reads the pinned staging buffer [q | k_post | v | k_pre] straight from host
+    memory (queries to a device buffer, the token into the fp16 windows at the device-side position), the two decode
+    kernels, the second of which stores the attention output straight into the pinned output buffer.  (States that
+    quantize non-fp16 layouts, or zero_copy=False, use copy nodes instead: staging buffer to the device, append,
+    decode, output to the host.)  None of these launches has a per-step argument (positions and page counts live in device
     memory), so the sequence is captured once and replayed; on the steps where the flush schedule commits pages
     (one in `page`) the step runs through `append` / `decode` instead.  bmx's counterpart is the Python of
     PackedStreamingLayer.update + attend per token (bmx: src/bmx/cache/packed_streaming.py:582-730, 832-1064).
@@ -524,7 +526,7 @@ class DecodeStepGraph:
     (batch, heads, 128).
     """
 
-    def __init__(self, state: K2bLayerState, hin: torch.Tensor, hout: torch.Tensor):
+    def __init__(self, state: K2bLayerState, hin: torch.Tensor, hout: torch.Tensor, zero_copy: bool = True):
         g = state.geom
         h_kv = g.h_kv
         n_q_groups = getattr(state, "n_q_groups", None) or g.n_q_groups
@@ -539,12 +541,24 @@ class DecodeStepGraph:
         self.v = self.din[nq + nk:nq + 2 * nk].view(B, h_kv, 1, HEAD_DIM)
         self.k_pre = self.din[nq + 2 * nk:].view(B, h_kv, 1, HEAD_DIM)
         self.out = torch.empty(B, heads, HEAD_DIM, dtype=torch.float16, device=state.device)
+        # the kernels read the pinned staging buffer and write the pinned output themselves (k2b states: the other decode
+        # wrappers take device outputs)
+        self.zero_copy = zero_copy and type(state) is K2bLayerState
+        self.h_q = hin[:nq].view(B, heads, HEAD_DIM)
+        self.h_k_post = hin[nq:nq + nk].view(B, h_kv, 1, HEAD_DIM)
+        self.h_v = hin[nq + nk:nq + 2 * nk].view(B, h_kv, 1, HEAD_DIM)
+        self.h_k_pre = hin[nq + 2 * nk:].view(B, h_kv, 1, HEAD_DIM)
         self.graph: torch.cuda.CUDAGraph | None = None
         self._captured_for = None  # (max_pages, pool identity): a pool that grew invalidates the captured pointers
         self._check_key = True     # pools and tables only change on the steps that go through append()
 
     def _launches(self) -> None:
         st = self.state
+        if self.zero_copy:
+            K.step_ingest(self.h_q, self.q, self.h_k_post, self.h_v, self.h_k_pre if st.pre_rope else self.h_k_post, st.k_win, st.v_win,
+                          st.k_pre_win, st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))
+            st.decode(self.q, out=self.hout)
+            return
         self.din.copy_(self.hin, non_blocking=True)
         K.window_append_devpos(self.k_post, self.v, self.k_pre if st.pre_rope else self.k_post, st.k_win, st.v_win, st.k_pre_win,
                                st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))

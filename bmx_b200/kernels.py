@@ -64,6 +64,13 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise RuntimeError("bmxk kernels take CUDA tensors; there is no CPU path")
 
 
+def _require_device_visible(*ts: torch.Tensor) -> None:
+    """CUDA tensors, or pinned host tensors (mapped into the device's address space: a kernel can read / write them)."""
+    for t in ts:
+        if t is not None and not (t.is_cuda or t.is_pinned()):
+            raise RuntimeError("this argument must be a CUDA tensor or a pinned host tensor")
+
+
 DEFAULT_K2B_LAYOUT = 1  # row order, read by the tcgen05 decode kernel
 
 
@@ -211,6 +218,7 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
     """One decode step for q (batch, heads, 128) fp16 over the paged k2b cache plus the fp16 window."""
     g = pool.geom
     _require_cuda(q, page_table, n_pages, workspace)
+    _require_device_visible(out)  # a pinned host tensor: the merge kernel stores the result there itself
     batch = q.shape[0]
     assert q.dtype == torch.float16 and q.is_contiguous() and q.shape[1:] == (g.h_kv * g.n_q_groups, HEAD_DIM)
     assert page_table.dtype == torch.int32 and n_pages.dtype == torch.int32 and page_table.dim() == 2
@@ -325,6 +333,25 @@ def window_append_devpos(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Ten
     call("bmxk_window_append_devpos", _ptr(k_post), _ptr(v), _ptr(k_src), _dtype_code(k_post), k_post.stride(0), k_post.stride(1),
          _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), _ptr(counters), _ptr(status), batch, h_kv, k_win.shape[2],
          _stream())
+
+
+def step_ingest(q_src: torch.Tensor, q_dst: torch.Tensor, k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor,
+                k_win: torch.Tensor, v_win: torch.Tensor, k_src_win: torch.Tensor, tail_len: torch.Tensor, counters: torch.Tensor,
+                status: torch.Tensor | None = None) -> None:
+    """One launch for a decode step's inputs: the token (k_post, v, k_src: (batch, h_kv, 1, 128) fp16) goes into the
+    windows at the device-side position, the queries q_src (batch, heads, 128) fp16 are staged into q_dst.  The four
+    sources may be pinned host tensors: the kernel then reads them over PCIe and no separate copy is needed."""
+    _require_device_visible(q_src, k_post, v, k_src)
+    _require_cuda(q_dst, k_win, v_win, k_src_win, tail_len, counters)
+    batch, h_kv = k_post.shape[0], k_post.shape[1]
+    for x in (k_post, v, k_src):
+        if x.dtype != torch.float16 or not _same_token_layout(x, k_post):
+            raise ValueError("step_ingest: token sources must be fp16 (batch, h_kv, 1, 128) with one layout")
+    assert q_src.dtype == q_dst.dtype == torch.float16 and q_src.shape == q_dst.shape and q_src.is_contiguous() and q_dst.is_contiguous()
+    assert q_src.shape[0] == batch and q_src.shape[1] % h_kv == 0 and q_src.shape[2] == HEAD_DIM
+    call("bmxk_step_ingest", _ptr(q_src), _ptr(q_dst), q_src.shape[1] // h_kv, _ptr(k_post), _ptr(v), _ptr(k_src), k_post.stride(0),
+         k_post.stride(1), _ptr(k_win), _ptr(v_win), _ptr(k_src_win), _ptr(tail_len), _ptr(counters), _ptr(status), batch, h_kv,
+         k_win.shape[2], _stream())
 
 
 def merge_partials(parts: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

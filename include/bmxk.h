@@ -341,6 +341,15 @@ int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_s
                               int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len,
                               int32_t* counters, int32_t* status, int batch, int h_kv, int tail_cap, void* stream);
 
+/* A decode step's inputs in one launch (no counterpart in bmx, whose step starts from device tensors): the append of
+ * bmxk_window_append_devpos for fp16 sources, plus the step's queries q_src (batch, h_kv*n_q_groups, 128) fp16 staged
+ * into q_dst.  q_src, k_post, v and k_src may be PINNED HOST memory (cudaHostAlloc / torch pin_memory: mapped into the
+ * device's address space): the kernel is then the host-to-device copy of the step.  Likewise the `out` of the decode
+ * entry points may be pinned host memory: the merge kernel stores the result there directly. */
+int bmxk_step_ingest(const void* q_src, void* q_dst, int n_q_groups, const void* k_post, const void* v, const void* k_src,
+                     int64_t stride_seq, int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len,
+                     int32_t* counters, int32_t* status, int batch, int h_kv, int tail_cap, void* stream);
+
 
 /* Reads back the status word of the last decode on this workspace (host-synchronising; for
  * tests and diagnostics).  Returns BMXK_ERR_DEVICE if a bounded wait ran out. */

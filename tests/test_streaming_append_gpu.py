@@ -102,9 +102,11 @@ def test_token_by_token_equals_bulk_and_prefix_is_frozen(page, dtype):
         assert np.all(err <= 2e-3), float(err.max())
 
 
-def test_decode_step_graph_equals_eager_steps():
-    """The captured (copy in, append at the device-side position, decode, copy out) step replayed token after token
-    gives the outputs and the state of append() + decode() called per token, across flushes and a pool that grows."""
+@pytest.mark.parametrize("zero_copy", [True, False])
+def test_decode_step_graph_equals_eager_steps(zero_copy):
+    """The captured step replayed token after token gives the outputs and the state of append() + decode() called per
+    token, across flushes and a pool that grows.  zero_copy: the ingest kernel reads the pinned staging buffer itself and
+    the merge kernel stores into the pinned output; otherwise copy nodes move both."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from bmx_b200 import kernels as K
@@ -138,7 +140,8 @@ def test_decode_step_graph_equals_eager_steps():
     nq, nk = B * h_kv * G * D, B * h_kv * D
     hin = torch.empty(nq + 3 * nk, dtype=torch.float16).pin_memory()
     hout = torch.empty(B, h_kv * G, D, dtype=torch.float16).pin_memory()
-    stepper = DecodeStepGraph(graphed, hin, hout)
+    stepper = DecodeStepGraph(graphed, hin, hout, zero_copy=zero_copy)
+    assert stepper.zero_copy == zero_copy
     replays = 0
     for i in range(steps):
         t = prefix + i
