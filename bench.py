@@ -56,7 +56,7 @@ class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc, self.windows = index, [], None, []
@@ -96,8 +96,14 @@ class ClockSampler:
         mx = [int(r[1]) for r in rows if len(r) > 1 and str(r[1]).isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in rows)]
+        watts = []
+        for r in rows:
+            try:
+                watts.append(float(r[6]))
+            except (IndexError, ValueError):
+                pass
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(mhz)}
+                "reasons": reasons, "samples": len(mhz), "power_w_max": max(watts) if watts else None}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -306,9 +312,8 @@ def run_ours(args, rank, world, local_rank):
     # Clock samples: nvidia-smi prints one line per 50 ms, so the timed steps (a few tens of ms) would catch one at best.
     # The same decode call therefore keeps running for 0.35 s after the timed steps and the per-kernel loop, and the
     # samples printed between the first warm-up step and the end of that tail are the ones summarised.  The warm-up
-    # BEFORE the timed steps is the W steps asked for and no more: a long one puts the GPU into its sustained power
-    # state first, in which the same steps run ~4 % slower (measured: 114.8 us per step in 200-step runs, 118-119 us
-    # in 2000-step runs, the sampled SM clock reading 1965 MHz in both).
+    # BEFORE the timed steps is the W steps asked for and no more (on one box the same steps ran ~4 % slower after a long
+    # pre-heating loop, with the sampled SM clock unchanged; on another they did not).
     clocks = ClockSampler(local_rank).__enter__()
     time.sleep(0.3)  # nvidia-smi needs a moment to print its first line
     t_load = time.perf_counter()
