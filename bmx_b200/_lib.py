@@ -57,6 +57,9 @@ _SIGNATURES = {
     "bmxk_k2b_append": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p]),
+    "bmxk_k2b_append_coefs": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                       c_void_p]),
     "bmxk_k2b_export_stacks": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "bmxk_k2b_dequant_pages": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

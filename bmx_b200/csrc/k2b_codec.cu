@@ -106,6 +106,16 @@ __global__ void k2b_project_kernel(K2bGeom g, const T* __restrict__ k_pre, int64
   for (int j = 0; j < 4; ++j) out[k2b_coef_idx(g.layout, r, 4 * iq + j, rank)] = __float2half_rn(acc[j]);
 }
 
+// Coefficients computed elsewhere (a projection summed over the GPUs that hold the other heads of a basis spanning all
+// heads): us (n_seq, n_pages * page, rank) float32, rounded to fp16 into the coefficient blocks.  One block per page.
+__global__ void k2b_store_coefs_kernel(K2bGeom g, const float* __restrict__ us, const int32_t* __restrict__ slots, int n_pages,
+                                       __half* __restrict__ coefs) {
+  const int item = blockIdx.x, seq = item / n_pages, pg = item % n_pages, rank = g.rank;
+  const float* src = us + ((int64_t)seq * n_pages + pg) * g.page * rank;
+  __half* out = coefs + (int64_t)slots[item] * (g.page * rank);  // one coefficient block per slot (n_coef_heads == 1)
+  for (int o = threadIdx.x; o < g.page * rank; o += blockDim.x) out[k2b_coef_idx(g.layout, o / rank, o % rank, rank)] = __float2half_rn(src[o]);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Page quantizer.  One block of 256 threads per (item, kv head); two blocks share an SM.
 //   staging: the head's key page (float32, KF_STRIDE per row) and its basis slice go to shared memory.
@@ -537,15 +547,19 @@ static int launch_quant(const K2bGeom& gg, const T* k_pre, const T* v, int64_t s
 template <typename T>
 static int append_impl(const bmxk_k2b_geom* g, const void* k_pre, const void* v, int64_t ss, int64_t sh, int64_t st,
                        const float* basis, const float* signs, const float* codebook, const int32_t* slots, int n_seq,
-                       int n_pages, void* pages, void* coefs, cudaStream_t s) {
+                       int n_pages, void* pages, void* coefs, cudaStream_t s, const float* us_given = nullptr) {
   const K2bGeom gg = to_geom(g);
   const int items = n_seq * n_pages;
   // one wide load per four source elements needs every row start aligned to it
   const uintptr_t align = 4 * sizeof(T);
   const bool vec = ((uintptr_t)k_pre % align == 0) && ((uintptr_t)v % align == 0) && (ss * sizeof(T)) % align == 0 &&
                    (sh * sizeof(T)) % align == 0 && (st * sizeof(T)) % align == 0 && ((uintptr_t)basis % 16 == 0);
-  const bool fused = g->n_coef_heads == g->h_kv;  // one basis per head: the page kernel projects by itself
-  if (!fused) {
+  const bool fused = g->n_coef_heads == g->h_kv && !us_given;  // one basis per head: the page kernel projects by itself
+  if (us_given) {
+    k2b_store_coefs_kernel<<<items, 256, 0, s>>>(gg, us_given, slots, n_pages, (__half*)coefs);
+    int rc = check_launch("bmxk_k2b_append_coefs(store)");
+    if (rc) return rc;
+  } else if (!fused) {
     BMXK_REQUIRE((uintptr_t)basis % 16 == 0, "bmxk_k2b_append: basis must be 16-byte aligned");
     const size_t psmem = ((size_t)32 * KF_STRIDE + (size_t)HEAD_DIM * g->rank) * sizeof(float);
     k2b_project_kernel<T><<<items * g->n_coef_heads * (g->page / 32), 8 * g->rank, psmem, s>>>(
@@ -597,6 +611,36 @@ int bmxk_k2b_append(const bmxk_k2b_geom* g, const void* k_pre, const void* v, in
                                 n_seq, n_pages, pages, coefs, s);
     default:
       set_error("bmxk_k2b_append: unknown src_dtype %d", src_dtype);
+      return BMXK_ERR_INVALID;
+  }
+}
+
+int bmxk_k2b_append_coefs(const bmxk_k2b_geom* g, const void* k_pre, const void* v, int src_dtype, int64_t stride_seq,
+                          int64_t stride_head, int64_t stride_tok, const float* us_f32, const float* basis_f32, const float* signs,
+                          const float* codebook, const int32_t* slots, int n_seq, int n_pages, void* pages, void* coefs,
+                          void* stream) {
+  int rc = check_geom(g, "bmxk_k2b_append_coefs");
+  if (rc) return rc;
+  BMXK_REQUIRE(g->n_coef_heads == 1, "bmxk_k2b_append_coefs: n_coef_heads=%d (given coefficients belong to one basis over all heads)",
+               g->n_coef_heads);
+  BMXK_REQUIRE(n_seq >= 0 && n_pages >= 0, "bmxk_k2b_append_coefs: negative counts");
+  if (n_seq == 0 || n_pages == 0) return BMXK_OK;
+  BMXK_REQUIRE(k_pre && v && us_f32 && basis_f32 && signs && codebook && slots && pages && coefs, "bmxk_k2b_append_coefs: null pointer");
+  BMXK_REQUIRE(stride_tok >= HEAD_DIM, "bmxk_k2b_append_coefs: stride_tok=%lld < 128", (long long)stride_tok);
+  BMXK_REQUIRE((int64_t)n_seq * n_pages * g->h_kv < (1LL << 31), "bmxk_k2b_append_coefs: too many pages in one call");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (src_dtype) {
+    case BMXK_DTYPE_F16:
+      return append_impl<__half>(g, k_pre, v, stride_seq, stride_head, stride_tok, basis_f32, signs, codebook, slots, n_seq, n_pages, pages,
+                                 coefs, s, us_f32);
+    case BMXK_DTYPE_BF16:
+      return append_impl<__nv_bfloat16>(g, k_pre, v, stride_seq, stride_head, stride_tok, basis_f32, signs, codebook, slots, n_seq, n_pages,
+                                        pages, coefs, s, us_f32);
+    case BMXK_DTYPE_F32:
+      return append_impl<float>(g, k_pre, v, stride_seq, stride_head, stride_tok, basis_f32, signs, codebook, slots, n_seq, n_pages, pages,
+                                coefs, s, us_f32);
+    default:
+      set_error("bmxk_k2b_append_coefs: unknown src_dtype %d", src_dtype);
       return BMXK_ERR_INVALID;
   }
 }

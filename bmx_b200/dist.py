@@ -41,6 +41,60 @@ def gather_partials(part: torch.Tensor, group=None) -> torch.Tensor:
     return out.view(world, *part.shape)
 
 
+class HeadShardedK2bLayer:
+    """KV heads of one layer split across the ranks of `group` while the key basis spans ALL heads (bmx's default: one
+    (h_kv*128, rank) basis per layer, src/bmx/cache/packed_streaming.py:513-520).  Decode needs no collective: every rank
+    holds the coefficients (they belong to the token, not to a head) and the pages of its own heads.  Append needs one:
+    the projection Us = M @ V runs over all heads' channels, so every rank projects the channels it holds and the partial
+    products are summed by one all-reduce of (batch, tokens, rank) float32 per flush.  The basis is fitted on the first
+    page of all heads (one all-gather of that page, once) and every rank keeps the rows of its own heads.
+
+    state(): a K2bLayerState over the local heads with n_coef_heads = 1; use its append / decode as usual."""
+
+    def __init__(self, h_kv_total: int, n_q_groups: int, rank_k: int, group_k: int, batch: int, max_tokens: int, recent_window: int,
+                 device, rope_cos: torch.Tensor, rope_sin: torch.Tensor, group=None, page: int = 128, v_seed: int = 0):
+        from . import kernels as K
+        from .engine import K2bLayerState
+
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.h0, self.h1 = shard_range(h_kv_total, self.world, self.rank)
+        assert self.h1 > self.h0, "more ranks than KV heads"
+        self.h_kv_total = h_kv_total
+        geom = K.k2b_geom(self.h1 - self.h0, n_q_groups, page, rank_k, group_k, 1)
+        self._state = K2bLayerState(geom, batch, max_tokens, recent_window, device, rope_cos, rope_sin, v_seed=v_seed)
+        self._state.project = self._project
+        self._state.fit_basis = self._fit_basis
+
+    def state(self):
+        return self._state
+
+    def set_basis(self, basis_all_heads: torch.Tensor) -> None:
+        """(h_kv_total*128, rank) float32, the same on every rank: the rows of the local heads are kept."""
+        self._state.set_basis(basis_all_heads[self.h0 * 128:self.h1 * 128].contiguous())
+
+    def _fit_basis(self, k_pre_page: torch.Tensor) -> None:
+        """First flush: gather the first page of every head (heads in rank order), fit one basis on all of them, as a
+        single-GPU state does."""
+        from . import kernels as K
+        from .engine import fit_basis
+
+        st = self._state
+        x = k_pre_page.float().contiguous()  # (batch, local heads, page, 128)
+        counts = [shard_range(self.h_kv_total, self.world, r) for r in range(self.world)]
+        parts = [torch.empty(x.shape[0], b - a, x.shape[2], x.shape[3], device=x.device) for a, b in counts]
+        dist.all_gather(parts, x, group=self.group)
+        full_geom = K.k2b_geom(self.h_kv_total, st.geom.n_q_groups, st.geom.page, st.geom.rank, st.geom.group, 1)
+        self.set_basis(fit_basis(full_geom, torch.cat(parts, 1)))
+
+    def _project(self, k_src: torch.Tensor, n_pages: int) -> torch.Tensor:
+        st = self._state
+        T = n_pages * st.page
+        M = k_src[:, :, :T].permute(0, 2, 1, 3).reshape(k_src.shape[0], T, -1).float()   # (batch, T, local channels)
+        us = torch.matmul(M, st.basis_f32)                                                  # partial projection
+        dist.all_reduce(us, op=dist.ReduceOp.SUM, group=self.group)
+        return us.contiguous()
+
+
 class PeerExchange:
     """This rank's exchange buffer plus the mappings of every other rank's (CUDA IPC, one node), for
     bmxk_xchg_merge.  Set-up is collective over `group` (one all-gather of the 64-byte handles); a step is not."""

@@ -53,6 +53,10 @@ def dequant_value_blocks(vpool: torch.Tensor, slots: torch.Tensor, codebook: tor
 class K2bLayerState:
     """Packed pages + fp16 recent window of one layer for `batch` sequences of equal length."""
 
+    # callable (k_src, n_pages) -> (batch, n_pages * page, rank) float32 that replaces the append kernel's own projection
+    # (a basis spanning heads that other GPUs hold: dist.HeadShardedK2bLayer); None: the kernel projects
+    project = None
+
     def __init__(self, geom, batch: int, max_tokens: int, recent_window: int, device, rope_cos: torch.Tensor,
                  rope_sin: torch.Tensor, *, codebook=None, v_seed: int = 0, pre_rope: bool = True):
         assert rope_cos.dtype == torch.float16 and rope_cos.shape[1] == HEAD_DIM and rope_cos.shape[0] >= 128
@@ -123,7 +127,11 @@ class K2bLayerState:
         self.ensure_pages(n_pages)
         p0 = self.committed // self.page
         slots = self.page_table[:, p0:p0 + n_pages].contiguous().view(-1)
-        K.k2b_append(self.pool, k_src, v_src, self.basis_f32, self.signs, self.codebook, slots, n_pages)
+        if self.project is None:
+            K.k2b_append(self.pool, k_src, v_src, self.basis_f32, self.signs, self.codebook, slots, n_pages)
+        else:  # the projection onto a basis that spans heads held elsewhere (dist.HeadShardedK2bLayer)
+            K.k2b_append_coefs(self.pool, k_src, v_src, self.project(k_src, n_pages), self.basis_f32, self.signs, self.codebook, slots,
+                               n_pages)
         self.committed += n_pages * self.page
         self.n_pages_dev.fill_(self.committed // self.page)
 

@@ -166,6 +166,25 @@ def k2b_append(pool: K2bPool, k_pre: torch.Tensor, v: torch.Tensor, basis_f32: t
          _ptr(pool.pages), _ptr(pool.coefs), _stream())
 
 
+def k2b_append_coefs(pool: K2bPool, k_pre: torch.Tensor, v: torch.Tensor, us_f32: torch.Tensor, basis_f32: torch.Tensor,
+                     signs: torch.Tensor, codebook: torch.Tensor, slots: torch.Tensor, n_pages: int) -> None:
+    """k2b_append with the projection given: us_f32 (n_seq, n_pages * page, rank) float32 = keys of ALL heads of a basis
+    spanning all heads, projected (e.g. summed over the ranks that hold the other heads); basis_f32: the basis rows of this
+    pool's h_kv heads.  The pool's geometry must have n_coef_heads == 1."""
+    g = pool.geom
+    _require_cuda(k_pre, v, us_f32, basis_f32, signs, codebook, slots)
+    assert g.n_coef_heads == 1, "given coefficients belong to one basis over all heads"
+    assert k_pre.shape == v.shape and k_pre.dim() == 4 and k_pre.shape[1] == g.h_kv and k_pre.shape[3] == HEAD_DIM
+    assert k_pre.dtype == v.dtype and k_pre.stride() == v.stride() and k_pre.stride(3) == 1
+    n_seq = k_pre.shape[0]
+    assert k_pre.shape[2] >= n_pages * g.page and slots.dtype == torch.int32 and slots.numel() == n_seq * n_pages
+    assert us_f32.dtype == torch.float32 and us_f32.shape == (n_seq, n_pages * g.page, g.rank) and us_f32.is_contiguous()
+    assert basis_f32.dtype == torch.float32 and basis_f32.shape == (g.h_kv * HEAD_DIM, g.rank) and basis_f32.is_contiguous()
+    call("bmxk_k2b_append_coefs", ctypes.byref(g), _ptr(k_pre), _ptr(v), _dtype_code(k_pre), k_pre.stride(0), k_pre.stride(1),
+         k_pre.stride(2), _ptr(us_f32), _ptr(basis_f32), _ptr(signs), _ptr(codebook), _ptr(slots), n_seq, n_pages,
+         _ptr(pool.pages), _ptr(pool.coefs), _stream())
+
+
 def k2b_export_stacks(pool: K2bPool, slots: torch.Tensor) -> dict:
     """Pages -> the tensors bmx's build_kv_stacked_k2b(pack_k=True, pack_v=True) would hold."""
     g = pool.geom

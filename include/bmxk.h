@@ -78,6 +78,16 @@ int bmxk_k2b_append(const bmxk_k2b_geom* g, const void* k_pre, const void* v, in
                     const float* signs, const float* codebook, const int32_t* slots, int n_seq, int n_pages,
                     void* pages, void* coefs, void* stream);
 
+/* The same append with the coefficients given instead of projected: us_f32 (n_seq, n_pages*page, rank) float32 = M @ V
+ * over ALL heads of a basis that spans all heads (n_coef_heads must be 1), e.g. the sum over GPUs of the partial
+ * projections of the heads each one holds (bmx projects on one device: src/bmx/cache/packed_streaming.py:513-520).
+ * They are rounded to fp16 into the coefficient blocks; residual, scales, codes and values as in bmxk_k2b_append,
+ * with basis_f32 = the rows of the basis that belong to THIS call's h_kv heads, (h_kv*128, rank). */
+int bmxk_k2b_append_coefs(const bmxk_k2b_geom* g, const void* k_pre, const void* v, int src_dtype, int64_t stride_seq,
+                          int64_t stride_head, int64_t stride_tok, const float* us_f32, const float* basis_f32,
+                          const float* signs, const float* codebook, const int32_t* slots, int n_seq, int n_pages,
+                          void* pages, void* coefs, void* stream);
+
 /* Rewrites n pages into the exact tensors bmx's stack builder produces, for byte parity.
  * bmx: src/bmx/cache/triton_dequant_attention.py:1118-1229 build_kv_stacked_k2b(pack_k, pack_v).
  * us (n, n_coef_heads, page, rank) fp16; res_int_packed (n, h_kv*128, page/2) u8;

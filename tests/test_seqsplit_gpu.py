@@ -1,4 +1,5 @@
-"""Sequence split over two GPUs with one NCCL all-gather (skipped on boxes with a single GPU)."""
+"""Multi-GPU partitions on two GPUs (skipped on boxes with a single GPU): the sequence split with its two exchanges, and
+KV heads sharded under a key basis that spans all heads."""
 
 import os
 import subprocess
@@ -20,3 +21,15 @@ def test_sequence_split_two_gpus():
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "OK" in r.stdout
+
+
+def test_head_shards_with_a_basis_over_all_heads_two_gpus():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(root, "tests", "multi_gpu_headshard.py")],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "headshard OK" in r.stdout
