@@ -175,84 +175,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
   Walker w;
   w.init(cum, npg_sm, f_begin, h_kv);
 
-  if (warp >= W_DQ && warp < SVC0) {
-    // ===================== dequant warps: tier codes -> fp16 Y_hat, the A operand of U1 =====================
-    // Warp wd takes the direction octets wd, wd + DQ_WARPS, ... (positions in tier order).  Lane = (direction
-    // lane / 4 of the octet, token pair q = lane % 4): for every 8-token block B it produces the half2 of tokens
-    // 8B + 2q, 8B + 2q + 1 of its direction, which is exactly what a transposed stmatrix wants from it.  Four
-    // blocks (32 tokens, one 8 / 16 / 32-byte piece of the direction's row) go out per stmatrix.
-    // A half2 costs four instructions whatever the tier: a byte permute drops the thread's code byte(s) under the
-    // fp16 exponent of 1024 in both halves, one LOP3 masks each half down to its field and flips two's-complement
-    // sign bits, an exact subtraction removes 1024 and the field's offset (times the field's position in the byte),
-    // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
-    // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
-    // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
-    set_regs<REG_DEQUANT>();
-    constexpr int OCT = 16 / DQ_WARPS;
-    const int wd = warp - W_DQ, q = lane & 3, dsub = lane >> 2;
-    const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
-    const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
-    const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
-    int s = 0;
-    uint32_t fp = 0;
-    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
-      const int n = w.it, b = n & 1, h = w.cur.h;
-      int meta[OCT];
-#pragma unroll
-      for (int oo = 0; oo < OCT; ++oo) meta[oo] = __ldg(p.meta + h * HEAD_DIM + 8 * (DQ_WARPS * oo + wd) + dsub);
-      const int n_oct = 2 * (((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1);  // octets that U1 reads for this head
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
-      // the buffer still feeds U1 of tile n-2
-      if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
-      const uint8_t* kb = stage0 + (size_t)s * STAGE_BYTES;
-      const float* scales = reinterpret_cast<const float*>(kb + p.scale_off);
-      const uint32_t ybase = smem_u32(ybuf0 + (size_t)b * OPER_BYTES);
-#pragma unroll 1
-      for (int oo = 0; oo < OCT; ++oo) {
-        const int o = DQ_WARPS * oo + wd;
-        if (o >= n_oct) break;  // the same for the whole warp
-        const int mt = meta[oo], off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
-        // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
-        const bool w2 = (bits == 2), w8 = (bits >= 5);
-        const uint32_t piece = w2 ? 8u : (w8 ? 32u : 16u);
-        // word (byte offset inside the piece) and byte selector of block m = 0..3 of a piece
-        //   2-bit: byte 2 (m % 2) + q / 2 of word m / 2;  4-bit: byte q of word m;  8-bit: bytes 2 (q % 2), + 1 of word 2 m + q / 2
-        const uint32_t wstep = w2 ? 2u : (w8 ? 8u : 4u);            // byte offset of block m's word = (m * wstep rounded down to 4) + wbase
-        const uint32_t wbase = w8 ? 4u * (uint32_t)(q >> 1) : 0u;
-        const uint32_t byte_e = w2 ? (uint32_t)(q >> 1) : (w8 ? 2u * (uint32_t)(q & 1) : (uint32_t)q);   // source byte that lands in the low half
-        const uint32_t hi_inc = w8 ? 1u : 0u;                                                              // the high half takes the next byte (8-bit) or the same one
-        const uint32_t sel_e = 0x4040u | byte_e | ((byte_e + hi_inc) << 8);
-        const uint32_t sel_o = w2 ? sel_e + 0x0202u : sel_e;       // 2-bit: odd blocks sit two bytes further in the same word
-        const uint32_t mask = w2 ? (((0xFF00u | (0x3u << (a2 + 2))) << 16) | (0xFF00u | (0x3u << a2))) : (w8 ? 0xFFFFFFFFu : 0xFFF0FF0Fu);
-        const uint32_t X2 = (bits == 3) ? 0x00800008u : (w8 ? 0x00800080u : 0u);   // two's-complement fields: flip the sign bit
-        // field offset still to subtract (times the field's position) and the position itself
-        const float blo = w2 ? (float)(2 << a2) : (w8 ? 128.f : 8.f), bhi = w2 ? (float)(2 << (a2 + 2)) : 128.f;
-        const float plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
-        const __half2 bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
-        const uint8_t* rowp = kb + off + wbase;
-        const float* scp = scales + d * ngrp;
-        const uint32_t st_addr = ybase + (uint32_t)o * 128u + st_lane;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[4];
-          const float scf = bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
-          const __half2 s2 = __floats2half2_rn(scf * plo, scf * phi);
-#pragma unroll
-          for (int m_ = 0; m_ < 4; ++m_) {
-            const uint32_t wo = ((uint32_t)m_ * wstep) & ~3u;
-            const uint32_t wv = *reinterpret_cast<const uint32_t*>(rowp + (uint32_t)c * piece + wo);
-            const uint32_t t = lop3<0x6A>(prmt(wv, 0x64646464u, (m_ & 1) ? sel_o : sel_e), mask, X2);
-            r[m_] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(t), bias2), s2));
-          }
-          stmatrix_x4_trans(st_addr + (uint32_t)(4 * c) * 16u * 128u, r);
-        }
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) smem_add_release(&sh->ycnt[b], 1);
-      if (++s == STG) s = 0, fp ^= 1u;
-    }
-  } else if (warp < KEY_WARPS) {
+  if (warp < KEY_WARPS) {
     // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
     set_regs<REG_KEY>();
     constexpr int KCH = 16 / KEY_WARPS;  // chunks of 16 + 16 channels per key warp
@@ -291,6 +214,90 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->kcnt[b], 1);
+    }
+  } else if (warp >= W_DQ && warp < SVC0) {
+    // ===================== dequant warps: tier codes -> fp16 Y_hat, the A operand of U1 =====================
+    // Warp wd takes the direction octets wd, wd + DQ_WARPS, ... (positions in tier order).  Lane = (direction
+    // lane / 4 of the octet, token pair q = lane % 4): for every 8-token block B it produces the half2 of tokens
+    // 8B + 2q, 8B + 2q + 1 of its direction, which is exactly what a transposed stmatrix wants from it.  Four
+    // blocks (32 tokens, one 8 / 16 / 32-byte piece of the direction's row) go out per stmatrix.
+    // A half2 costs four instructions whatever the tier: a byte permute drops the thread's code byte(s) under the
+    // fp16 exponent of 1024 in both halves, one LOP3 masks each half down to its field and flips two's-complement
+    // sign bits, an exact subtraction removes 1024 and the field's offset (times the field's position in the byte),
+    // and a multiply applies the scale (divided by that position, a power of two).  The tier only changes the
+    // constants (selectors, mask, offsets), which each lane derives for its own direction: one compact loop serves
+    // every width with no divergence, so the warp-wide stmatrix is always reached by all 32 lanes.
+    set_regs<REG_DEQUANT>();
+    constexpr int OCT = 16 / DQ_WARPS;
+    const int wd = warp - W_DQ, q = lane & 3, dsub = lane >> 2;
+    const int ngrp = 128 / p.group, gsh = (p.group == 32) ? 0 : (p.group == 64 ? 1 : 2);
+    const uint32_t st_lane = (uint32_t)((lane >> 3) * 16 * 128 + (lane & 7) * 16);
+    const int a2 = 4 * (q & 1);  // 2-bit containers: this thread's two fields start at bits a2 and a2 + 2 of its byte
+    static_assert(OCT == 1, "one direction octet per dequant warp: its constants live in registers for a whole range");
+    int s = 0;
+    uint32_t fp = 0;
+    // Constants of this lane's direction (position 8 wd + dsub of the head's tier order); they change with the head only.
+    int cur_h = -1;
+    bool active = false, has_bits = false;
+    uint32_t piece = 0, wo1 = 0, wo2 = 0, wo3 = 0, sel_e = 0, sel_o = 0, mask = 0, X2 = 0, row_off = 0, sc_off = 0;
+    float plo = 0.f, phi = 0.f;
+    __half2 bias2 = __floats2half2_rn(0.f, 0.f);
+    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
+      const int n = w.it, b = n & 1, h = w.cur.h;
+      if (h != cur_h) {
+        cur_h = h;
+        const int mt = __ldg(p.meta + h * HEAD_DIM + 8 * wd + dsub);
+        const int n_oct = 2 * (((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1);  // octets that U1 reads for this head
+        active = wd < n_oct;  // the same for the whole warp
+        const int off = mt & 0xFFFF, d = (mt >> 16) & 127, bits = (mt >> 24) & 15;
+        has_bits = bits != 0;
+        // container width 2 / 4 / 8 bits: one 32-token piece of the row is 8 / 16 / 32 bytes
+        const bool w2 = (bits == 2), w8 = (bits >= 5);
+        piece = w2 ? 8u : (w8 ? 32u : 16u);
+        // word (byte offset inside the piece) and byte selector of block m = 0..3 of a piece
+        //   2-bit: byte 2 (m % 2) + q / 2 of word m / 2;  4-bit: byte q of word m;  8-bit: bytes 2 (q % 2), + 1 of word 2 m + q / 2
+        const uint32_t wstep = w2 ? 2u : (w8 ? 8u : 4u);   // byte offset of block m's word = (m * wstep rounded down to 4) + wbase
+        wo1 = wstep & ~3u, wo2 = (2u * wstep) & ~3u, wo3 = (3u * wstep) & ~3u;
+        const uint32_t wbase = w8 ? 4u * (uint32_t)(q >> 1) : 0u;
+        const uint32_t byte_e = w2 ? (uint32_t)(q >> 1) : (w8 ? 2u * (uint32_t)(q & 1) : (uint32_t)q);   // source byte that lands in the low half
+        const uint32_t hi_inc = w8 ? 1u : 0u;                                                              // the high half takes the next byte (8-bit) or the same one
+        sel_e = 0x4040u | byte_e | ((byte_e + hi_inc) << 8);
+        sel_o = w2 ? sel_e + 0x0202u : sel_e;       // 2-bit: odd blocks sit two bytes further in the same word
+        mask = w2 ? (((0xFF00u | (0x3u << (a2 + 2))) << 16) | (0xFF00u | (0x3u << a2))) : (w8 ? 0xFFFFFFFFu : 0xFFF0FF0Fu);
+        X2 = (bits == 3) ? 0x00800008u : (w8 ? 0x00800080u : 0u);   // two's-complement fields: flip the sign bit
+        // field offset still to subtract (times the field's position) and the position itself
+        const float blo = w2 ? (float)(2 << a2) : (w8 ? 128.f : 8.f), bhi = w2 ? (float)(2 << (a2 + 2)) : 128.f;
+        plo = w2 ? 1.f / (float)(1 << a2) : 1.f, phi = w2 ? 1.f / (float)(1 << (a2 + 2)) : (w8 ? 1.f : 0.0625f);
+        bias2 = __floats2half2_rn(1024.f + blo, 1024.f + bhi);
+        row_off = (uint32_t)off + wbase;
+        sc_off = (uint32_t)(d * ngrp);
+      }
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
+      // the buffer still feeds U1 of tile n-2
+      if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
+      if (active) {
+        const uint8_t* kb = stage0 + (size_t)s * STAGE_BYTES;
+        const uint8_t* rowp = kb + row_off;
+        const float* scp = reinterpret_cast<const float*>(kb + p.scale_off) + sc_off;
+        uint32_t st_addr = smem_u32(ybuf0 + (size_t)b * OPER_BYTES) + (uint32_t)wd * 128u + st_lane;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c, rowp += piece, st_addr += 4u * 16u * 128u) {
+          const uint32_t wv0 = *reinterpret_cast<const uint32_t*>(rowp), wv1 = *reinterpret_cast<const uint32_t*>(rowp + wo1);
+          const uint32_t wv2 = *reinterpret_cast<const uint32_t*>(rowp + wo2), wv3 = *reinterpret_cast<const uint32_t*>(rowp + wo3);
+          const float scf = has_bits ? scp[c >> gsh] : 0.f;   // directions without bits: everything times zero
+          const __half2 s2 = __floats2half2_rn(scf * plo, scf * phi);
+          uint32_t r[4];
+          r[0] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lop3<0x6A>(prmt(wv0, 0x64646464u, sel_e), mask, X2)), bias2), s2));
+          r[1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lop3<0x6A>(prmt(wv1, 0x64646464u, sel_o), mask, X2)), bias2), s2));
+          r[2] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lop3<0x6A>(prmt(wv2, 0x64646464u, sel_e), mask, X2)), bias2), s2));
+          r[3] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(lop3<0x6A>(prmt(wv3, 0x64646464u, sel_o), mask, X2)), bias2), s2));
+          stmatrix_x4_trans(st_addr, r);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->ycnt[b], 1);
+      if (++s == STG) s = 0, fp ^= 1u;
     }
   } else if (warp >= W_VAL && warp < W_DQ) {
     // ===================== value warps: thread = channel, both 64-token halves of the tile =====================
