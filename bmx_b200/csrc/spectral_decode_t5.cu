@@ -55,6 +55,7 @@ struct S5Smem {
   volatile int slot_ring[16];
   int slot_seq[2];
   volatile int bsel[S5_MAX_STAGES], first[S5_MAX_STAGES], ksteps[S5_MAX_STAGES];  // per stage: decoder buffer, range start, K=16 steps of U1
+  volatile int head[S5_MAX_STAGES];                                               // per stage: KV head of the tile (for the dequant warps)
   float wmax[2][4][8];
   __align__(16) int flag[2][4];
   float red[2][4][16];
@@ -242,8 +243,10 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
     uint32_t piece = 0, wo1 = 0, wo2 = 0, wo3 = 0, sel_e = 0, sel_o = 0, mask = 0, X2 = 0, row_off = 0, sc_off = 0;
     float plo = 0.f, phi = 0.f;
     __half2 bias2 = __floats2half2_rn(0.f, 0.f);
-    for (; w.it < n_tiles; w.advance(npg_sm, h_kv, p.batch)) {
-      const int n = w.it, b = n & 1, h = w.cur.h;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int b = n & 1;
+      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
+      const int h = sh->head[s];  // left with the stage by the query rotation warp: these warps do not walk the tile list
       if (h != cur_h) {
         cur_h = h;
         const int mt = __ldg(p.meta + h * HEAD_DIM + 8 * wd + dsub);
@@ -272,7 +275,6 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
         row_off = (uint32_t)off + wbase;
         sc_off = (uint32_t)(d * ngrp);
       }
-      if (!wait_or_flag(&sh->full[s], fp, p.status, 13)) break;
       // the buffer still feeds U1 of tile n-2
       if (n >= 2 && !wait_or_flag(&sh->low[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 14)) break;
       if (active) {
@@ -616,6 +618,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
           if (lane == 0) {
             sh->bsel[s] = w.seg & 1, sh->first[s] = (w.it == first_cur) ? 1 : 0;
             sh->ksteps[s] = ((__ldg(p.meta + h * HEAD_DIM) >> 28) & 7) + 1;
+            sh->head[s] = h;
           }
           fence_proxy_async();
           __syncwarp();
