@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(S5_THREADS, 1) spectral_decode_t5_kernel(const
       if (n >= 2 && !wait_or_flag(&sh->odone[b], (uint32_t)((n - 2) >> 1) & 1u, p.status, 11)) break;
       tc5::fence_after();
       const uint4* vc = reinterpret_cast<const uint4*>(stage0 + (size_t)s * STAGE_BYTES + KB);
-#pragma unroll
+#pragma unroll 1
       for (int cc = cc0; cc < cc1; ++cc) {
         const uint4 cw = vc[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
