@@ -418,7 +418,10 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       constexpr uint32_t ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
       const uint64_t d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
-      int nC = 0, nP = 0;
+      // Stage indices, barrier phases and arrival thresholds are carried from action to action (no division in the
+      // polling loop): what runs between "operands complete" and "MMA issued" is what a tile waits for.
+      int nC = 0, nP = 0, sC = 0, sP = 0, need_p = 4, need_v = 8;   // arrivals that complete tile nC on its parity's counters
+      uint32_t phP = 1;                                             // parity to test on empty[sP]: a fresh barrier passes 1
       long long t_last = clock64();
       uint32_t idle = 0;
       bool ok = true;
@@ -427,12 +430,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         const int pc = smem_load_acquire(&sh->pcnt[nC & 1]);
         const int vc = smem_load_acquire(&sh->vcnt[nC & 1]);
         const int bdone = smem_load_acquire(&sh->bcnt);
-        if (nC < bdone && pc >= 4 * ((nC >> 1) + 1) && vc >= 8 * ((nC >> 1) + 1)) {
+        if (nC < bdone && pc >= need_p && vc >= need_v) {
           tc5::fence_after();
-          const int s = nC % T5_STAGES, b = nC & 1;
+          const int s = sC, b = nC & 1;
           const uint32_t keep = sh->first[s] ? 0u : 1u;  // the first tile of its parity in a range starts a new accumulator
           const uint64_t db = d_pb + (uint64_t)(b * (T5_QB_BYTES >> 4));
           ++nC;
+          if (b) need_p += 4, need_v += 8;  // the next tile of parity 0 needs one more round of arrivals
+          if (++sC == T5_STAGES) sC = 0;
           if (el) {
             tc5::mma_ts(tmem + TM_O + 16 * b, tmem + TM_V + 64 * b, db, ID_N16, keep);
 #pragma unroll
@@ -445,9 +450,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           __syncwarp();
           progressed = true;
         }
-        if (nP < n_tiles && smem_load_acquire(&sh->slot_seq[nP & 1]) > nP &&
-            mbar_test_wait(&sh->empty[nP % T5_STAGES], ((uint32_t)(nP / T5_STAGES) & 1u) ^ 1u)) {
-          const int s = nP % T5_STAGES, h = w.cur.h, slot = sh->slot_ring[nP & 15];
+        if (nP < n_tiles && smem_load_acquire(&sh->slot_seq[nP & 1]) > nP && mbar_test_wait(&sh->empty[sP], phP)) {
+          const int s = sP, h = w.cur.h, slot = sh->slot_ring[nP & 15];
           uint8_t* st = stage0 + (size_t)s * STAGE_BYTES;
           const int chd = (g.n_coef_heads == 1) ? 0 : h;
           if (el) {
@@ -458,6 +462,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           }
           __syncwarp();
           ++nP;
+          if (++sP == T5_STAGES) sP = 0, phP ^= 1u;
           if (nP < n_tiles) w.advance(npg_sm, g.h_kv, p.batch);
           progressed = true;
         }
@@ -558,7 +563,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
       // in lockstep, so that operand descriptors stay in uniform registers; one elected lane issues.
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_N16 = tc5::idesc_f16_f32(128, 16);
       const bool el = elect_one();
-      int nA = 0, nB = 0;
+      int nA = 0, nB = 0, sA = 0, sB = 0, need_k = 8;   // key-warp arrivals that complete tile nB on its parity's counter
+      uint32_t phA = 0;                                 // parity to test on full[sA]
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_bbuf = tc5::smem_desc(smem_u32(bbuf0), 128, AB_SBO);
       const uint64_t d_qb = tc5::smem_desc(smem_u32(qb0), 128, 2048), d_pb = tc5::smem_desc(smem_u32(pbuf0), 128, 2048);
       long long t_last = clock64();
@@ -571,9 +577,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
         const int kc = smem_load_acquire(&sh->kcnt[nB & 1]);
         const int nC = smem_load_acquire(&sh->ccnt);   // U3 issued so far (the other issuing warp)
         // ---- B ----
-        if (nB < nA && nB < nC + 2 && kc >= 8 * ((nB >> 1) + 1)) {
+        if (nB < nA && nB < nC + 2 && kc >= need_k) {
           tc5::fence_after();
-          const int s = nB % T5_STAGES, b = nB & 1;
+          const int s = sB, b = nB & 1;
           const uint64_t db = d_qb + (uint64_t)(s * (T5_QB_BYTES >> 4));
           if (el) {
 #pragma unroll
@@ -583,13 +589,15 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           }
           __syncwarp();
           ++nB;
+          if (b) need_k += 8;
+          if (++sB == T5_STAGES) sB = 0;
           progressed = true;
         }
         // ---- A ----
-        if (nA < n_tiles && nA < nB + 2 && mbar_test_wait(&sh->full[nA % T5_STAGES], (uint32_t)(nA / T5_STAGES) & 1u) &&
+        if (nA < n_tiles && nA < nB + 2 && mbar_test_wait(&sh->full[sA], phA) &&
             (nA < 2 || mbar_test_wait(&sh->sdone[nA & 1], (uint32_t)((nA - 2) >> 1) & 1u))) {
           tc5::fence_after();
-          const int s = nA % T5_STAGES, b = nA & 1;
+          const int s = sA, b = nA & 1;
           const uint64_t da = d_stage + (uint64_t)(s * (STAGE_BYTES >> 4)), db = d_bbuf + (uint64_t)(sh->bsel[s] * (COEF_BYTES >> 4));
           if (el) {
 #pragma unroll
@@ -598,6 +606,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) k2b_decode_t5_kernel(const K2bD
           }
           __syncwarp();
           ++nA;
+          if (++sA == T5_STAGES) sA = 0, phA ^= 1u;
           progressed = true;
         }
         if (progressed) {
