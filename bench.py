@@ -514,7 +514,7 @@ def _event_us(fn, n: int, warm: int = 3) -> float:
 
 
 def config_rtn(device) -> dict:
-    """BASELINE configs[0]: plain RTN cache, B = 1, 4096 committed tokens + a 128-token fp16 window; keys rtn_channel 4 bits,
+    """Benchmark configuration 1 (plain RTN cache), B = 1, 4096 committed tokens + a 128-token fp16 window; keys rtn_channel 4 bits,
     values rtn_token 2 bits, groups of 32; K ~ N(0,1) with 4 channels per head x 8.  4.2 MB per step: the step is bound by
     launch latency, so it is timed both as plain launches and replayed from a CUDA graph."""
     import torch
@@ -548,7 +548,7 @@ def config_rtn(device) -> dict:
 
 
 def config_append(device, B: int = 16) -> dict:
-    """BASELINE configs[2]: quantize-on-append of the k2b recipe, B = 16, bf16 sources, one layer (the 32 layers of the config
+    """Benchmark configuration 3: quantize-on-append of the k2b recipe, B = 16, bf16 sources, one layer (the 32 layers of the config
     repeat it).  Bulk: the 16384-token prefix of all sequences in one call (128 pages x 16 sequences x 8 heads).  Streaming:
     single-token steps on top of it, 127 of every 128 move one token into the fp16 window, the 128th commits a page per
     sequence.  Bytes per (page, head): read 2 x 128 x 128 x 2 (key and value sources), write 13056 + 8192."""
@@ -614,7 +614,7 @@ def config_append(device, B: int = 16) -> dict:
 
 
 def config_seq_split(device, rank, world, dist) -> dict:
-    """BASELINE configs[3]: one sequence of 131072 committed tokens (32 q / 8 kv heads, d 128, k2b recipe), its pages split
+    """Benchmark configuration 4: one sequence of 131072 committed tokens (32 q / 8 kv heads, d 128, k2b recipe), its pages split
     across the ranks; every rank decodes its part into an un-normalised state (max, sum, accumulator), ONE all-gather of
     (32 x 130) floats per rank, then the merge.  Rank 0 also holds the whole sequence and checks the merged output against
     its own single-GPU decode (2e-3).  At one GPU this is just the single-GPU long-context step."""
@@ -720,11 +720,11 @@ def config_seq_split(device, rank, world, dist) -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
-# Secondary workload (not the headline line): BASELINE configs[4], K4 spectral keys, one GPU
+# Secondary workload (not the headline line): benchmark configuration 5, K4 spectral keys, one GPU
 # ------------------------------------------------------------------------------------------------
 
 def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
-    """BASELINE configs[4]: K4 spectral keys, B = 64 sequences x 16384 committed tokens over all ranks (64 / N per rank:
+    """Benchmark configuration 5: K4 spectral keys, B = 64 sequences x 16384 committed tokens over all ranks (64 / N per rank:
     sequences are independent, no collective), per-head 128 x 128 packs at ~2.6 bits per direction, values as in the k2b
     workload; one page set is quantized for real and copied to every sequence (distinct memory).  The bound of this kernel
     is max(bytes at the HBM peak, decoder product at the sustained tensor peak)."""

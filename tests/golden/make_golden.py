@@ -177,7 +177,7 @@ def main() -> None:
     out["k2b_out_naive"] = npy(ca.naive_dense_attention(q, kb, vb, **kw))
     kw_nt = dict(kw, k_tail=None, v_tail=None)
     out["k2b_out_chunked_notail"] = npy(ca.chunked_dequant_attention(q, kb, vb, **kw_nt))
-    # RTN pair of the first BASELINE config: K rtn_channel 4b, V rtn_token 2b, group 32, post-RoPE K
+    # RTN pair of the first benchmark configuration: K rtn_channel 4b, V rtn_token 2b, group 32, post-RoPE K
     k_post = torch.randn(T, C, generator=gen(28))
     k_post[:, [0, 1, 2, 3, d, d + 1, d + 2, d + 3]] *= 8.0
     k_post = k_post.half().float()

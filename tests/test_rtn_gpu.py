@@ -23,7 +23,7 @@ def _dev():
 def _inputs(seed, n_seq, h_kv, T):
     g = torch.Generator().manual_seed(seed)
     k = torch.randn(n_seq, h_kv, T, D, generator=g)
-    k[..., :4] *= 8.0  # outlier channels, as in the RTN config of BASELINE
+    k[..., :4] *= 8.0  # outlier channels, as in the RTN benchmark configuration
     return k.half().contiguous(), torch.randn(n_seq, h_kv, T, D, generator=g).half().contiguous()
 
 
@@ -122,7 +122,7 @@ def test_decode_matches_oracle(page, k_arm, kg, vg, G):
 
 
 def test_first_baseline_config_shape():
-    """BASELINE configs[0]: 8 KV heads, GQA 4, T = 4096 + 128-token window, K rtn_channel 4b, V rtn_token 2b, g = 32."""
+    """Benchmark configuration 1: 8 KV heads, GQA 4, T = 4096 + 128-token window, K rtn_channel 4b, V rtn_token 2b, g = 32."""
     from bmx_b200 import kernels as K
     out, ref = _decode_case(K, _dev(), page=128, k_arm="rtn_channel", kg=32, vg=32, G=4, pages_per_seq=[32],
                             tail_lens=[128], seed=1000, h_kv=8)
