@@ -425,6 +425,7 @@ def run_ours(args, rank, world, local_rank):
         extra["rtn_b1_t4096"] = config_rtn(device)
         extra["append_b16"] = config_append(device)
         extra["prefill_b1_t16384"] = config_prefill(device)
+        extra["latency_b1"] = config_latency_b1(device)
     extra_all = {"spectral_b64_t16384": config_spectral(device, rank, world, dist if world > 1 else None),
                  "seq_split_t131072": config_seq_split(device, rank, world, dist if world > 1 else None)}
 
@@ -861,6 +862,56 @@ def config_prefill(device) -> dict:
     return out
 
 
+def config_latency_b1(device) -> dict:
+    """The shape bmx's own kernel tables are quoted on: one sequence (B = 1), 32 q / 8 kv heads, context 2k / 8k / 32k / 128k,
+    one attention layer-call; k2b with a rank-16 basis per head and 128-token pages (the configuration of its fastest
+    published kernel), window of 128 fp16 tokens.  Microseconds per decode step (both kernels), replayed from a CUDA graph,
+    CUDA events.  The published figures beside them were measured by bmx's author on another GPU (GH200) with bmx's Triton
+    kernel: context, not a like-for-like ratio."""
+    import torch
+
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope, default_rope_tables
+
+    rank, W = 16, 128
+    published_gh200_ms = {2048: 0.079, 8192: 0.241, 32768: 0.935, 131072: 3.709}
+    gen = torch.Generator(device=device).manual_seed(6000)
+    basis = torch.zeros(H_KV * D, rank, device=device)
+    for h in range(H_KV):
+        Q, R = torch.linalg.qr(torch.randn(D, rank, generator=gen, device=device))
+        basis[h * D:(h + 1) * D] = Q * torch.sign(torch.diagonal(R))
+    out = {"workload": "k2b decode latency, B=1, 32 q / 8 kv heads, rank-16 per-head basis, 128-token pages and window",
+           "published_reference_ms_on_gh200": {str(k): v for k, v in published_gh200_ms.items()}}
+    peak, _ = measured_peak_gbs()
+    per_unit = 64 + 4 + 32 + 2 + 2 * rank  # residual nibbles, scales, value codes, norm, fp16 coefficients
+    for T in (2048, 8192, 32768, 131072):
+        total = T + W
+        cos, sin = default_rope_tables(ROPE_THETA, D, total + 256, device=device)
+        geom = K.k2b_geom(H_KV, G, PAGE, rank, GROUP, H_KV)
+        st = K2bLayerState(geom, 1, total + 256, W, device, cos.half(), sin.half())
+        st.set_basis(basis)
+        decay = torch.arange(1, rank + 1, device=device).float() ** -1.5
+        coef = torch.randn(1, H_KV, total, rank, generator=gen, device=device) * decay
+        k_pre = (torch.einsum("bhtr,hcr->bhtc", coef, basis.view(H_KV, D, rank)) + 0.1 * torch.randn(1, H_KV, total, D, generator=gen, device=device)).half()
+        v = torch.randn(1, H_KV, total, D, generator=gen, device=device).half()
+        st.append(k_pre, apply_rope(k_pre.float(), cos[:total], sin[:total]).half(), v)
+        assert st.committed == T and st.tail_len == W
+        q = (torch.randn(1, H_KV * G, D, generator=gen, device=device) / math.sqrt(D)).half()
+        o = torch.empty(1, H_KV * G, D, dtype=torch.float16, device=device)
+        st.decode(q, out=o)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            st.decode(q, out=o)
+        us = _event_us(graph.replay, 200)
+        K.check_status(st.workspace)
+        algo = T * H_KV * per_unit
+        out[str(T)] = {"us_per_layer_step": us, "algorithmic_bytes": algo, "GBps": algo / us / 1e3, "frac_of_hbm_peak": algo / us / 1e3 / peak}
+        del st, k_pre, v, coef
+    return out
+
+
 def run_hf(args) -> None:
     """`--workload hf`: per-token decode latency of a random-init Llama-shaped model (Llama-3.1-8B layer dimensions, four
     layers, small vocabulary) with PackedStreamingCache (k2b) against DynamicCache: prefill 8192 tokens at B = 4, then time
@@ -944,7 +995,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX, help="committed tokens per sequence (smaller cases for profiling)")
     ap.add_argument("--batch", type=int, default=16, help="sequences of --workload append (smaller cases for profiling)")
-    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "append", "rtn", "prefill", "hf"],
+    ap.add_argument("--workload", default="k2b", choices=["k2b", "spectral", "append", "rtn", "prefill", "latency", "hf"],
                     help="k2b: the headline line (carries the other configurations under `configs`); spectral: the K4 spectral "
                          "cache alone, append / rtn: those configurations alone (one GPU, for profiling); hf: per-token latency "
                          "under a random-init Hugging Face model")
@@ -964,7 +1015,7 @@ def main():
                 raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
             print(json.dumps(config_spectral(torch.device("cuda", 0), 0, 1, None, steps=min(args.steps, 50))), flush=True)
         return
-    if args.workload in ("append", "rtn", "prefill"):
+    if args.workload in ("append", "rtn", "prefill", "latency"):
         if rank == 0:
             import torch
 
@@ -972,7 +1023,7 @@ def main():
                 raise SystemExit("bench.py: no CUDA device; the bmxk kernels have no CPU path")
             dev0 = torch.device("cuda", 0)
             fn = {"append": lambda: config_append(dev0, B=args.batch), "rtn": lambda: config_rtn(dev0),
-                  "prefill": lambda: config_prefill(dev0)}[args.workload]
+                  "prefill": lambda: config_prefill(dev0), "latency": lambda: config_latency_b1(dev0)}[args.workload]
             print(json.dumps(fn()), flush=True)
         return
     if args.workload == "hf":
