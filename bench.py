@@ -37,9 +37,9 @@ BATCH, CTX = 8, 32768
 BYTES_PER_UNIT = 166  # per (token, kv head): coefficients 64 + residual nibbles 64 + scales 4 + value codes 32 + norm 2
 ROPE_THETA = 500000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k2b_decode_t5_kernel launch from an ncu capture at 16384 tokens
-# (174.9 + 4.7 MB), scaled by 2 to this workload's 32768 tokens: the kernel streams every page once, so traffic grows
+# (174.68 + 4.66 MB), scaled by 2 to this workload's 32768 tokens: the kernel streams every page once, so traffic grows
 # in proportion to the tokens.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.90e6 + 4.69e6)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (174.68e6 + 4.66e6)
 
 
 def measured_peak_gbs():
