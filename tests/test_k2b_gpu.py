@@ -422,3 +422,37 @@ def test_decode_parity_at_benchmark_context(T, h_kv):
     err = np.abs(out - ref).max(axis=-1) / np.abs(ref).max(axis=-1)
     print(f"T={T}: worst relative error {float(err.max()):.3e} over {err.size} (sequence, head) rows")
     _assert_attn_close(out, ref)
+
+
+def test_append_with_given_coefficients_equals_the_projecting_append():
+    """bmxk_k2b_append_coefs (the projection handed in, as a head-sharded layer does after its all-reduce) against
+    bmxk_k2b_append with the same basis over all heads: the same pages, except where the float32 projection, summed here
+    by a library GEMM in another order, lands on the other side of an fp16 rounding boundary of a coefficient (and the
+    residual codes of that token move with it)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+
+    dev = torch.device("cuda:0")
+    n_seq, h_kv, n_pages, rank, page = 2, 4, 3, 16, 128
+    k, v, basis = make_k2b_inputs(77, n_seq, h_kv, n_pages * page, rank, per_head=False)
+    geom = K.k2b_geom(h_kv, 4, page, rank, 64, 1)
+    signs, cb = K.hadamard_signs(D, 0).to(dev), torch.tensor(K.GAUSSIAN_CODEBOOK[2], device=dev)
+    slots = torch.arange(n_seq * n_pages, dtype=torch.int32, device=dev)
+    a, b = K.K2bPool(geom, n_seq * n_pages, dev), K.K2bPool(geom, n_seq * n_pages, dev)
+    K.k2b_append(a, k.to(dev), v.to(dev), basis.to(dev), signs, cb, slots, n_pages)
+    M = k.to(dev).permute(0, 2, 1, 3).reshape(n_seq, n_pages * page, h_kv * D).float()
+    us = torch.matmul(M, basis.to(dev)).contiguous()
+    K.k2b_append_coefs(b, k.to(dev), v.to(dev), us, basis.to(dev), signs, cb, slots, n_pages)
+    ea, eb = to_np(K.k2b_export_stacks(a, slots)), to_np(K.k2b_export_stacks(b, slots))
+    ua, ub = ea["us"].astype(np.float32), eb["us"].astype(np.float32)
+    differ = ua != ub
+    print(f"coefficients differing {differ.mean():.4%}, residual bytes differing {(ea['res_int_packed'] != eb['res_int_packed']).mean():.4%}")
+    assert differ.mean() <= 0.0072
+    assert np.all(np.abs(ua - ub)[differ] <= np.spacing(np.abs(ua[differ]).astype(np.float16)).astype(np.float32) * 1.001)  # one fp16 step
+    assert (ea["res_int_packed"] != eb["res_int_packed"]).mean() <= 0.01
+    np.testing.assert_array_equal(ea["v_idx_packed"], eb["v_idx_packed"])   # the value side does not depend on the projection
+    np.testing.assert_array_equal(ea["v_norm"], eb["v_norm"])
+    with pytest.raises(AssertionError):  # a basis per head has nothing to be handed: the kernel projects by itself
+        K.k2b_append_coefs(K.K2bPool(K.k2b_geom(h_kv, 4, page, rank, 64, h_kv), 1, dev), k.to(dev), v.to(dev), us, basis.to(dev), signs, cb,
+                           slots[:0], 0)
