@@ -66,3 +66,36 @@ def test_bounded_wait_runs_out_and_reports_block_and_site():
     assert int((torch.ones(8, device=dev) * 2).sum()) == 16
     with pytest.raises(BmxkError):
         K.selftest_bounded_wait(status, 10**12)
+
+
+def test_exchange_kernel_alone_on_one_gpu():
+    """bmxk_xchg_merge with a world of one: the rank stores its state into its own buffer, flags, finds its flag and
+    normalises; two steps use both buffer parities, a third takes the step number from the buffer's own count.  (Several
+    ranks are exercised by tests/multi_gpu_seqsplit.py on boxes with more than one GPU; kernels of two ranks that wait for
+    each other are never launched on one GPU.)"""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import ctypes
+
+    from bmx_b200._lib import DTYPE_F32, call, lib
+
+    dev = torch.device("cuda:0")
+    rows = 48
+    lib()
+    buf, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    call("bmxk_xchg_alloc", rows, 1, ctypes.byref(buf), handle)
+    try:
+        ptrs = (ctypes.c_void_p * 1)(buf.value)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        g = torch.Generator().manual_seed(3)
+        stream = torch.cuda.current_stream().cuda_stream
+        for step in (1, 2, 0):  # 0: "the step after the last completed one" (3)
+            part = torch.rand(rows, 130, generator=g).to(dev)
+            part[:, 1] += 0.5
+            out = torch.empty(rows, 128, dtype=torch.float32, device=dev)
+            call("bmxk_xchg_merge", part.data_ptr(), rows, 0, 1, ptrs, step, 2_000_000_000, status.data_ptr(), out.data_ptr(), DTYPE_F32, stream)
+            torch.cuda.synchronize()
+            assert status.cpu().tolist() == [0, 0, 0, 0]
+            torch.testing.assert_close(out, part[:, 2:] / part[:, 1:2], rtol=1e-6, atol=0)
+    finally:
+        call("bmxk_xchg_free", buf)
