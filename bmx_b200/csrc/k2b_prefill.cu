@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k2b_prefill_kernel(const Prefil
   uint64_t* bar = reinterpret_cast<uint64_t*>(bsm + 128 * BP);        // [2] raw tile landed
   float* sg = reinterpret_cast<float*>(bar + 2);                      // [128] signs / 128
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
-  const int b = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PP;
+  // the latest positions see the most pages: their blocks are scheduled first, so that the last wave is the lightest
+  const int b = blockIdx.z, h = blockIdx.y, i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * PP;
   const int H = g.h_kv * G;
 
   // ---- set-up: barriers, basis, signs, this warp's query fragments ----
