@@ -109,6 +109,8 @@ _SIGNATURES = {
                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "bmxk_window_append_devpos": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "bmxk_gather_next_slots": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "bmxk_window_shift": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "bmxk_step_ingest": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "bmxk_check_workspace_status": (c_int, [c_void_p, c_void_p]),

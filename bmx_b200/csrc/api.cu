@@ -153,6 +153,47 @@ __global__ void step_ingest_kernel(const __half* __restrict__ q_src, __half* __r
   }
 }
 
+// After a flush: the tokens [off, off + rest) of every (sequence, head) window move to the front, the device-side window
+// length becomes `rest` and the device-side page count grows by `pages_added`.  One block per (sequence, head); the move
+// goes forward in chunks of 2048 elements, each read completely before it is written (source and destination overlap
+// when rest > off).  k_src_win may alias k_win (caches that quantize post-RoPE keys): it is then moved once.
+__global__ void window_shift_kernel(__half* __restrict__ k_win, __half* __restrict__ v_win, __half* __restrict__ k_src_win, int tail_cap,
+                                    int off, int rest, int h_kv, int32_t* __restrict__ tail_len, int32_t* __restrict__ n_pages,
+                                    int pages_added) {
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  __half* bufs[3] = {k_win, v_win, (k_src_win == k_win) ? nullptr : k_src_win};
+  const int total = rest * WIN_HEAD_DIM;  // elements to move per window; a multiple of 8
+  for (int w = 0; w < 3; ++w) {
+    if (!bufs[w]) continue;
+    uint4* base = reinterpret_cast<uint4*>(bufs[w] + (int64_t)bh * tail_cap * WIN_HEAD_DIM);
+    const int shift4 = off * WIN_HEAD_DIM / 8, n4 = total / 8;
+    for (int c0 = 0; c0 < n4; c0 += 256) {
+      const int i = c0 + tid;
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (i < n4) x = base[shift4 + i];
+      __syncthreads();  // the whole chunk is in registers before any of it is overwritten
+      if (i < n4) base[i] = x;
+      __syncthreads();
+    }
+  }
+  if (tid == 0 && bh % h_kv == 0) {
+    const int b = bh / h_kv;
+    tail_len[b] = rest;
+    if (n_pages) n_pages[b] += pages_added;
+  }
+}
+
+// slots_out[b * n + i] = page_table[b][n_pages[b] + i]: the slots of the next n pages of every sequence, looked up on the
+// device so that a captured flush step needs no per-step argument.
+__global__ void gather_next_slots_kernel(const int32_t* __restrict__ page_table, int table_stride, const int32_t* __restrict__ n_pages,
+                                         int batch, int n, int32_t* __restrict__ slots_out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < batch * n) {
+    const int b = i / n, j = i % n;
+    slots_out[i] = page_table[(int64_t)b * table_stride + n_pages[b] + j];
+  }
+}
+
 }  // namespace bmxk
 
 extern "C" {
@@ -258,6 +299,24 @@ int bmxk_step_ingest(const void* q_src, void* q_dst, int n_q_groups, const void*
       (const __half*)q_src, (__half*)q_dst, n_q_groups, (const __half*)k_post, (const __half*)v, (const __half*)k_src, stride_seq, stride_head,
       (__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_len, counters, status, h_kv, tail_cap);
   return check_launch("bmxk_step_ingest");
+}
+
+int bmxk_window_shift(void* k_win, void* v_win, void* k_src_win, int batch, int h_kv, int tail_cap, int off, int rest,
+                      int32_t* tail_len, int32_t* n_pages, int pages_added, void* stream) {
+  BMXK_REQUIRE(k_win && v_win && k_src_win && tail_len, "bmxk_window_shift: null pointer");
+  BMXK_REQUIRE(batch >= 1 && h_kv >= 1 && tail_cap >= 1 && off >= 0 && rest >= 0 && off + rest <= tail_cap,
+               "bmxk_window_shift: batch=%d h_kv=%d tail_cap=%d off=%d rest=%d", batch, h_kv, tail_cap, off, rest);
+  window_shift_kernel<<<batch * h_kv, 256, 0, (cudaStream_t)stream>>>((__half*)k_win, (__half*)v_win, (__half*)k_src_win, tail_cap, off, rest,
+                                                                     h_kv, tail_len, n_pages, pages_added);
+  return check_launch("bmxk_window_shift");
+}
+
+int bmxk_gather_next_slots(const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch, int n, int32_t* slots_out,
+                           void* stream) {
+  BMXK_REQUIRE(page_table && n_pages && slots_out, "bmxk_gather_next_slots: null pointer");
+  BMXK_REQUIRE(batch >= 1 && n >= 1 && table_stride >= n, "bmxk_gather_next_slots: batch=%d n=%d table_stride=%d", batch, n, table_stride);
+  gather_next_slots_kernel<<<(batch * n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(page_table, table_stride, n_pages, batch, n, slots_out);
+  return check_launch("bmxk_gather_next_slots");
 }
 
 }  // extern "C"

@@ -158,11 +158,8 @@ class K2bLayerState:
             self._commit_pages(self.k_pre_win if self.pre_rope else self.k_win, self.v_win, n_flush)
             off = n_flush * self.page
             rest = self.tail_len - off
-            wins = [self.k_win, self.v_win] + ([] if self.k_pre_win is self.k_win else [self.k_pre_win])
-            for wbuf in wins:
-                wbuf[:, :, :rest] = wbuf[:, :, off:off + rest].clone()
+            K.window_shift(self.k_win, self.v_win, self.k_pre_win, off, rest, self.tail_len_dev)  # one launch, sets the device-side length
             self.tail_len = rest
-            self.tail_len_dev.fill_(rest)
             return
         # general path: window ++ new tokens, commit whole pages, keep the rest as the new window
         t = self.tail_len
@@ -559,6 +556,12 @@ class DecodeStepGraph:
         self.graph: torch.cuda.CUDAGraph | None = None
         self._captured_for = None  # (max_pages, pool identity): a pool that grew invalidates the captured pointers
         self._check_key = True     # pools and tables only change on the steps that go through append()
+        # the step that commits pages, as a graph of its own (k2b states): slots are looked up on the device, so it has no
+        # per-step argument either; valid for one (pages committed, tokens left in the window) pair and one set of pools
+        self.flush_graph: torch.cuda.CUDAGraph | None = None
+        self._flush_captured_for = None
+        self._slots = torch.zeros(B * 4, dtype=torch.int32, device=state.device)
+        self.flush_replays = 0
 
     def _launches(self) -> None:
         st = self.state
@@ -572,6 +575,17 @@ class DecodeStepGraph:
                                st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))
         st.decode(self.q, out=self.out)
         self.hout.copy_(self.out, non_blocking=True)
+
+    def _flush_launches(self, n_flush: int, off: int, rest: int) -> None:
+        """Token in, n_flush pages quantized straight out of the windows into the next slots of every sequence, windows
+        shifted, decode: the launches of append() + decode() on a flush step, with nothing that depends on the step."""
+        st = self.state
+        K.step_ingest(self.h_q, self.q, self.h_k_post, self.h_v, self.h_k_pre if st.pre_rope else self.h_k_post, st.k_win, st.v_win,
+                      st.k_pre_win, st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))
+        slots = K.gather_next_slots(st.page_table, st.n_pages_dev, n_flush, self._slots)[: st.batch * n_flush]
+        K.k2b_append(st.pool, st.k_pre_win if st.pre_rope else st.k_win, st.v_win, st.basis_f32, st.signs, st.codebook, slots, n_flush)
+        K.window_shift(st.k_win, st.v_win, st.k_pre_win, off, rest, st.tail_len_dev, st.n_pages_dev, n_flush)
+        st.decode(self.q, out=self.hout)
 
     def _key(self):
         st = self.state
@@ -587,7 +601,24 @@ class DecodeStepGraph:
         """Runs one step on the current stream; the caller synchronizes the stream before reading hout."""
         st = self.state
         total = st.committed + st.tail_len + 1
-        if compute_flush_schedule(total, st.W, st.page) > st.committed:  # pages are committed on this step: eager path
+        new_commit = compute_flush_schedule(total, st.W, st.page)
+        if new_commit > st.committed:  # pages are committed on this step
+            n_flush = (new_commit - st.committed) // st.page
+            off, rest = n_flush * st.page, st.tail_len + 1 - n_flush * st.page
+            fits = st.committed // st.page + n_flush <= st.max_pages and n_flush <= 4 and st.tail_len < st.tail_cap
+            if self.zero_copy and st.basis_f32 is not None and st.project is None and fits:
+                want = (self._key(), n_flush, off, rest)
+                if self.flush_graph is not None and self._flush_captured_for == want:
+                    self.flush_graph.replay()
+                    self.flush_replays += 1
+                else:  # once for real, then captured for the flush steps to come
+                    self._flush_launches(n_flush, off, rest)
+                    torch.cuda.current_stream().synchronize()
+                    self.flush_graph, self._flush_captured_for = torch.cuda.CUDAGraph(), want
+                    with torch.cuda.graph(self.flush_graph):
+                        self._flush_launches(n_flush, off, rest)
+                st.committed, st.tail_len = new_commit, rest
+                return
             self.din.copy_(self.hin, non_blocking=True)
             st.append(self.k_pre, self.k_post, self.v)
             st.decode(self.q, out=self.out)

@@ -354,6 +354,27 @@ def window_append_devpos(k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Ten
          _stream())
 
 
+def gather_next_slots(page_table: torch.Tensor, n_pages: torch.Tensor, n: int, out: torch.Tensor) -> torch.Tensor:
+    """out[s * n + i] = page_table[s, n_pages[s] + i] (device-side lookup of the next n pages' slots of every sequence)."""
+    _require_cuda(page_table, n_pages, out)
+    assert page_table.dtype == n_pages.dtype == out.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
+    batch = page_table.shape[0]
+    assert out.numel() >= batch * n and out.is_contiguous()
+    call("bmxk_gather_next_slots", _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, int(n), _ptr(out), _stream())
+    return out
+
+
+def window_shift(k_win: torch.Tensor, v_win: torch.Tensor, k_src_win: torch.Tensor, off: int, rest: int, tail_len: torch.Tensor,
+                 n_pages: torch.Tensor | None = None, pages_added: int = 0) -> None:
+    """Moves tokens [off, off + rest) of every (sequence, head) window to the front (one launch for the three windows),
+    sets the device-side window length to rest and adds pages_added to the device-side page counts."""
+    _require_cuda(k_win, v_win, k_src_win, tail_len, n_pages)
+    assert k_win.is_contiguous() and v_win.is_contiguous() and k_src_win.is_contiguous() and k_win.shape == v_win.shape == k_src_win.shape
+    batch, h_kv, tail_cap = k_win.shape[0], k_win.shape[1], k_win.shape[2]
+    call("bmxk_window_shift", _ptr(k_win), _ptr(v_win), _ptr(k_src_win), batch, h_kv, tail_cap, int(off), int(rest), _ptr(tail_len),
+         _ptr(n_pages), int(pages_added), _stream())
+
+
 def step_ingest(q_src: torch.Tensor, q_dst: torch.Tensor, k_post: torch.Tensor, v: torch.Tensor, k_src: torch.Tensor,
                 k_win: torch.Tensor, v_win: torch.Tensor, k_src_win: torch.Tensor, tail_len: torch.Tensor, counters: torch.Tensor,
                 status: torch.Tensor | None = None) -> None:

@@ -351,6 +351,18 @@ int bmxk_window_append_devpos(const void* k_post, const void* v, const void* k_s
                               int64_t stride_head, void* k_win, void* v_win, void* k_src_win, int32_t* tail_len,
                               int32_t* counters, int32_t* status, int batch, int h_kv, int tail_cap, void* stream);
 
+/* After pages were committed out of the windows: the remaining tokens [off, off + rest) of every (sequence, head) move to
+ * the front of the three windows in one launch, tail_len[s] becomes rest and, when n_pages is not NULL, n_pages[s] grows by
+ * pages_added.  bmx slices its tail tensors instead (src/bmx/cache/packed_streaming.py:700-730).  k_src_win may be k_win. */
+int bmxk_window_shift(void* k_win, void* v_win, void* k_src_win, int batch, int h_kv, int tail_cap, int off, int rest,
+                      int32_t* tail_len, int32_t* n_pages, int pages_added, void* stream);
+
+/* slots_out[s * n + i] = page_table[s][n_pages[s] + i]: the pool slots of the next n pages of every sequence, read on the
+ * device (page counts are device-resident), so that a flush step -- token in, pages quantized out of the windows into
+ * these slots, windows shifted, decode -- has no per-step argument and replays as a CUDA graph like any other step. */
+int bmxk_gather_next_slots(const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch, int n,
+                           int32_t* slots_out, void* stream);
+
 /* A decode step's inputs in one launch (no counterpart in bmx, whose step starts from device tensors): the append of
  * bmxk_window_append_devpos for fp16 sources, plus the step's queries q_src (batch, h_kv*n_q_groups, 128) fp16 staged
  * into q_dst.  q_src, k_post, v and k_src may be PINNED HOST memory (cudaHostAlloc / torch pin_memory: mapped into the

@@ -102,8 +102,8 @@ def test_token_by_token_equals_bulk_and_prefix_is_frozen(page, dtype):
         assert np.all(err <= 2e-3), float(err.max())
 
 
-@pytest.mark.parametrize("zero_copy", [True, False])
-def test_decode_step_graph_equals_eager_steps(zero_copy):
+@pytest.mark.parametrize("zero_copy,room", [(True, 3), (False, 3), (True, 8)])
+def test_decode_step_graph_equals_eager_steps(zero_copy, room):
     """The captured step replayed token after token gives the outputs and the state of append() + decode() called per
     token, across flushes and a pool that grows.  zero_copy: the ingest kernel reads the pinned staging buffer itself and
     the merge kernel stores into the pinned output; otherwise copy nodes move both."""
@@ -131,7 +131,7 @@ def test_decode_step_graph_equals_eager_steps(zero_copy):
     geom = K.k2b_geom(h_kv, G, page, rank, group, h_kv)
 
     def fresh():
-        st = K2bLayerState(geom, B, 3 * page, W, dev, cos.half(), sin.half())  # room for 3 pages: the fourth makes it grow
+        st = K2bLayerState(geom, B, room * page, W, dev, cos.half(), sin.half())  # room for 3 pages: the fourth makes it grow
         st.set_basis(basis.to(dev))
         st.append(k_pre[:, :, :prefix], k_post[:, :, :prefix], v[:, :, :prefix])
         return st
@@ -160,7 +160,11 @@ def test_decode_step_graph_equals_eager_steps(zero_copy):
         assert torch.equal(hout, ref.cpu()), f"step {i}"
     K.check_status(graphed.workspace)
     assert replays > steps // 2, "most steps must have gone through the captured graph"
-    assert graphed.committed // page >= 4, "the pool had to grow during the run"
+    assert graphed.committed // page >= 4, "two pages were committed during the run (with room for 3, the pool had to grow)"
+    assert torch.equal(graphed.n_pages_dev.cpu(), eager.n_pages_dev.cpu())
+    if zero_copy:  # flush steps are graphs too: the first one that fits the pool runs for real and is captured, later ones replay
+        assert stepper.flush_graph is not None
+        assert stepper.flush_replays == (1 if room == 8 else 0)
 
 
 @pytest.mark.parametrize("kind", ["k2b", "spectral"])
