@@ -5,8 +5,10 @@ what dominates a decode step end to end, not the kernel (bmx: docs/2026-07-05-au
 scripts/profile_decode_ab.py:316-439).  Here a single-token forward has nothing that depends on the step: the token's
 position, the window lengths and the page counts live in device memory, so the model's forward -- every layer's
 projections, the window append, the fused decode attention, the MLP, the head -- is captured once and replayed per token.
-Steps on which the flush schedule commits a page (one in `page`) run through the ordinary eager path, after which the
-graph is still valid (same pools) or is captured again (a pool or the shared RoPE table grew).
+Steps on which the flush schedule commits a page (one in `page`) are a second graph for k2b caches (the slots of the new
+pages are looked up on the device, the pages are quantized out of the windows, one kernel shifts the windows); other caches,
+the first commit of a sequence (it freezes the key basis) and commits that make a pool grow run through the ordinary
+eager path, after which the graphs are still valid (same pools) or are captured again.
 """
 
 from __future__ import annotations
@@ -21,6 +23,9 @@ class GraphedDecoder:
     def __init__(self, model, cache):
         self.model, self.cache = model, cache
         self.graph: torch.cuda.CUDAGraph | None = None
+        self.flush_graph: torch.cuda.CUDAGraph | None = None
+        self._flush_key = None
+        self.flush_replays = 0
         self._key = None
         self.ids = self.pos = self.mask = self.logits = None
         self.replays = self.eager_steps = self.captures = 0
@@ -50,9 +55,23 @@ class GraphedDecoder:
         """input_ids: (batch, 1).  Returns the logits of the new position, (batch, vocab); valid until the next step."""
         layers = self._layers()
         assert layers and layers[0]._state is not None, "run the prompt through the model first"
-        if any(l.next_step_flushes() for l in layers):
-            return self._eager(input_ids)  # this step commits pages: append kernels, host-side slot bookkeeping
         S = layers[0].get_seq_length()
+        if any(l.next_step_flushes() for l in layers):
+            plans = [l.graph_flush_plan() for l in layers]
+            rope_ok = all(l._state.rope_cos is None or S + 2 <= l._state.rope_cos.shape[0] for l in layers)
+            if self.ids is None or not rope_ok or any(p is None for p in plans) or len(set(plans)) != 1:
+                return self._eager(input_ids)  # the first commit (basis fit), a growing pool, another codec: the ordinary path
+            key = (self._state_key(), plans[0])
+            if self.flush_graph is None or self._flush_key != key:
+                self._capture(flush=plans[0])
+                self._flush_key = key
+            self.ids.copy_(input_ids)
+            self.pos.fill_(S)
+            self.flush_graph.replay()
+            for l in layers:
+                l.advance_after_graph_flush(plans[0])
+            self.flush_replays += 1
+            return self.flush_logits
         need_rope = any(l._state.rope_cos is not None and S + 2 > l._state.rope_cos.shape[0] for l in layers)
         if need_rope or self.ids is None:
             # an ordinary step first: lazy one-time initialisation and a growing RoPE table stay outside any capture
@@ -73,18 +92,22 @@ class GraphedDecoder:
         self.replays += 1
         return self.logits
 
-    def _capture(self) -> None:
-        """Captures one single-token forward.  Capturing executes nothing: the step counters are not advanced."""
+    def _capture(self, flush=None) -> None:
+        """Captures one single-token forward (flush: the commit every layer makes on that step, for the second graph).
+        Capturing executes nothing: the step counters are not advanced."""
         layers = self._layers()
         torch.cuda.current_stream().synchronize()
         for l in layers:
-            l._graph_mode = True
+            l._graph_mode, l._graph_flush = True, flush
         try:
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.no_grad(), torch.cuda.graph(self.graph):
-                self.logits = self._forward()
+            graph = torch.cuda.CUDAGraph()
+            with torch.no_grad(), torch.cuda.graph(graph):
+                logits = self._forward()
         finally:
             for l in layers:
-                l._graph_mode = False
-        self._key = self._state_key()
+                l._graph_mode, l._graph_flush = False, None
+        if flush is None:
+            self.graph, self.logits, self._key = graph, logits, self._state_key()
+        else:
+            self.flush_graph, self.flush_logits = graph, logits
         self.captures += 1

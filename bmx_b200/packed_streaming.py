@@ -203,6 +203,8 @@ class PackedStreamingLayer(DynamicLayer):
         self._state: K2bLayerState | None = None
         self._batch = 0
         self._graph_mode = False  # set by GraphedDecoder around a captured / replayed single-token step
+        self._graph_flush = None  # (pages, offset, tokens left) while GraphedDecoder captures a step that commits pages
+        self._slots: torch.Tensor | None = None
 
     # ---- hooks ----------------------------------------------------------------------------------
     def stash_pre_rope(self, out: torch.Tensor) -> None:
@@ -262,9 +264,17 @@ class PackedStreamingLayer(DynamicLayer):
         st.append(k_pre, key_states.to(torch.float16), value_states.to(torch.float16))
         if st.basis_f32 is not None and self._frozen_svd is None:
             self._frozen_svd = (None, st.basis_f32)
-        # accounting: every newly committed page is charged the codec's bits per entry, the window 16 bits
+        self._account(before)
+        self.keys = st.k_win[:, :, : st.tail_len]
+        self.values = st.v_win[:, :, : st.tail_len]
+        return self.keys, self.values
+
+    def _account(self, committed_before: int) -> None:
+        """Bookkeeping after tokens were appended: every newly committed page is charged the codec's bits per entry, the
+        window 16 bits (bmx: src/bmx/cache/packed_streaming.py:680-730)."""
+        st = self._state
         C = self._h_kv * self._d_head
-        for pg0 in range(before, st.committed, self._page):
+        for pg0 in range(committed_before, st.committed, self._page):
             entries = self._page * C
             if self._kind == "spectral":  # mean bits + scales of the directions that carry any (bmx: spectral.py:602-615)
                 bits = self._pack.bits.float()
@@ -282,9 +292,6 @@ class PackedStreamingLayer(DynamicLayer):
         if S > 0:
             self.bpe_k = (self._quant_bits_k + st.tail_len * C * 16.0) / (S * C)
             self.bpe_v = (self._quant_bits_v + st.tail_len * C * 16.0) / (S * C)
-        self.keys = st.k_win[:, :, : st.tail_len]
-        self.values = st.v_win[:, :, : st.tail_len]
-        return self.keys, self.values
 
     def _update_graph_step(self, key_states: torch.Tensor, value_states: torch.Tensor):
         """The single-token, no-flush case of update() with nothing that depends on the step: the token goes into the
@@ -301,6 +308,13 @@ class PackedStreamingLayer(DynamicLayer):
             k_src = k_post
         K.window_append_devpos(k_post, v, k_src, st.k_win, st.v_win, st.k_pre_win, st.tail_len_dev, st.append_cnt,
                                st.workspace.view(torch.int32))
+        if self._graph_flush is not None:  # this step commits pages: slots looked up on the device, pages quantized out of the windows
+            n_flush, off, rest = self._graph_flush
+            if self._slots is None:
+                self._slots = torch.zeros(st.batch * 4, dtype=torch.int32, device=st.device)
+            slots = K.gather_next_slots(st.page_table, st.n_pages_dev, n_flush, self._slots)[: st.batch * n_flush]
+            K.k2b_append(st.pool, st.k_pre_win if st.pre_rope else st.k_win, st.v_win, st.basis_f32, st.signs, st.codebook, slots, n_flush)
+            K.window_shift(st.k_win, st.v_win, st.k_pre_win, off, rest, st.tail_len_dev, st.n_pages_dev, n_flush)
         return st.k_win, st.v_win  # the attention function reads the packed state, not these
 
     def advance_after_graph_step(self) -> None:
@@ -310,6 +324,28 @@ class PackedStreamingLayer(DynamicLayer):
         C, S = self._h_kv * self._d_head, st.seq_len()
         self.bpe_k = (self._quant_bits_k + st.tail_len * C * 16.0) / (S * C)
         self.bpe_v = (self._quant_bits_v + st.tail_len * C * 16.0) / (S * C)
+        self.keys, self.values = st.k_win[:, :, : st.tail_len], st.v_win[:, :, : st.tail_len]
+
+    def graph_flush_plan(self):
+        """(pages, offset, tokens left) of the commit the next single-token step makes, if that step can run without any
+        per-step host argument (k2b pages, basis frozen, room in the pool); None if the step commits nothing or has to run
+        eagerly."""
+        st = self._state
+        if st is None or self._kind != "k2b" or type(st) is not K2bLayerState or st.basis_f32 is None or st.project is not None:
+            return None
+        new_commit = compute_flush_schedule(st.seq_len() + 1, self.recent_window, self._page)
+        n_flush = (new_commit - st.committed) // self._page
+        if n_flush < 1 or n_flush > 4 or st.committed // self._page + n_flush > st.max_pages or st.tail_len >= st.tail_cap:
+            return None
+        return n_flush, n_flush * self._page, st.tail_len + 1 - n_flush * self._page
+
+    def advance_after_graph_flush(self, plan) -> None:
+        """Host-side bookkeeping of one replayed step that committed pages."""
+        st = self._state
+        n_flush, _, rest = plan
+        before = st.committed
+        st.committed, st.tail_len = before + n_flush * self._page, rest
+        self._account(before)
         self.keys, self.values = st.k_win[:, :, : st.tail_len], st.v_win[:, :, : st.tail_len]
 
     def next_step_flushes(self) -> bool:
