@@ -135,6 +135,18 @@ class K2bLayerState:
         self.committed += n_pages * self.page
         self.n_pages_dev.fill_(self.committed // self.page)
 
+    # ---- committing pages with device-side arguments only (steps replayed as CUDA graphs) --------------------
+    @property
+    def graph_commit_ok(self) -> bool:
+        """True when commit_from_windows() needs nothing from the host: the basis is frozen and projected by the kernel."""
+        return self.basis_f32 is not None and self.project is None
+
+    def commit_from_windows(self, slots: torch.Tensor, n_pages: int) -> None:
+        """Quantizes the first n_pages pages held in the windows into `slots` (device int32, sequence-major).  Launches
+        only: counters and windows are advanced by the caller (window_shift on the device, committed / tail_len on the host)."""
+        K.k2b_append(self.pool, self.k_pre_win if self.pre_rope else self.k_win, self.v_win, self.basis_f32, self.signs, self.codebook,
+                     slots, n_pages)
+
     def append(self, k_pre: torch.Tensor | None, k_post: torch.Tensor, v: torch.Tensor) -> None:
         """Appends n new tokens per sequence: (batch, h_kv, n, 128) tensors (fp16 or bf16).
 
@@ -315,6 +327,12 @@ class SpectralLayerState(K2bLayerState):
         self.committed += n_pages * self.page
         self.n_pages_dev.fill_(self.committed // self.page)
 
+    graph_commit_ok = True  # the pack is fitted offline: a commit needs nothing from the host
+
+    def commit_from_windows(self, slots: torch.Tensor, n_pages: int) -> None:
+        K.spectral_append(self.pack, self.kpool, self.k_pre_win, slots, n_pages)
+        K.vblock_append(self.vpool, self.v_win, self.signs, self.codebook, slots, n_pages)
+
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
                phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
         max_pages = self.max_pages if self.committed else 0
@@ -385,6 +403,8 @@ class FullSpectralLayerState(SpectralLayerState):
         K.vblock_append(self.vpool, v_src, self.signs, self.codebook, slots, n_pages)
         self.committed += n_pages * self.page
         self.n_pages_dev.fill_(self.committed // self.page)
+
+    graph_commit_ok = False  # the encoder product is a library GEMM with temporaries: commits run through append()
 
     def _dense_chunk(self, p0: int, p1: int) -> tuple[torch.Tensor, torch.Tensor]:
         """Pages p0 .. p1-1 of every sequence: pre-RoPE keys and values, float32 (batch, h_kv, tokens, 128)."""
@@ -491,6 +511,11 @@ class RtnLayerState(K2bLayerState):
         self.committed += n_pages * self.page
         self.n_pages_dev.fill_(self.committed // self.page)
 
+    graph_commit_ok = True
+
+    def commit_from_windows(self, slots: torch.Tensor, n_pages: int) -> None:
+        K.rtn_append(self.pool, self.k_win, self.v_win, slots, n_pages)
+
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, partial_out: torch.Tensor | None = None,
                phases: int = 3, pos_offset: int = 0) -> torch.Tensor:
         """q (batch, heads, 128) fp16 -> attention output over RTN pages + window (keys carry their rotation already, so
@@ -546,9 +571,8 @@ class DecodeStepGraph:
         self.v = self.din[nq + nk:nq + 2 * nk].view(B, h_kv, 1, HEAD_DIM)
         self.k_pre = self.din[nq + 2 * nk:].view(B, h_kv, 1, HEAD_DIM)
         self.out = torch.empty(B, heads, HEAD_DIM, dtype=torch.float16, device=state.device)
-        # the kernels read the pinned staging buffer and write the pinned output themselves (k2b states: the other decode
-        # wrappers take device outputs)
-        self.zero_copy = zero_copy and type(state) is K2bLayerState
+        # the kernels read the pinned staging buffer and write the pinned output themselves
+        self.zero_copy = zero_copy
         self.h_q = hin[:nq].view(B, heads, HEAD_DIM)
         self.h_k_post = hin[nq:nq + nk].view(B, h_kv, 1, HEAD_DIM)
         self.h_v = hin[nq + nk:nq + 2 * nk].view(B, h_kv, 1, HEAD_DIM)
@@ -556,7 +580,7 @@ class DecodeStepGraph:
         self.graph: torch.cuda.CUDAGraph | None = None
         self._captured_for = None  # (max_pages, pool identity): a pool that grew invalidates the captured pointers
         self._check_key = True     # pools and tables only change on the steps that go through append()
-        # the step that commits pages, as a graph of its own (k2b states): slots are looked up on the device, so it has no
+        # the step that commits pages, as a graph of its own: slots are looked up on the device, so it has no
         # per-step argument either; valid for one (pages committed, tokens left in the window) pair and one set of pools
         self.flush_graph: torch.cuda.CUDAGraph | None = None
         self._flush_captured_for = None
@@ -583,7 +607,7 @@ class DecodeStepGraph:
         K.step_ingest(self.h_q, self.q, self.h_k_post, self.h_v, self.h_k_pre if st.pre_rope else self.h_k_post, st.k_win, st.v_win,
                       st.k_pre_win, st.tail_len_dev, st.append_cnt, st.workspace.view(torch.int32))
         slots = K.gather_next_slots(st.page_table, st.n_pages_dev, n_flush, self._slots)[: st.batch * n_flush]
-        K.k2b_append(st.pool, st.k_pre_win if st.pre_rope else st.k_win, st.v_win, st.basis_f32, st.signs, st.codebook, slots, n_flush)
+        st.commit_from_windows(slots, n_flush)
         K.window_shift(st.k_win, st.v_win, st.k_pre_win, off, rest, st.tail_len_dev, st.n_pages_dev, n_flush)
         st.decode(self.q, out=self.hout)
 
@@ -606,7 +630,7 @@ class DecodeStepGraph:
             n_flush = (new_commit - st.committed) // st.page
             off, rest = n_flush * st.page, st.tail_len + 1 - n_flush * st.page
             fits = st.committed // st.page + n_flush <= st.max_pages and n_flush <= 4 and st.tail_len < st.tail_cap
-            if self.zero_copy and st.basis_f32 is not None and st.project is None and fits:
+            if self.zero_copy and st.graph_commit_ok and fits:
                 want = (self._key(), n_flush, off, rest)
                 if self.flush_graph is not None and self._flush_captured_for == want:
                     self.flush_graph.replay()

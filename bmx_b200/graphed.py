@@ -5,10 +5,10 @@ what dominates a decode step end to end, not the kernel (bmx: docs/2026-07-05-au
 scripts/profile_decode_ab.py:316-439).  Here a single-token forward has nothing that depends on the step: the token's
 position, the window lengths and the page counts live in device memory, so the model's forward -- every layer's
 projections, the window append, the fused decode attention, the MLP, the head -- is captured once and replayed per token.
-Steps on which the flush schedule commits a page (one in `page`) are a second graph for k2b caches (the slots of the new
-pages are looked up on the device, the pages are quantized out of the windows, one kernel shifts the windows); other caches,
-the first commit of a sequence (it freezes the key basis) and commits that make a pool grow run through the ordinary
-eager path, after which the graphs are still valid (same pools) or are captured again.
+Steps on which the flush schedule commits a page (one in `page`) are a second graph (the slots of the new pages are
+looked up on the device, the pages are quantized out of the windows, one kernel shifts the windows); the first commit of
+a k2b sequence (it freezes the key basis), commits that make a pool grow and spectral packs that mix heads run through the
+ordinary eager path, after which the graphs are still valid (same pools) or are captured again.
 """
 
 from __future__ import annotations

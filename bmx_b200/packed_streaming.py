@@ -313,7 +313,7 @@ class PackedStreamingLayer(DynamicLayer):
             if self._slots is None:
                 self._slots = torch.zeros(st.batch * 4, dtype=torch.int32, device=st.device)
             slots = K.gather_next_slots(st.page_table, st.n_pages_dev, n_flush, self._slots)[: st.batch * n_flush]
-            K.k2b_append(st.pool, st.k_pre_win if st.pre_rope else st.k_win, st.v_win, st.basis_f32, st.signs, st.codebook, slots, n_flush)
+            st.commit_from_windows(slots, n_flush)
             K.window_shift(st.k_win, st.v_win, st.k_pre_win, off, rest, st.tail_len_dev, st.n_pages_dev, n_flush)
         return st.k_win, st.v_win  # the attention function reads the packed state, not these
 
@@ -328,10 +328,10 @@ class PackedStreamingLayer(DynamicLayer):
 
     def graph_flush_plan(self):
         """(pages, offset, tokens left) of the commit the next single-token step makes, if that step can run without any
-        per-step host argument (k2b pages, basis frozen, room in the pool); None if the step commits nothing or has to run
-        eagerly."""
+        per-step host argument (the state can commit out of its windows, room in the pool); None if the step commits nothing
+        or has to run eagerly."""
         st = self._state
-        if st is None or self._kind != "k2b" or type(st) is not K2bLayerState or st.basis_f32 is None or st.project is not None:
+        if st is None or not st.graph_commit_ok:
             return None
         new_commit = compute_flush_schedule(st.seq_len() + 1, self.recent_window, self._page)
         n_flush = (new_commit - st.committed) // self._page
