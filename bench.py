@@ -297,6 +297,7 @@ def run_ours(args, rank, world, local_rank):
 
         # a rank that fails leaves the others in a collective: give up after two minutes, not the default ten
         dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=120))
+    clocks = ClockSampler(local_rank).__enter__()  # started before the workload is built: nvidia-smi needs a moment to print its first line
     state, q, gen, basis, (cos, sin) = build_state(device, seed=2000 + rank, ctx=args.ctx)
     from bmx_b200 import kernels as K
 
@@ -314,8 +315,6 @@ def run_ours(args, rank, world, local_rank):
     # samples printed between the first warm-up step and the end of that tail are the ones summarised.  The warm-up
     # BEFORE the timed steps is the W steps asked for and no more (on one box the same steps ran ~4 % slower after a long
     # pre-heating loop, with the sampled SM clock unchanged; on another they did not).
-    clocks = ClockSampler(local_rank).__enter__()
-    time.sleep(0.3)  # nvidia-smi needs a moment to print its first line
     t_load = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         state.decode(q, out=out)
