@@ -263,6 +263,35 @@ def test_decode_ragged_and_edge_cases():
     _assert_attn_close(out, ref)
 
 
+@pytest.mark.parametrize("sweep_seed", [1, 2])
+def test_decode_random_geometries(sweep_seed):
+    """Twenty geometries per seed drawn over every axis the path takes (page, rank, shared or per-head basis, residual
+    group, query heads per KV head, KV heads, ragged page counts, window lengths at and around the 64/128/256 edges),
+    each against the oracle on the pages the GPU stored."""
+    import random
+
+    dev, K = _dev(), _K()
+    rng = random.Random(sweep_seed)
+    worst = 0.0
+    for c in range(20):
+        page = rng.choice([64, 128])
+        n_seq = rng.randint(1, 5)
+        pages = [rng.choice([0, 1, 2, 3, 5, 9, 17]) for _ in range(n_seq)]
+        tails = [rng.choice([0, 1, 63, 64, 65, 127, 128, 129, 255, 256]) for _ in range(n_seq)]
+        tails = [max(t, 1) if p == 0 else t for p, t in zip(pages, tails)]  # a sequence holds at least one token
+        cfg = dict(n_seq=n_seq, h_kv=rng.choice([1, 2, 4, 8]), G=rng.choice([1, 2, 4, 8]), page=page,
+                   rank=rng.choice([16, 32]), per_head=rng.choice([True, False]),
+                   group=rng.choice([g for g in (32, 64, 128) if g <= page]),
+                   pages_per_seq=pages, tail_lens=tails, seed=1000 * sweep_seed + c)
+        out, ref = _decode_case(dev, K, **cfg)
+        try:
+            _assert_attn_close(out, ref)
+        except AssertionError as e:
+            raise AssertionError(f"{cfg}: {e}") from None
+        worst = max(worst, float((np.abs(out - ref).max(-1) / np.abs(ref).max(-1)).max()))
+    print(f"seed {sweep_seed}: worst relative error over 20 geometries {worst:.2e}")
+
+
 @pytest.mark.parametrize("layout", [0, 1])
 def test_decode_both_page_layouts(layout):
     """128-token pages can be stored in either byte order; each order has its own decode kernel (0: mma.sync,

@@ -121,6 +121,31 @@ def test_decode_matches_oracle(page, k_arm, kg, vg, G):
     _close(out, ref)
 
 
+def test_decode_random_geometries():
+    """Sixteen geometries drawn over page, key arm, group sizes, code width, KV heads, query heads per KV head, ragged
+    page counts and window lengths around the 64/128/256 edges, each against the oracle."""
+    import random
+
+    from bmx_b200 import kernels as K
+    rng, dev, worst = random.Random(5), _dev(), 0.0
+    for c in range(16):
+        page, n_seq = rng.choice([64, 128]), rng.randint(1, 5)
+        pages = [rng.choice([0, 1, 2, 3, 5, 9, 17]) for _ in range(n_seq)]
+        tails = [rng.choice([0, 1, 63, 64, 65, 127, 128, 129, 255, 256]) for _ in range(n_seq)]
+        tails = [max(t, 1) if p == 0 else t for p, t in zip(pages, tails)]  # a sequence holds at least one token
+        cfg = dict(page=page, k_arm=rng.choice(["rtn_channel", "rtn_token"]),
+                   kg=rng.choice([g for g in (32, 64, 128) if g <= page]), vg=rng.choice([32, 64, 128]),
+                   G=rng.choice([1, 2, 4, 8]), pages_per_seq=pages, tail_lens=tails, seed=2000 + c,
+                   h_kv=rng.choice([1, 2, 4, 8]), kbits=rng.choice([2, 3, 4]))
+        out, ref = _decode_case(K, dev, **cfg)
+        try:
+            _close(out, ref)
+        except AssertionError as e:
+            raise AssertionError(f"{cfg}: {e}") from None
+        worst = max(worst, float((np.abs(out - ref).max(-1) / np.abs(ref).max(-1)).max()))
+    print(f"worst relative error over 16 geometries {worst:.2e}")
+
+
 def test_first_baseline_config_shape():
     """Benchmark configuration 1: 8 KV heads, GQA 4, T = 4096 + 128-token window, K rtn_channel 4b, V rtn_token 2b, g = 32."""
     from bmx_b200 import kernels as K

@@ -164,6 +164,34 @@ def test_spectral_decode_matches_oracle(tiers, group, G, dec8):
     _assert_attn_close(out, ref)
 
 
+def test_spectral_decode_random_geometries():
+    """Sixteen geometries with random tier tables (widths 8/6/5/4/3/2 in ragged counts, the rest 0 bits), scale groups,
+    KV heads (3 included), query heads per KV head, ragged page counts and window lengths around the 64/128/256 edges."""
+    import random
+
+    rng, dev, worst = random.Random(9), _dev(), 0.0
+    for c in range(16):
+        left, tiers = D, {}
+        for b in (8, 6, 5, 4, 3, 2):
+            if left > 0 and rng.random() < 0.7:
+                tiers[b] = rng.randint(1, max(1, left // 2))
+                left -= tiers[b]
+        tiers = tiers or {4: 32}
+        n_seq = rng.randint(1, 5)
+        pages = [rng.choice([0, 1, 2, 3, 5, 9, 17]) for _ in range(n_seq)]
+        tails = [rng.choice([0, 1, 63, 64, 65, 127, 128, 129, 255, 256]) for _ in range(n_seq)]
+        tails = [max(t, 1) if p == 0 else t for p, t in zip(pages, tails)]  # a sequence holds at least one token
+        cfg = dict(n_seq=n_seq, h_kv=rng.choice([1, 2, 3, 4, 8]), G=rng.choice([1, 2, 4, 8]), group=rng.choice([32, 64, 128]),
+                   tier_counts=tiers, pages_per_seq=pages, tail_lens=tails, seed=3000 + c, dec8=rng.random() < 0.3)
+        out, ref = _case(dev, **cfg)
+        try:
+            _assert_attn_close(out, ref)
+        except AssertionError as e:
+            raise AssertionError(f"{cfg}: {e}") from None
+        worst = max(worst, float((np.abs(out - ref).max(-1) / np.abs(ref).max(-1)).max()))
+    print(f"worst relative error over 16 geometries {worst:.2e}")
+
+
 def test_spectral_decode_ragged_and_many_ranges():
     dev = _dev()
     # empty sequences, no window, more (sequence, head) ranges than CTAs can take one each
