@@ -72,6 +72,7 @@ _SIGNATURES = {
     "bmxk_k2b_prefill": (c_int, [POINTER(K2bGeom), c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
                                  c_void_p, c_void_p, c_void_p]),
+    "bmxk_k2b_prefill_select": (c_int, [c_int]),
     "bmxk_k2b_decode_static": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                         c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p]),

@@ -23,6 +23,7 @@ SOURCES = [
     ("k2b_decode.cu", []),
     ("k2b_decode_t5.cu", []),
     ("k2b_prefill.cu", []),
+    ("k2b_prefill_t5.cu", []),
     ("rtn.cu", ["-fmad=false"]),
     ("spectral.cu", ["-fmad=false"]),
     ("spectral_decode_t5.cu", []),

@@ -16,7 +16,7 @@
 // t <= p; window slots past tail_len are masked.
 #include <cstring>
 
-#include "decode_common.cuh"
+#include "prefill_common.cuh"
 
 namespace bmxk {
 
@@ -26,31 +26,6 @@ constexpr int PF_THREADS = 256;
 constexpr int KP = 136;  // halves per row of the dequantized K / V tiles: rows start 16 bytes apart modulo 128
 constexpr int BP = 40;   // halves per basis row (rank <= 32)
 
-struct PrefillParams {
-  K2bGeom g;
-  const __half* q;
-  int n_q;
-  int64_t q_pos0;
-  const uint8_t* pages;
-  const __half* coefs;
-  const __half* basis16;
-  const int32_t* page_table;
-  int table_stride;
-  const int32_t* n_pages;
-  const __half* rope_cos;
-  const __half* rope_sin;
-  int64_t pos_offset;
-  const __half* k_tail;
-  const __half* v_tail;
-  const int32_t* tail_len;
-  int tail_cap;
-  uint32_t lut_lo, lut_hi;
-  float lut_alpha, lut_beta;
-  const float* signs;
-  float scale_log2;
-  __half* out;
-  int32_t* status;
-};
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -418,7 +393,16 @@ size_t prefill_smem_bytes(int rank, int group) {
 
 using namespace bmxk;
 
+// 0: the tcgen05 kernel where its alignment needs are met, else the mma.sync kernel; 1: always the mma.sync kernel
+static int g_prefill_kernel = 0;
+
 extern "C" {
+
+int bmxk_k2b_prefill_select(int kernel) {
+  BMXK_REQUIRE(kernel == 0 || kernel == 1, "bmxk_k2b_prefill_select: kernel=%d (0: tcgen05 where it applies, 1: mma.sync)", kernel);
+  g_prefill_kernel = kernel;
+  return BMXK_OK;
+}
 
 int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
                      const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
@@ -458,6 +442,8 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
   const int pp = 128 / g->n_q_groups;
   const dim3 grid((unsigned)((n_q + pp - 1) / pp), (unsigned)g->h_kv, (unsigned)batch);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned16 = ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  if (g_prefill_kernel == 0 && aligned16) return launch_prefill_t5(prm, grid, s);
   static PerDeviceOnce configured;
   if (configured.first()) {
     cudaError_t e1 = cudaFuncSetAttribute(k2b_prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);

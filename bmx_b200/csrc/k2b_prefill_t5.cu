@@ -1,0 +1,675 @@
+// Paged dequant-prefill for the k2b cache on the sm_100a tensor-core path (tcgen05.mma + tensor memory).
+//
+// Same job and same grid as the mma.sync kernel of k2b_prefill.cu: one CTA owns 128 / G consecutive query positions
+// of one (sequence, KV head) -- 128 attention rows with the G query heads -- and walks the visible 128-token pages and
+// then the fp16 window.  Here the three contractions of a tile are tcgen05.mma instructions issued by one warp, the
+// attention rows live on the 128 lanes of tensor memory (one softmax thread per row: no reduction across threads),
+// and the dequantization of tile n+1 runs in its own warps while tile n is multiplied and normalised:
+//
+//   U1  K_low[128 tok x 128 ch]  = coef (smem, straight from the bulk copy) x basis^T (smem), fp16 accumulators
+//   key warps (8; thread = token, two chunks of 16 + 16 channels):
+//                                  K = K_low + scale * residual, rotated at the token's absolute position
+//                                  -> shared memory, as the B operand of U2 (double-buffered by tile parity).
+//                                  Two more "channels" carry log2(value norm) / scale as an fp16 pair (high part,
+//                                  remainder) against two ones in Q, so that the scores arrive with the norm in the
+//                                  exponent and the weights leave the softmax as p * norm with ONE rounding to fp16
+//   U2  S[128 rows x 128 tok]    = Q (smem) x K^T over 144 channels, fp32
+//   softmax warps (4; thread = row): running maximum in base 2 with a lazy rescale of the accumulator,
+//                                  weights -> tensor memory as fp16 (A operand of U3)
+//   value warps (8; thread = channel, warp = 64 tokens): 2-bit codes -> the four fp16 levels of the value table
+//                                  -> shared memory as the B operand of U3.  Rows 128 / 129 of that operand hold
+//                                  1 / norm as an fp16 pair and row 130 ones: the same contraction returns the sum
+//                                  of the weights p (to 2^-22, from the rounded weights the numerator uses) and the
+//                                  sum of p * norm (the affine term of the level table)
+//   U3  O[128 rows x 144]       += P (TMEM) x V^T, fp32
+//
+// The Hadamard rotation of the value codec is linear: it is undone once per row, in place in tensor memory, after
+// the last page and before the first window tile (whose values are not rotated).  Window tiles take the same route
+// with the key / value warps copying the fp16 window into the operand buffers (norm 1).
+//
+// Every wait is bounded and reports through the status words; nothing here waits on another CTA.
+#include "prefill_common.cuh"
+#include "tc5.cuh"
+
+namespace bmxk {
+
+namespace {
+
+constexpr int P5_THREADS = 768;  // warps 0-7 key, 8-11 softmax, 12 copies + every tcgen05.mma (13-15 idle), 16-23 value
+constexpr int P5_STAGES = 3;
+// Registers per thread after each group of four warps resizes itself; the pool is what the launch handed out.
+constexpr int P5_REG_LAUNCH = 80, P5_REG_KEY = 112, P5_REG_SOFTMAX = 112, P5_REG_SERVICE = 48, P5_REG_VALUE = 48;
+static_assert(8 * P5_REG_KEY + 4 * P5_REG_SOFTMAX + 4 * P5_REG_SERVICE + 8 * P5_REG_VALUE <= 24 * P5_REG_LAUNCH,
+              "register split exceeds the CTA's pool");
+// A [128 rows][144 K] fp16 operand in the unswizzled K-major form: 8-row x 16-byte core matrices, the 18 core matrices
+// of one row group 128 bytes apart along K, row groups 2304 bytes apart.  K index 128 / 129: the norm pair (see above).
+constexpr int OP_SBO = 18 * 128;
+constexpr int OP_BYTES = 16 * OP_SBO;
+constexpr int VROWS = 144;  // rows of the U3 operand: 128 channels, 1/norm (two rows), ones, 13 rows of zeros; K = 128 tokens
+constexpr int V_SBO = 16 * 128;
+constexpr int VOP_BYTES = (VROWS / 8) * V_SBO;
+constexpr float MIN_NORM = 9.765625e-4f;  // 2^-10: a zero value vector keeps a weight the fp16 pair can carry
+// TMEM columns: scores, weights (fp16 pairs), output accumulator (128 channels, sum of p in two parts, sum of p x norm, 13 unused), K_low
+constexpr uint32_t TM_S = 0, TM_P = 128, TM_O = 192, TM_KL = 336, TM_COLS = 512;
+
+struct P5Smem {
+  uint64_t full[P5_STAGES];          // raw tile landed (bulk copies)
+  uint64_t low, sdone[2], odone[2];  // completion of U1 / U2 / U3 (tcgen05.commit); U2 and U3 by tile parity
+  uint32_t tmem_base;
+  // Arrivals, never reset: key warps (8 per tile, counted per tile parity: a key warp may be two tiles ahead of another
+  // one, never two tiles of the same parity), value warps (8), scores read (4), weights written (4)
+  // klcnt: key warps that hold K_low of the tile in registers (U1 of the next tile may start)
+  int kcnt[2], klcnt[2], vcnt, scnt, pcnt;
+};
+
+__device__ __forceinline__ bool elect_one_p5() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
+
+// The bounded wait with one answer for the whole warp: what follows a wait is warp-wide (tcgen05.ld / st), so a warp
+// leaves its loop together or not at all.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int32_t* status, int where) {
+  return __all_sync(0xffffffffu, wait_or_flag(bar, parity, status, where) ? 1 : 0) != 0;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+}  // namespace
+
+template <int RANK>
+__global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const PrefillParams p) {
+  constexpr int KS = RANK / 16;
+  constexpr int COEF_BYTES = 128 * RANK * 2;
+  constexpr uint32_t AB_SBO = RANK * 16;  // bytes between 8-row groups of the coef / basis operands
+  extern __shared__ __align__(128) uint8_t smem[];
+  const K2bGeom g = p.g;
+  const int G = g.n_q_groups, PP = 128 / G;  // query positions per CTA
+  const int PB = k2b_page_block_bytes(128, g.group);
+  const int STAGE_BYTES = COEF_BYTES + PB;
+
+  uint8_t* stage0 = smem;                                  // [P5_STAGES][coefficient block | page block]
+  uint8_t* qop = stage0 + P5_STAGES * STAGE_BYTES;         // A of U2
+  uint8_t* kop0 = qop + OP_BYTES;                          // [2] B of U2
+  uint8_t* vop = kop0 + 2 * OP_BYTES;                      // B of U3
+  uint8_t* bop = vop + VOP_BYTES;                          // B of U1: this head's basis
+  float* sg = reinterpret_cast<float*>(bop + COEF_BYTES);  // [128] signs / 128
+  P5Smem* sh = reinterpret_cast<P5Smem*>(sg + 128);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the latest positions see the most pages: their blocks are scheduled first, so that the last wave is the lightest
+  const int b = blockIdx.z, h = blockIdx.y, i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * PP;
+  const int H = g.h_kv * G;
+
+  const int64_t pq_min = p.q_pos0 + i0;                                // first query position of the CTA
+  const int64_t pq_max = p.q_pos0 + min(i0 + PP, p.n_q) - 1;           // last one
+  const int n_pg = p.n_pages[b];
+  const int64_t vis = pq_max - p.pos_offset;
+  const int NP = (vis < 0) ? 0 : (int)min((int64_t)n_pg, vis / 128 + 1);  // pages whose first token the last position sees
+  const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
+  const int64_t tail_pos0 = p.pos_offset + (int64_t)n_pg * 128;
+  const int NW = (tl > 0 && pq_max >= tail_pos0) ? (int)((min((int64_t)tl, pq_max - tail_pos0 + 1) + 127) / 128) : 0;
+  const int NT = NP + NW;
+
+  // ---- prologue: barriers, tensor memory, the operands that do not change (Q, basis, constant rows of V') ----
+  if (tid == 0) {
+    for (int s = 0; s < P5_STAGES; ++s) mbar_init(&sh->full[s], 1);
+    mbar_init(&sh->low, 1);
+    for (int e = 0; e < 2; ++e) mbar_init(&sh->sdone[e], 1), mbar_init(&sh->odone[e], 1);
+    sh->kcnt[0] = sh->kcnt[1] = sh->klcnt[0] = sh->klcnt[1] = sh->vcnt = sh->scnt = sh->pcnt = 0;
+    fence_barrier_init();
+  }
+  if (warp == 12) {
+    tc5::alloc(smem_u32(&sh->tmem_base), TM_COLS);
+    tc5::relinquish();
+  }
+  for (int o = tid; o < 128 * 18; o += P5_THREADS) {  // row m = (query head m / PP, position i0 + m % PP)
+    const int m = o / 18, c8 = o % 18;
+    const int qi = m / PP, ip = min(i0 + m % PP, p.n_q - 1);
+    uint4 v = make_uint4(c8 == 16 ? 0x3C003C00u : 0u, 0u, 0u, 0u);  // K index 128, 129: ones against the norm pair
+    if (c8 < 16) v = reinterpret_cast<const uint4*>(p.q + (((int64_t)b * H + h * G + qi) * p.n_q + ip) * HEAD_DIM)[c8];
+    *reinterpret_cast<uint4*>(qop + (m >> 3) * OP_SBO + c8 * 128 + (m & 7) * 16) = v;
+    if (c8 == 17) {  // K index 136 .. 143 of both key buffers: zero for good
+      *reinterpret_cast<uint4*>(kop0 + (m >> 3) * OP_SBO + 17 * 128 + (m & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(kop0 + OP_BYTES + (m >> 3) * OP_SBO + 17 * 128 + (m & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  {
+    uint4* bd = reinterpret_cast<uint4*>(bop);
+    const uint4* bs = reinterpret_cast<const uint4*>(p.basis16 + (int64_t)h * HEAD_DIM * RANK);
+    for (int o = tid; o < 128 * (RANK / 8); o += P5_THREADS) {
+      const int c = o / (RANK / 8), i8 = o % (RANK / 8);
+      bd[((c >> 3) * (RANK / 8) + i8) * 8 + (c & 7)] = bs[o];
+    }
+  }
+  for (int o = tid; o < 16 * 16; o += P5_THREADS) {  // rows 128 .. 143: 1/norm pair (rewritten per tile), ones, zeros
+    const int r = 128 + (o >> 4), i = o & 15;
+    const uint32_t w = (r == 130) ? 0x3C003C00u : 0u;
+    *reinterpret_cast<uint4*>(vop + (r >> 3) * V_SBO + i * 128 + (r & 7) * 16) = make_uint4(w, w, w, w);
+  }
+  if (tid < 128) sg[tid] = p.signs[tid] * (1.0f / 128.0f);  // signs * fwht / sqrt(d), with the orthonormal fwht = butterflies / sqrt(d)
+  fence_proxy_async();
+  tc5::fence_before();
+  __syncthreads();
+  tc5::fence_after();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp < 8) {
+    // ===================== key warps: 32 token rows x two chunks of 16 + 16 channels =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(P5_REG_KEY));
+    const int wq = warp & 3, k0 = 2 * (warp >> 2), row = 32 * wq + lane;
+    const uint32_t tk = tmem + TM_KL + ((uint32_t)(32 * wq) << 16);
+    const int grp = row / g.group;
+    const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 cm72 = __floats2half2_rn(-72.f, -72.f);
+    const __half* kt = p.k_tail + ((int64_t)b * g.h_kv + h) * p.tail_cap * HEAD_DIM;
+    const float inv_scale = 1.0f / p.scale_log2;
+    // cos / sin of this token's rotary pairs 16k .. 16k+15 for both chunks, fetched one tile ahead: the registers of a
+    // chunk are reloaded for the next tile as soon as the chunk is done, so the loads have a whole tile to land
+    uint4 cs4[2][2], sn4[2][2];
+    auto load_rope = [&](int n, int kk) {
+      const int64_t pos = p.pos_offset + (int64_t)n * 128 + row;
+      const uint4* pc = reinterpret_cast<const uint4*>(p.rope_cos + pos * HEAD_DIM + 16 * (k0 + kk));
+      const uint4* ps = reinterpret_cast<const uint4*>(p.rope_sin + pos * HEAD_DIM + 16 * (k0 + kk));
+      cs4[kk][0] = pc[0], cs4[kk][1] = pc[1], sn4[kk][0] = ps[0], sn4[kk][1] = ps[1];
+    };
+    if (NP > 0) load_rope(0, 0), load_rope(0, 1);
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < NT; ++n) {
+      const int e = n & 1;
+      uint8_t* krow = kop0 + (size_t)e * OP_BYTES + (row >> 3) * OP_SBO + (row & 7) * 16;
+      // the buffer still feeds U2 of tile n-2
+      if (n >= 2 && !warp_wait(&sh->sdone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 41)) break;
+      if (n < NP) {
+        const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+        if (!warp_wait(&sh->full[s], fp, p.status, 42)) break;
+        if (!warp_wait(&sh->low, (uint32_t)n & 1u, p.status, 43)) break;
+        tc5::fence_after();
+        uint32_t dl[2][8], dh[2][8];
+        // a warp's TMEM loads complete one after the other: the second chunk's are issued when the first chunk's have
+        // landed and travel while the first chunk is computed
+        tc5::ld16_pack(tk + 16 * k0, dl[0]);
+        tc5::ld16_pack(tk + 64 + 16 * k0, dh[0]);
+        if (k0 == 0) {  // K index 128, 129 of this token: log2(norm) / scale as high part + remainder
+          const float nj = fmaxf(__half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]), MIN_NORM);
+          const float x = __log2f(nj) * inv_scale;
+          const __half xh = __float2half_rn(x), xl = __float2half_rn(x - __half2float(xh));
+          *reinterpret_cast<uint4*>(krow + 16 * 128) = make_uint4(h2_as_u32(__halves2half2(xh, xl)), 0u, 0u, 0u);
+        }
+        const uint4* ksc4 = reinterpret_cast<const uint4*>(blk + k2b_off_kscale(128)) + grp * 16;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int k = k0 + kk;
+          uint32_t out[16];
+          const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
+          const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
+          tc5::wait_ld();
+          if (kk == 0) {
+            tc5::ld16_pack(tk + 16 * k0 + 16, dl[1]);
+            tc5::ld16_pack(tk + 64 + 16 * k0 + 16, dh[1]);
+          } else {  // K_low of this tile is in registers: U1 of the next tile may overwrite it
+            tc5::fence_before();
+            __syncwarp();
+            if (lane == 0) smem_add_release(&sh->klcnt[e], 1);
+          }
+#pragma unroll
+          for (int wd = 0; wd < 2; ++wd) {
+            const uint32_t wlo = wd ? cw.y : cw.x, whi = wd ? cw.w : cw.z;
+            const uint32_t sl[4] = {scl[wd].x, scl[wd].y, scl[wd].z, scl[wd].w}, sh_[4] = {sch[wd].x, sch[wd].y, sch[wd].z, sch[wd].w};
+            const uint32_t cc_[4] = {cs4[kk][wd].x, cs4[kk][wd].y, cs4[kk][wd].z, cs4[kk][wd].w};
+            const uint32_t ss_[4] = {sn4[kk][wd].x, sn4[kk][wd].y, sn4[kk][wd].z, sn4[kk][wd].w};
+            __half2 rl[4], rh[4];
+            {
+              const uint32_t wl8 = wlo >> 8, wh8 = whi >> 8;
+              rl[0] = __hsub2(u32_as_h2(lop3<0x6A>(wlo, 0x000F000Fu, 0x64086408u)), c1032);
+              rl[1] = __hfma2(u32_as_h2(lop3<0x6A>(wlo, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+              rl[2] = __hsub2(u32_as_h2(lop3<0x6A>(wl8, 0x000F000Fu, 0x64086408u)), c1032);
+              rl[3] = __hfma2(u32_as_h2(lop3<0x6A>(wl8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+              rh[0] = __hsub2(u32_as_h2(lop3<0x6A>(whi, 0x000F000Fu, 0x64086408u)), c1032);
+              rh[1] = __hfma2(u32_as_h2(lop3<0x6A>(whi, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+              rh[2] = __hsub2(u32_as_h2(lop3<0x6A>(wh8, 0x000F000Fu, 0x64086408u)), c1032);
+              rh[3] = __hfma2(u32_as_h2(lop3<0x6A>(wh8, 0x00F000F0u, 0x64806480u)), c16th, cm72);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __half2 klo = __hfma2(rl[i], u32_as_h2(sl[i]), u32_as_h2(dl[kk][4 * wd + i]));
+              const __half2 khi = __hfma2(rh[i], u32_as_h2(sh_[i]), u32_as_h2(dh[kk][4 * wd + i]));
+              const __half2 c = u32_as_h2(cc_[i]), sn = u32_as_h2(ss_[i]);
+              out[4 * wd + i] = h2_as_u32(__hfma2(__hneg2(sn), khi, __hmul2(klo, c)));
+              out[8 + 4 * wd + i] = h2_as_u32(__hfma2(sn, klo, __hmul2(khi, c)));
+            }
+          }
+          if (n + 1 < NP) load_rope(n + 1, kk);
+          // channels 16k .. 16k+15 are 16-byte chunks 2k, 2k+1 of the row; channels 64+16k .. are chunks 8+2k, 9+2k
+          *reinterpret_cast<uint4*>(krow + (2 * k) * 128) = make_uint4(out[0], out[1], out[2], out[3]);
+          *reinterpret_cast<uint4*>(krow + (2 * k + 1) * 128) = make_uint4(out[4], out[5], out[6], out[7]);
+          *reinterpret_cast<uint4*>(krow + (8 + 2 * k) * 128) = make_uint4(out[8], out[9], out[10], out[11]);
+          *reinterpret_cast<uint4*>(krow + (9 + 2 * k) * 128) = make_uint4(out[12], out[13], out[14], out[15]);
+        }
+        if (++s == P5_STAGES) s = 0, fp ^= 1u;
+      } else {
+        // window tile: the keys are stored rotated; rows past the window's length are zero; norm 1
+        const int t0 = (n - NP) * 128;
+        const bool valid = t0 + row < tl;
+        const uint4* src = reinterpret_cast<const uint4*>(kt + (int64_t)(t0 + row) * HEAD_DIM);
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int k = k0 + kk;
+          const int cks[4] = {2 * k, 2 * k + 1, 8 + 2 * k, 9 + 2 * k};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(krow + cks[i] * 128) = valid ? src[cks[i]] : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (k0 == 0) *reinterpret_cast<uint4*>(krow + 16 * 128) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->kcnt[e], 1);
+    }
+  } else if (warp >= 16) {
+    // ===================== value warps: thread = channel, warp = one half (64 tokens) of the tile =====================
+    // (levels as stored in the table: the norm is in the weights)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(P5_REG_VALUE));
+    const int wq = warp & 3, cc = (warp - 16) >> 2, ch = 32 * wq + lane;
+    uint8_t* vrow = vop + (ch >> 3) * V_SBO + (ch & 7) * 16;
+    __half* vinv = reinterpret_cast<__half*>(vop + 16 * V_SBO + (ch >> 3) * 128) + (ch & 7);  // rows 128 / 129, token = ch (warps 16 - 19)
+    const __half* vt = p.v_tail + ((int64_t)b * g.h_kv + h) * p.tail_cap * HEAD_DIM;
+    int s = 0;
+    uint32_t fp = 0;
+    for (int n = 0; n < NT; ++n) {
+      // the buffer still feeds U3 of tile n-1
+      if (n >= 1 && !warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 44)) break;
+      if (n < NP) {
+        if (!warp_wait(&sh->full[s], fp, p.status, 45)) break;
+        const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
+        const uint4 cw = reinterpret_cast<const uint4*>(blk + k2b_off_vcode(128, g.group))[cc * 128 + ch];
+        const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int jw = 0; jw < 4; ++jw) {
+          const uint32_t wv = wd[jw];
+          const uint32_t x0 = wv & 0x33333333u, x1 = (wv >> 2) & 0x33333333u;
+          uint32_t outw[8];
+#pragma unroll
+          for (int hs = 0; hs < 2; ++hs) {
+            const uint32_t s0 = hs ? (x0 >> 16) : x0, s1 = hs ? (x1 >> 16) : x1;
+            const uint32_t lo0 = prmt(p.lut_lo, 0u, s0), hi0 = prmt(p.lut_hi, 0u, s0);
+            const uint32_t lo1 = prmt(p.lut_lo, 0u, s1), hi1 = prmt(p.lut_hi, 0u, s1);
+            outw[2 * hs] = prmt(lo0, hi0, 0x5140u), outw[2 * hs + 1] = prmt(lo0, hi0, 0x7362u);          // tokens 4 hs .. 4 hs + 3
+            outw[4 + 2 * hs] = prmt(lo1, hi1, 0x5140u), outw[4 + 2 * hs + 1] = prmt(lo1, hi1, 0x7362u);  // tokens 8 + 4 hs ..
+          }
+          *reinterpret_cast<uint4*>(vrow + (8 * cc + 2 * jw) * 128) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+          *reinterpret_cast<uint4*>(vrow + (8 * cc + 2 * jw + 1) * 128) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+        }
+        if (cc == 0) {  // rows 128 / 129, token = ch: 1 / norm as high part + remainder
+          const float nj = fmaxf(__half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[ch]), MIN_NORM);
+          const float r = 1.0f / nj;
+          const __half rh = __float2half_rn(r);
+          vinv[0] = rh, vinv[8] = __float2half_rn(r - __half2float(rh));
+        }
+        if (++s == P5_STAGES) s = 0, fp ^= 1u;
+      } else {
+        // window tile: values as stored, transposed; tokens past the window's length are zero
+        const int t0 = (n - NP) * 128;
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int ta = t0 + 64 * cc + 8 * i + 2 * j;
+            const __half a = (ta < tl) ? vt[(int64_t)ta * HEAD_DIM + ch] : __float2half_rn(0.f);
+            const __half c = (ta + 1 < tl) ? vt[(int64_t)(ta + 1) * HEAD_DIM + ch] : __float2half_rn(0.f);
+            w4[j] = h2_as_u32(__halves2half2(a, c));
+          }
+          *reinterpret_cast<uint4*>(vrow + (8 * cc + i) * 128) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
+        if (cc == 0) vinv[0] = __float2half_rn(1.f), vinv[8] = __float2half_rn(0.f);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->vcnt, 1);
+    }
+  } else if (warp < 12) {
+    // ===================== softmax warps: thread = attention row = TMEM lane =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(P5_REG_SOFTMAX));
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t tl_ = tmem + ((uint32_t)(32 * wq) << 16);
+    const int qi = row / PP, ip = i0 + row % PP;
+    const int64_t pq = p.q_pos0 + ip;
+    float m = -1e30f;
+    bool alive = true;
+
+    // O <- signs * fwht(alpha * sum(p n) + beta * O) / 128, in place (columns 0 .. 127 of the accumulator)
+    auto unrotate = [&]() {
+      uint32_t r4[4];
+      tc5::ld4(tl_ + TM_O + 128, r4);
+      tc5::wait_ld();
+      const float add = p.lut_alpha * __uint_as_float(r4[2]);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {  // index bits 0 .. 4: inside each chunk of 32 columns
+        uint32_t r[32];
+        tc5::ld32(tl_ + TM_O + 32 * c, r);
+        tc5::wait_ld();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(p.lut_beta, __uint_as_float(r[i]), add);
+#pragma unroll
+        for (int hb = 1; hb < 32; hb <<= 1)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!(i & hb)) {
+              const float a = v[i], bb = v[i | hb];
+              v[i] = a + bb, v[i | hb] = a - bb;
+            }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(v[i]);
+        tc5::st32(tl_ + TM_O + 32 * c, r);
+      }
+      tc5::wait_st();
+#pragma unroll 1
+      for (int j0 = 0; j0 < 32; j0 += 8) {  // index bits 5, 6: across the four chunks
+        uint32_t a0[8], a1[8], a2[8], a3[8];
+        tc5::ld8(tl_ + TM_O + j0, a0);
+        tc5::ld8(tl_ + TM_O + 32 + j0, a1);
+        tc5::ld8(tl_ + TM_O + 64 + j0, a2);
+        tc5::ld8(tl_ + TM_O + 96 + j0, a3);
+        tc5::wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float x0 = __uint_as_float(a0[i]), x1 = __uint_as_float(a1[i]), x2 = __uint_as_float(a2[i]), x3 = __uint_as_float(a3[i]);
+          const float y0 = x0 + x1, y1 = x0 - x1, y2 = x2 + x3, y3 = x2 - x3;
+          a0[i] = __float_as_uint((y0 + y2) * sg[j0 + i]);
+          a1[i] = __float_as_uint((y1 + y3) * sg[32 + j0 + i]);
+          a2[i] = __float_as_uint((y0 - y2) * sg[64 + j0 + i]);
+          a3[i] = __float_as_uint((y1 - y3) * sg[96 + j0 + i]);
+        }
+        tc5::st8(tl_ + TM_O + j0, a0);
+        tc5::st8(tl_ + TM_O + 32 + j0, a1);
+        tc5::st8(tl_ + TM_O + 64 + j0, a2);
+        tc5::st8(tl_ + TM_O + 96 + j0, a3);
+      }
+      tc5::wait_st();
+    };
+    // maximum of 32 scores (columns col0 ..) under the row's visibility limit
+    auto max32 = [&](const uint32_t (&r)[32], int col0, bool masked, int jlim, float acc) {
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc = fmaxf(acc, (col0 + i < jlim) ? __uint_as_float(r[i]) : -INFINITY);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc = fmaxf(acc, __uint_as_float(r[i]));
+      }
+      return acc;
+    };
+    // weights of 32 scores -> 16 columns of fp16 pairs
+    auto weights32 = [&](const uint32_t (&r)[32], int col0, bool masked, int jlim, float negm) {
+      uint32_t pk[16];
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = (col0 + 2 * i < jlim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, negm)) : 0.f;
+          const float p1 = (col0 + 2 * i + 1 < jlim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, negm)) : 0.f;
+          pk[i] = pack_h2(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          pk[i] = pack_h2(ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, negm)),
+                          ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, negm)));
+      }
+      tc5::st16(tl_ + TM_P + (col0 >> 1), pk);
+    };
+
+    for (int n = 0; n < NT && alive; ++n) {
+      const int e = n & 1;
+      const int64_t key_pos0 = (n < NP) ? p.pos_offset + (int64_t)n * 128 : tail_pos0 + (int64_t)(n - NP) * 128;
+      const int n_valid = (n < NP) ? 128 : min(128, tl - (n - NP) * 128);
+      const bool masked = (key_pos0 + 127 > pq_min) || (n_valid < 128);                     // the same for the whole CTA
+      const int jlim = (int)max((int64_t)0, min((int64_t)n_valid, pq - key_pos0 + 1));     // keys [0, jlim) of the tile are visible to this row
+      bool prev_done = (n == 0);  // U3 of tile n-1 finished: the weights and the accumulator may be written
+      if (n == NP && NP > 0) {    // first window tile after pages: leave the rotated space of the value codec
+        if (!warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 46)) { alive = false; break; }
+        tc5::fence_after();
+        unrotate();
+        prev_done = true;
+      }
+      if (!warp_wait(&sh->sdone[e], (uint32_t)(n >> 1) & 1u, p.status, 47)) { alive = false; break; }
+      tc5::fence_after();
+      // ---- pass 1: the row's maximum over the tile (the next chunk of scores travels while one is reduced) ----
+      uint32_t ra[32], rb[32];
+      float tmax = -INFINITY;
+      tc5::ld32(tl_ + TM_S, ra);
+      tc5::wait_ld();
+      tc5::ld32(tl_ + TM_S + 32, rb);
+      tmax = max32(ra, 0, masked, jlim, tmax);
+      tc5::wait_ld();
+      tc5::ld32(tl_ + TM_S + 64, ra);
+      tmax = max32(rb, 32, masked, jlim, tmax);
+      tc5::wait_ld();
+      tc5::ld32(tl_ + TM_S + 96, rb);
+      tmax = max32(ra, 64, masked, jlim, tmax);
+      tc5::wait_ld();
+      tmax = max32(rb, 96, masked, jlim, tmax);   // ra, rb keep the scores of columns 64 .. 127 for pass 2
+      const float ts = tmax * p.scale_log2;
+      // Lazy maximum: the accumulator is rescaled only when a score exceeds the running maximum by more than 8
+      // (weights stay below 2^8 otherwise), and then by the whole warp (TMEM access is warp-wide).
+      const bool need = ts > m + 8.f;
+      const bool wneed = __any_sync(0xffffffffu, need);
+      if (!prev_done) {
+        if (!warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 48)) { alive = false; break; }
+        tc5::fence_after();
+      }
+      if (wneed) {
+        const float f = need ? ex2_approx(m - ts) : 1.f;
+        if (need) m = ts;
+        if (n > 0) {
+          uint32_t r4[4];
+          tc5::ld4(tl_ + TM_O + 128, r4);
+          tc5::wait_ld();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) r4[i] = __float_as_uint(__uint_as_float(r4[i]) * f);
+          tc5::st4(tl_ + TM_O + 128, r4);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tc5::ld32(tl_ + TM_O + 32 * c, r);
+            tc5::wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+            tc5::st32(tl_ + TM_O + 32 * c, r);
+          }
+        }
+      }
+      // ---- pass 2: weights -> tensor memory (two fp16 per column); columns 96 .. and 64 .. are still in registers ----
+      const float negm = -m;
+      weights32(rb, 96, masked, jlim, negm);
+      tc5::ld32(tl_ + TM_S + 32, rb);
+      weights32(ra, 64, masked, jlim, negm);
+      tc5::wait_ld();
+      tc5::ld32(tl_ + TM_S, ra);
+      weights32(rb, 32, masked, jlim, negm);
+      tc5::wait_ld();
+      // every score has been read: U2 of the next tile may overwrite them
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->scnt, 1);
+      weights32(ra, 0, masked, jlim, negm);
+      tc5::wait_st();
+      tc5::fence_before();
+      __syncwarp();
+      if (lane == 0) smem_add_release(&sh->pcnt, 1);
+    }
+
+    // ---- the last U3, the rotation if no window tile undid it, normalise and store ----
+    if (alive && NT > 0 && !warp_wait(&sh->odone[(NT - 1) & 1], (uint32_t)((NT - 1) >> 1) & 1u, p.status, 49)) alive = false;
+    if (alive) {
+      float inv = 0.f;
+      if (NT > 0) {
+        tc5::fence_after();
+        if (NW == 0) unrotate();
+        uint32_t r4[4];
+        tc5::ld4(tl_ + TM_O + 128, r4);
+        tc5::wait_ld();
+        const float l = __uint_as_float(r4[0]) + __uint_as_float(r4[1]);
+        inv = (l > 0.f) ? 1.f / l : 0.f;
+      }
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (((int64_t)b * H + h * G + qi) * p.n_q + ip) * HEAD_DIM);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (NT > 0) {
+          tc5::ld32(tl_ + TM_O + 32 * c, r);
+          tc5::wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (ip < p.n_q) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w4[i] = pack_h2(__uint_as_float(r[8 * j + 2 * i]) * inv, __uint_as_float(r[8 * j + 2 * i + 1]) * inv);
+            dst[4 * c + j] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(P5_REG_SERVICE));
+    if (warp == 12) {
+      // ===================== copies and every tcgen05.mma =====================
+      // Tile n:  copy -> full[n % 3];  A: U1 -> low;  B: U2 -> sdone[n & 1];  C: U3 -> odone[n & 1].
+      // A(n) needs the copy landed and K_low of tile n-1 read by every key warp; B(n) the keys of tile n and the
+      // scores of tile n-1 read; C(n) the weights and the values of tile n; copy(n) the raw stage of tile n-3
+      // consumed by the key and value warps.  The whole warp walks the state machine, one elected lane issues.
+      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_U2 = tc5::idesc_f16_f32(128, 128), ID_U3 = tc5::idesc_f16_f32(128, VROWS);
+      const bool el = elect_one_p5();
+      const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_b = tc5::smem_desc(smem_u32(bop), 128, AB_SBO);
+      const uint64_t d_q = tc5::smem_desc(smem_u32(qop), 128, OP_SBO), d_k = tc5::smem_desc(smem_u32(kop0), 128, OP_SBO);
+      const uint64_t d_v = tc5::smem_desc(smem_u32(vop), 128, V_SBO);
+      const int chd = (g.n_coef_heads == 1) ? 0 : h;
+      const int32_t* table = p.page_table + (int64_t)b * p.table_stride;
+      int nP = 0, nA = 0, nB = 0, nC = 0, sP = 0, sA = 0;
+      uint32_t phA = 0;
+      int slot = (NP > 0) ? table[0] : 0;  // page slot of the next copy, fetched one copy ahead
+      long long t_last = clock64();
+      uint32_t idle = 0;
+      bool ok = true;
+      while (ok && nC < NT) {
+        bool progressed = false;
+        const int kc0 = smem_load_acquire(&sh->kcnt[0]), kc1 = smem_load_acquire(&sh->kcnt[1]), vc = smem_load_acquire(&sh->vcnt);
+        const int kl0 = smem_load_acquire(&sh->klcnt[0]), kl1 = smem_load_acquire(&sh->klcnt[1]);
+        auto kdone = [&](int t) { return t < 0 || ((t & 1) ? kc1 : kc0) >= 8 * ((t >> 1) + 1); };   // every key warp is through tile t
+        auto kldone = [&](int t) { return t < 0 || ((t & 1) ? kl1 : kl0) >= 8 * ((t >> 1) + 1); };  // ... holds K_low of tile t in registers
+        const int sc = smem_load_acquire(&sh->scnt), pc = smem_load_acquire(&sh->pcnt);
+        // ---- C ----
+        if (nC < nB && pc >= 4 * (nC + 1) && vc >= 8 * (nC + 1)) {
+          tc5::fence_after();
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              tc5::mma_ts(tmem + TM_O, tmem + TM_P + 8 * ks, d_v + 16 * ks, ID_U3, (nC > 0 || ks > 0) ? 1u : 0u);
+            tc5::commit(smem_u32(&sh->odone[nC & 1]));
+          }
+          __syncwarp();
+          ++nC;
+          progressed = true;
+        }
+        // ---- B ----
+        if (nB < NT && kdone(nB) && sc >= 4 * nB) {
+          tc5::fence_after();
+          const uint64_t db = d_k + (uint64_t)((nB & 1) * (OP_BYTES >> 4));
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < 9; ++ks) tc5::mma_ss(tmem + TM_S, d_q + 16 * ks, db + 16 * ks, ID_U2, ks > 0);  // 144 channels
+            tc5::commit(smem_u32(&sh->sdone[nB & 1]));
+          }
+          __syncwarp();
+          ++nB;
+          progressed = true;
+        }
+        // ---- A ----
+        if (nA < NP && kldone(nA - 1) && mbar_test_wait(&sh->full[sA], phA)) {
+          tc5::fence_after();
+          const uint64_t da = d_stage + (uint64_t)(sA * (STAGE_BYTES >> 4));
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) tc5::mma_ss(tmem + TM_KL, da + 16 * ks, d_b + 16 * ks, ID_U1, ks > 0);
+            tc5::commit(smem_u32(&sh->low));
+          }
+          __syncwarp();
+          ++nA;
+          if (++sA == P5_STAGES) sA = 0, phA ^= 1u;
+          progressed = true;
+        }
+        // ---- copy ----
+        if (nP < NP && (nP < P5_STAGES || (kdone(nP - P5_STAGES) && vc >= 8 * (nP - P5_STAGES + 1)))) {
+          uint8_t* st = stage0 + (size_t)sP * STAGE_BYTES;
+          if (el) {
+            mbar_arrive_expect_tx(&sh->full[sP], (uint32_t)STAGE_BYTES);
+            bulk_g2s(st, reinterpret_cast<const uint8_t*>(p.coefs) + ((int64_t)slot * g.n_coef_heads + chd) * COEF_BYTES, COEF_BYTES,
+                     &sh->full[sP]);
+            bulk_g2s(st + COEF_BYTES, p.pages + ((int64_t)slot * g.h_kv + h) * PB, PB, &sh->full[sP]);
+          }
+          __syncwarp();
+          ++nP;
+          if (++sP == P5_STAGES) sP = 0;
+          if (nP < NP) slot = table[nP];
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if ((++idle & 255u) == 0u) {
+          if (idle == 256u) t_last = clock64();
+          if (clock64() - t_last > WAIT_LIMIT_CYCLES || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+            if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 40;
+            ok = false;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- epilogue: every role ends here; the tensor memory goes back before the CTA leaves ----
+  tc5::fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc5::fence_after();
+    tc5::dealloc(tmem, TM_COLS);
+  }
+}
+
+static size_t p5_smem_bytes(int rank, int group) {
+  return (size_t)P5_STAGES * ((size_t)128 * rank * 2 + k2b_page_block_bytes(128, group)) + 3 * (size_t)OP_BYTES + VOP_BYTES +
+         (size_t)128 * rank * 2 + 128 * 4 + sizeof(P5Smem) + 128;
+}
+
+template <int RANK>
+static int launch_p5(const PrefillParams& prm, dim3 grid, size_t smem, cudaStream_t s) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
+    cudaError_t e = cudaFuncSetAttribute(k2b_prefill_t5_kernel<RANK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      configured.retract();
+      set_error("bmxk_k2b_prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return BMXK_ERR_CUDA;
+    }
+  }
+  k2b_prefill_t5_kernel<RANK><<<grid, P5_THREADS, smem, s>>>(prm);
+  return check_launch("bmxk_k2b_prefill(tcgen05)");
+}
+
+int launch_prefill_t5(const PrefillParams& prm, dim3 grid, cudaStream_t s) {
+  const size_t smem = p5_smem_bytes(prm.g.rank, prm.g.group);
+  BMXK_REQUIRE(smem <= 227 * 1024, "bmxk_k2b_prefill: rank=%d group=%d needs %zu bytes of shared memory", prm.g.rank, prm.g.group, smem);
+  return prm.g.rank == 32 ? launch_p5<32>(prm, grid, smem, s) : launch_p5<16>(prm, grid, smem, s);
+}
+
+}  // namespace bmxk

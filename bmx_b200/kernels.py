@@ -279,6 +279,11 @@ def k2b_prefill(pool: K2bPool, q: torch.Tensor, q_pos0: int, basis_f16: torch.Te
     return out
 
 
+def k2b_prefill_select(kernel: int) -> None:
+    """Process-wide choice of the paged-prefill kernel: 0 = tcgen05 where it applies (default), 1 = mma.sync."""
+    call("bmxk_k2b_prefill_select", int(kernel))
+
+
 STATIC_SCRATCH_BYTES = 2 * 1024 * 1024
 
 

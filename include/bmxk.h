@@ -149,6 +149,11 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
                      const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
                      int32_t* status, void* out, void* stream);
 
+/* Which kernel bmxk_k2b_prefill launches (process-wide; no counterpart in bmx).  0 (default): the tcgen05 kernel when q
+ * and out are 16-byte aligned, else the mma.sync kernel; 1: always the mma.sync kernel.  Both give the same attention
+ * within the path's tolerance. */
+int bmxk_k2b_prefill_select(int kernel);
+
 /* Decode step for hosts that must not allocate device memory.  (This entry point has no counterpart in
  * bmx; it exists for embedding.)
  *

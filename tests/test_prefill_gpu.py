@@ -15,6 +15,18 @@ pytestmark = pytest.mark.gpu
 D = 128
 
 
+@pytest.fixture(params=["tcgen05", "mma.sync"])
+def prefill_kernel(request):
+    """Both kernels behind bmxk_k2b_prefill, chosen process-wide for the test and put back afterwards."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+
+    K.k2b_prefill_select(0 if request.param == "tcgen05" else 1)
+    yield request.param
+    K.k2b_prefill_select(0)
+
+
 def _case(*, n_seq, h_kv, G, rank, per_head, group, n_pages, tail, n_q, seed):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -78,17 +90,20 @@ def _case(*, n_seq, h_kv, G, rank, per_head, group, n_pages, tail, n_q, seed):
     (1, 8, 32, True, 128, 2, 0, 256),      # no window; eight query heads per KV head
     (2, 2, 16, True, 32, 4, 128, 37),      # a ragged block of rows
     (2, 1, 32, True, 64, 1, 5, 133),       # one query head per KV head: 128 positions per CTA
+    (1, 4, 32, True, 64, 0, 150, 150),     # no committed page: two window tiles only
+    (1, 4, 16, True, 64, 9, 192, 500),     # the window's second tile partly filled, rows that start inside the pages
+    (3, 2, 32, False, 128, 6, 1, 1),       # a single query row
 ])
-def test_paged_prefill_matches_dense_oracle(h_kv, G, rank, per_head, group, n_pages, tail, n_q):
+def test_paged_prefill_matches_dense_oracle(prefill_kernel, h_kv, G, rank, per_head, group, n_pages, tail, n_q):
     err, _, _ = _case(n_seq=2, h_kv=h_kv, G=G, rank=rank, per_head=per_head, group=group, n_pages=n_pages, tail=tail, n_q=n_q, seed=51)
-    print(f"paged prefill: worst relative error {err:.3e}")
+    print(f"paged prefill ({prefill_kernel}): worst relative error {err:.3e}")
     assert err <= 1e-3
 
 
-def test_paged_prefill_long_context_rows_near_the_end():
+def test_paged_prefill_long_context_rows_near_the_end(prefill_kernel):
     """A 16384-token context and 64 query rows at its end: every page is fully visible, the window partly."""
     err, _, _ = _case(n_seq=1, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=128, tail=90, n_q=64, seed=53)
-    print(f"paged prefill, 16384-token context: worst relative error {err:.3e}")
+    print(f"paged prefill ({prefill_kernel}), 16384-token context: worst relative error {err:.3e}")
     assert err <= 1e-3
 
 
