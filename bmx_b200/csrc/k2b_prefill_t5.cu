@@ -2,7 +2,7 @@
 //
 // Same job and same grid as the mma.sync kernel of k2b_prefill.cu: one CTA owns 128 / G consecutive query positions
 // of one (sequence, KV head) -- 128 attention rows with the G query heads -- and walks the visible 128-token pages and
-// then the fp16 window.  Here the three contractions of a tile are tcgen05.mma instructions issued by one warp, the
+// then the fp16 window.  Here the three contractions of a tile are tcgen05.mma instructions issued by three warps, the
 // attention rows live on the 128 lanes of tensor memory (one softmax thread per row: no reduction across threads),
 // and the dequantization of tile n+1 runs in its own warps while tile n is multiplied and normalised:
 //
@@ -13,15 +13,18 @@
 //                                  Two more "channels" carry log2(value norm) / scale as an fp16 pair (high part,
 //                                  remainder) against two ones in Q, so that the scores arrive with the norm in the
 //                                  exponent and the weights leave the softmax as p * norm with ONE rounding to fp16
-//   U2  S[128 rows x 128 tok]    = Q (smem) x K^T over 144 channels, fp32
-//   softmax warps (4; thread = row): running maximum in base 2 with a lazy rescale of the accumulator,
+//   U2  S[128 rows x 64 tok]     = Q (smem) x K^T over 144 channels, fp32, once per half of the tile: the two halves
+//                                  have their own score and weight columns, so U2 of one half runs while the other
+//                                  half is in the softmax
+//   softmax warps (4; thread = row): one pass per half with the running maximum (base 2); only when a score exceeds it
+//                                  by more than 8 is the accumulator rescaled and the half redone;
 //                                  weights -> tensor memory as fp16 (A operand of U3)
 //   value warps (8; thread = channel, warp = 64 tokens): 2-bit codes -> the four fp16 levels of the value table
 //                                  -> shared memory as the B operand of U3.  Rows 128 / 129 of that operand hold
 //                                  1 / norm as an fp16 pair and row 130 ones: the same contraction returns the sum
 //                                  of the weights p (to 2^-22, from the rounded weights the numerator uses) and the
 //                                  sum of p * norm (the affine term of the level table)
-//   U3  O[128 rows x 144]       += P (TMEM) x V^T, fp32
+//   U3  O[128 rows x 144]       += P (TMEM) x V^T over the 64 tokens of the half, fp32
 //
 // The Hadamard rotation of the value codec is linear: it is undone once per row, in place in tensor memory, after
 // the last page and before the first window tile (whose values are not rotated).  Window tiles take the same route
@@ -35,7 +38,7 @@ namespace bmxk {
 
 namespace {
 
-constexpr int P5_THREADS = 768;  // warps 0-7 key, 8-11 softmax, 12 copies + every tcgen05.mma (13-15 idle), 16-23 value
+constexpr int P5_THREADS = 768;  // warps 0-7 key, 8-11 softmax, 12 copies + U1, 13 U2, 14 U3 (15 idle), 16-23 value
 constexpr int P5_STAGES = 3;
 // Registers per thread after each group of four warps resizes itself; the pool is what the launch handed out.
 constexpr int P5_REG_LAUNCH = 80, P5_REG_KEY = 112, P5_REG_SOFTMAX = 112, P5_REG_SERVICE = 48, P5_REG_VALUE = 48;
@@ -49,18 +52,29 @@ constexpr int VROWS = 144;  // rows of the U3 operand: 128 channels, 1/norm (two
 constexpr int V_SBO = 16 * 128;
 constexpr int VOP_BYTES = (VROWS / 8) * V_SBO;
 constexpr float MIN_NORM = 9.765625e-4f;  // 2^-10: a zero value vector keeps a weight the fp16 pair can carry
-// TMEM columns: scores, weights (fp16 pairs), output accumulator (128 channels, sum of p in two parts, sum of p x norm, 13 unused), K_low
+// TMEM columns: scores (64 per half of a tile), weights (fp16 pairs, 32 per half), output accumulator (128 channels, sum of p in two parts, sum of p x norm, 13 unused), K_low
 constexpr uint32_t TM_S = 0, TM_P = 128, TM_O = 192, TM_KL = 336, TM_COLS = 512;
 
 struct P5Smem {
   uint64_t full[P5_STAGES];          // raw tile landed (bulk copies)
-  uint64_t low, sdone[2], odone[2];  // completion of U1 / U2 / U3 (tcgen05.commit); U2 and U3 by tile parity
+  uint64_t low, sdone[2][2], odone[2];  // completion of U1, of U2 [half][tile parity] and of U3 [half] (tcgen05.commit)
   uint32_t tmem_base;
   // Arrivals, never reset: key warps (8 per tile, counted per tile parity: a key warp may be two tiles ahead of another
-  // one, never two tiles of the same parity), value warps (8), scores read (4), weights written (4)
+  // one, never two tiles of the same parity), value warps (8), scores read (4 per half tile), weights written (4 per half tile)
   // klcnt: key warps that hold K_low of the tile in registers (U1 of the next tile may start)
   int kcnt[2], klcnt[2], vcnt, scnt, pcnt;
 };
+
+// Per-role wait / work cycle counters of CTA (0, 0, 0), compiled in with -DP5_PROF only (written behind the status words).
+#ifdef P5_PROF
+#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64();
+#define PROF_ADD(i) { const long long prof_n = clock64(); prof_acc[i] += prof_n - prof_t; prof_t = prof_n; }
+#define PROF_OUT(base, n) if (lane == 0 && (warp & 3) == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { for (int i_ = 0; i_ < n; ++i_) p.status[base + i_] = (int32_t)(prof_acc[i_] >> 4); }
+#else
+#define PROF_DECL(n)
+#define PROF_ADD(i)
+#define PROF_OUT(base, n)
+#endif
 
 __device__ __forceinline__ bool elect_one_p5() {
   uint32_t pred;
@@ -120,7 +134,7 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
   if (tid == 0) {
     for (int s = 0; s < P5_STAGES; ++s) mbar_init(&sh->full[s], 1);
     mbar_init(&sh->low, 1);
-    for (int e = 0; e < 2; ++e) mbar_init(&sh->sdone[e], 1), mbar_init(&sh->odone[e], 1);
+    for (int e = 0; e < 2; ++e) mbar_init(&sh->sdone[0][e], 1), mbar_init(&sh->sdone[1][e], 1), mbar_init(&sh->odone[e], 1);
     sh->kcnt[0] = sh->kcnt[1] = sh->klcnt[0] = sh->klcnt[1] = sh->vcnt = sh->scnt = sh->pcnt = 0;
     fence_barrier_init();
   }
@@ -182,21 +196,27 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
     if (NP > 0) load_rope(0, 0), load_rope(0, 1);
     int s = 0;
     uint32_t fp = 0;
+    PROF_DECL(6)
     for (int n = 0; n < NT; ++n) {
       const int e = n & 1;
       uint8_t* krow = kop0 + (size_t)e * OP_BYTES + (row >> 3) * OP_SBO + (row & 7) * 16;
       // the buffer still feeds U2 of tile n-2
-      if (n >= 2 && !warp_wait(&sh->sdone[e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 41)) break;
+      if (n >= 2 && !(warp_wait(&sh->sdone[0][e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 41) &&
+                      warp_wait(&sh->sdone[1][e], (uint32_t)((n - 2) >> 1) & 1u, p.status, 41))) break;
+      PROF_ADD(0)
       if (n < NP) {
         const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
         if (!warp_wait(&sh->full[s], fp, p.status, 42)) break;
+        PROF_ADD(1)
         if (!warp_wait(&sh->low, (uint32_t)n & 1u, p.status, 43)) break;
+        PROF_ADD(2)
         tc5::fence_after();
         uint32_t dl[2][8], dh[2][8];
-        // a warp's TMEM loads complete one after the other: the second chunk's are issued when the first chunk's have
-        // landed and travel while the first chunk is computed
+        // all of this thread's K_low (both chunks) in one round trip; U1 of the next tile may then overwrite it
         tc5::ld16_pack(tk + 16 * k0, dl[0]);
         tc5::ld16_pack(tk + 64 + 16 * k0, dh[0]);
+        tc5::ld16_pack(tk + 16 * k0 + 16, dl[1]);
+        tc5::ld16_pack(tk + 64 + 16 * k0 + 16, dh[1]);
         if (k0 == 0) {  // K index 128, 129 of this token: log2(norm) / scale as high part + remainder
           const float nj = fmaxf(__half2float(reinterpret_cast<const __half*>(blk + k2b_off_vnorm(128, g.group))[row]), MIN_NORM);
           const float x = __log2f(nj) * inv_scale;
@@ -210,11 +230,9 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
           uint32_t out[16];
           const uint4 cw = reinterpret_cast<const uint4*>(blk)[k * 128 + row];
           const uint4 scl[2] = {ksc4[2 * k], ksc4[2 * k + 1]}, sch[2] = {ksc4[8 + 2 * k], ksc4[9 + 2 * k]};
-          tc5::wait_ld();
           if (kk == 0) {
-            tc5::ld16_pack(tk + 16 * k0 + 16, dl[1]);
-            tc5::ld16_pack(tk + 64 + 16 * k0 + 16, dh[1]);
-          } else {  // K_low of this tile is in registers: U1 of the next tile may overwrite it
+            tc5::wait_ld();
+            PROF_ADD(3)
             tc5::fence_before();
             __syncwarp();
             if (lane == 0) smem_add_release(&sh->klcnt[e], 1);
@@ -271,7 +289,9 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->kcnt[e], 1);
+      PROF_ADD(4)
     }
+    PROF_OUT(16, 6)
   } else if (warp >= 16) {
     // ===================== value warps: thread = channel, warp = one half (64 tokens) of the tile =====================
     // (levels as stored in the table: the norm is in the weights)
@@ -282,11 +302,14 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
     const __half* vt = p.v_tail + ((int64_t)b * g.h_kv + h) * p.tail_cap * HEAD_DIM;
     int s = 0;
     uint32_t fp = 0;
+    PROF_DECL(4)
     for (int n = 0; n < NT; ++n) {
       // the buffer still feeds U3 of tile n-1
-      if (n >= 1 && !warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 44)) break;
+      if (n >= 1 && !(warp_wait(&sh->odone[0], (uint32_t)(n - 1) & 1u, p.status, 44) && warp_wait(&sh->odone[1], (uint32_t)(n - 1) & 1u, p.status, 44))) break;
+      PROF_ADD(0)
       if (n < NP) {
         if (!warp_wait(&sh->full[s], fp, p.status, 45)) break;
+        PROF_ADD(1)
         const uint8_t* blk = stage0 + (size_t)s * STAGE_BYTES + COEF_BYTES;
         const uint4 cw = reinterpret_cast<const uint4*>(blk + k2b_off_vcode(128, g.group))[cc * 128 + ch];
         const uint32_t wd[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -333,7 +356,9 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->vcnt, 1);
+      PROF_ADD(2)
     }
+    PROF_OUT(32, 4)
   } else if (warp < 12) {
     // ===================== softmax warps: thread = attention row = TMEM lane =====================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(P5_REG_SOFTMAX));
@@ -395,79 +420,78 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
       }
       tc5::wait_st();
     };
-    // maximum of 32 scores (columns col0 ..) under the row's visibility limit
-    auto max32 = [&](const uint32_t (&r)[32], int col0, bool masked, int jlim, float acc) {
-      if (masked) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc = fmaxf(acc, (col0 + i < jlim) ? __uint_as_float(r[i]) : -INFINITY);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc = fmaxf(acc, __uint_as_float(r[i]));
-      }
-      return acc;
-    };
-    // weights of 32 scores -> 16 columns of fp16 pairs
-    auto weights32 = [&](const uint32_t (&r)[32], int col0, bool masked, int jlim, float negm) {
+    // 32 scores (token columns col0 .. of the half tile) -> weights with the running maximum -> 16 columns of fp16
+    // pairs; returns the maximum of the visible scores together with `acc`
+    auto weights32 = [&](const uint32_t (&r)[32], uint32_t tp, int col0, bool masked, int jl, float negm, float acc) {
       uint32_t pk[16];
       if (masked) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = (col0 + 2 * i < jlim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, negm)) : 0.f;
-          const float p1 = (col0 + 2 * i + 1 < jlim) ? ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, negm)) : 0.f;
-          pk[i] = pack_h2(p0, p1);
+          const bool v0 = col0 + 2 * i < jl, v1 = col0 + 2 * i + 1 < jl;
+          const float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
+          acc = fmaxf(acc, fmaxf(v0 ? s0 : -INFINITY, v1 ? s1 : -INFINITY));
+          pk[i] = pack_h2(v0 ? ex2_approx(fmaf(s0, p.scale_log2, negm)) : 0.f, v1 ? ex2_approx(fmaf(s1, p.scale_log2, negm)) : 0.f);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          pk[i] = pack_h2(ex2_approx(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, negm)),
-                          ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, negm)));
+        for (int i = 0; i < 16; ++i) {
+          const float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
+          acc = fmaxf(acc, fmaxf(s0, s1));
+          pk[i] = pack_h2(ex2_approx(fmaf(s0, p.scale_log2, negm)), ex2_approx(fmaf(s1, p.scale_log2, negm)));
+        }
       }
-      tc5::st16(tl_ + TM_P + (col0 >> 1), pk);
+      tc5::st16(tp + (col0 >> 1), pk);
+      return acc;
     };
 
-    for (int n = 0; n < NT && alive; ++n) {
-      const int e = n & 1;
-      const int64_t key_pos0 = (n < NP) ? p.pos_offset + (int64_t)n * 128 : tail_pos0 + (int64_t)(n - NP) * 128;
-      const int n_valid = (n < NP) ? 128 : min(128, tl - (n - NP) * 128);
-      const bool masked = (key_pos0 + 127 > pq_min) || (n_valid < 128);                     // the same for the whole CTA
-      const int jlim = (int)max((int64_t)0, min((int64_t)n_valid, pq - key_pos0 + 1));     // keys [0, jlim) of the tile are visible to this row
-      bool prev_done = (n == 0);  // U3 of tile n-1 finished: the weights and the accumulator may be written
-      if (n == NP && NP > 0) {    // first window tile after pages: leave the rotated space of the value codec
-        if (!warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 46)) { alive = false; break; }
+    // keys of the current half visible to this row / to the CTA's first row: position - first key position + 1
+    int64_t rel = pq - p.pos_offset + 1, rel_min = pq_min - p.pos_offset + 1;
+    PROF_DECL(8)
+    for (int u = 0; u < 2 * NT && alive; ++u) {  // half tile u = (tile n, half hf): tokens 64 hf .. 64 hf + 63
+      const int n = u >> 1, hf = u & 1, e = n & 1;
+      if (u == 2 * NP) rel = pq - tail_pos0 + 1, rel_min = pq_min - tail_pos0 + 1;  // the window's first token follows the last page
+      const int n_valid = (n < NP) ? 64 : max(0, min(64, tl - (n - NP) * 128 - 64 * hf));
+      const bool masked = (rel_min < 64) || (n_valid < 64);                               // the same for the whole CTA
+      const int jl = (int)max((int64_t)0, min((int64_t)n_valid, rel));                    // keys [0, jl) of the half are visible to this row
+      rel -= 64, rel_min -= 64;
+      const uint32_t tS = tl_ + TM_S + 64 * hf, tP = tl_ + TM_P + 32 * hf;
+      if (u == 2 * NP && NP > 0) {  // first window tile after pages: leave the rotated space of the value codec
+        if (!(warp_wait(&sh->odone[0], (uint32_t)(n - 1) & 1u, p.status, 46) && warp_wait(&sh->odone[1], (uint32_t)(n - 1) & 1u, p.status, 46))) {
+          alive = false;
+          break;
+        }
         tc5::fence_after();
         unrotate();
-        prev_done = true;
       }
-      if (!warp_wait(&sh->sdone[e], (uint32_t)(n >> 1) & 1u, p.status, 47)) { alive = false; break; }
+      PROF_ADD(0)
+      if (!warp_wait(&sh->sdone[hf][e], (uint32_t)(n >> 1) & 1u, p.status, 47)) { alive = false; break; }
+      PROF_ADD(1)
+      // the weight columns of this half still feed U3 of the previous tile's same half
+      if (n >= 1 && !warp_wait(&sh->odone[hf], (uint32_t)(n - 1) & 1u, p.status, 48)) { alive = false; break; }
       tc5::fence_after();
-      // ---- pass 1: the row's maximum over the tile (the next chunk of scores travels while one is reduced) ----
-      uint32_t ra[32], rb[32];
-      float tmax = -INFINITY;
-      tc5::ld32(tl_ + TM_S, ra);
-      tc5::wait_ld();
-      tc5::ld32(tl_ + TM_S + 32, rb);
-      tmax = max32(ra, 0, masked, jlim, tmax);
-      tc5::wait_ld();
-      tc5::ld32(tl_ + TM_S + 64, ra);
-      tmax = max32(rb, 32, masked, jlim, tmax);
-      tc5::wait_ld();
-      tc5::ld32(tl_ + TM_S + 96, rb);
-      tmax = max32(ra, 64, masked, jlim, tmax);
-      tc5::wait_ld();
-      tmax = max32(rb, 96, masked, jlim, tmax);   // ra, rb keep the scores of columns 64 .. 127 for pass 2
-      const float ts = tmax * p.scale_log2;
-      // Lazy maximum: the accumulator is rescaled only when a score exceeds the running maximum by more than 8
-      // (weights stay below 2^8 otherwise), and then by the whole warp (TMEM access is warp-wide).
-      const bool need = ts > m + 8.f;
-      const bool wneed = __any_sync(0xffffffffu, need);
-      if (!prev_done) {
-        if (!warp_wait(&sh->odone[(n - 1) & 1], (uint32_t)((n - 1) >> 1) & 1u, p.status, 48)) { alive = false; break; }
-        tc5::fence_after();
-      }
-      if (wneed) {
+      PROF_ADD(2)
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        uint32_t ra[32], rb[32];
+        const float negm = -m;
+        tc5::ld32(tS, ra);
+        tc5::ld32(tS + 32, rb);
+        tc5::wait_ld();
+        float tmax = weights32(ra, tP, 0, masked, jl, negm, -INFINITY);
+        tmax = weights32(rb, tP, 32, masked, jl, negm, tmax);
+        // Lazy maximum: as long as no score exceeds the running maximum by more than 8 (weights below 2^8) the weights
+        // just written stand.  Otherwise the whole warp (TMEM access is warp-wide) rescales its rows of the accumulator
+        // once every earlier U3 has finished, and goes through the half again with the new maximum.
+        const float ts = tmax * p.scale_log2;
+        const bool need = ts > m + 8.f;
+        if (!__any_sync(0xffffffffu, need)) break;
+        if (u > 0) {  // the U3 just before this half: the other half of this tile, or of the previous one
+          const bool ok = hf ? warp_wait(&sh->odone[0], (uint32_t)n & 1u, p.status, 50) : warp_wait(&sh->odone[1], (uint32_t)(n - 1) & 1u, p.status, 50);
+          if (!ok) { alive = false; break; }
+          tc5::fence_after();
+        }
         const float f = need ? ex2_approx(m - ts) : 1.f;
         if (need) m = ts;
-        if (n > 0) {
+        if (u > 0) {
           uint32_t r4[4];
           tc5::ld4(tl_ + TM_O + 128, r4);
           tc5::wait_ld();
@@ -485,28 +509,23 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
           }
         }
       }
-      // ---- pass 2: weights -> tensor memory (two fp16 per column); columns 96 .. and 64 .. are still in registers ----
-      const float negm = -m;
-      weights32(rb, 96, masked, jlim, negm);
-      tc5::ld32(tl_ + TM_S + 32, rb);
-      weights32(ra, 64, masked, jlim, negm);
-      tc5::wait_ld();
-      tc5::ld32(tl_ + TM_S, ra);
-      weights32(rb, 32, masked, jlim, negm);
-      tc5::wait_ld();
-      // every score has been read: U2 of the next tile may overwrite them
+      if (!alive) break;
+      PROF_ADD(3)
+      // every score of the half has been read: U2 of the next tile's same half may overwrite them
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->scnt, 1);
-      weights32(ra, 0, masked, jlim, negm);
       tc5::wait_st();
       tc5::fence_before();
       __syncwarp();
       if (lane == 0) smem_add_release(&sh->pcnt, 1);
+      PROF_ADD(4)
     }
+    PROF_OUT(48, 8)
 
     // ---- the last U3, the rotation if no window tile undid it, normalise and store ----
-    if (alive && NT > 0 && !warp_wait(&sh->odone[(NT - 1) & 1], (uint32_t)((NT - 1) >> 1) & 1u, p.status, 49)) alive = false;
+    if (alive && NT > 0 && !(warp_wait(&sh->odone[0], (uint32_t)(NT - 1) & 1u, p.status, 49) && warp_wait(&sh->odone[1], (uint32_t)(NT - 1) & 1u, p.status, 49)))
+      alive = false;
     if (alive) {
       float inv = 0.f;
       if (NT > 0) {
@@ -543,60 +562,46 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
     }
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(P5_REG_SERVICE));
+    // ===================== service warps: 12 copies + U1, 13 U2, 14 U3 (15 idle) =====================
+    // Tile n:  copy -> full[n % 3];  A: U1 -> low;  per half hf:  B: U2 -> sdone[hf][n & 1];  C: U3 -> odone[hf].
+    // A(n) needs the copy landed and K_low of tile n-1 read by every key warp; B(n, hf) the keys of tile n and the
+    // scores of the same half of tile n-1 read; C(n, hf) the weights of the half and the values of tile n; copy(n) the
+    // raw stage of tile n-3 consumed by the key and value warps.  A thread gets an MMA out every 100 - 200 cycles, far
+    // less than the tensor pipe takes: the three contractions are issued by three warps, each polling only the counters
+    // its own action needs.  A whole warp walks its state machine, one elected lane issues.
+    const bool el = elect_one_p5();
+    long long t_last = clock64();
+    uint32_t idle = 0;
+    bool ok = true;
+    // bounded polling: gives up (and says where) once nothing has moved for the wait limit, or another wait gave up
+    auto stalled = [&](bool progressed, int where) {
+      if (progressed) {
+        idle = 0;
+      } else if ((++idle & 255u) == 0u) {
+        if (idle == 256u) t_last = clock64();
+        if (clock64() - t_last > WAIT_LIMIT_CYCLES || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
+          if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = where;
+          return true;
+        }
+      }
+      return false;
+    };
     if (warp == 12) {
-      // ===================== copies and every tcgen05.mma =====================
-      // Tile n:  copy -> full[n % 3];  A: U1 -> low;  B: U2 -> sdone[n & 1];  C: U3 -> odone[n & 1].
-      // A(n) needs the copy landed and K_low of tile n-1 read by every key warp; B(n) the keys of tile n and the
-      // scores of tile n-1 read; C(n) the weights and the values of tile n; copy(n) the raw stage of tile n-3
-      // consumed by the key and value warps.  The whole warp walks the state machine, one elected lane issues.
-      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128), ID_U2 = tc5::idesc_f16_f32(128, 128), ID_U3 = tc5::idesc_f16_f32(128, VROWS);
-      const bool el = elect_one_p5();
+      constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128);
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_b = tc5::smem_desc(smem_u32(bop), 128, AB_SBO);
-      const uint64_t d_q = tc5::smem_desc(smem_u32(qop), 128, OP_SBO), d_k = tc5::smem_desc(smem_u32(kop0), 128, OP_SBO);
-      const uint64_t d_v = tc5::smem_desc(smem_u32(vop), 128, V_SBO);
       const int chd = (g.n_coef_heads == 1) ? 0 : h;
       const int32_t* table = p.page_table + (int64_t)b * p.table_stride;
-      int nP = 0, nA = 0, nB = 0, nC = 0, sP = 0, sA = 0;
+      int nP = 0, nA = 0, sP = 0, sA = 0;
       uint32_t phA = 0;
       int slot = (NP > 0) ? table[0] : 0;  // page slot of the next copy, fetched one copy ahead
-      long long t_last = clock64();
-      uint32_t idle = 0;
-      bool ok = true;
-      while (ok && nC < NT) {
+      while (ok && nA < NP) {
         bool progressed = false;
         const int kc0 = smem_load_acquire(&sh->kcnt[0]), kc1 = smem_load_acquire(&sh->kcnt[1]), vc = smem_load_acquire(&sh->vcnt);
         const int kl0 = smem_load_acquire(&sh->klcnt[0]), kl1 = smem_load_acquire(&sh->klcnt[1]);
         auto kdone = [&](int t) { return t < 0 || ((t & 1) ? kc1 : kc0) >= 8 * ((t >> 1) + 1); };   // every key warp is through tile t
         auto kldone = [&](int t) { return t < 0 || ((t & 1) ? kl1 : kl0) >= 8 * ((t >> 1) + 1); };  // ... holds K_low of tile t in registers
-        const int sc = smem_load_acquire(&sh->scnt), pc = smem_load_acquire(&sh->pcnt);
-        // ---- C ----
-        if (nC < nB && pc >= 4 * (nC + 1) && vc >= 8 * (nC + 1)) {
-          tc5::fence_after();
-          if (el) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              tc5::mma_ts(tmem + TM_O, tmem + TM_P + 8 * ks, d_v + 16 * ks, ID_U3, (nC > 0 || ks > 0) ? 1u : 0u);
-            tc5::commit(smem_u32(&sh->odone[nC & 1]));
-          }
-          __syncwarp();
-          ++nC;
-          progressed = true;
-        }
-        // ---- B ----
-        if (nB < NT && kdone(nB) && sc >= 4 * nB) {
-          tc5::fence_after();
-          const uint64_t db = d_k + (uint64_t)((nB & 1) * (OP_BYTES >> 4));
-          if (el) {
-#pragma unroll
-            for (int ks = 0; ks < 9; ++ks) tc5::mma_ss(tmem + TM_S, d_q + 16 * ks, db + 16 * ks, ID_U2, ks > 0);  // 144 channels
-            tc5::commit(smem_u32(&sh->sdone[nB & 1]));
-          }
-          __syncwarp();
-          ++nB;
-          progressed = true;
-        }
         // ---- A ----
-        if (nA < NP && kldone(nA - 1) && mbar_test_wait(&sh->full[sA], phA)) {
+        if (nA < nP && kldone(nA - 1) && mbar_test_wait(&sh->full[sA], phA)) {
           tc5::fence_after();
           const uint64_t da = d_stage + (uint64_t)(sA * (STAGE_BYTES >> 4));
           if (el) {
@@ -624,15 +629,51 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
           if (nP < NP) slot = table[nP];
           progressed = true;
         }
-        if (progressed) {
-          idle = 0;
-        } else if ((++idle & 255u) == 0u) {
-          if (idle == 256u) t_last = clock64();
-          if (clock64() - t_last > WAIT_LIMIT_CYCLES || *reinterpret_cast<volatile int32_t*>(p.status) != 0) {
-            if (el && atomicCAS(p.status, 0, 1) == 0) p.status[1] = blockIdx.x, p.status[2] = 40;
-            ok = false;
+        if (stalled(progressed, 40)) ok = false;
+      }
+    } else if (warp == 13) {
+      constexpr uint32_t ID_U2 = tc5::idesc_f16_f32(128, 64);
+      const uint64_t d_q = tc5::smem_desc(smem_u32(qop), 128, OP_SBO), d_k = tc5::smem_desc(smem_u32(kop0), 128, OP_SBO);
+      int uB = 0;  // half tiles issued
+      while (ok && uB < 2 * NT) {
+        const int n = uB >> 1, hf = uB & 1;
+        const int kc = smem_load_acquire(&sh->kcnt[n & 1]), sc = smem_load_acquire(&sh->scnt);
+        bool progressed = false;
+        if (kc >= 8 * ((n >> 1) + 1) && sc >= 4 * (uB - 1)) {
+          tc5::fence_after();
+          const uint64_t db = d_k + (uint64_t)((n & 1) * (OP_BYTES >> 4) + hf * (8 * OP_SBO >> 4));  // token rows 64 hf ..
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < 9; ++ks) tc5::mma_ss(tmem + TM_S + 64 * hf, d_q + 16 * ks, db + 16 * ks, ID_U2, ks > 0);  // 144 channels
+            tc5::commit(smem_u32(&sh->sdone[hf][n & 1]));
           }
+          __syncwarp();
+          ++uB;
+          progressed = true;
         }
+        if (stalled(progressed, 51)) ok = false;
+      }
+    } else if (warp == 14) {
+      constexpr uint32_t ID_U3 = tc5::idesc_f16_f32(128, VROWS);
+      const uint64_t d_v = tc5::smem_desc(smem_u32(vop), 128, V_SBO);
+      int uC = 0;
+      while (ok && uC < 2 * NT) {
+        const int hf = uC & 1;
+        const int pc = smem_load_acquire(&sh->pcnt), vc = smem_load_acquire(&sh->vcnt);
+        bool progressed = false;
+        if (pc >= 4 * (uC + 1) && vc >= 8 * ((uC >> 1) + 1)) {
+          tc5::fence_after();
+          if (el) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)  // 64 tokens of the half: weight columns 32 hf .., token chunks 8 hf ..
+              tc5::mma_ts(tmem + TM_O, tmem + TM_P + 32 * hf + 8 * ks, d_v + 64 * hf + 16 * ks, ID_U3, (uC > 0 || ks > 0) ? 1u : 0u);
+            tc5::commit(smem_u32(&sh->odone[hf]));
+          }
+          __syncwarp();
+          ++uC;
+          progressed = true;
+        }
+        if (stalled(progressed, 52)) ok = false;
       }
     }
   }
