@@ -829,8 +829,9 @@ def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
 def config_prefill(device) -> dict:
     """Prefill attention of the k2b cache: one sequence of 16384 committed tokens + a 128-token window (32 q / 8 kv heads);
     (a) the last 2048 positions as one query block (a chunk of a chunked prefill), (b) the whole prompt at once.  Timed:
-    the paged kernel (pages dequantized in shared memory, no dense K / V) against the route it replaces, dequantize every
-    page + rotate + scaled_dot_product_attention with the same causal mask.  FLOPs counted over the visible part only."""
+    the paged kernel (pages dequantized in shared memory, no dense K / V; tcgen05, and the mma.sync kernel it succeeded)
+    against the route it replaces, dequantize every page + rotate + scaled_dot_product_attention with the same causal mask.
+    FLOPs counted over the visible part only."""
     import torch
     import torch.nn.functional as F
 
@@ -849,6 +850,9 @@ def config_prefill(device) -> dict:
     for name, n_q in (("last_2048_rows", 2048), ("whole_prompt", S)):
         q = (torch.randn(1, H, n_q, D, generator=gen, device=device) / math.sqrt(D)).half()
         o = torch.empty_like(q)
+        K.k2b_prefill_select(1)  # the mma.sync kernel, for the record
+        legacy_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
+        K.k2b_prefill_select(0)  # the tcgen05 kernel (default)
         paged_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
         K.check_status(state.workspace)
 
@@ -873,7 +877,8 @@ def config_prefill(device) -> dict:
         err = float((o.float() - ref.float()).abs().max() / ref.float().abs().max())
         visible = n_q * (S - n_q) + n_q * (n_q + 1) // 2
         flops = 4.0 * H * D * visible
-        out[name] = {"rows": n_q, "paged_kernel_us": paged_us, "dequantize_then_sdpa_us": dense_us, "speedup": dense_us / paged_us,
+        out[name] = {"rows": n_q, "paged_kernel_us": paged_us, "paged_mma_sync_kernel_us": legacy_us, "dequantize_then_sdpa_us": dense_us,
+                     "speedup": dense_us / paged_us,
                      "paged_tflops": flops / paged_us / 1e6, "peak_tflops": tf_peak,
                      "frac_of_tensor_peak": None if not tf_peak else flops / paged_us / 1e6 / tf_peak,
                      "dense_route_transient_bytes": int(dense_peak), "paged_route_transient_bytes": 0,

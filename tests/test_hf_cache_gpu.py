@@ -18,12 +18,12 @@ def _tiny_llama(dev):
     return LlamaForCausalLM(cfg).to(dev).eval()  # float32: the fp16 logits of a random-init model tie exactly at some steps
 
 
-def _run(model, ids, n_prefill, force_dense):
+def _run(model, ids, n_prefill, force_dense, prefill_route="auto"):
     from bmx_b200.packed_streaming import PackedStreamingCache, PackedStreamingLayer
     from bmx_b200.recipes import spec_pair
 
     k_spec, v_spec = spec_pair("k2b_ph", rank=16, group=64)
-    cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+    cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32, prefill_route=prefill_route)
     logits = []
     orig = PackedStreamingLayer.attend
     from bmx_b200.engine import K2bLayerState
@@ -98,7 +98,9 @@ def test_streaming_twin_matches_packed_cache_tokens():
     model = _tiny_llama(dev)
     g = torch.Generator().manual_seed(2)
     ids = torch.randint(0, 256, (1, 200 + 40), generator=g).to(dev)
-    la, pcache = _run(model, ids, 200, force_dense=False)
+    # the twin attends its prompt over dequantized tensors with SDPA; the packed cache is put on the same route for the
+    # prompt (its paged kernel agrees with it to 1e-3, which a near-tie of this random-init model's logits does not survive)
+    la, pcache = _run(model, ids, 200, force_dense=False, prefill_route="dense")
     k_spec, v_spec = spec_pair("k2b_ph", rank=16, group=64)
     cache = StreamingQuantizedCache(model.config, k_spec, v_spec, recent_window=32)
     logits = []

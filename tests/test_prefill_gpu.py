@@ -109,8 +109,9 @@ def test_paged_prefill_long_context_rows_near_the_end(prefill_kernel):
 
 def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     """Under a Hugging Face model the prompt's attention goes through the paged kernel when the mask is the plain causal
-    one and the cache's prefill_route asks for it ("auto" asks once the dense transient would pass its budget); the dense
-    route (dequantize every page, SDPA) gives the same logits to fp16 accuracy."""
+    one and the cache's prefill_route asks for it ("auto" asks for blocks below the measured row crossover, and for longer
+    ones once the dense transient would pass its budget); the dense route (dequantize every page, SDPA) gives the same
+    logits to fp16 accuracy."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from bmx_b200.engine import K2bLayerState
@@ -146,20 +147,28 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     assert calls == [(450, 0), (450, 0), (250, 450), (250, 450)], calls  # two layers, two blocks; none from the dense run
     from bmx_b200.packed_streaming import PackedStreamingLayer
 
-    assert PackedStreamingLayer.DENSE_PREFILL_BUDGET == 1 << 30  # "auto": a 700-token prompt is far below it -> dense route
+    # "auto": blocks of up to PAGED_MAX_ROWS rows take the paged kernel (it beats dequantize + SDPA there); longer blocks
+    # take the dense route until its transient would pass DENSE_PREFILL_BUDGET
+    assert PackedStreamingLayer.DENSE_PREFILL_BUDGET == 1 << 30 and PackedStreamingLayer.PAGED_MAX_ROWS == 2560
     cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
     n_before = len(calls)
     K2bLayerState.prefill_attend = lambda self, q, q_pos0, out=None: calls.append("auto") or orig(self, q, q_pos0, out)
     try:
         with cache.attach(model), torch.no_grad():
             la = model(ids[:, :450], past_key_values=cache, use_cache=True).logits.float()
-            assert len(calls) == n_before
-            PackedStreamingLayer.DENSE_PREFILL_BUDGET = 0  # now every committed page is over budget
+            assert calls[n_before:] == ["auto", "auto"]                # 450 rows: paged, both layers
+            PackedStreamingLayer.PAGED_MAX_ROWS = 100                  # a 250-row block now counts as long ...
             lb = model(ids[:, 450:], past_key_values=cache, use_cache=True).logits.float()
-            assert calls[n_before:] == ["auto", "auto"]
+            assert calls[n_before:] == ["auto", "auto"]                # ... and is far below the budget: dense route
+        cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
+        PackedStreamingLayer.DENSE_PREFILL_BUDGET = 0                  # every committed page is over budget: paged again
+        with cache.attach(model), torch.no_grad():
+            model(ids[:, :450], past_key_values=cache, use_cache=True)
+            assert calls[n_before:] == ["auto"] * 4
     finally:
         K2bLayerState.prefill_attend = orig
         PackedStreamingLayer.DENSE_PREFILL_BUDGET = 1 << 30
+        PackedStreamingLayer.PAGED_MAX_ROWS = 2560
     assert float((torch.cat([la, lb], 1) - ld).abs().max()) < 5e-2
     diff = float((lp - ld).abs().max())
     print(f"paged vs dense prefill logits: max diff {diff:.3e}")
