@@ -65,7 +65,8 @@ struct P5Smem {
   int kcnt[2], klcnt[2], vcnt, scnt, pcnt;
 };
 
-// Per-role wait / work cycle counters of CTA (0, 0, 0), compiled in with -DP5_PROF only (written behind the status words).
+// Per-role wait / work cycle counters of CTA (0, 0, 0), compiled in with -DP5_PROF only: written behind the status words
+// (words 16 .. 71, in units of 16 cycles), so the status buffer of such a build must hold 72 words.
 #ifdef P5_PROF
 #define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64();
 #define PROF_ADD(i) { const long long prof_n = clock64(); prof_acc[i] += prof_n - prof_t; prof_t = prof_n; }
