@@ -100,6 +100,26 @@ def test_paged_prefill_matches_dense_oracle(prefill_kernel, h_kv, G, rank, per_h
     assert err <= 1e-3
 
 
+def test_paged_prefill_random_geometries(prefill_kernel):
+    """Ten geometries drawn over KV heads, query heads per KV head, rank, shared or per-head basis, residual group, page
+    count (none included), window length (none, partial second tile) and the number of trailing query rows."""
+    import random
+
+    rng, worst = random.Random(17), 0.0
+    for c in range(10):
+        n_pages, tail = rng.choice([0, 1, 2, 3, 5, 9]), rng.choice([0, 1, 63, 64, 65, 127, 128, 129, 191, 192])
+        if n_pages == 0 and tail == 0:
+            tail = 40
+        T = n_pages * 128 + tail
+        cfg = dict(n_seq=rng.randint(1, 2), h_kv=rng.choice([1, 2, 4]), G=rng.choice([1, 2, 4, 8]), rank=rng.choice([16, 32]),
+                   per_head=rng.choice([True, False]), group=rng.choice([32, 64, 128]), n_pages=n_pages, tail=tail,
+                   n_q=rng.randint(1, min(T, 300)), seed=400 + c)
+        err, _, _ = _case(**cfg)
+        assert err <= 1e-3, (cfg, err)
+        worst = max(worst, err)
+    print(f"paged prefill ({prefill_kernel}): worst relative error over 10 geometries {worst:.3e}")
+
+
 def test_paged_prefill_long_context_rows_near_the_end(prefill_kernel):
     """A 16384-token context and 64 query rows at its end: every page is fully visible, the window partly."""
     err, _, _ = _case(n_seq=1, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=128, tail=90, n_q=64, seed=53)
