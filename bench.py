@@ -972,10 +972,16 @@ def run_hf(args) -> None:
         try:
             with torch.no_grad():
                 pos = 0
+                p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                p0.record()
                 while pos < context:  # prefill in chunks
                     n = min(2048, context - pos)
                     model(ids[:, pos:pos + n], past_key_values=cache, use_cache=True)
                     pos += n
+                p1.record()
+                torch.cuda.synchronize()
+                prefill_ms.append(p0.elapsed_time(p1))
                 for t in range(3):
                     step(ids[:, pos + t:pos + t + 1])
                 pos += 3
@@ -995,19 +1001,23 @@ def run_hf(args) -> None:
                 cache.detach()
 
     k_spec, v_spec = spec_pair("k2b_ph", rank=32, group=64)
+    prefill_ms = []  # one entry per run below, in order: the 8192-token prompt in four 2048-token blocks (first run: with warm-up costs)
     dense = {}
     for impl in ("sdpa", "eager"):
         model.config._attn_implementation = impl
         ms, wall = run(lambda: DynamicCache(config=cfg), attach=False)
-        dense[impl] = {"ms_per_token": ms, "wall_ms_per_token": wall}
+        dense[impl] = {"ms_per_token": ms, "wall_ms_per_token": wall, "prompt_ms": prefill_ms[-1]}
     model.config._attn_implementation = "sdpa"
     packed_ms, packed_wall = run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window), attach=True)
     graph_ms, graph_wall = run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window), attach=True, graphed=True)
+    run(lambda: PackedStreamingCache(cfg, k_spec, v_spec, recent_window=window, prefill_route="dense"), attach=True)
     dense_ms = min(v["ms_per_token"] for v in dense.values())
     print(json.dumps({"metric": "hf_decode_ms_per_token", "model": f"Llama-3.1-8B layer shape x {layers} layers, random init, fp16",
                       "batch": batch, "context": context, "steps": steps, "dynamic_cache": dense,
                       "packed_streaming_cache_k2b": {"ms_per_token": packed_ms, "wall_ms_per_token": packed_wall},
                       "packed_streaming_cache_k2b_whole_step_graph": {"ms_per_token": graph_ms, "wall_ms_per_token": graph_wall},
+                      "prompt_ms_packed_cache": {"paged_prefill_kernel": prefill_ms[3], "dequantize_then_sdpa": prefill_ms[4],
+                                                 "note": "quantize-on-append of every page included; blocks of 2048 rows"},
                       "per_layer_us": {"dynamic": dense_ms * 1e3 / layers, "packed": packed_ms * 1e3 / layers,
                                        "packed_graph": graph_ms * 1e3 / layers}}), flush=True)
 
