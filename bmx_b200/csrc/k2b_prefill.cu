@@ -14,6 +14,7 @@
 //
 // Layout 1 pools (128-token pages) only.  Causality is by position: key t is visible to the query at position p iff
 // t <= p; window slots past tail_len are masked.
+#include <atomic>
 #include <cstring>
 
 #include "prefill_common.cuh"
@@ -394,13 +395,13 @@ size_t prefill_smem_bytes(int rank, int group) {
 using namespace bmxk;
 
 // 0: the tcgen05 kernel where its alignment needs are met, else the mma.sync kernel; 1: always the mma.sync kernel
-static int g_prefill_kernel = 0;
+static std::atomic<int> g_prefill_kernel{0};
 
 extern "C" {
 
 int bmxk_k2b_prefill_select(int kernel) {
   BMXK_REQUIRE(kernel == 0 || kernel == 1, "bmxk_k2b_prefill_select: kernel=%d (0: tcgen05 where it applies, 1: mma.sync)", kernel);
-  g_prefill_kernel = kernel;
+  g_prefill_kernel.store(kernel, std::memory_order_relaxed);
   return BMXK_OK;
 }
 
@@ -443,7 +444,7 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
   const dim3 grid((unsigned)((n_q + pp - 1) / pp), (unsigned)g->h_kv, (unsigned)batch);
   cudaStream_t s = (cudaStream_t)stream;
   const bool aligned16 = ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0;
-  if (g_prefill_kernel == 0 && aligned16) return launch_prefill_t5(prm, grid, s);
+  if (g_prefill_kernel.load(std::memory_order_relaxed) == 0 && aligned16) return launch_prefill_t5(prm, grid, s);
   static PerDeviceOnce configured;
   if (configured.first()) {
     cudaError_t e1 = cudaFuncSetAttribute(k2b_prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
