@@ -828,7 +828,8 @@ def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
 
 def config_prefill(device) -> dict:
     """Prefill attention of the k2b cache: one sequence of 16384 committed tokens + a 128-token window (32 q / 8 kv heads);
-    (a) the last 2048 positions as one query block (a chunk of a chunked prefill), (b) the whole prompt at once.  Timed:
+    (a) the last 512 and the last 2048 positions as one query block (a follow-up turn, a chunk of a chunked prefill), (b) the
+    whole prompt at once.  Timed:
     the paged kernel (pages dequantized in shared memory, no dense K / V; tcgen05, and the mma.sync kernel it succeeded)
     against the route it replaces, dequantize every page + rotate + scaled_dot_product_attention with the same causal mask.
     FLOPs counted over the visible part only."""
@@ -847,7 +848,7 @@ def config_prefill(device) -> dict:
             tf_peak = float(json.load(f).get("bf16_tflops_sustained") or 0) or None
     except (OSError, ValueError):
         tf_peak = None
-    for name, n_q in (("last_2048_rows", 2048), ("whole_prompt", S)):
+    for name, n_q in (("last_512_rows", 512), ("last_2048_rows", 2048), ("whole_prompt", S)):
         q = (torch.randn(1, H, n_q, D, generator=gen, device=device) / math.sqrt(D)).half()
         o = torch.empty_like(q)
         K.k2b_prefill_select(1)  # the mma.sync kernel, for the record
@@ -856,14 +857,8 @@ def config_prefill(device) -> dict:
         paged_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
         K.check_status(state.workspace)
 
-        def dense():
-            slots = state.page_table[:, :T // PAGE].contiguous().view(-1)
-            kd, vd = K.k2b_dequant_pages(state.pool, slots, state.basis_f16, state.signs, state.codebook)
-            kd = kd.view(1, T, H_KV, D).permute(0, 2, 1, 3)
-            vd = vd.view(1, T, H_KV, D).permute(0, 2, 1, 3)
-            kd = apply_rope(kd.half(), state.rope_cos[:T], state.rope_sin[:T])
-            kx = torch.cat([kd, state.k_win[:, :, :WINDOW]], 2)
-            vx = torch.cat([vd.half(), state.v_win[:, :, :WINDOW]], 2)
+        def dense():  # the product's dense route: one dequantizer kernel writes rotated fp16 K and V in place, then SDPA
+            kx, vx = state.dense_kv(torch.float16)
             if n_q == S:
                 return F.scaled_dot_product_attention(q, kx, vx, is_causal=True, scale=state.sm_scale, enable_gqa=True)
             mask = torch.ones(n_q, S, dtype=torch.bool, device=device).tril(S - n_q)

@@ -497,6 +497,88 @@ __global__ void __launch_bounds__(128) k2b_dequant_kernel(K2bGeom g, const uint8
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Page dequantizer of the dense prefill route: the same arithmetic as above, then the rotation of the keys at their
+// absolute positions in float32 and ONE rounding to the model's 16-bit type, written straight into
+// (batch, h_kv, row_stride, 128) tensors whose tail the caller fills with the fp16 window.  What bmx builds in float32,
+// rotates and casts (src/bmx/cache/chunked_attention.py:320-395) costs 20 bytes of transient per element this way; here 4.
+// One block per (sequence, page, head); thread = one rotary pair (c, c + 64) of every second row.
+// ---------------------------------------------------------------------------------------------
+template <typename OutT>
+__device__ __forceinline__ OutT to_out(float x);
+template <>
+__device__ __forceinline__ __half to_out<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+template <typename OutT>
+__global__ void __launch_bounds__(128) k2b_dequant_dense_kernel(K2bGeom g, const uint8_t* __restrict__ pages,
+                                                                const __half* __restrict__ coefs, const __half* __restrict__ basis16,
+                                                                const float* __restrict__ signs, const float* __restrict__ codebook,
+                                                                const int32_t* __restrict__ page_table, int table_stride, int n_pg,
+                                                                const __half* __restrict__ rope_cos, const __half* __restrict__ rope_sin,
+                                                                int64_t pos_offset, OutT* __restrict__ k_out, OutT* __restrict__ v_out,
+                                                                int64_t row_stride) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* us = reinterpret_cast<float*>(smem);
+  const int b = blockIdx.x / n_pg, j = blockIdx.x % n_pg, h = blockIdx.y;
+  const int slot = page_table[(int64_t)b * table_stride + j], page = g.page, group = g.group, rank = g.rank;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint8_t* blk = pages + ((int64_t)slot * g.h_kv + h) * k2b_page_block_bytes(page, group);
+  const uint32_t* kres = reinterpret_cast<const uint32_t*>(blk);
+  const __half* kscale = reinterpret_cast<const __half*>(blk + k2b_off_kscale(page));
+  const uint32_t* vw = reinterpret_cast<const uint32_t*>(blk + k2b_off_vcode(page, group));
+  const __half* vn = reinterpret_cast<const __half*>(blk + k2b_off_vnorm(page, group));
+  const int ch = (g.n_coef_heads == 1) ? 0 : h;
+  const __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (page * rank);
+  const int64_t out_row0 = ((int64_t)b * g.h_kv + h) * row_stride + (int64_t)j * page;  // first row of this page in the outputs
+  if (k_out) {
+    for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
+    __syncthreads();
+    const int c1 = tid & 63, c2 = c1 + 64;
+    float vb1[32], vb2[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      vb1[i] = (i < rank) ? __half2float(basis16[((int64_t)h * HEAD_DIM + c1) * rank + i]) : 0.f;
+      vb2[i] = (i < rank) ? __half2float(basis16[((int64_t)h * HEAD_DIM + c2) * rank + i]) : 0.f;
+    }
+    for (int r = tid >> 6; r < page; r += 2) {
+      float L1 = 0.f, L2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < rank) L1 = fmaf(us[r * rank + i], vb1[i], L1), L2 = fmaf(us[r * rank + i], vb2[i], L2);
+      const int grp = r / group;
+      float x1 = L1 + (float)k2b_read_kcode(g.layout, kres, r, c1) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c1)]);
+      float x2 = L2 + (float)k2b_read_kcode(g.layout, kres, r, c2) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c2)]);
+      if (rope_cos) {  // x * cos + rotate_half(x) * sin, tables (position, 128)
+        const int64_t pos = pos_offset + (int64_t)j * page + r;
+        const float cs1 = __half2float(rope_cos[pos * HEAD_DIM + c1]), sn1 = __half2float(rope_sin[pos * HEAD_DIM + c1]);
+        const float cs2 = __half2float(rope_cos[pos * HEAD_DIM + c2]), sn2 = __half2float(rope_sin[pos * HEAD_DIM + c2]);
+        const float y1 = x1 * cs1 - x2 * sn1, y2 = x2 * cs2 + x1 * sn2;
+        x1 = y1, x2 = y2;
+      }
+      OutT* dst = k_out + (out_row0 + r) * HEAD_DIM;
+      dst[c1] = to_out<OutT>(x1), dst[c2] = to_out<OutT>(x2);
+    }
+  }
+  if (v_out) {
+    float sg[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) sg[k] = signs[4 * lane + k];
+    const float sqrt_d = 11.313708498984761f;
+    for (int r = warp; r < page; r += 4) {
+      float x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = codebook[k2b_read_vcode(g.layout, vw, r, 4 * lane + k)] / sqrt_d;
+      fwht128_warp(x, lane);
+      const float nn = __half2float(vn[r]);
+      OutT* dst = v_out + (out_row0 + r) * HEAD_DIM + 4 * lane;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) dst[k] = to_out<OutT>((x[k] * sg[k]) * nn);
+    }
+  }
+}
+
 static int check_geom(const bmxk_k2b_geom* g, const char* who) {
   BMXK_REQUIRE(g != nullptr, "%s: null geometry", who);
   BMXK_REQUIRE(g->h_kv >= 1 && g->h_kv <= 64, "%s: h_kv=%d out of range", who, g->h_kv);
@@ -676,6 +758,35 @@ int bmxk_k2b_dequant_pages(const bmxk_k2b_geom* g, const void* pages, const void
                                                                       (const __half*)coefs, (const __half*)basis_f16,
                                                                       signs, codebook, slots, k_out, v_out);
   return check_launch("bmxk_k2b_dequant_pages");
+}
+
+int bmxk_k2b_dequant_dense(const bmxk_k2b_geom* g, const void* pages, const void* coefs, const void* basis_f16,
+                           const float* signs, const float* codebook, const int32_t* page_table, int table_stride,
+                           int n_pages, int batch, const void* rope_cos, const void* rope_sin, int64_t pos_offset,
+                           void* k_out, void* v_out, int64_t row_stride, int out_dtype, void* stream) {
+  int rc = check_geom(g, "bmxk_k2b_dequant_dense");
+  if (rc) return rc;
+  BMXK_REQUIRE(n_pages >= 0 && batch >= 1 && (int64_t)n_pages * batch <= 0x7fffffff, "bmxk_k2b_dequant_dense: n_pages=%d batch=%d", n_pages, batch);
+  if (n_pages == 0) return BMXK_OK;
+  BMXK_REQUIRE(pages && coefs && page_table && table_stride >= n_pages, "bmxk_k2b_dequant_dense: null pointer or table_stride=%d < n_pages", table_stride);
+  BMXK_REQUIRE(!k_out || basis_f16, "bmxk_k2b_dequant_dense: keys need basis_f16");
+  BMXK_REQUIRE(!v_out || (signs && codebook), "bmxk_k2b_dequant_dense: values need signs and codebook");
+  BMXK_REQUIRE((rope_cos == nullptr) == (rope_sin == nullptr), "bmxk_k2b_dequant_dense: one rotation table without the other");
+  BMXK_REQUIRE(row_stride >= (int64_t)n_pages * g->page, "bmxk_k2b_dequant_dense: row_stride=%lld below the %d committed rows",
+               (long long)row_stride, n_pages * g->page);
+  BMXK_REQUIRE(out_dtype == BMXK_DTYPE_F16 || out_dtype == BMXK_DTYPE_BF16, "bmxk_k2b_dequant_dense: out_dtype=%d (fp16 or bf16)", out_dtype);
+  BMXK_REQUIRE(g->h_kv <= 65535, "bmxk_k2b_dequant_dense: h_kv=%d", g->h_kv);
+  const size_t smem = (size_t)g->page * g->rank * 4;
+  const dim3 grid((unsigned)(n_pages * batch), (unsigned)g->h_kv);
+  if (out_dtype == BMXK_DTYPE_F16)
+    k2b_dequant_dense_kernel<__half><<<grid, 128, smem, (cudaStream_t)stream>>>(
+        to_geom(g), (const uint8_t*)pages, (const __half*)coefs, (const __half*)basis_f16, signs, codebook, page_table, table_stride, n_pages,
+        (const __half*)rope_cos, (const __half*)rope_sin, pos_offset, (__half*)k_out, (__half*)v_out, row_stride);
+  else
+    k2b_dequant_dense_kernel<__nv_bfloat16><<<grid, 128, smem, (cudaStream_t)stream>>>(
+        to_geom(g), (const uint8_t*)pages, (const __half*)coefs, (const __half*)basis_f16, signs, codebook, page_table, table_stride, n_pages,
+        (const __half*)rope_cos, (const __half*)rope_sin, pos_offset, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, row_stride);
+  return check_launch("bmxk_k2b_dequant_dense");
 }
 
 }  // extern "C"

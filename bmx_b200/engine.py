@@ -215,6 +215,21 @@ class K2bLayerState:
     def seq_len(self) -> int:
         return self.committed + self.tail_len
 
+    def dense_kv(self, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
+        """Everything held as dense tensors (batch, h_kv, committed + window, 128) of the model's 16-bit type, for the
+        dense prefill route: the committed pages dequantized, keys rotated at their positions, by one kernel that writes
+        the final layout (4 bytes of transient per element), the fp16 window behind them."""
+        assert type(self) is K2bLayerState and dtype in (torch.float16, torch.bfloat16), (type(self).__name__, dtype)
+        S, n_pg = self.seq_len(), self.committed // self.page
+        kd = torch.empty(self.batch, self.geom.h_kv, S, HEAD_DIM, dtype=dtype, device=self.device)
+        vd = torch.empty_like(kd)
+        if n_pg:
+            K.k2b_dequant_dense(self.pool, self.page_table, n_pg, self.basis_f16, self.signs, self.codebook,
+                                self.rope_cos if self.pre_rope else None, self.rope_sin if self.pre_rope else None, kd, vd)
+        kd[:, :, self.committed:] = self.k_win[:, :, : self.tail_len]
+        vd[:, :, self.committed:] = self.v_win[:, :, : self.tail_len]
+        return kd, vd
+
     # ---- save / restore ---------------------------------------------------------------------
     def _pools(self) -> dict:
         return {"pages": self.pool.pages, "coefs": self.pool.coefs}

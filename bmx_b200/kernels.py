@@ -213,6 +213,24 @@ def k2b_dequant_pages(pool: K2bPool, slots: torch.Tensor, basis_f16: torch.Tenso
     return k, v
 
 
+def k2b_dequant_dense(pool: K2bPool, page_table: torch.Tensor, n_pages: int, basis_f16: torch.Tensor, signs: torch.Tensor,
+                      codebook: torch.Tensor, rope_cos: torch.Tensor | None, rope_sin: torch.Tensor | None, k_out: torch.Tensor,
+                      v_out: torch.Tensor, pos_offset: int = 0) -> None:
+    """The first n_pages pages of every sequence -> rotated keys and values in k_out / v_out (batch, h_kv, rows, 128), fp16
+    or bf16, rows 0 .. n_pages*page - 1; the rest of the rows is the caller's (the fp16 window)."""
+    g = pool.geom
+    _require_cuda(page_table, k_out, v_out)
+    batch = page_table.shape[0]
+    assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1
+    assert k_out.shape == v_out.shape and k_out.shape[:2] == (batch, g.h_kv) and k_out.shape[3] == HEAD_DIM
+    assert k_out.is_contiguous() and v_out.is_contiguous() and k_out.dtype == v_out.dtype
+    assert k_out.dtype in (torch.float16, torch.bfloat16), k_out.dtype
+    assert rope_cos is None or (rope_cos.dtype == torch.float16 and rope_sin.dtype == torch.float16)
+    call("bmxk_k2b_dequant_dense", ctypes.byref(g), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16), _ptr(signs), _ptr(codebook),
+         _ptr(page_table), page_table.stride(0), int(n_pages), batch, _ptr(rope_cos), _ptr(rope_sin), int(pos_offset), _ptr(k_out),
+         _ptr(v_out), k_out.shape[2], DTYPE_BF16 if k_out.dtype == torch.bfloat16 else DTYPE_F16, _stream())
+
+
 @functools.lru_cache(maxsize=8)
 def make_v_lut(codebook: tuple) -> tuple:
     """(lo bytes, hi bytes, alpha bits, beta bits) of the fp16 value-level table for `codebook`."""

@@ -152,17 +152,18 @@ class PackedStreamingLayer(DynamicLayer):
     """Per-layer packed cache: page pool + frozen key basis + fp16 recent window."""
 
     # Prompt attention over a k2b cache has two routes.  "paged": the kernel that dequantizes one page at a time in shared
-    # memory (no dense K / V for the context); "dense": dequantize every committed page, then the library's
-    # scaled_dot_product_attention (what bmx does).  The dense route pays for the dequantization of the whole context once,
-    # the paged kernel once per block of 128 / G query positions: measured at 16384 committed tokens, 2048 new rows take
-    # 1.29 ms paged against 1.80 ms dense, the whole prompt 5.0 ms against 2.33 ms, and both sides grow with the context
-    # alike, so the crossover sits near 2800 rows whatever the context.  "auto" takes the paged kernel for blocks of up to
-    # PAGED_MAX_ROWS rows (a chunk of a chunked prefill, a follow-up turn), and for longer blocks once the dense route's
-    # transient would pass DENSE_PREFILL_BUDGET bytes.
+    # memory (no dense K / V for the context); "dense": dequantize every committed page (one kernel writes rotated K and V
+    # in the model's 16-bit type), then the library's scaled_dot_product_attention (what bmx does, in float32 and with
+    # five times the transient).  The dense route pays for the dequantization of the whole context once, the paged kernel
+    # once per block of 128 / G query positions: measured at 16384 committed tokens, 512 new rows take 0.37 ms paged
+    # against 0.84 ms dense, 2048 rows 1.30 against 1.34 ms, the whole prompt 5.0 against 1.9 ms, and both sides grow
+    # with the context alike, so the crossover sits near 2000 rows whatever the context.  "auto" takes the paged kernel
+    # for blocks of up to PAGED_MAX_ROWS rows (a follow-up turn, a chunk of a chunked prefill), and for longer blocks once
+    # the dense route's transient would pass DENSE_PREFILL_BUDGET bytes.
     PREFILL_ROUTES = ("auto", "paged", "dense")
-    PAGED_MAX_ROWS = 2560
+    PAGED_MAX_ROWS = 2048
     DENSE_PREFILL_BUDGET = 1 << 30
-    DENSE_BYTES_PER_ELEMENT = 20  # measured: float32 page dequantizer output, the rotated copy, fp16 K and V, the concatenation
+    DENSE_BYTES_PER_ELEMENT = 12  # measured peak: K and V in the model's 16-bit type (4) + the attention call's own workspace
 
     def __init__(self, k_spec: CacheCodecSpec, v_spec: CacheCodecSpec, model_config, recent_window: int = 32,
                  pack_v: bool = True, pack_k: bool = True, pack=None, prefill_route: str = "auto"):
@@ -366,6 +367,8 @@ class PackedStreamingLayer(DynamicLayer):
         """All committed pages dequantized (keys rotated at their positions) + the window: (b, h_kv, S, d)."""
         st = self._state
         n_pg = st.committed // self._page
+        if self._kind == "k2b" and dtype in (torch.float16, torch.bfloat16):
+            return st.dense_kv(dtype)
         parts_k, parts_v = [], []
         if n_pg:
             if self._kind in ("spectral", "rtn"):
@@ -423,8 +426,14 @@ class PackedStreamingLayer(DynamicLayer):
             if out is not None:
                 return out.to(q.dtype)
         Kd, Vd = self._dense_kv(q.dtype)
+        gqa = self._n_q_groups > 1
         if attention_mask is None:  # no mask: a multi-row block is the whole prompt, causal; KV heads are shared, not copied
-            return F.scaled_dot_product_attention(q, Kd, Vd, is_causal=n_q > 1, scale=scaling, enable_gqa=self._n_q_groups > 1)
+            return F.scaled_dot_product_attention(q, Kd, Vd, is_causal=n_q > 1, scale=scaling, enable_gqa=gqa)
+        if self._mask_is_causal(attention_mask, n_q, S):  # the model's plain causal mask: no per-sequence mask, no copies of K / V
+            if n_q == S:
+                return F.scaled_dot_product_attention(q, Kd, Vd, is_causal=n_q > 1, scale=scaling, enable_gqa=gqa)
+            mask = torch.ones(n_q, S, dtype=torch.bool, device=q.device).tril(S - n_q)
+            return F.scaled_dot_product_attention(q, Kd, Vd, attn_mask=mask, scale=scaling, enable_gqa=gqa)
         Kx = Kd.repeat_interleave(self._n_q_groups, dim=1)
         Vx = Vd.repeat_interleave(self._n_q_groups, dim=1)
         return F.scaled_dot_product_attention(q, Kx, Vx, attn_mask=attention_mask, scale=scaling)

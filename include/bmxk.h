@@ -104,6 +104,17 @@ int bmxk_k2b_dequant_pages(const bmxk_k2b_geom* g, const void* pages, const void
                            const float* signs, const float* codebook, const int32_t* slots, int n, float* k_out,
                            float* v_out, void* stream);
 
+/* The dense prefill route's dequantizer: the first n_pages pages of `batch` sequences (page_table rows of table_stride
+ * entries) -> keys rotated at their positions (float32 arithmetic, one rounding) and values, as fp16 or bf16
+ * (out_dtype) written into (batch, h_kv, row_stride, 128) tensors at rows 0 .. n_pages*page - 1; the caller appends the
+ * fp16 window behind them.  bmx: src/bmx/cache/chunked_attention.py:320-395 _prefill_dense_attention, which dequantizes
+ * to float32, rotates and casts.  rope_cos / rope_sin: fp16 (positions, 128), both NULL for keys stored rotated.
+ * Either output may be NULL. */
+int bmxk_k2b_dequant_dense(const bmxk_k2b_geom* g, const void* pages, const void* coefs, const void* basis_f16,
+                           const float* signs, const float* codebook, const int32_t* page_table, int table_stride,
+                           int n_pages, int batch, const void* rope_cos, const void* rope_sin, int64_t pos_offset,
+                           void* k_out, void* v_out, int64_t row_stride, int out_dtype, void* stream);
+
 /* ---- k2b split-KV decode ---------------------------------------------------------------- */
 /* Workspace (bytes) for a decode call over at most max_pages pages per sequence. */
 size_t bmxk_k2b_decode_workspace_bytes(const bmxk_k2b_geom* g, int batch, int max_pages);

@@ -120,6 +120,41 @@ def test_paged_prefill_random_geometries(prefill_kernel):
     print(f"paged prefill ({prefill_kernel}): worst relative error over 10 geometries {worst:.3e}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("page,rank,per_head,group", [(128, 32, True, 64), (64, 16, False, 32), (128, 16, True, 128)])
+def test_dense_route_dequantizer_equals_dequantize_rotate_cast(dtype, page, rank, per_head, group):
+    """The dense prefill route's one-kernel dequantizer (keys rotated in float32, one rounding to the model's type, written
+    in (batch, heads, rows, 128) with the window behind the pages) against the float32 page dequantizer + float32 rotation
+    + cast: the same arithmetic in the same order, so the 16-bit results are EQUAL."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+    from bmx_b200.rope import apply_rope
+
+    dev = torch.device("cuda:0")
+    n_seq, h_kv, n_pages, tail, W = 2, 2, 3, 37, 64
+    T = n_pages * page + tail
+    k_pre, v, basis = make_k2b_inputs(61, n_seq, h_kv, T, rank, per_head)
+    cos16, sin16 = rope_tables(T + 256)
+    cos, sin = torch.from_numpy(cos16).to(dev), torch.from_numpy(sin16).to(dev)
+    st = K2bLayerState(K.k2b_geom(h_kv, 4, page, rank, group, h_kv if per_head else 1), n_seq, T + 256, W, dev, cos, sin)
+    st.set_basis(basis.to(dev))
+    st.append(k_pre.to(dev), apply_rope(k_pre.to(dev).float(), cos[:T].float(), sin[:T].float()).half(), v.to(dev))
+    n_pg = st.committed // page
+    assert n_pg >= 1 and st.tail_len > 0
+    kd, vd = st.dense_kv(dtype)
+    assert kd.shape == vd.shape == (n_seq, h_kv, st.seq_len(), D) and kd.dtype == dtype
+    slots = st.page_table[:, :n_pg].contiguous().view(-1)
+    k32, v32 = K.k2b_dequant_pages(st.pool, slots, st.basis_f16, st.signs, st.codebook)
+    shp = (n_seq, n_pg * page, h_kv, D)
+    k32 = apply_rope(k32.view(*shp).permute(0, 2, 1, 3), cos[: st.committed].float(), sin[: st.committed].float())
+    assert torch.equal(kd[:, :, : st.committed], k32.to(dtype))
+    assert torch.equal(vd[:, :, : st.committed], v32.view(*shp).permute(0, 2, 1, 3).to(dtype))
+    assert torch.equal(kd[:, :, st.committed:], st.k_win[:, :, : st.tail_len].to(dtype))
+    assert torch.equal(vd[:, :, st.committed:], st.v_win[:, :, : st.tail_len].to(dtype))
+
+
 def test_paged_prefill_long_context_rows_near_the_end(prefill_kernel):
     """A 16384-token context and 64 query rows at its end: every page is fully visible, the window partly."""
     err, _, _ = _case(n_seq=1, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=128, tail=90, n_q=64, seed=53)
@@ -169,7 +204,7 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
 
     # "auto": blocks of up to PAGED_MAX_ROWS rows take the paged kernel (it beats dequantize + SDPA there); longer blocks
     # take the dense route until its transient would pass DENSE_PREFILL_BUDGET
-    assert PackedStreamingLayer.DENSE_PREFILL_BUDGET == 1 << 30 and PackedStreamingLayer.PAGED_MAX_ROWS == 2560
+    assert PackedStreamingLayer.DENSE_PREFILL_BUDGET == 1 << 30 and PackedStreamingLayer.PAGED_MAX_ROWS == 2048
     cache = PackedStreamingCache(model.config, k_spec, v_spec, recent_window=32)
     n_before = len(calls)
     K2bLayerState.prefill_attend = lambda self, q, q_pos0, out=None: calls.append("auto") or orig(self, q, q_pos0, out)
@@ -188,7 +223,7 @@ def test_cache_prefill_takes_the_paged_route_and_agrees_with_the_dense_one():
     finally:
         K2bLayerState.prefill_attend = orig
         PackedStreamingLayer.DENSE_PREFILL_BUDGET = 1 << 30
-        PackedStreamingLayer.PAGED_MAX_ROWS = 2560
+        PackedStreamingLayer.PAGED_MAX_ROWS = 2048
     assert float((torch.cat([la, lb], 1) - ld).abs().max()) < 5e-2
     diff = float((lp - ld).abs().max())
     print(f"paged vs dense prefill logits: max diff {diff:.3e}")
