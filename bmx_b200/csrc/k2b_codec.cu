@@ -502,7 +502,7 @@ __global__ void __launch_bounds__(128) k2b_dequant_kernel(K2bGeom g, const uint8
 // absolute positions in float32 and ONE rounding to the model's 16-bit type, written straight into
 // (batch, h_kv, row_stride, 128) tensors whose tail the caller fills with the fp16 window.  What bmx builds in float32,
 // rotates and casts (src/bmx/cache/chunked_attention.py:320-395) costs 20 bytes of transient per element this way; here 4.
-// One block per (sequence, page, head); thread = one rotary pair (c, c + 64) of every second row.
+// One block per (sequence, page, head).
 // ---------------------------------------------------------------------------------------------
 template <typename OutT>
 __device__ __forceinline__ OutT to_out(float x);
@@ -511,72 +511,126 @@ __device__ __forceinline__ __half to_out<__half>(float x) { return __float2half_
 template <>
 __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+constexpr int DD_THREADS = 256, DD_BP = 40, DD_KP = 136;  // halves per staged coefficient / basis row and per staged key row
+
 template <typename OutT>
-__global__ void __launch_bounds__(128) k2b_dequant_dense_kernel(K2bGeom g, const uint8_t* __restrict__ pages,
-                                                                const __half* __restrict__ coefs, const __half* __restrict__ basis16,
-                                                                const float* __restrict__ signs, const float* __restrict__ codebook,
-                                                                const int32_t* __restrict__ page_table, int table_stride, int n_pg,
-                                                                const __half* __restrict__ rope_cos, const __half* __restrict__ rope_sin,
-                                                                int64_t pos_offset, OutT* __restrict__ k_out, OutT* __restrict__ v_out,
-                                                                int64_t row_stride) {
+__device__ __forceinline__ uint32_t pack2_out(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2_out<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2_out<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// The page block, the coefficients (as plain rows) and the head's basis are staged in shared memory; the low-rank
+// product runs as mma.sync (fp16 operands are the stored values, fp32 accumulators), each warp 16 token rows; a
+// thread then holds both channels of every rotary pair of its rows, adds code x scale, rotates and stages the rows
+// for 16-byte stores.  Values: one warp per token row (butterflies over the lanes), 8-byte stores.
+template <typename OutT>
+__global__ void __launch_bounds__(DD_THREADS) k2b_dequant_dense_kernel(K2bGeom g, const uint8_t* __restrict__ pages,
+                                                                       const __half* __restrict__ coefs, const __half* __restrict__ basis16,
+                                                                       const float* __restrict__ signs, const float* __restrict__ codebook,
+                                                                       const int32_t* __restrict__ page_table, int table_stride, int n_pg,
+                                                                       const __half* __restrict__ rope_cos, const __half* __restrict__ rope_sin,
+                                                                       int64_t pos_offset, OutT* __restrict__ k_out, OutT* __restrict__ v_out,
+                                                                       int64_t row_stride) {
   extern __shared__ __align__(16) uint8_t smem[];
-  float* us = reinterpret_cast<float*>(smem);
   const int b = blockIdx.x / n_pg, j = blockIdx.x % n_pg, h = blockIdx.y;
   const int slot = page_table[(int64_t)b * table_stride + j], page = g.page, group = g.group, rank = g.rank;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint8_t* blk = pages + ((int64_t)slot * g.h_kv + h) * k2b_page_block_bytes(page, group);
-  const uint32_t* kres = reinterpret_cast<const uint32_t*>(blk);
-  const __half* kscale = reinterpret_cast<const __half*>(blk + k2b_off_kscale(page));
-  const uint32_t* vw = reinterpret_cast<const uint32_t*>(blk + k2b_off_vcode(page, group));
-  const __half* vn = reinterpret_cast<const __half*>(blk + k2b_off_vnorm(page, group));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+  const int PB = k2b_page_block_bytes(page, group);
+  uint8_t* raw = smem;
+  __half* ca = reinterpret_cast<__half*>(raw + ((PB + 15) & ~15));  // [page][DD_BP]
+  __half* bb = ca + 128 * DD_BP;                                     // [128][DD_BP]
+  OutT* kt = reinterpret_cast<OutT*>(bb + 128 * DD_BP);              // [page][DD_KP]
+  const uint8_t* blk = pages + ((int64_t)slot * g.h_kv + h) * PB;
   const int ch = (g.n_coef_heads == 1) ? 0 : h;
   const __half* cblk = coefs + ((int64_t)slot * g.n_coef_heads + ch) * (page * rank);
-  const int64_t out_row0 = ((int64_t)b * g.h_kv + h) * row_stride + (int64_t)j * page;  // first row of this page in the outputs
+  for (int o = tid; o < PB / 16; o += DD_THREADS) reinterpret_cast<uint4*>(raw)[o] = reinterpret_cast<const uint4*>(blk)[o];
   if (k_out) {
-    for (int o = tid; o < page * rank; o += blockDim.x) us[o] = __half2float(cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)]);
-    __syncthreads();
-    const int c1 = tid & 63, c2 = c1 + 64;
-    float vb1[32], vb2[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      vb1[i] = (i < rank) ? __half2float(basis16[((int64_t)h * HEAD_DIM + c1) * rank + i]) : 0.f;
-      vb2[i] = (i < rank) ? __half2float(basis16[((int64_t)h * HEAD_DIM + c2) * rank + i]) : 0.f;
-    }
-    for (int r = tid >> 6; r < page; r += 2) {
-      float L1 = 0.f, L2 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < rank) L1 = fmaf(us[r * rank + i], vb1[i], L1), L2 = fmaf(us[r * rank + i], vb2[i], L2);
-      const int grp = r / group;
-      float x1 = L1 + (float)k2b_read_kcode(g.layout, kres, r, c1) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c1)]);
-      float x2 = L2 + (float)k2b_read_kcode(g.layout, kres, r, c2) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c2)]);
-      if (rope_cos) {  // x * cos + rotate_half(x) * sin, tables (position, 128)
-        const int64_t pos = pos_offset + (int64_t)j * page + r;
-        const float cs1 = __half2float(rope_cos[pos * HEAD_DIM + c1]), sn1 = __half2float(rope_sin[pos * HEAD_DIM + c1]);
-        const float cs2 = __half2float(rope_cos[pos * HEAD_DIM + c2]), sn2 = __half2float(rope_sin[pos * HEAD_DIM + c2]);
-        const float y1 = x1 * cs1 - x2 * sn1, y2 = x2 * cs2 + x1 * sn2;
-        x1 = y1, x2 = y2;
-      }
-      OutT* dst = k_out + (out_row0 + r) * HEAD_DIM;
-      dst[c1] = to_out<OutT>(x1), dst[c2] = to_out<OutT>(x2);
+    for (int o = tid; o < page * rank; o += DD_THREADS) ca[(o / rank) * DD_BP + o % rank] = cblk[k2b_coef_idx(g.layout, o / rank, o % rank, rank)];
+    for (int o = tid; o < 128 * (rank / 8); o += DD_THREADS) {
+      const int c = o / (rank / 8), i8 = o % (rank / 8);
+      *reinterpret_cast<uint4*>(bb + c * DD_BP + 8 * i8) = reinterpret_cast<const uint4*>(basis16 + ((int64_t)h * HEAD_DIM + c) * rank)[i8];
     }
   }
+  __syncthreads();
+  const uint32_t* kres = reinterpret_cast<const uint32_t*>(raw);
+  const __half* kscale = reinterpret_cast<const __half*>(raw + k2b_off_kscale(page));
+  const uint32_t* vw = reinterpret_cast<const uint32_t*>(raw + k2b_off_vcode(page, group));
+  const __half* vn = reinterpret_cast<const __half*>(raw + k2b_off_vnorm(page, group));
+  const int64_t out_row0 = ((int64_t)b * g.h_kv + h) * row_stride + (int64_t)j * page;  // first row of this page in the outputs
+  if (k_out && 16 * warp < page) {
+    float c[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+    for (int ks = 0; ks < rank / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4(a0, a1, a2, a3, smem_u32(ca + (16 * warp + (lane & 15)) * DD_BP + 16 * ks + 8 * (lane >> 4)));
+#pragma unroll
+      for (int n2 = 0; n2 < 8; ++n2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, smem_u32(bb + (16 * n2 + (lane & 7) + ((lane >> 4) << 3)) * DD_BP + 16 * ks + (((lane >> 3) & 1) << 3)));
+        mma_f32acc(c[2 * n2][0], c[2 * n2][1], c[2 * n2][2], c[2 * n2][3], a0, a1, a2, a3, b0, b1);
+        mma_f32acc(c[2 * n2 + 1][0], c[2 * n2 + 1][1], c[2 * n2 + 1][2], c[2 * n2 + 1][3], a0, a1, a2, a3, b2, b3);
+      }
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = 16 * warp + gq + 8 * rr, grp = r / group;
+      const int64_t pos = pos_offset + (int64_t)j * page + r;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {  // channels 8n + 2tq + {0, 1} and their rotary partners 64 further
+        const int c1 = 8 * n + 2 * tq, c2 = c1 + 64;
+        float x1[2], x2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          x1[e] = c[n][2 * rr + e] + (float)k2b_read_kcode(g.layout, kres, r, c1 + e) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c1 + e)]);
+          x2[e] = c[n + 8][2 * rr + e] + (float)k2b_read_kcode(g.layout, kres, r, c2 + e) * __half2float(kscale[k2b_kscale_idx(g.layout, grp, c2 + e)]);
+        }
+        if (rope_cos) {  // x * cos + rotate_half(x) * sin, tables (position, 128)
+          const float2 cs1 = __half22float2(*reinterpret_cast<const __half2*>(rope_cos + pos * HEAD_DIM + c1));
+          const float2 sn1 = __half22float2(*reinterpret_cast<const __half2*>(rope_sin + pos * HEAD_DIM + c1));
+          const float2 cs2 = __half22float2(*reinterpret_cast<const __half2*>(rope_cos + pos * HEAD_DIM + c2));
+          const float2 sn2 = __half22float2(*reinterpret_cast<const __half2*>(rope_sin + pos * HEAD_DIM + c2));
+          const float y10 = x1[0] * cs1.x - x2[0] * sn1.x, y11 = x1[1] * cs1.y - x2[1] * sn1.y;
+          const float y20 = x2[0] * cs2.x + x1[0] * sn2.x, y21 = x2[1] * cs2.y + x1[1] * sn2.y;
+          x1[0] = y10, x1[1] = y11, x2[0] = y20, x2[1] = y21;
+        }
+        *reinterpret_cast<uint32_t*>(kt + r * DD_KP + c1) = pack2_out<OutT>(x1[0], x1[1]);
+        *reinterpret_cast<uint32_t*>(kt + r * DD_KP + c2) = pack2_out<OutT>(x2[0], x2[1]);
+      }
+    }
+  }
+  __syncthreads();
+  if (k_out)
+    for (int o = tid; o < page * 16; o += DD_THREADS) {
+      const int r = o >> 4, c8 = o & 15;
+      reinterpret_cast<uint4*>(k_out + (out_row0 + r) * HEAD_DIM)[c8] = *reinterpret_cast<const uint4*>(kt + r * DD_KP + 8 * c8);
+    }
   if (v_out) {
     float sg[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) sg[k] = signs[4 * lane + k];
     const float sqrt_d = 11.313708498984761f;
-    for (int r = warp; r < page; r += 4) {
+    for (int r = warp; r < page; r += DD_THREADS / 32) {
       float x[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) x[k] = codebook[k2b_read_vcode(g.layout, vw, r, 4 * lane + k)] / sqrt_d;
       fwht128_warp(x, lane);
       const float nn = __half2float(vn[r]);
-      OutT* dst = v_out + (out_row0 + r) * HEAD_DIM + 4 * lane;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) dst[k] = to_out<OutT>((x[k] * sg[k]) * nn);
+      const uint2 w = make_uint2(pack2_out<OutT>((x[0] * sg[0]) * nn, (x[1] * sg[1]) * nn), pack2_out<OutT>((x[2] * sg[2]) * nn, (x[3] * sg[3]) * nn));
+      *reinterpret_cast<uint2*>(v_out + (out_row0 + r) * HEAD_DIM + 4 * lane) = w;
     }
   }
+}
+
+static size_t dequant_dense_smem(int page, int group) {
+  return (size_t)((k2b_page_block_bytes(page, group) + 15) & ~15) + (size_t)2 * 128 * DD_BP * 2 + (size_t)page * DD_KP * 2;
 }
 
 static int check_geom(const bmxk_k2b_geom* g, const char* who) {
@@ -776,14 +830,27 @@ int bmxk_k2b_dequant_dense(const bmxk_k2b_geom* g, const void* pages, const void
                (long long)row_stride, n_pages * g->page);
   BMXK_REQUIRE(out_dtype == BMXK_DTYPE_F16 || out_dtype == BMXK_DTYPE_BF16, "bmxk_k2b_dequant_dense: out_dtype=%d (fp16 or bf16)", out_dtype);
   BMXK_REQUIRE(g->h_kv <= 65535, "bmxk_k2b_dequant_dense: h_kv=%d", g->h_kv);
-  const size_t smem = (size_t)g->page * g->rank * 4;
+  BMXK_REQUIRE(((uintptr_t)pages & 15) == 0 && ((uintptr_t)basis_f16 & 15) == 0 && (!k_out || ((uintptr_t)k_out & 15) == 0) &&
+                   (!v_out || ((uintptr_t)v_out & 7) == 0) && (!rope_cos || (((uintptr_t)rope_cos | (uintptr_t)rope_sin) & 3) == 0),
+               "bmxk_k2b_dequant_dense: misaligned buffer");
+  const size_t smem = dequant_dense_smem(g->page, g->group);
   const dim3 grid((unsigned)(n_pages * batch), (unsigned)g->h_kv);
+  static PerDeviceOnce configured;
+  if (configured.first()) {
+    cudaError_t e1 = cudaFuncSetAttribute(k2b_dequant_dense_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaError_t e2 = cudaFuncSetAttribute(k2b_dequant_dense_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) {
+      configured.retract();
+      set_error("bmxk_k2b_dequant_dense: cudaFuncSetAttribute: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+      return BMXK_ERR_CUDA;
+    }
+  }
   if (out_dtype == BMXK_DTYPE_F16)
-    k2b_dequant_dense_kernel<__half><<<grid, 128, smem, (cudaStream_t)stream>>>(
+    k2b_dequant_dense_kernel<__half><<<grid, DD_THREADS, smem, (cudaStream_t)stream>>>(
         to_geom(g), (const uint8_t*)pages, (const __half*)coefs, (const __half*)basis_f16, signs, codebook, page_table, table_stride, n_pages,
         (const __half*)rope_cos, (const __half*)rope_sin, pos_offset, (__half*)k_out, (__half*)v_out, row_stride);
   else
-    k2b_dequant_dense_kernel<__nv_bfloat16><<<grid, 128, smem, (cudaStream_t)stream>>>(
+    k2b_dequant_dense_kernel<__nv_bfloat16><<<grid, DD_THREADS, smem, (cudaStream_t)stream>>>(
         to_geom(g), (const uint8_t*)pages, (const __half*)coefs, (const __half*)basis_f16, signs, codebook, page_table, table_stride, n_pages,
         (const __half*)rope_cos, (const __half*)rope_sin, pos_offset, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, row_stride);
   return check_launch("bmxk_k2b_dequant_dense");

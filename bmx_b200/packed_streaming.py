@@ -155,11 +155,12 @@ class PackedStreamingLayer(DynamicLayer):
     # memory (no dense K / V for the context); "dense": dequantize every committed page (one kernel writes rotated K and V
     # in the model's 16-bit type), then the library's scaled_dot_product_attention (what bmx does, in float32 and with
     # five times the transient).  The dense route pays for the dequantization of the whole context once, the paged kernel
-    # once per block of 128 / G query positions: measured at 16384 committed tokens, 512 new rows take 0.37 ms paged
-    # against 0.84 ms dense, 2048 rows 1.30 against 1.34 ms, the whole prompt 5.0 against 1.9 ms, and both sides grow
-    # with the context alike, so the crossover sits near 2000 rows whatever the context.  "auto" takes the paged kernel
-    # for blocks of up to PAGED_MAX_ROWS rows (a follow-up turn, a chunk of a chunked prefill), and for longer blocks once
-    # the dense route's transient would pass DENSE_PREFILL_BUDGET bytes.
+    # once per block of 128 / G query positions, but the library's attention is slow on few rows against a long context.
+    # Measured at 16384 committed tokens, B = 1: 512 new rows 0.37 ms paged against 0.67 ms dense, 2048 rows 1.30 against
+    # 1.15 ms, the whole prompt 5.0 against 1.76 ms; under a model at B = 4 (context growing through the prompt) 2048-row
+    # blocks are 1.6 x faster paged.  "auto" takes the paged kernel for blocks of up to PAGED_MAX_ROWS rows (a follow-up
+    # turn, a chunk of a chunked prefill), and for longer blocks once the dense route's transient would pass
+    # DENSE_PREFILL_BUDGET bytes.
     PREFILL_ROUTES = ("auto", "paged", "dense")
     PAGED_MAX_ROWS = 2048
     DENSE_PREFILL_BUDGET = 1 << 30

@@ -125,7 +125,9 @@ def test_paged_prefill_random_geometries(prefill_kernel):
 def test_dense_route_dequantizer_equals_dequantize_rotate_cast(dtype, page, rank, per_head, group):
     """The dense prefill route's one-kernel dequantizer (keys rotated in float32, one rounding to the model's type, written
     in (batch, heads, rows, 128) with the window behind the pages) against the float32 page dequantizer + float32 rotation
-    + cast: the same arithmetic in the same order, so the 16-bit results are EQUAL."""
+    + cast.  Values: the same arithmetic in the same order, EQUAL.  Keys: the low-rank product is summed by mma.sync in
+    another order (float32, ~1e-7), so a result may land on the other side of a 16-bit rounding boundary: at most one
+    unit in the last place, in well under 1 % of the entries."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from bmx_b200 import kernels as K
@@ -149,7 +151,10 @@ def test_dense_route_dequantizer_equals_dequantize_rotate_cast(dtype, page, rank
     k32, v32 = K.k2b_dequant_pages(st.pool, slots, st.basis_f16, st.signs, st.codebook)
     shp = (n_seq, n_pg * page, h_kv, D)
     k32 = apply_rope(k32.view(*shp).permute(0, 2, 1, 3), cos[: st.committed].float(), sin[: st.committed].float())
-    assert torch.equal(kd[:, :, : st.committed], k32.to(dtype))
+    got, want = kd[:, :, : st.committed].float(), k32.to(dtype).float()
+    ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+    assert bool(((got - want).abs() <= ulp * want.abs().clamp_min(2.0 ** -14)).all())
+    assert float((got != want).float().mean()) < 0.01
     assert torch.equal(vd[:, :, : st.committed], v32.view(*shp).permute(0, 2, 1, 3).to(dtype))
     assert torch.equal(kd[:, :, st.committed:], st.k_win[:, :, : st.tail_len].to(dtype))
     assert torch.equal(vd[:, :, st.committed:], st.v_win[:, :, : st.tail_len].to(dtype))
