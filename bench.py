@@ -828,7 +828,7 @@ def config_spectral(device, rank, world, dist, steps: int = 30) -> dict:
 
 def config_prefill(device) -> dict:
     """Prefill attention of the k2b cache: one sequence of 16384 committed tokens + a 128-token window (32 q / 8 kv heads);
-    (a) the last 512 and the last 2048 positions as one query block (a follow-up turn, a chunk of a chunked prefill), (b) the
+    (a) the last 32, 512 and 2048 positions as one query block (a follow-up turn, a chunk of a chunked prefill), (b) the
     whole prompt at once.  Timed:
     the paged kernel (pages dequantized in shared memory, no dense K / V; tcgen05, and the mma.sync kernel it succeeded)
     against the route it replaces, dequantize every page + rotate + scaled_dot_product_attention with the same causal mask.
@@ -848,14 +848,15 @@ def config_prefill(device) -> dict:
             tf_peak = float(json.load(f).get("bf16_tflops_sustained") or 0) or None
     except (OSError, ValueError):
         tf_peak = None
-    for name, n_q in (("last_512_rows", 512), ("last_2048_rows", 2048), ("whole_prompt", S)):
+    for name, n_q in (("last_32_rows", 32), ("last_512_rows", 512), ("last_2048_rows", 2048), ("whole_prompt", S)):
         q = (torch.randn(1, H, n_q, D, generator=gen, device=device) / math.sqrt(D)).half()
         o = torch.empty_like(q)
         K.k2b_prefill_select(1)  # the mma.sync kernel, for the record
         legacy_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
-        K.k2b_prefill_select(0)  # the tcgen05 kernel (default)
+        K.k2b_prefill_select(0)  # the tcgen05 kernel (default); few rows: the page walk shared out over CTAs + merge kernel
         paged_us = _event_us(lambda: state.prefill_attend(q, S - n_q, out=o), 3, warm=1)
         K.check_status(state.workspace)
+        n_split = state.prefill_split(n_q)
 
         def dense():  # the product's dense route: one dequantizer kernel writes rotated fp16 K and V in place, then SDPA
             kx, vx = state.dense_kv(torch.float16)
@@ -877,7 +878,7 @@ def config_prefill(device) -> dict:
                      "paged_tflops": flops / paged_us / 1e6, "peak_tflops": tf_peak,
                      "frac_of_tensor_peak": None if not tf_peak else flops / paged_us / 1e6 / tf_peak,
                      "dense_route_transient_bytes": int(dense_peak), "paged_route_transient_bytes": 0,
-                     "max_rel_diff_between_routes": err, "gpu_launches": 1}
+                     "max_rel_diff_between_routes": err, "page_walk_shares": n_split, "gpu_launches": 1 if n_split == 1 else 2}
         del q, o, ref
     return out
 

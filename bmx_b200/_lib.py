@@ -73,6 +73,10 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
                                  c_void_p, c_void_p, c_void_p]),
     "bmxk_k2b_prefill_select": (c_int, [c_int]),
+    "bmxk_k2b_prefill_workspace_bytes": (c_size_t, [POINTER(K2bGeom), c_int, c_int, c_int]),
+    "bmxk_k2b_prefill_split": (c_int, [POINTER(K2bGeom), c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                                       c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "bmxk_k2b_dequant_dense": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                        c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "bmxk_k2b_decode_static": (c_int, [POINTER(K2bGeom), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

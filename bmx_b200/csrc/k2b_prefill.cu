@@ -405,11 +405,42 @@ int bmxk_k2b_prefill_select(int kernel) {
   return BMXK_OK;
 }
 
+size_t bmxk_k2b_prefill_workspace_bytes(const bmxk_k2b_geom* g, int n_q, int batch, int n_split) {
+  if (!g || n_q < 1 || batch < 1 || n_split <= 1) return 0;
+  return (size_t)batch * g->h_kv * g->n_q_groups * n_q * n_split * PF_PART_STRIDE * sizeof(float);
+}
+
+static int prefill_impl(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
+                        const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
+                        const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                        const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
+                        int32_t* status, void* out, int n_split, void* workspace, size_t workspace_bytes, void* stream);
+
 int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
                      const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
                      const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
                      const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
                      int32_t* status, void* out, void* stream) {
+  return prefill_impl(g, q, n_q, q_pos0, pages, coefs, basis_f16, page_table, table_stride, n_pages, batch, rope_cos, rope_sin, pos_offset,
+                      k_tail, v_tail, tail_len, tail_cap, v_lut, signs, sm_scale, status, out, 1, nullptr, 0, stream);
+}
+
+int bmxk_k2b_prefill_split(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
+                           const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
+                           const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                           const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
+                           int32_t* status, void* out, int n_split, void* workspace, size_t workspace_bytes, void* stream) {
+  return prefill_impl(g, q, n_q, q_pos0, pages, coefs, basis_f16, page_table, table_stride, n_pages, batch, rope_cos, rope_sin, pos_offset,
+                      k_tail, v_tail, tail_len, tail_cap, v_lut, signs, sm_scale, status, out, n_split, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"
+
+static int prefill_impl(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
+                        const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
+                        const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                        const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
+                        int32_t* status, void* out, int n_split, void* workspace, size_t workspace_bytes, void* stream) {
   BMXK_REQUIRE(g != nullptr, "bmxk_k2b_prefill: null geometry");
   BMXK_REQUIRE(g->layout == 1 && g->page == 128, "bmxk_k2b_prefill: layout=%d page=%d (row-order pools of 128-token pages only)", g->layout,
                g->page);
@@ -444,7 +475,19 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
   const dim3 grid((unsigned)((n_q + pp - 1) / pp), (unsigned)g->h_kv, (unsigned)batch);
   cudaStream_t s = (cudaStream_t)stream;
   const bool aligned16 = ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0;
-  if (g_prefill_kernel.load(std::memory_order_relaxed) == 0 && aligned16) return launch_prefill_t5(prm, grid, s);
+  const bool t5 = g_prefill_kernel.load(std::memory_order_relaxed) == 0 && aligned16;
+  BMXK_REQUIRE(n_split >= 1 && n_split <= 64, "bmxk_k2b_prefill_split: n_split=%d must be in 1..64", n_split);
+  if (!t5) n_split = 1;  // the split is the tcgen05 kernel's; the mma.sync kernel walks every page of a block in one CTA
+  prm.n_split = n_split, prm.part = (float*)workspace;
+  if (n_split > 1) {
+    const size_t need = bmxk_k2b_prefill_workspace_bytes(g, n_q, batch, n_split);
+    BMXK_REQUIRE(workspace && workspace_bytes >= need && ((uintptr_t)workspace & 15) == 0,
+                 "bmxk_k2b_prefill_split: workspace of %zu bytes needed (16-byte aligned), %zu given", need, workspace_bytes);
+    BMXK_REQUIRE((int64_t)grid.x * n_split <= 0x7fffffff && (int64_t)batch * g->h_kv * g->n_q_groups * n_q <= 0x7fffffff,
+                 "bmxk_k2b_prefill_split: n_q=%d batch=%d n_split=%d too large", n_q, batch, n_split);
+    return launch_prefill_t5(prm, dim3(grid.x * (unsigned)n_split, grid.y, grid.z), s);
+  }
+  if (t5) return launch_prefill_t5(prm, grid, s);
   static PerDeviceOnce configured;
   if (configured.first()) {
     cudaError_t e1 = cudaFuncSetAttribute(k2b_prefill_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -460,4 +503,4 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
   return check_launch("bmxk_k2b_prefill");
 }
 
-}  // extern "C"
+

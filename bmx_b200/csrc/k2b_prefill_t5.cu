@@ -30,6 +30,10 @@
 // the last page and before the first window tile (whose values are not rotated).  Window tiles take the same route
 // with the key / value warps copying the fp16 window into the operand buffers (norm 1).
 //
+// Few query rows against a long context leave most SMs idle and one CTA with the whole page walk: with n_split > 1 the
+// visible pages of a block are shared out over n_split CTAs, each writes a partial record per row (accumulators after
+// the rotation is undone, running maximum, sum of weights) and a small kernel merges them.
+//
 // Every wait is bounded and reports through the status words; nothing here waits on another CTA.
 #include "prefill_common.cuh"
 #include "tc5.cuh"
@@ -118,18 +122,24 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the latest positions see the most pages: their blocks are scheduled first, so that the last wave is the lightest
-  const int b = blockIdx.z, h = blockIdx.y, i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * PP;
+  // (blockIdx.x = position block * n_split + share: the shares of a block run side by side)
+  const int n_split = p.n_split, share = (int)blockIdx.x % n_split, n_blocks = (int)gridDim.x / n_split;
+  const int b = blockIdx.z, h = blockIdx.y, i0 = (n_blocks - 1 - (int)blockIdx.x / n_split) * PP;
   const int H = g.h_kv * G;
 
   const int64_t pq_min = p.q_pos0 + i0;                                // first query position of the CTA
   const int64_t pq_max = p.q_pos0 + min(i0 + PP, p.n_q) - 1;           // last one
   const int n_pg = p.n_pages[b];
   const int64_t vis = pq_max - p.pos_offset;
-  const int NP = (vis < 0) ? 0 : (int)min((int64_t)n_pg, vis / 128 + 1);  // pages whose first token the last position sees
+  const int NPv = (vis < 0) ? 0 : (int)min((int64_t)n_pg, vis / 128 + 1);  // pages whose first token the last position sees
+  // this CTA's share of them: pages T0 .. T0 + NP - 1; the window goes with the last share
+  const int per_share = (NPv + n_split - 1) / n_split;
+  const int T0 = min(NPv, share * per_share), NP = min(NPv, T0 + per_share) - T0;
   const int tl = p.tail_len ? min(p.tail_len[b], p.tail_cap) : 0;
   const int64_t tail_pos0 = p.pos_offset + (int64_t)n_pg * 128;
-  const int NW = (tl > 0 && pq_max >= tail_pos0) ? (int)((min((int64_t)tl, pq_max - tail_pos0 + 1) + 127) / 128) : 0;
+  const int NW = (share == n_split - 1 && tl > 0 && pq_max >= tail_pos0) ? (int)((min((int64_t)tl, pq_max - tail_pos0 + 1) + 127) / 128) : 0;
   const int NT = NP + NW;
+  const int64_t page_pos0 = p.pos_offset + (int64_t)T0 * 128;  // position of the first key of this share
 
   // ---- prologue: barriers, tensor memory, the operands that do not change (Q, basis, constant rows of V') ----
   if (tid == 0) {
@@ -189,7 +199,7 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
     // chunk are reloaded for the next tile as soon as the chunk is done, so the loads have a whole tile to land
     uint4 cs4[2][2], sn4[2][2];
     auto load_rope = [&](int n, int kk) {
-      const int64_t pos = p.pos_offset + (int64_t)n * 128 + row;
+      const int64_t pos = page_pos0 + (int64_t)n * 128 + row;
       const uint4* pc = reinterpret_cast<const uint4*>(p.rope_cos + pos * HEAD_DIM + 16 * (k0 + kk));
       const uint4* ps = reinterpret_cast<const uint4*>(p.rope_sin + pos * HEAD_DIM + 16 * (k0 + kk));
       cs4[kk][0] = pc[0], cs4[kk][1] = pc[1], sn4[kk][0] = ps[0], sn4[kk][1] = ps[1];
@@ -446,7 +456,7 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
     };
 
     // keys of the current half visible to this row / to the CTA's first row: position - first key position + 1
-    int64_t rel = pq - p.pos_offset + 1, rel_min = pq_min - p.pos_offset + 1;
+    int64_t rel = pq - page_pos0 + 1, rel_min = pq_min - page_pos0 + 1;
     PROF_DECL(8)
     for (int u = 0; u < 2 * NT && alive; ++u) {  // half tile u = (tile n, half hf): tokens 64 hf .. 64 hf + 63
       const int n = u >> 1, hf = u & 1, e = n & 1;
@@ -538,7 +548,34 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
         const float l = __uint_as_float(r4[0]) + __uint_as_float(r4[1]);
         inv = (l > 0.f) ? 1.f / l : 0.f;
       }
-      uint4* dst = reinterpret_cast<uint4*>(p.out + (((int64_t)b * H + h * G + qi) * p.n_q + ip) * HEAD_DIM);
+      const int64_t grow = ((int64_t)b * H + h * G + qi) * p.n_q + ip;  // row of q / out
+      if (n_split > 1) {  // partial record of this share: unnormalised accumulators, running maximum, sum of weights
+        float* rec = p.part + (grow * n_split + share) * PF_PART_STRIDE;
+        float lsum = 0.f;
+        if (NT > 0) {
+          uint32_t r4[4];
+          tc5::ld4(tl_ + TM_O + 128, r4);
+          tc5::wait_ld();
+          lsum = __uint_as_float(r4[0]) + __uint_as_float(r4[1]);
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          if (NT > 0) {
+            tc5::ld32(tl_ + TM_O + 32 * c, r);
+            tc5::wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (ip < p.n_q) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(rec + 32 * c)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+        }
+        if (ip < p.n_q) *reinterpret_cast<float4*>(rec + 128) = make_float4(m, lsum, 0.f, 0.f);
+      } else {
+      uint4* dst = reinterpret_cast<uint4*>(p.out + grow * HEAD_DIM);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -559,6 +596,7 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
             dst[4 * c + j] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
           }
         }
+      }
       }
     }
   } else {
@@ -591,7 +629,7 @@ __global__ void __launch_bounds__(P5_THREADS, 1) k2b_prefill_t5_kernel(const Pre
       constexpr uint32_t ID_U1 = tc5::idesc_f16_f16(128, 128);
       const uint64_t d_stage = tc5::smem_desc(smem_u32(stage0), 128, AB_SBO), d_b = tc5::smem_desc(smem_u32(bop), 128, AB_SBO);
       const int chd = (g.n_coef_heads == 1) ? 0 : h;
-      const int32_t* table = p.page_table + (int64_t)b * p.table_stride;
+      const int32_t* table = p.page_table + (int64_t)b * p.table_stride + T0;
       int nP = 0, nA = 0, sP = 0, sA = 0;
       uint32_t phA = 0;
       int slot = (NP > 0) ? table[0] : 0;  // page slot of the next copy, fetched one copy ahead
@@ -708,10 +746,30 @@ static int launch_p5(const PrefillParams& prm, dim3 grid, size_t smem, cudaStrea
   return check_launch("bmxk_k2b_prefill(tcgen05)");
 }
 
+// out[row] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the n_split partial records of the row; one block of 128
+// threads (one per channel) per row.
+__global__ void __launch_bounds__(128) prefill_merge_kernel(const float* __restrict__ part, int n_split, __half* __restrict__ out) {
+  const int64_t row = blockIdx.x;
+  const float* rec = part + row * n_split * PF_PART_STRIDE;
+  float M = -INFINITY;
+  for (int s = 0; s < n_split; ++s) M = fmaxf(M, rec[s * PF_PART_STRIDE + 128]);
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < n_split; ++s) {
+    const float w = ex2_approx(rec[s * PF_PART_STRIDE + 128] - M);
+    acc = fmaf(w, rec[s * PF_PART_STRIDE + threadIdx.x], acc);
+    l = fmaf(w, rec[s * PF_PART_STRIDE + 129], l);
+  }
+  out[row * HEAD_DIM + threadIdx.x] = __float2half_rn(l > 0.f ? acc / l : 0.f);
+}
+
 int launch_prefill_t5(const PrefillParams& prm, dim3 grid, cudaStream_t s) {
   const size_t smem = p5_smem_bytes(prm.g.rank, prm.g.group);
   BMXK_REQUIRE(smem <= 227 * 1024, "bmxk_k2b_prefill: rank=%d group=%d needs %zu bytes of shared memory", prm.g.rank, prm.g.group, smem);
-  return prm.g.rank == 32 ? launch_p5<32>(prm, grid, smem, s) : launch_p5<16>(prm, grid, smem, s);
+  const int rc = prm.g.rank == 32 ? launch_p5<32>(prm, grid, smem, s) : launch_p5<16>(prm, grid, smem, s);
+  if (rc != BMXK_OK || prm.n_split <= 1) return rc;
+  const int64_t rows = (int64_t)grid.z * prm.g.h_kv * prm.g.n_q_groups * prm.n_q;
+  prefill_merge_kernel<<<(unsigned)rows, 128, 0, s>>>(prm.part, prm.n_split, prm.out);
+  return check_launch("bmxk_k2b_prefill(merge)");
 }
 
 }  // namespace bmxk

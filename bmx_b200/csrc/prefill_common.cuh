@@ -28,9 +28,16 @@ struct PrefillParams {
   float scale_log2;
   __half* out;
   int32_t* status;
+  // Split of the page range over CTAs (tcgen05 kernel only): n_split > 1 makes every CTA take one share of its block's
+  // visible pages (the last share also the window) and write a partial record per row -- 128 accumulators, running
+  // maximum (log2 units), sum of weights, 2 unused -- to `part`; prefill_merge_kernel combines them into `out`.
+  int n_split;
+  float* part;
 };
+constexpr int PF_PART_STRIDE = 132;  // floats per (row, share) record: 16-byte aligned rows
 
-// tcgen05 prefill kernel (k2b_prefill_t5.cu); same grid as the mma.sync kernel.  Needs q, out and the window 16-byte aligned.
+// tcgen05 prefill kernel (k2b_prefill_t5.cu); the mma.sync kernel's grid with x multiplied by n_split.  Needs q, out and the
+// window 16-byte aligned.  With n_split > 1 the merge kernel is launched behind it.
 int launch_prefill_t5(const PrefillParams& prm, dim3 grid, cudaStream_t s);
 
 }  // namespace bmxk

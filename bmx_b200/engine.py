@@ -210,7 +210,27 @@ class K2bLayerState:
             return None
         return K.k2b_prefill(self.pool, q, q_pos0, self.basis_f16, self.page_table, self.n_pages_dev, self.rope_cos, self.rope_sin,
                              self.k_win, self.v_win, self.tail_len_dev, self.v_lut, self.signs, self.sm_scale,
-                             self.workspace.view(torch.int32), out=out)
+                             self.workspace.view(torch.int32), out=out, n_split=self.prefill_split(q.shape[2]))
+
+    def prefill_split(self, n_q: int) -> int:
+        """Shares of the page walk per block of query positions.  One CTA per (block, KV head, sequence) fills the GPU only
+        for blocks of ~600 rows and more; below that the pages are shared out.  The kernel's time is (waves of CTAs) x (pages
+        per share + the CTA's set-up, about four pages' worth): the number of shares (16 at most) that makes it smallest.  With a
+        wave or more of whole walks the split is left alone (its partial records would only add traffic)."""
+        pp = 128 // self.geom.n_q_groups
+        ctas = -(-n_q // pp) * self.geom.h_kv * self.batch
+        n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
+        pages = self.committed // self.page
+        if ctas >= n_sm:  # a wave or more of whole walks: the shares' records and their merge would only add traffic
+            return 1
+        best, best_cost = 1, None
+        for s in range(1, 17):
+            if s > 1 and pages < 4 * s:
+                break
+            cost = -(-ctas * s // n_sm) * (-(-pages // s) + 4)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
 
     def seq_len(self) -> int:
         return self.committed + self.tail_len

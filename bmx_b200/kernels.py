@@ -276,9 +276,10 @@ def k2b_decode(pool: K2bPool, q: torch.Tensor, basis_f16: torch.Tensor, page_tab
 def k2b_prefill(pool: K2bPool, q: torch.Tensor, q_pos0: int, basis_f16: torch.Tensor, page_table: torch.Tensor, n_pages: torch.Tensor,
                 rope_cos: torch.Tensor, rope_sin: torch.Tensor, k_tail: torch.Tensor | None, v_tail: torch.Tensor | None,
                 tail_len: torch.Tensor | None, v_lut_dev: torch.Tensor, signs: torch.Tensor, sm_scale: float, status: torch.Tensor,
-                out: torch.Tensor | None = None, pos_offset: int = 0) -> torch.Tensor:
+                out: torch.Tensor | None = None, pos_offset: int = 0, n_split: int = 1) -> torch.Tensor:
     """Causal attention of q (batch, heads, n_q, 128) fp16, rows at positions q_pos0 .. q_pos0 + n_q - 1, over the paged k2b
-    cache and the fp16 window, page by page in shared memory (no dense K / V).  status: zeroed device int32 (>= 4)."""
+    cache and the fp16 window, page by page in shared memory (no dense K / V).  status: zeroed device int32 (>= 4).
+    n_split > 1 shares the pages of every block of query positions out over that many CTAs (few rows, long context)."""
     g = pool.geom
     _require_cuda(q, page_table, n_pages, status)
     batch, heads, n_q = q.shape[0], q.shape[1], q.shape[2]
@@ -291,9 +292,15 @@ def k2b_prefill(pool: K2bPool, q: torch.Tensor, q_pos0: int, basis_f16: torch.Te
     if out is None:
         out = torch.empty_like(q)
     assert out.dtype == torch.float16 and out.is_contiguous() and out.shape == q.shape
-    call("bmxk_k2b_prefill", ctypes.byref(g), _ptr(q), n_q, int(q_pos0), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
-         _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, _ptr(rope_cos), _ptr(rope_sin), int(pos_offset), _ptr(k_tail),
-         _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut_dev), _ptr(signs), ctypes.c_float(sm_scale), _ptr(status), _ptr(out), _stream())
+    args = (ctypes.byref(g), _ptr(q), n_q, int(q_pos0), _ptr(pool.pages), _ptr(pool.coefs), _ptr(basis_f16),
+            _ptr(page_table), page_table.stride(0), _ptr(n_pages), batch, _ptr(rope_cos), _ptr(rope_sin), int(pos_offset), _ptr(k_tail),
+            _ptr(v_tail), _ptr(tail_len), tail_cap, _ptr(v_lut_dev), _ptr(signs), ctypes.c_float(sm_scale), _ptr(status), _ptr(out))
+    if n_split <= 1:
+        call("bmxk_k2b_prefill", *args, _stream())
+        return out
+    nbytes = int(_lib.lib().bmxk_k2b_prefill_workspace_bytes(ctypes.byref(g), n_q, batch, int(n_split)))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)  # the caching allocator keeps it alive until the stream is through
+    call("bmxk_k2b_prefill_split", *args, int(n_split), _ptr(ws), nbytes, _stream())
     return out
 
 

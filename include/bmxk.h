@@ -160,6 +160,19 @@ int bmxk_k2b_prefill(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_p
                      const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
                      int32_t* status, void* out, void* stream);
 
+/* The same attention with the visible pages of every block of query positions shared out over n_split CTAs (1..64), which
+ * write partial records into `workspace` (bmxk_k2b_prefill_workspace_bytes; 16-byte aligned device memory) for a merge
+ * kernel launched behind them: for few query rows against a long context, where one CTA per block would walk every page
+ * alone and most SMs would idle (bmx's split-KV decode kernels do the same for a single row:
+ * src/bmx/cache/triton_dequant_attention.py:409-461).  n_split = 1 is bmxk_k2b_prefill; the split is the tcgen05 kernel's,
+ * where the mma.sync kernel runs (q or out not 16-byte aligned, or selected) n_split is taken as 1. */
+size_t bmxk_k2b_prefill_workspace_bytes(const bmxk_k2b_geom* g, int n_q, int batch, int n_split);
+int bmxk_k2b_prefill_split(const bmxk_k2b_geom* g, const void* q, int n_q, int64_t q_pos0, const void* pages, const void* coefs,
+                           const void* basis_f16, const int32_t* page_table, int table_stride, const int32_t* n_pages, int batch,
+                           const void* rope_cos, const void* rope_sin, int64_t pos_offset, const void* k_tail, const void* v_tail,
+                           const int32_t* tail_len, int tail_cap, const uint32_t* v_lut, const float* signs, float sm_scale,
+                           int32_t* status, void* out, int n_split, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Which kernel bmxk_k2b_prefill launches (process-wide; no counterpart in bmx).  0 (default): the tcgen05 kernel when q
  * and out are 16-byte aligned, else the mma.sync kernel; 1: always the mma.sync kernel.  Both give the same attention
  * within the path's tolerance. */

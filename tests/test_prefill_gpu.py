@@ -160,6 +160,50 @@ def test_dense_route_dequantizer_equals_dequantize_rotate_cast(dtype, page, rank
     assert torch.equal(vd[:, :, st.committed:], st.v_win[:, :, : st.tail_len].to(dtype))
 
 
+@pytest.mark.parametrize("n_split", [2, 3, 7, 16])
+def test_paged_prefill_split_pages_matches_oracle(n_split):
+    """Few query rows against many pages, the page walk of every block shared out over n_split CTAs + the merge kernel:
+    shares of unequal size, shares without any page (more shares than pages a block sees), the window in the last one."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200.engine import K2bLayerState
+
+    orig = K2bLayerState.prefill_split
+    K2bLayerState.prefill_split = lambda self, n_q: n_split
+    try:
+        for kw in (dict(n_seq=2, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=11, tail=70, n_q=40, seed=71),
+                   dict(n_seq=1, h_kv=1, G=8, rank=16, per_head=False, group=32, n_pages=5, tail=0, n_q=300, seed=72),
+                   dict(n_seq=1, h_kv=2, G=2, rank=32, per_head=True, group=128, n_pages=2, tail=150, n_q=1, seed=73)):
+            err, _, _ = _case(**kw)
+            assert err <= 1e-3, (n_split, kw, err)
+    finally:
+        K2bLayerState.prefill_split = orig
+
+
+def test_prefill_split_heuristic():
+    """One CTA per (block, head, sequence) unless that leaves SMs idle; then the number of shares that minimises
+    (waves of CTAs) x (pages per share + set-up), at least four pages per share."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from bmx_b200 import kernels as K
+    from bmx_b200.engine import K2bLayerState
+
+    dev = torch.device("cuda:0")
+    cos16, sin16 = rope_tables(512)
+    st = K2bLayerState(K.k2b_geom(8, 4, 128, 32, 64, 8), 1, 256, 64, dev, torch.from_numpy(cos16).to(dev), torch.from_numpy(sin16).to(dev))
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    st.committed = 128 * 128
+    assert st.prefill_split(8192) == 1 and st.prefill_split(32 * (n_sm // 8 + 1)) == 1      # a wave or more of whole walks
+    s32 = st.prefill_split(32)                                                              # 8 CTAs: as many shares as one wave takes
+    assert 8 * s32 <= n_sm and s32 == 16
+    s256 = st.prefill_split(256)                                                            # 64 CTAs
+    assert s256 > 1 and 64 * s256 <= n_sm or n_sm < 128
+    st.committed = 128 * 9
+    assert st.prefill_split(32) == 2            # 9 pages: shares of at least four
+    st.committed = 128 * 5
+    assert st.prefill_split(32) == 1
+
+
 def test_paged_prefill_long_context_rows_near_the_end(prefill_kernel):
     """A 16384-token context and 64 query rows at its end: every page is fully visible, the window partly."""
     err, _, _ = _case(n_seq=1, h_kv=2, G=4, rank=32, per_head=True, group=64, n_pages=128, tail=90, n_q=64, seed=53)
